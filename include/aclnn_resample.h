@@ -1,0 +1,165 @@
+/*
+ * aclnn_resample.h - the image-resampling entry points of hicann/ops-cv, served by hand-written CUDA kernels
+ * for NVIDIA B200 (sm_100a).
+ *
+ * Every operator keeps the reference's two-phase protocol (docs/zh/context/two_phase_api.md):
+ *
+ *   1. aclnnXxxGetWorkspaceSize(...) validates the arguments, chooses the launch configuration, and returns
+ *      the number of device bytes of workspace the caller must provide plus an executor. No GPU work happens.
+ *   2. aclnnXxx(workspace, workspaceSize, executor, stream) enqueues the kernels on `stream` (a cudaStream_t)
+ *      and returns without synchronising. The executor is consumed: it must not be passed to a second call.
+ *
+ * Argument meaning, dtype / format rules, the order of the checks and the status codes follow the reference
+ * files cited at each declaration (paths relative to the reference repository). Arithmetic follows the
+ * reference's "arch35" SIMT kernels: all interpolation is done in fp32 and rounded once to the storage dtype.
+ * There is no CPU fallback: without a CUDA device the second-phase call returns ACLNN_ERR_RUNTIME_ERROR.
+ *
+ * Supported storage dtypes: ACL_FLOAT, ACL_FLOAT16, ACL_BF16. (The reference routes ACL_DOUBLE / ACL_UINT8 to
+ * AI-CPU kernels; those dtypes are rejected here with ACLNN_ERR_PARAM_INVALID.)
+ */
+#ifndef ACLNN_RESAMPLE_H
+#define ACLNN_RESAMPLE_H
+
+#include "opscv_acl.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- UpsampleNearest2d ---------------------------------------------------------------------------------
+ * Replaces image/resize_nearest_neighbor_v2/op_api/aclnn_upsample_nearest_2d.h:49-80
+ * (implementation aclnn_upsample_nearest_2d.cpp:247-311; kernel resize_nearest_neighbor_v2_simt.h:104-155).
+ * self/out: 4-D, NCHW or NHWC (same format, same dtype), out H,W == outputSize. src = min(floor(dst*in/out), in-1).
+ */
+ACLNN_API aclnnStatus aclnnUpsampleNearest2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                             aclTensor* out, uint64_t* workspaceSize,
+                                                             aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearest2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                             const aclrtStream stream);
+
+/* Replaces image/upsample_nearest3d/op_host/op_api/aclnn_upsample_nearest_2d_v2.h:38-55 (implementation
+ * aclnn_upsample_nearest_2d_v2.cpp:316-400). Same as above with user scales: when scalesH/W > 0 the source
+ * index uses 1/scales instead of in/out. */
+ACLNN_API aclnnStatus aclnnUpsampleNearest2dV2GetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                               float scalesH, float scalesW, aclTensor* out,
+                                                               uint64_t* workspaceSize, aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearest2dV2(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                               aclrtStream stream);
+
+/* Replaces image/upsample_nearest2d_grad/op_host/op_api/aclnn_upsample_nearest_2d_backward.h:40-59
+ * (implementation aclnn_upsample_nearest_2d_backward.cpp:320-388; kernel
+ * resize_nearest_neighbor_v2_grad_simt_determine.h:79-118). inputSize = {N,C,H,W} (or {N,H,W,C} for NHWC) of
+ * gradInput; deterministic gather with fp32 accumulation. */
+ACLNN_API aclnnStatus aclnnUpsampleNearest2dBackwardGetWorkspaceSize(const aclTensor* gradOut,
+                                                                     const aclIntArray* outputSize,
+                                                                     const aclIntArray* inputSize, double scalesH,
+                                                                     double scalesW, aclTensor* gradInput,
+                                                                     uint64_t* workspaceSize,
+                                                                     aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearest2dBackward(void* workspace, uint64_t workspaceSize,
+                                                     aclOpExecutor* executor, aclrtStream stream);
+
+/* ---- UpsampleBilinear2d --------------------------------------------------------------------------------
+ * Replaces image/upsample_bilinear2d/op_host/op_api/aclnn_upsample_bilinear_2d.h:24-34 (implementation
+ * aclnn_upsample_bilinear_2d.cpp:384-467; kernel resize_bilinear_v2_simt_nchw.h:84-146 / _simt_nhwc.h:88-151).
+ * Null self/out returns ACLNN_ERR_INNER_NULLPTR (561103) as the reference does (:175). */
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                              const bool alignCorners, const double scalesH,
+                                                              const double scalesW, aclTensor* out,
+                                                              uint64_t* workspaceSize, aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                              aclrtStream stream);
+
+/* Replaces image/resize_bilinear_v2_grad/op_api/aclnn_upsample_bilinear_2d_backward.h:23-32 (implementation
+ * aclnn_upsample_bilinear_2d_backward.cpp:226-309; kernels resize_bilinear_v2_grad_simt.h:107-152 and
+ * resize_bilinear_v2_grad_simt_determine.h:56-123). out dtype == gradOut dtype, or any supported dtype when
+ * gradOut is fp32. */
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dBackwardGetWorkspaceSize(const aclTensor* gradOut,
+                                                                      const aclIntArray* outputSize,
+                                                                      const aclIntArray* inputSize,
+                                                                      bool alignCorners, double scalesH,
+                                                                      double scalesW, aclTensor* out,
+                                                                      uint64_t* workspaceSize,
+                                                                      aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dBackward(void* workspace, uint64_t workspaceSize,
+                                                      aclOpExecutor* executor, aclrtStream stream);
+
+/* Replaces image/upsample_bilinear2d_grad/op_host/op_api/aclnn_upsample_bilinear_2d_backward_v2.h:33-58
+ * (implementation aclnn_upsample_bilinear_2d_backward_v2.cpp:354-446). Same kernels as above. */
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dBackwardV2GetWorkspaceSize(const aclTensor* gradOut,
+                                                                        const aclIntArray* outputSize,
+                                                                        const aclIntArray* inputSize,
+                                                                        bool alignCorners, double scalesH,
+                                                                        double scalesW, aclTensor* out,
+                                                                        uint64_t* workspaceSize,
+                                                                        aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dBackwardV2(void* workspace, uint64_t workspaceSize,
+                                                        aclOpExecutor* executor, aclrtStream stream);
+
+/* ---- UpsampleBicubic2dAA -------------------------------------------------------------------------------
+ * Replaces image/upsample_bicubic2d_aa/op_host/op_api/aclnn_upsample_bicubic2d_aa.h:40-58 (implementation
+ * aclnn_upsample_bicubic2d_aa.cpp:164-229; kernel upsample_bicubic2d_aa_simt_base.h:31-127; scale/support
+ * upsample_bicubic2d_aa_tiling_arch35.cpp:139-168). NCHW (or ND) only; Keys cubic with a = -0.5, support
+ * 2*scale when down-scaling. */
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const aclIntArray* outputSize,
+                                                               const bool alignCorners, const double scalesH,
+                                                               const double scalesW, aclTensor* out,
+                                                               uint64_t* workspaceSize, aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAA(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                               aclrtStream stream);
+
+/* Replaces image/upsample_bicubic2d_aa_grad/op_host/op_api/aclnn_upsample_bicubic2d_aa_grad.h:39-58
+ * (implementation aclnn_upsample_bicubic2d_aa_grad.cpp:183-232; kernels upsample_bicubic2d_aa_grad_simt_base.h:32-102
+ * and upsample_bicubic2d_aa_grad_simt_base_deter.h:30-122). */
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOutput,
+                                                                   const aclIntArray* outputSize,
+                                                                   const aclIntArray* inputSize, bool alignCorners,
+                                                                   double scalesH, double scalesW, aclTensor* out,
+                                                                   uint64_t* workspaceSize,
+                                                                   aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGrad(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                   aclrtStream stream);
+
+/* ---- GridSampler2D -------------------------------------------------------------------------------------
+ * Replaces image/grid_sample/op_api/aclnn_grid_sampler2d.h:53-82 (implementation aclnn_grid_sampler2d.cpp:266-340;
+ * arithmetic image/grid_sampler2_d/op_kernel/arch35/grid_sampler2_d_simt.h:106-215,303-514).
+ * input (N,C,H,W), grid (N,Ho,Wo,2), out (N,C,Ho,Wo), all one dtype. interpolationMode 0 bilinear, 1 nearest,
+ * 2 bicubic; paddingMode 0 zeros, 1 border, 2 reflection. */
+ACLNN_API aclnnStatus aclnnGridSampler2DGetWorkspaceSize(const aclTensor* input, const aclTensor* grid,
+                                                         int64_t interpolationMode, int64_t paddingMode,
+                                                         bool alignCorners, aclTensor* out, uint64_t* workspaceSize,
+                                                         aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnGridSampler2D(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                         aclrtStream stream);
+
+/* Replaces image/grid_sampler2_d_grad/op_host/op_api/aclnn_grid_sampler2d_backward.h:58-91 (implementation
+ * aclnn_grid_sampler2d_backward.cpp:214-357; arithmetic image/grid_sampler3_d_grad/op_kernel/arch35/
+ * grid_sampler3_d_grad_simt_base.h:51-184 and image/grid_sampler2_d_grad/op_kernel/arch35/
+ * grid_sampler2_d_grad_simt.h:64-144,235-290). outputMask = {want inputGrad, want gridGrad}; a NULL mask or
+ * {false,false} is a successful no-op. Atomic accumulation by default; bit-reproducible when
+ * ACL_OPT_DETERMINISTIC is set. Bilinear and nearest interpolation; bicubic returns ACLNN_ERR_PARAM_INVALID. */
+ACLNN_API aclnnStatus aclnnGridSampler2DBackwardGetWorkspaceSize(const aclTensor* gradOutput, const aclTensor* input,
+                                                                 const aclTensor* grid, int64_t interpolationMode,
+                                                                 int64_t paddingMode, bool alignCorners,
+                                                                 const aclBoolArray* outputMask, aclTensor* inputGrad,
+                                                                 aclTensor* gridGrad, uint64_t* workspaceSize,
+                                                                 aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnGridSampler2DBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                 aclrtStream stream);
+
+/* ---- Diagnostics (no counterpart in the reference) ------------------------------------------------------
+ * Build on the device, with the same kernels the operators use, the per-axis index / weight tables and copy
+ * them to HOST arrays, so that tests can compare the coordinate arithmetic bit for bit with a CPU statement of
+ * the reference formulas. `kind`: 0 nearest forward source index (i0 = src[outSize]);
+ * 1 nearest backward ranges (i0 = start[inSize], i1 = end[inSize]);
+ * 2 bilinear forward (i0 = lo[outSize], i1 = hi[outSize], f0 = delta[outSize]);
+ * 3 bicubic-AA forward (i0 = xmin[outSize], i1 = xsize[outSize], f0 = weights[outSize * taps], taps returned
+ *   through *tapsOut; pass f0 == NULL to query taps only).
+ * Synchronises the device. Returns 0 or an aclnn status. */
+ACLNN_API aclnnStatus opscvDebugAxisTable(int32_t kind, int64_t inSize, int64_t outSize, int32_t alignCorners,
+                                          float userScale, int32_t* i0, int32_t* i1, float* f0, int32_t* tapsOut);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ACLNN_RESAMPLE_H */

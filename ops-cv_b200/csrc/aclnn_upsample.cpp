@@ -1,0 +1,1085 @@
+// First- and second-phase entry points of the Upsample{Nearest,Bilinear,Bicubic2dAA} family. The first phase
+// mirrors the reference's CheckParams functions (same checks, same order, same status codes; file:line cited at
+// each function) and then freezes a launch plan into the executor: table builders, the resampling kernel, and
+// the staging copies for strided views. Scales are computed here, on the host, with the expressions of the
+// reference's arch35 tiling code.
+#include <cmath>
+
+#include "host_common.h"
+
+using namespace opscv;
+
+namespace {
+
+struct Geom {
+    int64_t n = 0, c = 0, h = 0, w = 0;
+};
+
+// View dims are [N,C,H,W] for NCHW / ND and [N,H,W,C] for NHWC.
+Geom GeomOf(const aclTensor* t)
+{
+    Geom g;
+    if (t->format == ACL_FORMAT_NHWC) {
+        g.n = t->dims[0];
+        g.h = t->dims[1];
+        g.w = t->dims[2];
+        g.c = t->dims[3];
+    } else {
+        g.n = t->dims[0];
+        g.c = t->dims[1];
+        g.h = t->dims[2];
+        g.w = t->dims[3];
+    }
+    return g;
+}
+
+// common/stub/op_api/aclnn_kernels/common/op_error_check.h:112-141 (CheckNCDimValid)
+bool CheckNCDimValid(const aclTensor* self, const aclTensor* out, const char* api)
+{
+    if (self->format != ACL_FORMAT_NCHW && self->format != ACL_FORMAT_NHWC) {
+        Fail(ACLNN_ERR_PARAM_INVALID, "%s: input and output format only support [NCHW, NHWC]", api);
+        return false;
+    }
+    const int cDim = self->format == ACL_FORMAT_NCHW ? 1 : 3;
+    if (self->dims[0] != out->dims[0] || self->dims[cDim] != out->dims[cDim]) {
+        Fail(ACLNN_ERR_PARAM_INVALID, "%s: N %ld/%ld or C %ld/%ld of input and output differ", api,
+             (long)self->dims[0], (long)out->dims[0], (long)self->dims[cDim], (long)out->dims[cDim]);
+        return false;
+    }
+    return true;
+}
+
+bool FitsInt32(const Geom& g) { return g.h <= INT32_MAX && g.w <= INT32_MAX && g.n >= 0 && g.c >= 0; }
+
+aclnnStatus EmptySuccess(const char* api, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    *workspaceSize = 0;
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+Shape4 MakeShape(const Geom& in, const Geom& out)
+{
+    Shape4 s;
+    s.n = in.n;
+    s.c = in.c;
+    s.hin = static_cast<int32_t>(in.h);
+    s.win = static_cast<int32_t>(in.w);
+    s.hout = static_cast<int32_t>(out.h);
+    s.wout = static_cast<int32_t>(out.w);
+    return s;
+}
+
+struct TableAlloc {
+    uint64_t off[4]; // workspace offsets, meaning depends on the table type
+};
+
+// ---- UpsampleNearest2d ----------------------------------------------------------------------------------------
+// image/resize_nearest_neighbor_v2/op_host/arch35/resize_nearest_neighbor_v2_tiling_base.cpp:251-262
+float NearestScale(int64_t in, int64_t out, float userScale)
+{
+    return userScale > 0.0f ? 1.0f / userScale : static_cast<float>(in) / static_cast<float>(out);
+}
+
+// image/resize_nearest_neighbor_v2/op_api/aclnn_upsample_nearest_2d.cpp:187-216 (CheckParams), :74-213 helpers
+aclnnStatus CheckNearestFwd(const char* api, const aclTensor* self, const aclIntArray* outputSize,
+                            const aclTensor* out)
+{
+    if (!DtypeSupported(self->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(self->dtype));
+    }
+    if (self->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from self dtype %s", api, DtypeName(out->dtype),
+                    DtypeName(self->dtype));
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: outputSize must have 2 values, got %zu", api, outputSize->v.size());
+    }
+    if (self->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self must be 4-D, got %zu-D", api, self->dims.size());
+    }
+    if (self->dims[2] == 0 || self->dims[3] == 0 || outputSize->v[0] == 0 || outputSize->v[1] == 0) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input and output sizes must be greater than 0", api);
+    }
+    if (self->dims[1] == 0) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: non-empty 4-D data tensor expected", api);
+    }
+    if (self->format != ACL_FORMAT_NCHW && self->format != ACL_FORMAT_NHWC) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format %s of input not supported", api, FormatName(self->format));
+    }
+    if (self->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format of input (%s) and output (%s) must be equal", api,
+                    FormatName(self->format), FormatName(out->format));
+    }
+    if (out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out must be 4-D, got %zu-D", api, out->dims.size());
+    }
+    if (!CheckNCDimValid(self, out, api)) {
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    const Geom go = GeomOf(out);
+    if (outputSize->v[0] != go.h || outputSize->v[1] != go.w) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: expected output size (H: %ld, W: %ld) but out tensor has (H: %ld, W: %ld)",
+                    api, (long)outputSize->v[0], (long)outputSize->v[1], (long)go.h, (long)go.w);
+    }
+    if (!FitsInt32(GeomOf(self)) || !FitsInt32(go)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
+    }
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTensor* out, float userScaleH,
+                           float userScaleW, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const Geom gi = GeomOf(self), go = GeomOf(out);
+    const BufRef x = StageInput(self, ws, ex);
+    const BufRef y = StageOutput(out, ws);
+    const Shape4 sh = MakeShape(gi, go);
+    const Dt dt = ToDt(self->dtype);
+    const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
+    const AxisGeom ah{sh.hin, sh.hout, NearestScale(gi.h, go.h, userScaleH)};
+    const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, go.w, userScaleW)};
+    const uint64_t offH = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.hout));
+    const uint64_t offW = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.wout));
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        const NearestAxis th{reinterpret_cast<int32_t*>(w + offH)}, tw{reinterpret_cast<int32_t*>(w + offW)};
+        cudaError_t e = BuildNearestFwdTables(ah, aw, th, tw, s);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        return NearestFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, s);
+    });
+    FinishOutput(out, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+// ---- UpsampleNearest2dBackward --------------------------------------------------------------------------------
+// image/upsample_nearest2d_grad/op_host/op_api/aclnn_upsample_nearest_2d_backward.cpp:147-166 (CheckParams)
+aclnnStatus CheckBackwardCommon(const char* api, const aclTensor* gradOut, const aclIntArray* outputSize,
+                                const aclIntArray* inputSize, const aclTensor* gradInput, bool allowF32ToAny)
+{
+    if (!DtypeSupported(gradOut->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(gradOut->dtype));
+    }
+    if (allowF32ToAny && gradOut->dtype == ACL_FLOAT) {
+        if (!DtypeSupported(gradInput->dtype)) {
+            return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s not supported", api, DtypeName(gradInput->dtype));
+        }
+    } else if (gradInput->dtype != gradOut->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from gradOut dtype %s", api,
+                    DtypeName(gradInput->dtype), DtypeName(gradOut->dtype));
+    }
+    return ACLNN_SUCCESS;
+    (void)outputSize;
+    (void)inputSize;
+}
+
+aclnnStatus CheckBackwardShape(const char* api, const aclTensor* gradOut, const aclIntArray* outputSize,
+                               const aclIntArray* inputSize, const aclTensor* gradInput, bool checkOutShape)
+{
+    if (gradOut->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut must be 4-D, got %zu-D", api, gradOut->dims.size());
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: output_size must have 2 values, got %zu", api, outputSize->v.size());
+    }
+    if (inputSize->v.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input_size must have 4 values, got %zu", api, inputSize->v.size());
+    }
+    if (gradInput->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out must be 4-D, got %zu-D", api, gradInput->dims.size());
+    }
+    const bool nhwc = gradOut->format == ACL_FORMAT_NHWC;
+    const int64_t outH = outputSize->v[0], outW = outputSize->v[1];
+    const int64_t batch = inputSize->v[0];
+    const int64_t channels = nhwc ? inputSize->v[3] : inputSize->v[1];
+    const int64_t inH = nhwc ? inputSize->v[1] : inputSize->v[2];
+    const int64_t inW = nhwc ? inputSize->v[2] : inputSize->v[3];
+    if (!(inH > 0 && inW > 0 && outH > 0 && outW > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID,
+                    "%s: input and output sizes should be greater than 0, got input (H: %ld, W: %ld) output (H: %ld, W: %ld)",
+                    api, (long)inH, (long)inW, (long)outH, (long)outW);
+    }
+    const int64_t fullOut[4] = {batch, nhwc ? outH : channels, nhwc ? outW : outH, nhwc ? channels : outW};
+    const int64_t fullIn[4] = {batch, nhwc ? inH : channels, nhwc ? inW : inH, nhwc ? channels : inW};
+    for (int i = 0; i < 4; ++i) {
+        if (gradOut->dims[i] != fullOut[i]) {
+            return Fail(ACLNN_ERR_PARAM_INVALID, "%s: expected grad_output.size(%d) = %ld but got %ld", api, i,
+                        (long)fullOut[i], (long)gradOut->dims[i]);
+        }
+    }
+    if (checkOutShape) {
+        for (int i = 0; i < 4; ++i) {
+            if (gradInput->dims[i] != fullIn[i]) {
+                return Fail(ACLNN_ERR_PARAM_INVALID, "%s: expected out.size(%d) = %ld but got %ld", api, i,
+                            (long)fullIn[i], (long)gradInput->dims[i]);
+            }
+        }
+    }
+    if (inH > INT32_MAX || inW > INT32_MAX || outH > INT32_MAX || outW > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
+    }
+    return ACLNN_SUCCESS;
+}
+
+// ---- UpsampleBilinear2d ---------------------------------------------------------------------------------------
+// image/resize_bilinear_v2/op_host/arch35/resize_bilinear_v2_tiling_arch35.cpp:175-243
+float BilinearScale(int64_t in, int64_t out, bool align, float userScale)
+{
+    if (!align) {
+        return userScale > 0.0f ? 1.0f / userScale : static_cast<float>(in) / static_cast<float>(out);
+    }
+    float s = static_cast<float>(in) / static_cast<float>(out);
+    if (out > 1) {
+        s = static_cast<float>(in - 1) / static_cast<float>(out - 1);
+    }
+    return s;
+}
+
+// image/resize_bilinear_v2_grad/op_host/arch35/resize_bilinear_v2_grad_tiling_arch35.cpp:352-384 (scatter form)
+float BilinearGradScale(int64_t in, int64_t out, bool align, float userScale)
+{
+    if (align) {
+        return out > 1 ? static_cast<float>(in - 1) / static_cast<float>(out - 1) : 0.0f;
+    }
+    return userScale > 0.0f ? 1.0f / userScale : static_cast<float>(in) / static_cast<float>(out);
+}
+
+struct LerpOffsets {
+    uint64_t lo, hi, delta;
+};
+LerpOffsets AllocLerp(WsPlan& ws, int64_t n)
+{
+    LerpOffsets o;
+    o.lo = ws.Alloc(4 * static_cast<uint64_t>(n));
+    o.hi = ws.Alloc(4 * static_cast<uint64_t>(n));
+    o.delta = ws.Alloc(4 * static_cast<uint64_t>(n));
+    return o;
+}
+LerpAxis LerpAt(char* w, const LerpOffsets& o)
+{
+    return LerpAxis{reinterpret_cast<int32_t*>(w + o.lo), reinterpret_cast<int32_t*>(w + o.hi),
+                    reinterpret_cast<float*>(w + o.delta)};
+}
+struct RangeOffsets {
+    uint64_t start, end;
+};
+RangeOffsets AllocRange(WsPlan& ws, int64_t n)
+{
+    RangeOffsets o;
+    o.start = ws.Alloc(4 * static_cast<uint64_t>(n));
+    o.end = ws.Alloc(4 * static_cast<uint64_t>(n));
+    return o;
+}
+RangeAxis RangeAt(char* w, const RangeOffsets& o)
+{
+    return RangeAxis{reinterpret_cast<int32_t*>(w + o.start), reinterpret_cast<int32_t*>(w + o.end)};
+}
+
+aclnnStatus PlanCopy(const char* api, const aclTensor* src, const aclTensor* dst, uint64_t* workspaceSize,
+                     aclOpExecutor** executor)
+{
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef x = StageInput(src, ws, ex);
+    const BufRef y = StageOutput(dst, ws);
+    const uint64_t bytes = static_cast<uint64_t>(Numel(src)) * ElemSize(src->dtype);
+    ex->steps.push_back([=](char* w, cudaStream_t s) { return CopyBytes(y.At(w), x.At(w), bytes, s); });
+    FinishOutput(dst, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+// Shared by aclnnUpsampleBilinear2dBackward and ...BackwardV2 (both reach ResizeBilinearV2Grad on arch35).
+aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const aclIntArray* inputSize, bool alignCorners,
+                            double scalesH, double scalesW, aclTensor* out, uint64_t* workspaceSize,
+                            aclOpExecutor** executor)
+{
+    const Geom gg = GeomOf(gradOut), gi = GeomOf(out);
+    (void)inputSize;
+    if (gg.h == gi.h && gg.w == gi.w && gradOut->dtype == out->dtype) {
+        // same spatial size: plain copy (aclnn_upsample_bilinear_2d_backward.cpp:252,299-301; all-copy tiling key)
+        return PlanCopy(api, gradOut, out, workspaceSize, executor);
+    }
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef g = StageInput(gradOut, ws, ex);
+    const BufRef y = StageOutput(out, ws);
+    Shape4 sh = MakeShape(gi, gg); // hin/win = grad_input extent, hout/wout = grads extent
+    const Dt dtIn = ToDt(gradOut->dtype), dtOut = ToDt(out->dtype);
+    const Layout lay = gradOut->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
+    const AxisGeom ah{sh.hin, sh.hout, BilinearGradScale(gi.h, gg.h, alignCorners, static_cast<float>(scalesH))};
+    const AxisGeom aw{sh.win, sh.wout, BilinearGradScale(gi.w, gg.w, alignCorners, static_cast<float>(scalesW))};
+    const bool halfPixel = !alignCorners;
+    const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
+    // The atomic scatter is used only on request (opscvSetBackwardAlgo(1)) and never in deterministic mode or
+    // when the output dtype differs (the reference's IsMatchSimtDetermine, ..._grad_tiling_arch35.cpp:296-299).
+    const bool atomic = GetBackwardAlgo() == 1 && GetDeterministic() == 0 && dtIn == dtOut;
+    if (atomic) {
+        const int64_t elems = gi.n * gi.c * gi.h * gi.w;
+        const bool needAcc = dtOut != Dt::F32;
+        const uint64_t accOff = needAcc ? ws.Alloc(static_cast<uint64_t>(elems) * 4) : 0;
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
+            cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 1, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            float* acc = needAcc ? reinterpret_cast<float*>(w + accOff) : static_cast<float*>(y.At(w));
+            return BilinearBwdAtomic(dtIn, dtOut, lay, g.At(w), y.At(w), acc, sh, th, tw, s);
+        });
+    } else {
+        const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
+            const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
+            cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 1, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            e = BuildLerpBwdRanges(ah, aw, th, tw, qh, qw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, s);
+        });
+    }
+    FinishOutput(out, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+// ---- UpsampleBicubic2dAA --------------------------------------------------------------------------------------
+struct AAGeom {
+    float scale, inv, support;
+    int32_t taps;
+};
+// image/upsample_bicubic2d_aa/op_host/upsample_bicubic2d_aa_tiling_arch35.cpp:139-168 (forward: originalScale is the
+// API's scales value) and image/upsample_bicubic2d_aa_grad/op_host/upsample_bicubic2d_aa_grad_tiling_arch35.cpp:158-183
+// (backward: the API passes float(1/scales), used as the scale itself). `in` = forward input extent.
+AAGeom MakeAAGeom(int64_t in, int64_t out, bool align, double userScale, bool backward)
+{
+    AAGeom g;
+    if (align) {
+        g.scale = out > 1 ? static_cast<float>(in - 1) / static_cast<float>(out - 1) : 0.0f;
+    } else if (!backward) {
+        const float original = userScale > 0 ? static_cast<float>(userScale) : 0.0f;
+        g.scale = original > 0.0f ? 1.0f / original : static_cast<float>(in) / static_cast<float>(out);
+    } else {
+        const float original = userScale > 0 ? static_cast<float>(1.0 / userScale) : 0.0f;
+        g.scale = original > 0.0f ? original : static_cast<float>(in) / static_cast<float>(out);
+    }
+    g.inv = g.scale >= 1.0f ? 1.0f / g.scale : 1.0f;
+    g.support = g.scale >= 1.0f ? 2.0f * g.scale : 2.0f;
+    // window = floor(c + s + 0.5) - floor(c - s + 0.5) <= 2s + 1
+    int64_t taps = static_cast<int64_t>(std::floor(2.0 * static_cast<double>(g.support))) + 2;
+    taps = taps > in ? in : taps;
+    g.taps = static_cast<int32_t>(taps < 1 ? 1 : taps);
+    return g;
+}
+
+struct AAOffsets {
+    uint64_t xmin, xsize, w;
+};
+AAOffsets AllocAA(WsPlan& ws, int64_t n, int32_t taps)
+{
+    AAOffsets o;
+    o.xmin = ws.Alloc(4 * static_cast<uint64_t>(n));
+    o.xsize = ws.Alloc(4 * static_cast<uint64_t>(n));
+    o.w = ws.Alloc(4 * static_cast<uint64_t>(n) * static_cast<uint64_t>(taps));
+    return o;
+}
+AAAxis AAAt(char* w, const AAOffsets& o, int32_t taps)
+{
+    return AAAxis{reinterpret_cast<int32_t*>(w + o.xmin), reinterpret_cast<int32_t*>(w + o.xsize),
+                  reinterpret_cast<float*>(w + o.w), taps};
+}
+
+bool AAIsCopy(const Geom& in, const Geom& out, const AAGeom& h, const AAGeom& w)
+{
+    // upsample_bicubic2d_aa_tiling_arch35.cpp:115-125
+    return out.h == in.h && out.w == in.w && std::fabs(h.scale - 1.0f) < 1e-6f && std::fabs(w.scale - 1.0f) < 1e-6f;
+}
+
+} // namespace
+
+extern "C" {
+
+// ===============================================================================================================
+aclnnStatus aclnnUpsampleNearest2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                   aclTensor* out, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleNearest2d";
+    if (self == nullptr || outputSize == nullptr || out == nullptr || workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    const aclnnStatus st = CheckNearestFwd(api, self, outputSize, out);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    if (IsEmpty(self) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    // scales = nullptr in the reference call (aclnn_upsample_nearest_2d.cpp:271-272)
+    return PlanNearestFwd(api, self, out, 0.0f, 0.0f, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleNearest2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                   const aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearest2d", workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus aclnnUpsampleNearest2dV2GetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                     float scalesH, float scalesW, aclTensor* out,
+                                                     uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleNearest2dV2";
+    // aclnn_upsample_nearest_2d_v2.cpp:324-333: null check, then the empty shortcut, then CheckParams
+    if (self == nullptr || out == nullptr || workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (IsEmpty(self) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    if (outputSize == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: outputSize is null", api);
+    }
+    const aclnnStatus st = CheckNearestFwd(api, self, outputSize, out);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    return PlanNearestFwd(api, self, out, scalesH, scalesW, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleNearest2dV2(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                     aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearest2dV2", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+aclnnStatus aclnnUpsampleNearest2dBackwardGetWorkspaceSize(const aclTensor* gradOut, const aclIntArray* outputSize,
+                                                           const aclIntArray* inputSize, double scalesH,
+                                                           double scalesW, aclTensor* gradInput,
+                                                           uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleNearest2dBackward";
+    if (gradOut == nullptr || outputSize == nullptr || inputSize == nullptr || gradInput == nullptr ||
+        workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    // order: dtype, shape, N/C, elements (aclnn_upsample_nearest_2d_backward.cpp:147-166)
+    aclnnStatus st = CheckBackwardCommon(api, gradOut, outputSize, inputSize, gradInput, false);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    if (gradOut->dims.size() != 4 || outputSize->v.size() != 2 || inputSize->v.size() != 4 ||
+        gradInput->dims.size() != 4) {
+        return CheckBackwardShape(api, gradOut, outputSize, inputSize, gradInput, false);
+    }
+    if (!CheckNCDimValid(gradInput, gradOut, api)) {
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (gradInput->format != gradOut->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut and gradInput must have the same format", api);
+    }
+    st = CheckBackwardShape(api, gradOut, outputSize, inputSize, gradInput, true);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    if (IsEmpty(gradOut) || IsEmpty(gradInput)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    const Geom gg = GeomOf(gradOut), gi = GeomOf(gradInput);
+    if (gg.h == gi.h && gg.w == gi.w) {
+        // all-copy schedule (resize_nearest_neighbor_v2_grad_tiling_base.cpp:449-452)
+        return PlanCopy(api, gradOut, gradInput, workspaceSize, executor);
+    }
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef g = StageInput(gradOut, ws, ex);
+    const BufRef y = StageOutput(gradInput, ws);
+    const Shape4 sh = MakeShape(gi, gg);
+    const Dt dt = ToDt(gradOut->dtype);
+    const Layout lay = gradOut->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
+    // scales reach the tiling as floats (aclnn_upsample_nearest_2d_backward.cpp:351-354)
+    const AxisGeom ah{sh.hin, sh.hout, NearestScale(gi.h, gg.h, static_cast<float>(scalesH))};
+    const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, gg.w, static_cast<float>(scalesW))};
+    const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        const RangeAxis th = RangeAt(w, rh), tw = RangeAt(w, rw);
+        cudaError_t e = BuildNearestBwdTables(ah, aw, th, tw, s);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        return NearestBwd(dt, lay, g.At(w), y.At(w), sh, th, tw, s);
+    });
+    FinishOutput(gradInput, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnUpsampleNearest2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                           aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearest2dBackward", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/upsample_bilinear2d/op_host/op_api/aclnn_upsample_bilinear_2d.cpp:170-195 (CheckParams)
+aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                    const bool alignCorners, const double scalesH,
+                                                    const double scalesW, aclTensor* out, uint64_t* workspaceSize,
+                                                    aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleBilinear2d";
+    if (self == nullptr || out == nullptr) {
+        return Fail(ACLNN_ERR_INNER_NULLPTR, "%s: self or out is null", api); // sic: 561103 (:175)
+    }
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (!DtypeSupported(self->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(self->dtype));
+    }
+    if (self->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from self dtype %s", api, DtypeName(out->dtype),
+                    DtypeName(self->dtype));
+    }
+    if (self->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format of input (%s) and output (%s) must be equal", api,
+                    FormatName(self->format), FormatName(out->format));
+    }
+    if (self->format != ACL_FORMAT_NCHW && self->format != ACL_FORMAT_NHWC) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format %s not supported", api, FormatName(self->format));
+    }
+    if (self->dims.size() != 4 || out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self and out must be 4-D", api);
+    }
+    if (!CheckNCDimValid(self, out, api)) {
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (scalesW < 0 || scalesH < 0) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales cannot be negative (w %f, h %f)", api, scalesW, scalesH);
+    }
+    if (outputSize == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: outputSize must not be null", api);
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: outputSize size must be 2, got %zu", api, outputSize->v.size());
+    }
+    const Geom gi = GeomOf(self), go = GeomOf(out);
+    if (outputSize->v[0] != go.h || outputSize->v[1] != go.w) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: expected output size (H: %ld, W: %ld) but out tensor has (H: %ld, W: %ld)",
+                    api, (long)outputSize->v[0], (long)outputSize->v[1], (long)go.h, (long)go.w);
+    }
+    if (IsEmpty(self) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    if (!FitsInt32(gi) || !FitsInt32(go)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
+    }
+    if (gi.h == go.h && gi.w == go.w) {
+        // all-copy schedule (resize_bilinear_v2_tiling_arch35.cpp:245-252)
+        return PlanCopy(api, self, out, workspaceSize, executor);
+    }
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef x = StageInput(self, ws, ex);
+    const BufRef y = StageOutput(out, ws);
+    const Shape4 sh = MakeShape(gi, go);
+    const Dt dt = ToDt(self->dtype);
+    const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
+    // scales reach the tiling as floats (aclnn_upsample_bilinear_2d.cpp:413)
+    const AxisGeom ah{sh.hin, sh.hout, BilinearScale(gi.h, go.h, alignCorners, static_cast<float>(scalesH))};
+    const AxisGeom aw{sh.win, sh.wout, BilinearScale(gi.w, go.w, alignCorners, static_cast<float>(scalesW))};
+    const bool halfPixel = !alignCorners; // resize_bilinear_v2.cpp:99
+    const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
+        cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 0, th, tw, s);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        return BilinearFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, s);
+    });
+    FinishOutput(out, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnUpsampleBilinear2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                    aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBilinear2d", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/resize_bilinear_v2_grad/op_api/aclnn_upsample_bilinear_2d_backward.cpp:195-224 (CheckParams):
+// null, shape, dtype, elements, N/C, format
+aclnnStatus aclnnUpsampleBilinear2dBackwardGetWorkspaceSize(const aclTensor* gradOut, const aclIntArray* outputSize,
+                                                            const aclIntArray* inputSize, bool alignCorners,
+                                                            double scalesH, double scalesW, aclTensor* out,
+                                                            uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleBilinear2dBackward";
+    if (gradOut == nullptr || outputSize == nullptr || inputSize == nullptr || out == nullptr ||
+        workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    aclnnStatus st = CheckBackwardShape(api, gradOut, outputSize, inputSize, out, true);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    st = CheckBackwardCommon(api, gradOut, outputSize, inputSize, out, true);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    if (!CheckNCDimValid(gradOut, out, api)) {
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (gradOut->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut and out must have the same format", api);
+    }
+    if (IsEmpty(gradOut)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    return PlanBilinearBwd(api, gradOut, inputSize, alignCorners, scalesH, scalesW, out, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleBilinear2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                            aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBilinear2dBackward", workspace, workspaceSize, executor, stream);
+}
+
+// image/upsample_bilinear2d_grad/op_host/op_api/aclnn_upsample_bilinear_2d_backward_v2.cpp:190-213 (CheckParams):
+// null, shape, format, elements, N/C, dtype
+aclnnStatus aclnnUpsampleBilinear2dBackwardV2GetWorkspaceSize(const aclTensor* gradOut, const aclIntArray* outputSize,
+                                                              const aclIntArray* inputSize, bool alignCorners,
+                                                              double scalesH, double scalesW, aclTensor* out,
+                                                              uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleBilinear2dBackwardV2";
+    if (gradOut == nullptr || inputSize == nullptr || outputSize == nullptr || out == nullptr ||
+        workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (gradOut->dims.size() != 4 || inputSize->v.size() != 4 || outputSize->v.size() != 2) {
+        return CheckBackwardShape(api, gradOut, outputSize, inputSize, out, false);
+    }
+    if (out->format != ACL_FORMAT_NCHW && out->format != ACL_FORMAT_NHWC) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format %s of out not supported", api, FormatName(out->format));
+    }
+    aclnnStatus st = CheckBackwardShape(api, gradOut, outputSize, inputSize, out, true);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    if (!CheckNCDimValid(gradOut, out, api)) {
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    st = CheckBackwardCommon(api, gradOut, outputSize, inputSize, out, false);
+    if (st != ACLNN_SUCCESS) {
+        return st;
+    }
+    if (gradOut->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut and out must have the same format", api);
+    }
+    if (IsEmpty(gradOut) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    return PlanBilinearBwd(api, gradOut, inputSize, alignCorners, scalesH, scalesW, out, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleBilinear2dBackwardV2(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                              aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBilinear2dBackwardV2", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/upsample_bicubic2d_aa/op_host/op_api/aclnn_upsample_bicubic2d_aa.cpp:145-162 (CheckParams), :59-124
+aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const aclIntArray* outputSize,
+                                                     const bool alignCorners, const double scalesH,
+                                                     const double scalesW, aclTensor* out, uint64_t* workspaceSize,
+                                                     aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleBicubic2dAA";
+    if (workspaceSize == nullptr || executor == nullptr) { // OP_CHECK_COMM_INPUT (:168)
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (x == nullptr || outputSize == nullptr || out == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (!DtypeSupported(x->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: x dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(x->dtype));
+    }
+    if (x->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from x dtype %s", api, DtypeName(out->dtype),
+                    DtypeName(x->dtype));
+    }
+    if (x->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: x must be 4-D, got %zu-D", api, x->dims.size());
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: output_size must have 2 values, got %zu", api, outputSize->v.size());
+    }
+    if (out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out must be 4-D, got %zu-D", api, out->dims.size());
+    }
+    const int64_t inH = x->dims[2], inW = x->dims[3], outH = outputSize->v[0], outW = outputSize->v[1];
+    if (!(inH > 0 && inW > 0 && outH > 0 && outW > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID,
+                    "%s: input and output sizes should be greater than 0, got input (H: %ld, W: %ld) output (H: %ld, W: %ld)",
+                    api, (long)inH, (long)inW, (long)outH, (long)outW);
+    }
+    if (!(x->dims[1] > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: non-empty 4-D data tensor expected", api);
+    }
+    if (x->dims[0] != out->dims[0] || x->dims[1] != out->dims[1]) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: N and C of x and out must be equal", api);
+    }
+    if (out->dims[2] != outH || out->dims[3] != outW) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out H/W (%ld, %ld) differ from output_size (%ld, %ld)", api,
+                    (long)out->dims[2], (long)out->dims[3], (long)outH, (long)outW);
+    }
+    const bool fmtOk = (x->format == ACL_FORMAT_ND || x->format == ACL_FORMAT_NCHW) &&
+                       (out->format == ACL_FORMAT_ND || out->format == ACL_FORMAT_NCHW);
+    if (!fmtOk) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: storage format only supports NCHW, got %s and %s", api,
+                    FormatName(x->format), FormatName(out->format));
+    }
+    if (inH > INT32_MAX || inW > INT32_MAX || outH > INT32_MAX || outW > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
+    }
+    if (IsEmpty(x) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    Geom gi{x->dims[0], x->dims[1], inH, inW}, go{x->dims[0], x->dims[1], outH, outW};
+    const AAGeom ah = MakeAAGeom(inH, outH, alignCorners, scalesH, false);
+    const AAGeom aw = MakeAAGeom(inW, outW, alignCorners, scalesW, false);
+    if (AAIsCopy(gi, go, ah, aw)) {
+        return PlanCopy(api, x, out, workspaceSize, executor);
+    }
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef xin = StageInput(x, ws, ex);
+    const BufRef y = StageOutput(out, ws);
+    const Shape4 sh = MakeShape(gi, go);
+    const Dt dt = ToDt(x->dtype);
+    const AxisGeom gh{sh.hin, sh.hout, ah.scale}, gw{sh.win, sh.wout, aw.scale};
+    const AAOffsets oh = AllocAA(ws, sh.hout, ah.taps), ow = AllocAA(ws, sh.wout, aw.taps);
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
+        cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, s);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        return BicubicAAFwd(dt, xin.At(w), y.At(w), sh, th, tw, s);
+    });
+    FinishOutput(out, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnUpsampleBicubic2dAA(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                     aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBicubic2dAA", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/upsample_bicubic2d_aa_grad/op_host/op_api/aclnn_upsample_bicubic2d_aa_grad.cpp:159-181 (CheckParams):
+// null, dtype, scales, shape, N/C, elements
+aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOutput, const aclIntArray* outputSize,
+                                                         const aclIntArray* inputSize, bool alignCorners,
+                                                         double scalesH, double scalesW, aclTensor* out,
+                                                         uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleBicubic2dAAGrad";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (gradOutput == nullptr || inputSize == nullptr || out == nullptr || outputSize == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (!DtypeSupported(gradOutput->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOutput dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(gradOutput->dtype));
+    }
+    if (gradOutput->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from gradOutput dtype %s", api,
+                    DtypeName(out->dtype), DtypeName(gradOutput->dtype));
+    }
+    if (scalesW < 0 || scalesH < 0) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales cannot be negative (w %f, h %f)", api, scalesW, scalesH);
+    }
+    if (gradOutput->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format of gradOutput (%s) and out (%s) must be equal", api,
+                    FormatName(gradOutput->format), FormatName(out->format));
+    }
+    if (gradOutput->dims.size() != 4 || out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOutput and out must be 4-D", api);
+    }
+    if (inputSize->v.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input_size must have 4 values, got %zu", api, inputSize->v.size());
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: output_size must have 2 values, got %zu", api, outputSize->v.size());
+    }
+    if (gradOutput->format == ACL_FORMAT_NCHW && !CheckNCDimValid(gradOutput, out, api)) {
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    const int64_t outN = gradOutput->dims[0], outC = gradOutput->dims[1], outH = gradOutput->dims[2],
+                  outW = gradOutput->dims[3];
+    const int64_t inH = inputSize->v[2], inW = inputSize->v[3];
+    if (!(outN > 0 && inH > 0 && inW > 0 && outC > 0 && outH > 0 && outW > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input and output sizes should be greater than 0", api);
+    }
+    const bool fmtOk = (gradOutput->format == ACL_FORMAT_ND || gradOutput->format == ACL_FORMAT_NCHW);
+    if (!fmtOk) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: storage format only supports NCHW, got %s", api,
+                    FormatName(gradOutput->format));
+    }
+    if (outputSize->v[0] != outH || outputSize->v[1] != outW) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOutput H/W (%ld, %ld) differ from output_size (%ld, %ld)", api,
+                    (long)outH, (long)outW, (long)outputSize->v[0], (long)outputSize->v[1]);
+    }
+    if (out->dims[0] != inputSize->v[0] || out->dims[1] != inputSize->v[1] || out->dims[2] != inH ||
+        out->dims[3] != inW || out->dims[0] != outN || out->dims[1] != outC) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out shape must equal input_size and share N, C with gradOutput", api);
+    }
+    if (inH > INT32_MAX || inW > INT32_MAX || outH > INT32_MAX || outW > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
+    }
+    if (IsEmpty(gradOutput) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    Geom gi{outN, outC, inH, inW}, gg{outN, outC, outH, outW};
+    const AAGeom ah = MakeAAGeom(inH, outH, alignCorners, scalesH, true);
+    const AAGeom aw = MakeAAGeom(inW, outW, alignCorners, scalesW, true);
+    if (AAIsCopy(gi, gg, ah, aw)) {
+        return PlanCopy(api, gradOutput, out, workspaceSize, executor);
+    }
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef g = StageInput(gradOutput, ws, ex);
+    const BufRef y = StageOutput(out, ws);
+    const Shape4 sh = MakeShape(gi, gg);
+    const Dt dt = ToDt(gradOutput->dtype);
+    const AxisGeom gh{sh.hin, sh.hout, ah.scale}, gw{sh.win, sh.wout, aw.scale};
+    const AAOffsets oh = AllocAA(ws, sh.hout, ah.taps), ow = AllocAA(ws, sh.wout, aw.taps);
+    const bool atomic = GetBackwardAlgo() == 1 && GetDeterministic() == 0;
+    if (atomic) {
+        const int64_t elems = gi.n * gi.c * gi.h * gi.w;
+        const bool needAcc = dt != Dt::F32;
+        const uint64_t accOff = needAcc ? ws.Alloc(static_cast<uint64_t>(elems) * 4) : 0;
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
+            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            float* acc = needAcc ? reinterpret_cast<float*>(w + accOff) : static_cast<float*>(y.At(w));
+            return BicubicAABwdAtomic(dt, g.At(w), y.At(w), acc, sh, th, tw, s);
+        });
+    } else {
+        const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
+            const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
+            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            e = BuildAABwdRanges(gh, gw, th, tw, qh, qw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            return BicubicAABwdGather(dt, g.At(w), y.At(w), sh, th, tw, qh, qw, s);
+        });
+    }
+    FinishOutput(out, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnUpsampleBicubic2dAAGrad(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                         aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBicubic2dAAGrad", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+aclnnStatus opscvDebugAxisTable(int32_t kind, int64_t inSize, int64_t outSize, int32_t alignCorners, float userScale,
+                                int32_t* i0, int32_t* i1, float* f0, int32_t* tapsOut)
+{
+    static const char* api = "opscvDebugAxisTable";
+    if (inSize <= 0 || outSize <= 0 || inSize > INT32_MAX || outSize > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: sizes must be in [1, INT32_MAX]", api);
+    }
+    const int32_t in = static_cast<int32_t>(inSize), out = static_cast<int32_t>(outSize);
+    AAGeom aa{};
+    int64_t nInt = 0, nFloat = 0;
+    switch (kind) {
+        case 0: nInt = out; break;
+        case 1: nInt = in; break;
+        case 2: nInt = out; nFloat = out; break;
+        case 3:
+            aa = MakeAAGeom(in, out, alignCorners != 0, userScale, false);
+            if (tapsOut != nullptr) {
+                *tapsOut = aa.taps;
+            }
+            if (f0 == nullptr) {
+                return ACLNN_SUCCESS;
+            }
+            nInt = out;
+            nFloat = static_cast<int64_t>(out) * aa.taps;
+            break;
+        default: return Fail(ACLNN_ERR_PARAM_INVALID, "%s: unknown kind %d", api, kind);
+    }
+    if (i0 == nullptr || (kind != 0 && i1 == nullptr) || (nFloat > 0 && f0 == nullptr)) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null output array", api);
+    }
+    int32_t *d0 = nullptr, *d1 = nullptr;
+    float* df = nullptr;
+    cudaError_t e = cudaMalloc(&d0, sizeof(int32_t) * nInt);
+    if (e == cudaSuccess) {
+        e = cudaMalloc(&d1, sizeof(int32_t) * nInt);
+    }
+    if (e == cudaSuccess && nFloat > 0) {
+        e = cudaMalloc(&df, sizeof(float) * nFloat);
+    }
+    if (e == cudaSuccess) {
+        if (kind == 0) {
+            const AxisGeom g{in, out, NearestScale(in, out, userScale)};
+            e = BuildNearestFwdTables(g, g, NearestAxis{d0}, NearestAxis{d1}, nullptr);
+        } else if (kind == 1) {
+            const AxisGeom g{in, out, NearestScale(in, out, userScale)};
+            // second table goes to scratch; only the first pair is returned
+            int32_t *s0 = nullptr, *s1 = nullptr;
+            e = cudaMalloc(&s0, sizeof(int32_t) * nInt);
+            if (e == cudaSuccess) {
+                e = cudaMalloc(&s1, sizeof(int32_t) * nInt);
+            }
+            if (e == cudaSuccess) {
+                e = BuildNearestBwdTables(g, g, RangeAxis{d0, d1}, RangeAxis{s0, s1}, nullptr);
+            }
+            if (e == cudaSuccess) {
+                e = cudaDeviceSynchronize();
+            }
+            cudaFree(s0);
+            cudaFree(s1);
+        } else if (kind == 2) {
+            const AxisGeom g{in, out, BilinearScale(in, out, alignCorners != 0, userScale)};
+            int32_t *s0 = nullptr, *s1 = nullptr;
+            float* sf = nullptr;
+            e = cudaMalloc(&s0, sizeof(int32_t) * nInt);
+            if (e == cudaSuccess) {
+                e = cudaMalloc(&s1, sizeof(int32_t) * nInt);
+            }
+            if (e == cudaSuccess) {
+                e = cudaMalloc(&sf, sizeof(float) * nFloat);
+            }
+            if (e == cudaSuccess) {
+                e = BuildLerpTables(g, g, alignCorners == 0, 0, LerpAxis{d0, d1, df}, LerpAxis{s0, s1, sf}, nullptr);
+            }
+            if (e == cudaSuccess) {
+                e = cudaDeviceSynchronize();
+            }
+            cudaFree(s0);
+            cudaFree(s1);
+            cudaFree(sf);
+        } else {
+            const AxisGeom g{in, out, aa.scale};
+            int32_t *s0 = nullptr, *s1 = nullptr;
+            float* sf = nullptr;
+            e = cudaMalloc(&s0, sizeof(int32_t) * nInt);
+            if (e == cudaSuccess) {
+                e = cudaMalloc(&s1, sizeof(int32_t) * nInt);
+            }
+            if (e == cudaSuccess) {
+                e = cudaMalloc(&sf, sizeof(float) * nFloat);
+            }
+            if (e == cudaSuccess) {
+                e = BuildAATables(g, g, aa.inv, aa.inv, aa.support, aa.support, AAAxis{d0, d1, df, aa.taps},
+                                  AAAxis{s0, s1, sf, aa.taps}, nullptr);
+            }
+            if (e == cudaSuccess) {
+                e = cudaDeviceSynchronize();
+            }
+            cudaFree(s0);
+            cudaFree(s1);
+            cudaFree(sf);
+        }
+    }
+    if (e == cudaSuccess) {
+        e = cudaDeviceSynchronize();
+    }
+    if (e == cudaSuccess) {
+        e = cudaMemcpy(i0, d0, sizeof(int32_t) * nInt, cudaMemcpyDeviceToHost);
+    }
+    if (e == cudaSuccess && kind != 0) {
+        e = cudaMemcpy(i1, d1, sizeof(int32_t) * nInt, cudaMemcpyDeviceToHost);
+    }
+    if (e == cudaSuccess && nFloat > 0) {
+        e = cudaMemcpy(f0, df, sizeof(float) * nFloat, cudaMemcpyDeviceToHost);
+    }
+    cudaFree(d0);
+    cudaFree(d1);
+    cudaFree(df);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return Fail(ACLNN_ERR_RUNTIME_ERROR, "%s: CUDA error %d (%s)", api, static_cast<int>(e), cudaGetErrorString(e));
+    }
+    return ACLNN_SUCCESS;
+}
+
+} // extern "C"

@@ -1,0 +1,107 @@
+// Shared device helpers: storage-dtype traits, 16-byte vector access, exact (non-contracted) fp32 arithmetic.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace opscv {
+
+constexpr int kNumSMsFallback = 148; // B200
+
+// ---- storage dtype <-> fp32 ------------------------------------------------------------------------------
+// All interpolation arithmetic is fp32; the storage dtype is only touched on load and on the final store,
+// which rounds once to nearest-even (the reference kernels cast the fp32 result to T in the same way).
+template <typename T>
+struct DType;
+template <>
+struct DType<float> {
+    static __device__ __forceinline__ float Load(const float* p) { return __ldg(p); }
+    static __device__ __forceinline__ float ToF(float v) { return v; }
+    static __device__ __forceinline__ float FromF(float v) { return v; }
+};
+template <>
+struct DType<__half> {
+    static __device__ __forceinline__ float Load(const __half* p) { return __half2float(__ldg(p)); }
+    static __device__ __forceinline__ float ToF(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half FromF(float v) { return __float2half_rn(v); }
+};
+template <>
+struct DType<__nv_bfloat16> {
+    static __device__ __forceinline__ float Load(const __nv_bfloat16* p) { return __bfloat162float(__ldg(p)); }
+    static __device__ __forceinline__ float ToF(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 FromF(float v) { return __float2bfloat16_rn(v); }
+};
+
+// ---- 16-byte vectors of T ----------------------------------------------------------------------------------
+template <typename T>
+struct VecOf {
+    static constexpr int kLanes = 16 / sizeof(T);
+};
+
+template <typename T, int V>
+struct alignas(sizeof(T) * V) Pack {
+    T v[V];
+};
+
+template <typename T, int V>
+__device__ __forceinline__ void StorePack(T* dst, const float (&vals)[V])
+{
+    Pack<T, V> p;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        p.v[k] = DType<T>::FromF(vals[k]);
+    }
+    *reinterpret_cast<Pack<T, V>*>(dst) = p;
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void LoadPack(const T* src, float (&vals)[V])
+{
+    Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(src);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        vals[k] = DType<T>::ToF(p.v[k]);
+    }
+}
+
+// Read-only-path version of LoadPack for 16-byte packs.
+template <typename T, int V>
+__device__ __forceinline__ void LoadPackLdg(const T* src, float (&vals)[V])
+{
+    if constexpr (sizeof(T) * V == 16) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+        const Pack<T, V>& p = reinterpret_cast<const Pack<T, V>&>(raw);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            vals[k] = DType<T>::ToF(p.v[k]);
+        }
+    } else if constexpr (sizeof(T) * V == 8) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src));
+        const Pack<T, V>& p = reinterpret_cast<const Pack<T, V>&>(raw);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            vals[k] = DType<T>::ToF(p.v[k]);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            vals[k] = DType<T>::Load(src + k);
+        }
+    }
+}
+
+// ---- exact fp32 arithmetic -----------------------------------------------------------------------------------
+// The reference kernels are compiled without floating-point contraction; a*b+c there is two roundings. These
+// wrappers keep nvcc from fusing them so that coordinates, weights and interpolated values can be compared bit
+// for bit with a CPU statement of the same formulas.
+__device__ __forceinline__ float Mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float Add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float Sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float Div(float a, float b) { return __fdiv_rn(a, b); }
+
+// Launch helper: ceil-div.
+__host__ __device__ __forceinline__ int64_t CeilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+} // namespace opscv

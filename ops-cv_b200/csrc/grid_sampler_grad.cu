@@ -1,0 +1,468 @@
+// GridSampler2DGrad: grad_input (N,C,H,W) and grad_grid (N,Ho,Wo,2) from grad_output (N,C,Ho,Wo), input and grid.
+//
+// grad_grid is a per-sample sum over channels; every mode computes it with one thread per sample walking the
+// channels in order, so it is reproducible and equals the serial reference order.
+//
+// grad_input is a data-dependent scatter. Two modes:
+//   * atomic (default): one thread per sample, channels inner, four fp32 atomics per channel into a zeroed fp32
+//     accumulator (grad_input itself for fp32 tensors, workspace for 16-bit tensors, followed by one cast).
+//   * deterministic (ACL_OPT_DETERMINISTIC): the scatter is turned into a gather with a fixed summation order.
+//       1. count   - per image, how many taps land on each input pixel (integer atomics: order-free).
+//       2. scan    - per image exclusive prefix sum of the counts -> segment offsets.
+//       3. fill    - per image, warps partition the destination pixels; every warp walks ALL samples of the
+//                    image in the order in which the reference's deterministic kernel replays them (256-sample
+//                    chunks; inside a chunk tap NW, NE, SW, SE; inside a tap ascending sample index) and appends
+//                    the taps that fall in its partition to their destination's segment. Ranks inside a
+//                    32-sample step come from __match_any_sync, so no sort is needed.
+//       4. gather  - one thread per (destination pixel, channel group) adds  weight * grad_output  over its
+//                    segment in that order and writes grad_input once.
+//     The summation order per destination is fixed by the data alone, so results are bit-identical from run to
+//     run, and equal to a serial replay in the reference's order. The segment lists are built once per call and
+//     reused by all channels.
+//
+// Arithmetic: image/grid_sampler3_d_grad/op_kernel/arch35/grid_sampler3_d_grad_simt_base.h:51-184,
+// image/grid_sampler2_d_grad/op_kernel/arch35/grid_sampler2_d_grad_simt.h:64-144,235-290. All arithmetic is fp32.
+#include "grid_coords.cuh"
+#include "launch_util.cuh"
+
+namespace opscv {
+namespace {
+
+constexpr int kThreads = 256;
+
+inline uint64_t Align256(uint64_t v) { return (v + 255) & ~static_cast<uint64_t>(255); }
+
+struct GradTaps {
+    int32_t x0, y0;
+    float ix, iy, mx, my;
+    float tnw, tne, tsw, tse;
+};
+
+__device__ __forceinline__ GradTaps MakeGradTaps(float gx, float gy, const GridShape& g)
+{
+    GradTaps t;
+    t.ix = gs::SourceIndexSetGrad(gx, g.win, g.pad, g.align, &t.mx);
+    t.iy = gs::SourceIndexSetGrad(gy, g.hin, g.pad, g.align, &t.my);
+    if (g.interp == 0) {
+        t.x0 = static_cast<int32_t>(floorf(t.ix));
+        t.y0 = static_cast<int32_t>(floorf(t.iy));
+        const float xe = Sub(static_cast<float>(t.x0 + 1), t.ix), ye = Sub(static_cast<float>(t.y0 + 1), t.iy);
+        const float xw = Sub(t.ix, static_cast<float>(t.x0)), yw = Sub(t.iy, static_cast<float>(t.y0));
+        t.tnw = Mul(xe, ye);
+        t.tne = Mul(xw, ye);
+        t.tsw = Mul(xe, yw);
+        t.tse = Mul(xw, yw);
+    } else {
+        t.x0 = static_cast<int32_t>(rintf(t.ix));
+        t.y0 = static_cast<int32_t>(rintf(t.iy));
+        t.tnw = 1.0f;
+        t.tne = t.tsw = t.tse = 0.0f;
+    }
+    return t;
+}
+
+// One thread per sample; channels inner. ATOMIC_GI: scatter grad_input with fp32 atomics. WANT_GRID: grad_grid.
+template <typename T, bool ATOMIC_GI, bool WANT_GRID>
+__global__ void __launch_bounds__(kThreads)
+    GridGradSampleKernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ grid,
+                         float* __restrict__ acc, T* __restrict__ ggrid, GridShape g, int64_t total)
+{
+    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win;
+    const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
+        const int64_t n = s / outPlane;
+        const int64_t p = s - n * outPlane;
+        const GradTaps t = MakeGradTaps(DType<T>::Load(grid + 2 * s), DType<T>::Load(grid + 2 * s + 1), g);
+        const T* gob = go + n * g.c * outPlane + p;
+        const T* xb = x + n * g.c * inPlane;
+        float* ab = acc + n * g.c * inPlane;
+        if (g.interp == 0) {
+            const bool bnw = gs::Within(t.y0, t.x0, g.hin, g.win), bne = gs::Within(t.y0, t.x0 + 1, g.hin, g.win);
+            const bool bsw = gs::Within(t.y0 + 1, t.x0, g.hin, g.win),
+                       bse = gs::Within(t.y0 + 1, t.x0 + 1, g.hin, g.win);
+            const int64_t o = static_cast<int64_t>(t.y0) * g.win + t.x0;
+            const float ye = Sub(static_cast<float>(t.y0 + 1), t.iy), xe = Sub(static_cast<float>(t.x0 + 1), t.ix);
+            const float yw = Sub(t.iy, static_cast<float>(t.y0)), xw = Sub(t.ix, static_cast<float>(t.x0));
+            float gix = 0.0f, giy = 0.0f;
+            for (int64_t c = 0; c < g.c; ++c) {
+                const float gv = DType<T>::Load(gob + c * outPlane);
+                const int64_t base = c * inPlane + o;
+                if (bnw) {
+                    if (ATOMIC_GI) {
+                        atomicAdd(ab + base, Mul(t.tnw, gv));
+                    }
+                    if (WANT_GRID) {
+                        const float v = DType<T>::Load(xb + base);
+                        gix = Sub(gix, Mul(Mul(v, ye), gv));
+                        giy = Sub(giy, Mul(Mul(v, xe), gv));
+                    }
+                }
+                if (bne) {
+                    if (ATOMIC_GI) {
+                        atomicAdd(ab + base + 1, Mul(t.tne, gv));
+                    }
+                    if (WANT_GRID) {
+                        const float v = DType<T>::Load(xb + base + 1);
+                        gix = Add(gix, Mul(Mul(v, ye), gv));
+                        giy = Sub(giy, Mul(Mul(v, xw), gv));
+                    }
+                }
+                if (bsw) {
+                    if (ATOMIC_GI) {
+                        atomicAdd(ab + base + g.win, Mul(t.tsw, gv));
+                    }
+                    if (WANT_GRID) {
+                        const float v = DType<T>::Load(xb + base + g.win);
+                        gix = Sub(gix, Mul(Mul(v, yw), gv));
+                        giy = Add(giy, Mul(Mul(v, xe), gv));
+                    }
+                }
+                if (bse) {
+                    if (ATOMIC_GI) {
+                        atomicAdd(ab + base + g.win + 1, Mul(t.tse, gv));
+                    }
+                    if (WANT_GRID) {
+                        const float v = DType<T>::Load(xb + base + g.win + 1);
+                        gix = Add(gix, Mul(Mul(v, yw), gv));
+                        giy = Add(giy, Mul(Mul(v, xw), gv));
+                    }
+                }
+            }
+            if (WANT_GRID) {
+                ggrid[2 * s] = DType<T>::FromF(Mul(t.mx, gix));
+                ggrid[2 * s + 1] = DType<T>::FromF(Mul(t.my, giy));
+            }
+        } else {
+            if (ATOMIC_GI && gs::Within(t.y0, t.x0, g.hin, g.win)) {
+                const int64_t o = static_cast<int64_t>(t.y0) * g.win + t.x0;
+                for (int64_t c = 0; c < g.c; ++c) {
+                    atomicAdd(ab + c * inPlane + o, DType<T>::Load(gob + c * outPlane));
+                }
+            }
+            if (WANT_GRID) {
+                ggrid[2 * s] = DType<T>::FromF(0.0f);
+                ggrid[2 * s + 1] = DType<T>::FromF(0.0f);
+            }
+        }
+    }
+}
+
+// ---- deterministic mode --------------------------------------------------------------------------------------
+struct Entry {
+    int32_t sample; // pixel index inside the image's output plane
+    float weight;
+};
+
+__device__ __forceinline__ int32_t TapDest(const GradTaps& t, int tap, const GridShape& g)
+{
+    const int32_t yy = t.y0 + (tap >> 1), xx = t.x0 + (tap & 1);
+    if (g.interp != 0 && tap != 0) {
+        return -1;
+    }
+    return gs::Within(yy, xx, g.hin, g.win) ? yy * g.win + xx : -1;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    DetCountKernel(const T* __restrict__ grid, int32_t* __restrict__ counts, GridShape g, int64_t total)
+{
+    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win;
+    const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
+        const int64_t n = s / outPlane;
+        const GradTaps t = MakeGradTaps(DType<T>::Load(grid + 2 * s), DType<T>::Load(grid + 2 * s + 1), g);
+#pragma unroll
+        for (int tap = 0; tap < 4; ++tap) {
+            const int32_t d = TapDest(t, tap, g);
+            if (d >= 0) {
+                atomicAdd(counts + n * (inPlane + 1) + d, 1);
+            }
+        }
+    }
+}
+
+// One block per image: exclusive scan of counts[n][0..inPlane) in place; counts[n][inPlane] = total. Also copies
+// the offsets into `cursor` (the running append positions used by the fill kernel).
+__global__ void __launch_bounds__(1024) DetScanKernel(int32_t* __restrict__ counts, int32_t* __restrict__ cursor,
+                                                       int64_t inPlane)
+{
+    __shared__ int32_t warpSums[32];
+    __shared__ int32_t carry;
+    int32_t* c = counts + blockIdx.x * (inPlane + 1);
+    int32_t* cur = cursor + blockIdx.x * inPlane;
+    if (threadIdx.x == 0) {
+        carry = 0;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int64_t base = 0; base < inPlane; base += blockDim.x) {
+        const int64_t i = base + threadIdx.x;
+        const int32_t v = i < inPlane ? c[i] : 0;
+        int32_t incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) {
+                incl += up;
+            }
+        }
+        if (lane == 31) {
+            warpSums[warp] = incl;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            int32_t ws = lane < (blockDim.x >> 5) ? warpSums[lane] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int32_t up = __shfl_up_sync(0xffffffffu, ws, o);
+                if (lane >= o) {
+                    ws += up;
+                }
+            }
+            warpSums[lane] = ws; // inclusive over warps
+        }
+        __syncthreads();
+        const int32_t warpOffset = warp == 0 ? 0 : warpSums[warp - 1];
+        const int32_t excl = carry + warpOffset + incl - v;
+        if (i < inPlane) {
+            c[i] = excl;
+            cur[i] = excl;
+        }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) {
+            carry = excl + v;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        c[inPlane] = carry;
+    }
+}
+
+// The reference's deterministic kernel stages the contributions of 256 consecutive samples and lets one thread
+// replay them tap by tap (grid_sampler2_d_grad_simt_det.h:78-106, VF_MAX_THREAD_NUM = 256), so per destination
+// the order is: 256-sample chunk, then tap (NW, NE, SW, SE), then sample index. The fill keeps that order.
+constexpr int kDetChunk = 256;
+constexpr int kDetSub = kDetChunk / 32;
+
+// grid.x = warpsPerImage * N blocks of one warp. Warp w of image n owns destinations [d0, d1).
+template <typename T>
+__global__ void __launch_bounds__(32)
+    DetFillKernel(const T* __restrict__ grid, int32_t* cursor, Entry* __restrict__ entries, GridShape g,
+                  int32_t warpsPerImage, int64_t entriesPerImage)
+{
+    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win;
+    const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int64_t n = blockIdx.x / warpsPerImage;
+    const int32_t w = blockIdx.x - n * warpsPerImage;
+    const int64_t per = CeilDiv(inPlane, warpsPerImage);
+    const int32_t d0 = static_cast<int32_t>(min(inPlane, per * w));
+    const int32_t d1 = static_cast<int32_t>(min(inPlane, per * (w + 1)));
+    if (d0 >= d1) {
+        return;
+    }
+    const int lane = threadIdx.x;
+    const unsigned lower = (1u << lane) - 1u;
+    volatile int32_t* cur = cursor + n * inPlane;
+    Entry* ent = entries + n * entriesPerImage;
+    const T* gb = grid + 2 * n * outPlane;
+    for (int64_t chunk = 0; chunk < outPlane; chunk += kDetChunk) {
+        int32_t x0[kDetSub], y0[kDetSub];
+        float wt[kDetSub][4];
+#pragma unroll
+        for (int sub = 0; sub < kDetSub; ++sub) {
+            const int64_t p = chunk + sub * 32 + lane;
+            x0[sub] = INT32_MIN / 2; // far out of bounds: no tap of a dead lane is in range
+            y0[sub] = INT32_MIN / 2;
+            wt[sub][0] = wt[sub][1] = wt[sub][2] = wt[sub][3] = 0.0f;
+            if (p < outPlane) {
+                const GradTaps t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
+                x0[sub] = t.x0;
+                y0[sub] = t.y0;
+                wt[sub][0] = t.tnw;
+                wt[sub][1] = t.tne;
+                wt[sub][2] = t.tsw;
+                wt[sub][3] = t.tse;
+            }
+        }
+        const int numTaps = g.interp == 0 ? 4 : 1;
+        for (int tap = 0; tap < numTaps; ++tap) {
+#pragma unroll
+            for (int sub = 0; sub < kDetSub; ++sub) {
+                const int32_t yy = y0[sub] + (tap >> 1), xx = x0[sub] + (tap & 1);
+                const int32_t d = gs::Within(yy, xx, g.hin, g.win) ? yy * g.win + xx : -1;
+                const bool mine = d >= d0 && d < d1;
+                // Lanes without a tap in this partition get a key no other lane has: they match only themselves.
+                const int32_t key = mine ? d : -1 - lane;
+                const unsigned peers = __match_any_sync(0xffffffffu, key);
+                if (mine) {
+                    const int32_t start = cur[d];
+                    const int32_t rank = __popc(peers & lower);
+                    const float wgt = tap == 0 ? wt[sub][0] : (tap == 1 ? wt[sub][1] : (tap == 2 ? wt[sub][2] : wt[sub][3]));
+                    ent[start + rank] = Entry{static_cast<int32_t>(chunk + sub * 32 + lane), wgt};
+                }
+                __syncwarp();
+                if (mine && (peers & lower) == 0) { // lowest lane of each group advances the cursor
+                    cur[d] = cur[d] + __popc(peers);
+                }
+                __syncwarp();
+            }
+        }
+    }
+}
+
+// One thread per (image, channel group, destination pixel); consecutive threads -> consecutive destinations.
+template <typename T, int CG>
+__global__ void __launch_bounds__(kThreads)
+    DetGatherKernel(const T* __restrict__ go, const int32_t* __restrict__ offsets, const Entry* __restrict__ entries,
+                    T* __restrict__ gi, GridShape g, int32_t chanGroups, int64_t entriesPerImage, int64_t total)
+{
+    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win;
+    const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int64_t ng = idx / inPlane;
+        const int64_t d = idx - ng * inPlane;
+        const int64_t n = ng / chanGroups;
+        const int32_t cg = static_cast<int32_t>(ng - n * chanGroups);
+        const int64_t c0 = static_cast<int64_t>(cg) * CG;
+        const int32_t* off = offsets + n * (inPlane + 1);
+        const int32_t a = __ldg(off + d), b = __ldg(off + d + 1);
+        const Entry* ent = entries + n * entriesPerImage;
+        const T* gob = go + (n * g.c + c0) * outPlane;
+        float acc[CG];
+#pragma unroll
+        for (int k = 0; k < CG; ++k) {
+            acc[k] = 0.0f;
+        }
+        for (int32_t e = a; e < b; ++e) {
+            const int2 raw = __ldg(reinterpret_cast<const int2*>(ent + e));
+            const float wgt = __int_as_float(raw.y);
+            const T* gs_ = gob + raw.x;
+#pragma unroll
+            for (int k = 0; k < CG; ++k) {
+                if (c0 + k < g.c) {
+                    acc[k] = Add(acc[k], Mul(wgt, DType<T>::Load(gs_ + k * outPlane)));
+                }
+            }
+        }
+        T* gib = gi + (n * g.c + c0) * inPlane + d;
+#pragma unroll
+        for (int k = 0; k < CG; ++k) {
+            if (c0 + k < g.c) {
+                gib[k * inPlane] = DType<T>::FromF(acc[k]);
+            }
+        }
+    }
+}
+
+} // namespace
+
+GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool wantInput, bool wantGrid)
+{
+    GridGradPlan p{};
+    p.deterministic = deterministic;
+    p.wantInput = wantInput;
+    p.wantGrid = wantGrid;
+    const uint64_t inPlane = static_cast<uint64_t>(g.hin) * g.win;
+    const uint64_t outPlane = static_cast<uint64_t>(g.hout) * g.wout;
+    if (wantInput) {
+        if (deterministic) {
+            // counts/offsets [N][inPlane+1] and cursors [N][inPlane], then entries [N][4*outPlane]
+            p.countBytes = Align256(static_cast<uint64_t>(g.n) * (inPlane + 1) * 4) +
+                           Align256(static_cast<uint64_t>(g.n) * inPlane * 4);
+            p.entryBytes = Align256(static_cast<uint64_t>(g.n) * 4 * outPlane * sizeof(Entry));
+        } else if (dt != Dt::F32) {
+            p.accBytes = Align256(static_cast<uint64_t>(g.n) * g.c * inPlane * 4);
+        }
+    }
+    p.total = p.accBytes + p.countBytes + p.entryBytes;
+    return p;
+}
+
+cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* grid, void* gi, void* ggrid,
+                             GridShape g, const GridGradPlan& plan, void* workspace, cudaStream_t s)
+{
+    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win;
+    const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int64_t samples = g.n * outPlane;
+    const int64_t giElems = g.n * g.c * inPlane;
+    cudaError_t e = cudaSuccess;
+    char* ws = static_cast<char*>(workspace);
+
+    if (!plan.deterministic || !plan.wantInput) {
+        float* acc = nullptr;
+        if (plan.wantInput) {
+            acc = dt == Dt::F32 ? static_cast<float*>(gi) : reinterpret_cast<float*>(ws);
+            e = cudaMemsetAsync(acc, 0, static_cast<size_t>(giElems) * sizeof(float), s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            CountLaunch();
+        }
+        OPSCV_DISPATCH_DT(dt, T, {
+            const unsigned blocks = GridFor(samples, kThreads, 16);
+            const T* pgo = static_cast<const T*>(go);
+            const T* px = static_cast<const T*>(x);
+            const T* pg = static_cast<const T*>(grid);
+            T* pgg = static_cast<T*>(ggrid);
+            if (plan.wantInput && plan.wantGrid) {
+                GridGradSampleKernel<T, true, true><<<blocks, kThreads, 0, s>>>(pgo, px, pg, acc, pgg, g, samples);
+            } else if (plan.wantInput) {
+                GridGradSampleKernel<T, true, false><<<blocks, kThreads, 0, s>>>(pgo, px, pg, acc, pgg, g, samples);
+            } else {
+                GridGradSampleKernel<T, false, true><<<blocks, kThreads, 0, s>>>(pgo, px, pg, acc, pgg, g, samples);
+            }
+        });
+        CountLaunch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            return e;
+        }
+        if (plan.wantInput && dt != Dt::F32) {
+            return CastFromF32(dt, gi, acc, giElems, s);
+        }
+        return cudaSuccess;
+    }
+
+    // deterministic grad_input
+    const uint64_t countsBytes = Align256(static_cast<uint64_t>(g.n) * (inPlane + 1) * 4);
+    int32_t* counts = reinterpret_cast<int32_t*>(ws);
+    int32_t* cursor = reinterpret_cast<int32_t*>(ws + countsBytes);
+    Entry* entries = reinterpret_cast<Entry*>(ws + plan.countBytes);
+    const int64_t entriesPerImage = 4 * outPlane;
+    e = cudaMemsetAsync(counts, 0, static_cast<size_t>(g.n) * (inPlane + 1) * 4, s);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    CountLaunch();
+    // Enough one-warp blocks per image to occupy the machine, but never more than one per 32 destinations.
+    int64_t warpsPerImage = CeilDiv(static_cast<int64_t>(NumSMs()) * 32, g.n > 0 ? g.n : 1);
+    warpsPerImage = warpsPerImage > CeilDiv(inPlane, 32) ? CeilDiv(inPlane, 32) : warpsPerImage;
+    warpsPerImage = warpsPerImage < 1 ? 1 : warpsPerImage;
+    constexpr int CG = 8;
+    const int32_t chanGroups = static_cast<int32_t>(CeilDiv(g.c, CG));
+    const int64_t gatherTotal = g.n * chanGroups * inPlane;
+    OPSCV_DISPATCH_DT(dt, T, {
+        const T* pgo = static_cast<const T*>(go);
+        const T* px = static_cast<const T*>(x);
+        const T* pg = static_cast<const T*>(grid);
+        DetCountKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(pg, counts, g, samples);
+        DetScanKernel<<<static_cast<unsigned>(g.n), 1024, 0, s>>>(counts, cursor, inPlane);
+        DetFillKernel<T><<<static_cast<unsigned>(g.n * warpsPerImage), 32, 0, s>>>(
+            pg, cursor, entries, g, static_cast<int32_t>(warpsPerImage), entriesPerImage);
+        DetGatherKernel<T, CG><<<GridFor(gatherTotal, kThreads, 16), kThreads, 0, s>>>(
+            pgo, counts, entries, static_cast<T*>(gi), g, chanGroups, entriesPerImage, gatherTotal);
+        CountLaunch(4);
+        if (plan.wantGrid) {
+            GridGradSampleKernel<T, false, true><<<GridFor(samples, kThreads, 16), kThreads, 0, s>>>(
+                pgo, px, pg, nullptr, static_cast<T*>(ggrid), g, samples);
+            CountLaunch();
+        }
+    });
+    return cudaGetLastError();
+}
+
+} // namespace opscv

@@ -1,0 +1,118 @@
+// Host-callable launchers of the CUDA kernels. Plain C++ (no CUDA types beyond cudaStream_t / cudaError_t) so
+// that the aclnn host layer can be compiled as ordinary C++.
+#pragma once
+
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+
+namespace opscv {
+
+enum class Dt : int32_t { F32 = 0, F16 = 1, BF16 = 2 };
+inline int DtSize(Dt d) { return d == Dt::F32 ? 4 : 2; }
+
+enum Layout : int32_t { kNCHW = 0, kNHWC = 1 };
+
+// Per-thread launch counter (incremented by every kernel launch made through these launchers).
+void CountLaunch(int n = 1);
+uint64_t LaunchCount();
+void ResetLaunchCount();
+
+// ---- per-axis tables (device memory, normally carved out of the caller's workspace) ---------------------------
+struct NearestAxis { // one entry per OUTPUT index
+    int32_t* src;
+};
+struct RangeAxis { // one entry per grad_input index: window [start, end) of grad_output indices
+    int32_t* start;
+    int32_t* end;
+};
+struct LerpAxis { // one entry per output (forward) / grad_output (backward) index
+    int32_t* lo;
+    int32_t* hi;
+    float* delta;
+};
+struct AAAxis { // one entry per output index; w is [out][taps], zero padded, already normalised
+    int32_t* xmin;
+    int32_t* xsize;
+    float* w;
+    int32_t taps;
+};
+
+struct AxisGeom {
+    int32_t in;  // extent on the forward-input side (grad_input side for backward ops)
+    int32_t out; // extent on the forward-output side
+    float scale; // forward source-coordinate scale as the reference's tiling computes it
+};
+
+// Table builders (tables.cu). Each fills the H and the W table in one launch.
+cudaError_t BuildNearestFwdTables(AxisGeom h, AxisGeom w, NearestAxis th, NearestAxis tw, cudaStream_t s);
+cudaError_t BuildNearestBwdTables(AxisGeom h, AxisGeom w, RangeAxis th, RangeAxis tw, cudaStream_t s);
+// variant 0 = forward kernel's formula, 1 = backward (scatter-definition) formula.
+cudaError_t BuildLerpTables(AxisGeom h, AxisGeom w, bool halfPixel, int variant, LerpAxis th, LerpAxis tw,
+                            cudaStream_t s);
+// For every grad_input index y: [first, first+count) = the grad_output indices i with lo[i] == y or hi[i] == y.
+cudaError_t BuildLerpBwdRanges(AxisGeom h, AxisGeom w, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw,
+                               cudaStream_t s);
+cudaError_t BuildAATables(AxisGeom h, AxisGeom w, float invH, float invW, float supH, float supW, AAAxis th,
+                          AAAxis tw, cudaStream_t s);
+// For every forward-input index y: [start, end) = output indices whose window covers y.
+cudaError_t BuildAABwdRanges(AxisGeom h, AxisGeom w, AAAxis th, AAAxis tw, RangeAxis rh, RangeAxis rw,
+                             cudaStream_t s);
+
+// ---- resampling kernels ----------------------------------------------------------------------------------
+struct Shape4 {
+    int64_t n, c;
+    int32_t hin, win, hout, wout; // hin/win = forward input extent, hout/wout = forward output extent
+};
+
+cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, NearestAxis th, NearestAxis tw,
+                       cudaStream_t s);
+cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, RangeAxis th, RangeAxis tw,
+                       cudaStream_t s);
+cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
+                        cudaStream_t s);
+// Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
+cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
+                              LerpAxis tw, RangeAxis rh, RangeAxis rw, cudaStream_t s);
+// Scatter backward with fp32 atomics into `acc` (fp32, N*C*hin*win, zeroed by this call). If dtOut is fp32 the
+// caller passes acc == gi; otherwise a cast pass writes gi.
+cudaError_t BilinearBwdAtomic(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, float* acc, Shape4 sh,
+                              LerpAxis th, LerpAxis tw, cudaStream_t s);
+
+cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, cudaStream_t s);
+cudaError_t BicubicAABwdGather(Dt dt, const void* go, void* gi, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh,
+                               RangeAxis rw, cudaStream_t s);
+cudaError_t BicubicAABwdAtomic(Dt dt, const void* go, void* gi, float* acc, Shape4 sh, AAAxis th, AAAxis tw,
+                               cudaStream_t s);
+
+struct GridShape {
+    int64_t n, c;
+    int32_t hin, win, hout, wout;
+    int32_t interp, pad, align;
+};
+cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, GridShape g, cudaStream_t s);
+
+// Workspace needs of the grid-sampler backward (bytes, 256-byte aligned pieces); see grid_sampler_grad.cu.
+struct GridGradPlan {
+    bool deterministic;
+    bool wantInput, wantGrid;
+    uint64_t accBytes;   // fp32 grad_input accumulator (16-bit dtypes, atomic mode)
+    uint64_t countBytes; // deterministic: per-destination tap counts / offsets
+    uint64_t entryBytes; // deterministic: sorted (sample, weight) entries
+    uint64_t total;
+};
+GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool wantInput, bool wantGrid);
+cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* grid, void* gi, void* ggrid,
+                             GridShape g, const GridGradPlan& plan, void* workspace, cudaStream_t s);
+
+// ---- strided views -----------------------------------------------------------------------------------------
+struct View4 {
+    int64_t dim[4];
+    int64_t stride[4]; // in elements
+};
+// dst (contiguous, dims = v.dim) <- src view, or the reverse when `toView` is true. elemSize 2 or 4.
+cudaError_t StridedCopy(int elemSize, void* contiguous, void* viewBase, View4 v, bool toView, cudaStream_t s);
+cudaError_t CopyBytes(void* dst, const void* src, uint64_t bytes, cudaStream_t s);
+// dst[i] = (T)src[i] for fp32 src.
+cudaError_t CastFromF32(Dt dt, void* dst, const float* src, int64_t n, cudaStream_t s);
+
+} // namespace opscv

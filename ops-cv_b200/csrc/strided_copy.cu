@@ -1,0 +1,133 @@
+// Data-movement helpers: strided view <-> contiguous staging (what the reference does with its Contiguous and
+// ViewCopy steps around every operator), device-to-device copies for the same-size shortcuts, and the final
+// fp32 -> storage-dtype cast of the atomic backward paths.
+#include "launch_util.cuh"
+
+namespace opscv {
+
+namespace {
+
+thread_local int g_numSMs = 0;
+thread_local uint64_t g_launches = 0;
+
+constexpr int kThreads = 256;
+
+template <typename E>
+__global__ void __launch_bounds__(kThreads)
+    StridedCopyKernel(E* __restrict__ contiguous, E* __restrict__ viewBase, View4 v, bool toView, int64_t total)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        int64_t r = idx;
+        const int64_t i3 = r % v.dim[3];
+        r /= v.dim[3];
+        const int64_t i2 = r % v.dim[2];
+        r /= v.dim[2];
+        const int64_t i1 = r % v.dim[1];
+        const int64_t i0 = r / v.dim[1];
+        const int64_t off = i0 * v.stride[0] + i1 * v.stride[1] + i2 * v.stride[2] + i3 * v.stride[3];
+        if (toView) {
+            viewBase[off] = contiguous[idx];
+        } else {
+            contiguous[idx] = viewBase[off];
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) CastKernel(T* __restrict__ dst, const float* __restrict__ src, int64_t n)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        dst[i] = DType<T>::FromF(src[i]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    CastVec4Kernel(T* __restrict__ dst, const float* __restrict__ src, int64_t groups)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < groups; i += stride) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(src) + i);
+        const float vals[4] = {v.x, v.y, v.z, v.w};
+        StorePack<T, 4>(dst + i * 4, vals);
+    }
+}
+
+} // namespace
+
+int NumSMs()
+{
+    if (g_numSMs == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
+            g_numSMs = n;
+        } else {
+            (void)cudaGetLastError();
+            return kNumSMsFallback;
+        }
+    }
+    return g_numSMs;
+}
+
+void CountLaunch(int n) { g_launches += static_cast<uint64_t>(n); }
+uint64_t LaunchCount() { return g_launches; }
+void ResetLaunchCount() { g_launches = 0; }
+
+cudaError_t StridedCopy(int elemSize, void* contiguous, void* viewBase, View4 v, bool toView, cudaStream_t s)
+{
+    const int64_t total = v.dim[0] * v.dim[1] * v.dim[2] * v.dim[3];
+    if (total == 0) {
+        return cudaSuccess;
+    }
+    if (elemSize == 4) {
+        StridedCopyKernel<uint32_t><<<GridFor(total, kThreads), kThreads, 0, s>>>(
+            static_cast<uint32_t*>(contiguous), static_cast<uint32_t*>(viewBase), v, toView, total);
+    } else {
+        StridedCopyKernel<uint16_t><<<GridFor(total, kThreads), kThreads, 0, s>>>(
+            static_cast<uint16_t*>(contiguous), static_cast<uint16_t*>(viewBase), v, toView, total);
+    }
+    CountLaunch();
+    return cudaGetLastError();
+}
+
+cudaError_t CopyBytes(void* dst, const void* src, uint64_t bytes, cudaStream_t s)
+{
+    if (bytes == 0 || dst == src) {
+        return cudaSuccess;
+    }
+    CountLaunch();
+    return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s);
+}
+
+cudaError_t CastFromF32(Dt dt, void* dst, const float* src, int64_t n, cudaStream_t s)
+{
+    if (n == 0) {
+        return cudaSuccess;
+    }
+    if (dt == Dt::F32) {
+        return CopyBytes(dst, src, static_cast<uint64_t>(n) * 4, s);
+    }
+    const bool vec = n % 4 == 0 && Aligned(dst, 8) && Aligned(src, 16);
+    if (dt == Dt::F16) {
+        if (vec) {
+            CastVec4Kernel<__half><<<GridFor(n / 4, kThreads), kThreads, 0, s>>>(static_cast<__half*>(dst), src, n / 4);
+        } else {
+            CastKernel<__half><<<GridFor(n, kThreads), kThreads, 0, s>>>(static_cast<__half*>(dst), src, n);
+        }
+    } else {
+        if (vec) {
+            CastVec4Kernel<__nv_bfloat16><<<GridFor(n / 4, kThreads), kThreads, 0, s>>>(
+                static_cast<__nv_bfloat16*>(dst), src, n / 4);
+        } else {
+            CastKernel<__nv_bfloat16><<<GridFor(n, kThreads), kThreads, 0, s>>>(static_cast<__nv_bfloat16*>(dst), src,
+                                                                                n);
+        }
+    }
+    CountLaunch();
+    return cudaGetLastError();
+}
+
+} // namespace opscv

@@ -1,0 +1,259 @@
+"""First-phase behaviour of the aclnn entry points, without a GPU: the library loads, exports every symbol the
+headers declare, and returns the reference's status codes for invalid arguments. Mirrors the reference's
+op_api unit tests, which assert only the GetWorkspaceSize status (e.g.
+image/upsample_bilinear2d/tests/ut/op_host/op_api/test_aclnn_upsample_bilinear_2d.cpp:92-110: null self ->
+ACLNN_ERR_INNER_NULLPTR; image/grid_sampler2_d_grad/tests/ut/op_host/op_api/
+test_aclnn_grid_sampler2d_backward.cpp:86-197: one ACLNN_ERR_PARAM_NULLPTR case per tensor, :391-532 integer
+dtypes -> ACLNN_ERR_PARAM_INVALID).
+
+No compute call is made: tensors wrap host memory and only phase one runs.
+"""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+OK, NULLPTR, INVALID, INNER_NULL = 0, 161001, 161002, 561103
+
+
+def phase1(ops, name, *args):
+    ws = ctypes.c_uint64(123)
+    ex = ctypes.c_void_p(None)
+    status = getattr(ops.lib(), name + "GetWorkspaceSize")(*args, ctypes.byref(ws), ctypes.byref(ex))
+    if ex.value:
+        assert ops.lib().aclDestroyAclOpExecutor(ex) == 0
+    return status, ws.value
+
+
+_KEEP = []  # handles must outlive the calls that receive their raw pointers
+
+
+def T(ops, shape, dtype=torch.float32, fmt="NCHW"):
+    h = ops.acl_tensor(torch.zeros(shape, dtype=dtype), fmt)
+    _KEEP.append(h)
+    return h
+
+
+def IA(ops, values):
+    h = ops.int_array(values)
+    _KEEP.append(h)
+    return h
+
+
+def BA(ops, values):
+    h = ops.bool_array(values)
+    _KEEP.append(h)
+    return h
+
+
+def test_library_exports_every_declared_symbol(ops):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    declared = set()
+    for header in ("aclnn_resample.h", "opscv_acl.h"):
+        text = open(os.path.join(root, "include", header)).read()
+        declared |= set(re.findall(r"ACLNN_API\s+[\w\s\*]+?\b(\w+)\s*\(", text))
+    assert len(declared) >= 36
+    handle = ctypes.CDLL(ops.LIB_PATH)
+    missing = [s for s in sorted(declared) if not hasattr(handle, s)]
+    assert not missing, missing
+    assert declared == set(ops.SYMBOLS), declared ^ set(ops.SYMBOLS)
+    assert ops.lib().opscvVersion() >= 100
+
+
+def test_nearest_forward_status(ops):
+    x, y, sz = T(ops, (2, 3, 4, 5)), T(ops, (2, 3, 8, 10)), IA(ops, [8, 10])
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, sz.ptr, y.ptr)[0] == OK
+    assert phase1(ops, "aclnnUpsampleNearest2d", None, sz.ptr, y.ptr)[0] == NULLPTR
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, None, y.ptr)[0] == NULLPTR
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, sz.ptr, None)[0] == NULLPTR
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, sz.ptr, T(ops, (2, 3, 8, 10), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearest2d", T(ops, (2, 3, 4, 5), torch.int32).ptr, sz.ptr,
+                  T(ops, (2, 3, 8, 10), torch.int32).ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, IA(ops, [8]).ptr, y.ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearest2d", T(ops, (3, 4, 5)).ptr, sz.ptr, y.ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, IA(ops, [8, 11]).ptr, y.ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, sz.ptr, T(ops, (2, 4, 8, 10)).ptr)[0] == INVALID  # C differs
+    assert phase1(ops, "aclnnUpsampleNearest2d", x.ptr, sz.ptr, T(ops, (2, 3, 8, 10), fmt="NHWC").ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearest2d", T(ops, (2, 3, 4, 5), fmt="ND").ptr, sz.ptr,
+                  T(ops, (2, 3, 8, 10), fmt="ND").ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearest2d", T(ops, (2, 3, 0, 5)).ptr, sz.ptr, y.ptr)[0] == INVALID
+    # empty batch: success without workspace
+    st, ws = phase1(ops, "aclnnUpsampleNearest2d", T(ops, (0, 3, 4, 5)).ptr, sz.ptr, T(ops, (0, 3, 8, 10)).ptr)
+    assert (st, ws) == (OK, 0)
+    # NHWC
+    xn, yn = T(ops, (2, 4, 5, 3), fmt="NHWC"), T(ops, (2, 8, 10, 3), fmt="NHWC")
+    assert phase1(ops, "aclnnUpsampleNearest2d", xn.ptr, sz.ptr, yn.ptr)[0] == OK
+    # V2 takes float scales
+    assert phase1(ops, "aclnnUpsampleNearest2dV2", x.ptr, sz.ptr, ctypes.c_float(2.0), ctypes.c_float(2.0),
+                  y.ptr)[0] == OK
+    assert phase1(ops, "aclnnUpsampleNearest2dV2", None, sz.ptr, ctypes.c_float(2.0), ctypes.c_float(2.0),
+                  y.ptr)[0] == NULLPTR
+
+
+def test_bilinear_forward_status(ops):
+    x, y, sz = T(ops, (1, 3, 64, 64)), T(ops, (1, 3, 128, 128)), IA(ops, [128, 128])
+    args = lambda a, s, o, sh=0.0, sw=0.0: (a, s, False, sh, sw, o)  # noqa: E731
+    st, ws = phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, sz.ptr, y.ptr))
+    assert st == OK and ws > 0 and ws % 256 == 0
+    # the reference returns the INNER null-pointer code for a null self / out
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(None, sz.ptr, y.ptr))[0] == INNER_NULL
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, sz.ptr, None))[0] == INNER_NULL
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, None, y.ptr))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, IA(ops, [128]).ptr, y.ptr))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, IA(ops, [128, 64]).ptr, y.ptr))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, sz.ptr, y.ptr, -1.0, 2.0))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, sz.ptr, T(ops, (1, 3, 128, 128), torch.bfloat16).ptr))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(T(ops, (1, 3, 64, 64), torch.float64).ptr, sz.ptr,
+                                                        T(ops, (1, 3, 128, 128), torch.float64).ptr))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, sz.ptr, T(ops, (2, 3, 128, 128)).ptr))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(T(ops, (3, 64, 64)).ptr, sz.ptr, y.ptr))[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, sz.ptr, T(ops, (1, 128, 128, 3), fmt="NHWC").ptr))[0] == INVALID
+    assert "aclnnUpsampleBilinear2d" in ops.last_error()
+    # same size: copy plan, no workspace for contiguous tensors
+    st, ws = phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, IA(ops, [64, 64]).ptr, T(ops, (1, 3, 64, 64)).ptr))
+    assert (st, ws) == (OK, 0)
+    # a strided output needs staging space on top of the tables
+    big = torch.zeros((1, 3, 128, 256))
+    yv = ops.acl_tensor(big[:, :, :, ::2], "NCHW")
+    _KEEP.append(yv)
+    st2, ws2 = phase1(ops, "aclnnUpsampleBilinear2d", *args(x.ptr, sz.ptr, yv.ptr))
+    assert st2 == OK and ws2 >= ws + 3 * 128 * 128 * 4
+
+
+def test_backward_status(ops):
+    g, out = T(ops, (2, 3, 8, 10)), T(ops, (2, 3, 4, 5))
+    osz, isz = IA(ops, [8, 10]), IA(ops, [2, 3, 4, 5])
+    for name, extra in (("aclnnUpsampleNearest2dBackward", ()), ("aclnnUpsampleBilinear2dBackward", (False,)),
+                        ("aclnnUpsampleBilinear2dBackwardV2", (True,)), ("aclnnUpsampleBicubic2dAAGrad", (False,))):
+        def call(gp, op, ip, outp, sh=0.0, sw=0.0):
+            return phase1(ops, name, gp, op, ip, *extra, sh, sw, outp)[0]
+        assert call(g.ptr, osz.ptr, isz.ptr, out.ptr) == OK, name
+        assert call(None, osz.ptr, isz.ptr, out.ptr) == NULLPTR, name
+        assert call(g.ptr, None, isz.ptr, out.ptr) == NULLPTR, name
+        assert call(g.ptr, osz.ptr, None, out.ptr) == NULLPTR, name
+        assert call(g.ptr, osz.ptr, isz.ptr, None) == NULLPTR, name
+        assert call(g.ptr, IA(ops, [8]).ptr, isz.ptr, out.ptr) == INVALID, name
+        assert call(g.ptr, osz.ptr, IA(ops, [2, 3, 4]).ptr, out.ptr) == INVALID, name
+        assert call(g.ptr, IA(ops, [8, 11]).ptr, isz.ptr, out.ptr) == INVALID, name
+        if name != "aclnnUpsampleBilinear2dBackward":  # that one lets fp32 grads produce any supported dtype
+            assert call(g.ptr, osz.ptr, isz.ptr, T(ops, (2, 3, 4, 5), torch.float16).ptr) == INVALID, name
+        assert call(T(ops, (2, 3, 8, 10), torch.int32).ptr, osz.ptr, isz.ptr, T(ops, (2, 3, 4, 5), torch.int32).ptr) == INVALID, name
+        assert call(g.ptr, osz.ptr, IA(ops, [2, 3, 0, 5]).ptr, out.ptr) == INVALID, name
+    # bilinear backward: fp32 grads may produce a 16-bit gradient (resize_bilinear_v2_grad dtype rule)
+    assert phase1(ops, "aclnnUpsampleBilinear2dBackward", g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0,
+                  T(ops, (2, 3, 4, 5), torch.bfloat16).ptr)[0] == OK
+    assert phase1(ops, "aclnnUpsampleBilinear2dBackward", T(ops, (2, 3, 8, 10), torch.float16).ptr, osz.ptr, isz.ptr,
+                  False, 0.0, 0.0, T(ops, (2, 3, 4, 5), torch.float32).ptr)[0] == INVALID
+    # bicubic AA: NCHW / ND only, negative scales rejected
+    assert phase1(ops, "aclnnUpsampleBicubic2dAAGrad", T(ops, (2, 8, 10, 3), fmt="NHWC").ptr, osz.ptr,
+                  IA(ops, [2, 4, 5, 3]).ptr, False, 0.0, 0.0, T(ops, (2, 4, 5, 3), fmt="NHWC").ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBicubic2dAAGrad", g.ptr, osz.ptr, isz.ptr, False, -1.0, 0.0, out.ptr)[0] == INVALID
+
+
+def test_bicubic_aa_forward_status(ops):
+    x, y, sz = T(ops, (2, 3, 32, 32)), T(ops, (2, 3, 7, 9)), IA(ops, [7, 9])
+    st, ws = phase1(ops, "aclnnUpsampleBicubic2dAA", x.ptr, sz.ptr, False, 0.0, 0.0, y.ptr)
+    assert st == OK and ws > 0
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", None, sz.ptr, False, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", x.ptr, None, False, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", x.ptr, sz.ptr, False, 0.0, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", x.ptr, IA(ops, [7, 9, 1]).ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", x.ptr, IA(ops, [7, 8]).ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", x.ptr, IA(ops, [0, 9]).ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", x.ptr, sz.ptr, False, 0.0, 0.0, T(ops, (2, 3, 7, 9), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", T(ops, (2, 32, 32, 3), fmt="NHWC").ptr, sz.ptr, False, 0.0, 0.0,
+                  T(ops, (2, 7, 9, 3), fmt="NHWC").ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleBicubic2dAA", T(ops, (2, 3, 32, 32), fmt="ND").ptr, sz.ptr, False, 0.0, 0.0,
+                  T(ops, (2, 3, 7, 9), fmt="ND").ptr)[0] == OK
+
+
+def test_grid_sampler_status(ops):
+    x, grid, out = T(ops, (2, 3, 6, 7)), T(ops, (2, 5, 4, 2), fmt="ND"), T(ops, (2, 3, 5, 4))
+    call = lambda *a: phase1(ops, "aclnnGridSampler2D", *a)[0]  # noqa: E731
+    assert call(x.ptr, grid.ptr, 0, 0, False, out.ptr) == OK
+    assert call(None, grid.ptr, 0, 0, False, out.ptr) == NULLPTR
+    assert call(x.ptr, None, 0, 0, False, out.ptr) == NULLPTR
+    assert call(x.ptr, grid.ptr, 0, 0, False, None) == NULLPTR
+    for bad in (-1, 3):
+        assert call(x.ptr, grid.ptr, bad, 0, False, out.ptr) == INVALID
+        assert call(x.ptr, grid.ptr, 0, bad, False, out.ptr) == INVALID
+    assert call(x.ptr, T(ops, (2, 5, 4, 2), torch.float16, "ND").ptr, 0, 0, False, out.ptr) == INVALID
+    assert call(x.ptr, grid.ptr, 0, 0, False, T(ops, (2, 3, 5, 4), torch.float16).ptr) == INVALID
+    for dt in (torch.uint8, torch.int32, torch.int64, torch.float64):
+        assert call(T(ops, (2, 3, 6, 7), dt).ptr, T(ops, (2, 5, 4, 2), dt, "ND").ptr, 0, 0, False,
+                    T(ops, (2, 3, 5, 4), dt).ptr) == INVALID
+    assert call(x.ptr, T(ops, (3, 5, 4, 2), fmt="ND").ptr, 0, 0, False, out.ptr) == INVALID      # batch
+    assert call(x.ptr, grid.ptr, 0, 0, False, T(ops, (2, 4, 5, 4)).ptr) == INVALID                # channels
+    assert call(x.ptr, grid.ptr, 0, 0, False, T(ops, (2, 3, 5, 5)).ptr) == INVALID                # H/W
+    assert call(x.ptr, T(ops, (2, 5, 4, 3), fmt="ND").ptr, 0, 0, False, out.ptr) == INVALID       # last dim != 2
+    assert call(T(ops, (2, 3, 0, 7)).ptr, grid.ptr, 0, 0, False, out.ptr) == INVALID
+    assert call(T(ops, (3, 6, 7)).ptr, grid.ptr, 0, 0, False, out.ptr) == INVALID
+
+
+def test_grid_sampler_backward_status(ops):
+    x, grid, go = T(ops, (1, 1, 5, 8)), T(ops, (1, 3, 3, 2), fmt="ND"), T(ops, (1, 1, 3, 3))
+    gi, gg, mask = T(ops, (1, 1, 5, 8)), T(ops, (1, 3, 3, 2), fmt="ND"), BA(ops, [True, True])
+
+    def call(go_, x_, grid_, gi_, gg_, mask_=mask.ptr, interp=0, pad=0):
+        return phase1(ops, "aclnnGridSampler2DBackward", go_, x_, grid_, interp, pad, False, mask_, gi_, gg_)
+
+    st, ws = call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr)
+    assert st == OK and ws == 0  # fp32, atomic mode: accumulates in place
+    for i in range(5):  # one null tensor at a time
+        args = [go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr]
+        args[i] = None
+        assert call(*args)[0] == NULLPTR
+    assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, mask_=None) == (OK, 0)          # null mask: no-op
+    assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, mask_=BA(ops, [False, False]).ptr) == (OK, 0)
+    assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, mask_=BA(ops, [True]).ptr)[0] == INVALID
+    assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, interp=3)[0] == INVALID
+    assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, pad=-1)[0] == INVALID
+    assert call(go.ptr, x.ptr, grid.ptr, T(ops, (1, 1, 5, 7)).ptr, gg.ptr)[0] == INVALID
+    assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, T(ops, (1, 3, 4, 2), fmt="ND").ptr)[0] == INVALID
+    assert call(T(ops, (1, 2, 3, 3)).ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr)[0] == INVALID
+    for dt in (torch.uint8, torch.int8, torch.int16, torch.int32, torch.int64, torch.bool):
+        if dt not in (torch.uint8, torch.int32, torch.int64):
+            continue  # the ctypes caller maps only these integer dtypes
+        assert call(T(ops, (1, 1, 3, 3), dt).ptr, T(ops, (1, 1, 5, 8), dt).ptr, T(ops, (1, 3, 3, 2), dt, "ND").ptr,
+                    T(ops, (1, 1, 5, 8), dt).ptr, T(ops, (1, 3, 3, 2), dt, "ND").ptr)[0] == INVALID
+    assert call(T(ops, (1, 1, 3, 3), torch.float16).ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr)[0] == INVALID
+    # 16-bit tensors accumulate in an fp32 workspace; deterministic mode needs the segment lists
+    h = torch.float16
+    st, ws16 = call(T(ops, (1, 1, 3, 3), h).ptr, T(ops, (1, 1, 5, 8), h).ptr, T(ops, (1, 3, 3, 2), h, "ND").ptr,
+                    T(ops, (1, 1, 5, 8), h).ptr, T(ops, (1, 3, 3, 2), h, "ND").ptr)
+    assert st == OK and ws16 >= 40 * 4
+    ops.set_deterministic(True)
+    try:
+        st, wsdet = call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr)
+    finally:
+        ops.set_deterministic(False)
+    assert st == OK and wsdet >= 4 * 9 * 8
+
+
+def test_options_and_executor_lifecycle(ops):
+    L = ops.lib()
+    v = ctypes.c_int64(-1)
+    assert L.aclrtCtxGetSysParamOpt(0, ctypes.byref(v)) == 0 and v.value == 0
+    assert L.aclrtCtxSetSysParamOpt(0, 1) == 0
+    assert L.aclrtCtxGetSysParamOpt(0, ctypes.byref(v)) == 0 and v.value == 1
+    assert L.aclrtCtxSetSysParamOpt(0, 0) == 0
+    assert L.aclrtCtxSetSysParamOpt(7, 0) != 0
+    assert L.opscvSetBackwardAlgo(1) == 0 and L.opscvGetBackwardAlgo() == 1
+    assert L.opscvSetBackwardAlgo(5) == INVALID
+    assert L.opscvSetBackwardAlgo(0) == 0
+    # executors: destroying twice, or running a destroyed one, is rejected instead of touching freed memory
+    x, y, sz = T(ops, (1, 3, 4, 4)), T(ops, (1, 3, 8, 8)), IA(ops, [8, 8])
+    ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(None)
+    assert L.aclnnUpsampleNearest2dGetWorkspaceSize(x.ptr, sz.ptr, y.ptr, ctypes.byref(ws), ctypes.byref(ex)) == 0
+    # second phase validates the workspace before any CUDA call
+    assert L.aclnnUpsampleNearest2d(None, ws.value, ex, None) == NULLPTR
+    assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(256), ws.value - 1, ex, None) == INVALID
+    assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(257), ws.value, ex, None) == INVALID
+    assert L.aclnnUpsampleBilinear2d(ctypes.c_void_p(256), ws.value, ex, None) == INVALID  # wrong operator
+    assert L.aclDestroyAclOpExecutor(ex) == 0
+    assert L.aclDestroyAclOpExecutor(ex) == INVALID
+    assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(256), ws.value, ex, None) == INVALID
+    assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(256), ws.value, None, None) == NULLPTR
+    assert L.aclCreateTensor(None, 4, 0, None, 0, 0, None, 0, None) is None

@@ -1,0 +1,417 @@
+"""GPU parity: the CUDA library, called through its C ABI, against the CPU oracle on the same seeded inputs.
+
+Bars (written into each assertion):
+  * integer tables (source indices, window bounds), nearest forward, nearest-mode grid sampling: bit-exact;
+  * fp32 interpolated values and gradients: rtol 1e-5 / atol 1e-6 (most kernels keep the oracle's operation
+    order and are in fact bit-identical, which is asserted where it holds by construction);
+  * fp16 / bf16: the fp32 result rounded once; at most 1 ulp of the output dtype from the rounded oracle value.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-5, 1e-6
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def ulp_diff(a, b):
+    """Distance in units of the last place between two tensors of one 16-bit (or 32-bit) float dtype."""
+    it = {torch.float16: torch.int16, torch.bfloat16: torch.int16, torch.float32: torch.int32}[a.dtype]
+    ai, bi = a.contiguous().view(it).to(torch.int64), b.contiguous().view(it).to(torch.int64)
+    sign = 1 << (15 if a.dtype != torch.float32 else 31)
+    ai = torch.where(ai < 0, -(ai + sign) - 0, ai)  # map sign-magnitude to a monotone integer line
+    bi = torch.where(bi < 0, -(bi + sign) - 0, bi)
+    return (ai - bi).abs().max().item() if a.numel() else 0
+
+
+def check(got, ref32, dtype, exact=False, rtol=RTOL, atol=ATOL):
+    """got: device tensor of `dtype`; ref32: fp32 numpy oracle result (before the final rounding)."""
+    got = got.detach().cpu()
+    ref = torch.from_numpy(np.ascontiguousarray(ref32))
+    assert got.shape == ref.shape
+    if dtype == torch.float32:
+        if exact:
+            assert torch.equal(got, ref), f"max abs diff {(got - ref).abs().max().item()}"
+        else:
+            np.testing.assert_allclose(got.numpy(), ref.numpy(), rtol=rtol, atol=atol)
+    else:
+        want = ref.to(dtype)
+        if exact:
+            assert torch.equal(got, want)
+        else:
+            d = ulp_diff(got, want)
+            assert d <= 1, f"{d} ulp of {dtype}"
+
+
+def quant(x, dtype):
+    """Round an fp32 tensor to the storage dtype; returns (storage tensor, its exact fp32 value as numpy)."""
+    xs = x.to(dtype)
+    return xs, xs.float().numpy()
+
+
+def nhwc(a):
+    return np.ascontiguousarray(np.transpose(a, (0, 2, 3, 1)))
+
+
+SHAPES = [
+    # (N, C, Hin, Win, Hout, Wout)
+    (1, 3, 64, 64, 128, 128),   # configs[0]
+    (2, 8, 14, 14, 28, 28),     # exact 2x
+    (2, 3, 7, 9, 15, 20),       # ragged up-scale
+    (1, 4, 16, 24, 5, 7),       # down-scale
+    (1, 2, 1, 1, 3, 5),         # 1x1 input
+    (2, 2, 5, 6, 1, 1),         # 1x1 output
+    (1, 1, 3, 1, 7, 1),         # one column
+    (1, 5, 9, 8, 9, 16),        # one axis unchanged
+    (1, 16, 6, 8, 12, 16),      # C multiple of 8 (NHWC vector path), W multiple of 8
+]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# tables
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("sizes", [(64, 128), (56, 112), (7, 15), (16, 5), (1, 4), (5, 1), (1024, 224), (96, 96 * 3)])
+def test_axis_tables_bit_exact(ops, oracle, sizes):
+    i, o = sizes
+    for scale in (0.0, 2.0, 1.7):
+        src, _, _ = ops.debug_axis_table("nearest_fwd", i, o, user_scale=scale)
+        assert np.array_equal(src, oracle.nearest_src_index(i, o, scale))
+        s, e, _ = ops.debug_axis_table("nearest_bwd", i, o, user_scale=scale)
+        rs, re = oracle.nearest_bwd_ranges(i, o, scale)
+        assert np.array_equal(s, rs) and np.array_equal(e, re)
+        for align in (False, True):
+            lo, hi, d = ops.debug_axis_table("bilinear", i, o, align, scale)
+            rlo, rhi, rd = oracle.bilinear_table(i, o, align, scale)
+            assert np.array_equal(lo, rlo) and np.array_equal(hi, rhi)
+            assert np.array_equal(d.view(np.int32), rd.view(np.int32))  # fp32 weights bit for bit
+            xmin, xsize, w = ops.debug_axis_table("bicubic_aa", i, o, align, scale)
+            rmin, rsize, rw = oracle.bicubic_aa_table(i, o, align, scale)
+            assert np.array_equal(xmin, rmin) and np.array_equal(xsize, rsize)
+            assert w.shape[1] >= rw.shape[1]
+            assert np.array_equal(w[:, :rw.shape[1]].view(np.int32), rw.view(np.int32))
+            assert not w[:, rw.shape[1]:].any()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# nearest
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("fmt", ["NCHW", "NHWC"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_nearest_forward_backward(ops, oracle, dev, dtype, fmt, shape):
+    n, c, hi, wi, ho, wo = shape
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(1)), dtype)
+    g, g32 = quant(torch.randn((n, c, ho, wo), generator=gen(2)), dtype)
+    f = oracle.NCHW if fmt == "NCHW" else oracle.NHWC
+    if fmt == "NHWC":
+        x, x32 = x.permute(0, 2, 3, 1).contiguous(), nhwc(x32)
+        g, g32 = g.permute(0, 2, 3, 1).contiguous(), nhwc(g32)
+    y = ops.upsample_nearest2d(x.to(dev), (ho, wo), fmt)
+    check(y, oracle.nearest2d_fwd(x32, (ho, wo), fmt=f), dtype, exact=True)
+    gi = ops.upsample_nearest2d_backward(g.to(dev), (ho, wo), tuple(x.shape), fmt)
+    check(gi, oracle.nearest2d_bwd(g32, (hi, wi), fmt=f), dtype, exact=True)  # same fp32 summation order
+
+
+def test_nearest_v2_user_scales(ops, oracle, dev):
+    x = torch.randn((1, 2, 5, 6), generator=gen(3))
+    y = ops.upsample_nearest2d(x.to(dev), (12, 16), scales=(2.5, 2.7))
+    check(y, oracle.nearest2d_fwd(x.numpy(), (12, 16), (2.5, 2.7)), torch.float32, exact=True)
+    g = torch.randn((1, 2, 12, 16), generator=gen(4))
+    gi = ops.upsample_nearest2d_backward(g.to(dev), (12, 16), (1, 2, 5, 6), scales=(2.5, 2.7))
+    check(gi, oracle.nearest2d_bwd(g.numpy(), (5, 6), (2.5, 2.7)), torch.float32, exact=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# bilinear
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("fmt", ["NCHW", "NHWC"])
+@pytest.mark.parametrize("align", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_bilinear_forward(ops, oracle, dev, dtype, fmt, align, shape):
+    n, c, hi, wi, ho, wo = shape
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(5)), dtype)
+    f = oracle.NCHW if fmt == "NCHW" else oracle.NHWC
+    if fmt == "NHWC":
+        x, x32 = x.permute(0, 2, 3, 1).contiguous(), nhwc(x32)
+    y = ops.upsample_bilinear2d(x.to(dev), (ho, wo), align, fmt)
+    check(y, oracle.bilinear2d_fwd(x32, (ho, wo), align, fmt=f), dtype, exact=True)  # same operation order
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("fmt", ["NCHW", "NHWC"])
+@pytest.mark.parametrize("align", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_bilinear_backward_gather(ops, oracle, dev, dtype, fmt, align, shape):
+    n, c, hi, wi, ho, wo = shape
+    g, g32 = quant(torch.randn((n, c, ho, wo), generator=gen(6)), dtype)
+    f = oracle.NCHW if fmt == "NCHW" else oracle.NHWC
+    in_shape = (n, c, hi, wi)
+    if fmt == "NHWC":
+        g, g32 = g.permute(0, 2, 3, 1).contiguous(), nhwc(g32)
+        in_shape = (n, hi, wi, c)
+    for v2 in (False, True):
+        gi = ops.upsample_bilinear2d_backward(g.to(dev), (ho, wo), in_shape, align, fmt, v2=v2)
+        # the gather adds the scatter kernel's products in the serial scatter order: identical to that oracle
+        check(gi, oracle.bilinear2d_bwd(g32, (hi, wi), align, fmt=f, definition="scatter"), dtype, exact=True)
+    if dtype == torch.float32:
+        # and within tolerance of the reference's deterministic (gather) formulation
+        np.testing.assert_allclose(gi.cpu().numpy(),
+                                   oracle.bilinear2d_bwd(g32, (hi, wi), align, fmt=f, definition="gather"),
+                                   rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("fmt", ["NCHW", "NHWC"])
+def test_bilinear_backward_atomic_mode(ops, oracle, dev, dtype, fmt):
+    n, c, hi, wi, ho, wo = 2, 8, 14, 12, 28, 24
+    g, g32 = quant(torch.randn((n, c, ho, wo), generator=gen(7)), dtype)
+    f = oracle.NCHW if fmt == "NCHW" else oracle.NHWC
+    in_shape = (n, c, hi, wi)
+    if fmt == "NHWC":
+        g, g32 = g.permute(0, 2, 3, 1).contiguous(), nhwc(g32)
+        in_shape = (n, hi, wi, c)
+    ops.set_backward_algo("atomic")
+    try:
+        gi = ops.upsample_bilinear2d_backward(g.to(dev), (ho, wo), in_shape, False, fmt)
+    finally:
+        ops.set_backward_algo("gather")
+    check(gi, oracle.bilinear2d_bwd(g32, (hi, wi), False, fmt=f), dtype)
+
+
+def test_bilinear_user_scales_and_mixed_dtype(ops, oracle, dev):
+    x = torch.randn((1, 2, 8, 8), generator=gen(8))
+    y = ops.upsample_bilinear2d(x.to(dev), (16, 16), False, scales=(2.0, 2.0))
+    check(y, oracle.bilinear2d_fwd(x.numpy(), (16, 16), False, (2.0, 2.0)), torch.float32, exact=True)
+    # user scales that disagree with the size ratio (the reference's "determine_scales" situation)
+    g = torch.randn((1, 2, 20, 22), generator=gen(9))
+    gi = ops.upsample_bilinear2d_backward(g.to(dev), (20, 22), (1, 2, 8, 8), False, scales=(2.0, 2.0))
+    check(gi, oracle.bilinear2d_bwd(g.numpy(), (8, 8), False, (2.0, 2.0)), torch.float32, exact=True)
+    # fp32 grads -> bf16 gradient
+    gi16 = ops.upsample_bilinear2d_backward(g.to(dev), (20, 22), (1, 2, 8, 8), False, out_dtype=torch.bfloat16)
+    check(gi16, oracle.bilinear2d_bwd(g.numpy(), (8, 8), False), torch.bfloat16, exact=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# bicubic, anti-aliased
+# ---------------------------------------------------------------------------------------------------------------
+AA_SHAPES = [(1, 2, 32, 40, 7, 9), (2, 3, 64, 64, 14, 14), (1, 2, 6, 7, 13, 15), (1, 1, 9, 9, 9, 4),
+             (1, 3, 128, 96, 28, 21), (1, 1, 5, 5, 1, 1), (1, 2, 1, 1, 4, 4), (1, 1, 40, 3, 8, 3)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("align", [False, True])
+@pytest.mark.parametrize("shape", AA_SHAPES)
+def test_bicubic_aa_forward(ops, oracle, dev, dtype, align, shape):
+    n, c, hi, wi, ho, wo = shape
+    x, x32 = quant(torch.rand((n, c, hi, wi), generator=gen(10)), dtype)
+    y = ops.upsample_bicubic2d_aa(x.to(dev), (ho, wo), align)
+    check(y, oracle.bicubic_aa_fwd(x32, (ho, wo), align), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("align", [False, True])
+@pytest.mark.parametrize("shape", AA_SHAPES)
+@pytest.mark.parametrize("algo", ["gather", "atomic"])
+def test_bicubic_aa_backward(ops, oracle, dev, dtype, align, shape, algo):
+    n, c, hi, wi, ho, wo = shape
+    g, g32 = quant(torch.randn((n, c, ho, wo), generator=gen(11)), dtype)
+    ops.set_backward_algo(algo)
+    try:
+        gi = ops.upsample_bicubic2d_aa_grad(g.to(dev), (ho, wo), (n, c, hi, wi), align)
+    finally:
+        ops.set_backward_algo("gather")
+    ref = oracle.bicubic_aa_bwd(g32, (hi, wi), align, definition="scatter")
+    check(gi, ref, dtype, atol=2e-6)
+    if dtype == torch.float32:
+        np.testing.assert_allclose(gi.cpu().numpy(), oracle.bicubic_aa_bwd(g32, (hi, wi), align, definition="gather"),
+                                   rtol=1e-4, atol=1e-5)
+
+
+def test_bicubic_aa_user_scales(ops, oracle, dev):
+    x = torch.rand((1, 2, 20, 24), generator=gen(12))
+    y = ops.upsample_bicubic2d_aa(x.to(dev), (10, 8), False, scales=(0.5, 1.0 / 3.0))
+    check(y, oracle.bicubic_aa_fwd(x.numpy(), (10, 8), False, (0.5, 1.0 / 3.0)), torch.float32)
+    g = torch.randn((1, 2, 10, 8), generator=gen(13))
+    gi = ops.upsample_bicubic2d_aa_grad(g.to(dev), (10, 8), (1, 2, 20, 24), False, scales=(0.5, 1.0 / 3.0))
+    check(gi, oracle.bicubic_aa_bwd(g.numpy(), (20, 24), False, (0.5, 1.0 / 3.0)), torch.float32, atol=2e-6)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# grid sampler
+# ---------------------------------------------------------------------------------------------------------------
+def make_grid(n, ho, wo, seed, span=1.1):
+    return torch.rand((n, ho, wo, 2), generator=gen(seed)) * (2 * span) - span
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interp", [0, 1, 2])
+@pytest.mark.parametrize("pad", [0, 1, 2])
+@pytest.mark.parametrize("align", [False, True])
+def test_grid_sampler_forward(ops, oracle, dev, dtype, interp, pad, align):
+    n, c, hi, wi, ho, wo = 2, 5, 9, 11, 6, 7
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(20)), dtype)
+    grid, grid32 = quant(make_grid(n, ho, wo, 21, 1.3), dtype)
+    y = ops.grid_sampler2d(x.to(dev), grid.to(dev), interp, pad, align)
+    # same operation order as the oracle: the fp32 result is identical
+    check(y, oracle.grid_sampler2d_fwd(x32, grid32, interp, pad, align), dtype, exact=True)
+
+
+def test_grid_sampler_forward_special_values(ops, oracle, dev):
+    x = torch.randn((1, 3, 4, 5), generator=gen(22))
+    grid = make_grid(1, 3, 4, 23)
+    grid[0, 0, 0, 0] = float("nan")
+    grid[0, 0, 1, 1] = float("inf")
+    grid[0, 1, 0, 0] = -float("inf")
+    grid[0, 1, 1] = torch.tensor([1e10, -1e10])
+    grid[0, 2, 0] = torch.tensor([-1.0, 1.0])
+    for interp in (0, 1):
+        for pad in (0, 1, 2):
+            y = ops.grid_sampler2d(x.to(dev), grid.to(dev), interp, pad, False).cpu().numpy()
+            ref = oracle.grid_sampler2d_fwd(x.numpy(), grid.numpy(), interp, pad, False)
+            assert np.array_equal(np.isnan(y), np.isnan(ref)), (interp, pad)
+            assert np.array_equal(np.nan_to_num(y), np.nan_to_num(ref)), (interp, pad)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interp", [0, 1])
+@pytest.mark.parametrize("pad", [0, 1, 2])
+@pytest.mark.parametrize("align", [False, True])
+@pytest.mark.parametrize("det", [False, True])
+def test_grid_sampler_backward(ops, oracle, dev, dtype, interp, pad, align, det):
+    n, c, hi, wi, ho, wo = 2, 5, 9, 11, 12, 23
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(24)), dtype)
+    grid, grid32 = quant(make_grid(n, ho, wo, 25, 1.2), dtype)
+    g, g32 = quant(torch.randn((n, c, ho, wo), generator=gen(26)), dtype)
+    ops.set_deterministic(det)
+    try:
+        gi, gg = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), interp, pad, align)
+        if det:
+            gi2, gg2 = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), interp, pad, align)
+            assert torch.equal(gi.view(torch.int16 if dtype != torch.float32 else torch.int32),
+                               gi2.view(torch.int16 if dtype != torch.float32 else torch.int32))
+            assert torch.equal(gg, gg2) or (torch.isnan(gg) == torch.isnan(gg2)).all()
+    finally:
+        ops.set_deterministic(False)
+    ri, rg = oracle.grid_sampler2d_bwd(g32, x32, grid32, interp, pad, align)
+    check(gi, ri, dtype, atol=2e-6)
+    check(gg, rg, dtype, exact=True)  # per-sample channel sum in channel order, as the oracle
+
+
+def test_grid_sampler_backward_masks_and_collisions(ops, oracle, dev):
+    # every sample hits the same source pixel: worst case for atomics and for the deterministic segment lists
+    n, c, hi, wi, ho, wo = 1, 3, 4, 4, 40, 37
+    x = torch.randn((n, c, hi, wi), generator=gen(27))
+    grid = torch.zeros((n, ho, wo, 2)) + 0.01
+    g = torch.randn((n, c, ho, wo), generator=gen(28))
+    ri, rg = oracle.grid_sampler2d_bwd(g.numpy(), x.numpy(), grid.numpy())
+    for det in (False, True):
+        ops.set_deterministic(det)
+        try:
+            gi, gg = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev))
+            np.testing.assert_allclose(gi.cpu().numpy(), ri, rtol=1e-4, atol=1e-4)
+            assert np.array_equal(gg.cpu().numpy(), rg)
+            # masks: an unrequested output is left untouched
+            sentinel = torch.full_like(x, 7.0).to(dev)
+            gi3, gg3 = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), mask=(False, True),
+                                                   input_grad=sentinel)
+            assert torch.equal(gi3.cpu(), torch.full_like(x, 7.0)) and np.array_equal(gg3.cpu().numpy(), rg)
+            sentinel_g = torch.full_like(grid, 7.0).to(dev)
+            gi4, gg4 = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), mask=(True, False),
+                                                   grid_grad=sentinel_g)
+            assert torch.equal(gg4.cpu(), torch.full_like(grid, 7.0))
+            np.testing.assert_allclose(gi4.cpu().numpy(), ri, rtol=1e-4, atol=1e-4)
+        finally:
+            ops.set_deterministic(False)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# views, empties, golden fixtures
+# ---------------------------------------------------------------------------------------------------------------
+def test_strided_views(ops, oracle, dev):
+    base = torch.randn((2, 3, 10, 24), generator=gen(30)).to(dev)
+    x = base[:, :, 1:8, ::2]  # non-contiguous input view
+    assert not x.is_contiguous()
+    out_base = torch.zeros((2, 3, 14, 48), device=dev)
+    out = out_base[:, :, :, ::2]  # non-contiguous output view
+    ops.upsample_bilinear2d(x, (14, 24), False, out=out)
+    ref = oracle.bilinear2d_fwd(x.cpu().numpy(), (14, 24), False)
+    assert np.array_equal(out.cpu().numpy(), ref)
+    assert not out_base[:, :, :, 1::2].any()  # the gaps of the view are untouched
+    # channels-last storage passed as an NCHW view (strides (HWC, 1, WC, C))
+    xc = torch.randn((2, 4, 6, 5), generator=gen(31)).to(dev).contiguous(memory_format=torch.channels_last)
+    y = ops.upsample_nearest2d(xc, (12, 10))
+    assert np.array_equal(y.cpu().numpy(), oracle.nearest2d_fwd(xc.cpu().numpy(), (12, 10)))
+    grid = make_grid(2, 3, 4, 32).to(dev)
+    gs = ops.grid_sampler2d(xc, grid)
+    assert np.array_equal(gs.cpu().numpy(), oracle.grid_sampler2d_fwd(xc.cpu().numpy(), grid.cpu().numpy()))
+
+
+def test_empty_tensors_are_noops(ops, dev):
+    x = torch.zeros((0, 3, 4, 5), device=dev)
+    assert ops.upsample_nearest2d(x, (8, 10)).shape == (0, 3, 8, 10)
+    assert ops.upsample_bilinear2d(x, (8, 10)).shape == (0, 3, 8, 10)
+    assert ops.upsample_bicubic2d_aa(x, (2, 2)).shape == (0, 3, 2, 2)
+    assert ops.grid_sampler2d(x, torch.zeros((0, 2, 2, 2), device=dev)).shape == (0, 3, 2, 2)
+    before = ops.launch_count()
+    ops.upsample_nearest2d(x, (8, 10))
+    assert ops.launch_count() == before
+
+
+def test_golden_fixtures_on_gpu(ops, dev):
+    """The committed reference goldens (see tests/golden/make_golden.py), at the reference tests' own tolerance."""
+    import ast
+    import os
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "resample_golden.npz"))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
+    for m in gold["meta.interp"]:
+        name, mode, shape, out, align, scales = ast.literal_eval(str(m))
+        sc = scales if scales is not None else (0.0, 0.0)
+        x, g = t(gold[name + ".x"]), t(gold[name + ".g"])
+        if mode == "nearest":
+            y = ops.upsample_nearest2d(x, out, scales=None if scales is None else sc)
+            gx = ops.upsample_nearest2d_backward(g, out, shape, scales=sc)
+        elif name.startswith("bilinear"):
+            y = ops.upsample_bilinear2d(x, out, align, scales=sc)
+            gx = ops.upsample_bilinear2d_backward(g, out, shape, align, scales=sc)
+        else:
+            y = ops.upsample_bicubic2d_aa(x, out, align, scales=sc)
+            gx = ops.upsample_bicubic2d_aa_grad(g, out, shape, align, scales=sc)
+        np.testing.assert_allclose(y.cpu().numpy(), gold[name + ".y"], rtol=1e-4, atol=1e-5, err_msg=name)
+        np.testing.assert_allclose(gx.cpu().numpy(), gold[name + ".gx"], rtol=1e-4, atol=2e-5, err_msg=name)
+    for mi, mode in enumerate(["bilinear", "nearest", "bicubic"]):
+        for pi, pad in enumerate(["zeros", "border", "reflection"]):
+            for align in (False, True):
+                name = f"grid.{mode}.{pad}.{'ac' if align else 'hp'}"
+                x, grid = t(gold[name + ".x"]), t(gold[name + ".grid"])
+                y = ops.grid_sampler2d(x, grid, mi, pi, align)
+                np.testing.assert_allclose(y.cpu().numpy(), gold[name + ".y"], rtol=1e-4, atol=1e-5, err_msg=name)
+                if mode != "bicubic":
+                    gi, gg = ops.grid_sampler2d_backward(t(gold[name + ".g"]), x, grid, mi, pi, align)
+                    np.testing.assert_allclose(gi.cpu().numpy(), gold[name + ".gx"], rtol=1e-4, atol=1e-5)
+                    np.testing.assert_allclose(gg.cpu().numpy(), gold[name + ".ggrid"], rtol=1e-3, atol=1e-4)
+    y = ops.upsample_bilinear2d(t(gold["example.bilinear.x"]), (8, 4), True, scales=(2.0, 2.0))
+    np.testing.assert_allclose(y.cpu().numpy(), gold["example.bilinear.y"], rtol=1e-5, atol=1e-6)
+
+
+def test_second_phase_consumes_executor(ops, dev):
+    import ctypes
+    L = ops.lib()
+    x = torch.randn((1, 1, 4, 4), device=dev)
+    y = torch.empty((1, 1, 8, 8), device=dev)
+    tx, ty, sz = ops.acl_tensor(x), ops.acl_tensor(y), ops.int_array([8, 8])
+    ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(None)
+    assert L.aclnnUpsampleNearest2dGetWorkspaceSize(tx.ptr, sz.ptr, ty.ptr, ctypes.byref(ws), ctypes.byref(ex)) == 0
+    buf = torch.empty(ws.value, dtype=torch.uint8, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(buf.data_ptr()), ws.value, ex, stream) == 0
+    # the executor is gone: a second call must fail cleanly (two_phase_api.md: phase 2 may not be repeated)
+    assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(buf.data_ptr()), ws.value, ex, stream) == 161002
+    torch.cuda.synchronize()
+    assert torch.equal(y.cpu(), x.cpu().repeat_interleave(2, 2).repeat_interleave(2, 3))
