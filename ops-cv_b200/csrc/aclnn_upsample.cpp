@@ -811,7 +811,7 @@ aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const a
     const AAOffsets oh = AllocAA(ws, sh.hout, ah.taps), ow = AllocAA(ws, sh.wout, aw.taps);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
-        cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, s);
+        cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, false, s);
         if (e != cudaSuccess) {
             return e;
         }
@@ -915,13 +915,17 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
     const AxisGeom gh{sh.hin, sh.hout, ah.scale}, gw{sh.win, sh.wout, aw.scale};
     const AAOffsets oh = AllocAA(ws, sh.hout, ah.taps), ow = AllocAA(ws, sh.wout, aw.taps);
     const bool atomic = GetBackwardAlgo() == 1 && GetDeterministic() == 0;
+    // With scale == 0 (align_corners and a single output pixel) the reference's two backward kernels disagree on
+    // the filter centre: the default (atomic) kernel uses 0.5, the deterministic one keeps the forward's 0
+    // (upsample_bicubic2d_aa_grad_simt_base.h:38 vs ..._simt_base_deter.h:96). Follow whichever the mode selects.
+    const bool bwdCentre = GetDeterministic() == 0;
     if (atomic) {
         const int64_t elems = gi.n * gi.c * gi.h * gi.w;
         const bool needAcc = dt != Dt::F32;
         const uint64_t accOff = needAcc ? ws.Alloc(static_cast<uint64_t>(elems) * 4) : 0;
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
-            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, s);
+            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, bwdCentre, s);
             if (e != cudaSuccess) {
                 return e;
             }
@@ -933,7 +937,7 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
-            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, s);
+            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, bwdCentre, s);
             if (e != cudaSuccess) {
                 return e;
             }
@@ -1050,7 +1054,7 @@ aclnnStatus opscvDebugAxisTable(int32_t kind, int64_t inSize, int64_t outSize, i
             }
             if (e == cudaSuccess) {
                 e = BuildAATables(g, g, aa.inv, aa.inv, aa.support, aa.support, AAAxis{d0, d1, df, aa.taps},
-                                  AAAxis{s0, s1, sf, aa.taps}, nullptr);
+                                  AAAxis{s0, s1, sf, aa.taps}, false, nullptr);
             }
             if (e == cudaSuccess) {
                 e = cudaDeviceSynchronize();

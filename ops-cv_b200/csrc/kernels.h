@@ -52,8 +52,9 @@ cudaError_t BuildLerpTables(AxisGeom h, AxisGeom w, bool halfPixel, int variant,
 // For every grad_input index y: [first, first+count) = the grad_output indices i with lo[i] == y or hi[i] == y.
 cudaError_t BuildLerpBwdRanges(AxisGeom h, AxisGeom w, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw,
                                cudaStream_t s);
+// backward = true: centre rule of the reference's backward kernel (0.5 when the scale is 0).
 cudaError_t BuildAATables(AxisGeom h, AxisGeom w, float invH, float invW, float supH, float supW, AAAxis th,
-                          AAAxis tw, cudaStream_t s);
+                          AAAxis tw, bool backward, cudaStream_t s);
 // For every forward-input index y: [start, end) = output indices whose window covers y.
 cudaError_t BuildAABwdRanges(AxisGeom h, AxisGeom w, AAAxis th, AAAxis tw, RangeAxis rh, RangeAxis rw,
                              cudaStream_t s);

@@ -160,7 +160,7 @@ __device__ __forceinline__ float CubicFilterAA(float m)
 
 // upsample_bicubic2d_aa_simt_base.h:70-124: window [xmin, xmin+xsize), weights normalised by their sum.
 __global__ void AATableKernel(AxisGeom gh, AxisGeom gw, float invH, float invW, float supH, float supW, AAAxis th,
-                              AAAxis tw)
+                              AAAxis tw, int backward)
 {
     const bool isH = blockIdx.y == 0;
     const AxisGeom g = isH ? gh : gw;
@@ -171,7 +171,12 @@ __global__ void AATableKernel(AxisGeom gh, AxisGeom gw, float invH, float invW, 
     if (i >= g.out) {
         return;
     }
-    const float center = Mul(g.scale, Add(static_cast<float>(i), 0.5f));
+    // The backward kernel places the centre at 0.5 when the scale is 0 (align_corners with a single output,
+    // upsample_bicubic2d_aa_grad_simt_base.h:38); the forward kernel does not (simt_base.h:72-73).
+    float center = Mul(g.scale, Add(static_cast<float>(i), 0.5f));
+    if (backward) {
+        center = (g.scale > 0.0f) ? Mul(Add(static_cast<float>(i), 0.5f), g.scale) : 0.5f;
+    }
     long long lo = static_cast<long long>(floorf(Add(Sub(center, support), 0.5f)));
     long long hi = static_cast<long long>(floorf(Add(Add(center, support), 0.5f)));
     lo = lo > 0 ? lo : 0;
@@ -271,9 +276,10 @@ cudaError_t BuildLerpBwdRanges(AxisGeom h, AxisGeom w, LerpAxis th, LerpAxis tw,
 }
 
 cudaError_t BuildAATables(AxisGeom h, AxisGeom w, float invH, float invW, float supH, float supW, AAAxis th,
-                          AAAxis tw, cudaStream_t s)
+                          AAAxis tw, bool backward, cudaStream_t s)
 {
-    AATableKernel<<<TableGrid(h.out, w.out), kTableThreads, 0, s>>>(h, w, invH, invW, supH, supW, th, tw);
+    AATableKernel<<<TableGrid(h.out, w.out), kTableThreads, 0, s>>>(h, w, invH, invW, supH, supW, th, tw,
+                                                                    backward ? 1 : 0);
     CountLaunch();
     return cudaGetLastError();
 }

@@ -229,9 +229,22 @@ def test_bicubic_aa_backward(ops, oracle, dev, dtype, align, shape, algo):
         ops.set_backward_algo("gather")
     ref = oracle.bicubic_aa_bwd(g32, (hi, wi), align, definition="scatter")
     check(gi, ref, dtype, atol=2e-6)
+    # The reference's deterministic kernel is a second formulation of the same gradient. The two agree except when
+    # the scale is 0 (align_corners with a single output pixel), where they place the filter centre differently;
+    # the library follows the kernel the mode selects.
+    ops.set_deterministic(True)
+    try:
+        gd = ops.upsample_bicubic2d_aa_grad(g.to(dev), (ho, wo), (n, c, hi, wi), align)
+        gd2 = ops.upsample_bicubic2d_aa_grad(g.to(dev), (ho, wo), (n, c, hi, wi), align)
+    finally:
+        ops.set_deterministic(False)
+    assert torch.equal(gd, gd2)
+    rd = oracle.bicubic_aa_bwd(g32, (hi, wi), align, definition="gather")
     if dtype == torch.float32:
-        np.testing.assert_allclose(gi.cpu().numpy(), oracle.bicubic_aa_bwd(g32, (hi, wi), align, definition="gather"),
-                                   rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(gd.cpu().numpy(), rd, rtol=1e-4, atol=1e-5)
+    degenerate = align and (ho == 1 or wo == 1)
+    if not degenerate and dtype == torch.float32:
+        np.testing.assert_allclose(gi.cpu().numpy(), rd, rtol=1e-4, atol=1e-5)
 
 
 def test_bicubic_aa_user_scales(ops, oracle, dev):
