@@ -352,6 +352,9 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
         });
     } else {
         const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
+        // user scales that differ from the size ratio change how many grads rows feed one grad_input row
+        const bool exactScale = alignCorners || (ah.scale == static_cast<float>(gi.h) / static_cast<float>(gg.h) &&
+                                                 aw.scale == static_cast<float>(gi.w) / static_cast<float>(gg.w));
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
@@ -363,7 +366,7 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
             if (e != cudaSuccess) {
                 return e;
             }
-            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, s);
+            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, exactScale, ah.scale, aw.scale, s);
         });
     }
     FinishOutput(out, y, ex);

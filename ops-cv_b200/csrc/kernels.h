@@ -71,9 +71,12 @@ cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, R
                        cudaStream_t s);
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
                         cudaStream_t s);
-// Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
+// Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype. scaleH/W = the scales the tables were built
+// with; exactScale = they equal in/out (or the align_corners ratio), i.e. source coordinates never overshoot the
+// input. Both are needed by the staged row-walk kernel to bound its taps.
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
-                              LerpAxis tw, RangeAxis rh, RangeAxis rw, cudaStream_t s);
+                              LerpAxis tw, RangeAxis rh, RangeAxis rw, bool exactScale, float scaleH, float scaleW,
+                              cudaStream_t s);
 // Scatter backward with fp32 atomics into `acc` (fp32, N*C*hin*win, zeroed by this call). If dtOut is fp32 the
 // caller passes acc == gi; otherwise a cast pass writes gi.
 cudaError_t BilinearBwdAtomic(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, float* acc, Shape4 sh,

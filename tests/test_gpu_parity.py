@@ -158,8 +158,11 @@ def test_bilinear_backward_gather(ops, oracle, dev, dtype, fmt, align, shape):
         in_shape = (n, hi, wi, c)
     for v2 in (False, True):
         gi = ops.upsample_bilinear2d_backward(g.to(dev), (ho, wo), in_shape, align, fmt, v2=v2)
-        # the gather adds the scatter kernel's products in the serial scatter order: identical to that oracle
-        check(gi, oracle.bilinear2d_bwd(g32, (hi, wi), align, fmt=f, definition="scatter"), dtype, exact=True)
+        # NHWC: the gather adds the scatter kernel's products in the serial scatter order: identical to that
+        # oracle. NCHW: separable row walk with fused multiply-adds, fixed order: within tolerance (<= 1 ulp 16-bit).
+        check(gi, oracle.bilinear2d_bwd(g32, (hi, wi), align, fmt=f, definition="scatter"), dtype, exact=(fmt == "NHWC"))
+        gi_again = ops.upsample_bilinear2d_backward(g.to(dev), (ho, wo), in_shape, align, fmt, v2=v2)
+        assert torch.equal(gi.cpu().view(torch.uint8), gi_again.cpu().view(torch.uint8))  # reproducible
     if dtype == torch.float32:
         # and within tolerance of the reference's deterministic (gather) formulation
         np.testing.assert_allclose(gi.cpu().numpy(),
@@ -195,7 +198,7 @@ def test_bilinear_user_scales_and_mixed_dtype(ops, oracle, dev):
     check(gi, oracle.bilinear2d_bwd(g.numpy(), (8, 8), False, (2.0, 2.0)), torch.float32, exact=True)
     # fp32 grads -> bf16 gradient
     gi16 = ops.upsample_bilinear2d_backward(g.to(dev), (20, 22), (1, 2, 8, 8), False, out_dtype=torch.bfloat16)
-    check(gi16, oracle.bilinear2d_bwd(g.numpy(), (8, 8), False), torch.bfloat16, exact=True)
+    check(gi16, oracle.bilinear2d_bwd(g.numpy(), (8, 8), False), torch.bfloat16)
 
 
 # ---------------------------------------------------------------------------------------------------------------
