@@ -151,13 +151,14 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
     const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, go.w, userScaleW)};
     const uint64_t offH = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.hout));
     const uint64_t offW = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.wout));
+    const NearestPlan plan = MakeNearestFwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const NearestAxis th{reinterpret_cast<int32_t*>(w + offH)}, tw{reinterpret_cast<int32_t*>(w + offW)};
         cudaError_t e = BuildNearestFwdTables(ah, aw, th, tw, s);
         if (e != cudaSuccess) {
             return e;
         }
-        return NearestFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, s);
+        return NearestFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, plan, s);
     });
     FinishOutput(out, y, ex);
     ex->workspaceSize = ws.Size();
@@ -352,9 +353,7 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
         });
     } else {
         const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
-        // user scales that differ from the size ratio change how many grads rows feed one grad_input row
-        const bool exactScale = alignCorners || (ah.scale == static_cast<float>(gi.h) / static_cast<float>(gg.h) &&
-                                                 aw.scale == static_cast<float>(gi.w) / static_cast<float>(gg.w));
+        const BilinearPlan plan = MakeBilinearBwdPlan(dtIn, lay, sh, ah, aw, halfPixel);
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
@@ -366,7 +365,7 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
             if (e != cudaSuccess) {
                 return e;
             }
-            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, exactScale, ah.scale, aw.scale, s);
+            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, plan, s);
         });
     }
     FinishOutput(out, y, ex);
@@ -537,13 +536,14 @@ aclnnStatus aclnnUpsampleNearest2dBackwardGetWorkspaceSize(const aclTensor* grad
     const AxisGeom ah{sh.hin, sh.hout, NearestScale(gi.h, gg.h, static_cast<float>(scalesH))};
     const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, gg.w, static_cast<float>(scalesW))};
     const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
+    const NearestPlan plan = MakeNearestBwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const RangeAxis th = RangeAt(w, rh), tw = RangeAt(w, rw);
         cudaError_t e = BuildNearestBwdTables(ah, aw, th, tw, s);
         if (e != cudaSuccess) {
             return e;
         }
-        return NearestBwd(dt, lay, g.At(w), y.At(w), sh, th, tw, s);
+        return NearestBwd(dt, lay, g.At(w), y.At(w), sh, th, tw, plan, s);
     });
     FinishOutput(gradInput, y, ex);
     ex->workspaceSize = ws.Size();
@@ -632,13 +632,14 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     const AxisGeom aw{sh.win, sh.wout, BilinearScale(gi.w, go.w, alignCorners, static_cast<float>(scalesW))};
     const bool halfPixel = !alignCorners; // resize_bilinear_v2.cpp:99
     const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
+    const BilinearPlan plan = MakeBilinearFwdPlan(dt, lay, sh, ah, aw, halfPixel);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
         cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 0, th, tw, s);
         if (e != cudaSuccess) {
             return e;
         }
-        return BilinearFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, s);
+        return BilinearFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, plan, s);
     });
     FinishOutput(out, y, ex);
     ex->workspaceSize = ws.Size();

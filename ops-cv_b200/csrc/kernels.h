@@ -65,18 +65,35 @@ struct Shape4 {
     int32_t hin, win, hout, wout; // hin/win = forward input extent, hout/wout = forward output extent
 };
 
+// Launch plans are made in the first phase, on the host, from exact host copies of the index tables
+// (host_tables.h), and frozen into the executor.
+struct NearestPlan {
+    enum Schedule : int32_t { kDirect = 0, kTiled = 1, kInteger = 2 };
+    int32_t schedule;
+    int32_t tileRows; // kTiled: output rows per block
+    int32_t bandRows; // kTiled: most input rows any tile reads (sizes the shared-memory stage)
+    int32_t rh, rw;   // kInteger: replication factors
+};
+NearestPlan MakeNearestFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw);
+NearestPlan MakeNearestBwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw);
 cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, NearestAxis th, NearestAxis tw,
-                       cudaStream_t s);
+                       const NearestPlan& plan, cudaStream_t s);
 cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, RangeAxis th, RangeAxis tw,
-                       cudaStream_t s);
+                       const NearestPlan& plan, cudaStream_t s);
+struct BilinearPlan {
+    enum Schedule : int32_t { kDirect = 0, kTiled = 1, kW2 = 2 };
+    int32_t schedule;
+    int32_t tileRows; // kTiled: output (forward) / grad_input (backward) rows per block
+    int32_t bandRows; // kTiled: most rows of the other tensor any tile reads
+    int32_t tapsW;    // kTiled backward: most grads columns feeding one grad_input column
+};
+BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
+BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
-                        cudaStream_t s);
-// Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype. scaleH/W = the scales the tables were built
-// with; exactScale = they equal in/out (or the align_corners ratio), i.e. source coordinates never overshoot the
-// input. Both are needed by the staged row-walk kernel to bound its taps.
+                        const BilinearPlan& plan, cudaStream_t s);
+// Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
-                              LerpAxis tw, RangeAxis rh, RangeAxis rw, bool exactScale, float scaleH, float scaleW,
-                              cudaStream_t s);
+                              LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s);
 // Scatter backward with fp32 atomics into `acc` (fp32, N*C*hin*win, zeroed by this call). If dtOut is fp32 the
 // caller passes acc == gi; otherwise a cast pass writes gi.
 cudaError_t BilinearBwdAtomic(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, float* acc, Shape4 sh,

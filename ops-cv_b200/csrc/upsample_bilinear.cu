@@ -1,26 +1,33 @@
 // UpsampleBilinear2d forward and backward.
 //
-// Forward, NCHW: a block copies the input rows its band of output rows reads into shared memory (coalesced
-// 16-byte loads, tile_stage.cuh). A thread owns one 16-byte group of output columns and walks down a chunk of output rows. The
-// reference formula  (1-dy)*((1-dx)*TL + dx*TR) + dy*((1-dx)*BL + dx*BR)  is a vertical blend of two horizontally
-// interpolated input rows, so the thread keeps the horizontal interpolation of the current top and bottom input
-// rows in registers and only touches memory when the walk reaches a new input row: for 2x up-sampling that is
-// one gathered load per output element instead of four, with bit-identical results.
-// Forward, NHWC: a thread owns 16 bytes of channels of one output pixel; the four taps are 16-byte loads.
+// The reference formula  (1-dy)*((1-dx)*TL + dx*TR) + dy*((1-dx)*BL + dx*BR)  is a vertical blend of two
+// horizontally interpolated input rows. All NCHW forward kernels use that: a thread owns a group of output columns,
+// walks down a run of output rows, keeps the horizontal interpolation of the current top and bottom input rows in
+// registers and touches memory only when the walk reaches a new input row. The operation order is the
+// reference's, so results are bit-identical to it.
 //
-// Backward, gather (default and deterministic mode). NCHW: the grads rows feeding a band of grad_input rows are
-// staged in shared memory; a thread owns a group of grad_input columns, holds their horizontal tap weights in
-// registers and walks down the grads rows: each grads row is reduced horizontally once and added, with its two
-// vertical weights, to the (at most two) grad_input rows it touches. Fixed summation order: reproducible.
-// NHWC (and NCHW shapes the walk does not cover): a thread owns a 16-byte group of grad_input elements and sums, in
-// grads row-major order, the products the reference's scatter kernel would add to them; equal to that kernel run
-// serially.
-// Backward, atomic: the scatter itself with fp32 atomics (kept selectable; slower than the gather here).
+// Kernel schedules (chosen on the host from exact copies of the index tables, see MakeBilinearFwdPlan /
+// MakeBilinearBwdPlan):
+//   * NCHW, output width = 2 x input width (FPN-style up-sampling): input-major. A thread loads one vector of four
+//     input columns (plus one neighbour on each side) per input row and produces the eight output columns they
+//     feed; loads and stores are coalesced vectors and every input element is fetched once per row walk.
+//     The backward is the transpose: a thread loads eight grads columns (plus neighbours) per grads row, reduces
+//     them to four grad_input columns and adds the row, with its two vertical weights, to the (at most two)
+//     grad_input rows it touches.
+//   * NCHW, any other scale: the same walks over shared memory. A block copies the rows its band reads into shared
+//     memory (coalesced 16-byte loads, tile_stage.cuh); horizontal taps are shared-memory reads.
+//   * NCHW rows too long to stage, user scales that overshoot the input, unaligned tensors: direct kernels.
+//   * NHWC: a thread owns 16 bytes of channels of one pixel; taps are 16-byte global loads.
+// Backward results are reproducible in every schedule (fixed summation order, no atomics). The direct and NHWC
+// backward kernels add the reference scatter kernel's products in its serial order and equal it bit for bit; the
+// row-walk kernels reduce rows first (separable, fused multiply-add) and agree to fp32 rounding.
+// The atomic scatter (the reference's non-deterministic schedule) is kept selectable; it is slower here.
 //
 // Reference arithmetic: image/resize_bilinear_v2/op_kernel/arch35/resize_bilinear_v2_simt_nchw.h:84-146,
 // _simt_nhwc.h:88-151; image/resize_bilinear_v2_grad/op_kernel/arch35/resize_bilinear_v2_grad_simt.h:107-152.
 #include <algorithm>
 
+#include "host_tables.h"
 #include "launch_util.cuh"
 #include "tile_stage.cuh"
 
@@ -28,8 +35,7 @@ namespace opscv {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kWalkThreads = 256;
-constexpr int64_t kStageBudget = 32 * 1024; // staged bytes per block: keeps >= 6 blocks resident per SM
+constexpr int64_t kStageBudget = 24 * 1024; // staged bytes per block: keeps 8 blocks resident per SM
 
 // ---- forward, NCHW ----------------------------------------------------------------------------------------
 template <typename T, int V>
@@ -104,12 +110,35 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// Vertical blend shared by the forward walks: given the horizontal interpolations of the top and bottom rows.
+template <typename T, int V>
+__device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const float (&bot)[V], float dy)
+{
+    const float dy1 = Sub(1.0f, dy);
+    float out[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        out[k] = Add(Mul(dy1, top[k]), Mul(dy, bot[k]));
+    }
+    StorePack<T, V>(dst, out);
+}
+
+// Splits the rows [h0, h1) of a tile among the row-threads of a block: thread `rc` of `rowThreads` gets [ha, hb).
+__device__ __forceinline__ void RowChunk(int32_t h0, int32_t h1, int32_t rc, int32_t rowThreads, int32_t& ha,
+                                         int32_t& hb)
+{
+    const int32_t chunk = (h1 - h0 + rowThreads - 1) / rowThreads;
+    ha = min(h1, h0 + rc * chunk);
+    hb = min(h1, ha + chunk);
+}
+
 // ---- forward, NCHW, shared-memory staged ---------------------------------------------------------------------
+// grid.x = planes * tilesPerPlane. A tile is `tileRows` output rows; its input rows [lo[h0], hi[h1-1]] are staged
+// (the host sized the tile so that they fit).
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
     BilinearFwdTileKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
-                          int32_t wout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t tilesPerPlane,
-                          int64_t capElems)
+                          int32_t wout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t tilesPerPlane)
 {
     extern __shared__ __align__(16) unsigned char smemRaw[];
     const int64_t p = blockIdx.x / tilesPerPlane;
@@ -117,25 +146,17 @@ __global__ void __launch_bounds__(kThreads)
     const int32_t h0 = tile * tileRows, h1 = min(hout, h0 + tileRows);
     const int32_t r0 = __ldg(th.lo + h0), r1 = __ldg(th.hi + h1 - 1) + 1;
     const T* plane = x + p * hin * static_cast<int64_t>(win);
-    const int64_t count = static_cast<int64_t>(r1 - r0) * win;
-    const T* src = plane;
-    int32_t rbase = 0;
-    if (count <= capElems) {
-        src = StageSpan<T>(plane + static_cast<int64_t>(r0) * win, count, smemRaw);
-        rbase = r0;
-    }
+    const T* src = StageSpan<T>(plane + static_cast<int64_t>(r0) * win, static_cast<int64_t>(r1 - r0) * win, smemRaw);
     __syncthreads();
-    // Lanes of a warp take adjacent column groups (whole warps per row), so that their shared-memory reads fall in
-    // adjacent words (no bank conflicts) and each warp stores one contiguous run per row.
     const int32_t groups = wout / V;
-    const int32_t colThreads = min((groups + 31) & ~31, static_cast<int32_t>(blockDim.x));
+    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
     const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
     const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
     if (rc >= rowThreads) {
         return;
     }
-    const int32_t chunk = (h1 - h0 + rowThreads - 1) / rowThreads;
-    const int32_t ha = h0 + rc * chunk, hb = min(h1, ha + chunk);
+    int32_t ha, hb;
+    RowChunk(h0, h1, rc, rowThreads, ha, hb);
     T* yp = y + p * hout * static_cast<int64_t>(wout);
     for (int32_t g = cg0; g < groups; g += colThreads) {
         int32_t wl[V], wh[V];
@@ -149,9 +170,9 @@ __global__ void __launch_bounds__(kThreads)
         }
         float top[V], bot[V];
         int32_t curTop = -1, curBot = -1;
+        T* dst = yp + static_cast<int64_t>(ha) * wout + g * V;
         for (int32_t h = ha; h < hb; ++h) {
             const int32_t lo = __ldg(th.lo + h), hi = __ldg(th.hi + h);
-            const float dy = __ldg(th.delta + h);
             if (lo != curTop) {
                 if (lo == curBot) {
 #pragma unroll
@@ -159,7 +180,7 @@ __global__ void __launch_bounds__(kThreads)
                         top[k] = bot[k];
                     }
                 } else {
-                    const T* xr = src + static_cast<int64_t>(lo - rbase) * win;
+                    const T* xr = src + (lo - r0) * win;
 #pragma unroll
                     for (int k = 0; k < V; ++k) {
                         top[k] = Add(Mul(dx1[k], DType<T>::ToF(xr[wl[k]])), Mul(dx[k], DType<T>::ToF(xr[wh[k]])));
@@ -174,7 +195,7 @@ __global__ void __launch_bounds__(kThreads)
                         bot[k] = top[k];
                     }
                 } else {
-                    const T* xr = src + static_cast<int64_t>(hi - rbase) * win;
+                    const T* xr = src + (hi - r0) * win;
 #pragma unroll
                     for (int k = 0; k < V; ++k) {
                         bot[k] = Add(Mul(dx1[k], DType<T>::ToF(xr[wl[k]])), Mul(dx[k], DType<T>::ToF(xr[wh[k]])));
@@ -182,14 +203,323 @@ __global__ void __launch_bounds__(kThreads)
                 }
                 curBot = hi;
             }
-            const float dy1 = Sub(1.0f, dy);
-            float out[V];
+            BlendStore<T, V>(dst, top, bot, __ldg(th.delta + h));
+            dst += wout;
+        }
+    }
+}
+
+// ---- forward, NCHW, output width = 2 x input width, input-major ---------------------------------------------------
+// The host has verified the column pattern lo[w] = max((w-1)>>1, 0), hi[w] = w ? min((w+1)>>1, win-1) : 0, so the
+// eight outputs of input columns c0..c0+3 read columns c0-1..c0+4 (clamped). Weights still come from the table.
+// grid.x = planes * tilesPerPlane; rows are table-driven (any vertical scale).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
+                        LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t tilesPerPlane)
+{
+    constexpr int VI = 4, VO = 8;
+    const int32_t wout = 2 * win;
+    const int64_t p = blockIdx.x / tilesPerPlane;
+    const int32_t tile = blockIdx.x - p * tilesPerPlane;
+    const int32_t h0 = tile * tileRows, h1 = min(hout, h0 + tileRows);
+    const int32_t groups = win / VI;
+    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
+    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
+    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
+    if (rc >= rowThreads) {
+        return;
+    }
+    int32_t ha, hb;
+    RowChunk(h0, h1, rc, rowThreads, ha, hb);
+    const T* xp = x + p * hin * static_cast<int64_t>(win);
+    T* yp = y + p * hout * static_cast<int64_t>(wout);
+    for (int32_t g = cg0; g < groups; g += colThreads) {
+        const int32_t c0 = g * VI;
+        const int32_t cl = max(c0 - 1, 0), cr = min(c0 + VI, win - 1);
+        float dx[VO], dx1[VO];
+#pragma unroll
+        for (int k = 0; k < VO; ++k) {
+            dx[k] = __ldg(tw.delta + c0 * 2 + k);
+            dx1[k] = Sub(1.0f, dx[k]);
+        }
+        auto loadRow = [&](int32_t r, float (&h)[VO]) {
+            const T* xr = xp + static_cast<int64_t>(r) * win;
+            float v[VI + 2]; // columns c0-1 .. c0+4
+            v[0] = DType<T>::Load(xr + cl);
+            float mid[VI];
+            LoadPackLdg<T, VI>(xr + c0, mid);
+#pragma unroll
+            for (int k = 0; k < VI; ++k) {
+                v[k + 1] = mid[k];
+            }
+            v[VI + 1] = DType<T>::Load(xr + cr);
+#pragma unroll
+            for (int j = 0; j < VI; ++j) {
+                // outputs 2(c0+j) (taps c0+j-1, c0+j) and 2(c0+j)+1 (taps c0+j, c0+j+1)
+                h[2 * j] = Add(Mul(dx1[2 * j], v[j]), Mul(dx[2 * j], v[j + 1]));
+                h[2 * j + 1] = Add(Mul(dx1[2 * j + 1], v[j + 1]), Mul(dx[2 * j + 1], v[j + 2]));
+            }
+        };
+        float top[VO], bot[VO];
+        int32_t curTop = -1, curBot = -1;
+        T* dst = yp + static_cast<int64_t>(ha) * wout + c0 * 2;
+        for (int32_t h = ha; h < hb; ++h) {
+            const int32_t lo = __ldg(th.lo + h), hi = __ldg(th.hi + h);
+            if (lo != curTop) {
+                if (lo == curBot) {
+#pragma unroll
+                    for (int k = 0; k < VO; ++k) {
+                        top[k] = bot[k];
+                    }
+                } else {
+                    loadRow(lo, top);
+                }
+                curTop = lo;
+            }
+            if (hi != curBot) {
+                if (hi == curTop) {
+#pragma unroll
+                    for (int k = 0; k < VO; ++k) {
+                        bot[k] = top[k];
+                    }
+                } else {
+                    loadRow(hi, bot);
+                }
+                curBot = hi;
+            }
+            BlendStore<T, VO>(dst, top, bot, __ldg(th.delta + h));
+            dst += wout;
+        }
+    }
+}
+
+// ---- backward row walk ---------------------------------------------------------------------------------------
+// Combined weight with which grads index j feeds input index xcol: (lo == xcol ? 1-d : 0) + (hi == xcol ? d : 0).
+__device__ __forceinline__ float CombinedWeight(const LerpAxis& t, int32_t j, int32_t xcol)
+{
+    const float d = __ldg(t.delta + j);
+    float w = 0.0f;
+    if (__ldg(t.lo + j) == xcol) {
+        w = Sub(1.0f, d);
+    }
+    if (__ldg(t.hi + j) == xcol) {
+        w = Add(w, d);
+    }
+    return w;
+}
+
+// Vertical part of the walk, shared by the staged and the input-major kernels. `reduceRow(i, hp)` fills hp[] with the
+// horizontally reduced grads row i for this thread's V grad_input columns. Rows [ya, yb) of grad_input are
+// produced; grads rows are visited in increasing order and each contributes to rows lo[i] and hi[i] only.
+template <typename TOut, int V, typename F>
+__device__ __forceinline__ void WalkRows(TOut* dstBase, int32_t win, int32_t ya, int32_t yb, const LerpAxis& th,
+                                         const RangeAxis& rh, F reduceRow)
+{
+    float accA[V], accB[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        accA[k] = 0.0f;
+        accB[k] = 0.0f;
+    }
+    int32_t cur = ya;
+    TOut* dst = dstBase + static_cast<int64_t>(ya) * win;
+    const int32_t is = __ldg(rh.start + ya), ie = max(is, __ldg(rh.end + yb - 1));
+    for (int32_t i = is; i < ie; ++i) {
+        const int32_t loY = __ldg(th.lo + i), hiY = __ldg(th.hi + i);
+        const float dY = __ldg(th.delta + i);
+        while (cur < loY && cur < yb) { // rows below lo[i] are complete
+            StorePack<TOut, V>(dst, accA);
+            dst += win;
 #pragma unroll
             for (int k = 0; k < V; ++k) {
-                out[k] = Add(Mul(dy1, top[k]), Mul(dy, bot[k]));
+                accA[k] = accB[k];
+                accB[k] = 0.0f;
             }
-            StorePack<T, V>(yp + static_cast<int64_t>(h) * wout + g * V, out);
+            ++cur;
         }
+        if (cur >= yb) {
+            break;
+        }
+        float hp[V];
+        reduceRow(i, hp);
+        const float wLo = Sub(1.0f, dY), wHi = dY;
+        if (loY == cur) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                accA[k] = fmaf(wLo, hp[k], accA[k]);
+            }
+        } else if (loY == cur + 1) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                accB[k] = fmaf(wLo, hp[k], accB[k]);
+            }
+        }
+        if (hiY == cur) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                accA[k] = fmaf(wHi, hp[k], accA[k]);
+            }
+        } else if (hiY == cur + 1 && cur + 1 < yb) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                accB[k] = fmaf(wHi, hp[k], accB[k]);
+            }
+        }
+    }
+    while (cur < yb) {
+        StorePack<TOut, V>(dst, accA);
+        dst += win;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            accA[k] = accB[k];
+            accB[k] = 0.0f;
+        }
+        ++cur;
+    }
+}
+
+// ---- backward, NCHW, shared-memory staged ------------------------------------------------------------------------
+// KW = compile-time bound on the number of grads columns feeding one grad_input column (the host checks it).
+template <typename TIn, typename TOut, int V, int KW>
+__global__ void __launch_bounds__(kThreads)
+    BilinearBwdTileKernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
+                          int32_t wout, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw, int32_t tileRows,
+                          int32_t tilesPerPlane)
+{
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    const int64_t p = blockIdx.x / tilesPerPlane;
+    const int32_t tile = blockIdx.x - p * tilesPerPlane;
+    const int32_t y0 = tile * tileRows, y1 = min(hin, y0 + tileRows);
+    const int32_t r0 = __ldg(rh.start + y0);
+    const int32_t r1 = max(r0, __ldg(rh.end + y1 - 1));
+    const TIn* plane = go + p * hout * static_cast<int64_t>(wout);
+    const TIn* src = StageSpan<TIn>(plane + static_cast<int64_t>(r0) * wout, static_cast<int64_t>(r1 - r0) * wout,
+                                    smemRaw);
+    __syncthreads();
+    const int32_t groups = win / V;
+    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
+    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
+    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
+    if (rc >= rowThreads) {
+        return;
+    }
+    int32_t ya, yb;
+    RowChunk(y0, y1, rc, rowThreads, ya, yb);
+    if (ya >= yb) {
+        return;
+    }
+    TOut* gp = gi + p * hin * static_cast<int64_t>(win);
+    for (int32_t g = cg0; g < groups; g += colThreads) {
+        int32_t js[V], cnt[V];
+        float wx[V][KW];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            const int32_t xcol = g * V + k;
+            js[k] = __ldg(rw.start + xcol);
+            cnt[k] = __ldg(rw.end + xcol) - js[k];
+#pragma unroll
+            for (int t = 0; t < KW; ++t) {
+                wx[k][t] = t < cnt[k] ? CombinedWeight(tw, js[k] + t, xcol) : 0.0f;
+            }
+        }
+        WalkRows<TOut, V>(gp + g * V, win, ya, yb, th, rh, [&](int32_t i, float (&hp)[V]) {
+            const TIn* row = src + (i - r0) * wout;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                float a = 0.0f;
+#pragma unroll
+                for (int t = 0; t < KW; ++t) {
+                    // taps past the run are not read (they may lie outside the row, or hold Inf / NaN)
+                    const float v = (t < cnt[k]) ? DType<TIn>::ToF(row[js[k] + t]) : 0.0f;
+                    a = fmaf(wx[k][t], v, a);
+                }
+                hp[k] = a;
+            }
+        });
+    }
+}
+
+// ---- backward, NCHW, grads width = 2 x grad_input width, input-major ------------------------------------------------
+// The host has verified the column pattern: grad_input column x is fed by grads columns 2x-1 .. 2x+2 (clipped to
+// the row). A thread owns four grad_input columns x0..x0+3 and reads grads columns 2*x0-1 .. 2*x0+8 of each row:
+// one 16-byte (fp16/bf16) or two 16-byte (fp32) vectors plus one neighbour on each side.
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(kThreads)
+    BilinearBwdW2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
+                        LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows, int32_t tilesPerPlane)
+{
+    constexpr int V = 4, VG = 8;
+    const int32_t wout = 2 * win;
+    const int64_t p = blockIdx.x / tilesPerPlane;
+    const int32_t tile = blockIdx.x - p * tilesPerPlane;
+    const int32_t y0 = tile * tileRows, y1 = min(hin, y0 + tileRows);
+    const int32_t groups = win / V;
+    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
+    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
+    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
+    if (rc >= rowThreads) {
+        return;
+    }
+    int32_t ya, yb;
+    RowChunk(y0, y1, rc, rowThreads, ya, yb);
+    if (ya >= yb) {
+        return;
+    }
+    const TIn* gp = go + p * hout * static_cast<int64_t>(wout);
+    TOut* op = gi + p * hin * static_cast<int64_t>(win);
+    for (int32_t g = cg0; g < groups; g += colThreads) {
+        const int32_t x0 = g * V, j0 = 2 * x0;
+        const bool hasLeft = j0 > 0, hasRight = j0 + VG < wout;
+        // wx[k][t]: weight of grads column 2*(x0+k) - 1 + t for grad_input column x0+k (0 outside the row)
+        float wx[V][4];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int32_t j = j0 + 2 * k - 1 + t;
+                wx[k][t] = (j >= 0 && j < wout) ? CombinedWeight(tw, j, x0 + k) : 0.0f;
+            }
+        }
+        // Column 1 has one more source: grads column 0 is clamped to input column 0 with delta 0, and the
+        // reference still adds its (zero-weight) "hi" product to column 1.
+        const bool extra = x0 == 0 && win > 1;
+        const float wExtra = extra ? CombinedWeight(tw, 0, 1) : 0.0f;
+        WalkRows<TOut, V>(op + x0, win, ya, yb, th, rh, [&](int32_t i, float (&hp)[V]) {
+            const TIn* row = gp + static_cast<int64_t>(i) * wout + j0;
+            float v[VG + 2]; // grads columns j0-1 .. j0+8; neighbours outside the row read as 0 (weight 0)
+            v[0] = hasLeft ? DType<TIn>::Load(row - 1) : 0.0f;
+            float mid[VG];
+            if constexpr (sizeof(TIn) == 2) {
+                LoadPackLdg<TIn, VG>(row, mid);
+            } else {
+                float a[4], b[4];
+                LoadPackLdg<TIn, 4>(row, a);
+                LoadPackLdg<TIn, 4>(row + 4, b);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mid[k] = a[k];
+                    mid[k + 4] = b[k];
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < VG; ++k) {
+                v[k + 1] = mid[k];
+            }
+            v[VG + 1] = hasRight ? DType<TIn>::Load(row + VG) : 0.0f;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                float a = 0.0f;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    a = fmaf(wx[k][t], v[2 * k + t], a);
+                }
+                hp[k] = a;
+            }
+            if (extra) {
+                hp[1] = fmaf(wExtra, v[1], hp[1]);
+            }
+        });
     }
 }
 
@@ -332,153 +662,6 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// ---- backward, gather, NCHW, shared-memory staged row walk -----------------------------------------------------
-// KW = compile-time bound on the number of grads columns feeding one grad_input column.
-template <typename TIn, typename TOut, int V, int KW>
-__global__ void __launch_bounds__(kWalkThreads)
-    BilinearBwdWalkKernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
-                          int32_t wout, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw, int32_t tileRows,
-                          int32_t tilesPerPlane, int64_t capElems)
-{
-    extern __shared__ __align__(16) unsigned char smemRaw[];
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
-    const int32_t y0 = tile * tileRows, y1 = min(hin, y0 + tileRows);
-    const int32_t r0 = __ldg(rh.start + y0);
-    const int32_t r1 = max(r0, __ldg(rh.end + y1 - 1));
-    const TIn* plane = go + p * hout * static_cast<int64_t>(wout);
-    const int64_t count = static_cast<int64_t>(r1 - r0) * wout;
-    const TIn* src = plane;
-    int32_t rbase = 0;
-    if (count <= capElems) {
-        src = StageSpan<TIn>(plane + static_cast<int64_t>(r0) * wout, count, smemRaw);
-        rbase = r0;
-    }
-    __syncthreads();
-    // Lanes of a warp take adjacent column groups (whole warps per row), so that their shared-memory reads fall in
-    // adjacent words (no bank conflicts) and each warp stores one contiguous run per row.
-    const int32_t groups = win / V;
-    const int32_t colThreads = min((groups + 31) & ~31, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
-        return;
-    }
-    const int32_t chunk = (y1 - y0 + rowThreads - 1) / rowThreads;
-    const int32_t ya = y0 + rc * chunk, yb = min(y1, ya + chunk);
-    if (ya >= yb) {
-        return;
-    }
-    TOut* gp = gi + p * hin * static_cast<int64_t>(win);
-    for (int32_t g = cg0; g < groups; g += colThreads) {
-        // horizontal taps of my columns: grads columns [js, js + cnt), cnt <= KW, with their combined weights
-        int32_t js[V], cnt[V];
-        float wx[V][KW];
-#pragma unroll
-        for (int k = 0; k < V; ++k) {
-            const int32_t xcol = g * V + k;
-            js[k] = __ldg(rw.start + xcol);
-            cnt[k] = __ldg(rw.end + xcol) - js[k]; // normally <= KW; longer runs take the slow tail loop below
-#pragma unroll
-            for (int t = 0; t < KW; ++t) {
-                float w = 0.0f;
-                if (t < cnt[k]) {
-                    const int32_t j = js[k] + t;
-                    const float d = __ldg(tw.delta + j);
-                    if (__ldg(tw.lo + j) == xcol) {
-                        w = Sub(1.0f, d);
-                    }
-                    if (__ldg(tw.hi + j) == xcol) {
-                        w = Add(w, d);
-                    }
-                }
-                wx[k][t] = w;
-            }
-        }
-        float accA[V], accB[V];
-#pragma unroll
-        for (int k = 0; k < V; ++k) {
-            accA[k] = 0.0f;
-            accB[k] = 0.0f;
-        }
-        int32_t cur = ya;
-        const int32_t is = __ldg(rh.start + ya), ie = max(is, __ldg(rh.end + yb - 1));
-        for (int32_t i = is; i < ie; ++i) {
-            const int32_t loY = __ldg(th.lo + i), hiY = __ldg(th.hi + i);
-            const float dY = __ldg(th.delta + i);
-            while (cur < loY && cur < yb) { // rows below loY are complete
-                StorePack<TOut, V>(gp + static_cast<int64_t>(cur) * win + g * V, accA);
-#pragma unroll
-                for (int k = 0; k < V; ++k) {
-                    accA[k] = accB[k];
-                    accB[k] = 0.0f;
-                }
-                ++cur;
-            }
-            if (cur >= yb) {
-                break;
-            }
-            const TIn* row = src + static_cast<int64_t>(i - rbase) * wout;
-            float hp[V];
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                float a = 0.0f;
-#pragma unroll
-                for (int t = 0; t < KW; ++t) {
-                    // taps past the run are not read (they may lie outside the row, or hold Inf / NaN)
-                    const float v = (t < cnt[k]) ? DType<TIn>::ToF(row[js[k] + t]) : 0.0f;
-                    a = fmaf(wx[k][t], v, a);
-                }
-                for (int32_t t = KW; t < cnt[k]; ++t) { // run longer than the register-held taps (not expected)
-                    const int32_t j = js[k] + t, xcol = g * V + k;
-                    const float d = __ldg(tw.delta + j);
-                    float w = 0.0f;
-                    if (__ldg(tw.lo + j) == xcol) {
-                        w = Sub(1.0f, d);
-                    }
-                    if (__ldg(tw.hi + j) == xcol) {
-                        w = Add(w, d);
-                    }
-                    a = fmaf(w, DType<TIn>::ToF(row[j]), a);
-                }
-                hp[k] = a;
-            }
-            const float wLo = Sub(1.0f, dY), wHi = dY;
-            if (loY == cur) {
-#pragma unroll
-                for (int k = 0; k < V; ++k) {
-                    accA[k] = fmaf(wLo, hp[k], accA[k]);
-                }
-            } else if (loY == cur + 1) {
-#pragma unroll
-                for (int k = 0; k < V; ++k) {
-                    accB[k] = fmaf(wLo, hp[k], accB[k]);
-                }
-            }
-            if (hiY == cur) {
-#pragma unroll
-                for (int k = 0; k < V; ++k) {
-                    accA[k] = fmaf(wHi, hp[k], accA[k]);
-                }
-            } else if (hiY == cur + 1 && cur + 1 < yb) {
-#pragma unroll
-                for (int k = 0; k < V; ++k) {
-                    accB[k] = fmaf(wHi, hp[k], accB[k]);
-                }
-            }
-        }
-        while (cur < yb) {
-            StorePack<TOut, V>(gp + static_cast<int64_t>(cur) * win + g * V, accA);
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                accA[k] = accB[k];
-                accB[k] = 0.0f;
-            }
-            ++cur;
-        }
-    }
-}
-
 // ---- backward, atomic ---------------------------------------------------------------------------------------
 template <typename TIn, int V, int LAY>
 __global__ void __launch_bounds__(kThreads)
@@ -532,52 +715,84 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+
+bool IsW2ForwardPattern(const host::Lerp& t, int32_t in)
+{
+    const int32_t out = static_cast<int32_t>(t.lo.size());
+    if (out != 2 * in) {
+        return false;
+    }
+    for (int32_t w = 0; w < out; ++w) {
+        const int32_t lo = std::max((w - 1) >> 1, 0), hi = w ? std::min((w + 1) >> 1, in - 1) : 0;
+        if (t.lo[w] != lo || t.hi[w] != hi) {
+            return false;
+        }
+    }
+    return true;
+}
+
+bool IsW2BackwardPattern(const host::Ranges& r, int32_t in, int32_t out)
+{
+    if (out != 2 * in) {
+        return false;
+    }
+    for (int32_t x = 0; x < in; ++x) {
+        const int32_t start = std::max(2 * x - 1, 0), end = std::min(2 * x + 3, out);
+        const bool startOk = r.start[x] == start || (x == 1 && r.start[x] == 0);
+        if (!startOk || r.end[x] != end) {
+            return false;
+        }
+    }
+    return true;
+}
+
+// Rows per block for the kernels that do not stage: whole planes when there are many, bands when there are few.
+int32_t RowsForOccupancy(int64_t planes, int32_t rows)
+{
+    const int64_t wantBlocks = static_cast<int64_t>(NumSMs()) * 4;
+    if (planes >= wantBlocks) {
+        return rows;
+    }
+    const int64_t tiles = CeilDiv(wantBlocks, planes > 0 ? planes : 1);
+    return static_cast<int32_t>(std::max<int64_t>(8, CeilDiv(rows, tiles)));
+}
+
 template <typename TIn, typename TOut>
 cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th, LerpAxis tw, RangeAxis rh,
-                         RangeAxis rw, bool exactScale, float scaleH, float scaleW, cudaStream_t s)
+                         RangeAxis rw, const BilinearPlan& plan, cudaStream_t s)
 {
+    const int64_t planes = sh.n * sh.c;
     if (lay == kNCHW) {
-        int v = PickVec(sizeof(TOut), sh.win, {gi});
-        // grads rows / columns feeding one grad_input row / column: those with source coordinate in (y-1, y+1),
-        // i.e. at most 2/scale + 2. That bound needs the source coordinates to stay inside the input (true for
-        // scale = in/out and for align_corners); user scales that overshoot pile many grads columns onto the last
-        // input column, so they go to the direct kernel (exactScale = false).
-        const double invH = scaleH > 0.0f ? 1.0 / scaleH : 1e9, invW = scaleW > 0.0f ? 1.0 / scaleW : 1e9;
-        const int64_t tapsW = invW > 100.0 ? 1000 : static_cast<int64_t>(2.0 * invW) + 2;
-        auto need = [&](int32_t t) {
-            const double r = (t + 1) * invH + 4.0;
-            return r < sh.hout ? static_cast<int32_t>(r) : sh.hout;
-        };
-        const int64_t rowBytes = static_cast<int64_t>(sh.wout) * sizeof(TIn);
-        const int32_t tileRows = PickTileRows(sh.hin, rowBytes, kStageBudget, need);
-        const int64_t planes = sh.n * sh.c;
-        const bool walk = exactScale && tapsW <= 8 && tileRows > 0 && planes * CeilDiv(sh.hin, tileRows) < (1LL << 31);
-        if (walk) {
-            v = std::min<int>(v, std::max<int>(1, 4 / static_cast<int>(sizeof(TOut)))); // 4 bytes per lane
+        const int v = PickVec(sizeof(TOut), sh.win, {gi});
+        const TIn* pg = static_cast<const TIn*>(go);
+        TOut* po = static_cast<TOut*>(gi);
+        if (plan.schedule == BilinearPlan::kW2 && v >= 4 && Aligned(go, 16)) {
+            const int32_t tileRows = RowsForOccupancy(planes, sh.hin);
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, tileRows));
-            const int64_t cap = static_cast<int64_t>(need(tileRows)) * sh.wout;
-            const size_t smem = StageBytes(cap, sizeof(TIn));
+            BilinearBwdW2Kernel<TIn, TOut><<<static_cast<unsigned>(planes * tiles), kThreads, 0, s>>>(
+                pg, po, sh.hin, sh.win, sh.hout, th, tw, rh, tileRows, tiles);
+        } else if (plan.schedule != BilinearPlan::kDirect && plan.tileRows > 0) {
+            const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, plan.tileRows));
+            const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.wout, sizeof(TIn));
             const unsigned blocks = static_cast<unsigned>(planes * tiles);
-            OPSCV_DISPATCH_VEC(v, V, {
-                if constexpr (V <= 2) {
-                    if (tapsW <= 4) {
-                        BilinearBwdWalkKernel<TIn, TOut, V, 4><<<blocks, kWalkThreads, smem, s>>>(
-                            static_cast<const TIn*>(go), static_cast<TOut*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th,
-                            tw, rh, rw, tileRows, tiles, cap);
+            const int vv = std::min(v, 4);
+            OPSCV_DISPATCH_VEC(vv, V, {
+                if constexpr (V <= 4) {
+                    if (plan.tapsW <= 4) {
+                        BilinearBwdTileKernel<TIn, TOut, V, 4><<<blocks, kThreads, smem, s>>>(
+                            pg, po, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, plan.tileRows, tiles);
                     } else {
-                        BilinearBwdWalkKernel<TIn, TOut, V, 8><<<blocks, kWalkThreads, smem, s>>>(
-                            static_cast<const TIn*>(go), static_cast<TOut*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th,
-                            tw, rh, rw, tileRows, tiles, cap);
+                        BilinearBwdTileKernel<TIn, TOut, V, 8><<<blocks, kThreads, smem, s>>>(
+                            pg, po, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, plan.tileRows, tiles);
                     }
                 }
             });
         } else {
             OPSCV_DISPATCH_VEC(v, V, {
                 if constexpr (V * sizeof(TOut) <= 16) {
-                    const int64_t total = sh.n * sh.c * sh.hin * (sh.win / V);
+                    const int64_t total = planes * sh.hin * (sh.win / V);
                     BilinearBwdGatherNCHWKernel<TIn, TOut, V><<<GridFor(total, kThreads), kThreads, 0, s>>>(
-                        static_cast<const TIn*>(go), static_cast<TOut*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th, tw,
-                        rh, rw, total);
+                        pg, po, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, total);
                 }
             });
         }
@@ -599,37 +814,98 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
 
 } // namespace
 
-cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
-                        cudaStream_t s)
+BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel)
 {
+    BilinearPlan plan{};
+    plan.schedule = BilinearPlan::kDirect;
+    if (lay != kNCHW) {
+        return plan;
+    }
+    const int es = DtSize(dt);
+    const host::Lerp tH = host::LerpTable(sh.hin, sh.hout, gh.scale, halfPixel, 0);
+    const host::Lerp tW = host::LerpTable(sh.win, sh.wout, gw.scale, halfPixel, 0);
+    if (sh.win % 4 == 0 && IsW2ForwardPattern(tW, sh.win)) {
+        plan.schedule = BilinearPlan::kW2;
+        return plan;
+    }
+    const int64_t rowBytes = static_cast<int64_t>(sh.win) * es;
+    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hin));
+    auto need = [&](int32_t h0, int32_t h1) { return tH.hi[h1 - 1] - tH.lo[h0] + 1; };
+    const int32_t tileRows = host::PickTileRows(sh.hout, budgetRows, need);
+    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hout, tileRows) < (1LL << 31)) {
+        plan.schedule = BilinearPlan::kTiled;
+        plan.tileRows = tileRows;
+        plan.bandRows = host::MaxBand(sh.hout, tileRows, need);
+    }
+    return plan;
+}
+
+BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel)
+{
+    BilinearPlan plan{};
+    plan.schedule = BilinearPlan::kDirect;
+    if (lay != kNCHW) {
+        return plan;
+    }
+    const int es = DtSize(dtIn);
+    const host::Lerp tH = host::LerpTable(sh.hin, sh.hout, gh.scale, halfPixel, 1);
+    const host::Lerp tW = host::LerpTable(sh.win, sh.wout, gw.scale, halfPixel, 1);
+    const host::Ranges rH = host::LerpBwdRanges(tH, sh.hin);
+    const host::Ranges rW = host::LerpBwdRanges(tW, sh.win);
+    if (sh.win % 4 == 0 && IsW2BackwardPattern(rW, sh.win, sh.wout)) {
+        plan.schedule = BilinearPlan::kW2;
+        return plan;
+    }
+    int32_t taps = 0;
+    for (int32_t x = 0; x < sh.win; ++x) {
+        taps = std::max(taps, rW.end[x] - rW.start[x]);
+    }
+    const int64_t rowBytes = static_cast<int64_t>(sh.wout) * es;
+    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hout));
+    auto need = [&](int32_t y0, int32_t y1) { return std::max(0, rH.end[y1 - 1] - rH.start[y0]); };
+    const int32_t tileRows = taps <= 8 ? host::PickTileRows(sh.hin, budgetRows, need) : 0;
+    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hin, tileRows) < (1LL << 31)) {
+        plan.schedule = BilinearPlan::kTiled;
+        plan.tileRows = tileRows;
+        plan.bandRows = host::MaxBand(sh.hin, tileRows, need);
+        plan.tapsW = taps;
+    }
+    return plan;
+}
+
+cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
+                        const BilinearPlan& plan, cudaStream_t s)
+{
+    const int64_t planes = sh.n * sh.c;
     OPSCV_DISPATCH_DT(dt, T, {
         if (lay == kNCHW) {
-            int v = PickVec(sizeof(T), sh.wout, {y});
-            // input rows read by t consecutive output rows: hi(h0+t-1) - lo(h0) + 1 <= (t-1)*scale + 3
-            const double ratio = static_cast<double>(sh.hin) / sh.hout;
-            auto need = [&](int32_t t) {
-                const int64_t r = static_cast<int64_t>((t - 1) * ratio) + 4;
-                return static_cast<int32_t>(r < sh.hin ? r : sh.hin);
-            };
-            const int64_t rowBytes = static_cast<int64_t>(sh.win) * sizeof(T);
-            const int32_t tileRows = PickTileRows(sh.hout, rowBytes, kStageBudget, need);
-            const int64_t planes = sh.n * sh.c;
-            const bool tiled = tileRows > 0 && planes * CeilDiv(sh.hout, tileRows) < (1LL << 31);
-            if (tiled) {
-                v = std::min<int>(v, 4 / static_cast<int>(sizeof(T))); // 4 bytes per lane: see the kernel's mapping
-            }
-            OPSCV_DISPATCH_VEC(v, V, {
-                if constexpr (V * sizeof(T) <= 16) {
-                    if (tiled) {
-                        const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
-                        const int64_t cap = static_cast<int64_t>(need(tileRows)) * sh.win;
-                        BilinearFwdTileKernel<T, V>
-                            <<<static_cast<unsigned>(planes * tiles), kThreads, StageBytes(cap, sizeof(T)), s>>>(
-                                static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th, tw,
-                                tileRows, tiles, cap);
-                    } else {
-                        // Rows too long to stage: gather from global memory. Split the rows of a plane into
-                        // chunks only as far as needed to fill the machine (longer walks reuse more rows).
+            const int v = PickVec(sizeof(T), sh.wout, {y});
+            const T* px = static_cast<const T*>(x);
+            T* py = static_cast<T*>(y);
+            // the 2x kernel loads 4 input columns and stores 8 output columns per thread as vectors
+            const bool w2Ok = plan.schedule == BilinearPlan::kW2 && Aligned(x, 4 * sizeof(T)) &&
+                              Aligned(y, sizeof(T) == 2 ? 16 : 16) && (sh.wout * sizeof(T)) % 16 == 0;
+            if (w2Ok) {
+                const int32_t tileRows = RowsForOccupancy(planes, sh.hout);
+                const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
+                BilinearFwdW2Kernel<T><<<static_cast<unsigned>(planes * tiles), kThreads, 0, s>>>(
+                    px, py, sh.hin, sh.win, sh.hout, th, tw, tileRows, tiles);
+            } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
+                const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
+                const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.win, sizeof(T));
+                const unsigned blocks = static_cast<unsigned>(planes * tiles);
+                const int vv = std::min(v, 4);
+                OPSCV_DISPATCH_VEC(vv, V, {
+                    if constexpr (V <= 4) {
+                        BilinearFwdTileKernel<T, V><<<blocks, kThreads, smem, s>>>(px, py, sh.hin, sh.win, sh.hout,
+                                                                                  sh.wout, th, tw, plan.tileRows, tiles);
+                    }
+                });
+            } else {
+                OPSCV_DISPATCH_VEC(v, V, {
+                    if constexpr (V * sizeof(T) <= 16) {
+                        // Split the rows of a plane into chunks only as far as needed to fill the machine (longer
+                        // walks reuse more rows).
                         const int64_t columns = planes * (sh.wout / V);
                         const int64_t wanted = static_cast<int64_t>(NumSMs()) * 2048 * 2;
                         int64_t chunks = CeilDiv(wanted, columns > 0 ? columns : 1);
@@ -638,11 +914,10 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                         const int32_t rowChunks = static_cast<int32_t>(CeilDiv(sh.hout, rows));
                         const int64_t total = columns * rowChunks;
                         BilinearFwdNCHWKernel<T, V><<<GridFor(total, kThreads, 16), kThreads, 0, s>>>(
-                            static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th, tw,
-                            rows, rowChunks, total);
+                            px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rows, rowChunks, total);
                     }
-                }
-            });
+                });
+            }
         } else {
             const int v = PickVec(sizeof(T), sh.c, {x, y});
             OPSCV_DISPATCH_VEC(v, V, {
@@ -660,16 +935,16 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
 }
 
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
-                              LerpAxis tw, RangeAxis rh, RangeAxis rw, bool exactScale, float scaleH, float scaleW, cudaStream_t s)
+                              LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s)
 {
     if (dtIn == dtOut) {
-        OPSCV_DISPATCH_DT(dtIn, T, { return (LaunchGather<T, T>(lay, go, gi, sh, th, tw, rh, rw, exactScale, scaleH, scaleW, s)); });
+        OPSCV_DISPATCH_DT(dtIn, T, { return (LaunchGather<T, T>(lay, go, gi, sh, th, tw, rh, rw, plan, s)); });
     }
     if (dtIn == Dt::F32 && dtOut == Dt::F16) {
-        return LaunchGather<float, __half>(lay, go, gi, sh, th, tw, rh, rw, exactScale, scaleH, scaleW, s);
+        return LaunchGather<float, __half>(lay, go, gi, sh, th, tw, rh, rw, plan, s);
     }
     if (dtIn == Dt::F32 && dtOut == Dt::BF16) {
-        return LaunchGather<float, __nv_bfloat16>(lay, go, gi, sh, th, tw, rh, rw, exactScale, scaleH, scaleW, s);
+        return LaunchGather<float, __nv_bfloat16>(lay, go, gi, sh, th, tw, rh, rw, plan, s);
     }
     return cudaErrorInvalidValue;
 }

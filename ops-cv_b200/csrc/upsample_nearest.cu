@@ -1,19 +1,25 @@
 // UpsampleNearest2d forward and backward.
 //
-// Both directions are output-major: one thread produces one 16-byte (or narrower, when alignment or the row
-// length does not allow it) group of consecutive output elements, so every store is a full-width coalesced
-// vector store. NCHW: a block owns a band of output rows of one plane, copies the input rows that band reads into
-// shared memory with coalesced 16-byte loads (tile_stage.cuh) and gathers from there; a thread keeps the source
-// columns of its output group in registers and walks down the rows of the band. NHWC: a gathered pixel is a
-// contiguous run of channels, so the taps are 16-byte global loads. The per-row / per-column source indices come
-// from the tables built by tables.cu.
+// Kernel schedules (chosen on the host from the exact index tables, see MakeNearestFwdPlan / MakeNearestBwdPlan):
+//   * NCHW, integer up-scale factors (the common 2x / 4x case): input-major. A thread loads one 16-byte vector of
+//     input, replicates its elements in registers and writes the RW * RH output vectors it feeds; the backward
+//     loads RH 16-byte vectors of grads and reduces them to one output vector. Every global access is a
+//     coalesced 16-byte access and nothing is read twice.
+//   * NCHW, any other scale: output-major over shared memory. A block copies the input rows that its band of
+//     output rows reads into shared memory (coalesced 16-byte loads, tile_stage.cuh); a thread owns one 16-byte
+//     group of output columns, keeps their source columns in registers and walks down the rows of the band.
+//   * NCHW rows too long to stage, or unaligned tensors: direct gather from global memory.
+//   * NHWC: a gathered pixel is a contiguous run of channels, so taps are 16-byte global loads.
+// The first version of the NCHW kernels gathered 2-byte elements straight from global memory and was bound by L1
+// sector look-ups (ncu: l1tex throughput 85-95 %, 25 % of HBM peak); the schedules above remove that traffic.
 //
 // Reference arithmetic: image/resize_nearest_neighbor_v2/op_kernel/arch35/resize_nearest_neighbor_v2_simt.h:127-155
 // (forward copy) and image/resize_nearest_neighbor_v2_grad/op_kernel/arch35/
 // resize_nearest_neighbor_v2_grad_simt_determine.h:90-118 (backward: fp32 sum over the window, rows outer,
-// columns inner, then one cast).
+// columns inner, then one cast). All schedules keep that summation order, so results are bit-identical.
 #include <algorithm>
 
+#include "host_tables.h"
 #include "launch_util.cuh"
 #include "tile_stage.cuh"
 
@@ -21,9 +27,9 @@ namespace opscv {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int64_t kStageBudget = 32 * 1024; // staged bytes per block: keeps >= 6 blocks resident per SM
+constexpr int64_t kStageBudget = 24 * 1024; // staged bytes per block: keeps 8 blocks resident per SM
 
-// ---- forward ----------------------------------------------------------------------------------------------
+// ---- direct kernels (fallbacks; NHWC main path) ----------------------------------------------------------------
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
     NearestFwdNCHWKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
@@ -68,56 +74,6 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// NCHW, shared-memory staged. grid.x = planes * tilesPerPlane; a tile is `tileRows` output rows of one plane.
-template <typename T, int V>
-__global__ void __launch_bounds__(kThreads)
-    NearestFwdTileKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
-                         int32_t wout, const int32_t* __restrict__ sh, const int32_t* __restrict__ sw,
-                         int32_t tileRows, int32_t tilesPerPlane, int64_t capElems)
-{
-    extern __shared__ __align__(16) unsigned char smemRaw[];
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
-    const int32_t h0 = tile * tileRows, h1 = min(hout, h0 + tileRows);
-    const int32_t r0 = __ldg(sh + h0), r1 = __ldg(sh + h1 - 1) + 1;
-    const T* plane = x + p * hin * static_cast<int64_t>(win);
-    const int64_t count = static_cast<int64_t>(r1 - r0) * win;
-    const T* src = plane; // fallback: gather from global memory if the band does not fit (never with host tiling)
-    int32_t rbase = 0;
-    if (count <= capElems) {
-        src = StageSpan<T>(plane + static_cast<int64_t>(r0) * win, count, smemRaw);
-        rbase = r0;
-    }
-    __syncthreads();
-    // Lanes of a warp take adjacent column groups (whole warps per row), so that their shared-memory reads fall in
-    // adjacent words (no bank conflicts) and each warp stores one contiguous run per row.
-    const int32_t groups = wout / V;
-    const int32_t colThreads = min((groups + 31) & ~31, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
-        return;
-    }
-    T* yp = y + p * hout * static_cast<int64_t>(wout);
-    for (int32_t g = cg0; g < groups; g += colThreads) {
-        int32_t col[V];
-#pragma unroll
-        for (int k = 0; k < V; ++k) {
-            col[k] = __ldg(sw + g * V + k);
-        }
-        for (int32_t h = h0 + rc; h < h1; h += rowThreads) {
-            const T* row = src + static_cast<int64_t>(__ldg(sh + h) - rbase) * win;
-            Pack<T, V> out;
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                out.v[k] = row[col[k]];
-            }
-            *reinterpret_cast<Pack<T, V>*>(yp + static_cast<int64_t>(h) * wout + g * V) = out;
-        }
-    }
-}
-
-// ---- backward ---------------------------------------------------------------------------------------------
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
     NearestBwdNCHWKernel(const T* __restrict__ go, T* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
@@ -188,13 +144,132 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// NCHW, shared-memory staged: a tile is `tileRows` grad_input rows of one plane; the grads rows of their windows
-// are staged. Summation order per element is the reference's (window rows outer, columns inner), in fp32.
+// ---- NCHW, integer factors, input-major -------------------------------------------------------------------------
+// Forward: out[h][w] = in[h / RH][w / RW]. grid.x = planes; a thread takes 16-byte input vectors of its plane.
+template <typename T, int RW>
+__global__ void __launch_bounds__(kThreads)
+    NearestFwdReplicateKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t rh,
+                              int64_t planes)
+{
+    constexpr int VI = 16 / sizeof(T);
+    const int32_t vecsPerRow = win / VI;
+    const int32_t vecsPerPlane = vecsPerRow * hin;
+    const int32_t wout = win * RW;
+    for (int64_t p = blockIdx.x; p < planes; p += gridDim.x) {
+        const T* xp = x + p * hin * static_cast<int64_t>(win);
+        T* yp = y + p * hin * static_cast<int64_t>(rh) * wout;
+        for (int32_t v = threadIdx.x; v < vecsPerPlane; v += blockDim.x) {
+            const int32_t r = v / vecsPerRow;
+            const int32_t c0 = (v - r * vecsPerRow) * VI;
+            const Pack<T, VI> in = *reinterpret_cast<const Pack<T, VI>*>(xp + static_cast<int64_t>(v) * VI);
+            Pack<T, VI> out[RW];
+#pragma unroll
+            for (int o = 0; o < VI * RW; ++o) {
+                out[o / VI].v[o % VI] = in.v[o / RW];
+            }
+            T* dst = yp + static_cast<int64_t>(r) * rh * wout + c0 * RW;
+            for (int32_t i = 0; i < rh; ++i) {
+#pragma unroll
+                for (int q = 0; q < RW; ++q) {
+                    *reinterpret_cast<Pack<T, VI>*>(dst + q * VI) = out[q];
+                }
+                dst += wout;
+            }
+        }
+    }
+}
+
+// Backward: gi[y][x] = sum over the RH x RW block of grads, rows outer, columns inner (the reference's order).
+template <typename T, int RW>
+__global__ void __launch_bounds__(kThreads)
+    NearestBwdPoolKernel(const T* __restrict__ go, T* __restrict__ gi, int32_t hin, int32_t win, int32_t rh,
+                         int64_t planes)
+{
+    constexpr int VI = 16 / sizeof(T); // grads elements per 16-byte load
+    constexpr int VO = VI / RW;        // grad_input elements produced from them
+    const int32_t wout = win * RW;
+    const int32_t vecsPerRow = wout / VI;
+    const int32_t vecsPerPlane = vecsPerRow * hin;
+    for (int64_t p = blockIdx.x; p < planes; p += gridDim.x) {
+        const T* gp = go + p * hin * static_cast<int64_t>(rh) * wout;
+        T* op = gi + p * hin * static_cast<int64_t>(win);
+        for (int32_t v = threadIdx.x; v < vecsPerPlane; v += blockDim.x) {
+            const int32_t r = v / vecsPerRow;
+            const int32_t cv = v - r * vecsPerRow;
+            const T* src = gp + static_cast<int64_t>(r) * rh * wout + cv * VI;
+            float acc[VO];
+#pragma unroll
+            for (int k = 0; k < VO; ++k) {
+                acc[k] = 0.0f;
+            }
+            for (int32_t i = 0; i < rh; ++i) {
+                float g[VI];
+                LoadPackLdg<T, VI>(src, g);
+#pragma unroll
+                for (int k = 0; k < VO; ++k) {
+#pragma unroll
+                    for (int j = 0; j < RW; ++j) {
+                        acc[k] = Add(acc[k], g[k * RW + j]);
+                    }
+                }
+                src += wout;
+            }
+            StorePack<T, VO>(op + static_cast<int64_t>(r) * win + cv * VO, acc);
+        }
+    }
+}
+
+// ---- NCHW, any scale, shared-memory staged -----------------------------------------------------------------------
+// grid.x = planes * tilesPerPlane; a tile is `tileRows` output rows of one plane, whose input rows
+// [sh[h0], sh[h1-1]] are staged (the host sized the tile so that they fit).
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads)
+    NearestFwdTileKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
+                         int32_t wout, const int32_t* __restrict__ sh, const int32_t* __restrict__ sw,
+                         int32_t tileRows, int32_t tilesPerPlane)
+{
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    const int64_t p = blockIdx.x / tilesPerPlane;
+    const int32_t tile = blockIdx.x - p * tilesPerPlane;
+    const int32_t h0 = tile * tileRows, h1 = min(hout, h0 + tileRows);
+    const int32_t r0 = __ldg(sh + h0), r1 = __ldg(sh + h1 - 1) + 1;
+    const T* plane = x + p * hin * static_cast<int64_t>(win);
+    const T* src = StageSpan<T>(plane + static_cast<int64_t>(r0) * win, static_cast<int64_t>(r1 - r0) * win, smemRaw);
+    __syncthreads();
+    const int32_t groups = wout / V;
+    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
+    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
+    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
+    if (rc >= rowThreads) {
+        return;
+    }
+    T* yp = y + p * hout * static_cast<int64_t>(wout);
+    for (int32_t g = cg0; g < groups; g += colThreads) {
+        int32_t col[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            col[k] = __ldg(sw + g * V + k);
+        }
+        T* dst = yp + static_cast<int64_t>(h0 + rc) * wout + g * V;
+        for (int32_t h = h0 + rc; h < h1; h += rowThreads) {
+            const T* row = src + (__ldg(sh + h) - r0) * win;
+            Pack<T, V> out;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                out.v[k] = row[col[k]];
+            }
+            *reinterpret_cast<Pack<T, V>*>(dst) = out;
+            dst += static_cast<int64_t>(rowThreads) * wout;
+        }
+    }
+}
+
+// A tile is `tileRows` grad_input rows of one plane; the grads rows of their windows are staged. Summation order
+// per element: window rows outer, columns inner, in fp32.
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
     NearestBwdTileKernel(const T* __restrict__ go, T* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
-                         int32_t wout, RangeAxis th, RangeAxis tw, int32_t tileRows, int32_t tilesPerPlane,
-                         int64_t capElems)
+                         int32_t wout, RangeAxis th, RangeAxis tw, int32_t tileRows, int32_t tilesPerPlane)
 {
     extern __shared__ __align__(16) unsigned char smemRaw[];
     const int64_t p = blockIdx.x / tilesPerPlane;
@@ -203,18 +278,11 @@ __global__ void __launch_bounds__(kThreads)
     const int32_t r0 = __ldg(th.start + y0);
     const int32_t r1 = max(r0, __ldg(th.end + y1 - 1));
     const T* plane = go + p * hout * static_cast<int64_t>(wout);
-    const int64_t count = static_cast<int64_t>(r1 - r0) * wout;
-    const T* src = plane;
-    int32_t rbase = 0;
-    if (count <= capElems) {
-        src = StageSpan<T>(plane + static_cast<int64_t>(r0) * wout, count, smemRaw);
-        rbase = r0;
-    }
+    const T* src = StageSpan<T>(plane + static_cast<int64_t>(r0) * wout, static_cast<int64_t>(r1 - r0) * wout,
+                                smemRaw);
     __syncthreads();
-    // Lanes of a warp take adjacent column groups (whole warps per row), so that their shared-memory reads fall in
-    // adjacent words (no bank conflicts) and each warp stores one contiguous run per row.
     const int32_t groups = win / V;
-    const int32_t colThreads = min((groups + 31) & ~31, static_cast<int32_t>(blockDim.x));
+    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
     const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
     const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
     if (rc >= rowThreads) {
@@ -236,7 +304,7 @@ __global__ void __launch_bounds__(kThreads)
                 acc[k] = 0.0f;
             }
             for (int32_t i = hs; i < he; ++i) {
-                const T* row = src + static_cast<int64_t>(i - rbase) * wout;
+                const T* row = src + (i - r0) * wout;
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
                     for (int32_t j = ws[k]; j < we[k]; ++j) {
@@ -249,46 +317,125 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+bool IsIntegerReplication(const std::vector<int32_t>& src, int32_t factor)
+{
+    for (size_t d = 0; d < src.size(); ++d) {
+        if (src[d] != static_cast<int32_t>(d) / factor) {
+            return false;
+        }
+    }
+    return true;
+}
+
+bool IsIntegerPooling(const host::Ranges& r, int32_t factor)
+{
+    for (size_t y = 0; y < r.start.size(); ++y) {
+        if (r.start[y] != static_cast<int32_t>(y) * factor || r.end[y] != static_cast<int32_t>(y + 1) * factor) {
+            return false;
+        }
+    }
+    return true;
+}
+
 } // namespace
 
+NearestPlan MakeNearestFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw)
+{
+    NearestPlan plan{};
+    plan.schedule = NearestPlan::kDirect;
+    if (lay != kNCHW) {
+        return plan;
+    }
+    const int es = DtSize(dt), vi = 16 / es;
+    const std::vector<int32_t> srcH = host::NearestSrc(sh.hin, sh.hout, gh.scale);
+    const std::vector<int32_t> srcW = host::NearestSrc(sh.win, sh.wout, gw.scale);
+    const int32_t rh = sh.hout / sh.hin, rw = sh.wout / sh.win;
+    if (sh.hout == rh * sh.hin && sh.wout == rw * sh.win && (rw == 2 || rw == 3 || rw == 4) && sh.win % vi == 0 &&
+        IsIntegerReplication(srcH, rh) && IsIntegerReplication(srcW, rw)) {
+        plan.schedule = NearestPlan::kInteger;
+        plan.rh = rh;
+        plan.rw = rw;
+        return plan;
+    }
+    const int64_t rowBytes = static_cast<int64_t>(sh.win) * es;
+    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hin));
+    auto need = [&](int32_t h0, int32_t h1) { return srcH[h1 - 1] - srcH[h0] + 1; };
+    const int32_t tileRows = host::PickTileRows(sh.hout, budgetRows, need);
+    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hout, tileRows) < (1LL << 31)) {
+        plan.schedule = NearestPlan::kTiled;
+        plan.tileRows = tileRows;
+        plan.bandRows = host::MaxBand(sh.hout, tileRows, need);
+    }
+    return plan;
+}
+
+NearestPlan MakeNearestBwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw)
+{
+    NearestPlan plan{};
+    plan.schedule = NearestPlan::kDirect;
+    if (lay != kNCHW) {
+        return plan;
+    }
+    const int es = DtSize(dt), vi = 16 / es;
+    const host::Ranges rH = host::NearestBwdRanges(sh.hin, sh.hout, gh.scale);
+    const host::Ranges rW = host::NearestBwdRanges(sh.win, sh.wout, gw.scale);
+    const int32_t rh = sh.hout / sh.hin, rw = sh.wout / sh.win;
+    if (sh.hout == rh * sh.hin && sh.wout == rw * sh.win && (rw == 2 || rw == 4) && sh.wout % vi == 0 &&
+        IsIntegerPooling(rH, rh) && IsIntegerPooling(rW, rw)) {
+        plan.schedule = NearestPlan::kInteger;
+        plan.rh = rh;
+        plan.rw = rw;
+        return plan;
+    }
+    const int64_t rowBytes = static_cast<int64_t>(sh.wout) * es;
+    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hout));
+    auto need = [&](int32_t y0, int32_t y1) { return std::max(0, rH.end[y1 - 1] - rH.start[y0]); };
+    const int32_t tileRows = host::PickTileRows(sh.hin, budgetRows, need);
+    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hin, tileRows) < (1LL << 31)) {
+        plan.schedule = NearestPlan::kTiled;
+        plan.tileRows = tileRows;
+        plan.bandRows = host::MaxBand(sh.hin, tileRows, need);
+    }
+    return plan;
+}
+
 cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, NearestAxis th, NearestAxis tw,
-                       cudaStream_t s)
+                       const NearestPlan& plan, cudaStream_t s)
 {
     const int64_t planes = sh.n * sh.c;
     OPSCV_DISPATCH_DT(dt, T, {
         if (lay == kNCHW) {
-            int v = PickVec(sizeof(T), sh.wout, {y});
-            // rows of input needed by t consecutive output rows: src = floor(dst * scale), so at most
-            // floor((t-1)*scale) + 2; the ratio in/out bounds the scale the tables were built with from above
-            // unless user scales were given, hence the generous +3 and the in-kernel fallback.
-            const double ratio = static_cast<double>(sh.hin) / sh.hout;
-            auto need = [&](int32_t t) {
-                const int64_t r = static_cast<int64_t>((t - 1) * ratio) + 3;
-                return static_cast<int32_t>(r < sh.hin ? r : sh.hin);
-            };
-            const int64_t rowBytes = static_cast<int64_t>(sh.win) * sizeof(T);
-            const int32_t tileRows = PickTileRows(sh.hout, rowBytes, kStageBudget, need);
-            const bool tiled = tileRows > 0 && planes * CeilDiv(sh.hout, tileRows) < (1LL << 31);
-            if (tiled) {
-                v = std::min<int>(v, 4 / static_cast<int>(sizeof(T))); // 4 bytes per lane: see the kernel's mapping
-            }
-            OPSCV_DISPATCH_VEC(v, V, {
-                if constexpr (V * sizeof(T) <= 16) {
-                    if (tiled) {
-                        const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
-                        const int64_t cap = static_cast<int64_t>(need(tileRows)) * sh.win;
-                        NearestFwdTileKernel<T, V>
-                            <<<static_cast<unsigned>(planes * tiles), kThreads, StageBytes(cap, sizeof(T)), s>>>(
-                                static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th.src,
-                                tw.src, tileRows, tiles, cap);
-                    } else {
-                        const int64_t total = planes * sh.hout * (sh.wout / V);
-                        NearestFwdNCHWKernel<T, V><<<GridFor(total, kThreads), kThreads, 0, s>>>(
-                            static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th.src,
-                            tw.src, total);
-                    }
+            const int v = PickVec(sizeof(T), sh.wout, {y});
+            const bool vec16 = v * sizeof(T) == 16;
+            if (plan.schedule == NearestPlan::kInteger && vec16 && Aligned(x, 16)) {
+                const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(planes, 1 << 30));
+                const T* px = static_cast<const T*>(x);
+                T* py = static_cast<T*>(y);
+                if (plan.rw == 2) {
+                    NearestFwdReplicateKernel<T, 2><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
+                } else if (plan.rw == 3) {
+                    NearestFwdReplicateKernel<T, 3><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
+                } else {
+                    NearestFwdReplicateKernel<T, 4><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
                 }
-            });
+            } else {
+                OPSCV_DISPATCH_VEC(v, V, {
+                    if constexpr (V * sizeof(T) <= 16) {
+                        if (plan.schedule != NearestPlan::kDirect && plan.tileRows > 0) {
+                            const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
+                            const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.win, sizeof(T));
+                            NearestFwdTileKernel<T, V><<<static_cast<unsigned>(planes * tiles), kThreads, smem, s>>>(
+                                static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th.src,
+                                tw.src, plan.tileRows, tiles);
+                        } else {
+                            const int64_t total = planes * sh.hout * (sh.wout / V);
+                            NearestFwdNCHWKernel<T, V><<<GridFor(total, kThreads), kThreads, 0, s>>>(
+                                static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th.src,
+                                tw.src, total);
+                        }
+                    }
+                });
+            }
         } else {
             const int v = PickVec(sizeof(T), sh.c, {x, y});
             OPSCV_DISPATCH_VEC(v, V, {
@@ -306,41 +453,43 @@ cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Nea
 }
 
 cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, RangeAxis th, RangeAxis tw,
-                       cudaStream_t s)
+                       const NearestPlan& plan, cudaStream_t s)
 {
     const int64_t planes = sh.n * sh.c;
     OPSCV_DISPATCH_DT(dt, T, {
         if (lay == kNCHW) {
-            int v = PickVec(sizeof(T), sh.win, {gi});
-            // grads rows needed by t consecutive grad_input rows: [ceil(y*inv), ceil((y+t)*inv)) -> t*inv + 2
-            const double inv = static_cast<double>(sh.hout) / sh.hin;
-            auto need = [&](int32_t t) {
-                const int64_t r = static_cast<int64_t>(t * inv) + 3;
-                return static_cast<int32_t>(r < sh.hout ? r : sh.hout);
-            };
-            const int64_t rowBytes = static_cast<int64_t>(sh.wout) * sizeof(T);
-            const int32_t tileRows = PickTileRows(sh.hin, rowBytes, kStageBudget, need);
-            const bool tiled = tileRows > 0 && planes * CeilDiv(sh.hin, tileRows) < (1LL << 31);
-            if (tiled) {
-                v = std::min<int>(v, 4 / static_cast<int>(sizeof(T)));
-            }
-            OPSCV_DISPATCH_VEC(v, V, {
-                if constexpr (V * sizeof(T) <= 16) {
-                    if (tiled) {
-                        const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, tileRows));
-                        const int64_t cap = static_cast<int64_t>(need(tileRows)) * sh.wout;
-                        NearestBwdTileKernel<T, V>
-                            <<<static_cast<unsigned>(planes * tiles), kThreads, StageBytes(cap, sizeof(T)), s>>>(
-                                static_cast<const T*>(go), static_cast<T*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th, tw,
-                                tileRows, tiles, cap);
-                    } else {
-                        const int64_t total = planes * sh.hin * (sh.win / V);
-                        NearestBwdNCHWKernel<T, V><<<GridFor(total, kThreads), kThreads, 0, s>>>(
-                            static_cast<const T*>(go), static_cast<T*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th, tw,
-                            total);
-                    }
+            const int v = PickVec(sizeof(T), sh.win, {gi});
+            constexpr int VI = 16 / sizeof(T);
+            // the pooling kernel stores VI / rw elements per thread: needs that alignment on grad_input
+            const bool poolOk = plan.schedule == NearestPlan::kInteger && Aligned(go, 16) &&
+                                Aligned(gi, sizeof(T) * VI / plan.rw);
+            if (poolOk) {
+                const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(planes, 1 << 30));
+                const T* pg = static_cast<const T*>(go);
+                T* po = static_cast<T*>(gi);
+                if (plan.rw == 2) {
+                    NearestBwdPoolKernel<T, 2><<<blocks, kThreads, 0, s>>>(pg, po, sh.hin, sh.win, plan.rh, planes);
+                } else {
+                    NearestBwdPoolKernel<T, 4><<<blocks, kThreads, 0, s>>>(pg, po, sh.hin, sh.win, plan.rh, planes);
                 }
-            });
+            } else {
+                OPSCV_DISPATCH_VEC(v, V, {
+                    if constexpr (V * sizeof(T) <= 16) {
+                        if (plan.schedule != NearestPlan::kDirect && plan.tileRows > 0) {
+                            const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, plan.tileRows));
+                            const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.wout, sizeof(T));
+                            NearestBwdTileKernel<T, V><<<static_cast<unsigned>(planes * tiles), kThreads, smem, s>>>(
+                                static_cast<const T*>(go), static_cast<T*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th,
+                                tw, plan.tileRows, tiles);
+                        } else {
+                            const int64_t total = planes * sh.hin * (sh.win / V);
+                            NearestBwdNCHWKernel<T, V><<<GridFor(total, kThreads), kThreads, 0, s>>>(
+                                static_cast<const T*>(go), static_cast<T*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th,
+                                tw, total);
+                        }
+                    }
+                });
+            }
         } else {
             const int v = PickVec(sizeof(T), sh.c, {go, gi});
             OPSCV_DISPATCH_VEC(v, V, {
