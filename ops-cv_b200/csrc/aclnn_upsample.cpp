@@ -154,9 +154,11 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
     const NearestPlan plan = MakeNearestFwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const NearestAxis th{reinterpret_cast<int32_t*>(w + offH)}, tw{reinterpret_cast<int32_t*>(w + offW)};
-        cudaError_t e = BuildNearestFwdTables(ah, aw, th, tw, s);
-        if (e != cudaSuccess) {
-            return e;
+        if (!NearestFwdUsesInteger(dt, lay, x.At(w), y.At(w), sh, plan)) {
+            const cudaError_t e = BuildNearestFwdTables(ah, aw, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
         }
         return NearestFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, plan, s);
     });
@@ -539,9 +541,11 @@ aclnnStatus aclnnUpsampleNearest2dBackwardGetWorkspaceSize(const aclTensor* grad
     const NearestPlan plan = MakeNearestBwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const RangeAxis th = RangeAt(w, rh), tw = RangeAt(w, rw);
-        cudaError_t e = BuildNearestBwdTables(ah, aw, th, tw, s);
-        if (e != cudaSuccess) {
-            return e;
+        if (!NearestBwdUsesInteger(dt, lay, g.At(w), y.At(w), sh, plan)) {
+            const cudaError_t e = BuildNearestBwdTables(ah, aw, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
         }
         return NearestBwd(dt, lay, g.At(w), y.At(w), sh, th, tw, plan, s);
     });

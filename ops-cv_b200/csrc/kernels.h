@@ -76,6 +76,8 @@ struct NearestPlan {
 };
 NearestPlan MakeNearestFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw);
 NearestPlan MakeNearestBwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw);
+bool NearestFwdUsesInteger(Dt dt, Layout lay, const void* x, const void* y, Shape4 sh, const NearestPlan& plan);
+bool NearestBwdUsesInteger(Dt dt, Layout lay, const void* go, const void* gi, Shape4 sh, const NearestPlan& plan);
 cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, NearestAxis th, NearestAxis tw,
                        const NearestPlan& plan, cudaStream_t s);
 cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, RangeAxis th, RangeAxis tw,
@@ -86,6 +88,7 @@ struct BilinearPlan {
     int32_t tileRows; // kTiled: output (forward) / grad_input (backward) rows per block
     int32_t bandRows; // kTiled: most rows of the other tensor any tile reads
     int32_t tapsW;    // kTiled backward: most grads columns feeding one grad_input column
+    int32_t planesPerBlock; // kTiled: planes whose bands share one block's shared memory
 };
 BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
 BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);

@@ -26,6 +26,19 @@ inline unsigned GridFor(int64_t items, int threads, int blocksPerSm = 8)
     return static_cast<unsigned>(g);
 }
 
+// Block shape (column threads, row threads) of the plane-tile kernels: one thread per column group, and as many
+// row threads as keep about `rowsPerThread` rows of the tile for each of them (long walks reuse more).
+inline dim3 TileBlock(int32_t groups, int32_t rows, int32_t rowsPerThread = 16)
+{
+    int32_t ct = groups < 256 ? groups : 256;
+    ct = ct < 1 ? 1 : ct;
+    int32_t rt = 256 / ct;
+    const int32_t wantRt = (rows + rowsPerThread - 1) / rowsPerThread;
+    rt = rt < wantRt ? rt : wantRt;
+    rt = rt < 1 ? 1 : rt;
+    return dim3(static_cast<unsigned>(ct), static_cast<unsigned>(rt), 1);
+}
+
 inline bool Aligned(const void* p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
 
 // Largest vector width (in elements, power of two, at most 16 bytes) such that `inner` is a multiple of it and

@@ -14,7 +14,7 @@ namespace opscv {
 // Copies `count` consecutive elements starting at `src` (global) into shared memory and returns the shared
 // pointer p with p[k] == src[k]. `raw` must be 16-byte aligned and hold count * sizeof(T) + 16 bytes: the copy is
 // shifted so that shared and global addresses are congruent modulo 16, which lets the body move as uint4.
-// All threads of the block must call it; the caller synchronises afterwards.
+// All threads of the (1-D or 2-D) block must call it; the caller synchronises afterwards.
 template <typename T>
 __device__ __forceinline__ T* StageSpan(const T* __restrict__ src, int64_t count, unsigned char* raw)
 {
@@ -27,15 +27,16 @@ __device__ __forceinline__ T* StageSpan(const T* __restrict__ src, int64_t count
     }
     const int64_t body = (count - head) / kPer;
     const int64_t tailStart = head + body * kPer;
-    for (int64_t i = threadIdx.x; i < head; i += blockDim.x) {
+    const int32_t tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
+    for (int64_t i = tid; i < head; i += nthreads) {
         dst[i] = __ldg(src + i);
     }
     const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
     uint4* d4 = reinterpret_cast<uint4*>(dst + head);
-    for (int64_t i = threadIdx.x; i < body; i += blockDim.x) {
+    for (int64_t i = tid; i < body; i += nthreads) {
         d4[i] = __ldg(s4 + i);
     }
-    for (int64_t i = tailStart + threadIdx.x; i < count; i += blockDim.x) {
+    for (int64_t i = tailStart + tid; i < count; i += nthreads) {
         dst[i] = __ldg(src + i);
     }
     return dst;

@@ -35,7 +35,7 @@ namespace opscv {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int64_t kStageBudget = 24 * 1024; // staged bytes per block: keeps 8 blocks resident per SM
+constexpr int64_t kStageBudget = 40 * 1024; // staged bytes per block: 5 blocks resident per SM
 
 // ---- forward, NCHW ----------------------------------------------------------------------------------------
 template <typename T, int V>
@@ -123,40 +123,36 @@ __device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const 
     StorePack<T, V>(dst, out);
 }
 
-// Splits the rows [h0, h1) of a tile among the row-threads of a block: thread `rc` of `rowThreads` gets [ha, hb).
-__device__ __forceinline__ void RowChunk(int32_t h0, int32_t h1, int32_t rc, int32_t rowThreads, int32_t& ha,
-                                         int32_t& hb)
-{
-    const int32_t chunk = (h1 - h0 + rowThreads - 1) / rowThreads;
-    ha = min(h1, h0 + rc * chunk);
-    hb = min(h1, ha + chunk);
-}
-
 // ---- forward, NCHW, shared-memory staged ---------------------------------------------------------------------
-// grid.x = planes * tilesPerPlane. A tile is `tileRows` output rows; its input rows [lo[h0], hi[h1-1]] are staged
-// (the host sized the tile so that they fit).
+// grid = (plane groups, tiles per plane), block = (column threads, planes). A tile is `tileRows` output rows; its
+// input rows [lo[h0], hi[h1-1]] are staged for every plane of the block (the host sized the tile so that they fit).
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
-    BilinearFwdTileKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
-                          int32_t wout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t tilesPerPlane)
+    BilinearFwdTileKernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
+                          int32_t hout, int32_t wout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t stageStride)
 {
     extern __shared__ __align__(16) unsigned char smemRaw[];
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
-    const int32_t h0 = tile * tileRows, h1 = min(hout, h0 + tileRows);
-    const int32_t r0 = __ldg(th.lo + h0), r1 = __ldg(th.hi + h1 - 1) + 1;
-    const T* plane = x + p * hin * static_cast<int64_t>(win);
-    const T* src = StageSpan<T>(plane + static_cast<int64_t>(r0) * win, static_cast<int64_t>(r1 - r0) * win, smemRaw);
+    // block = (column threads, planes): the bands of blockDim.y planes are staged, `stageStride` bytes apart
+    const int64_t pBase = static_cast<int64_t>(blockIdx.x) * blockDim.y;
+    const int32_t np = static_cast<int32_t>(min(static_cast<int64_t>(blockDim.y), planes - pBase));
+    const int32_t ha = blockIdx.y * tileRows, hb = min(hout, ha + tileRows);
+    const int32_t r0 = __ldg(th.lo + ha), r1 = __ldg(th.hi + hb - 1) + 1;
+    const int64_t planeElems = hin * static_cast<int64_t>(win);
+    const T* src = nullptr;
+    for (int32_t pl = 0; pl < np; ++pl) {
+        const T* staged = StageSpan<T>(x + (pBase + pl) * planeElems + static_cast<int64_t>(r0) * win,
+                                       static_cast<int64_t>(r1 - r0) * win, smemRaw + pl * stageStride);
+        if (pl == static_cast<int32_t>(threadIdx.y)) {
+            src = staged;
+        }
+    }
     __syncthreads();
-    const int32_t groups = wout / V;
-    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
+    if (static_cast<int32_t>(threadIdx.y) >= np) {
         return;
     }
-    int32_t ha, hb;
-    RowChunk(h0, h1, rc, rowThreads, ha, hb);
+    const int64_t p = pBase + threadIdx.y;
+    const int32_t groups = wout / V;
+    const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
     T* yp = y + p * hout * static_cast<int64_t>(wout);
     for (int32_t g = cg0; g < groups; g += colThreads) {
         int32_t wl[V], wh[V];
@@ -212,26 +208,23 @@ __global__ void __launch_bounds__(kThreads)
 // ---- forward, NCHW, output width = 2 x input width, input-major ---------------------------------------------------
 // The host has verified the column pattern lo[w] = max((w-1)>>1, 0), hi[w] = w ? min((w+1)>>1, win-1) : 0, so the
 // eight outputs of input columns c0..c0+3 read columns c0-1..c0+4 (clamped). Weights still come from the table.
-// grid.x = planes * tilesPerPlane; rows are table-driven (any vertical scale).
+// grid = (plane groups, tiles per plane), block = (column threads, planes); rows are table-driven (any vertical
+// scale).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-    BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
-                        LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t tilesPerPlane)
+    BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
+                        int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows)
 {
     constexpr int VI = 4, VO = 8;
     const int32_t wout = 2 * win;
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
-    const int32_t h0 = tile * tileRows, h1 = min(hout, h0 + tileRows);
-    const int32_t groups = win / VI;
-    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
+    // block = (column threads, planes): every thread of a block walks the same rows, so the row logic is uniform
+    const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.y + threadIdx.y;
+    if (p >= planes) {
         return;
     }
-    int32_t ha, hb;
-    RowChunk(h0, h1, rc, rowThreads, ha, hb);
+    const int32_t ha = blockIdx.y * tileRows, hb = min(hout, ha + tileRows);
+    const int32_t groups = win / VI;
+    const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
     const T* xp = x + p * hin * static_cast<int64_t>(win);
     T* yp = y + p * hout * static_cast<int64_t>(wout);
     for (int32_t g = cg0; g < groups; g += colThreads) {
@@ -383,32 +376,33 @@ __device__ __forceinline__ void WalkRows(TOut* dstBase, int32_t win, int32_t ya,
 // KW = compile-time bound on the number of grads columns feeding one grad_input column (the host checks it).
 template <typename TIn, typename TOut, int V, int KW>
 __global__ void __launch_bounds__(kThreads)
-    BilinearBwdTileKernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
-                          int32_t wout, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw, int32_t tileRows,
-                          int32_t tilesPerPlane)
+    BilinearBwdTileKernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
+                          int32_t hout, int32_t wout, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw,
+                          int32_t tileRows, int32_t stageStride)
 {
     extern __shared__ __align__(16) unsigned char smemRaw[];
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
-    const int32_t y0 = tile * tileRows, y1 = min(hin, y0 + tileRows);
-    const int32_t r0 = __ldg(rh.start + y0);
-    const int32_t r1 = max(r0, __ldg(rh.end + y1 - 1));
-    const TIn* plane = go + p * hout * static_cast<int64_t>(wout);
-    const TIn* src = StageSpan<TIn>(plane + static_cast<int64_t>(r0) * wout, static_cast<int64_t>(r1 - r0) * wout,
-                                    smemRaw);
+    // block = (column threads, planes): the bands of blockDim.y planes are staged, `stageStride` bytes apart
+    const int64_t pBase = static_cast<int64_t>(blockIdx.x) * blockDim.y;
+    const int32_t np = static_cast<int32_t>(min(static_cast<int64_t>(blockDim.y), planes - pBase));
+    const int32_t ya = blockIdx.y * tileRows, yb = min(hin, ya + tileRows);
+    const int32_t r0 = __ldg(rh.start + ya);
+    const int32_t r1 = max(r0, __ldg(rh.end + yb - 1));
+    const int64_t planeElems = hout * static_cast<int64_t>(wout);
+    const TIn* src = nullptr;
+    for (int32_t pl = 0; pl < np; ++pl) {
+        const TIn* staged = StageSpan<TIn>(go + (pBase + pl) * planeElems + static_cast<int64_t>(r0) * wout,
+                                           static_cast<int64_t>(r1 - r0) * wout, smemRaw + pl * stageStride);
+        if (pl == static_cast<int32_t>(threadIdx.y)) {
+            src = staged;
+        }
+    }
     __syncthreads();
+    if (static_cast<int32_t>(threadIdx.y) >= np) {
+        return;
+    }
+    const int64_t p = pBase + threadIdx.y;
     const int32_t groups = win / V;
-    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
-        return;
-    }
-    int32_t ya, yb;
-    RowChunk(y0, y1, rc, rowThreads, ya, yb);
-    if (ya >= yb) {
-        return;
-    }
+    const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
     TOut* gp = gi + p * hin * static_cast<int64_t>(win);
     for (int32_t g = cg0; g < groups; g += colThreads) {
         int32_t js[V], cnt[V];
@@ -446,26 +440,19 @@ __global__ void __launch_bounds__(kThreads)
 // one 16-byte (fp16/bf16) or two 16-byte (fp32) vectors plus one neighbour on each side.
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(kThreads)
-    BilinearBwdW2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
-                        LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows, int32_t tilesPerPlane)
+    BilinearBwdW2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
+                        int32_t hout, LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows)
 {
     constexpr int V = 4, VG = 8;
     const int32_t wout = 2 * win;
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
-    const int32_t y0 = tile * tileRows, y1 = min(hin, y0 + tileRows);
+    // block = (column threads, planes): every thread of a block walks the same rows, so the row logic is uniform
+    const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.y + threadIdx.y;
+    if (p >= planes) {
+        return;
+    }
+    const int32_t ya = blockIdx.y * tileRows, yb = min(hin, ya + tileRows);
     const int32_t groups = win / V;
-    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
-        return;
-    }
-    int32_t ya, yb;
-    RowChunk(y0, y1, rc, rowThreads, ya, yb);
-    if (ya >= yb) {
-        return;
-    }
+    const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
     const TIn* gp = go + p * hout * static_cast<int64_t>(wout);
     TOut* op = gi + p * hin * static_cast<int64_t>(win);
     for (int32_t g = cg0; g < groups; g += colThreads) {
@@ -746,15 +733,25 @@ bool IsW2BackwardPattern(const host::Ranges& r, int32_t in, int32_t out)
     return true;
 }
 
-// Rows per block for the kernels that do not stage: whole planes when there are many, bands when there are few.
-int32_t RowsForOccupancy(int64_t planes, int32_t rows)
+// Block shape (column threads, planes per block).
+dim3 PlaneBlock(int32_t groups, int64_t planes, int32_t maxPlanes = 256)
 {
-    const int64_t wantBlocks = static_cast<int64_t>(NumSMs()) * 4;
-    if (planes >= wantBlocks) {
+    const int32_t ct = std::max(1, std::min(groups, kThreads));
+    int64_t pb = std::max(1, kThreads / ct);
+    pb = std::min<int64_t>({pb, planes, static_cast<int64_t>(maxPlanes)});
+    return dim3(static_cast<unsigned>(ct), static_cast<unsigned>(std::max<int64_t>(pb, 1)), 1);
+}
+
+// Rows per block for the kernels that do not stage: whole planes when there are many, bands when there are few.
+int32_t RowsForOccupancy(int64_t threadsPerTileRowSet, int32_t rows)
+{
+    // enough tiles for about two full waves of resident threads, but walks of at least 8 rows
+    const int64_t wantThreads = static_cast<int64_t>(NumSMs()) * 2048 * 2;
+    if (threadsPerTileRowSet >= wantThreads) {
         return rows;
     }
-    const int64_t tiles = CeilDiv(wantBlocks, planes > 0 ? planes : 1);
-    return static_cast<int32_t>(std::max<int64_t>(8, CeilDiv(rows, tiles)));
+    const int64_t tiles = CeilDiv(wantThreads, threadsPerTileRowSet > 0 ? threadsPerTileRowSet : 1);
+    return static_cast<int32_t>(std::max<int64_t>({8, CeilDiv(rows, tiles), CeilDiv(rows, 65535)}));
 }
 
 template <typename TIn, typename TOut>
@@ -767,23 +764,28 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
         const TIn* pg = static_cast<const TIn*>(go);
         TOut* po = static_cast<TOut*>(gi);
         if (plan.schedule == BilinearPlan::kW2 && v >= 4 && Aligned(go, 16)) {
-            const int32_t tileRows = RowsForOccupancy(planes, sh.hin);
+            const int32_t tileRows = RowsForOccupancy(planes * (sh.win / 4), sh.hin);
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, tileRows));
-            BilinearBwdW2Kernel<TIn, TOut><<<static_cast<unsigned>(planes * tiles), kThreads, 0, s>>>(
-                pg, po, sh.hin, sh.win, sh.hout, th, tw, rh, tileRows, tiles);
+            const dim3 block = PlaneBlock(sh.win / 4, planes);
+            const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
+            BilinearBwdW2Kernel<TIn, TOut><<<grid, block, 0, s>>>(pg, po, planes, sh.hin, sh.win, sh.hout, th, tw, rh,
+                                                                  tileRows);
         } else if (plan.schedule != BilinearPlan::kDirect && plan.tileRows > 0) {
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, plan.tileRows));
-            const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.wout, sizeof(TIn));
-            const unsigned blocks = static_cast<unsigned>(planes * tiles);
+            const int32_t stride = static_cast<int32_t>(
+                (StageBytes(static_cast<int64_t>(plan.bandRows) * sh.wout, sizeof(TIn)) + 15) & ~size_t(15));
             const int vv = std::min(v, 4);
             OPSCV_DISPATCH_VEC(vv, V, {
                 if constexpr (V <= 4) {
+                    const dim3 block = PlaneBlock(sh.win / V, planes, plan.planesPerBlock);
+                    const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
+                    const size_t smem = static_cast<size_t>(stride) * block.y;
                     if (plan.tapsW <= 4) {
-                        BilinearBwdTileKernel<TIn, TOut, V, 4><<<blocks, kThreads, smem, s>>>(
-                            pg, po, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, plan.tileRows, tiles);
+                        BilinearBwdTileKernel<TIn, TOut, V, 4><<<grid, block, smem, s>>>(
+                            pg, po, planes, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, plan.tileRows, stride);
                     } else {
-                        BilinearBwdTileKernel<TIn, TOut, V, 8><<<blocks, kThreads, smem, s>>>(
-                            pg, po, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, plan.tileRows, tiles);
+                        BilinearBwdTileKernel<TIn, TOut, V, 8><<<grid, block, smem, s>>>(
+                            pg, po, planes, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, plan.tileRows, stride);
                     }
                 }
             });
@@ -828,14 +830,23 @@ BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, Axis
         plan.schedule = BilinearPlan::kW2;
         return plan;
     }
+    // Several planes share a block (uniform row walks, full warps even for narrow images); their bands share the
+    // staging budget. Aim for bands of at least 8 input rows, with fewer planes per block if rows are long.
     const int64_t rowBytes = static_cast<int64_t>(sh.win) * es;
-    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hin));
+    const int32_t vMax = std::min(4, 16 / es);
+    int32_t pb = static_cast<int32_t>(PlaneBlock(std::max(1, sh.wout / vMax), sh.n * sh.c).y);
+    pb = static_cast<int32_t>(std::max<int64_t>(1, std::min<int64_t>(pb, kStageBudget / (rowBytes * 8 + 32))));
+    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>((kStageBudget / pb - 32) / rowBytes, sh.hin));
     auto need = [&](int32_t h0, int32_t h1) { return tH.hi[h1 - 1] - tH.lo[h0] + 1; };
-    const int32_t tileRows = host::PickTileRows(sh.hout, budgetRows, need);
-    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hout, tileRows) < (1LL << 31)) {
+    int32_t tileRows = host::PickTileRows(sh.hout, budgetRows, need);
+    if (tileRows > 0) { // no taller than needed to keep the machine busy
+        tileRows = std::min(tileRows, RowsForOccupancy(sh.n * sh.c * std::max(1, sh.wout / vMax), sh.hout));
+    }
+    if (tileRows > 0 && sh.n * sh.c < (1LL << 31) && CeilDiv(sh.hout, tileRows) <= 65535) {
         plan.schedule = BilinearPlan::kTiled;
         plan.tileRows = tileRows;
         plan.bandRows = host::MaxBand(sh.hout, tileRows, need);
+        plan.planesPerBlock = pb;
     }
     return plan;
 }
@@ -861,14 +872,21 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
         taps = std::max(taps, rW.end[x] - rW.start[x]);
     }
     const int64_t rowBytes = static_cast<int64_t>(sh.wout) * es;
-    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hout));
+    const int32_t vMax = std::min(4, 16 / es);
+    int32_t pb = static_cast<int32_t>(PlaneBlock(std::max(1, sh.win / vMax), sh.n * sh.c).y);
+    pb = static_cast<int32_t>(std::max<int64_t>(1, std::min<int64_t>(pb, kStageBudget / (rowBytes * 8 + 32))));
+    const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>((kStageBudget / pb - 32) / rowBytes, sh.hout));
     auto need = [&](int32_t y0, int32_t y1) { return std::max(0, rH.end[y1 - 1] - rH.start[y0]); };
-    const int32_t tileRows = taps <= 8 ? host::PickTileRows(sh.hin, budgetRows, need) : 0;
-    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hin, tileRows) < (1LL << 31)) {
+    int32_t tileRows = taps <= 8 ? host::PickTileRows(sh.hin, budgetRows, need) : 0;
+    if (tileRows > 0) {
+        tileRows = std::min(tileRows, RowsForOccupancy(sh.n * sh.c * std::max(1, sh.win / vMax), sh.hin));
+    }
+    if (tileRows > 0 && sh.n * sh.c < (1LL << 31) && CeilDiv(sh.hin, tileRows) <= 65535) {
         plan.schedule = BilinearPlan::kTiled;
         plan.tileRows = tileRows;
         plan.bandRows = host::MaxBand(sh.hin, tileRows, need);
         plan.tapsW = taps;
+        plan.planesPerBlock = pb;
     }
     return plan;
 }
@@ -886,19 +904,22 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
             const bool w2Ok = plan.schedule == BilinearPlan::kW2 && Aligned(x, 4 * sizeof(T)) &&
                               Aligned(y, sizeof(T) == 2 ? 16 : 16) && (sh.wout * sizeof(T)) % 16 == 0;
             if (w2Ok) {
-                const int32_t tileRows = RowsForOccupancy(planes, sh.hout);
+                const int32_t tileRows = RowsForOccupancy(planes * (sh.win / 4), sh.hout);
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
-                BilinearFwdW2Kernel<T><<<static_cast<unsigned>(planes * tiles), kThreads, 0, s>>>(
-                    px, py, sh.hin, sh.win, sh.hout, th, tw, tileRows, tiles);
+                const dim3 block = PlaneBlock(sh.win / 4, planes);
+                const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
+                BilinearFwdW2Kernel<T><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows);
             } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
-                const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.win, sizeof(T));
-                const unsigned blocks = static_cast<unsigned>(planes * tiles);
+                const int32_t stride = static_cast<int32_t>(
+                    (StageBytes(static_cast<int64_t>(plan.bandRows) * sh.win, sizeof(T)) + 15) & ~size_t(15));
                 const int vv = std::min(v, 4);
                 OPSCV_DISPATCH_VEC(vv, V, {
                     if constexpr (V <= 4) {
-                        BilinearFwdTileKernel<T, V><<<blocks, kThreads, smem, s>>>(px, py, sh.hin, sh.win, sh.hout,
-                                                                                  sh.wout, th, tw, plan.tileRows, tiles);
+                        const dim3 block = PlaneBlock(sh.wout / V, planes, plan.planesPerBlock);
+                        const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
+                        BilinearFwdTileKernel<T, V><<<grid, block, static_cast<size_t>(stride) * block.y, s>>>(
+                            px, py, planes, sh.hin, sh.win, sh.hout, sh.wout, th, tw, plan.tileRows, stride);
                     }
                 });
             } else {

@@ -220,29 +220,26 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 // ---- NCHW, any scale, shared-memory staged -----------------------------------------------------------------------
-// grid.x = planes * tilesPerPlane; a tile is `tileRows` output rows of one plane, whose input rows
+// grid = (planes, tiles per plane), block = (column threads, row threads); a tile is `tileRows` output rows of one plane, whose input rows
 // [sh[h0], sh[h1-1]] are staged (the host sized the tile so that they fit).
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
     NearestFwdTileKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
                          int32_t wout, const int32_t* __restrict__ sh, const int32_t* __restrict__ sw,
-                         int32_t tileRows, int32_t tilesPerPlane)
+                         int32_t tileRows)
 {
     extern __shared__ __align__(16) unsigned char smemRaw[];
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
+    const int64_t p = blockIdx.x;
+    const int32_t tile = blockIdx.y;
     const int32_t h0 = tile * tileRows, h1 = min(hout, h0 + tileRows);
     const int32_t r0 = __ldg(sh + h0), r1 = __ldg(sh + h1 - 1) + 1;
     const T* plane = x + p * hin * static_cast<int64_t>(win);
     const T* src = StageSpan<T>(plane + static_cast<int64_t>(r0) * win, static_cast<int64_t>(r1 - r0) * win, smemRaw);
     __syncthreads();
+    // blockDim = (column threads, row threads)
     const int32_t groups = wout / V;
-    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
-        return;
-    }
+    const int32_t colThreads = blockDim.x, rowThreads = blockDim.y;
+    const int32_t cg0 = threadIdx.x, rc = threadIdx.y;
     T* yp = y + p * hout * static_cast<int64_t>(wout);
     for (int32_t g = cg0; g < groups; g += colThreads) {
         int32_t col[V];
@@ -269,11 +266,11 @@ __global__ void __launch_bounds__(kThreads)
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
     NearestBwdTileKernel(const T* __restrict__ go, T* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
-                         int32_t wout, RangeAxis th, RangeAxis tw, int32_t tileRows, int32_t tilesPerPlane)
+                         int32_t wout, RangeAxis th, RangeAxis tw, int32_t tileRows)
 {
     extern __shared__ __align__(16) unsigned char smemRaw[];
-    const int64_t p = blockIdx.x / tilesPerPlane;
-    const int32_t tile = blockIdx.x - p * tilesPerPlane;
+    const int64_t p = blockIdx.x;
+    const int32_t tile = blockIdx.y;
     const int32_t y0 = tile * tileRows, y1 = min(hin, y0 + tileRows);
     const int32_t r0 = __ldg(th.start + y0);
     const int32_t r1 = max(r0, __ldg(th.end + y1 - 1));
@@ -281,13 +278,10 @@ __global__ void __launch_bounds__(kThreads)
     const T* src = StageSpan<T>(plane + static_cast<int64_t>(r0) * wout, static_cast<int64_t>(r1 - r0) * wout,
                                 smemRaw);
     __syncthreads();
+    // blockDim = (column threads, row threads)
     const int32_t groups = win / V;
-    const int32_t colThreads = min(groups, static_cast<int32_t>(blockDim.x));
-    const int32_t rowThreads = static_cast<int32_t>(blockDim.x) / colThreads;
-    const int32_t cg0 = threadIdx.x % colThreads, rc = threadIdx.x / colThreads;
-    if (rc >= rowThreads) {
-        return;
-    }
+    const int32_t colThreads = blockDim.x, rowThreads = blockDim.y;
+    const int32_t cg0 = threadIdx.x, rc = threadIdx.y;
     T* gp = gi + p * hin * static_cast<int64_t>(win);
     for (int32_t g = cg0; g < groups; g += colThreads) {
         int32_t ws[V], we[V];
@@ -361,7 +355,7 @@ NearestPlan MakeNearestFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGe
     const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hin));
     auto need = [&](int32_t h0, int32_t h1) { return srcH[h1 - 1] - srcH[h0] + 1; };
     const int32_t tileRows = host::PickTileRows(sh.hout, budgetRows, need);
-    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hout, tileRows) < (1LL << 31)) {
+    if (tileRows > 0 && sh.n * sh.c < (1LL << 31) && CeilDiv(sh.hout, tileRows) <= 65535) {
         plan.schedule = NearestPlan::kTiled;
         plan.tileRows = tileRows;
         plan.bandRows = host::MaxBand(sh.hout, tileRows, need);
@@ -391,12 +385,28 @@ NearestPlan MakeNearestBwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGe
     const int32_t budgetRows = static_cast<int32_t>(std::min<int64_t>(kStageBudget / rowBytes, sh.hout));
     auto need = [&](int32_t y0, int32_t y1) { return std::max(0, rH.end[y1 - 1] - rH.start[y0]); };
     const int32_t tileRows = host::PickTileRows(sh.hin, budgetRows, need);
-    if (tileRows > 0 && sh.n * sh.c * CeilDiv(sh.hin, tileRows) < (1LL << 31)) {
+    if (tileRows > 0 && sh.n * sh.c < (1LL << 31) && CeilDiv(sh.hin, tileRows) <= 65535) {
         plan.schedule = NearestPlan::kTiled;
         plan.tileRows = tileRows;
         plan.bandRows = host::MaxBand(sh.hin, tileRows, need);
     }
     return plan;
+}
+
+// The integer-factor kernels address everything arithmetically and need 16-byte aligned rows; when they apply
+// the index tables are not read at all (the host then skips building them).
+bool NearestFwdUsesInteger(Dt dt, Layout lay, const void* x, const void* y, Shape4 sh, const NearestPlan& plan)
+{
+    const int vi = 16 / DtSize(dt);
+    return lay == kNCHW && plan.schedule == NearestPlan::kInteger && sh.wout % vi == 0 && Aligned(x, 16) &&
+           Aligned(y, 16);
+}
+
+bool NearestBwdUsesInteger(Dt dt, Layout lay, const void* go, const void* gi, Shape4 sh, const NearestPlan& plan)
+{
+    const int vi = 16 / DtSize(dt);
+    return lay == kNCHW && plan.schedule == NearestPlan::kInteger && sh.wout % vi == 0 && Aligned(go, 16) &&
+           Aligned(gi, static_cast<size_t>(16 / plan.rw));
 }
 
 cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, NearestAxis th, NearestAxis tw,
@@ -406,8 +416,7 @@ cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Nea
     OPSCV_DISPATCH_DT(dt, T, {
         if (lay == kNCHW) {
             const int v = PickVec(sizeof(T), sh.wout, {y});
-            const bool vec16 = v * sizeof(T) == 16;
-            if (plan.schedule == NearestPlan::kInteger && vec16 && Aligned(x, 16)) {
+            if (NearestFwdUsesInteger(dt, lay, x, y, sh, plan)) {
                 const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(planes, 1 << 30));
                 const T* px = static_cast<const T*>(x);
                 T* py = static_cast<T*>(y);
@@ -424,9 +433,10 @@ cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Nea
                         if (plan.schedule != NearestPlan::kDirect && plan.tileRows > 0) {
                             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
                             const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.win, sizeof(T));
-                            NearestFwdTileKernel<T, V><<<static_cast<unsigned>(planes * tiles), kThreads, smem, s>>>(
+                            const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(tiles));
+                            NearestFwdTileKernel<T, V><<<grid, TileBlock(sh.wout / V, plan.tileRows, 8), smem, s>>>(
                                 static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th.src,
-                                tw.src, plan.tileRows, tiles);
+                                tw.src, plan.tileRows);
                         } else {
                             const int64_t total = planes * sh.hout * (sh.wout / V);
                             NearestFwdNCHWKernel<T, V><<<GridFor(total, kThreads), kThreads, 0, s>>>(
@@ -459,11 +469,7 @@ cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, R
     OPSCV_DISPATCH_DT(dt, T, {
         if (lay == kNCHW) {
             const int v = PickVec(sizeof(T), sh.win, {gi});
-            constexpr int VI = 16 / sizeof(T);
-            // the pooling kernel stores VI / rw elements per thread: needs that alignment on grad_input
-            const bool poolOk = plan.schedule == NearestPlan::kInteger && Aligned(go, 16) &&
-                                Aligned(gi, sizeof(T) * VI / plan.rw);
-            if (poolOk) {
+            if (NearestBwdUsesInteger(dt, lay, go, gi, sh, plan)) {
                 const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(planes, 1 << 30));
                 const T* pg = static_cast<const T*>(go);
                 T* po = static_cast<T*>(gi);
@@ -478,9 +484,10 @@ cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, R
                         if (plan.schedule != NearestPlan::kDirect && plan.tileRows > 0) {
                             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, plan.tileRows));
                             const size_t smem = StageBytes(static_cast<int64_t>(plan.bandRows) * sh.wout, sizeof(T));
-                            NearestBwdTileKernel<T, V><<<static_cast<unsigned>(planes * tiles), kThreads, smem, s>>>(
+                            const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(tiles));
+                            NearestBwdTileKernel<T, V><<<grid, TileBlock(sh.win / V, plan.tileRows, 8), smem, s>>>(
                                 static_cast<const T*>(go), static_cast<T*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th,
-                                tw, plan.tileRows, tiles);
+                                tw, plan.tileRows);
                         } else {
                             const int64_t total = planes * sh.hin * (sh.win / V);
                             NearestBwdNCHWKernel<T, V><<<GridFor(total, kThreads), kThreads, 0, s>>>(
