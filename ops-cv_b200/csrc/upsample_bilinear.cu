@@ -115,12 +115,16 @@ template <typename T, int V>
 __device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const float (&bot)[V], float dy)
 {
     const float dy1 = Sub(1.0f, dy);
-    float out[V];
+    constexpr int kPer = (V * sizeof(T) > 16) ? 16 / sizeof(T) : V; // at most 16 bytes per store
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-        out[k] = Add(Mul(dy1, top[k]), Mul(dy, bot[k]));
+    for (int q = 0; q < V / kPer; ++q) {
+        float out[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            out[k] = Add(Mul(dy1, top[q * kPer + k]), Mul(dy, bot[q * kPer + k]));
+        }
+        StorePack<T, kPer>(dst + q * kPer, out);
     }
-    StorePack<T, V>(dst, out);
 }
 
 // ---- forward, NCHW, shared-memory staged ---------------------------------------------------------------------
@@ -207,15 +211,15 @@ __global__ void __launch_bounds__(kThreads)
 
 // ---- forward, NCHW, output width = 2 x input width, input-major ---------------------------------------------------
 // The host has verified the column pattern lo[w] = max((w-1)>>1, 0), hi[w] = w ? min((w+1)>>1, win-1) : 0, so the
-// eight outputs of input columns c0..c0+3 read columns c0-1..c0+4 (clamped). Weights still come from the table.
+// 2*VI outputs of input columns c0..c0+VI-1 read columns c0-1..c0+VI (clamped). Weights still come from the table.
 // grid = (plane groups, tiles per plane), block = (column threads, planes); rows are table-driven (any vertical
 // scale).
-template <typename T>
+template <typename T, int VI>
 __global__ void __launch_bounds__(kThreads)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows)
 {
-    constexpr int VI = 4, VO = 8;
+    constexpr int VO = 2 * VI;
     const int32_t wout = 2 * win;
     // block = (column threads, planes): every thread of a block walks the same rows, so the row logic is uniform
     const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.y + threadIdx.y;
@@ -904,11 +908,19 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
             const bool w2Ok = plan.schedule == BilinearPlan::kW2 && Aligned(x, 4 * sizeof(T)) &&
                               Aligned(y, sizeof(T) == 2 ? 16 : 16) && (sh.wout * sizeof(T)) % 16 == 0;
             if (w2Ok) {
-                const int32_t tileRows = RowsForOccupancy(planes * (sh.win / 4), sh.hout);
+                // 16-bit tensors: eight input columns (one 16-byte load) per thread when the rows allow it
+                const int vi = (sizeof(T) == 2 && sh.win % 8 == 0 && Aligned(x, 16)) ? 8 : 4;
+                const int32_t tileRows = RowsForOccupancy(planes * (sh.win / vi), sh.hout);
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
-                const dim3 block = PlaneBlock(sh.win / 4, planes);
+                const dim3 block = PlaneBlock(sh.win / vi, planes);
                 const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
-                BilinearFwdW2Kernel<T><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows);
+                if (vi == 8) {
+                    if constexpr (sizeof(T) == 2) {
+                        BilinearFwdW2Kernel<T, 8><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows);
+                    }
+                } else {
+                    BilinearFwdW2Kernel<T, 4><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows);
+                }
             } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
                 const int32_t stride = static_cast<int32_t>(
