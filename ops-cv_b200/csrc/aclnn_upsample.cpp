@@ -817,13 +817,23 @@ aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const a
     const Dt dt = ToDt(x->dtype);
     const AxisGeom gh{sh.hin, sh.hout, ah.scale}, gw{sh.win, sh.wout, aw.scale};
     const AAOffsets oh = AllocAA(ws, sh.hout, ah.taps), ow = AllocAA(ws, sh.wout, aw.taps);
+    const AAFwdPlan plan = MakeAAFwdPlan(dt, sh, ah.scale, aw.taps);
+    const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
+    const uint64_t wrowOff = ws.Alloc(plan.wrowBytes);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
+        const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
         cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, false, s);
         if (e != cudaSuccess) {
             return e;
         }
-        return BicubicAAFwd(dt, xin.At(w), y.At(w), sh, th, tw, s);
+        if (plan.stream) {
+            e = BuildAABwdRanges(gh, gw, th, tw, qh, qw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+        }
+        return BicubicAAFwd(dt, xin.At(w), y.At(w), sh, th, tw, qh, reinterpret_cast<float*>(w + wrowOff), plan, s);
     });
     FinishOutput(out, y, ex);
     ex->workspaceSize = ws.Size();

@@ -102,7 +102,17 @@ cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, voi
 cudaError_t BilinearBwdAtomic(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, float* acc, Shape4 sh,
                               LerpAxis th, LerpAxis tw, cudaStream_t s);
 
-cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, cudaStream_t s);
+struct AAFwdPlan {
+    bool stream;        // streaming down-scale kernel (else one thread per output element)
+    bool regWeights;    // horizontal weights of an output column fit in registers
+    int32_t threads;    // block size of the streaming kernel
+    int32_t bandRows;   // output rows per block
+    uint64_t wrowBytes; // workspace for the per-input-row vertical weights
+};
+AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW);
+// rh (ranges of outputs covering each input row) and wrow are only used by the streaming kernel.
+cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh, float* wrow,
+                         const AAFwdPlan& plan, cudaStream_t s);
 cudaError_t BicubicAABwdGather(Dt dt, const void* go, void* gi, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh,
                                RangeAxis rw, cudaStream_t s);
 cudaError_t BicubicAABwdAtomic(Dt dt, const void* go, void* gi, float* acc, Shape4 sh, AAAxis th, AAAxis tw,

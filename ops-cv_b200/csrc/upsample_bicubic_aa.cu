@@ -23,6 +23,8 @@
 // Reference arithmetic: image/upsample_bicubic2d_aa/op_kernel/arch35/upsample_bicubic2d_aa_simt_base.h:52-127,
 // image/upsample_bicubic2d_aa_grad/op_kernel/arch35/upsample_bicubic2d_aa_grad_simt_base.h:32-102 and
 // upsample_bicubic2d_aa_grad_simt_base_deter.h:30-122.
+#include <algorithm>
+
 #include "launch_util.cuh"
 
 namespace opscv {
@@ -57,6 +59,192 @@ __global__ void __launch_bounds__(kThreads)
             }
         }
         y[idx] = DType<T>::FromF(value);
+    }
+}
+
+// ---- forward, streaming (down-scaling) -----------------------------------------------------------------------
+// Per input row r, the outputs whose vertical window covers r form a short run [start(r), end(r)): for scale >= 1 an
+// output covers r iff |centre - (r + 0.5)| < support + 0.5, a span of 4*scale + 1 input pixels that holds at most
+// 4 + 1/scale + 1 <= 6 = kSlots centres. AARowWeightKernel tabulates, once per call, the weight of output
+// start(r) + a at row r for a < kSlots (0 past the run; rows are kSlotStride floats apart), so the streaming
+// kernel needs two uniform vector loads of weights per input row.
+constexpr int kSlots = 6;
+constexpr int kSlotStride = 8;
+constexpr int kStreamMaxThreads = 512; // leaves 128 registers per thread for the accumulator ring
+
+__global__ void AARowWeightKernel(AAAxis th, RangeAxis rh, int32_t hin, float* __restrict__ wrow)
+{
+    const int32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= hin) {
+        return;
+    }
+    const int32_t s = __ldg(rh.start + r), e = __ldg(rh.end + r);
+#pragma unroll
+    for (int a = 0; a < kSlots; ++a) {
+        const int32_t i = s + a;
+        float w = 0.0f;
+        if (i < e) {
+            const int32_t t = r - __ldg(th.xmin + i);
+            if (t >= 0 && t < __ldg(th.xsize + i)) {
+                w = __ldg(th.w + static_cast<int64_t>(i) * th.taps + t);
+            }
+        }
+        wrow[static_cast<int64_t>(r) * kSlotStride + a] = w;
+    }
+}
+
+// grid = (planes, bands); a band is `bandRows` output rows. Thread t owns input columns 4t..4t+3 of every row.
+// REGW: each thread also owns output column t; the horizontal weights of all columns (at most TW each) are copied to
+// shared memory once, transposed so that the threads of a warp read consecutive words.
+template <typename T, bool REGW, int TW, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+    AAFwdStreamKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
+                      int32_t wout, AAAxis th, AAAxis tw, RangeAxis rh, const float* __restrict__ wrow,
+                      int32_t bandRows)
+{
+    constexpr int VC = 4;  // input columns per thread
+    constexpr int PF = 8;  // input rows in flight per thread
+    extern __shared__ __align__(16) float rowbuf[]; // one vertically filtered row, at input width
+    float* wsm = rowbuf + ((win + 3) & ~3);          // REGW: weights [TW][wout]
+    const int64_t p = blockIdx.x;
+    const int32_t i0 = blockIdx.y * bandRows, i1 = min(hout, i0 + bandRows);
+    const int32_t rlo = __ldg(th.xmin + i0);
+    const int32_t rhi = __ldg(th.xmin + i1 - 1) + __ldg(th.xsize + i1 - 1);
+    const int32_t c = threadIdx.x * VC;
+    const bool hasCols = c < win;
+    const T* xp = x + p * hin * static_cast<int64_t>(win) + c;
+    T* yp = y + p * hout * static_cast<int64_t>(wout);
+
+    int32_t wmin = 0, wsz = 0;
+    if (REGW) {
+        if (static_cast<int32_t>(threadIdx.x) < wout) {
+            wmin = __ldg(tw.xmin + threadIdx.x);
+            wsz = min(__ldg(tw.xsize + threadIdx.x), TW);
+            for (int32_t t = 0; t < wsz; ++t) {
+                wsm[t * wout + threadIdx.x] = __ldg(tw.w + static_cast<int64_t>(threadIdx.x) * tw.taps + t);
+            }
+        }
+        __syncthreads();
+    }
+
+    float acc[kSlots][VC];
+#pragma unroll
+    for (int a = 0; a < kSlots; ++a) {
+#pragma unroll
+        for (int k = 0; k < VC; ++k) {
+            acc[a][k] = 0.0f;
+        }
+    }
+    // Emits output row i from the oldest accumulator slot: vertical result -> shared row -> horizontal filter.
+    auto flush = [&](int32_t i) {
+        if (hasCols) {
+            *reinterpret_cast<float4*>(rowbuf + c) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+        }
+        __syncthreads();
+        if (REGW) {
+            if (static_cast<int32_t>(threadIdx.x) < wout) {
+                float v = 0.0f;
+                for (int32_t t = 0; t < wsz; ++t) {
+                    v = fmaf(wsm[t * wout + threadIdx.x], rowbuf[wmin + t], v);
+                }
+                yp[static_cast<int64_t>(i) * wout + threadIdx.x] = DType<T>::FromF(v);
+            }
+        } else {
+            for (int32_t j = threadIdx.x; j < wout; j += blockDim.x) {
+                const int32_t m = __ldg(tw.xmin + j), n = __ldg(tw.xsize + j);
+                const float* wj = tw.w + static_cast<int64_t>(j) * tw.taps;
+                float v = 0.0f;
+                for (int32_t t = 0; t < n; ++t) {
+                    v = fmaf(__ldg(wj + t), rowbuf[m + t], v);
+                }
+                yp[static_cast<int64_t>(i) * wout + j] = DType<T>::FromF(v);
+            }
+        }
+        __syncthreads();
+    };
+    auto shift = [&]() {
+#pragma unroll
+        for (int a = 0; a + 1 < kSlots; ++a) {
+#pragma unroll
+            for (int k = 0; k < VC; ++k) {
+                acc[a][k] = acc[a + 1][k];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < VC; ++k) {
+            acc[kSlots - 1][k] = 0.0f;
+        }
+    };
+    auto loadRow = [&](int32_t r, float (&v)[VC]) {
+        if (hasCols && r < rhi) {
+            LoadPackLdg<T, VC>(xp + static_cast<int64_t>(r) * win, v);
+        } else {
+#pragma unroll
+            for (int k = 0; k < VC; ++k) {
+                v[k] = 0.0f;
+            }
+        }
+    };
+
+    // Row metadata (first covering output, run length, slot weights) is fetched one row ahead; input rows PF rows
+    // ahead. The row loop is unrolled by PF so that the queue slots are fixed registers (rotating them through
+    // moves would make every iteration wait for the newest load).
+    struct RowMeta {
+        int32_t s, cnt;
+        float4 w0;
+        float2 w1;
+    };
+    auto loadMeta = [&](int32_t r) {
+        RowMeta m;
+        const int32_t rr = min(r, rhi - 1);
+        m.s = __ldg(rh.start + rr);
+        m.cnt = __ldg(rh.end + rr) - m.s;
+        m.w0 = __ldg(reinterpret_cast<const float4*>(wrow) + static_cast<int64_t>(rr) * 2);
+        m.w1 = __ldg(reinterpret_cast<const float2*>(wrow) + static_cast<int64_t>(rr) * 4 + 2);
+        return m;
+    };
+    float q[PF][VC];
+#pragma unroll
+    for (int f = 0; f < PF; ++f) {
+        loadRow(rlo + f, q[f]);
+    }
+    int32_t curStart = __ldg(rh.start + rlo);
+    RowMeta meta = loadMeta(rlo);
+    for (int32_t r0 = rlo; r0 < rhi; r0 += PF) {
+#pragma unroll
+        for (int f = 0; f < PF; ++f) {
+            const int32_t r = r0 + f;
+            if (r < rhi) {
+                const RowMeta m = meta;
+                meta = loadMeta(r + 1);
+                while (curStart < m.s) { // outputs before start(r) no longer receive rows: complete
+                    if (curStart >= i0 && curStart < i1) {
+                        flush(curStart);
+                    }
+                    shift();
+                    ++curStart;
+                }
+                const float w[kSlots] = {m.w0.x, m.w0.y, m.w0.z, m.w0.w, m.w1.x, m.w1.y};
+#pragma unroll
+                for (int a = 0; a < kSlots; ++a) {
+                    if (a < m.cnt) { // slots past the run are not touched (an Inf / NaN input must not leak in)
+#pragma unroll
+                        for (int k = 0; k < VC; ++k) {
+                            acc[a][k] = fmaf(w[a], q[f][k], acc[a][k]);
+                        }
+                    }
+                }
+                loadRow(r + PF, q[f]);
+            }
+        }
+    }
+    const int32_t lastEnd = __ldg(rh.end + rhi - 1);
+    while (curStart < i1 && curStart < lastEnd) {
+        if (curStart >= i0) {
+            flush(curStart);
+        }
+        shift();
+        ++curStart;
     }
 }
 
@@ -139,9 +327,71 @@ __global__ void __launch_bounds__(kThreads)
 
 } // namespace
 
-cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, cudaStream_t s)
+AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW)
 {
-    const int64_t total = sh.n * sh.c * sh.hout * static_cast<int64_t>(sh.wout);
+    AAFwdPlan plan{};
+    // Streaming needs: every input row covered by at most kSlots outputs (true for scale >= 1), rows that one
+    // block can own (4 columns per thread) and 16-byte aligned rows.
+    const int es = DtSize(dt);
+    plan.stream = scaleH >= 1.0f && sh.win % 4 == 0 && sh.win <= 4 * kStreamMaxThreads && sh.hin >= 1 && (sh.win * es) % 8 == 0;
+    if (!plan.stream) {
+        return plan;
+    }
+    plan.regWeights = sh.wout <= kStreamMaxThreads && tapsW <= 24; // 24 * wout floats of shared memory
+    int32_t threads = static_cast<int32_t>(CeilDiv(sh.win, 4));
+    threads = std::max(threads, plan.regWeights ? sh.wout : std::min(sh.wout, 256));
+    plan.threads = std::min(kStreamMaxThreads, (threads + 31) & ~31);
+    // Bands: pick the number of bands per plane whose block count fills whole waves of resident blocks best
+    // (every band re-reads the input rows of its first window, so no more than 8, and at least 16 rows each).
+    const int64_t planes = std::max<int64_t>(sh.n * sh.c, 1);
+    const int64_t resident = static_cast<int64_t>(NumSMs()) * std::max(1, 512 / plan.threads);
+    int64_t bestBands = 1;
+    double bestEff = 0.0;
+    for (int64_t b = 1; b <= 8 && sh.hout / b >= 16; ++b) {
+        const int64_t blocks = planes * b;
+        const double eff = static_cast<double>(blocks) / (static_cast<double>(CeilDiv(blocks, resident)) * resident);
+        if (eff > bestEff + 0.02) {
+            bestEff = eff;
+            bestBands = b;
+        }
+    }
+    plan.bandRows = static_cast<int32_t>(CeilDiv(sh.hout, bestBands));
+    plan.wrowBytes = static_cast<uint64_t>(sh.hin) * kSlotStride * sizeof(float);
+    return plan;
+}
+
+cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh,
+                         float* wrow, const AAFwdPlan& plan, cudaStream_t s)
+{
+    const int64_t planes = sh.n * sh.c;
+    const bool stream = plan.stream && Aligned(x, 16) && planes < (1LL << 31) && CeilDiv(sh.hout, plan.bandRows) <= 65535;
+    if (stream) {
+        AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.hin, 128)), 128, 0, s>>>(th, rh, sh.hin, wrow);
+        const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(CeilDiv(sh.hout, plan.bandRows)));
+        const size_t smem = (static_cast<size_t>((sh.win + 3) & ~3) +
+                             (plan.regWeights ? static_cast<size_t>(24) * sh.wout : 0)) * sizeof(float);
+        OPSCV_DISPATCH_DT(dt, T, {
+            const T* px = static_cast<const T*>(x);
+            T* py = static_cast<T*>(y);
+            // blocks of at most 256 threads may use up to 255 registers: no spills of the accumulator ring
+            if (plan.regWeights && plan.threads <= 256) {
+                AAFwdStreamKernel<T, true, 24, 256><<<grid, plan.threads, smem, s>>>(
+                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
+            } else if (plan.regWeights) {
+                AAFwdStreamKernel<T, true, 24, kStreamMaxThreads><<<grid, plan.threads, smem, s>>>(
+                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
+            } else if (plan.threads <= 256) {
+                AAFwdStreamKernel<T, false, 1, 256><<<grid, plan.threads, smem, s>>>(
+                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
+            } else {
+                AAFwdStreamKernel<T, false, 1, kStreamMaxThreads><<<grid, plan.threads, smem, s>>>(
+                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
+            }
+        });
+        CountLaunch(2);
+        return cudaGetLastError();
+    }
+    const int64_t total = planes * sh.hout * static_cast<int64_t>(sh.wout);
     OPSCV_DISPATCH_DT(dt, T, {
         AAFwdDirectKernel<T><<<GridFor(total, kThreads), kThreads, 0, s>>>(
             static_cast<const T*>(x), static_cast<T*>(y), sh.hin, sh.win, sh.hout, sh.wout, th, tw, total);
