@@ -952,6 +952,8 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
         });
     } else {
         const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
+        const AABwdPlan plan = MakeAABwdPlan(dt, sh, ah.scale, aw.scale);
+        const uint64_t wrowH = ws.Alloc(plan.wrowBytesH), wrowW = ws.Alloc(plan.wrowBytesW);
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
@@ -963,7 +965,8 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
             if (e != cudaSuccess) {
                 return e;
             }
-            return BicubicAABwdGather(dt, g.At(w), y.At(w), sh, th, tw, qh, qw, s);
+            return BicubicAABwdGather(dt, g.At(w), y.At(w), sh, th, tw, qh, qw, reinterpret_cast<float*>(w + wrowH),
+                                      reinterpret_cast<float*>(w + wrowW), plan, s);
         });
     }
     FinishOutput(out, y, ex);

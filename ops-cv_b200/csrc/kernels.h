@@ -113,8 +113,16 @@ AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW);
 // rh (ranges of outputs covering each input row) and wrow are only used by the streaming kernel.
 cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh, float* wrow,
                          const AAFwdPlan& plan, cudaStream_t s);
+struct AABwdPlan {
+    bool band;         // band-tiled separable kernel (else one thread per grad_input element)
+    int32_t threads;   // block size
+    int32_t bandRows;  // grad_input rows per block
+    int32_t stageRows; // grads rows staged in shared memory per block
+    uint64_t wrowBytesH, wrowBytesW; // workspace for the per-row / per-column slot weights
+};
+AABwdPlan MakeAABwdPlan(Dt dt, Shape4 sh, float scaleH, float scaleW);
 cudaError_t BicubicAABwdGather(Dt dt, const void* go, void* gi, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh,
-                               RangeAxis rw, cudaStream_t s);
+                               RangeAxis rw, float* wrowH, float* wrowW, const AABwdPlan& plan, cudaStream_t s);
 cudaError_t BicubicAABwdAtomic(Dt dt, const void* go, void* gi, float* acc, Shape4 sh, AAAxis th, AAAxis tw,
                                cudaStream_t s);
 

@@ -290,6 +290,96 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// ---- backward, band-tiled (down-scaling forward) ----------------------------------------------------------------
+// gi[y][x] = sum_i wH(i,y) * sum_j wW(j,x) * go[i][j]. For scale >= 1 only a few outputs cover any input row or
+// column, so the sum is done separably per block: the grads rows feeding a band of grad_input rows are staged in
+// shared memory (fp32); for kBwdRows grad_input rows at a time the block first reduces vertically
+// (t[y][j] = sum_i wH * go[i][j], one thread per (row, grads column)), then every thread expands horizontally for
+// its four grad_input columns with the column weights it keeps in registers, and stores 16 bytes per row.
+// Vertical and horizontal weights come from the slot tables built by AARowWeightKernel for both axes.
+constexpr int kBwdRows = 4;   // grad_input rows per synchronisation
+constexpr int kBwdColSlots = 8; // grads columns covering four consecutive grad_input columns (<= kSlots + 2)
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+    AABwdBandKernel(const T* __restrict__ go, T* __restrict__ gi, int32_t hin, int32_t win, int32_t hout,
+                    int32_t wout, RangeAxis rh, RangeAxis rw, const float* __restrict__ wrowH,
+                    const float* __restrict__ wrowW, int32_t bandRows, int32_t stageRows)
+{
+    extern __shared__ __align__(16) float smemF[];
+    float* gos = smemF;                                        // [stageRows][wout] grads rows of the band
+    float* tbuf = smemF + static_cast<int64_t>(stageRows) * wout; // [kBwdRows][wout]
+    const int64_t p = blockIdx.x;
+    const int32_t y0 = blockIdx.y * bandRows, y1 = min(hin, y0 + bandRows);
+    const int32_t i0 = __ldg(rh.start + y0);
+    const int32_t i1 = min(max(i0, __ldg(rh.end + y1 - 1)), i0 + stageRows);
+    const T* gp = go + (p * hout + i0) * static_cast<int64_t>(wout);
+    for (int32_t e = threadIdx.x; e < (i1 - i0) * wout; e += blockDim.x) {
+        gos[e] = DType<T>::Load(gp + e);
+    }
+    // horizontal weights of my four columns: slot u <-> grads column j0 + u
+    const int32_t x = threadIdx.x * 4;
+    const bool hasCols = x < win;
+    int32_t j0 = 0;
+    float wreg[4][kBwdColSlots];
+    if (hasCols) {
+        j0 = __ldg(rw.start + x);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int32_t sk = __ldg(rw.start + x + k), ek = __ldg(rw.end + x + k);
+#pragma unroll
+            for (int u = 0; u < kBwdColSlots; ++u) {
+                const int32_t a = j0 + u - sk; // slot of grads column j0 + u in column x + k's own table
+                wreg[k][u] = (a >= 0 && a < kSlots && j0 + u < ek)
+                                 ? __ldg(wrowW + static_cast<int64_t>(x + k) * kSlotStride + a)
+                                 : 0.0f;
+            }
+        }
+    }
+    const int32_t jcnt = hasCols ? min(kBwdColSlots, __ldg(rw.end + x + 3) - j0) : 0;
+    __syncthreads();
+    T* op = gi + p * hin * static_cast<int64_t>(win);
+    for (int32_t yb = y0; yb < y1; yb += kBwdRows) {
+        // vertical: one (row, grads column) item per thread
+        for (int32_t item = threadIdx.x; item < kBwdRows * wout; item += blockDim.x) {
+            const int32_t ry = item / wout, j = item - ry * wout;
+            const int32_t y = yb + ry;
+            float v = 0.0f;
+            if (y < y1) {
+                const int32_t s = __ldg(rh.start + y), cnt = __ldg(rh.end + y) - s;
+                const float* wy = wrowH + static_cast<int64_t>(y) * kSlotStride;
+                for (int32_t a = 0; a < cnt && a < kSlots; ++a) {
+                    v = fmaf(__ldg(wy + a), gos[(s + a - i0) * wout + j], v);
+                }
+            }
+            tbuf[item] = v;
+        }
+        __syncthreads();
+        if (hasCols) {
+#pragma unroll
+            for (int ry = 0; ry < kBwdRows; ++ry) {
+                const int32_t y = yb + ry;
+                if (y < y1) {
+                    const float* tr = tbuf + ry * wout + j0;
+                    float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int u = 0; u < kBwdColSlots; ++u) {
+                        if (u < jcnt) { // slots past the run are not read
+                            const float t = tr[u];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                out[k] = fmaf(wreg[k][u], t, out[k]);
+                            }
+                        }
+                    }
+                    StorePack<T, 4>(op + static_cast<int64_t>(y) * win + x, out);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---- backward, atomic -------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -400,10 +490,63 @@ cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AA
     return cudaGetLastError();
 }
 
-cudaError_t BicubicAABwdGather(Dt dt, const void* go, void* gi, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh,
-                               RangeAxis rw, cudaStream_t s)
+AABwdPlan MakeAABwdPlan(Dt dt, Shape4 sh, float scaleH, float scaleW)
 {
-    const int64_t total = sh.n * sh.c * sh.hin * static_cast<int64_t>(sh.win);
+    AABwdPlan plan{};
+    const int es = DtSize(dt);
+    // Same covering bound as the forward streaming kernel, on both axes; one block owns whole grad_input rows.
+    plan.band = scaleH >= 1.0f && scaleW >= 1.0f && sh.win % 4 == 0 && sh.win <= 4096 && (sh.win * es) % 8 == 0;
+    if (!plan.band) {
+        return plan;
+    }
+    plan.threads = std::min(1024, std::max(128, static_cast<int32_t>((CeilDiv(sh.win, 4) + 31) & ~31)));
+    // Band height: as tall as the shared-memory stage allows (fewer re-read halo rows), but enough blocks.
+    const int64_t planes = std::max<int64_t>(sh.n * sh.c, 1);
+    const int64_t budgetFloats = (64 * 1024) / 4 - static_cast<int64_t>(kBwdRows) * sh.wout;
+    const int32_t maxStageRows = static_cast<int32_t>(std::min<int64_t>(budgetFloats / std::max(sh.wout, 1), sh.hout));
+    if (maxStageRows < kSlots + 2) {
+        plan.band = false;
+        return plan;
+    }
+    // t grad_input rows are fed by at most t / scale + kSlots grads rows
+    int32_t band = static_cast<int32_t>(std::min<double>((maxStageRows - kSlots - 1) * static_cast<double>(scaleH), sh.hin));
+    const int64_t wantBlocks = static_cast<int64_t>(NumSMs()) * 4;
+    band = static_cast<int32_t>(std::max<int64_t>(kBwdRows, std::min<int64_t>(band, CeilDiv(sh.hin * planes, wantBlocks))));
+    band = (band + kBwdRows - 1) / kBwdRows * kBwdRows;
+    plan.bandRows = band;
+    plan.stageRows = static_cast<int32_t>(std::min<int64_t>(static_cast<int64_t>(band / static_cast<double>(scaleH)) + kSlots + 2,
+                                                          sh.hout));
+    plan.wrowBytesH = static_cast<uint64_t>(sh.hin) * kSlotStride * sizeof(float);
+    plan.wrowBytesW = static_cast<uint64_t>(sh.win) * kSlotStride * sizeof(float);
+    return plan;
+}
+
+cudaError_t BicubicAABwdGather(Dt dt, const void* go, void* gi, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh,
+                               RangeAxis rw, float* wrowH, float* wrowW, const AABwdPlan& plan, cudaStream_t s)
+{
+    const int64_t planes = sh.n * sh.c;
+    const bool band = plan.band && Aligned(gi, 16) && planes < (1LL << 31) && CeilDiv(sh.hin, plan.bandRows) <= 65535;
+    if (band) {
+        AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.hin, 128)), 128, 0, s>>>(th, rh, sh.hin, wrowH);
+        AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.win, 128)), 128, 0, s>>>(tw, rw, sh.win, wrowW);
+        const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(CeilDiv(sh.hin, plan.bandRows)));
+        const size_t smem = (static_cast<size_t>(plan.stageRows) + kBwdRows) * sh.wout * sizeof(float);
+        cudaError_t e = cudaSuccess;
+        OPSCV_DISPATCH_DT(dt, T, {
+            if (smem > 48 * 1024) {
+                e = cudaFuncSetAttribute(AABwdBandKernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+            }
+            if (e == cudaSuccess) {
+                AABwdBandKernel<T><<<grid, plan.threads, smem, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), sh.hin,
+                                                                   sh.win, sh.hout, sh.wout, rh, rw, wrowH, wrowW,
+                                                                   plan.bandRows, plan.stageRows);
+            }
+        });
+        CountLaunch(3);
+        return e != cudaSuccess ? e : cudaGetLastError();
+    }
+    const int64_t total = planes * sh.hin * static_cast<int64_t>(sh.win);
     OPSCV_DISPATCH_DT(dt, T, {
         AABwdGatherKernel<T><<<GridFor(total, kThreads), kThreads, 0, s>>>(
             static_cast<const T*>(go), static_cast<T*>(gi), sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, rw, total);
