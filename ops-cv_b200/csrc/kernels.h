@@ -104,7 +104,8 @@ cudaError_t BilinearBwdAtomic(Dt dtIn, Dt dtOut, Layout lay, const void* go, voi
 
 struct AAFwdPlan {
     bool stream;        // streaming down-scale kernel (else one thread per output element)
-    bool regWeights;    // horizontal weights of an output column fit in registers
+    bool regWeights;    // horizontal weights of all output columns fit in shared memory
+    int32_t metaRows;   // most input rows a band touches (sizes the shared slot-weight records)
     int32_t threads;    // block size of the streaming kernel
     int32_t bandRows;   // output rows per block
     uint64_t wrowBytes; // workspace for the per-input-row vertical weights

@@ -66,11 +66,11 @@ __global__ void __launch_bounds__(kThreads)
 // Per input row r, the outputs whose vertical window covers r form a short run [start(r), end(r)): for scale >= 1 an
 // output covers r iff |centre - (r + 0.5)| < support + 0.5, a span of 4*scale + 1 input pixels that holds at most
 // 4 + 1/scale + 1 <= 6 = kSlots centres. AARowWeightKernel tabulates, once per call, the weight of output
-// start(r) + a at row r for a < kSlots (0 past the run; rows are kSlotStride floats apart), so the streaming
-// kernel needs two uniform vector loads of weights per input row.
+// start(r) + a at row r for a < kSlots (0 past the run), followed by start(r) and the run length as integer bit
+// patterns: one 32-byte record per input row.
 constexpr int kSlots = 6;
 constexpr int kSlotStride = 8;
-constexpr int kStreamMaxThreads = 512; // leaves 128 registers per thread for the accumulator ring
+constexpr int kStreamMaxThreads = 256; // up to 255 registers per thread for the accumulator ring and the row queue
 
 __global__ void AARowWeightKernel(AAAxis th, RangeAxis rh, int32_t hin, float* __restrict__ wrow)
 {
@@ -91,41 +91,46 @@ __global__ void AARowWeightKernel(AAAxis th, RangeAxis rh, int32_t hin, float* _
         }
         wrow[static_cast<int64_t>(r) * kSlotStride + a] = w;
     }
+    // the run itself rides along in the two spare floats of the row, so that one 32-byte read gives everything
+    wrow[static_cast<int64_t>(r) * kSlotStride + 6] = __int_as_float(s);
+    wrow[static_cast<int64_t>(r) * kSlotStride + 7] = __int_as_float(min(e - s, kSlots));
 }
 
-// grid = (planes, bands); a band is `bandRows` output rows. Thread t owns input columns 4t..4t+3 of every row.
-// REGW: each thread also owns output column t; the horizontal weights of all columns (at most TW each) are copied to
-// shared memory once, transposed so that the threads of a warp read consecutive words.
-template <typename T, bool REGW, int TW, int MAXT>
+// grid = (planes, bands); a band is `bandRows` output rows. Thread t owns input columns VC*t .. VC*t+VC-1 of every
+// row (VC * sizeof(T) = 16 or 32 bytes) and keeps one partial sum per open output row (kSlots of them) for each.
+// Shared memory: the vertically filtered row being flushed, the slot-weight rows of the band's input rows, and
+// (wTaps > 0) the horizontal weights of all output columns, transposed.
+template <typename T, int VC, int MAXT>
 __global__ void __launch_bounds__(MAXT)
     AAFwdStreamKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
-                      int32_t wout, AAAxis th, AAAxis tw, RangeAxis rh, const float* __restrict__ wrow,
-                      int32_t bandRows)
+                      int32_t wout, AAAxis th, AAAxis tw, const float* __restrict__ wrow, int32_t bandRows,
+                      int32_t metaRows, int32_t wTaps)
 {
-    constexpr int VC = 4;  // input columns per thread
-    constexpr int PF = 8;  // input rows in flight per thread
-    extern __shared__ __align__(16) float rowbuf[]; // one vertically filtered row, at input width
-    float* wsm = rowbuf + ((win + 3) & ~3);          // REGW: weights [TW][wout]
+    constexpr int PF = 4;                  // input rows in flight per thread
+    constexpr int LV = 16 / sizeof(T);     // elements per 16-byte load
+    constexpr int NL = VC / LV;            // 16-byte loads per row
+    extern __shared__ __align__(16) float smemF[];
+    float* rowbuf = smemF;                                            // [win]
+    float4* msm = reinterpret_cast<float4*>(smemF + ((win + 3) & ~3)); // [metaRows][2]
+    float* wsm = reinterpret_cast<float*>(msm + 2 * metaRows);        // [wTaps][wout]
     const int64_t p = blockIdx.x;
     const int32_t i0 = blockIdx.y * bandRows, i1 = min(hout, i0 + bandRows);
     const int32_t rlo = __ldg(th.xmin + i0);
-    const int32_t rhi = __ldg(th.xmin + i1 - 1) + __ldg(th.xsize + i1 - 1);
+    const int32_t rhi = min(__ldg(th.xmin + i1 - 1) + __ldg(th.xsize + i1 - 1), rlo + metaRows);
     const int32_t c = threadIdx.x * VC;
     const bool hasCols = c < win;
-    const T* xp = x + p * hin * static_cast<int64_t>(win) + c;
     T* yp = y + p * hout * static_cast<int64_t>(wout);
 
-    int32_t wmin = 0, wsz = 0;
-    if (REGW) {
-        if (static_cast<int32_t>(threadIdx.x) < wout) {
-            wmin = __ldg(tw.xmin + threadIdx.x);
-            wsz = min(__ldg(tw.xsize + threadIdx.x), TW);
-            for (int32_t t = 0; t < wsz; ++t) {
-                wsm[t * wout + threadIdx.x] = __ldg(tw.w + static_cast<int64_t>(threadIdx.x) * tw.taps + t);
-            }
-        }
-        __syncthreads();
+    for (int32_t e = threadIdx.x; e < 2 * (rhi - rlo); e += blockDim.x) {
+        msm[e] = __ldg(reinterpret_cast<const float4*>(wrow) + static_cast<int64_t>(rlo) * 2 + e);
     }
+    for (int32_t j = threadIdx.x; j < wout && wTaps > 0; j += blockDim.x) {
+        const int32_t n = min(__ldg(tw.xsize + j), wTaps);
+        for (int32_t t = 0; t < n; ++t) {
+            wsm[t * wout + j] = __ldg(tw.w + static_cast<int64_t>(j) * tw.taps + t);
+        }
+    }
+    __syncthreads();
 
     float acc[kSlots][VC];
 #pragma unroll
@@ -138,27 +143,27 @@ __global__ void __launch_bounds__(MAXT)
     // Emits output row i from the oldest accumulator slot: vertical result -> shared row -> horizontal filter.
     auto flush = [&](int32_t i) {
         if (hasCols) {
-            *reinterpret_cast<float4*>(rowbuf + c) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+#pragma unroll
+            for (int k = 0; k < VC; k += 4) {
+                *reinterpret_cast<float4*>(rowbuf + c + k) =
+                    make_float4(acc[0][k], acc[0][k + 1], acc[0][k + 2], acc[0][k + 3]);
+            }
         }
         __syncthreads();
-        if (REGW) {
-            if (static_cast<int32_t>(threadIdx.x) < wout) {
-                float v = 0.0f;
-                for (int32_t t = 0; t < wsz; ++t) {
-                    v = fmaf(wsm[t * wout + threadIdx.x], rowbuf[wmin + t], v);
+        for (int32_t j = threadIdx.x; j < wout; j += blockDim.x) {
+            const int32_t m = __ldg(tw.xmin + j), n = __ldg(tw.xsize + j);
+            float v = 0.0f;
+            if (wTaps > 0) {
+                for (int32_t t = 0; t < n; ++t) {
+                    v = fmaf(wsm[t * wout + j], rowbuf[m + t], v);
                 }
-                yp[static_cast<int64_t>(i) * wout + threadIdx.x] = DType<T>::FromF(v);
-            }
-        } else {
-            for (int32_t j = threadIdx.x; j < wout; j += blockDim.x) {
-                const int32_t m = __ldg(tw.xmin + j), n = __ldg(tw.xsize + j);
+            } else {
                 const float* wj = tw.w + static_cast<int64_t>(j) * tw.taps;
-                float v = 0.0f;
                 for (int32_t t = 0; t < n; ++t) {
                     v = fmaf(__ldg(wj + t), rowbuf[m + t], v);
                 }
-                yp[static_cast<int64_t>(i) * wout + j] = DType<T>::FromF(v);
             }
+            yp[static_cast<int64_t>(i) * wout + j] = DType<T>::FromF(v);
         }
         __syncthreads();
     };
@@ -175,70 +180,61 @@ __global__ void __launch_bounds__(MAXT)
             acc[kSlots - 1][k] = 0.0f;
         }
     };
-    auto loadRow = [&](int32_t r, float (&v)[VC]) {
-        if (hasCols && r < rhi) {
-            LoadPackLdg<T, VC>(xp + static_cast<int64_t>(r) * win, v);
-        } else {
+    // Input rows are fetched PF rows ahead into fixed registers (the row loop is unrolled by PF; rotating a queue
+    // through moves would make every iteration wait for the newest load).
+    using Vec = Pack<T, LV>;
+    Vec q[PF][NL];
+    const T* xnext = x + (p * hin + rlo) * static_cast<int64_t>(win) + c; // next row to fetch
+    int32_t rnext = rlo;
+    auto fetch = [&](Vec (&dst)[NL]) {
+        if (hasCols && rnext < rhi) {
 #pragma unroll
-            for (int k = 0; k < VC; ++k) {
-                v[k] = 0.0f;
+            for (int l = 0; l < NL; ++l) {
+                dst[l] = *reinterpret_cast<const Vec*>(xnext + l * LV);
             }
         }
+        xnext += win;
+        ++rnext;
     };
-
-    // Row metadata (first covering output, run length, slot weights) is fetched one row ahead; input rows PF rows
-    // ahead. The row loop is unrolled by PF so that the queue slots are fixed registers (rotating them through
-    // moves would make every iteration wait for the newest load).
-    struct RowMeta {
-        int32_t s, cnt;
-        float4 w0;
-        float2 w1;
-    };
-    auto loadMeta = [&](int32_t r) {
-        RowMeta m;
-        const int32_t rr = min(r, rhi - 1);
-        m.s = __ldg(rh.start + rr);
-        m.cnt = __ldg(rh.end + rr) - m.s;
-        m.w0 = __ldg(reinterpret_cast<const float4*>(wrow) + static_cast<int64_t>(rr) * 2);
-        m.w1 = __ldg(reinterpret_cast<const float2*>(wrow) + static_cast<int64_t>(rr) * 4 + 2);
-        return m;
-    };
-    float q[PF][VC];
 #pragma unroll
     for (int f = 0; f < PF; ++f) {
-        loadRow(rlo + f, q[f]);
+        fetch(q[f]);
     }
-    int32_t curStart = __ldg(rh.start + rlo);
-    RowMeta meta = loadMeta(rlo);
+    int32_t curStart = __float_as_int(msm[1].z);
     for (int32_t r0 = rlo; r0 < rhi; r0 += PF) {
 #pragma unroll
         for (int f = 0; f < PF; ++f) {
             const int32_t r = r0 + f;
             if (r < rhi) {
-                const RowMeta m = meta;
-                meta = loadMeta(r + 1);
-                while (curStart < m.s) { // outputs before start(r) no longer receive rows: complete
+                const float4 m0 = msm[2 * (r - rlo)], m1 = msm[2 * (r - rlo) + 1];
+                const int32_t s = __float_as_int(m1.z), cnt = __float_as_int(m1.w);
+                while (curStart < s) { // outputs before start(r) no longer receive rows: complete
                     if (curStart >= i0 && curStart < i1) {
                         flush(curStart);
                     }
                     shift();
                     ++curStart;
                 }
-                const float w[kSlots] = {m.w0.x, m.w0.y, m.w0.z, m.w0.w, m.w1.x, m.w1.y};
+                const float w[kSlots] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y};
+                float xv[VC];
+#pragma unroll
+                for (int k = 0; k < VC; ++k) {
+                    xv[k] = DType<T>::ToF(q[f][k / LV].v[k % LV]);
+                }
 #pragma unroll
                 for (int a = 0; a < kSlots; ++a) {
-                    if (a < m.cnt) { // slots past the run are not touched (an Inf / NaN input must not leak in)
+                    if (a < cnt) { // slots past the run are not touched (an Inf / NaN input must not leak in)
 #pragma unroll
                         for (int k = 0; k < VC; ++k) {
-                            acc[a][k] = fmaf(w[a], q[f][k], acc[a][k]);
+                            acc[a][k] = fmaf(w[a], xv[k], acc[a][k]);
                         }
                     }
                 }
-                loadRow(r + PF, q[f]);
+                fetch(q[f]);
             }
         }
     }
-    const int32_t lastEnd = __ldg(rh.end + rhi - 1);
+    const int32_t lastEnd = __float_as_int(msm[2 * (rhi - 1 - rlo) + 1].z) + __float_as_int(msm[2 * (rhi - 1 - rlo) + 1].w);
     while (curStart < i1 && curStart < lastEnd) {
         if (curStart >= i0) {
             flush(curStart);
@@ -421,16 +417,14 @@ AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW)
 {
     AAFwdPlan plan{};
     // Streaming needs: every input row covered by at most kSlots outputs (true for scale >= 1), rows that one
-    // block can own (4 columns per thread) and 16-byte aligned rows.
+    // block can own (8 columns per thread) and 16-byte aligned rows.
     const int es = DtSize(dt);
-    plan.stream = scaleH >= 1.0f && sh.win % 4 == 0 && sh.win <= 4 * kStreamMaxThreads && sh.hin >= 1 && (sh.win * es) % 8 == 0;
+    plan.stream = scaleH >= 1.0f && sh.win % 8 == 0 && sh.win <= 8 * kStreamMaxThreads && (sh.win * es) % 16 == 0;
     if (!plan.stream) {
         return plan;
     }
-    plan.regWeights = sh.wout <= kStreamMaxThreads && tapsW <= 24; // 24 * wout floats of shared memory
-    int32_t threads = static_cast<int32_t>(CeilDiv(sh.win, 4));
-    threads = std::max(threads, plan.regWeights ? sh.wout : std::min(sh.wout, 256));
-    plan.threads = std::min(kStreamMaxThreads, (threads + 31) & ~31);
+    const int32_t threads = std::max(64, static_cast<int32_t>((CeilDiv(sh.win, 8) + 31) & ~31));
+    plan.threads = std::min(kStreamMaxThreads, threads);
     // Bands: pick the number of bands per plane whose block count fills whole waves of resident blocks best
     // (every band re-reads the input rows of its first window, so no more than 8, and at least 16 rows each).
     const int64_t planes = std::max<int64_t>(sh.n * sh.c, 1);
@@ -446,6 +440,16 @@ AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW)
         }
     }
     plan.bandRows = static_cast<int32_t>(CeilDiv(sh.hout, bestBands));
+    // input rows of a band: its windows span bandRows * scale + 2 * support (+ rounding) rows
+    plan.metaRows = static_cast<int32_t>(
+        std::min<double>(sh.hin, std::ceil(static_cast<double>(plan.bandRows) * scaleH + 4.0 * scaleH + 4.0)));
+    // horizontal weights in shared memory if they fit beside the row buffer and the slot records
+    const size_t wBytes = static_cast<size_t>(tapsW) * sh.wout * sizeof(float);
+    const size_t rest = (static_cast<size_t>(sh.win) + static_cast<size_t>(plan.metaRows) * 8 + 8) * sizeof(float);
+    plan.regWeights = wBytes + rest <= 96 * 1024;
+    if (rest > 96 * 1024) {
+        plan.stream = false;
+    }
     plan.wrowBytes = static_cast<uint64_t>(sh.hin) * kSlotStride * sizeof(float);
     return plan;
 }
@@ -458,28 +462,24 @@ cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AA
     if (stream) {
         AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.hin, 128)), 128, 0, s>>>(th, rh, sh.hin, wrow);
         const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(CeilDiv(sh.hout, plan.bandRows)));
-        const size_t smem = (static_cast<size_t>((sh.win + 3) & ~3) +
-                             (plan.regWeights ? static_cast<size_t>(24) * sh.wout : 0)) * sizeof(float);
+        const int32_t wTaps = plan.regWeights ? tw.taps : 0;
+        const size_t smem = (static_cast<size_t>((sh.win + 3) & ~3) + static_cast<size_t>(plan.metaRows) * 8 +
+                             static_cast<size_t>(wTaps) * sh.wout) * sizeof(float);
+        cudaError_t e = cudaSuccess;
         OPSCV_DISPATCH_DT(dt, T, {
             const T* px = static_cast<const T*>(x);
             T* py = static_cast<T*>(y);
-            // blocks of at most 256 threads may use up to 255 registers: no spills of the accumulator ring
-            if (plan.regWeights && plan.threads <= 256) {
-                AAFwdStreamKernel<T, true, 24, 256><<<grid, plan.threads, smem, s>>>(
-                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
-            } else if (plan.regWeights) {
-                AAFwdStreamKernel<T, true, 24, kStreamMaxThreads><<<grid, plan.threads, smem, s>>>(
-                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
-            } else if (plan.threads <= 256) {
-                AAFwdStreamKernel<T, false, 1, 256><<<grid, plan.threads, smem, s>>>(
-                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
-            } else {
-                AAFwdStreamKernel<T, false, 1, kStreamMaxThreads><<<grid, plan.threads, smem, s>>>(
-                    px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, rh, wrow, plan.bandRows);
+            auto kernel = AAFwdStreamKernel<T, 8, kStreamMaxThreads>;
+            if (smem > 48 * 1024) {
+                e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            }
+            if (e == cudaSuccess) {
+                kernel<<<grid, plan.threads, smem, s>>>(px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, wrow,
+                                                        plan.bandRows, plan.metaRows, wTaps);
             }
         });
         CountLaunch(2);
-        return cudaGetLastError();
+        return e != cudaSuccess ? e : cudaGetLastError();
     }
     const int64_t total = planes * sh.hout * static_cast<int64_t>(sh.wout);
     OPSCV_DISPATCH_DT(dt, T, {
