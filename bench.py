@@ -464,10 +464,9 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
     total_ms = t_start.elapsed_time(t_end)
     per_op_ms = [statistics.mean(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(args.steps))
                  for j in range(len(oplist))]
-    if dist is not None:
-        t = torch.tensor([total_ms] + per_op_ms, device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, per_op_ms = t[0].item(), t[1:].tolist()
+    from opscv_b200 import sharding  # the box time of a step is that of its slowest rank
+    reduced = sharding.max_over_ranks([total_ms] + per_op_ms, dist, dev)
+    total_ms, per_op_ms = reduced[0], reduced[1:]
     step_ms = total_ms / args.steps
     step_bytes = sum(op.algo_bytes for op in oplist)
     step_pix = sum(op.pixels for op in oplist)
@@ -511,10 +510,7 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
         b.record(stream)
         barrier()
         ms = a.elapsed_time(b)
-        if dist is not None:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = t[0].item()
+        ms = sharding.max_over_ranks([ms], dist, dev)[0]
         e2e = {"value": world * step_bytes * e2e_steps / (ms * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms / e2e_steps,
                "steps": e2e_steps}

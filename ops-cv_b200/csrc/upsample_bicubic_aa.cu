@@ -96,8 +96,8 @@ __global__ void AARowWeightKernel(AAAxis th, RangeAxis rh, int32_t hin, float* _
     wrow[static_cast<int64_t>(r) * kSlotStride + 7] = __int_as_float(min(e - s, kSlots));
 }
 
-// grid = (planes, bands); a band is `bandRows` output rows. Thread t owns input columns VC*t .. VC*t+VC-1 of every
-// row (VC * sizeof(T) = 16 or 32 bytes) and keeps one partial sum per open output row (kSlots of them) for each.
+// grid = (planes, bands); a band is `bandRows` output rows. A thread owns VC input columns of every row (one or two
+// 16-byte groups) and keeps one partial sum per open output row (kSlots of them) for each.
 // Shared memory: the vertically filtered row being flushed, the slot-weight rows of the band's input rows, and
 // (wTaps > 0) the horizontal weights of all output columns, transposed.
 template <typename T, int VC, int MAXT>
@@ -110,15 +110,18 @@ __global__ void __launch_bounds__(MAXT)
     constexpr int LV = 16 / sizeof(T);     // elements per 16-byte load
     constexpr int NL = VC / LV;            // 16-byte loads per row
     extern __shared__ __align__(16) float smemF[];
-    float* rowbuf = smemF;                                            // [win]
-    float4* msm = reinterpret_cast<float4*>(smemF + ((win + 3) & ~3)); // [metaRows][2]
+    const int32_t winPad = (win + 3) & ~3;
+    float* rowbufs = smemF;                                           // [2][winPad], alternating between flushes
+    float4* msm = reinterpret_cast<float4*>(smemF + 2 * winPad);      // [metaRows][2]
     float* wsm = reinterpret_cast<float*>(msm + 2 * metaRows);        // [wTaps][wout]
     const int64_t p = blockIdx.x;
     const int32_t i0 = blockIdx.y * bandRows, i1 = min(hout, i0 + bandRows);
     const int32_t rlo = __ldg(th.xmin + i0);
     const int32_t rhi = min(__ldg(th.xmin + i1 - 1) + __ldg(th.xsize + i1 - 1), rlo + metaRows);
-    const int32_t c = threadIdx.x * VC;
-    const bool hasCols = c < win;
+    // Column ownership: 16-byte load l of a thread covers columns l * (blockDim.x * LV) + threadIdx.x * LV ..,
+    // so every load instruction of a warp reads one contiguous 512-byte run.
+    const int32_t groupSpan = blockDim.x * LV;
+    const int32_t c = threadIdx.x * LV;
     T* yp = y + p * hout * static_cast<int64_t>(wout);
 
     for (int32_t e = threadIdx.x; e < 2 * (rhi - rlo); e += blockDim.x) {
@@ -141,11 +144,18 @@ __global__ void __launch_bounds__(MAXT)
         }
     }
     // Emits output row i from the oldest accumulator slot: vertical result -> shared row -> horizontal filter.
+    // The shared row alternates between two buffers, so one barrier per flush is enough: a thread can only write
+    // buffer b again after passing the barrier of the flush in between, which every thread reaches after it has
+    // finished reading b.
+    int32_t flip = 0;
     auto flush = [&](int32_t i) {
-        if (hasCols) {
+        float* rowbuf = rowbufs + flip * winPad;
+        flip ^= 1;
 #pragma unroll
-            for (int k = 0; k < VC; k += 4) {
-                *reinterpret_cast<float4*>(rowbuf + c + k) =
+        for (int k = 0; k < VC; k += 4) {
+            const int32_t col = (k / LV) * groupSpan + c + k % LV;
+            if (col < win) {
+                *reinterpret_cast<float4*>(rowbuf + col) =
                     make_float4(acc[0][k], acc[0][k + 1], acc[0][k + 2], acc[0][k + 3]);
             }
         }
@@ -165,7 +175,6 @@ __global__ void __launch_bounds__(MAXT)
             }
             yp[static_cast<int64_t>(i) * wout + j] = DType<T>::FromF(v);
         }
-        __syncthreads();
     };
     auto shift = [&]() {
 #pragma unroll
@@ -187,10 +196,12 @@ __global__ void __launch_bounds__(MAXT)
     const T* xnext = x + (p * hin + rlo) * static_cast<int64_t>(win) + c; // next row to fetch
     int32_t rnext = rlo;
     auto fetch = [&](Vec (&dst)[NL]) {
-        if (hasCols && rnext < rhi) {
+        if (rnext < rhi) {
 #pragma unroll
             for (int l = 0; l < NL; ++l) {
-                dst[l] = *reinterpret_cast<const Vec*>(xnext + l * LV);
+                if (l * groupSpan + c < win) {
+                    dst[l] = *reinterpret_cast<const Vec*>(xnext + l * groupSpan);
+                }
             }
         }
         xnext += win;
@@ -445,7 +456,7 @@ AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW)
         std::min<double>(sh.hin, std::ceil(static_cast<double>(plan.bandRows) * scaleH + 4.0 * scaleH + 4.0)));
     // horizontal weights in shared memory if they fit beside the row buffer and the slot records
     const size_t wBytes = static_cast<size_t>(tapsW) * sh.wout * sizeof(float);
-    const size_t rest = (static_cast<size_t>(sh.win) + static_cast<size_t>(plan.metaRows) * 8 + 8) * sizeof(float);
+    const size_t rest = (2 * static_cast<size_t>(sh.win) + static_cast<size_t>(plan.metaRows) * 8 + 8) * sizeof(float);
     plan.regWeights = wBytes + rest <= 96 * 1024;
     if (rest > 96 * 1024) {
         plan.stream = false;
@@ -463,7 +474,7 @@ cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AA
         AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.hin, 128)), 128, 0, s>>>(th, rh, sh.hin, wrow);
         const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(CeilDiv(sh.hout, plan.bandRows)));
         const int32_t wTaps = plan.regWeights ? tw.taps : 0;
-        const size_t smem = (static_cast<size_t>((sh.win + 3) & ~3) + static_cast<size_t>(plan.metaRows) * 8 +
+        const size_t smem = (2 * static_cast<size_t>((sh.win + 3) & ~3) + static_cast<size_t>(plan.metaRows) * 8 +
                              static_cast<size_t>(wTaps) * sh.wout) * sizeof(float);
         cudaError_t e = cudaSuccess;
         OPSCV_DISPATCH_DT(dt, T, {
