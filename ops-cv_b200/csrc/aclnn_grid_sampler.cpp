@@ -112,8 +112,12 @@ aclnnStatus aclnnGridSampler2DGetWorkspaceSize(const aclTensor* input, const acl
     const BufRef y = StageOutput(out, ws);
     const GridShape g = MakeGridShape(input, grid, interpolationMode, paddingMode, alignCorners);
     const Dt dt = ToDt(input->dtype);
-    ex->steps.push_back(
-        [=](char* w, cudaStream_t s) { return GridSampler2DFwd(dt, x.At(w), gr.At(w), y.At(w), g, s); });
+    const GridFwdPlan plan = PlanGridSampler2DFwd(dt, g);
+    const uint64_t scratch = plan.recBytes > 0 ? ws.Alloc(plan.recBytes) : 0;
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        return GridSampler2DFwd(dt, x.At(w), gr.At(w), y.At(w), g, plan,
+                                plan.recBytes > 0 ? static_cast<void*>(w + scratch) : nullptr, s);
+    });
     FinishOutput(out, y, ex);
     ex->workspaceSize = ws.Size();
     *workspaceSize = ws.Size();

@@ -14,6 +14,8 @@
 #include "grid_coords.cuh"
 #include "launch_util.cuh"
 
+#include <algorithm>
+
 namespace opscv {
 namespace {
 
@@ -155,11 +157,197 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// ---- staged kernel (bilinear, every padding mode) -------------------------------------------------------------
+// Source coordinates are the same for all channels of a sample, so a prologue kernel evaluates them once per
+// sample into a float2 record (ix, iy), already padded / reflected / range-limited; a NaN ix marks a sample whose
+// coordinates were NaN or infinite (its outputs are NaN).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    GridCoordsKernel(const T* __restrict__ grid, float2* __restrict__ rec, GridShape g, int64_t total)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
+        float ix = gs::ComputeSourceIndex(DType<T>::Load(grid + 2 * s), g.win, g.pad, g.align);
+        float iy = gs::ComputeSourceIndex(DType<T>::Load(grid + 2 * s + 1), g.hin, g.pad, g.align);
+        const bool bad = gs::IsNanOrInf(ix) || gs::IsNanOrInf(iy);
+        ix = gs::SafeDowngradeToIntRange(ix);
+        iy = gs::SafeDowngradeToIntRange(iy);
+        rec[s] = bad ? make_float2(__int_as_float(0x7fc00000), 0.0f) : make_float2(ix, iy);
+    }
+}
+
+// blockIdx.x = (image * groups + channel group) * split + part. A group is NV 16-byte vectors of channels
+// (CG = NV * 16 / sizeof(T)). The block copies the group's input planes into shared memory as
+// tile[((y + 2) * (win + 4) + x + 2) * NV + v], surrounded by a two-pixel border of zeros, then handles the output
+// pixels [part * per, ...) of the image, one pixel per thread and trip. With the border, a tap outside the image
+// reads a zero instead of being skipped: adding 0 * weight leaves the fp32 sum unchanged bit for bit (the
+// weights are finite), so the kernel needs no bounds tests; tap positions are clamped into the border.
+constexpr int kStageThreads = 512;
+constexpr int kBorder = 2;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(kStageThreads)
+    GridSamplerStagedKernel(const T* __restrict__ x, const float2* __restrict__ rec, T* __restrict__ y, GridShape g,
+                            int32_t groups, int32_t split, int32_t per)
+{
+    extern __shared__ __align__(16) unsigned char stagedSmem[];
+    constexpr int LV = 16 / sizeof(T);
+    constexpr int CG = NV * LV;
+    using Vec = Pack<T, LV>;
+    Vec* tile = reinterpret_cast<Vec*>(stagedSmem);
+    const int32_t inPlane = g.hin * g.win, outPlane = g.hout * g.wout;
+    const int32_t tw = g.win + 2 * kBorder, th = g.hin + 2 * kBorder;
+    const int32_t part = blockIdx.x % split;
+    const int64_t ng = blockIdx.x / split;
+    const int64_t n = ng / groups;
+    const int32_t c0 = static_cast<int32_t>(ng - n * groups) * CG;
+    const int32_t nch = min(CG, static_cast<int32_t>(g.c) - c0);
+    const T* xb = x + (n * g.c + c0) * inPlane;
+    const int32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int32_t ty = warp; ty < th; ty += warps) {
+        const int32_t sy = ty - kBorder;
+        const bool rowIn = sy >= 0 && sy < g.hin;
+        for (int32_t tx = lane; tx < tw; tx += 32) {
+            const int32_t sx = tx - kBorder;
+            const bool in = rowIn && sx >= 0 && sx < g.win;
+            const T* src = xb + sy * g.win + sx;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                Vec q;
+#pragma unroll
+                for (int k = 0; k < LV; ++k) {
+                    const int ch = v * LV + k;
+                    q.v[k] = (in && ch < nch) ? __ldg(src + static_cast<int64_t>(ch) * inPlane) : DType<T>::FromF(0.0f);
+                }
+                tile[(ty * tw + tx) * NV + v] = q;
+            }
+        }
+    }
+    __syncthreads();
+    const int32_t p1 = min(outPlane, (part + 1) * per);
+    const float2* rb = rec + n * outPlane;
+    T* yb = y + (n * g.c + c0) * outPlane;
+    for (int32_t p = part * per + threadIdx.x; p < p1; p += blockDim.x) {
+        const float2 r = __ldg(rb + p);
+        float out[CG];
+        if (r.x != r.x) {
+#pragma unroll
+            for (int k = 0; k < CG; ++k) {
+                out[k] = __int_as_float(0x7fc00000);
+            }
+        } else {
+            const float ixF = floorf(r.x), iyF = floorf(r.y);
+            const float xe = Sub(Add(ixF, 1.0f), r.x), ye = Sub(Add(iyF, 1.0f), r.y);
+            const float xw = Sub(r.x, ixF), yw = Sub(r.y, iyF);
+            const float wt[4] = {Mul(xe, ye), Mul(xw, ye), Mul(xe, yw), Mul(xw, yw)};
+            const int32_t cx = min(max(static_cast<int32_t>(ixF), -kBorder), g.win);
+            const int32_t cy = min(max(static_cast<int32_t>(iyF), -kBorder), g.hin);
+            const Vec* t0 = tile + ((cy + kBorder) * tw + cx + kBorder) * NV;
+#pragma unroll
+            for (int k = 0; k < CG; ++k) {
+                out[k] = 0.0f;
+            }
+#pragma unroll
+            for (int tap = 0; tap < 4; ++tap) {
+                const Vec* tp = t0 + ((tap >> 1) * tw + (tap & 1)) * NV;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    const Vec q = tp[v];
+#pragma unroll
+                    for (int k = 0; k < LV; ++k) {
+                        out[v * LV + k] = Add(out[v * LV + k], Mul(DType<T>::ToF(q.v[k]), wt[tap]));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < CG; ++k) {
+            if (k < nch) {
+                yb[static_cast<int64_t>(k) * outPlane + p] = DType<T>::FromF(out[k]);
+            }
+        }
+    }
+}
+
+inline size_t StagedFwdSmem(int64_t hin, int64_t win, int nv)
+{
+    return static_cast<size_t>((hin + 2 * kBorder) * (win + 2 * kBorder)) * nv * 16;
+}
+
+template <typename T, int NV>
+cudaError_t LaunchStaged(const T* x, const T* grid, T* y, float2* rec, GridShape g, cudaStream_t s)
+{
+    constexpr int CG = NV * 16 / static_cast<int>(sizeof(T));
+    const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int64_t samples = g.n * outPlane;
+    GridCoordsKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(grid, rec, g, samples);
+    const int32_t groups = static_cast<int32_t>(CeilDiv(g.c, CG));
+    const size_t smem = StagedFwdSmem(g.hin, g.win, NV);
+    const int64_t slots = static_cast<int64_t>(NumSMs()) * std::max<int64_t>(1, (220 * 1024) / (smem + 1024));
+    // Split the pixels of an image over several blocks only while that is needed for ~4 waves of blocks (every
+    // part stages the planes again, from L2).
+    int32_t split = 1;
+    while (split < 8 && g.n * groups * split < 4 * slots && outPlane / (split * 2) >= 2048) {
+        split *= 2;
+    }
+    const int32_t per = static_cast<int32_t>(CeilDiv(outPlane, split));
+    auto kernel = GridSamplerStagedKernel<T, NV>;
+    cudaError_t e = cudaSuccess;
+    if (smem > 48 * 1024) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) {
+            return e;
+        }
+    }
+    kernel<<<static_cast<unsigned>(g.n * groups * split), kStageThreads, smem, s>>>(x, rec, y, g, groups, split, per);
+    CountLaunch(2);
+    return cudaGetLastError();
+}
+
 } // namespace
 
-cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, GridShape g, cudaStream_t s)
+GridFwdPlan PlanGridSampler2DFwd(Dt dt, GridShape g)
+{
+    GridFwdPlan plan{};
+    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win, outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int lanes = 16 / DtSize(dt);
+    // Staging pays for bilinear sampling when an image has at least as many output pixels as a plane has inputs;
+    // it needs planes that fit shared memory and 32-bit in-image offsets and block indices.
+    if (g.interp != 0 || outPlane * 2 < inPlane || outPlane >= (1LL << 30) || g.c < lanes / 2 ||
+        g.n * CeilDiv(g.c, lanes) * 8 >= (1LL << 31)) {
+        return plan;
+    }
+    // At least two blocks per SM must fit, so that one block's staging overlaps another's sampling; larger planes
+    // take the direct kernel. (Two channel vectors per pixel measured slower than one: the kernel is bound by
+    // shared-memory wavefronts, not by the per-pixel coordinate work.)
+    if (StagedFwdSmem(g.hin, g.win, 1) + 1024 <= 110 * 1024) {
+        plan.vectors = 1;
+    }
+    if (plan.vectors > 0) {
+        plan.recBytes = static_cast<uint64_t>(g.n) * outPlane * sizeof(float2);
+    }
+    return plan;
+}
+
+cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, GridShape g, const GridFwdPlan& plan,
+                             void* workspace, cudaStream_t s)
 {
     const int64_t pixels = g.n * g.hout * static_cast<int64_t>(g.wout);
+    if (plan.vectors > 0) {
+        cudaError_t e = cudaSuccess;
+        float2* rec = static_cast<float2*>(workspace);
+        OPSCV_DISPATCH_DT(dt, T, {
+            const T* px = static_cast<const T*>(x);
+            const T* pg = static_cast<const T*>(grid);
+            T* py = static_cast<T*>(y);
+            if (plan.vectors == 2) {
+                e = LaunchStaged<T, 2>(px, pg, py, rec, g, s);
+            } else {
+                e = LaunchStaged<T, 1>(px, pg, py, rec, g, s);
+            }
+        });
+        return e;
+    }
     // Split channels across threads only as far as needed to fill the machine.
     const int64_t wanted = static_cast<int64_t>(NumSMs()) * 2048 * 2;
     int64_t chunks = CeilDiv(wanted, pixels > 0 ? pixels : 1);

@@ -358,6 +358,183 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// ---- staged kernel (bilinear, atomic mode) ---------------------------------------------------------------------
+// One block per (image, group of CG channels). Shared memory holds the group's grad_input planes as fp32
+// accumulators, acc[k * inPlane + y * win + x] (planar: the lanes of a warp scatter to random pixels of ONE channel
+// per instruction, and a planar plane spreads them over all 32 banks), and (for grad_grid) the group's input planes
+// interleaved by channel, tile[y * win + x] = {CG channels}.
+// Threads walk the output pixels of the image: grad_output is read coalesced, the scatter goes to shared-memory
+// atomics, the input taps come from shared memory. At the end the accumulators are written to grad_input once, in
+// the storage dtype: no zero-fill of grad_input, no global atomics on it, no fp32 staging buffer for 16-bit tensors.
+// grad_grid needs the sum over ALL channels: every block adds its group's partial (gix, giy) to an fp32 buffer with
+// one 8-byte global atomic per pixel; GridGradFinishKernel scales by the coordinate multipliers and stores.
+template <typename T, int CG, bool WANT_IN, bool WANT_GRID>
+__global__ void __launch_bounds__(1024)
+    GridGradStagedKernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ grid,
+                         T* __restrict__ gi, float2* __restrict__ ggAcc, GridShape g, int32_t groups)
+{
+    extern __shared__ __align__(16) unsigned char stagedSmem[];
+    using Vec = Pack<T, CG>;
+    const int32_t inPlane = g.hin * g.win, outPlane = g.hout * g.wout;
+    float* acc = reinterpret_cast<float*>(stagedSmem);
+    Vec* tile = reinterpret_cast<Vec*>(stagedSmem + (WANT_IN ? static_cast<size_t>(inPlane) * CG * sizeof(float) : 0));
+    const int64_t n = blockIdx.x / groups;
+    const int32_t c0 = static_cast<int32_t>(blockIdx.x - n * groups) * CG;
+    const int32_t nch = min(CG, static_cast<int32_t>(g.c) - c0);
+    if (WANT_IN) {
+        for (int32_t i = threadIdx.x; i < inPlane * CG; i += blockDim.x) {
+            acc[i] = 0.0f;
+        }
+    }
+    if (WANT_GRID) {
+        const T* xb = x + (n * g.c + c0) * inPlane;
+        for (int32_t i = threadIdx.x; i < inPlane; i += blockDim.x) {
+            Vec v;
+#pragma unroll
+            for (int k = 0; k < CG; ++k) {
+                v.v[k] = k < nch ? __ldg(xb + static_cast<int64_t>(k) * inPlane + i) : DType<T>::FromF(0.0f);
+            }
+            tile[i] = v;
+        }
+    }
+    __syncthreads();
+    const T* gb = grid + 2 * n * outPlane;
+    const T* gob = go + (n * g.c + c0) * outPlane;
+    for (int32_t p = threadIdx.x; p < outPlane; p += blockDim.x) {
+        const GradTaps t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
+        float gv[CG];
+#pragma unroll
+        for (int k = 0; k < CG; ++k) {
+            gv[k] = k < nch ? DType<T>::Load(gob + static_cast<int64_t>(k) * outPlane + p) : 0.0f;
+        }
+        const int32_t o = t.y0 * g.win + t.x0;
+        const float ye = Sub(static_cast<float>(t.y0 + 1), t.iy), xe = Sub(static_cast<float>(t.x0 + 1), t.ix);
+        const float yw = Sub(t.iy, static_cast<float>(t.y0)), xw = Sub(t.ix, static_cast<float>(t.x0));
+        float gix = 0.0f, giy = 0.0f;
+        // sx / sy: sign of the tap's term in d/dx and d/dy; fx / fy: the factor (ye or yw, xe or xw).
+        auto tap = [&](bool in, int32_t off, float w, float fx, float fy, bool negX, bool negY) {
+            if (!in) {
+                return;
+            }
+            const int32_t d = o + off;
+            Vec v{};
+            if (WANT_GRID) {
+                v = tile[d];
+            }
+#pragma unroll
+            for (int k = 0; k < CG; ++k) {
+                if (k < nch) {
+                    if (WANT_IN) {
+                        atomicAdd(acc + k * inPlane + d, Mul(w, gv[k]));
+                    }
+                    if (WANT_GRID) {
+                        const float xv = DType<T>::ToF(v.v[k]);
+                        const float tx = Mul(Mul(xv, fx), gv[k]), ty = Mul(Mul(xv, fy), gv[k]);
+                        gix = negX ? Sub(gix, tx) : Add(gix, tx);
+                        giy = negY ? Sub(giy, ty) : Add(giy, ty);
+                    }
+                }
+            }
+        };
+        tap(gs::Within(t.y0, t.x0, g.hin, g.win), 0, t.tnw, ye, xe, true, true);
+        tap(gs::Within(t.y0, t.x0 + 1, g.hin, g.win), 1, t.tne, ye, xw, false, true);
+        tap(gs::Within(t.y0 + 1, t.x0, g.hin, g.win), g.win, t.tsw, yw, xe, true, false);
+        tap(gs::Within(t.y0 + 1, t.x0 + 1, g.hin, g.win), g.win + 1, t.tse, yw, xw, false, false);
+        if (WANT_GRID) {
+            atomicAdd(ggAcc + n * outPlane + p, make_float2(gix, giy));
+        }
+    }
+    if (WANT_IN) {
+        __syncthreads();
+        T* gib = gi + (n * g.c + c0) * inPlane;
+        for (int32_t i = threadIdx.x; i < inPlane; i += blockDim.x) {
+#pragma unroll
+            for (int k = 0; k < CG; ++k) {
+                if (k < nch) {
+                    gib[static_cast<int64_t>(k) * inPlane + i] = DType<T>::FromF(acc[k * inPlane + i]);
+                }
+            }
+        }
+    }
+}
+
+// grad_grid = multiplier * (sum over channels), from the fp32 sums of the staged kernel.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    GridGradFinishKernel(const T* __restrict__ grid, const float2* __restrict__ ggAcc, T* __restrict__ ggrid,
+                         GridShape g, int64_t total)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
+        float mx, my;
+        gs::SourceIndexSetGrad(DType<T>::Load(grid + 2 * s), g.win, g.pad, g.align, &mx);
+        gs::SourceIndexSetGrad(DType<T>::Load(grid + 2 * s + 1), g.hin, g.pad, g.align, &my);
+        const float2 a = ggAcc[s];
+        ggrid[2 * s] = DType<T>::FromF(Mul(mx, a.x));
+        ggrid[2 * s + 1] = DType<T>::FromF(Mul(my, a.y));
+    }
+}
+
+// Bytes of shared memory per block of the staged kernel for a group of cg channels.
+inline size_t StagedBwdSmem(int es, int64_t inPlane, int cg, bool wantInput, bool wantGrid)
+{
+    return static_cast<size_t>(inPlane) * cg * ((wantInput ? 4 : 0) + (wantGrid ? es : 0));
+}
+
+// Group width for the staged kernel: the widest that fits the shared memory of an SM (0: none does).
+inline int32_t StagedBwdGroup(int es, int64_t inPlane, int64_t c, bool wantInput, bool wantGrid)
+{
+    for (int cg = 16 / es; cg * es >= 4; cg /= 2) {
+        if (StagedBwdSmem(es, inPlane, cg, wantInput, wantGrid) <= 220 * 1024 && (cg == 1 || cg / 2 < c)) {
+            return cg;
+        }
+    }
+    return 0;
+}
+
+template <typename T, int CG>
+cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* ggrid, float2* ggAcc, GridShape g,
+                            const GridGradPlan& plan, cudaStream_t s)
+{
+    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win, outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int32_t groups = static_cast<int32_t>(CeilDiv(g.c, CG));
+    const size_t smem = StagedBwdSmem(sizeof(T), inPlane, CG, plan.wantInput, plan.wantGrid);
+    const int threads = smem <= 110 * 1024 ? 512 : 1024;
+    cudaError_t e = cudaSuccess;
+    if (plan.wantGrid) {
+        e = cudaMemsetAsync(ggAcc, 0, static_cast<size_t>(g.n * outPlane) * sizeof(float2), s);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        CountLaunch();
+    }
+    auto launch = [&](auto kernel) {
+        if (smem > 48 * 1024) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (e != cudaSuccess) {
+                return;
+            }
+        }
+        kernel<<<static_cast<unsigned>(g.n * groups), threads, smem, s>>>(go, x, grid, gi, ggAcc, g, groups);
+        CountLaunch();
+        e = cudaGetLastError();
+    };
+    if (plan.wantInput && plan.wantGrid) {
+        launch(GridGradStagedKernel<T, CG, true, true>);
+    } else if (plan.wantInput) {
+        launch(GridGradStagedKernel<T, CG, true, false>);
+    } else {
+        launch(GridGradStagedKernel<T, CG, false, true>);
+    }
+    if (e == cudaSuccess && plan.wantGrid) {
+        const int64_t samples = g.n * outPlane;
+        GridGradFinishKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(grid, ggAcc, ggrid, g, samples);
+        CountLaunch();
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
 } // namespace
 
 GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool wantInput, bool wantGrid)
@@ -368,6 +545,18 @@ GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool w
     p.wantGrid = wantGrid;
     const uint64_t inPlane = static_cast<uint64_t>(g.hin) * g.win;
     const uint64_t outPlane = static_cast<uint64_t>(g.hout) * g.wout;
+    // Staged kernel: bilinear, atomic mode, planes that fit shared memory, enough (image, group) blocks to occupy
+    // the machine, and an image with at least as many output pixels as a plane has inputs.
+    if (!deterministic && g.interp == 0 && (wantInput || wantGrid) && outPlane < (1ULL << 30)) {
+        const int32_t cg = StagedBwdGroup(DtSize(dt), static_cast<int64_t>(inPlane), g.c, wantInput, wantGrid);
+        if (cg > 0 && g.n * CeilDiv(g.c, cg) >= NumSMs() / 2 && outPlane * 2 >= inPlane &&
+            g.n * CeilDiv(g.c, cg) < (1LL << 31)) {
+            p.stagedGroup = cg;
+            p.gridAccBytes = wantGrid ? Align256(static_cast<uint64_t>(g.n) * outPlane * 8) : 0;
+            p.total = p.gridAccBytes;
+            return p;
+        }
+    }
     if (wantInput) {
         if (deterministic) {
             // counts/offsets [N][inPlane+1] and cursors [N][inPlane], then entries [N][4*outPlane]
@@ -391,6 +580,26 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
     const int64_t giElems = g.n * g.c * inPlane;
     cudaError_t e = cudaSuccess;
     char* ws = static_cast<char*>(workspace);
+
+    if (plan.stagedGroup > 0) {
+        OPSCV_DISPATCH_DT(dt, T, {
+            const T* pgo = static_cast<const T*>(go);
+            const T* px = static_cast<const T*>(x);
+            const T* pg = static_cast<const T*>(grid);
+            T* pgi = static_cast<T*>(gi);
+            T* pgg = static_cast<T*>(ggrid);
+            float2* ggAcc = reinterpret_cast<float2*>(ws);
+            constexpr int kMax = 16 / sizeof(T);
+            if (plan.stagedGroup == kMax) {
+                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, ggAcc, g, plan, s);
+            } else if (plan.stagedGroup == kMax / 2) {
+                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, ggAcc, g, plan, s);
+            } else {
+                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, ggAcc, g, plan, s);
+            }
+        });
+        return e;
+    }
 
     if (!plan.deterministic || !plan.wantInput) {
         float* acc = nullptr;

@@ -132,12 +132,22 @@ struct GridShape {
     int32_t hin, win, hout, wout;
     int32_t interp, pad, align;
 };
-cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, GridShape g, cudaStream_t s);
+// Forward plan: vectors > 0 selects the shared-memory staged kernel with that many 16-byte channel vectors per
+// pixel; it needs recBytes of workspace for the per-sample source coordinates.
+struct GridFwdPlan {
+    int32_t vectors;
+    uint64_t recBytes;
+};
+GridFwdPlan PlanGridSampler2DFwd(Dt dt, GridShape g);
+cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, GridShape g, const GridFwdPlan& plan,
+                             void* workspace, cudaStream_t s);
 
 // Workspace needs of the grid-sampler backward (bytes, 256-byte aligned pieces); see grid_sampler_grad.cu.
 struct GridGradPlan {
     bool deterministic;
     bool wantInput, wantGrid;
+    int32_t stagedGroup; // > 0: shared-memory staged kernel with this many channels per block
+    uint64_t gridAccBytes; // staged kernel: fp32 (gix, giy) sums per sample
     uint64_t accBytes;   // fp32 grad_input accumulator (16-bit dtypes, atomic mode)
     uint64_t countBytes; // deterministic: per-destination tap counts / offsets
     uint64_t entryBytes; // deterministic: sorted (sample, weight) entries

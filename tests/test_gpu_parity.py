@@ -320,6 +320,50 @@ def test_grid_sampler_backward(ops, oracle, dev, dtype, interp, pad, align, det)
     check(gg, rg, dtype, exact=True)  # per-sample channel sum in channel order, as the oracle
 
 
+
+def check_sum(got, ref32, dtype):
+    """For values that are long sums evaluated in a different order than the oracle's (atomics, partial sums):
+    relative tolerance of the dtype plus an absolute term scaled by the largest magnitude, because a sum that
+    cancels to nearly zero carries the rounding of its large terms."""
+    got = got.detach().cpu().float().numpy()
+    ref = np.ascontiguousarray(ref32)
+    assert got.shape == ref.shape
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    scale = float(np.nanmax(np.abs(ref))) if ref.size else 0.0
+    rel = {torch.float32: 1e-5, torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}[dtype]
+    abs_ = (1e-6 if dtype == torch.float32 else rel * 1e-2) * max(scale, 1.0)
+    np.testing.assert_allclose(np.nan_to_num(got), np.nan_to_num(ref), rtol=rel, atol=abs_)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pad", [0, 1, 2])
+@pytest.mark.parametrize("align", [False, True])
+@pytest.mark.parametrize("c", [80, 161])
+def test_grid_sampler_staged_kernels(ops, oracle, dev, dtype, pad, align, c):
+    """Enough (image, channel group) blocks for the shared-memory staged kernels of the bilinear forward and the
+    atomic-mode backward; c = 161 leaves a partial last group."""
+    n, hi, wi, ho, wo = 8, 9, 11, 14, 13
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(40)), dtype)
+    grid, grid32 = quant(make_grid(n, ho, wo, 41, 1.2), dtype)
+    g, g32 = quant(torch.randn((n, c, ho, wo), generator=gen(42)), dtype)
+    y = ops.grid_sampler2d(x.to(dev), grid.to(dev), 0, pad, align)
+    check(y, oracle.grid_sampler2d_fwd(x32, grid32, 0, pad, align), dtype, exact=(dtype == torch.float32))
+    ri, rg = oracle.grid_sampler2d_bwd(g32, x32, grid32, 0, pad, align)
+    gi, gg = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), 0, pad, align)
+    check_sum(gi, ri, dtype)
+    check_sum(gg, rg, dtype)
+    sentinel = torch.full_like(x, 7.0).to(dev)
+    gi3, gg3 = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), 0, pad, align, mask=(False, True),
+                                           input_grad=sentinel)
+    assert torch.equal(gi3.cpu(), torch.full_like(x, 7.0))
+    check_sum(gg3, rg, dtype)
+    sentinel_g = torch.full_like(grid, 7.0).to(dev)
+    gi4, gg4 = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), 0, pad, align, mask=(True, False),
+                                           grid_grad=sentinel_g)
+    assert torch.equal(gg4.cpu(), torch.full_like(grid, 7.0))
+    check_sum(gi4, ri, dtype)
+
+
 def test_grid_sampler_backward_masks_and_collisions(ops, oracle, dev):
     # every sample hits the same source pixel: worst case for atomics and for the deterministic segment lists
     n, c, hi, wi, ho, wo = 1, 3, 4, 4, 40, 37
