@@ -159,6 +159,20 @@ ACLNN_API aclnnStatus aclnnGridSampler2DBackward(void* workspace, uint64_t works
 ACLNN_API aclnnStatus opscvDebugAxisTable(int32_t kind, int64_t inSize, int64_t outSize, int32_t alignCorners,
                                           float userScale, int32_t* i0, int32_t* i1, float* f0, int32_t* tapsOut);
 
+/* ---- allocation-free bilinear forward ------------------------------------------------------------------------
+ * No counterpart in the reference (its entry points all take a workspace). For callers that can neither allocate
+ * device memory nor pass a workspace at the point of the call: the per-axis tap tables live in a fixed 192 KiB
+ * array inside the library's device image. Same arithmetic and kernels as aclnnUpsampleBilinear2d on contiguous
+ * NCHW / NHWC data (dtype ACL_FLOAT, ACL_FLOAT16 or ACL_BF16); the work is enqueued on `stream`.
+ * Limits and rules: outH and outW at most 8192 each (larger: ACLNN_ERR_PARAM_INVALID); the first call on a device
+ * looks up the array's address and should be made before any stream capture on that device; all calls on a device
+ * share the array, so calls that may overlap (different streams or unordered threads) must be serialised by the
+ * caller. */
+ACLNN_API aclnnStatus opscvUpsampleBilinear2dNoAlloc(const void* self, void* out, aclDataType dtype, aclFormat format,
+                                                     int64_t n, int64_t c, int64_t inH, int64_t inW, int64_t outH,
+                                                     int64_t outW, bool alignCorners, double scalesH, double scalesW,
+                                                     aclrtStream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,6 +51,7 @@ SYMBOLS = {
     "opscvGetLaunchCount": (_U64, []),
     "opscvResetLaunchCount": (None, []),
     "opscvDebugAxisTable": (_I32, [_I32, _I64, _I64, _I32, _F, _P, _P, _P, ctypes.POINTER(_I32)]),
+    "opscvUpsampleBilinear2dNoAlloc": (_I32, [_P, _P, _I32, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _B, _D, _D, _P]),
     "aclnnUpsampleNearest2dGetWorkspaceSize": (_I32, [_P, _P, _P, _PU64, _PP]),
     "aclnnUpsampleNearest2d": _PHASE2,
     "aclnnUpsampleNearest2dV2GetWorkspaceSize": (_I32, [_P, _P, _F, _F, _P, _PU64, _PP]),

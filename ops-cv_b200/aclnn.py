@@ -9,7 +9,8 @@ from . import (ACL_BF16, ACL_DOUBLE, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_NCHW, AC
 __all__ = [
     "AclnnError", "acl_tensor", "int_array", "bool_array", "two_phase", "set_deterministic", "set_backward_algo",
     "launch_count", "reset_launch_count", "last_error", "debug_axis_table", "upsample_nearest2d",
-    "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_backward", "upsample_bicubic2d_aa",
+    "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_no_alloc",
+    "upsample_bilinear2d_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
 ]
 
@@ -179,6 +180,20 @@ def upsample_bilinear2d(x, out_hw, align_corners=False, fmt="NCHW", scales=(0.0,
     tx, ty, size = acl_tensor(x, fmt), acl_tensor(out, fmt), int_array(out_hw)
     two_phase("aclnnUpsampleBilinear2d", [tx.ptr, size.ptr, bool(align_corners), float(scales[0]), float(scales[1]),
                                           ty.ptr], x.device, workspace)
+    return out
+
+
+def upsample_bilinear2d_no_alloc(x, out_hw, align_corners=False, fmt="NCHW", scales=(0.0, 0.0), out=None):
+    """opscvUpsampleBilinear2dNoAlloc: one call, no workspace (tap tables live in the library's device image)."""
+    out = torch.empty(_out_shape(x, out_hw, fmt), dtype=x.dtype, device=x.device) if out is None else out
+    assert x.is_contiguous() and out.is_contiguous()
+    n, c, h, w = (x.shape[0], x.shape[3], x.shape[1], x.shape[2]) if fmt == "NHWC" else tuple(x.shape)
+    with torch.cuda.device(x.device):
+        status = lib().opscvUpsampleBilinear2dNoAlloc(
+            x.data_ptr(), out.data_ptr(), _DTYPES[x.dtype], _FORMATS[fmt], n, c, h, w, int(out_hw[0]), int(out_hw[1]),
+            bool(align_corners), float(scales[0]), float(scales[1]), torch.cuda.current_stream(x.device).cuda_stream)
+    if status != 0:
+        raise AclnnError("opscvUpsampleBilinear2dNoAlloc", status)
     return out
 
 
