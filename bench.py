@@ -68,7 +68,7 @@ def nbytes(t):
 
 def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
     """Returns (description, make_buffers(gen) -> dict of CPU tensors, [Op], config dict)."""
-    ws = ops.Workspace(dev)
+    ws = ops.Workspace(dev) if ops is not None else None  # None: only the description is wanted
 
     if name == "cfg2":
         n, c, hi, wi, ho, wo = 32 // batch_div, 256, 56, 56, 112, 112
@@ -293,7 +293,9 @@ def cpu_baseline(workload, budget_s=12.0):
     import torch
     import oracle
     oracle.build()
-    cores = len(os.sched_getaffinity(0))
+    # all host cores this process may use, whatever OMP_NUM_THREADS a launcher (torchrun sets 1) exported
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))
+    cores = oracle.num_threads()
     rng = np.random.default_rng(1234)
     if workload in ("cfg2", "all"):
         n, c = 4, 256  # 1/8 of the batch of the GPU workload; planes are independent
@@ -377,13 +379,16 @@ def main():
             return
         wl = "cfg2" if args.workload == "all" else args.workload
         base = cpu_baseline(wl, budget_s=max(5.0, min(60.0, 2.0 * args.steps)))
-        import torch  # noqa: F401  (only for the config text below)
+        import torch
+        cfg = make_workload(wl, None, torch, None)[2]
         line = {
-            "impl": "reference", "metric": "effective HBM GB/s (algorithmic bytes / time)", "value": base["value"],
-            "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "impl": "reference",
+            "metric": "effective HBM GB/s (algorithmic bytes / device time), all operators of the step",
+            "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": base["ms_per_sample"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl + " (bounded sample on the host CPU: " + base["sample"] + ")"},
+            "dtype": cfg["dtype"], "data": "synthetic",
+            "config": {"workload": cfg["workload"],
+                       "sample": "each step is a bounded sample on the host CPU: " + base["sample"]},
             "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
@@ -426,7 +431,7 @@ def main():
         "roofline": head["roofline"], "ops": head["ops"], "e2e": head["e2e"], "gpu_launches": head["gpu_launches"],
         "clocks": head["clocks"], "peak_source": peak_src,
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:  # reported at N=1 only
         base = cpu_baseline(names[0])
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if len(names) > 1:

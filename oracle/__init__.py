@@ -40,6 +40,15 @@ def lib():
     return _lib
 
 
+def num_threads():
+    """OpenMP threads the oracle's loops use."""
+    return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n):
+    lib().oracle_set_num_threads(int(n))
+
+
 def _f(a):
     a = np.ascontiguousarray(a, dtype=np.float32)
     return a, a.ctypes.data_as(ctypes.c_void_p)
