@@ -7,15 +7,16 @@
 //   * atomic (default): one thread per sample, channels inner, four fp32 atomics per channel into a zeroed fp32
 //     accumulator (grad_input itself for fp32 tensors, workspace for 16-bit tensors, followed by one cast).
 //   * deterministic (ACL_OPT_DETERMINISTIC): the scatter is turned into a gather with a fixed summation order.
-//       1. count   - per image, how many taps land on each input pixel (integer atomics: order-free).
-//       2. scan    - per image exclusive prefix sum of the counts -> segment offsets.
-//       3. fill    - per image, warps partition the destination pixels; every warp walks ALL samples of the
-//                    image in the order in which the reference's deterministic kernel replays them (256-sample
-//                    chunks; inside a chunk tap NW, NE, SW, SE; inside a tap ascending sample index) and appends
-//                    the taps that fall in its partition to their destination's segment. Ranks inside a
-//                    32-sample step come from __match_any_sync, so no sort is needed.
-//       4. gather  - one thread per (destination pixel, channel group) adds  weight * grad_output  over its
-//                    segment in that order and writes grad_input once.
+//       1. count   - how many taps of every chunk of samples land on each input pixel (integer atomics: order-free).
+//       2. scan    - prefix sums over chunks (per destination) and over destinations (per image): where each
+//                    destination's segment starts, and where inside it each chunk appends.
+//       3. fill    - one block per (image, chunk) appends the chunk's taps to the segments in the order in which
+//                    the reference's deterministic kernel replays them (256-sample steps; inside a step tap NW, NE,
+//                    SW, SE; inside a tap ascending sample index). Ranks inside a warp come from
+//                    __match_any_sync and the warps of a block take turns, so no sort is needed.
+//       4. gather  - per (image, channel group) the group's grad_output planes are staged in shared memory; one
+//                    thread per destination pixel adds  weight * grad_output  over its segment in list order and
+//                    writes grad_input once. (Planes too large for shared memory gather from global memory.)
 //     The summation order per destination is fixed by the data alone, so results are bit-identical from run to
 //     run, and equal to a serial replay in the reference's order. The segment lists are built once per call and
 //     reused by all channels.
@@ -163,43 +164,73 @@ __device__ __forceinline__ int32_t TapDest(const GradTaps& t, int tap, const Gri
     return gs::Within(yy, xx, g.hin, g.win) ? yy * g.win + xx : -1;
 }
 
+// The reference's deterministic kernel stages the contributions of 256 consecutive samples and lets one thread
+// replay them tap by tap (grid_sampler2_d_grad_simt_det.h:78-106, VF_MAX_THREAD_NUM = 256), so per destination
+// the order is: 256-sample step, then tap (NW, NE, SW, SE), then sample index. The lists keep that order.
+constexpr int kDetStep = 256;
+
+// counts[(n * chunks + c) * inPlane + d] = taps of the samples of chunk c of image n that land on destination d.
+// A chunk is `chunkSamples` consecutive samples (a multiple of kDetStep).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-    DetCountKernel(const T* __restrict__ grid, int32_t* __restrict__ counts, GridShape g, int64_t total)
+    DetCountKernel(const T* __restrict__ grid, int32_t* __restrict__ counts, GridShape g, int32_t chunks,
+                   int32_t chunkSamples, int64_t total)
 {
     const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win;
     const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
         const int64_t n = s / outPlane;
+        const int64_t c = (s - n * outPlane) / chunkSamples;
         const GradTaps t = MakeGradTaps(DType<T>::Load(grid + 2 * s), DType<T>::Load(grid + 2 * s + 1), g);
+        int32_t* cnt = counts + (n * chunks + c) * inPlane;
 #pragma unroll
         for (int tap = 0; tap < 4; ++tap) {
             const int32_t d = TapDest(t, tap, g);
             if (d >= 0) {
-                atomicAdd(counts + n * (inPlane + 1) + d, 1);
+                atomicAdd(cnt + d, 1);
             }
         }
     }
 }
 
-// One block per image: exclusive scan of counts[n][0..inPlane) in place; counts[n][inPlane] = total. Also copies
-// the offsets into `cursor` (the running append positions used by the fill kernel).
-__global__ void __launch_bounds__(1024) DetScanKernel(int32_t* __restrict__ counts, int32_t* __restrict__ cursor,
-                                                       int64_t inPlane)
+// Turns the per-chunk counts into list positions, in two steps.
+// Column step (one thread per (image, destination)): counts[n][c][d] becomes the number of entries that earlier
+// chunks append to destination d, and segStart[n][d] the destination's total.
+__global__ void __launch_bounds__(kThreads)
+    DetColumnKernel(int32_t* __restrict__ counts, int32_t* __restrict__ segStart, int64_t inPlane, int32_t chunks,
+                    int64_t total)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t n = i / inPlane;
+        const int64_t d = i - n * inPlane;
+        int32_t* cnt = counts + n * chunks * inPlane + d;
+        int32_t run = 0;
+        for (int32_t c = 0; c < chunks; ++c) {
+            const int32_t t = cnt[c * inPlane];
+            cnt[c * inPlane] = run;
+            run += t;
+        }
+        segStart[n * (inPlane + 1) + d] = run;
+    }
+}
+
+// Segment step (one block per image): exclusive prefix sum of the totals in place; segStart[n][inPlane] = number of
+// entries of the image.
+__global__ void __launch_bounds__(1024) DetScanKernel(int32_t* __restrict__ segStart, int64_t inPlane)
 {
     __shared__ int32_t warpSums[32];
     __shared__ int32_t carry;
-    int32_t* c = counts + blockIdx.x * (inPlane + 1);
-    int32_t* cur = cursor + blockIdx.x * inPlane;
+    int32_t* seg = segStart + static_cast<int64_t>(blockIdx.x) * (inPlane + 1);
     if (threadIdx.x == 0) {
         carry = 0;
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int64_t base = 0; base < inPlane; base += blockDim.x) {
-        const int64_t i = base + threadIdx.x;
-        const int32_t v = i < inPlane ? c[i] : 0;
+        const int64_t d = base + threadIdx.x;
+        const int32_t v = d < inPlane ? seg[d] : 0;
         int32_t incl = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -226,9 +257,8 @@ __global__ void __launch_bounds__(1024) DetScanKernel(int32_t* __restrict__ coun
         __syncthreads();
         const int32_t warpOffset = warp == 0 ? 0 : warpSums[warp - 1];
         const int32_t excl = carry + warpOffset + incl - v;
-        if (i < inPlane) {
-            c[i] = excl;
-            cur[i] = excl;
+        if (d < inPlane) {
+            seg[d] = excl;
         }
         __syncthreads();
         if (threadIdx.x == blockDim.x - 1) {
@@ -237,77 +267,138 @@ __global__ void __launch_bounds__(1024) DetScanKernel(int32_t* __restrict__ coun
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        c[inPlane] = carry;
+        seg[inPlane] = carry;
     }
 }
 
-// The reference's deterministic kernel stages the contributions of 256 consecutive samples and lets one thread
-// replay them tap by tap (grid_sampler2_d_grad_simt_det.h:78-106, VF_MAX_THREAD_NUM = 256), so per destination
-// the order is: 256-sample chunk, then tap (NW, NE, SW, SE), then sample index. The fill keeps that order.
-constexpr int kDetChunk = 256;
-constexpr int kDetSub = kDetChunk / 32;
-
-// grid.x = warpsPerImage * N blocks of one warp. Warp w of image n owns destinations [d0, d1).
+// One block of kDetStep threads per (image, chunk). The block appends the taps of its chunk to the destination
+// segments in list order: 256-sample step by step; inside a step tap by tap; inside a tap the eight warps take turns
+// (a barrier between turns), and inside a warp the rank among lanes with the same destination comes from
+// __match_any_sync, so the position of every entry is a function of the data alone. The running positions live in
+// shared memory when the plane fits (cursorInSmem), else in the chunk's own slice of the offsets array.
 template <typename T>
-__global__ void __launch_bounds__(32)
-    DetFillKernel(const T* __restrict__ grid, int32_t* cursor, Entry* __restrict__ entries, GridShape g,
-                  int32_t warpsPerImage, int64_t entriesPerImage)
+__global__ void __launch_bounds__(kDetStep)
+    DetFillKernel(const T* __restrict__ grid, int32_t* offsets, const int32_t* __restrict__ segStart,
+                  Entry* __restrict__ entries, GridShape g, int32_t chunks, int32_t chunkSamples,
+                  int64_t entriesPerImage, int32_t cursorInSmem)
 {
-    const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win;
+    extern __shared__ int32_t cursorSmem[];
+    const int32_t inPlane = g.hin * g.win;
     const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
-    const int64_t n = blockIdx.x / warpsPerImage;
-    const int32_t w = blockIdx.x - n * warpsPerImage;
-    const int64_t per = CeilDiv(inPlane, warpsPerImage);
-    const int32_t d0 = static_cast<int32_t>(min(inPlane, per * w));
-    const int32_t d1 = static_cast<int32_t>(min(inPlane, per * (w + 1)));
-    if (d0 >= d1) {
-        return;
+    const int64_t n = blockIdx.x / chunks;
+    const int32_t c = static_cast<int32_t>(blockIdx.x - n * chunks);
+    int32_t* off = offsets + (n * chunks + c) * static_cast<int64_t>(inPlane);
+    // running position = start of the destination's segment + what earlier chunks append to it
+    const int32_t* seg = segStart + n * (static_cast<int64_t>(inPlane) + 1);
+    for (int32_t i = threadIdx.x; i < inPlane; i += blockDim.x) {
+        if (cursorInSmem) {
+            cursorSmem[i] = off[i] + seg[i];
+        } else {
+            off[i] += seg[i];
+        }
     }
-    const int lane = threadIdx.x;
-    const unsigned lower = (1u << lane) - 1u;
-    volatile int32_t* cur = cursor + n * inPlane;
+    __syncthreads();
+    volatile int32_t* cur = cursorInSmem ? cursorSmem : off;
     Entry* ent = entries + n * entriesPerImage;
     const T* gb = grid + 2 * n * outPlane;
-    for (int64_t chunk = 0; chunk < outPlane; chunk += kDetChunk) {
-        int32_t x0[kDetSub], y0[kDetSub];
-        float wt[kDetSub][4];
-#pragma unroll
-        for (int sub = 0; sub < kDetSub; ++sub) {
-            const int64_t p = chunk + sub * 32 + lane;
-            x0[sub] = INT32_MIN / 2; // far out of bounds: no tap of a dead lane is in range
-            y0[sub] = INT32_MIN / 2;
-            wt[sub][0] = wt[sub][1] = wt[sub][2] = wt[sub][3] = 0.0f;
-            if (p < outPlane) {
-                const GradTaps t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
-                x0[sub] = t.x0;
-                y0[sub] = t.y0;
-                wt[sub][0] = t.tnw;
-                wt[sub][1] = t.tne;
-                wt[sub][2] = t.tsw;
-                wt[sub][3] = t.tse;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned lower = (1u << lane) - 1u;
+    const int64_t p0 = static_cast<int64_t>(c) * chunkSamples, p1 = min(outPlane, p0 + chunkSamples);
+    const int numTaps = g.interp == 0 ? 4 : 1;
+    for (int64_t base = p0; base < p1; base += kDetStep) {
+        const int64_t p = base + threadIdx.x;
+        GradTaps t{};
+        t.x0 = INT32_MIN / 2; // far out of bounds: a thread past the end has no tap in range
+        t.y0 = INT32_MIN / 2;
+        if (p < p1) {
+            t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
+        }
+        for (int tap = 0; tap < numTaps; ++tap) {
+            const int32_t d = TapDest(t, tap, g);
+            const float wgt = tap == 0 ? t.tnw : (tap == 1 ? t.tne : (tap == 2 ? t.tsw : t.tse));
+            for (int turn = 0; turn < kDetStep / 32; ++turn) {
+                if (warp == turn) {
+                    // lanes without a tap get a key no other lane has: they match only themselves
+                    const unsigned peers = __match_any_sync(0xffffffffu, d >= 0 ? d : -1 - lane);
+                    int32_t start = 0;
+                    if (d >= 0) {
+                        start = cur[d];
+                        ent[start + __popc(peers & lower)] = Entry{static_cast<int32_t>(p), wgt};
+                    }
+                    __syncwarp();
+                    if (d >= 0 && (peers & lower) == 0) { // lowest lane of each group advances the position
+                        cur[d] = start + __popc(peers);
+                    }
+                }
+                __syncthreads();
             }
         }
-        const int numTaps = g.interp == 0 ? 4 : 1;
-        for (int tap = 0; tap < numTaps; ++tap) {
+    }
+}
+
+// Gather with grad_output staged in shared memory: one block per (image, group of CG channels) copies the group's
+// grad_output planes into shared memory as tile[sample] = {CG channels}; then one thread per destination pixel adds
+// weight * grad_output over the destination's segment, in list order, and writes grad_input once.
+template <typename T, int CG>
+__global__ void __launch_bounds__(1024)
+    DetGatherStagedKernel(const T* __restrict__ go, const int32_t* __restrict__ segStart,
+                          const Entry* __restrict__ entries, T* __restrict__ gi, GridShape g, int32_t groups,
+                          int64_t entriesPerImage)
+{
+    extern __shared__ __align__(16) unsigned char stagedSmem[];
+    using Vec = Pack<T, CG>;
+    Vec* tile = reinterpret_cast<Vec*>(stagedSmem);
+    const int32_t inPlane = g.hin * g.win, outPlane = g.hout * g.wout;
+    const int64_t n = blockIdx.x / groups;
+    const int32_t c0 = static_cast<int32_t>(blockIdx.x - n * groups) * CG;
+    const int32_t nch = min(CG, static_cast<int32_t>(g.c) - c0);
+    const T* gob = go + (n * g.c + c0) * outPlane;
+    for (int32_t i = threadIdx.x; i < outPlane; i += blockDim.x) {
+        Vec v;
 #pragma unroll
-            for (int sub = 0; sub < kDetSub; ++sub) {
-                const int32_t yy = y0[sub] + (tap >> 1), xx = x0[sub] + (tap & 1);
-                const int32_t d = gs::Within(yy, xx, g.hin, g.win) ? yy * g.win + xx : -1;
-                const bool mine = d >= d0 && d < d1;
-                // Lanes without a tap in this partition get a key no other lane has: they match only themselves.
-                const int32_t key = mine ? d : -1 - lane;
-                const unsigned peers = __match_any_sync(0xffffffffu, key);
-                if (mine) {
-                    const int32_t start = cur[d];
-                    const int32_t rank = __popc(peers & lower);
-                    const float wgt = tap == 0 ? wt[sub][0] : (tap == 1 ? wt[sub][1] : (tap == 2 ? wt[sub][2] : wt[sub][3]));
-                    ent[start + rank] = Entry{static_cast<int32_t>(chunk + sub * 32 + lane), wgt};
+        for (int k = 0; k < CG; ++k) {
+            v.v[k] = k < nch ? __ldg(gob + static_cast<int64_t>(k) * outPlane + i) : DType<T>::FromF(0.0f);
+        }
+        tile[i] = v;
+    }
+    __syncthreads();
+    const int32_t* seg = segStart + n * (inPlane + 1);
+    const Entry* ent = entries + n * entriesPerImage;
+    T* gib = gi + (n * g.c + c0) * inPlane;
+    for (int32_t d = threadIdx.x; d < inPlane; d += blockDim.x) {
+        const int32_t a = __ldg(seg + d), b = __ldg(seg + d + 1);
+        float acc[CG];
+#pragma unroll
+        for (int k = 0; k < CG; ++k) {
+            acc[k] = 0.0f;
+        }
+        // four entries per trip: their loads are independent, the additions stay in list order
+        for (int32_t e = a; e < b; e += 4) {
+            int2 raw[4];
+            Vec v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                raw[u] = e + u < b ? __ldg(reinterpret_cast<const int2*>(ent + e + u)) : make_int2(0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                v[u] = tile[raw[u].x];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (e + u < b) {
+                    const float wgt = __int_as_float(raw[u].y);
+#pragma unroll
+                    for (int k = 0; k < CG; ++k) {
+                        acc[k] = Add(acc[k], Mul(wgt, DType<T>::ToF(v[u].v[k])));
+                    }
                 }
-                __syncwarp();
-                if (mine && (peers & lower) == 0) { // lowest lane of each group advances the cursor
-                    cur[d] = cur[d] + __popc(peers);
-                }
-                __syncwarp();
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < CG; ++k) {
+            if (k < nch) {
+                gib[static_cast<int64_t>(k) * inPlane + d] = DType<T>::FromF(acc[k]);
             }
         }
     }
@@ -367,11 +458,13 @@ __global__ void __launch_bounds__(kThreads)
 // atomics, the input taps come from shared memory. At the end the accumulators are written to grad_input once, in
 // the storage dtype: no zero-fill of grad_input, no global atomics on it, no fp32 staging buffer for 16-bit tensors.
 // grad_grid needs the sum over ALL channels: every block adds its group's partial (gix, giy) to an fp32 buffer with
-// one 8-byte global atomic per pixel; GridGradFinishKernel scales by the coordinate multipliers and stores.
+// one 8-byte global atomic per pixel (or, in the reproducible mode, stores it in the group's own slice of a partial
+// buffer); GridGradFinishKernel adds the partials in group order, scales by the coordinate multipliers and stores.
 template <typename T, int CG, bool WANT_IN, bool WANT_GRID>
 __global__ void __launch_bounds__(1024)
     GridGradStagedKernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ grid,
-                         T* __restrict__ gi, float2* __restrict__ ggAcc, GridShape g, int32_t groups)
+                         T* __restrict__ gi, float2* __restrict__ ggAcc, GridShape g, int32_t groups,
+                         int64_t partStride)
 {
     extern __shared__ __align__(16) unsigned char stagedSmem[];
     using Vec = Pack<T, CG>;
@@ -441,7 +534,11 @@ __global__ void __launch_bounds__(1024)
         tap(gs::Within(t.y0 + 1, t.x0, g.hin, g.win), g.win, t.tsw, yw, xe, true, false);
         tap(gs::Within(t.y0 + 1, t.x0 + 1, g.hin, g.win), g.win + 1, t.tse, yw, xw, false, false);
         if (WANT_GRID) {
-            atomicAdd(ggAcc + n * outPlane + p, make_float2(gix, giy));
+            if (partStride > 0) { // reproducible mode: every group keeps its own partial sums
+                ggAcc[(blockIdx.x - n * groups) * partStride + n * outPlane + p] = make_float2(gix, giy);
+            } else {
+                atomicAdd(ggAcc + n * outPlane + p, make_float2(gix, giy));
+            }
         }
     }
     if (WANT_IN) {
@@ -462,14 +559,19 @@ __global__ void __launch_bounds__(1024)
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     GridGradFinishKernel(const T* __restrict__ grid, const float2* __restrict__ ggAcc, T* __restrict__ ggrid,
-                         GridShape g, int64_t total)
+                         GridShape g, int64_t total, int32_t parts, int64_t partStride)
 {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
         float mx, my;
         gs::SourceIndexSetGrad(DType<T>::Load(grid + 2 * s), g.win, g.pad, g.align, &mx);
         gs::SourceIndexSetGrad(DType<T>::Load(grid + 2 * s + 1), g.hin, g.pad, g.align, &my);
-        const float2 a = ggAcc[s];
+        float2 a = ggAcc[s];
+        for (int32_t q = 1; q < parts; ++q) {
+            const float2 b = ggAcc[q * partStride + s];
+            a.x = Add(a.x, b.x);
+            a.y = Add(a.y, b.y);
+        }
         ggrid[2 * s] = DType<T>::FromF(Mul(mx, a.x));
         ggrid[2 * s + 1] = DType<T>::FromF(Mul(my, a.y));
     }
@@ -494,14 +596,18 @@ inline int32_t StagedBwdGroup(int es, int64_t inPlane, int64_t c, bool wantInput
 
 template <typename T, int CG>
 cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* ggrid, float2* ggAcc, GridShape g,
-                            const GridGradPlan& plan, cudaStream_t s)
+                            bool wantInput, bool wantGrid, bool partials, cudaStream_t s)
 {
+    struct {
+        bool wantInput, wantGrid;
+    } plan{wantInput, wantGrid};
     const int64_t inPlane = static_cast<int64_t>(g.hin) * g.win, outPlane = static_cast<int64_t>(g.hout) * g.wout;
     const int32_t groups = static_cast<int32_t>(CeilDiv(g.c, CG));
     const size_t smem = StagedBwdSmem(sizeof(T), inPlane, CG, plan.wantInput, plan.wantGrid);
     const int threads = smem <= 110 * 1024 ? 512 : 1024;
     cudaError_t e = cudaSuccess;
-    if (plan.wantGrid) {
+    const int64_t partStride = partials ? g.n * outPlane : 0;
+    if (plan.wantGrid && !partials) {
         e = cudaMemsetAsync(ggAcc, 0, static_cast<size_t>(g.n * outPlane) * sizeof(float2), s);
         if (e != cudaSuccess) {
             return e;
@@ -515,7 +621,8 @@ cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* gg
                 return;
             }
         }
-        kernel<<<static_cast<unsigned>(g.n * groups), threads, smem, s>>>(go, x, grid, gi, ggAcc, g, groups);
+        kernel<<<static_cast<unsigned>(g.n * groups), threads, smem, s>>>(go, x, grid, gi, ggAcc, g, groups,
+                                                                          partStride);
         CountLaunch();
         e = cudaGetLastError();
     };
@@ -528,7 +635,8 @@ cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* gg
     }
     if (e == cudaSuccess && plan.wantGrid) {
         const int64_t samples = g.n * outPlane;
-        GridGradFinishKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(grid, ggAcc, ggrid, g, samples);
+        GridGradFinishKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(grid, ggAcc, ggrid, g, samples,
+                                                                                partials ? groups : 1, partStride);
         CountLaunch();
         e = cudaGetLastError();
     }
@@ -559,15 +667,46 @@ GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool w
     }
     if (wantInput) {
         if (deterministic) {
-            // counts/offsets [N][inPlane+1] and cursors [N][inPlane], then entries [N][4*outPlane]
-            p.countBytes = Align256(static_cast<uint64_t>(g.n) * (inPlane + 1) * 4) +
-                           Align256(static_cast<uint64_t>(g.n) * inPlane * 4);
+            // Chunks of the sample sequence get their own append positions, so that they can be filled in
+            // parallel. Start from one 256-sample step per chunk and coarsen while the positions
+            // [N][chunks][inPlane] would exceed 256 MB.
+            int64_t chunkSamples = kDetStep;
+            int64_t chunks = CeilDiv(static_cast<int64_t>(outPlane), chunkSamples);
+            while (chunks > 1 && static_cast<uint64_t>(g.n) * chunks * inPlane * 4 > (256ULL << 20)) {
+                chunkSamples *= 2;
+                chunks = CeilDiv(static_cast<int64_t>(outPlane), chunkSamples);
+            }
+            p.detChunks = static_cast<int32_t>(chunks);
+            p.detChunkSamples = static_cast<int32_t>(chunkSamples);
+            p.detCursorSmem = inPlane * 4 <= 200 * 1024;
+            // gather with grad_output in shared memory: widest channel vector whose planes fit
+            p.detGatherGroup = 0;
+            const int es = DtSize(dt);
+            for (int cg = 16 / es; cg * es >= 4 && outPlane < (1ULL << 30); cg /= 2) {
+                if (outPlane * cg * es <= 220ULL * 1024 && (cg == 1 || cg / 2 < g.c)) {
+                    p.detGatherGroup = cg;
+                    break;
+                }
+            }
+            // positions [N][chunks][inPlane] and segment starts [N][inPlane+1], then entries [N][4*outPlane]
+            p.countBytes = Align256(static_cast<uint64_t>(g.n) * chunks * inPlane * 4) +
+                           Align256(static_cast<uint64_t>(g.n) * (inPlane + 1) * 4);
             p.entryBytes = Align256(static_cast<uint64_t>(g.n) * 4 * outPlane * sizeof(Entry));
         } else if (dt != Dt::F32) {
             p.accBytes = Align256(static_cast<uint64_t>(g.n) * g.c * inPlane * 4);
         }
     }
-    p.total = p.accBytes + p.countBytes + p.entryBytes;
+    if (deterministic && wantGrid && g.interp == 0 && outPlane < (1ULL << 30)) {
+        // grad_grid from the staged kernel with per-group partial sums added in group order (needs
+        // [groups][N * outPlane] float2; the per-sample kernel is the fallback)
+        const int32_t cg = StagedBwdGroup(DtSize(dt), static_cast<int64_t>(inPlane), g.c, false, true);
+        if (cg > 0 && g.n * CeilDiv(g.c, cg) >= NumSMs() / 2 && g.n * CeilDiv(g.c, cg) < (1LL << 31) &&
+            static_cast<uint64_t>(CeilDiv(g.c, cg)) * g.n * outPlane * 8 <= (1ULL << 30)) {
+            p.detGridGroup = cg;
+            p.gridAccBytes = Align256(static_cast<uint64_t>(CeilDiv(g.c, cg)) * g.n * outPlane * 8);
+        }
+    }
+    p.total = p.gridAccBytes + p.accBytes + p.countBytes + p.entryBytes;
     return p;
 }
 
@@ -591,11 +730,30 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
             float2* ggAcc = reinterpret_cast<float2*>(ws);
             constexpr int kMax = 16 / sizeof(T);
             if (plan.stagedGroup == kMax) {
-                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, ggAcc, g, plan, s);
+                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, ggAcc, g, plan.wantInput, plan.wantGrid, false, s);
             } else if (plan.stagedGroup == kMax / 2) {
-                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, ggAcc, g, plan, s);
+                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, ggAcc, g, plan.wantInput, plan.wantGrid, false, s);
             } else {
-                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, ggAcc, g, plan, s);
+                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, ggAcc, g, plan.wantInput, plan.wantGrid, false, s);
+            }
+        });
+        return e;
+    }
+
+    if (plan.deterministic && !plan.wantInput && plan.detGridGroup > 0) {
+        OPSCV_DISPATCH_DT(dt, T, {
+            const T* pgo = static_cast<const T*>(go);
+            const T* px = static_cast<const T*>(x);
+            const T* pg = static_cast<const T*>(grid);
+            T* pgg = static_cast<T*>(ggrid);
+            float2* parts = reinterpret_cast<float2*>(ws);
+            constexpr int kMax = 16 / sizeof(T);
+            if (plan.detGridGroup == kMax) {
+                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, nullptr, pgg, parts, g, false, true, true, s);
+            } else if (plan.detGridGroup == kMax / 2) {
+                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, nullptr, pgg, parts, g, false, true, true, s);
+            } else {
+                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, nullptr, pgg, parts, g, false, true, true, s);
             }
         });
         return e;
@@ -637,35 +795,86 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
     }
 
     // deterministic grad_input
-    const uint64_t countsBytes = Align256(static_cast<uint64_t>(g.n) * (inPlane + 1) * 4);
-    int32_t* counts = reinterpret_cast<int32_t*>(ws);
-    int32_t* cursor = reinterpret_cast<int32_t*>(ws + countsBytes);
+    const uint64_t posBytes = Align256(static_cast<uint64_t>(g.n) * plan.detChunks * inPlane * 4);
+    int32_t* positions = reinterpret_cast<int32_t*>(ws);
+    int32_t* segStart = reinterpret_cast<int32_t*>(ws + posBytes);
     Entry* entries = reinterpret_cast<Entry*>(ws + plan.countBytes);
     const int64_t entriesPerImage = 4 * outPlane;
-    e = cudaMemsetAsync(counts, 0, static_cast<size_t>(g.n) * (inPlane + 1) * 4, s);
+    e = cudaMemsetAsync(positions, 0, static_cast<size_t>(g.n) * plan.detChunks * inPlane * 4, s);
     if (e != cudaSuccess) {
         return e;
     }
     CountLaunch();
-    // Enough one-warp blocks per image to occupy the machine, but never more than one per 32 destinations.
-    int64_t warpsPerImage = CeilDiv(static_cast<int64_t>(NumSMs()) * 32, g.n > 0 ? g.n : 1);
-    warpsPerImage = warpsPerImage > CeilDiv(inPlane, 32) ? CeilDiv(inPlane, 32) : warpsPerImage;
-    warpsPerImage = warpsPerImage < 1 ? 1 : warpsPerImage;
-    constexpr int CG = 8;
-    const int32_t chanGroups = static_cast<int32_t>(CeilDiv(g.c, CG));
-    const int64_t gatherTotal = g.n * chanGroups * inPlane;
     OPSCV_DISPATCH_DT(dt, T, {
         const T* pgo = static_cast<const T*>(go);
         const T* px = static_cast<const T*>(x);
         const T* pg = static_cast<const T*>(grid);
-        DetCountKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(pg, counts, g, samples);
-        DetScanKernel<<<static_cast<unsigned>(g.n), 1024, 0, s>>>(counts, cursor, inPlane);
-        DetFillKernel<T><<<static_cast<unsigned>(g.n * warpsPerImage), 32, 0, s>>>(
-            pg, cursor, entries, g, static_cast<int32_t>(warpsPerImage), entriesPerImage);
-        DetGatherKernel<T, CG><<<GridFor(gatherTotal, kThreads, 16), kThreads, 0, s>>>(
-            pgo, counts, entries, static_cast<T*>(gi), g, chanGroups, entriesPerImage, gatherTotal);
+        T* pgi = static_cast<T*>(gi);
+        DetCountKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(pg, positions, g, plan.detChunks,
+                                                                          plan.detChunkSamples, samples);
+        DetColumnKernel<<<GridFor(g.n * inPlane, kThreads), kThreads, 0, s>>>(positions, segStart, inPlane,
+                                                                              plan.detChunks, g.n * inPlane);
+        DetScanKernel<<<static_cast<unsigned>(g.n), 1024, 0, s>>>(segStart, inPlane);
+        const size_t cursorBytes = plan.detCursorSmem ? static_cast<size_t>(inPlane) * 4 : 0;
+        if (cursorBytes > 48 * 1024) {
+            e = cudaFuncSetAttribute(DetFillKernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(cursorBytes));
+        }
+        if (e == cudaSuccess) {
+            DetFillKernel<T><<<static_cast<unsigned>(g.n * plan.detChunks), kDetStep, cursorBytes, s>>>(
+                pg, positions, segStart, entries, g, plan.detChunks, plan.detChunkSamples, entriesPerImage,
+                plan.detCursorSmem ? 1 : 0);
+        }
         CountLaunch(4);
-        if (plan.wantGrid) {
+        if (e == cudaSuccess && plan.detGatherGroup > 0) {
+            auto gather = [&](auto kernel, int cg) {
+                const size_t smem = static_cast<size_t>(outPlane) * cg * sizeof(T);
+                if (smem > 48 * 1024) {
+                    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+                    if (e != cudaSuccess) {
+                        return;
+                    }
+                }
+                const int32_t groups = static_cast<int32_t>(CeilDiv(g.c, cg));
+                const int threads = smem <= 110 * 1024 ? 512 : 1024;
+                kernel<<<static_cast<unsigned>(g.n * groups), threads, smem, s>>>(pgo, segStart, entries, pgi, g,
+                                                                                  groups, entriesPerImage);
+            };
+            constexpr int kMax = 16 / sizeof(T);
+            if (plan.detGatherGroup == kMax) {
+                gather(DetGatherStagedKernel<T, kMax>, kMax);
+            } else if (plan.detGatherGroup == kMax / 2) {
+                gather(DetGatherStagedKernel<T, kMax / 2>, kMax / 2);
+            } else {
+                gather(DetGatherStagedKernel<T, kMax / 4>, kMax / 4);
+            }
+        } else if (e == cudaSuccess) {
+            constexpr int CG = 8;
+            const int32_t chanGroups = static_cast<int32_t>(CeilDiv(g.c, CG));
+            const int64_t gatherTotal = g.n * chanGroups * inPlane;
+            DetGatherKernel<T, CG><<<GridFor(gatherTotal, kThreads, 16), kThreads, 0, s>>>(
+                pgo, segStart, entries, pgi, g, chanGroups, entriesPerImage, gatherTotal);
+        }
+        CountLaunch();
+        if (e != cudaSuccess) {
+            return e;
+        }
+        if (plan.wantGrid && plan.detGridGroup > 0) {
+            float2* parts = reinterpret_cast<float2*>(ws + plan.countBytes + plan.entryBytes);
+            T* pgg = static_cast<T*>(ggrid);
+            constexpr int kMax = 16 / sizeof(T);
+            if (plan.detGridGroup == kMax) {
+                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, parts, g, false, true, true, s);
+            } else if (plan.detGridGroup == kMax / 2) {
+                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, parts, g, false, true, true, s);
+            } else {
+                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, parts, g, false, true, true, s);
+            }
+            if (e != cudaSuccess) {
+                return e;
+            }
+        } else if (plan.wantGrid) {
             GridGradSampleKernel<T, false, true><<<GridFor(samples, kThreads, 16), kThreads, 0, s>>>(
                 pgo, px, pg, nullptr, static_cast<T*>(ggrid), g, samples);
             CountLaunch();

@@ -147,9 +147,13 @@ struct GridGradPlan {
     bool deterministic;
     bool wantInput, wantGrid;
     int32_t stagedGroup; // > 0: shared-memory staged kernel with this many channels per block
-    uint64_t gridAccBytes; // staged kernel: fp32 (gix, giy) sums per sample
+    int32_t detGridGroup;  // deterministic grad_grid from the staged kernel with per-group partials (0: per-sample kernel)
+    uint64_t gridAccBytes; // staged kernel: fp32 (gix, giy) sums per sample (per group and sample with partials)
     uint64_t accBytes;   // fp32 grad_input accumulator (16-bit dtypes, atomic mode)
-    uint64_t countBytes; // deterministic: per-destination tap counts / offsets
+    int32_t detChunks, detChunkSamples; // deterministic: chunks of the sample sequence filled in parallel
+    bool detCursorSmem;   // deterministic fill: append positions fit shared memory
+    int32_t detGatherGroup; // deterministic gather: channels per block with grad_output staged (0: global gather)
+    uint64_t countBytes; // deterministic: append positions per chunk and segment starts
     uint64_t entryBytes; // deterministic: sorted (sample, weight) entries
     uint64_t total;
 };

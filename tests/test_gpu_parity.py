@@ -352,6 +352,19 @@ def test_grid_sampler_staged_kernels(ops, oracle, dev, dtype, pad, align, c):
     gi, gg = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), 0, pad, align)
     check_sum(gi, ri, dtype)
     check_sum(gg, rg, dtype)
+    # reproducible mode: chunked segment lists + staged gather, grad_grid from per-group partial sums
+    ops.set_deterministic(True)
+    try:
+        runs = [ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), 0, pad, align) for _ in range(2)]
+        only_grid = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), 0, pad, align, mask=(False, True))
+    finally:
+        ops.set_deterministic(False)
+    bits = torch.int32 if dtype == torch.float32 else torch.int16
+    assert torch.equal(runs[0][0].view(bits), runs[1][0].view(bits))
+    assert torch.equal(runs[0][1].view(bits), runs[1][1].view(bits))
+    assert torch.equal(runs[0][1].view(bits), only_grid[1].view(bits))
+    check_sum(runs[0][0], ri, dtype)
+    check_sum(runs[0][1], rg, dtype)
     sentinel = torch.full_like(x, 7.0).to(dev)
     gi3, gg3 = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), 0, pad, align, mask=(False, True),
                                            input_grad=sentinel)
