@@ -39,11 +39,9 @@ struct GradTaps {
     float tnw, tne, tsw, tse;
 };
 
-__device__ __forceinline__ GradTaps MakeGradTaps(float gx, float gy, const GridShape& g)
+// Taps from source coordinates that SourceIndexSetGrad has already produced (t.ix, t.iy set by the caller).
+__device__ __forceinline__ void FinishGradTaps(GradTaps& t, const GridShape& g)
 {
-    GradTaps t;
-    t.ix = gs::SourceIndexSetGrad(gx, g.win, g.pad, g.align, &t.mx);
-    t.iy = gs::SourceIndexSetGrad(gy, g.hin, g.pad, g.align, &t.my);
     if (g.interp == 0) {
         t.x0 = static_cast<int32_t>(floorf(t.ix));
         t.y0 = static_cast<int32_t>(floorf(t.iy));
@@ -59,7 +57,29 @@ __device__ __forceinline__ GradTaps MakeGradTaps(float gx, float gy, const GridS
         t.tnw = 1.0f;
         t.tne = t.tsw = t.tse = 0.0f;
     }
+}
+
+__device__ __forceinline__ GradTaps MakeGradTaps(float gx, float gy, const GridShape& g)
+{
+    GradTaps t;
+    t.ix = gs::SourceIndexSetGrad(gx, g.win, g.pad, g.align, &t.mx);
+    t.iy = gs::SourceIndexSetGrad(gy, g.hin, g.pad, g.align, &t.my);
+    FinishGradTaps(t, g);
     return t;
+}
+
+// Source coordinates of every sample, evaluated once instead of once per channel group (staged kernel).
+template <typename T>
+__global__ void __launch_bounds__(256)
+    GridGradCoordsKernel(const T* __restrict__ grid, float2* __restrict__ rec, GridShape g, int64_t total)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
+        float mx, my;
+        const float ix = gs::SourceIndexSetGrad(DType<T>::Load(grid + 2 * s), g.win, g.pad, g.align, &mx);
+        const float iy = gs::SourceIndexSetGrad(DType<T>::Load(grid + 2 * s + 1), g.hin, g.pad, g.align, &my);
+        rec[s] = make_float2(ix, iy);
+    }
 }
 
 // One thread per sample; channels inner. ATOMIC_GI: scatter grad_input with fp32 atomics. WANT_GRID: grad_grid.
@@ -207,10 +227,19 @@ __global__ void __launch_bounds__(kThreads)
         const int64_t d = i - n * inPlane;
         int32_t* cnt = counts + n * chunks * inPlane + d;
         int32_t run = 0;
-        for (int32_t c = 0; c < chunks; ++c) {
-            const int32_t t = cnt[c * inPlane];
-            cnt[c * inPlane] = run;
-            run += t;
+        for (int32_t c0 = 0; c0 < chunks; c0 += 8) { // eight independent loads per trip, then the running sum
+            int32_t t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                t[u] = c0 + u < chunks ? cnt[(c0 + u) * inPlane] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (c0 + u < chunks) {
+                    cnt[(c0 + u) * inPlane] = run;
+                    run += t[u];
+                }
+            }
         }
         segStart[n * (inPlane + 1) + d] = run;
     }
@@ -462,7 +491,7 @@ __global__ void __launch_bounds__(kThreads)
 // buffer); GridGradFinishKernel adds the partials in group order, scales by the coordinate multipliers and stores.
 template <typename T, int CG, bool WANT_IN, bool WANT_GRID>
 __global__ void __launch_bounds__(1024)
-    GridGradStagedKernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ grid,
+    GridGradStagedKernel(const T* __restrict__ go, const T* __restrict__ x, const float2* __restrict__ rec,
                          T* __restrict__ gi, float2* __restrict__ ggAcc, GridShape g, int32_t groups,
                          int64_t partStride)
 {
@@ -491,10 +520,14 @@ __global__ void __launch_bounds__(1024)
         }
     }
     __syncthreads();
-    const T* gb = grid + 2 * n * outPlane;
+    const float2* rb = rec + n * outPlane;
     const T* gob = go + (n * g.c + c0) * outPlane;
     for (int32_t p = threadIdx.x; p < outPlane; p += blockDim.x) {
-        const GradTaps t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
+        const float2 r = __ldg(rb + p);
+        GradTaps t;
+        t.ix = r.x;
+        t.iy = r.y;
+        FinishGradTaps(t, g);
         float gv[CG];
 #pragma unroll
         for (int k = 0; k < CG; ++k) {
@@ -595,8 +628,8 @@ inline int32_t StagedBwdGroup(int es, int64_t inPlane, int64_t c, bool wantInput
 }
 
 template <typename T, int CG>
-cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* ggrid, float2* ggAcc, GridShape g,
-                            bool wantInput, bool wantGrid, bool partials, cudaStream_t s)
+cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* ggrid, float2* ggAcc, float2* rec,
+                            GridShape g, bool wantInput, bool wantGrid, bool partials, cudaStream_t s)
 {
     struct {
         bool wantInput, wantGrid;
@@ -606,6 +639,8 @@ cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* gg
     const size_t smem = StagedBwdSmem(sizeof(T), inPlane, CG, plan.wantInput, plan.wantGrid);
     const int threads = smem <= 110 * 1024 ? 512 : 1024;
     cudaError_t e = cudaSuccess;
+    GridGradCoordsKernel<T><<<GridFor(g.n * outPlane, 256), 256, 0, s>>>(grid, rec, g, g.n * outPlane);
+    CountLaunch();
     const int64_t partStride = partials ? g.n * outPlane : 0;
     if (plan.wantGrid && !partials) {
         e = cudaMemsetAsync(ggAcc, 0, static_cast<size_t>(g.n * outPlane) * sizeof(float2), s);
@@ -621,7 +656,7 @@ cudaError_t LaunchStagedBwd(const T* go, const T* x, const T* grid, T* gi, T* gg
                 return;
             }
         }
-        kernel<<<static_cast<unsigned>(g.n * groups), threads, smem, s>>>(go, x, grid, gi, ggAcc, g, groups,
+        kernel<<<static_cast<unsigned>(g.n * groups), threads, smem, s>>>(go, x, rec, gi, ggAcc, g, groups,
                                                                           partStride);
         CountLaunch();
         e = cudaGetLastError();
@@ -661,7 +696,8 @@ GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool w
             g.n * CeilDiv(g.c, cg) < (1LL << 31)) {
             p.stagedGroup = cg;
             p.gridAccBytes = wantGrid ? Align256(static_cast<uint64_t>(g.n) * outPlane * 8) : 0;
-            p.total = p.gridAccBytes;
+            p.recBytes = Align256(static_cast<uint64_t>(g.n) * outPlane * 8);
+            p.total = p.gridAccBytes + p.recBytes;
             return p;
         }
     }
@@ -679,7 +715,8 @@ GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool w
             p.detChunks = static_cast<int32_t>(chunks);
             p.detChunkSamples = static_cast<int32_t>(chunkSamples);
             p.detCursorSmem = inPlane * 4 <= 200 * 1024;
-            // gather with grad_output in shared memory: widest channel vector whose planes fit
+            // gather with grad_output in shared memory: the widest channel vector whose planes fit (every block
+            // reads the whole entry list of its image from L2, so fewer, wider groups win over more resident blocks)
             p.detGatherGroup = 0;
             const int es = DtSize(dt);
             for (int cg = 16 / es; cg * es >= 4 && outPlane < (1ULL << 30); cg /= 2) {
@@ -704,9 +741,10 @@ GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool w
             static_cast<uint64_t>(CeilDiv(g.c, cg)) * g.n * outPlane * 8 <= (1ULL << 30)) {
             p.detGridGroup = cg;
             p.gridAccBytes = Align256(static_cast<uint64_t>(CeilDiv(g.c, cg)) * g.n * outPlane * 8);
+            p.recBytes = Align256(static_cast<uint64_t>(g.n) * outPlane * 8);
         }
     }
-    p.total = p.gridAccBytes + p.accBytes + p.countBytes + p.entryBytes;
+    p.total = p.gridAccBytes + p.accBytes + p.countBytes + p.entryBytes + p.recBytes;
     return p;
 }
 
@@ -719,6 +757,8 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
     const int64_t giElems = g.n * g.c * inPlane;
     cudaError_t e = cudaSuccess;
     char* ws = static_cast<char*>(workspace);
+    // per-sample source coordinates of the staged kernels: always the last piece of the workspace
+    float2* recs = plan.recBytes > 0 ? reinterpret_cast<float2*>(ws + plan.total - plan.recBytes) : nullptr;
 
     if (plan.stagedGroup > 0) {
         OPSCV_DISPATCH_DT(dt, T, {
@@ -730,11 +770,11 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
             float2* ggAcc = reinterpret_cast<float2*>(ws);
             constexpr int kMax = 16 / sizeof(T);
             if (plan.stagedGroup == kMax) {
-                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, ggAcc, g, plan.wantInput, plan.wantGrid, false, s);
+                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, ggAcc, recs, g, plan.wantInput, plan.wantGrid, false, s);
             } else if (plan.stagedGroup == kMax / 2) {
-                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, ggAcc, g, plan.wantInput, plan.wantGrid, false, s);
+                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, ggAcc, recs, g, plan.wantInput, plan.wantGrid, false, s);
             } else {
-                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, ggAcc, g, plan.wantInput, plan.wantGrid, false, s);
+                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, ggAcc, recs, g, plan.wantInput, plan.wantGrid, false, s);
             }
         });
         return e;
@@ -749,11 +789,11 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
             float2* parts = reinterpret_cast<float2*>(ws);
             constexpr int kMax = 16 / sizeof(T);
             if (plan.detGridGroup == kMax) {
-                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, nullptr, pgg, parts, g, false, true, true, s);
+                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, nullptr, pgg, parts, recs, g, false, true, true, s);
             } else if (plan.detGridGroup == kMax / 2) {
-                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, nullptr, pgg, parts, g, false, true, true, s);
+                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, nullptr, pgg, parts, recs, g, false, true, true, s);
             } else {
-                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, nullptr, pgg, parts, g, false, true, true, s);
+                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, nullptr, pgg, parts, recs, g, false, true, true, s);
             }
         });
         return e;
@@ -865,11 +905,11 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
             T* pgg = static_cast<T*>(ggrid);
             constexpr int kMax = 16 / sizeof(T);
             if (plan.detGridGroup == kMax) {
-                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, parts, g, false, true, true, s);
+                e = LaunchStagedBwd<T, kMax>(pgo, px, pg, pgi, pgg, parts, recs, g, false, true, true, s);
             } else if (plan.detGridGroup == kMax / 2) {
-                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, parts, g, false, true, true, s);
+                e = LaunchStagedBwd<T, kMax / 2>(pgo, px, pg, pgi, pgg, parts, recs, g, false, true, true, s);
             } else {
-                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, parts, g, false, true, true, s);
+                e = LaunchStagedBwd<T, kMax / 4>(pgo, px, pg, pgi, pgg, parts, recs, g, false, true, true, s);
             }
             if (e != cudaSuccess) {
                 return e;

@@ -149,6 +149,7 @@ struct GridGradPlan {
     int32_t stagedGroup; // > 0: shared-memory staged kernel with this many channels per block
     int32_t detGridGroup;  // deterministic grad_grid from the staged kernel with per-group partials (0: per-sample kernel)
     uint64_t gridAccBytes; // staged kernel: fp32 (gix, giy) sums per sample (per group and sample with partials)
+    uint64_t recBytes;   // staged kernels: per-sample source coordinates (last piece of the workspace)
     uint64_t accBytes;   // fp32 grad_input accumulator (16-bit dtypes, atomic mode)
     int32_t detChunks, detChunkSamples; // deterministic: chunks of the sample sequence filled in parallel
     bool detCursorSmem;   // deterministic fill: append positions fit shared memory
