@@ -119,6 +119,10 @@ ACLNN_API int32_t opscvVersion(void);
 /* Number of kernel launches this thread has enqueued through second-phase calls since the last reset. */
 ACLNN_API uint64_t opscvGetLaunchCount(void);
 ACLNN_API void opscvResetLaunchCount(void);
+/* Number of bounded device-side waits on asynchronous copies that ran out on the current device since the library
+ * was loaded (a kernel that gives up a wait abandons its block's work and counts here instead of hanging).
+ * 0 in a healthy run; 0xffffffff if the counter cannot be read. Synchronises the device. */
+ACLNN_API uint32_t opscvGetAsyncCopyTimeouts(void);
 
 #ifdef __cplusplus
 }

@@ -50,6 +50,7 @@ SYMBOLS = {
     "opscvVersion": (_I32, []),
     "opscvGetLaunchCount": (_U64, []),
     "opscvResetLaunchCount": (None, []),
+    "opscvGetAsyncCopyTimeouts": (ctypes.c_uint32, []),
     "opscvDebugAxisTable": (_I32, [_I32, _I64, _I64, _I32, _F, _P, _P, _P, ctypes.POINTER(_I32)]),
     "opscvUpsampleBilinear2dNoAlloc": (_I32, [_P, _P, _I32, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _B, _D, _D, _P]),
     "aclnnUpsampleNearest2dGetWorkspaceSize": (_I32, [_P, _P, _P, _PU64, _PP]),

@@ -8,7 +8,7 @@ from . import (ACL_BF16, ACL_DOUBLE, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_NCHW, AC
 
 __all__ = [
     "AclnnError", "acl_tensor", "int_array", "bool_array", "two_phase", "set_deterministic", "set_backward_algo",
-    "launch_count", "reset_launch_count", "last_error", "debug_axis_table", "upsample_nearest2d",
+    "launch_count", "reset_launch_count", "async_copy_timeouts", "last_error", "debug_axis_table", "upsample_nearest2d",
     "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_no_alloc",
     "upsample_bilinear2d_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
@@ -118,6 +118,11 @@ def launch_count():
 
 def reset_launch_count():
     lib().opscvResetLaunchCount()
+
+
+def async_copy_timeouts():
+    """Bounded device-side waits that ran out (0 in a healthy run)."""
+    return lib().opscvGetAsyncCopyTimeouts()
 
 
 def debug_axis_table(kind, in_size, out_size, align=False, user_scale=0.0):

@@ -366,5 +366,6 @@ int32_t opscvGetBackwardAlgo(void) { return g_backwardAlgo; }
 int32_t opscvVersion(void) { return 100; }
 uint64_t opscvGetLaunchCount(void) { return LaunchCount(); }
 void opscvResetLaunchCount(void) { ResetLaunchCount(); }
+uint32_t opscvGetAsyncCopyTimeouts(void) { return AsyncCopyTimeouts(); }
 
 } // extern "C"

@@ -106,6 +106,8 @@ struct AAFwdPlan {
     bool stream;        // streaming down-scale kernel (else one thread per output element)
     bool regWeights;    // horizontal weights of all output columns fit in shared memory
     int32_t metaRows;   // most input rows a band touches (sizes the shared slot-weight records)
+    int32_t cols;       // input columns per thread of the streaming kernel (4 or 8)
+    int32_t ringGroups; // > 0: rows arrive by bulk asynchronous copies into a shared ring of this many 4-row groups
     int32_t threads;    // block size of the streaming kernel
     int32_t bandRows;   // output rows per block
     uint64_t wrowBytes; // workspace for the per-input-row vertical weights
@@ -114,6 +116,9 @@ AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW);
 // rh (ranges of outputs covering each input row) and wrow are only used by the streaming kernel.
 cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh, float* wrow,
                          const AAFwdPlan& plan, cudaStream_t s);
+// Bounded waits on asynchronous copies that ran out since the library was loaded (0 in a healthy run).
+uint32_t AsyncCopyTimeouts();
+
 struct AABwdPlan {
     bool band;         // band-tiled separable kernel (else one thread per grad_input element)
     int32_t threads;   // block size

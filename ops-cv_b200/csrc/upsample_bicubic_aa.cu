@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(kThreads)
 // patterns: one 32-byte record per input row.
 constexpr int kSlots = 6;
 constexpr int kSlotStride = 8;
+constexpr int kFlushBatch = 4;        // output rows per horizontal pass of the streaming forward kernel
 constexpr int kStreamMaxThreads = 256; // up to 255 registers per thread for the accumulator ring and the row queue
 
 __global__ void AARowWeightKernel(AAAxis th, RangeAxis rh, int32_t hin, float* __restrict__ wrow)
@@ -96,23 +97,85 @@ __global__ void AARowWeightKernel(AAAxis th, RangeAxis rh, int32_t hin, float* _
     wrow[static_cast<int64_t>(r) * kSlotStride + 7] = __int_as_float(min(e - s, kSlots));
 }
 
+// ---- bulk asynchronous copies (global -> shared) with mbarrier completion ----------------------------------------
+// Used by the streaming forward kernel to keep whole input rows in flight without holding them in registers.
+// Every wait is bounded: a wait that runs out bumps g_asyncCopyTimeouts (read by AsyncCopyTimeouts()), the block
+// waits (bounded again) for the copies it still has in flight and returns, so the context stays usable.
+__device__ unsigned int g_asyncCopyTimeouts = 0;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void BarrierInit(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void BarrierInitFence()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Arms the barrier for `bytes` of copy traffic and starts one row copy that completes on it. dst, src and bytes are
+// multiples of 16.
+__device__ __forceinline__ void BulkLoadRow(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     SmemAddr(dst)),
+                 "l"(src), "r"(bytes), "r"(SmemAddr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool BarrierWait(uint64_t* bar, uint32_t parity, uint32_t limit)
+{
+    const uint32_t addr = SmemAddr(bar);
+    for (uint32_t it = 0; it < limit; ++it) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(addr), "r"(parity)
+                     : "memory");
+        if (ok) {
+            return true;
+        }
+    }
+    return false;
+}
+
+// The parked rows are skewed by one float per 32 columns: the horizontal pass reads them at a stride of `scale`
+// columns per lane, and without the skew lanes 32 / scale apart would always meet in one bank.
+__host__ __device__ __forceinline__ int32_t Skew(int32_t col) { return col + (col >> 5); }
+__host__ __device__ __forceinline__ int32_t ParkedRowFloats(int32_t win) { return (Skew(win) + 4) & ~3; }
+
 // grid = (planes, bands); a band is `bandRows` output rows. A thread owns VC input columns of every row (one or two
 // 16-byte groups) and keeps one partial sum per open output row (kSlots of them) for each.
 // Shared memory: the vertically filtered row being flushed, the slot-weight rows of the band's input rows, and
 // (wTaps > 0) the horizontal weights of all output columns, transposed.
-template <typename T, int VC, int MAXT>
-__global__ void __launch_bounds__(MAXT)
+// Two ways of bringing the input rows in:
+//   BULK = false: every thread loads its own columns, PF rows ahead, into registers;
+//   BULK = true : thread 0 starts one bulk asynchronous copy per row into a ring of ringGroups * PF row slots in
+//                 shared memory (completion on one mbarrier per slot); the rows of a group of PF are consumed by all
+//                 threads from shared memory, and after a block barrier the group's slots are refilled with the rows
+//                 ringGroups groups ahead. Whole rows are in flight at no register cost.
+template <typename T, int VC, int MAXT, bool BULK>
+__global__ void __launch_bounds__(MAXT, (VC == 4 && !BULK) ? 4 : (BULK ? 1 : 2))
     AAFwdStreamKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t hout,
                       int32_t wout, AAAxis th, AAAxis tw, const float* __restrict__ wrow, int32_t bandRows,
-                      int32_t metaRows, int32_t wTaps)
+                      int32_t metaRows, int32_t wTaps, int32_t ringGroups)
 {
-    constexpr int PF = 4;                  // input rows in flight per thread
+    // input rows in flight per thread / rows per ring group (three keep the 4-column variant within 64 registers)
+    constexpr int PF = (VC == 4 && !BULK) ? 3 : 4;
     constexpr int LV = 16 / sizeof(T);     // elements per 16-byte load
     constexpr int NL = VC / LV;            // 16-byte loads per row
-    extern __shared__ __align__(16) float smemF[];
-    const int32_t winPad = (win + 3) & ~3;
-    float* rowbufs = smemF;                                           // [2][winPad], alternating between flushes
-    float4* msm = reinterpret_cast<float4*>(smemF + 2 * winPad);      // [metaRows][2]
+    extern __shared__ __align__(16) float smemAll[];
+    // BULK: the ring comes first (16-byte aligned slots of one row each), then the slot barriers
+    const uint32_t rowBytes = static_cast<uint32_t>(win) * sizeof(T);
+    const int32_t ringSlots = BULK ? ringGroups * PF : 0;
+    unsigned char* ring = reinterpret_cast<unsigned char*>(smemAll);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(ringSlots) * rowBytes);
+    float* smemF = reinterpret_cast<float*>(bars + ((ringSlots + 1) & ~1));
+    const int32_t winPad = ParkedRowFloats(win);
+    float* rowbufs = smemF;                                           // [kFlushBatch][winPad]
+    float4* msm = reinterpret_cast<float4*>(smemF + kFlushBatch * winPad); // [metaRows][2]
     float* wsm = reinterpret_cast<float*>(msm + 2 * metaRows);        // [wTaps][wout]
     const int64_t p = blockIdx.x;
     const int32_t i0 = blockIdx.y * bandRows, i1 = min(hout, i0 + bandRows);
@@ -143,37 +206,57 @@ __global__ void __launch_bounds__(MAXT)
             acc[a][k] = 0.0f;
         }
     }
-    // Emits output row i from the oldest accumulator slot: vertical result -> shared row -> horizontal filter.
-    // The shared row alternates between two buffers, so one barrier per flush is enough: a thread can only write
-    // buffer b again after passing the barrier of the flush in between, which every thread reaches after it has
-    // finished reading b.
-    int32_t flip = 0;
+    // Completed output rows (vertical results, taken from the oldest accumulator slot) are parked in shared memory,
+    // kFlushBatch rows at a time, and the horizontal filter then runs over the whole batch: a thread takes one
+    // output column of all the batch's rows, so every weight is loaded once per batch and the rows give
+    // independent accumulation chains. Output rows complete in increasing order, so a batch is rows
+    // batchRow0 .. batchRow0 + pending - 1.
+    int32_t pending = 0, batchRow0 = 0;
+    auto runBatch = [&]() {
+        __syncthreads(); // the batch's rows are written
+        for (int32_t j = threadIdx.x; j < wout; j += blockDim.x) {
+            const int32_t m = __ldg(tw.xmin + j), n = __ldg(tw.xsize + j);
+            const float* wj = tw.w + static_cast<int64_t>(j) * tw.taps;
+            float v[kFlushBatch];
+#pragma unroll
+            for (int bb = 0; bb < kFlushBatch; ++bb) {
+                v[bb] = 0.0f;
+            }
+            for (int32_t t = 0; t < n; ++t) {
+                const float w = wTaps > 0 ? wsm[t * wout + j] : __ldg(wj + t);
+#pragma unroll
+                for (int bb = 0; bb < kFlushBatch; ++bb) { // rows past `pending` hold stale values; not stored
+                    v[bb] = fmaf(w, rowbufs[bb * winPad + Skew(m + t)], v[bb]);
+                }
+            }
+#pragma unroll
+            for (int bb = 0; bb < kFlushBatch; ++bb) {
+                if (bb < pending) {
+                    yp[static_cast<int64_t>(batchRow0 + bb) * wout + j] = DType<T>::FromF(v[bb]);
+                }
+            }
+        }
+        __syncthreads(); // the rows have been read: the buffer can take the next batch
+        pending = 0;
+    };
     auto flush = [&](int32_t i) {
-        float* rowbuf = rowbufs + flip * winPad;
-        flip ^= 1;
+        if (pending == 0) {
+            batchRow0 = i;
+        }
+        float* rowbuf = rowbufs + pending * winPad;
 #pragma unroll
         for (int k = 0; k < VC; k += 4) {
             const int32_t col = (k / LV) * groupSpan + c + k % LV;
-            if (col < win) {
-                *reinterpret_cast<float4*>(rowbuf + col) =
-                    make_float4(acc[0][k], acc[0][k + 1], acc[0][k + 2], acc[0][k + 3]);
+            if (col < win) { // four scalar stores: under the skew they are conflict-free across the warp
+                const int32_t sc = Skew(col); // col is a multiple of 4: its four columns share one skew
+                rowbuf[sc] = acc[0][k];
+                rowbuf[sc + 1] = acc[0][k + 1];
+                rowbuf[sc + 2] = acc[0][k + 2];
+                rowbuf[sc + 3] = acc[0][k + 3];
             }
         }
-        __syncthreads();
-        for (int32_t j = threadIdx.x; j < wout; j += blockDim.x) {
-            const int32_t m = __ldg(tw.xmin + j), n = __ldg(tw.xsize + j);
-            float v = 0.0f;
-            if (wTaps > 0) {
-                for (int32_t t = 0; t < n; ++t) {
-                    v = fmaf(wsm[t * wout + j], rowbuf[m + t], v);
-                }
-            } else {
-                const float* wj = tw.w + static_cast<int64_t>(j) * tw.taps;
-                for (int32_t t = 0; t < n; ++t) {
-                    v = fmaf(__ldg(wj + t), rowbuf[m + t], v);
-                }
-            }
-            yp[static_cast<int64_t>(i) * wout + j] = DType<T>::FromF(v);
+        if (++pending == kFlushBatch) {
+            runBatch();
         }
     };
     auto shift = [&]() {
@@ -190,10 +273,11 @@ __global__ void __launch_bounds__(MAXT)
         }
     };
     // Input rows are fetched PF rows ahead into fixed registers (the row loop is unrolled by PF; rotating a queue
-    // through moves would make every iteration wait for the newest load).
+    // through moves would make every iteration wait for the newest load), or ringGroups groups ahead into the ring.
     using Vec = Pack<T, LV>;
     Vec q[PF][NL];
-    const T* xnext = x + (p * hin + rlo) * static_cast<int64_t>(win) + c; // next row to fetch
+    const T* xrows = x + (p * hin + rlo) * static_cast<int64_t>(win); // row rlo of this plane
+    const T* xnext = xrows + c;                                       // next row to fetch (register path)
     int32_t rnext = rlo;
     auto fetch = [&](Vec (&dst)[NL]) {
         if (rnext < rhi) {
@@ -207,12 +291,67 @@ __global__ void __launch_bounds__(MAXT)
         xnext += win;
         ++rnext;
     };
+    // BULK: thread 0 starts the copies of group `grp` (rows rlo + grp * PF ..) into the group's slots
+    auto issueGroup = [&](int32_t grp) {
+        const int32_t slot0 = (grp % ringGroups) * PF;
 #pragma unroll
-    for (int f = 0; f < PF; ++f) {
-        fetch(q[f]);
+        for (int f = 0; f < PF; ++f) {
+            const int32_t rr = grp * PF + f; // row index relative to rlo
+            if (rlo + rr < rhi) {
+                BulkLoadRow(ring + static_cast<size_t>(slot0 + f) * rowBytes, xrows + static_cast<int64_t>(rr) * win,
+                            rowBytes, bars + slot0 + f);
+            }
+        }
+    };
+    if (BULK) {
+        if (threadIdx.x == 0) {
+            for (int32_t sl = 0; sl < ringSlots; ++sl) {
+                BarrierInit(bars + sl, 1);
+            }
+            BarrierInitFence();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int32_t grp = 0; grp < ringGroups; ++grp) {
+                issueGroup(grp);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int f = 0; f < PF; ++f) {
+            fetch(q[f]);
+        }
     }
     int32_t curStart = __float_as_int(msm[1].z);
     for (int32_t r0 = rlo; r0 < rhi; r0 += PF) {
+        const int32_t grp = (r0 - rlo) / PF;
+        const int32_t slot0 = BULK ? (grp % ringGroups) * PF : 0;
+        if (BULK) {
+            // wait for the rows of this group; the outcome is made uniform so that the block leaves together
+            const uint32_t parity = static_cast<uint32_t>(grp / ringGroups) & 1u;
+            bool ok = true;
+#pragma unroll
+            for (int f = 0; f < PF; ++f) {
+                if (r0 + f < rhi) {
+                    ok = BarrierWait(bars + slot0 + f, parity, kWaitLimit) && ok;
+                }
+            }
+            if (__syncthreads_or(!ok)) {
+                if (threadIdx.x == 0) {
+                    atomicAdd(&g_asyncCopyTimeouts, 1u);
+                    // copies still in flight target this block's shared memory: give them a bounded chance to land
+                    for (int32_t g2 = grp; g2 < grp + ringGroups; ++g2) {
+                        for (int f = 0; f < PF; ++f) {
+                            if (rlo + g2 * PF + f < rhi) {
+                                BarrierWait(bars + (g2 % ringGroups) * PF + f,
+                                            static_cast<uint32_t>(g2 / ringGroups) & 1u, 1u << 16);
+                            }
+                        }
+                    }
+                }
+                return;
+            }
+        }
 #pragma unroll
         for (int f = 0; f < PF; ++f) {
             const int32_t r = r0 + f;
@@ -228,9 +367,24 @@ __global__ void __launch_bounds__(MAXT)
                 }
                 const float w[kSlots] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y};
                 float xv[VC];
+                if (BULK) {
+                    const T* srow = reinterpret_cast<const T*>(ring + static_cast<size_t>(slot0 + f) * rowBytes);
 #pragma unroll
-                for (int k = 0; k < VC; ++k) {
-                    xv[k] = DType<T>::ToF(q[f][k / LV].v[k % LV]);
+                    for (int l = 0; l < NL; ++l) {
+                        Vec v{};
+                        if (l * groupSpan + c < win) {
+                            v = *reinterpret_cast<const Vec*>(srow + l * groupSpan + c);
+                        }
+#pragma unroll
+                        for (int k = 0; k < LV; ++k) {
+                            xv[l * LV + k] = DType<T>::ToF(v.v[k]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < VC; ++k) {
+                        xv[k] = DType<T>::ToF(q[f][k / LV].v[k % LV]);
+                    }
                 }
 #pragma unroll
                 for (int a = 0; a < kSlots; ++a) {
@@ -241,7 +395,15 @@ __global__ void __launch_bounds__(MAXT)
                         }
                     }
                 }
-                fetch(q[f]);
+                if (!BULK) {
+                    fetch(q[f]);
+                }
+            }
+        }
+        if (BULK) {
+            __syncthreads(); // every thread has read the group's slots: they can be refilled
+            if (threadIdx.x == 0 && rlo + (grp + ringGroups) * PF < rhi) {
+                issueGroup(grp + ringGroups);
             }
         }
     }
@@ -252,6 +414,9 @@ __global__ void __launch_bounds__(MAXT)
         }
         shift();
         ++curStart;
+    }
+    if (pending > 0) {
+        runBatch();
     }
 }
 
@@ -434,12 +599,16 @@ AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW)
     if (!plan.stream) {
         return plan;
     }
-    const int32_t threads = std::max(64, static_cast<int32_t>((CeilDiv(sh.win, 8) + 31) & ~31));
+    // fp32 rows of up to 1024 columns: four columns per thread (twice the warps of the 8-column variant at the same
+    // number of resident blocks measured ~8 % faster); 16-bit rows and longer rows: eight columns (one or two
+    // 16-byte loads per thread and row).
+    plan.cols = (es == 4 && sh.win <= 4 * kStreamMaxThreads) ? 4 : 8;
+    const int32_t threads = std::max(64, static_cast<int32_t>((CeilDiv(sh.win, plan.cols) + 31) & ~31));
     plan.threads = std::min(kStreamMaxThreads, threads);
     // Bands: pick the number of bands per plane whose block count fills whole waves of resident blocks best
     // (every band re-reads the input rows of its first window, so no more than 8, and at least 16 rows each).
     const int64_t planes = std::max<int64_t>(sh.n * sh.c, 1);
-    const int64_t resident = static_cast<int64_t>(NumSMs()) * std::max(1, 512 / plan.threads);
+    const int64_t resident = static_cast<int64_t>(NumSMs()) * (plan.cols == 4 ? 4 : std::max(1, 512 / plan.threads));
     int64_t bestBands = 1;
     double bestEff = 0.0;
     for (int64_t b = 1; b <= 8 && sh.hout / b >= 16; ++b) {
@@ -456,13 +625,34 @@ AAFwdPlan MakeAAFwdPlan(Dt dt, Shape4 sh, float scaleH, int32_t tapsW)
         std::min<double>(sh.hin, std::ceil(static_cast<double>(plan.bandRows) * scaleH + 4.0 * scaleH + 4.0)));
     // horizontal weights in shared memory if they fit beside the row buffer and the slot records
     const size_t wBytes = static_cast<size_t>(tapsW) * sh.wout * sizeof(float);
-    const size_t rest = (2 * static_cast<size_t>(sh.win) + static_cast<size_t>(plan.metaRows) * 8 + 8) * sizeof(float);
+    const size_t rest = (kFlushBatch * static_cast<size_t>(ParkedRowFloats(sh.win)) + static_cast<size_t>(plan.metaRows) * 8 + 8) * sizeof(float);
     plan.regWeights = wBytes + rest <= 96 * 1024;
     if (rest > 96 * 1024) {
         plan.stream = false;
     }
     plan.wrowBytes = static_cast<uint64_t>(sh.hin) * kSlotStride * sizeof(float);
+    // The bulk-copy row ring is off by default: on B200 it measured 15-25 % slower than register prefetch for this
+    // kernel (the limiter is the shared-memory data pipe of the horizontal pass, not load latency, and the ring adds
+    // shared-memory traffic and two block barriers per four rows). OPSCV_AA_RING=<groups> (2..4) selects it.
+    plan.ringGroups = 0;
+    if (const char* o = getenv("OPSCV_AA_RING")) {
+        const int groups = atoi(o);
+        const size_t ring = static_cast<size_t>(groups) * 4 * sh.win * es + 64;
+        const size_t used = rest + (plan.regWeights ? wBytes : 0);
+        if (groups >= 2 && groups <= 4 && used + ring <= 200 * 1024) {
+            plan.ringGroups = groups;
+        }
+    }
     return plan;
+}
+
+uint32_t AsyncCopyTimeouts()
+{
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_asyncCopyTimeouts, sizeof(v)) != cudaSuccess) {
+        return 0xffffffffu;
+    }
+    return v;
 }
 
 cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AAAxis tw, RangeAxis rh,
@@ -474,19 +664,38 @@ cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AA
         AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.hin, 128)), 128, 0, s>>>(th, rh, sh.hin, wrow);
         const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(CeilDiv(sh.hout, plan.bandRows)));
         const int32_t wTaps = plan.regWeights ? tw.taps : 0;
-        const size_t smem = (2 * static_cast<size_t>((sh.win + 3) & ~3) + static_cast<size_t>(plan.metaRows) * 8 +
+        const size_t base = (kFlushBatch * static_cast<size_t>(ParkedRowFloats(sh.win)) + static_cast<size_t>(plan.metaRows) * 8 +
                              static_cast<size_t>(wTaps) * sh.wout) * sizeof(float);
         cudaError_t e = cudaSuccess;
         OPSCV_DISPATCH_DT(dt, T, {
             const T* px = static_cast<const T*>(x);
             T* py = static_cast<T*>(y);
-            auto kernel = AAFwdStreamKernel<T, 8, kStreamMaxThreads>;
-            if (smem > 48 * 1024) {
-                e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-            }
-            if (e == cudaSuccess) {
-                kernel<<<grid, plan.threads, smem, s>>>(px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, wrow,
-                                                        plan.bandRows, plan.metaRows, wTaps);
+            const int32_t slots = plan.ringGroups * 4;
+            const size_t smem = base + (plan.ringGroups > 0 ? static_cast<size_t>(slots) * sh.win * sizeof(T) +
+                                                                  static_cast<size_t>((slots + 1) & ~1) * 8
+                                                            : 0);
+            auto launch = [&](auto kernel) {
+                if (smem > 48 * 1024) {
+                    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+                }
+                if (e == cudaSuccess) {
+                    kernel<<<grid, plan.threads, smem, s>>>(px, py, sh.hin, sh.win, sh.hout, sh.wout, th, tw, wrow,
+                                                            plan.bandRows, plan.metaRows, wTaps, plan.ringGroups);
+                }
+            };
+            if (plan.cols == 4) {
+                if constexpr (sizeof(T) == 4) {
+                    if (plan.ringGroups > 0) {
+                        launch(AAFwdStreamKernel<T, 4, kStreamMaxThreads, true>);
+                    } else {
+                        launch(AAFwdStreamKernel<T, 4, kStreamMaxThreads, false>);
+                    }
+                }
+            } else if (plan.ringGroups > 0) {
+                launch(AAFwdStreamKernel<T, 8, kStreamMaxThreads, true>);
+            } else {
+                launch(AAFwdStreamKernel<T, 8, kStreamMaxThreads, false>);
             }
         });
         CountLaunch(2);

@@ -488,3 +488,26 @@ def test_second_phase_consumes_executor(ops, dev):
     assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(buf.data_ptr()), ws.value, ex, stream) == 161002
     torch.cuda.synchronize()
     assert torch.equal(y.cpu(), x.cpu().repeat_interleave(2, 2).repeat_interleave(2, 3))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_bicubic_aa_forward_bulk_copy_ring(ops, oracle, dev, dtype, monkeypatch):
+    """The streaming forward kernel fed by bulk asynchronous copies into a shared-memory row ring (off by default,
+    selected by OPSCV_AA_RING) gives the same result as the register-prefetch variant and the oracle."""
+    x, x32 = quant(torch.rand((3, 2, 150, 96), generator=gen(60)), dtype)
+    ref = oracle.bicubic_aa_fwd(x32, (33, 40), False)
+    base = ops.upsample_bicubic2d_aa(x.to(dev), (33, 40), False)
+    monkeypatch.setenv("OPSCV_AA_RING", "2")
+    ring = ops.upsample_bicubic2d_aa(x.to(dev), (33, 40), False)
+    monkeypatch.delenv("OPSCV_AA_RING")
+    check(base, ref, dtype, atol=2e-6)
+    check(ring, ref, dtype, atol=2e-6)
+    assert torch.equal(base.view(torch.int32 if dtype == torch.float32 else torch.int16),
+                       ring.view(torch.int32 if dtype == torch.float32 else torch.int16))
+    assert ops.async_copy_timeouts() == 0
+
+
+def test_no_device_wait_ran_out(ops, dev):
+    """Collected after the operator tests of this file: none of the bounded waits on asynchronous copies gave up."""
+    torch.cuda.synchronize(dev)
+    assert ops.async_copy_timeouts() == 0
