@@ -479,10 +479,14 @@ __global__ void __launch_bounds__(1024)
                     const float* __restrict__ wrowW, int32_t bandRows, int32_t stageRows)
 {
     extern __shared__ __align__(16) float smemF[];
-    float* gos = smemF;                                        // [stageRows][wout] grads rows of the band
-    float* tbuf = smemF + static_cast<int64_t>(stageRows) * wout; // [kBwdRows][wout]
+    float4* msm = reinterpret_cast<float4*>(smemF);            // [bandRows][2] vertical slot records of the band's rows
+    float* gos = smemF + static_cast<int64_t>(bandRows) * 8;   // [stageRows][wout] grads rows of the band
+    float* tbuf = gos + static_cast<int64_t>(stageRows) * wout; // [kBwdRows][wout]
     const int64_t p = blockIdx.x;
     const int32_t y0 = blockIdx.y * bandRows, y1 = min(hin, y0 + bandRows);
+    for (int32_t e = threadIdx.x; e < 2 * (y1 - y0); e += blockDim.x) {
+        msm[e] = __ldg(reinterpret_cast<const float4*>(wrowH) + static_cast<int64_t>(y0) * 2 + e);
+    }
     const int32_t i0 = __ldg(rh.start + y0);
     const int32_t i1 = min(max(i0, __ldg(rh.end + y1 - 1)), i0 + stageRows);
     const T* gp = go + (p * hout + i0) * static_cast<int64_t>(wout);
@@ -512,19 +516,27 @@ __global__ void __launch_bounds__(1024)
     __syncthreads();
     T* op = gi + p * hin * static_cast<int64_t>(win);
     for (int32_t yb = y0; yb < y1; yb += kBwdRows) {
-        // vertical: one (row, grads column) item per thread
-        for (int32_t item = threadIdx.x; item < kBwdRows * wout; item += blockDim.x) {
-            const int32_t ry = item / wout, j = item - ry * wout;
-            const int32_t y = yb + ry;
-            float v = 0.0f;
-            if (y < y1) {
-                const int32_t s = __ldg(rh.start + y), cnt = __ldg(rh.end + y) - s;
-                const float* wy = wrowH + static_cast<int64_t>(y) * kSlotStride;
-                for (int32_t a = 0; a < cnt && a < kSlots; ++a) {
-                    v = fmaf(__ldg(wy + a), gos[(s + a - i0) * wout + j], v);
+        // vertical: a thread takes one grads column for the kBwdRows rows of the step; the rows' slot records
+        // (weights, first grads row, count) are block-uniform shared-memory reads
+        for (int32_t j = threadIdx.x; j < wout; j += blockDim.x) {
+#pragma unroll
+            for (int ry = 0; ry < kBwdRows; ++ry) {
+                const int32_t y = yb + ry;
+                float v = 0.0f;
+                if (y < y1) {
+                    const float4 m0 = msm[2 * (y - y0)], m1 = msm[2 * (y - y0) + 1];
+                    const int32_t s = __float_as_int(m1.z), cnt = __float_as_int(m1.w);
+                    const float w[kSlots] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y};
+                    const float* gcol = gos + (s - i0) * wout + j;
+#pragma unroll
+                    for (int a = 0; a < kSlots; ++a) {
+                        if (a < cnt && s + a < i1) { // slots past the run (or past the staged rows) are not read
+                            v = fmaf(w[a], gcol[a * wout], v);
+                        }
+                    }
                 }
+                tbuf[ry * wout + j] = v;
             }
-            tbuf[item] = v;
         }
         __syncthreads();
         if (hasCols) {
@@ -710,6 +722,12 @@ cudaError_t BicubicAAFwd(Dt dt, const void* x, void* y, Shape4 sh, AAAxis th, AA
     return cudaGetLastError();
 }
 
+// Shared memory of one block of the band kernel: slot records of the band's rows, staged grads rows, step buffer.
+static size_t AABwdSmem(int32_t bandRows, int32_t stageRows, int32_t wout)
+{
+    return (static_cast<size_t>(bandRows) * 8 + (static_cast<size_t>(stageRows) + kBwdRows) * wout) * sizeof(float);
+}
+
 AABwdPlan MakeAABwdPlan(Dt dt, Shape4 sh, float scaleH, float scaleW)
 {
     AABwdPlan plan{};
@@ -720,22 +738,36 @@ AABwdPlan MakeAABwdPlan(Dt dt, Shape4 sh, float scaleH, float scaleW)
         return plan;
     }
     plan.threads = std::min(1024, std::max(128, static_cast<int32_t>((CeilDiv(sh.win, 4) + 31) & ~31)));
-    // Band height: as tall as the shared-memory stage allows (fewer re-read halo rows), but enough blocks.
+    // Bands per plane: the split whose blocks fill whole waves of resident blocks best (up to four 256-thread
+    // blocks per SM, fewer if the staged grads rows need more shared memory). t grad_input rows are fed by at most
+    // t / scale + kSlots + 2 grads rows.
     const int64_t planes = std::max<int64_t>(sh.n * sh.c, 1);
-    const int64_t budgetFloats = (64 * 1024) / 4 - static_cast<int64_t>(kBwdRows) * sh.wout;
-    const int32_t maxStageRows = static_cast<int32_t>(std::min<int64_t>(budgetFloats / std::max(sh.wout, 1), sh.hout));
-    if (maxStageRows < kSlots + 2) {
+    double bestScore = 0.0;
+    for (int32_t b = 1; b <= 64 && (b == 1 || sh.hin / b >= 4 * kBwdRows); ++b) {
+        int32_t band = static_cast<int32_t>(CeilDiv(sh.hin, b));
+        band = (band + kBwdRows - 1) / kBwdRows * kBwdRows;
+        const int32_t stage = static_cast<int32_t>(
+            std::min<int64_t>(static_cast<int64_t>(band / static_cast<double>(scaleH)) + kSlots + 2, sh.hout));
+        const size_t smem = AABwdSmem(band, stage, sh.wout);
+        if (smem > 200 * 1024) {
+            continue;
+        }
+        const int64_t perSm = std::min<int64_t>({4, 2048 / plan.threads, static_cast<int64_t>((225 * 1024) / (smem + 1024))});
+        const int64_t slots = static_cast<int64_t>(NumSMs()) * std::max<int64_t>(perSm, 1);
+        const int64_t blocks = planes * CeilDiv(sh.hin, band);
+        // waves filled, times the residency reached, with a slight preference for fewer (taller) bands
+        const double score = static_cast<double>(blocks) / (static_cast<double>(CeilDiv(blocks, slots)) * slots) *
+                             (0.5 + 0.125 * static_cast<double>(perSm)) - 0.001 * b;
+        if (score > bestScore) {
+            bestScore = score;
+            plan.bandRows = band;
+            plan.stageRows = stage;
+        }
+    }
+    if (bestScore <= 0.0) {
         plan.band = false;
         return plan;
     }
-    // t grad_input rows are fed by at most t / scale + kSlots grads rows
-    int32_t band = static_cast<int32_t>(std::min<double>((maxStageRows - kSlots - 1) * static_cast<double>(scaleH), sh.hin));
-    const int64_t wantBlocks = static_cast<int64_t>(NumSMs()) * 4;
-    band = static_cast<int32_t>(std::max<int64_t>(kBwdRows, std::min<int64_t>(band, CeilDiv(sh.hin * planes, wantBlocks))));
-    band = (band + kBwdRows - 1) / kBwdRows * kBwdRows;
-    plan.bandRows = band;
-    plan.stageRows = static_cast<int32_t>(std::min<int64_t>(static_cast<int64_t>(band / static_cast<double>(scaleH)) + kSlots + 2,
-                                                          sh.hout));
     plan.wrowBytesH = static_cast<uint64_t>(sh.hin) * kSlotStride * sizeof(float);
     plan.wrowBytesW = static_cast<uint64_t>(sh.win) * kSlotStride * sizeof(float);
     return plan;
@@ -750,7 +782,7 @@ cudaError_t BicubicAABwdGather(Dt dt, const void* go, void* gi, Shape4 sh, AAAxi
         AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.hin, 128)), 128, 0, s>>>(th, rh, sh.hin, wrowH);
         AARowWeightKernel<<<static_cast<unsigned>(CeilDiv(sh.win, 128)), 128, 0, s>>>(tw, rw, sh.win, wrowW);
         const dim3 grid(static_cast<unsigned>(planes), static_cast<unsigned>(CeilDiv(sh.hin, plan.bandRows)));
-        const size_t smem = (static_cast<size_t>(plan.stageRows) + kBwdRows) * sh.wout * sizeof(float);
+        const size_t smem = AABwdSmem(plan.bandRows, plan.stageRows, sh.wout);
         cudaError_t e = cudaSuccess;
         OPSCV_DISPATCH_DT(dt, T, {
             if (smem > 48 * 1024) {
