@@ -83,7 +83,7 @@ cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Nea
 cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, RangeAxis th, RangeAxis tw,
                        const NearestPlan& plan, cudaStream_t s);
 struct BilinearPlan {
-    enum Schedule : int32_t { kDirect = 0, kTiled = 1, kW2 = 2 };
+    enum Schedule : int32_t { kDirect = 0, kTiled = 1, kW2 = 2, kX2 = 3 }; // kX2: backward, 2x on both axes
     int32_t schedule;
     int32_t tileRows; // kTiled: output (forward) / grad_input (backward) rows per block
     int32_t bandRows; // kTiled: most rows of the other tensor any tile reads

@@ -514,6 +514,214 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// ---- backward, NCHW, grads = 2 x grad_input on both axes, input-major ---------------------------------------------
+// The host has verified the pattern on both axes: grad_input row y is fed by grads rows 2y-1 .. 2y+2 (clipped to the
+// plane; row 1 also by row 0, see below), and the same for columns. A thread owns four grad_input columns and walks
+// down the grad_input rows of its tile. It keeps the horizontally reduced grads rows of the current window in
+// registers, so every grads row is reduced once per tile.
+// The grads rows a thread consumes form a plain stream (rows 2*ya-2, 2*ya-1, ...). The thread copies its own piece of
+// each row (its eight columns plus one neighbour on each side) with cp.async into a private shared-memory queue
+// kX2Depth rows ahead: the walk is a serial chain per thread, so what bounds it is the number of bytes in flight,
+// and a queue in shared memory holds several times what the registers could.
+// The vertical weights of a tile's rows (five taps: grads rows 2y-2 .. 2y+2, with a mask of the taps that lie in the
+// row's range) are evaluated once per block into shared memory.
+// Tap 2y-2 exists because grads row 0 is clamped to input row 0 with weight 0 for its upper neighbour, and the
+// reference still adds that zero-weight product to row 1; keeping it preserves NaN / Inf propagation.
+constexpr int kX2Depth = 6;
+
+__device__ __forceinline__ void CpAsync16(void* smem, const void* gmem)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+                 "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void CpAsync4(void* smem, const void* gmem)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+                 "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void CpAsyncWait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+inline size_t X2SmemBytes(int32_t tileRows, int32_t threads, int elemSize)
+{
+    const size_t taps = (static_cast<size_t>(tileRows) * 6 * sizeof(float) + 15) & ~static_cast<size_t>(15);
+    return taps + static_cast<size_t>(kX2Depth) * threads * (8 * elemSize + 8);
+}
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(kThreads, 3)
+    BilinearBwdX2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
+                        LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows)
+{
+    constexpr int V = 4, VG = 8;
+    constexpr int NM = VG * sizeof(TIn) / 16; // 16-byte vectors holding grads columns j0 .. j0+7
+    constexpr int HE = 4 / sizeof(TIn);       // elements in a 4-byte neighbour word
+    extern __shared__ __align__(16) unsigned char x2Smem[];
+    float* rowTaps = reinterpret_cast<float*>(x2Smem); // [tileRows][6]: five weights and the tap mask
+    const int32_t wout = 2 * win, hout = 2 * hin;
+    const int32_t ya = blockIdx.y * tileRows, yb = min(hin, ya + tileRows);
+    const int32_t tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
+    // queue: [kX2Depth][nthreads] 16-byte vectors (NM per entry), then the left and right neighbour words
+    uint4* qMid = reinterpret_cast<uint4*>(x2Smem + ((static_cast<size_t>(tileRows) * 6 * sizeof(float) + 15) & ~size_t(15)));
+    uint32_t* qLeft = reinterpret_cast<uint32_t*>(qMid + static_cast<size_t>(kX2Depth) * nthreads * NM);
+    uint32_t* qRight = qLeft + static_cast<size_t>(kX2Depth) * nthreads;
+    for (int32_t e = tid; e < (yb - ya) * 5; e += nthreads) {
+        const int32_t r = e / 5, t = e - r * 5, y = ya + r;
+        const int32_t i = 2 * y - 2 + t;
+        const bool in = i >= __ldg(rh.start + y) && i < __ldg(rh.end + y);
+        rowTaps[r * 6 + t] = in ? CombinedWeight(th, i, y) : 0.0f;
+    }
+    for (int32_t r = tid; r < yb - ya; r += nthreads) {
+        const int32_t y = ya + r;
+        int32_t mask = 0;
+        for (int t = 0; t < 5; ++t) {
+            const int32_t i = 2 * y - 2 + t;
+            mask |= (i >= __ldg(rh.start + y) && i < __ldg(rh.end + y)) ? (1 << t) : 0;
+        }
+        rowTaps[r * 6 + 5] = __int_as_float(mask);
+    }
+    __syncthreads();
+    const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.y + threadIdx.y;
+    if (p >= planes) {
+        return;
+    }
+    const int32_t groups = win / V;
+    const TIn* gp = go + p * hout * static_cast<int64_t>(wout);
+    TOut* op = gi + p * hin * static_cast<int64_t>(win);
+    for (int32_t g = threadIdx.x; g < groups; g += blockDim.x) {
+        const int32_t x0 = g * V, j0 = 2 * x0;
+        const bool hasLeft = j0 > 0, hasRight = j0 + VG < wout;
+        // wx[k][t]: weight of grads column 2*(x0+k) - 1 + t for grad_input column x0+k (0 outside the row)
+        float wx[V][4];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int32_t j = j0 + 2 * k - 1 + t;
+                wx[k][t] = (j >= 0 && j < wout) ? CombinedWeight(tw, j, x0 + k) : 0.0f;
+            }
+        }
+        const bool extra = x0 == 0 && win > 1; // column 1 also takes grads column 0 (zero weight), as for rows
+        const float wExtra = extra ? CombinedWeight(tw, 0, 1) : 0.0f;
+        // stream of grads rows: element n of the stream is row first + n, for n < count
+        const int32_t first = 2 * ya - 2, count = 2 * (yb - ya) + 3;
+        auto issue = [&](int32_t n) { // one commit group per stream element, empty for rows outside the plane
+            const int32_t i = first + n;
+            if (n < count && i >= 0 && i < hout) {
+                const int32_t slot = (n % kX2Depth) * nthreads + tid;
+                const TIn* row = gp + static_cast<int64_t>(i) * wout + j0;
+#pragma unroll
+                for (int m = 0; m < NM; ++m) {
+                    CpAsync16(qMid + static_cast<size_t>(slot) * NM + m, reinterpret_cast<const uint4*>(row) + m);
+                }
+                if (hasLeft) { // the word holding column j0-1 (4-byte aligned: j0 is a multiple of 8)
+                    CpAsync4(qLeft + slot, row - HE);
+                }
+                if (hasRight) {
+                    CpAsync4(qRight + slot, row + VG);
+                }
+            }
+            CpAsyncCommit();
+        };
+        // Reduced row n of the stream (zeros outside the plane). Waits until all but the newest kX2Depth-1 groups
+        // have landed, i.e. until element n has, then refills the slot with element n + kX2Depth.
+        auto take = [&](int32_t n, float (&hp)[V]) {
+            CpAsyncWait<kX2Depth - 1>();
+            const int32_t i = first + n;
+            float v[VG + 2]; // grads columns j0-1 .. j0+8
+#pragma unroll
+            for (int k = 0; k < VG + 2; ++k) {
+                v[k] = 0.0f;
+            }
+            if (i >= 0 && i < hout) {
+                const int32_t slot = (n % kX2Depth) * nthreads + tid;
+                uint4 mid[NM];
+#pragma unroll
+                for (int m = 0; m < NM; ++m) {
+                    mid[m] = qMid[static_cast<size_t>(slot) * NM + m];
+                }
+                const TIn* me = reinterpret_cast<const TIn*>(mid);
+#pragma unroll
+                for (int k = 0; k < VG; ++k) {
+                    v[k + 1] = DType<TIn>::ToF(me[k]);
+                }
+                if (hasLeft) {
+                    const uint32_t wl = qLeft[slot];
+                    v[0] = DType<TIn>::ToF(reinterpret_cast<const TIn*>(&wl)[HE - 1]);
+                }
+                if (hasRight) {
+                    const uint32_t wr = qRight[slot];
+                    v[VG + 1] = DType<TIn>::ToF(reinterpret_cast<const TIn*>(&wr)[0]);
+                }
+            }
+            issue(n + kX2Depth);
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                float a = 0.0f;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    a = fmaf(wx[k][t], v[2 * k + t], a);
+                }
+                hp[k] = a;
+            }
+            if (extra) {
+                hp[1] = fmaf(wExtra, v[1], hp[1]);
+            }
+        };
+#pragma unroll
+        for (int n = 0; n < kX2Depth; ++n) {
+            issue(n);
+        }
+        // window of reduced rows: P = 2y-2, A = 2y-1, B = 2y, C = 2y+1, D = 2y+2 (rows outside the plane are 0
+        // and their taps are masked off)
+        float hpP[V], hpA[V], hpB[V], hpC[V], hpD[V];
+        take(0, hpP);
+        take(1, hpA);
+        take(2, hpB);
+        int32_t n = 3;
+        TOut* dst = op + static_cast<int64_t>(ya) * win + x0;
+        for (int32_t y = ya; y < yb; ++y) {
+            take(n, hpC);
+            take(n + 1, hpD);
+            n += 2;
+            const float* tp = rowTaps + (y - ya) * 6;
+            const int32_t mask = __float_as_int(tp[5]);
+            float out[V] = {0.0f, 0.0f, 0.0f, 0.0f};
+            auto tap = [&](int t, const float (&hp)[V]) {
+                if (mask & (1 << t)) { // uniform over the block; taps outside the row's range are not touched
+                    const float w = tp[t];
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        out[k] = fmaf(w, hp[k], out[k]);
+                    }
+                }
+            };
+            tap(0, hpP);
+            tap(1, hpA);
+            tap(2, hpB);
+            tap(3, hpC);
+            tap(4, hpD);
+            StorePack<TOut, V>(dst, out);
+            dst += win;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                hpP[k] = hpB[k];
+                hpA[k] = hpC[k];
+                hpB[k] = hpD[k];
+            }
+        }
+        CpAsyncWait<0>(); // nothing of this thread's queue is in flight when the next column group reuses it
+    }
+}
+
 // ---- forward, NHWC ----------------------------------------------------------------------------------------
 // A thread owns one vector of V channels of one output column (n, w) and walks down the output rows [h0, h1) of a
 // row chunk. Its column taps (wl, wh, dx) are fixed, so it keeps the horizontally interpolated values of the two
@@ -814,13 +1022,30 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
         const int v = PickVec(sizeof(TOut), sh.win, {gi});
         const TIn* pg = static_cast<const TIn*>(go);
         TOut* po = static_cast<TOut*>(gi);
-        if (plan.schedule == BilinearPlan::kW2 && v >= 4 && Aligned(go, 16)) {
-            const int32_t tileRows = RowsForOccupancy(planes * (sh.win / 4), sh.hin);
+        const bool w2 = plan.schedule == BilinearPlan::kW2 || plan.schedule == BilinearPlan::kX2;
+        if (w2 && v >= 4 && Aligned(go, 16)) {
+            int32_t tileRows = RowsForOccupancy(planes * (sh.win / 4), sh.hin);
+            if (plan.schedule == BilinearPlan::kX2) {
+                // every tile reduces three extra grads rows before its first output: taller tiles measured faster
+                // (28 rows: 81 us, 10 rows: 92 us on fp16 32x256x112x112 -> 56x56) as long as a wave stays full
+                tileRows = std::max(tileRows, std::min(sh.hin, 28));
+            }
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, tileRows));
             const dim3 block = PlaneBlock(sh.win / 4, planes);
             const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
-            BilinearBwdW2Kernel<TIn, TOut><<<grid, block, 0, s>>>(pg, po, planes, sh.hin, sh.win, sh.hout, th, tw, rh,
-                                                                  tileRows);
+            const size_t x2Smem = X2SmemBytes(tileRows, static_cast<int32_t>(block.x * block.y), sizeof(TIn));
+            cudaError_t attr = cudaSuccess;
+            if (plan.schedule == BilinearPlan::kX2 && x2Smem > 48 * 1024 && x2Smem <= 100 * 1024) {
+                attr = cudaFuncSetAttribute(BilinearBwdX2Kernel<TIn, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(x2Smem));
+            }
+            if (plan.schedule == BilinearPlan::kX2 && x2Smem <= 100 * 1024 && attr == cudaSuccess) {
+                BilinearBwdX2Kernel<TIn, TOut><<<grid, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win, th, tw, rh,
+                                                                           tileRows);
+            } else {
+                BilinearBwdW2Kernel<TIn, TOut><<<grid, block, 0, s>>>(pg, po, planes, sh.hin, sh.win, sh.hout, th, tw,
+                                                                      rh, tileRows);
+            }
         } else if (plan.schedule != BilinearPlan::kDirect && plan.tileRows > 0) {
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, plan.tileRows));
             const int32_t stride = static_cast<int32_t>(
@@ -915,7 +1140,7 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
     const host::Ranges rH = host::LerpBwdRanges(tH, sh.hin);
     const host::Ranges rW = host::LerpBwdRanges(tW, sh.win);
     if (sh.win % 4 == 0 && IsW2BackwardPattern(rW, sh.win, sh.wout)) {
-        plan.schedule = BilinearPlan::kW2;
+        plan.schedule = IsW2BackwardPattern(rH, sh.hin, sh.hout) ? BilinearPlan::kX2 : BilinearPlan::kW2;
         return plan;
     }
     int32_t taps = 0;
