@@ -169,6 +169,36 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// Copies `nch` planes of `count` elements each (plane k at src + k * planeStride) into shared memory interleaved by
+// channel, tile[i] = {CG channels} (zeros past nch). The loads of several elements per thread (32 scalar loads at
+// most) are issued before the first store, so a block that has an SM to itself does not pay one memory latency per
+// element.
+template <typename T, int CG>
+__device__ __forceinline__ void StageInterleaved(Pack<T, CG>* tile, const T* __restrict__ src, int64_t planeStride,
+                                                 int32_t nch, int32_t count)
+{
+    constexpr int kBatch = CG >= 8 ? 4 : 8;
+    const int32_t step = blockDim.x;
+    for (int32_t base = threadIdx.x; base < count; base += step * kBatch) {
+        Pack<T, CG> v[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int32_t i = base + u * step;
+#pragma unroll
+            for (int k = 0; k < CG; ++k) {
+                v[u].v[k] = (i < count && k < nch) ? __ldg(src + k * planeStride + i) : DType<T>::FromF(0.0f);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int32_t i = base + u * step;
+            if (i < count) {
+                tile[i] = v[u];
+            }
+        }
+    }
+}
+
 // ---- deterministic mode --------------------------------------------------------------------------------------
 struct Entry {
     int32_t sample; // pixel index inside the image's output plane
@@ -382,14 +412,7 @@ __global__ void __launch_bounds__(1024)
     const int32_t c0 = static_cast<int32_t>(blockIdx.x - n * groups) * CG;
     const int32_t nch = min(CG, static_cast<int32_t>(g.c) - c0);
     const T* gob = go + (n * g.c + c0) * outPlane;
-    for (int32_t i = threadIdx.x; i < outPlane; i += blockDim.x) {
-        Vec v;
-#pragma unroll
-        for (int k = 0; k < CG; ++k) {
-            v.v[k] = k < nch ? __ldg(gob + static_cast<int64_t>(k) * outPlane + i) : DType<T>::FromF(0.0f);
-        }
-        tile[i] = v;
-    }
+    StageInterleaved<T, CG>(tile, gob, outPlane, nch, outPlane);
     __syncthreads();
     const int32_t* seg = segStart + n * (inPlane + 1);
     const Entry* ent = entries + n * entriesPerImage;
@@ -401,25 +424,22 @@ __global__ void __launch_bounds__(1024)
         for (int k = 0; k < CG; ++k) {
             acc[k] = 0.0f;
         }
-        // four entries per trip: their loads are independent, the additions stay in list order
-        for (int32_t e = a; e < b; e += 4) {
-            int2 raw[4];
-            Vec v[4];
+        // eight entries per trip: their loads are independent, the additions stay in list order
+        constexpr int kTrip = 8;
+        for (int32_t e = a; e < b; e += kTrip) {
+            int2 raw[kTrip];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kTrip; ++u) {
                 raw[u] = e + u < b ? __ldg(reinterpret_cast<const int2*>(ent + e + u)) : make_int2(0, 0);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                v[u] = tile[raw[u].x];
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kTrip; ++u) {
                 if (e + u < b) {
                     const float wgt = __int_as_float(raw[u].y);
+                    const Vec v = tile[raw[u].x];
 #pragma unroll
                     for (int k = 0; k < CG; ++k) {
-                        acc[k] = Add(acc[k], Mul(wgt, DType<T>::ToF(v[u].v[k])));
+                        acc[k] = Add(acc[k], Mul(wgt, DType<T>::ToF(v.v[k])));
                     }
                 }
             }
@@ -509,15 +529,7 @@ __global__ void __launch_bounds__(1024)
         }
     }
     if (WANT_GRID) {
-        const T* xb = x + (n * g.c + c0) * inPlane;
-        for (int32_t i = threadIdx.x; i < inPlane; i += blockDim.x) {
-            Vec v;
-#pragma unroll
-            for (int k = 0; k < CG; ++k) {
-                v.v[k] = k < nch ? __ldg(xb + static_cast<int64_t>(k) * inPlane + i) : DType<T>::FromF(0.0f);
-            }
-            tile[i] = v;
-        }
+        StageInterleaved<T, CG>(tile, x + (n * g.c + c0) * inPlane, inPlane, nch, inPlane);
     }
     __syncthreads();
     const float2* rb = rec + n * outPlane;

@@ -1,0 +1,117 @@
+"""GPU parity at the full sizes of the benchmark configurations.
+
+The oracle is a scalar CPU program, so at these sizes it checks the first and the last image of the batch only
+(every operator is independent per image, so those two slices exercise the largest offsets), and size-independent
+properties cover the rest of the tensor:
+  * nearest 2x: backward(forward(x)) == 4 * x exactly (four equal copies summed);
+  * interpolation weights of an output sum to one, so a constant image maps to the same constant, and the sum
+    of a gradient is preserved by every backward;
+  * the reproducible modes give identical bits twice; the atomic and the reproducible grid-sampler backward agree.
+"""
+import numpy as np
+import pytest
+import torch
+
+from test_gpu_parity import check, check_sum, gen
+
+pytestmark = pytest.mark.gpu
+
+
+def ends(t):
+    """First and last image of a batch-major tensor, as one CPU tensor."""
+    return torch.cat([t[:1], t[-1:]]).cpu()
+
+
+def test_cfg2_fpn_upsample_fp16(ops, oracle, dev):
+    n, c, hi, wi, ho, wo = 32, 256, 56, 56, 112, 112
+    x = torch.randn((n, c, hi, wi), generator=gen(1236)).to(torch.float16)
+    go = torch.randn((n, c, ho, wo), generator=gen(1237)).to(torch.float16)
+    xd, god = x.to(dev), go.to(dev)
+    # nearest
+    yn = ops.upsample_nearest2d(xd, (ho, wo), scales=(2.0, 2.0))
+    check(ends(yn), oracle.nearest2d_fwd(ends(x).float().numpy(), (ho, wo), (2.0, 2.0)), torch.float16, exact=True)
+    back = ops.upsample_nearest2d_backward(yn, (ho, wo), (n, c, hi, wi), scales=(2.0, 2.0))
+    assert torch.equal(back.cpu(), (x.float() * 4).to(torch.float16))
+    gn = ops.upsample_nearest2d_backward(god, (ho, wo), (n, c, hi, wi), scales=(2.0, 2.0))
+    check(ends(gn), oracle.nearest2d_bwd(ends(go).float().numpy(), (hi, wi), (2.0, 2.0)), torch.float16)
+    # bilinear
+    yb = ops.upsample_bilinear2d(xd, (ho, wo), False, scales=(2.0, 2.0))
+    check(ends(yb), oracle.bilinear2d_fwd(ends(x).float().numpy(), (ho, wo), False, (2.0, 2.0)), torch.float16)
+    const = torch.full((n, c, hi, wi), 0.75, dtype=torch.float16, device=dev)
+    assert torch.equal(ops.upsample_bilinear2d(const, (ho, wo), False, scales=(2.0, 2.0)),
+                       torch.full((n, c, ho, wo), 0.75, dtype=torch.float16, device=dev))
+    gb = ops.upsample_bilinear2d_backward(god, (ho, wo), (n, c, hi, wi), False, scales=(2.0, 2.0))
+    gb2 = ops.upsample_bilinear2d_backward(god, (ho, wo), (n, c, hi, wi), False, scales=(2.0, 2.0))
+    assert torch.equal(gb.view(torch.int16), gb2.view(torch.int16))
+    check_sum(ends(gb), oracle.bilinear2d_bwd(ends(go).float().numpy(), (hi, wi), False, (2.0, 2.0)), torch.float16)
+    # per-plane sums are preserved (fp32 sums of the fp16 tensors; the fp16 rounding of gi bounds the difference)
+    s_in, s_out = god.float().sum((2, 3)), gb.float().sum((2, 3))
+    assert (s_in - s_out).abs().max().item() <= 2.0 ** -10 * gb.float().abs().sum((2, 3)).max().item()
+
+
+def test_cfg3_bicubic_aa_fp32(ops, oracle, dev):
+    n, c, hi, wi, ho, wo = 64, 3, 1024, 1024, 224, 224
+    x = torch.randint(0, 256, (n, c, hi, wi), generator=gen(1238)).float() / 255
+    go = torch.randn((n, c, ho, wo), generator=gen(1239))
+    xd, god = x.to(dev), go.to(dev)
+    y = ops.upsample_bicubic2d_aa(xd, (ho, wo), False)
+    check(ends(y), oracle.bicubic_aa_fwd(ends(x).numpy(), (ho, wo), False), torch.float32, atol=2e-6)
+    const = ops.upsample_bicubic2d_aa(torch.full((2, 1, hi, wi), 0.625, device=dev), (ho, wo), False)
+    assert (const - 0.625).abs().max().item() <= 1e-6
+    gi = ops.upsample_bicubic2d_aa_grad(god, (ho, wo), (n, c, hi, wi), False)
+    check(ends(gi), oracle.bicubic_aa_bwd(ends(go).numpy(), (hi, wi), False), torch.float32, atol=2e-6)
+    s_in, s_out = god.double().sum((2, 3)), gi.double().sum((2, 3))
+    assert (s_in - s_out).abs().max().item() <= 1e-4 * god.double().abs().sum((2, 3)).max().item()
+    assert ops.async_copy_timeouts() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_cfg4_grid_sampler(ops, oracle, dev, dtype):
+    n, c, hi, wi, ho, wo = 16, 256, 64, 64, 128, 128
+    x = torch.randn((n, c, hi, wi), generator=gen(1240)).to(dtype)
+    grid = (torch.rand((n, ho, wo, 2), generator=gen(1241)) * 2.2 - 1.1).to(dtype)
+    go = torch.randn((n, c, ho, wo), generator=gen(1242)).to(dtype)
+    xd, gd, god = x.to(dev), grid.to(dev), go.to(dev)
+    x32, g32, go32 = ends(x).float().numpy(), ends(grid).float().numpy(), ends(go).float().numpy()
+    y = ops.grid_sampler2d(xd, gd, 0, 0, False)
+    check(ends(y), oracle.grid_sampler2d_fwd(x32, g32, 0, 0, False), dtype, exact=(dtype == torch.float32))
+    ri, rg = oracle.grid_sampler2d_bwd(go32, x32, g32, 0, 0, False)
+    gi_a, gg_a = ops.grid_sampler2d_backward(god, xd, gd, 0, 0, False)
+    check_sum(ends(gi_a), ri, dtype)
+    check_sum(ends(gg_a), rg, dtype)
+    ops.set_deterministic(True)
+    try:
+        gi_d, gg_d = ops.grid_sampler2d_backward(god, xd, gd, 0, 0, False)
+        gi_e, gg_e = ops.grid_sampler2d_backward(god, xd, gd, 0, 0, False)
+    finally:
+        ops.set_deterministic(False)
+    bits = torch.int32 if dtype == torch.float32 else torch.int16
+    assert torch.equal(gi_d.view(bits), gi_e.view(bits)) and torch.equal(gg_d.view(bits), gg_e.view(bits))
+    check_sum(ends(gi_d), ri, dtype)
+    check_sum(ends(gg_d), rg, dtype)
+    # the two modes agree over the whole tensor
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -7
+    scale = gi_d.float().abs().max().item()
+    assert (gi_a.float() - gi_d.float()).abs().max().item() <= tol * scale
+
+
+def test_cfg5_box_sweep_shard(ops, oracle, dev):
+    # bilinear bf16 NHWC: one eighth of the box-level batch (the per-GPU shard at 8 GPUs)
+    n, c, hi, wi, ho, wo = 64, 256, 64, 64, 128, 128
+    x = torch.randn((n, hi, wi, c), generator=gen(1243)).to(torch.bfloat16)
+    y = ops.upsample_bilinear2d(x.to(dev), (ho, wo), False, "NHWC")
+    ref = oracle.bilinear2d_fwd(ends(x).float().numpy(), (ho, wo), False, fmt=oracle.NHWC)
+    check(ends(y), ref, torch.bfloat16)
+    # grid sampler fp32 with affine grids
+    n2, c2, h2 = 32, 128, 96
+    g = gen(1244)
+    phi = (torch.rand(n2, generator=g) * 60 - 30) * np.pi / 180
+    s = torch.rand(n2, generator=g) * 0.4 + 0.8
+    t = torch.rand((n2, 2), generator=g) * 0.2 - 0.1
+    theta = torch.stack([torch.stack([s * torch.cos(phi), -s * torch.sin(phi), t[:, 0]], 1),
+                         torch.stack([s * torch.sin(phi), s * torch.cos(phi), t[:, 1]], 1)], 1)
+    grid = torch.nn.functional.affine_grid(theta, (n2, c2, h2, h2), align_corners=False).contiguous()
+    gx = torch.randn((n2, c2, h2, h2), generator=g)
+    gy = ops.grid_sampler2d(gx.to(dev), grid.to(dev), 0, 0, False)
+    check(ends(gy), oracle.grid_sampler2d_fwd(ends(gx).numpy(), ends(grid).numpy(), 0, 0, False), torch.float32,
+          exact=True)
