@@ -210,3 +210,16 @@ def grid_sampler2d_bwd(go, x, grid, interp=BILINEAR, pad=ZEROS, align=False):
                                  I64(n), I64(c), I32(h), I32(w), I32(ho), I32(wo), I32(interp), I32(pad),
                                  I32(int(align)))
     return gi, gg
+
+
+def grid_sampler2d_bwd_det_order(go, x_shape, grid, interp=BILINEAR, pad=ZEROS, align=False):
+    """grad_input with the fp32 additions in the reference's deterministic replay order (256-sample step, tap,
+    sample)."""
+    go, pgo = _f(go)
+    grid, pg = _f(grid)
+    n, c, h, w = x_shape
+    _, ho, wo, _ = grid.shape
+    gi = np.empty(tuple(x_shape), dtype=np.float32)
+    lib().orc_grid_sampler2d_bwd_det_order(pgo, pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I32(h), I32(w),
+                                           I32(ho), I32(wo), I32(interp), I32(pad), I32(int(align)))
+    return gi

@@ -377,6 +377,30 @@ def test_grid_sampler_staged_kernels(ops, oracle, dev, dtype, pad, align, c):
     check_sum(gi4, ri, dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interp", [0, 1])
+@pytest.mark.parametrize("shape", [(2, 5, 9, 11, 12, 23), (3, 4, 16, 16, 40, 37), (8, 80, 9, 11, 30, 29)])
+def test_grid_sampler_backward_deterministic_order(ops, oracle, dev, dtype, interp, shape):
+    """The reproducible mode adds the contributions of a destination in the order of the reference's deterministic
+    kernel (256-sample steps; inside a step tap NW, NE, SW, SE; inside a tap ascending sample), so grad_input equals
+    a serial replay in that order bit for bit. Shapes: one and several steps per image, heavy collisions (a coarse
+    4-pixel grid of destinations), and enough blocks for the staged gather."""
+    n, c, hi, wi, ho, wo = shape
+    grid, grid32 = quant(make_grid(n, ho, wo, 71, 1.15), dtype)
+    if shape[1] == 4:  # many samples per destination
+        grid = (grid * 2).round() / 2
+        grid, grid32 = quant(grid.float(), dtype)
+    g, g32 = quant(torch.randn((n, c, ho, wo), generator=gen(72)), dtype)
+    x = torch.zeros((n, c, hi, wi), dtype=dtype)
+    ops.set_deterministic(True)
+    try:
+        gi, _ = ops.grid_sampler2d_backward(g.to(dev), x.to(dev), grid.to(dev), interp, 0, False, mask=(True, False))
+    finally:
+        ops.set_deterministic(False)
+    ref = oracle.grid_sampler2d_bwd_det_order(g32, (n, c, hi, wi), grid32, interp, 0, False)
+    check(gi, ref, dtype, exact=True)
+
+
 def test_grid_sampler_backward_masks_and_collisions(ops, oracle, dev):
     # every sample hits the same source pixel: worst case for atomics and for the deterministic segment lists
     n, c, hi, wi, ho, wo = 1, 3, 4, 4, 40, 37
