@@ -50,15 +50,39 @@ struct alignas(sizeof(T) * V) Pack {
     T v[V];
 };
 
+// Two fp32 values rounded (to nearest even, each on its own) and packed into one 32-bit register by a single
+// conversion instruction; the generic path converts one at a time and then packs.
+__device__ __forceinline__ uint32_t PackPair(float a, float b, const __half*)
+{
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t PackPair(float a, float b, const __nv_bfloat16*)
+{
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 template <typename T, int V>
 __device__ __forceinline__ void StorePack(T* dst, const float (&vals)[V])
 {
-    Pack<T, V> p;
+    if constexpr (sizeof(T) == 2 && V % 2 == 0) {
+        struct alignas(sizeof(T) * V) Words {
+            uint32_t w[V / 2];
+        } p;
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-        p.v[k] = DType<T>::FromF(vals[k]);
+        for (int k = 0; k < V / 2; ++k) {
+            p.w[k] = PackPair(vals[2 * k], vals[2 * k + 1], static_cast<const T*>(nullptr));
+        }
+        *reinterpret_cast<Words*>(dst) = p;
+    } else {
+        Pack<T, V> p;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            p.v[k] = DType<T>::FromF(vals[k]);
+        }
+        *reinterpret_cast<Pack<T, V>*>(dst) = p;
     }
-    *reinterpret_cast<Pack<T, V>*>(dst) = p;
 }
 
 template <typename T, int V>

@@ -424,23 +424,44 @@ __global__ void __launch_bounds__(1024)
         for (int k = 0; k < CG; ++k) {
             acc[k] = 0.0f;
         }
-        // eight entries per trip: their loads are independent, the additions stay in list order
-        constexpr int kTrip = 8;
-        for (int32_t e = a; e < b; e += kTrip) {
-            int2 raw[kTrip];
+        // Every lane walks its own segment, so the entry loads of a warp are scattered: 16-byte loads (two entries)
+        // halve their count. Four pairs per trip are loaded before the first use; additions stay in list order.
+        auto add = [&](int32_t sample, float wgt) {
+            const Vec v = tile[sample];
 #pragma unroll
-            for (int u = 0; u < kTrip; ++u) {
-                raw[u] = e + u < b ? __ldg(reinterpret_cast<const int2*>(ent + e + u)) : make_int2(0, 0);
+            for (int k = 0; k < CG; ++k) {
+                acc[k] = Add(acc[k], Mul(wgt, DType<T>::ToF(v.v[k])));
+            }
+        };
+        int32_t e = a;
+        if (e < b && (e & 1)) { // segments start at any entry; pairs are 16-byte aligned at even indices
+            const int2 r = __ldg(reinterpret_cast<const int2*>(ent + e));
+            add(r.x, __int_as_float(r.y));
+            ++e;
+        }
+        constexpr int kPairs = 4;
+        for (; e < b; e += 2 * kPairs) {
+            int4 raw[kPairs];
+#pragma unroll
+            for (int u = 0; u < kPairs; ++u) {
+                const int32_t q = e + 2 * u;
+                if (q + 1 < b) {
+                    raw[u] = __ldg(reinterpret_cast<const int4*>(ent + q));
+                } else if (q < b) {
+                    const int2 r = __ldg(reinterpret_cast<const int2*>(ent + q));
+                    raw[u] = make_int4(r.x, r.y, 0, 0);
+                } else {
+                    raw[u] = make_int4(0, 0, 0, 0);
+                }
             }
 #pragma unroll
-            for (int u = 0; u < kTrip; ++u) {
-                if (e + u < b) {
-                    const float wgt = __int_as_float(raw[u].y);
-                    const Vec v = tile[raw[u].x];
-#pragma unroll
-                    for (int k = 0; k < CG; ++k) {
-                        acc[k] = Add(acc[k], Mul(wgt, DType<T>::ToF(v.v[k])));
-                    }
+            for (int u = 0; u < kPairs; ++u) {
+                const int32_t q = e + 2 * u;
+                if (q < b) {
+                    add(raw[u].x, __int_as_float(raw[u].y));
+                }
+                if (q + 1 < b) {
+                    add(raw[u].z, __int_as_float(raw[u].w));
                 }
             }
         }
