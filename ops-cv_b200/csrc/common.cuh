@@ -85,6 +85,16 @@ __device__ __forceinline__ void StorePack(T* dst, const float (&vals)[V])
     }
 }
 
+// One 32-byte store (sm_100 has 256-bit global stores). A thread that owns 32 contiguous bytes and writes them as two
+// 16-byte stores makes every store instruction of its warp touch half of each 32-byte sector, which doubles the
+// sector traffic on the SM-to-L2 path; this keeps it at one full sector per lane. dst must be 32-byte aligned.
+__device__ __forceinline__ void Store32Bytes(void* dst, const uint4& lo, const uint4& hi)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(lo.x), "r"(lo.y),
+                 "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                 : "memory");
+}
+
 template <typename T, int V>
 __device__ __forceinline__ void LoadPack(const T* src, float (&vals)[V])
 {

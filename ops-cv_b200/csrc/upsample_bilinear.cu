@@ -112,9 +112,26 @@ __global__ void __launch_bounds__(kThreads)
 
 // Vertical blend shared by the forward walks: given the horizontal interpolations of the top and bottom rows.
 template <typename T, int V>
-__device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const float (&bot)[V], float dy)
+__device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const float (&bot)[V], float dy,
+                                           bool wide = false)
 {
     const float dy1 = Sub(1.0f, dy);
+    if constexpr (V * sizeof(T) == 32) {
+        if (wide) { // dst is 32-byte aligned: one full-sector store per lane
+            Pack<T, V / 2> half[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                float out[V / 2];
+#pragma unroll
+                for (int k = 0; k < V / 2; ++k) {
+                    out[k] = Add(Mul(dy1, top[q * (V / 2) + k]), Mul(dy, bot[q * (V / 2) + k]));
+                }
+                StorePack<T, V / 2>(half[q].v, out);
+            }
+            Store32Bytes(dst, reinterpret_cast<const uint4&>(half[0]), reinterpret_cast<const uint4&>(half[1]));
+            return;
+        }
+    }
     constexpr int kPer = (V * sizeof(T) > 16) ? 16 / sizeof(T) : V; // at most 16 bytes per store
 #pragma unroll
     for (int q = 0; q < V / kPer; ++q) {
@@ -217,7 +234,7 @@ __global__ void __launch_bounds__(kThreads)
 template <typename T, int VI>
 __global__ void __launch_bounds__(kThreads)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
-                        int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows)
+                        int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores)
 {
     constexpr int VO = 2 * VI;
     const int32_t wout = 2 * win;
@@ -285,7 +302,7 @@ __global__ void __launch_bounds__(kThreads)
                 }
                 curBot = hi;
             }
-            BlendStore<T, VO>(dst, top, bot, __ldg(th.delta + h));
+            BlendStore<T, VO>(dst, top, bot, __ldg(th.delta + h), wideStores != 0);
             dst += wout;
         }
     }
@@ -1186,12 +1203,15 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
                 const dim3 block = PlaneBlock(sh.win / vi, planes);
                 const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
+                // a thread writes 2 * vi elements per row; when that is 32 bytes and the rows are 32-byte aligned
+                // they go out as one 32-byte store
+                const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0) ? 1 : 0;
                 if (vi == 8) {
                     if constexpr (sizeof(T) == 2) {
-                        BilinearFwdW2Kernel<T, 8><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows);
+                        BilinearFwdW2Kernel<T, 8><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
                     }
                 } else {
-                    BilinearFwdW2Kernel<T, 4><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows);
+                    BilinearFwdW2Kernel<T, 4><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
                 }
             } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));

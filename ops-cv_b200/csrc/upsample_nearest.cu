@@ -146,7 +146,8 @@ __global__ void __launch_bounds__(kThreads)
 
 // ---- NCHW, integer factors, input-major -------------------------------------------------------------------------
 // Forward: out[h][w] = in[h / RH][w / RW]. grid.x = planes; a thread takes 16-byte input vectors of its plane.
-template <typename T, int RW>
+// WIDE: the output rows are 32-byte aligned, so pairs of output vectors go out as one 32-byte store.
+template <typename T, int RW, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
     NearestFwdReplicateKernel(const T* __restrict__ x, T* __restrict__ y, int32_t hin, int32_t win, int32_t rh,
                               int64_t planes)
@@ -171,7 +172,12 @@ __global__ void __launch_bounds__(kThreads)
             for (int32_t i = 0; i < rh; ++i) {
 #pragma unroll
                 for (int q = 0; q < RW; ++q) {
-                    *reinterpret_cast<Pack<T, VI>*>(dst + q * VI) = out[q];
+                    if (WIDE && q + 1 < RW && q % 2 == 0) {
+                        Store32Bytes(dst + q * VI, reinterpret_cast<const uint4&>(out[q]),
+                                     reinterpret_cast<const uint4&>(out[q + 1]));
+                    } else if (!(WIDE && q % 2 == 1)) {
+                        *reinterpret_cast<Pack<T, VI>*>(dst + q * VI) = out[q];
+                    }
                 }
                 dst += wout;
             }
@@ -420,12 +426,18 @@ cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Nea
                 const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(planes, 1 << 30));
                 const T* px = static_cast<const T*>(x);
                 T* py = static_cast<T*>(y);
-                if (plan.rw == 2) {
-                    NearestFwdReplicateKernel<T, 2><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
+                // 32-byte stores need 32-byte aligned output rows (a thread's first column is a multiple of 32 bytes)
+                const bool wide = plan.rw != 3 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0;
+                if (plan.rw == 2 && wide) {
+                    NearestFwdReplicateKernel<T, 2, true><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
+                } else if (plan.rw == 2) {
+                    NearestFwdReplicateKernel<T, 2, false><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
                 } else if (plan.rw == 3) {
-                    NearestFwdReplicateKernel<T, 3><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
+                    NearestFwdReplicateKernel<T, 3, false><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
+                } else if (wide) {
+                    NearestFwdReplicateKernel<T, 4, true><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
                 } else {
-                    NearestFwdReplicateKernel<T, 4><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
+                    NearestFwdReplicateKernel<T, 4, false><<<blocks, kThreads, 0, s>>>(px, py, sh.hin, sh.win, plan.rh, planes);
                 }
             } else {
                 OPSCV_DISPATCH_VEC(v, V, {
