@@ -540,11 +540,11 @@ __global__ void __launch_bounds__(1024)
         }
         __syncthreads();
         if (hasCols) {
+            T* dst = op + static_cast<int64_t>(yb) * win + x;
+            const float* tr = tbuf + j0;
 #pragma unroll
             for (int ry = 0; ry < kBwdRows; ++ry) {
-                const int32_t y = yb + ry;
-                if (y < y1) {
-                    const float* tr = tbuf + ry * wout + j0;
+                if (yb + ry < y1) {
                     float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                     for (int u = 0; u < kBwdColSlots; ++u) {
@@ -556,8 +556,10 @@ __global__ void __launch_bounds__(1024)
                             }
                         }
                     }
-                    StorePack<T, 4>(op + static_cast<int64_t>(y) * win + x, out);
+                    StorePack<T, 4>(dst, out);
                 }
+                dst += win;
+                tr += wout;
             }
         }
         __syncthreads();
