@@ -129,15 +129,29 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
                            "(a = -0.5, support 2*scale), align_corners=false", "dtype": "f32"}
         return buffers, oplist, cfg
 
-    if name in ("cfg4", "cfg4bf16"):
+    if name in ("cfg4", "cfg4bf16", "cfg4affine"):
+        # cfg4affine: the cfg4 shapes with smooth grids (random rotation / scale / shift, as in cfg5) instead of
+        # uniform-random sample positions; not a BASELINE configuration, it separates the cost of the random
+        # access pattern from the cost of the kernels
         n, c, hi, wi, ho, wo = 16 // batch_div, 256, 64, 64, 128, 128
-        dt = torch.float32 if name == "cfg4" else torch.bfloat16
-        es = 4 if name == "cfg4" else 2
+        dt = torch.bfloat16 if name == "cfg4bf16" else torch.float32
+        es = 2 if name == "cfg4bf16" else 4
+
+        def make_grid(gen):
+            if name != "cfg4affine":
+                return torch.rand((n, ho, wo, 2), generator=gen) * 2.2 - 1.1
+            import math
+            phi = (torch.rand(n, generator=gen) * 60 - 30) * math.pi / 180
+            sc = torch.rand(n, generator=gen) * 0.4 + 0.8
+            t = torch.rand((n, 2), generator=gen) * 0.2 - 0.1
+            theta = torch.stack([torch.stack([sc * torch.cos(phi), -sc * torch.sin(phi), t[:, 0]], 1),
+                                 torch.stack([sc * torch.sin(phi), sc * torch.cos(phi), t[:, 1]], 1)], 1)
+            return torch.nn.functional.affine_grid(theta, (n, c, ho, wo), align_corners=False).contiguous()
 
         def buffers(gen):
             return {
                 "x": torch.randn((n, c, hi, wi), generator=gen).to(dt),
-                "grid": (torch.rand((n, ho, wo, 2), generator=gen) * 2.2 - 1.1).to(dt),
+                "grid": make_grid(gen).to(dt),
                 "go": torch.randn((n, c, ho, wo), generator=gen).to(dt),
                 "y": torch.empty((n, c, ho, wo), dtype=dt), "gi": torch.empty((n, c, hi, wi), dtype=dt),
                 "ggrid": torch.empty((n, ho, wo, 2), dtype=dt),
@@ -162,7 +176,9 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
                ["go", "x", "grid"], ["gi", "ggrid"]),
         ]
         cfg = {"workload": f"GridSampler2D forward + backward, bilinear/zeros/align_corners=false, {str(dt)[6:]} N={n} "
-                           "C=256 64x64, grid 128x128 uniform[-1.1,1.1]", "dtype": "f32" if es == 4 else "bf16"}
+                           "C=256 64x64, grid 128x128 " +
+                           ("random affine (rotation +-30 deg, scale 0.8-1.2, shift +-0.1)" if name == "cfg4affine"
+                            else "uniform[-1.1,1.1]"), "dtype": "f32" if es == 4 else "bf16"}
         return buffers, oplist, cfg
 
     if name == "cfg5":
@@ -326,7 +342,7 @@ def cpu_baseline(workload, budget_s=12.0):
             oracle.bicubic_aa_bwd(go, (1024, 1024), definition="scatter")
         algo = 2 * (x.size + go.size) * 4
         sample = "N=1 of 64 images, forward + backward (scatter definition)"
-    elif workload in ("cfg4", "cfg4bf16"):
+    elif workload in ("cfg4", "cfg4bf16", "cfg4affine"):
         es = 4 if workload == "cfg4" else 2
         x = rng.standard_normal((1, 256, 64, 64)).astype(np.float32)
         grid = (rng.random((1, 128, 128, 2), dtype=np.float32) * 2.2 - 1.1)
