@@ -1,6 +1,6 @@
 """Generates tests/golden/resample_golden.npz.
 
-Run in a container where the reference checkout is present (default /root/reference); the resulting file is
+Run where a checkout of the reference is present and pass its path as the first argument; the resulting file is
 committed, so the tests themselves never need the reference.
 
 Sources of the golden outputs (the reference stores no golden vectors; its tests create them at test time):
@@ -24,7 +24,9 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <path of the reference checkout>")
+REF = sys.argv[1]
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "resample_golden.npz")
 
 
