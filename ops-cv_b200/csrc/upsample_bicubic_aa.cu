@@ -222,11 +222,26 @@ __global__ void __launch_bounds__(MAXT, (VC == 4 && !BULK) ? 4 : (BULK ? 1 : 2))
             for (int bb = 0; bb < kFlushBatch; ++bb) {
                 v[bb] = 0.0f;
             }
-            for (int32_t t = 0; t < n; ++t) {
-                const float w = wTaps > 0 ? wsm[t * wout + j] : __ldg(wj + t);
+            // rows past `pending` hold stale values; their sums are not stored
+            if (wTaps > 0) {
+                const float* wp = wsm + j;
+#pragma unroll 4
+                for (int32_t t = 0; t < n; ++t) {
+                    const float w = wp[t * wout];
+                    const float* xr = rowbufs + Skew(m + t);
 #pragma unroll
-                for (int bb = 0; bb < kFlushBatch; ++bb) { // rows past `pending` hold stale values; not stored
-                    v[bb] = fmaf(w, rowbufs[bb * winPad + Skew(m + t)], v[bb]);
+                    for (int bb = 0; bb < kFlushBatch; ++bb) {
+                        v[bb] = fmaf(w, xr[bb * winPad], v[bb]);
+                    }
+                }
+            } else {
+                for (int32_t t = 0; t < n; ++t) {
+                    const float w = __ldg(wj + t);
+                    const float* xr = rowbufs + Skew(m + t);
+#pragma unroll
+                    for (int bb = 0; bb < kFlushBatch; ++bb) {
+                        v[bb] = fmaf(w, xr[bb * winPad], v[bb]);
+                    }
                 }
             }
 #pragma unroll
