@@ -544,7 +544,7 @@ __global__ void __launch_bounds__(kThreads)
 // row's range) are evaluated once per block into shared memory.
 // Tap 2y-2 exists because grads row 0 is clamped to input row 0 with weight 0 for its upper neighbour, and the
 // reference still adds that zero-weight product to row 1; keeping it preserves NaN / Inf propagation.
-constexpr int kX2Depth = 6;
+constexpr int kX2Depth = 8; // a power of two: the slot of a stream element is a mask away
 
 __device__ __forceinline__ void CpAsync16(void* smem, const void* gmem)
 {
@@ -630,22 +630,28 @@ __global__ void __launch_bounds__(kThreads, 3)
         const float wExtra = extra ? CombinedWeight(tw, 0, 1) : 0.0f;
         // stream of grads rows: element n of the stream is row first + n, for n < count
         const int32_t first = 2 * ya - 2, count = 2 * (yb - ya) + 3;
-        auto issue = [&](int32_t n) { // one commit group per stream element, empty for rows outside the plane
-            const int32_t i = first + n;
-            if (n < count && i >= 0 && i < hout) {
-                const int32_t slot = (n % kX2Depth) * nthreads + tid;
-                const TIn* row = gp + static_cast<int64_t>(i) * wout + j0;
+        // one commit group per stream element, empty for rows outside the plane; elements are issued in order, so
+        // the source row advances by one row per call
+        const TIn* issueRow = gp + static_cast<int64_t>(first) * wout + j0;
+        int32_t issueIdx = first; // grads row of the next element to issue
+        int32_t issueLeft = count;
+        auto issue = [&]() {
+            if (issueLeft > 0 && issueIdx >= 0 && issueIdx < hout) {
+                const int32_t slot = ((issueIdx - first) & (kX2Depth - 1)) * nthreads + tid;
 #pragma unroll
                 for (int m = 0; m < NM; ++m) {
-                    CpAsync16(qMid + static_cast<size_t>(slot) * NM + m, reinterpret_cast<const uint4*>(row) + m);
+                    CpAsync16(qMid + static_cast<size_t>(slot) * NM + m, reinterpret_cast<const uint4*>(issueRow) + m);
                 }
                 if (hasLeft) { // the word holding column j0-1 (4-byte aligned: j0 is a multiple of 8)
-                    CpAsync4(qLeft + slot, row - HE);
+                    CpAsync4(qLeft + slot, issueRow - HE);
                 }
                 if (hasRight) {
-                    CpAsync4(qRight + slot, row + VG);
+                    CpAsync4(qRight + slot, issueRow + VG);
                 }
             }
+            issueRow += wout;
+            ++issueIdx;
+            --issueLeft;
             CpAsyncCommit();
         };
         // Reduced row n of the stream (zeros outside the plane). Waits until all but the newest kX2Depth-1 groups
@@ -659,7 +665,7 @@ __global__ void __launch_bounds__(kThreads, 3)
                 v[k] = 0.0f;
             }
             if (i >= 0 && i < hout) {
-                const int32_t slot = (n % kX2Depth) * nthreads + tid;
+                const int32_t slot = (n & (kX2Depth - 1)) * nthreads + tid;
                 uint4 mid[NM];
 #pragma unroll
                 for (int m = 0; m < NM; ++m) {
@@ -679,7 +685,7 @@ __global__ void __launch_bounds__(kThreads, 3)
                     v[VG + 1] = DType<TIn>::ToF(reinterpret_cast<const TIn*>(&wr)[0]);
                 }
             }
-            issue(n + kX2Depth);
+            issue();
 #pragma unroll
             for (int k = 0; k < V; ++k) {
                 float a = 0.0f;
@@ -695,7 +701,7 @@ __global__ void __launch_bounds__(kThreads, 3)
         };
 #pragma unroll
         for (int n = 0; n < kX2Depth; ++n) {
-            issue(n);
+            issue();
         }
         // window of reduced rows: P = 2y-2, A = 2y-1, B = 2y, C = 2y+1, D = 2y+2 (rows outside the plane are 0
         // and their taps are masked off)
