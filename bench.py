@@ -449,7 +449,7 @@ def main():
         "dtype": head["config"]["dtype"], "data": "synthetic (seeded torch.Generator)",
         "config": {"workload": head["config"]["workload"], "l2": head["l2_note"], "per_gpu_batch": "fixed (weak scaling)",
                    "launch": "eager aclnn calls" if args.no_graph else
-                   "CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding all operators of the step; the per-operator times come from a separate pass of per-operator graphs, each bracketed by events"},
+                   "CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding all operators of the step; the per-operator times come from a separate pass: per-operator graphs launched back to back over all buffer sets between one pair of events"},
         "mpix_per_s": head["mpix_per_s"], "pct_of_hbm_peak": head["value"] / (peak * world),
         "roofline": head["roofline"], "ops": head["ops"], "e2e": head["e2e"], "gpu_launches": head["gpu_launches"],
         "clocks": head["clocks"], "peak_source": peak_src,
@@ -516,18 +516,21 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
         for j in range(len(oplist)):
             run_op(j, i % nsets)
     barrier()
-    # ---- per-operator breakdown: every operator bracketed by its own pair of events -------------------------
-    bsteps = min(args.steps, 50)
+    # ---- per-operator breakdown --------------------------------------------------------------------------------
+    # An operator's time is the average over back-to-back launches on all buffer sets between one pair of events
+    # (the sets rotate, so every launch still reads its inputs from HBM); bracketing single ~50 us launches would
+    # add the few microseconds it takes the host to get the next graph launch to an idle GPU.
+    bsteps = max(1, min(args.steps, 50) // nsets)
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in oplist]
           for _ in range(bsteps)]
     for i in range(bsteps):
-        s_i = i % nsets
         for j in range(len(oplist)):
             ev[i][j][0].record(stream)
-            run_op(j, s_i)
+            for s_i in range(nsets):
+                run_op(j, s_i)
             ev[i][j][1].record(stream)
     barrier()
-    per_op_ms = [statistics.mean(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(bsteps))
+    per_op_ms = [statistics.mean(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(bsteps)) / nsets
                  for j in range(len(oplist))]
     # ---- the timed region: exactly args.steps steps ---------------------------------------------------------
     if step_graphs is not None:
