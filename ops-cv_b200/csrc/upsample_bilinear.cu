@@ -323,6 +323,15 @@ __device__ __forceinline__ float CombinedWeight(const LerpAxis& t, int32_t j, in
     return w;
 }
 
+// A source j whose two taps fall on the same input index (lo == hi == xcol, at a clamped border) with a tap weight of
+// exactly zero: the reference adds both products, so a non-finite grads value must still turn into NaN there
+// although the combined weight is 1. Callers add one extra zero-weight product for such sources.
+__device__ __forceinline__ bool HasZeroTwin(const LerpAxis& t, int32_t j, int32_t xcol)
+{
+    const float d = __ldg(t.delta + j);
+    return __ldg(t.lo + j) == xcol && __ldg(t.hi + j) == xcol && (d == 0.0f || d == 1.0f);
+}
+
 // Vertical part of the walk, shared by the staged and the input-major kernels. `reduceRow(i, hp)` fills hp[] with the
 // horizontally reduced grads row i for this thread's V grad_input columns. Rows [ya, yb) of grad_input are
 // produced; grads rows are visited in increasing order and each contributes to rows lo[i] and hi[i] only.
@@ -428,6 +437,7 @@ __global__ void __launch_bounds__(kThreads)
     for (int32_t g = cg0; g < groups; g += colThreads) {
         int32_t js[V], cnt[V];
         float wx[V][KW];
+        uint32_t zeroTwins = 0; // bit k * KW + t: source js[k] + t adds one more zero-weight product to column k
 #pragma unroll
         for (int k = 0; k < V; ++k) {
             const int32_t xcol = g * V + k;
@@ -436,6 +446,9 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
             for (int t = 0; t < KW; ++t) {
                 wx[k][t] = t < cnt[k] ? CombinedWeight(tw, js[k] + t, xcol) : 0.0f;
+                if (t < cnt[k] && HasZeroTwin(tw, js[k] + t, xcol)) {
+                    zeroTwins |= 1u << (k * KW + t);
+                }
             }
         }
         WalkRows<TOut, V>(gp + g * V, win, ya, yb, th, rh, [&](int32_t i, float (&hp)[V]) {
@@ -450,6 +463,17 @@ __global__ void __launch_bounds__(kThreads)
                     a = fmaf(wx[k][t], v, a);
                 }
                 hp[k] = a;
+            }
+            if (zeroTwins != 0) { // only threads at a clamped border
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+#pragma unroll
+                    for (int t = 0; t < KW; ++t) {
+                        if (zeroTwins & (1u << (k * KW + t))) {
+                            hp[k] = fmaf(0.0f, DType<TIn>::ToF(row[js[k] + t]), hp[k]);
+                        }
+                    }
+                }
             }
         });
     }
@@ -481,12 +505,16 @@ __global__ void __launch_bounds__(kThreads)
         const bool hasLeft = j0 > 0, hasRight = j0 + VG < wout;
         // wx[k][t]: weight of grads column 2*(x0+k) - 1 + t for grad_input column x0+k (0 outside the row)
         float wx[V][4];
+        uint32_t zeroTwins = 0; // bit k * 4 + t: that source adds one more zero-weight product (clamped border)
 #pragma unroll
         for (int k = 0; k < V; ++k) {
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const int32_t j = j0 + 2 * k - 1 + t;
                 wx[k][t] = (j >= 0 && j < wout) ? CombinedWeight(tw, j, x0 + k) : 0.0f;
+                if (j >= 0 && j < wout && HasZeroTwin(tw, j, x0 + k)) {
+                    zeroTwins |= 1u << (k * 4 + t);
+                }
             }
         }
         // Column 1 has one more source: grads column 0 is clamped to input column 0 with delta 0, and the
@@ -526,6 +554,17 @@ __global__ void __launch_bounds__(kThreads)
             }
             if (extra) {
                 hp[1] = fmaf(wExtra, v[1], hp[1]);
+            }
+            if (zeroTwins != 0) { // only threads at a clamped border (align_corners)
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        if (zeroTwins & (1u << (k * 4 + t))) {
+                            hp[k] = fmaf(0.0f, v[2 * k + t], hp[k]);
+                        }
+                    }
+                }
             }
         });
     }
@@ -601,7 +640,9 @@ __global__ void __launch_bounds__(kThreads, 3)
         int32_t mask = 0;
         for (int t = 0; t < 5; ++t) {
             const int32_t i = 2 * y - 2 + t;
-            mask |= (i >= __ldg(rh.start + y) && i < __ldg(rh.end + y)) ? (1 << t) : 0;
+            const bool in = i >= __ldg(rh.start + y) && i < __ldg(rh.end + y);
+            mask |= in ? (1 << t) : 0;
+            mask |= (in && HasZeroTwin(th, i, y)) ? (256 << t) : 0; // one more zero-weight product for this row
         }
         rowTaps[r * 6 + 5] = __int_as_float(mask);
     }
@@ -618,12 +659,16 @@ __global__ void __launch_bounds__(kThreads, 3)
         const bool hasLeft = j0 > 0, hasRight = j0 + VG < wout;
         // wx[k][t]: weight of grads column 2*(x0+k) - 1 + t for grad_input column x0+k (0 outside the row)
         float wx[V][4];
+        uint32_t zeroTwins = 0; // bit k * 4 + t: that source adds one more zero-weight product (clamped border)
 #pragma unroll
         for (int k = 0; k < V; ++k) {
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const int32_t j = j0 + 2 * k - 1 + t;
                 wx[k][t] = (j >= 0 && j < wout) ? CombinedWeight(tw, j, x0 + k) : 0.0f;
+                if (j >= 0 && j < wout && HasZeroTwin(tw, j, x0 + k)) {
+                    zeroTwins |= 1u << (k * 4 + t);
+                }
             }
         }
         const bool extra = x0 == 0 && win > 1; // column 1 also takes grads column 0 (zero weight), as for rows
@@ -698,6 +743,17 @@ __global__ void __launch_bounds__(kThreads, 3)
             if (extra) {
                 hp[1] = fmaf(wExtra, v[1], hp[1]);
             }
+            if (zeroTwins != 0) { // only threads at a clamped border (align_corners)
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        if (zeroTwins & (1u << (k * 4 + t))) {
+                            hp[k] = fmaf(0.0f, v[2 * k + t], hp[k]);
+                        }
+                    }
+                }
+            }
         };
 #pragma unroll
         for (int n = 0; n < kX2Depth; ++n) {
@@ -724,6 +780,12 @@ __global__ void __launch_bounds__(kThreads, 3)
 #pragma unroll
                     for (int k = 0; k < V; ++k) {
                         out[k] = fmaf(w, hp[k], out[k]);
+                    }
+                    if (mask & (256 << t)) {
+#pragma unroll
+                        for (int k = 0; k < V; ++k) {
+                            out[k] = fmaf(0.0f, hp[k], out[k]);
+                        }
                     }
                 }
             };

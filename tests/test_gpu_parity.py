@@ -535,3 +535,46 @@ def test_no_device_wait_ran_out(ops, dev):
     """Collected after the operator tests of this file: none of the bounded waits on asynchronous copies gave up."""
     torch.cuda.synchronize(dev)
     assert ops.async_copy_timeouts() == 0
+
+
+def _poison(t, rng, count):
+    """Puts Inf / -Inf / NaN at `count` random positions plus the first and last element."""
+    flat = t.reshape(-1)
+    vals = [float("inf"), -float("inf"), float("nan")]
+    idx = [0, flat.numel() - 1] + [int(i) for i in rng.integers(0, flat.numel(), count)]
+    for j, i in enumerate(idx):
+        flat[i] = vals[j % 3]
+    return t
+
+
+def _same_nonfinite(got, ref32, what):
+    got = got.detach().cpu().float().numpy()
+    assert np.array_equal(np.isnan(got), np.isnan(ref32)), what
+    assert np.array_equal(np.isposinf(got), np.isposinf(ref32)), what
+    assert np.array_equal(np.isneginf(got), np.isneginf(ref32)), what
+    fin = np.isfinite(ref32)
+    np.testing.assert_allclose(got[fin], ref32[fin], rtol=1e-5, atol=1e-5, err_msg=what)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 8, 8, 16, 16), (1, 2, 8, 12, 16, 20), (2, 2, 9, 7, 5, 11), (1, 3, 40, 32, 9, 7)])
+def test_nonfinite_values_spread_as_in_the_reference(ops, oracle, dev, shape):
+    """An Inf or NaN in an input reaches exactly the outputs it reaches in the reference arithmetic: taps outside an
+    output's window are never touched, zero-weight taps inside it are (0 * Inf = NaN). Covers the 2x kernels, the
+    generic ones and the streaming bicubic-AA kernels (fp32)."""
+    n, c, hi, wi, ho, wo = shape
+    rng = np.random.default_rng(hi * 100 + wo)
+    x = _poison(torch.randn((n, c, hi, wi), generator=gen(80)), rng, 3)
+    go = _poison(torch.randn((n, c, ho, wo), generator=gen(81)), rng, 3)
+    xd, god = x.to(dev), go.to(dev)
+    _same_nonfinite(ops.upsample_nearest2d(xd, (ho, wo)), oracle.nearest2d_fwd(x.numpy(), (ho, wo)), "nearest fwd")
+    _same_nonfinite(ops.upsample_nearest2d_backward(god, (ho, wo), (n, c, hi, wi)),
+                    oracle.nearest2d_bwd(go.numpy(), (hi, wi)), "nearest bwd")
+    for align in (False, True):
+        _same_nonfinite(ops.upsample_bilinear2d(xd, (ho, wo), align), oracle.bilinear2d_fwd(x.numpy(), (ho, wo), align),
+                        f"bilinear fwd align={align}")
+        _same_nonfinite(ops.upsample_bilinear2d_backward(god, (ho, wo), (n, c, hi, wi), align),
+                        oracle.bilinear2d_bwd(go.numpy(), (hi, wi), align), f"bilinear bwd align={align}")
+    _same_nonfinite(ops.upsample_bicubic2d_aa(xd, (ho, wo), False), oracle.bicubic_aa_fwd(x.numpy(), (ho, wo), False),
+                    "bicubic-AA fwd")
+    _same_nonfinite(ops.upsample_bicubic2d_aa_grad(god, (ho, wo), (n, c, hi, wi), False),
+                    oracle.bicubic_aa_bwd(go.numpy(), (hi, wi), False), "bicubic-AA bwd")
