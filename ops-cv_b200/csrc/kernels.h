@@ -89,6 +89,7 @@ struct BilinearPlan {
     int32_t bandRows; // kTiled: most rows of the other tensor any tile reads
     int32_t tapsW;    // kTiled backward: most grads columns feeding one grad_input column
     int32_t planesPerBlock; // kTiled: planes whose bands share one block's shared memory
+    bool zeroTwins;         // backward: the tables hold clamped-border sources with a zero-weight twin tap
 };
 BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
 BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);

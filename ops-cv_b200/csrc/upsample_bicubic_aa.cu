@@ -497,13 +497,6 @@ __global__ void __launch_bounds__(1024)
     float4* msm = reinterpret_cast<float4*>(smemF);            // [bandRows][2] vertical slot records of the band's rows
     float* gos = smemF + static_cast<int64_t>(bandRows) * 8;   // [stageRows][wout] grads rows of the band
     float* tbuf = gos + static_cast<int64_t>(stageRows) * wout; // [kBwdRows][wout]
-    // rowBad[step parity][row of the step] != 0: the vertically reduced row holds an Inf / NaN. The horizontal step of
-    // such a row takes a path that only touches the sources covering each column, so that a non-finite value
-    // reaches exactly the columns it reaches in the reference (the fast path multiplies uncovered sources by 0).
-    __shared__ int32_t rowBad[2][kBwdRows];
-    if (threadIdx.x < 2 * kBwdRows) {
-        rowBad[threadIdx.x / kBwdRows][threadIdx.x % kBwdRows] = 0;
-    }
     const int64_t p = blockIdx.x;
     const int32_t y0 = blockIdx.y * bandRows, y1 = min(hin, y0 + bandRows);
     for (int32_t e = threadIdx.x; e < 2 * (y1 - y0); e += blockDim.x) {
@@ -512,8 +505,14 @@ __global__ void __launch_bounds__(1024)
     const int32_t i0 = __ldg(rh.start + y0);
     const int32_t i1 = min(max(i0, __ldg(rh.end + y1 - 1)), i0 + stageRows);
     const T* gp = go + (p * hout + i0) * static_cast<int64_t>(wout);
+    // While staging, note whether the band's grads rows hold an Inf / NaN: then the horizontal step takes a path that
+    // only touches the sources covering each column, so that a non-finite value reaches exactly the columns it
+    // reaches in the reference (the fast path multiplies uncovered sources by 0).
+    bool sawNonFinite = false;
     for (int32_t e = threadIdx.x; e < (i1 - i0) * wout; e += blockDim.x) {
-        gos[e] = DType<T>::Load(gp + e);
+        const float v = DType<T>::Load(gp + e);
+        gos[e] = v;
+        sawNonFinite |= !(fabsf(v) <= 3.402823466e38f);
     }
     // horizontal weights of my four columns: slot u <-> grads column j0 + u
     const int32_t x = threadIdx.x * 4;
@@ -535,10 +534,9 @@ __global__ void __launch_bounds__(1024)
         }
     }
     const int32_t jcnt = hasCols ? min(kBwdColSlots, __ldg(rw.end + x + 3) - j0) : 0;
-    __syncthreads();
+    const bool masked = __syncthreads_or(sawNonFinite) != 0; // also: the staged rows and records are visible
     T* op = gi + p * hin * static_cast<int64_t>(win);
     for (int32_t yb = y0; yb < y1; yb += kBwdRows) {
-        const int32_t par = ((yb - y0) / kBwdRows) & 1;
         // vertical: a thread takes one grads column for the kBwdRows rows of the step; the rows' slot records
         // (weights, first grads row, count) are block-uniform shared-memory reads
         for (int32_t j = threadIdx.x; j < wout; j += blockDim.x) {
@@ -559,15 +557,9 @@ __global__ void __launch_bounds__(1024)
                     }
                 }
                 tbuf[ry * wout + j] = v;
-                if (!(fabsf(v) <= 3.402823466e38f)) {
-                    rowBad[par][ry] = 1;
-                }
             }
         }
         __syncthreads();
-        if (threadIdx.x < kBwdRows) {
-            rowBad[par ^ 1][threadIdx.x] = 0; // the next step's flags; nobody reads or sets them before the barrier below
-        }
         if (hasCols) {
             T* dst = op + static_cast<int64_t>(yb) * win + x;
             const float* tr = tbuf + j0;
@@ -575,7 +567,7 @@ __global__ void __launch_bounds__(1024)
             for (int ry = 0; ry < kBwdRows; ++ry) {
                 if (yb + ry < y1) {
                     float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (rowBad[par][ry] == 0) {
+                    if (!masked) {
 #pragma unroll
                         for (int u = 0; u < kBwdColSlots; ++u) {
                             if (u < jcnt) { // slots past the run are not read

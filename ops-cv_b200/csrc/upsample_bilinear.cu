@@ -612,7 +612,10 @@ inline size_t X2SmemBytes(int32_t tileRows, int32_t threads, int elemSize)
     return taps + static_cast<size_t>(kX2Depth) * threads * (8 * elemSize + 8);
 }
 
-template <typename TIn, typename TOut>
+// TWINS: the tables hold clamped-border sources whose two taps fall on one index with a weight of exactly zero
+// (align_corners); the host knows from its copy of the tables, and only then the extra zero-weight products are
+// compiled in.
+template <typename TIn, typename TOut, bool TWINS>
 __global__ void __launch_bounds__(kThreads, 3)
     BilinearBwdX2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
                         LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows)
@@ -642,7 +645,7 @@ __global__ void __launch_bounds__(kThreads, 3)
             const int32_t i = 2 * y - 2 + t;
             const bool in = i >= __ldg(rh.start + y) && i < __ldg(rh.end + y);
             mask |= in ? (1 << t) : 0;
-            mask |= (in && HasZeroTwin(th, i, y)) ? (256 << t) : 0; // one more zero-weight product for this row
+            mask |= (TWINS && in && HasZeroTwin(th, i, y)) ? (256 << t) : 0; // one more zero-weight product
         }
         rowTaps[r * 6 + 5] = __int_as_float(mask);
     }
@@ -666,7 +669,7 @@ __global__ void __launch_bounds__(kThreads, 3)
             for (int t = 0; t < 4; ++t) {
                 const int32_t j = j0 + 2 * k - 1 + t;
                 wx[k][t] = (j >= 0 && j < wout) ? CombinedWeight(tw, j, x0 + k) : 0.0f;
-                if (j >= 0 && j < wout && HasZeroTwin(tw, j, x0 + k)) {
+                if (TWINS && j >= 0 && j < wout && HasZeroTwin(tw, j, x0 + k)) {
                     zeroTwins |= 1u << (k * 4 + t);
                 }
             }
@@ -743,7 +746,7 @@ __global__ void __launch_bounds__(kThreads, 3)
             if (extra) {
                 hp[1] = fmaf(wExtra, v[1], hp[1]);
             }
-            if (zeroTwins != 0) { // only threads at a clamped border (align_corners)
+            if (TWINS && zeroTwins != 0) { // only threads at a clamped border (align_corners)
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
 #pragma unroll
@@ -781,7 +784,7 @@ __global__ void __launch_bounds__(kThreads, 3)
                     for (int k = 0; k < V; ++k) {
                         out[k] = fmaf(w, hp[k], out[k]);
                     }
-                    if (mask & (256 << t)) {
+                    if (TWINS && (mask & (256 << t))) {
 #pragma unroll
                         for (int k = 0; k < V; ++k) {
                             out[k] = fmaf(0.0f, hp[k], out[k]);
@@ -1121,12 +1124,18 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
             const size_t x2Smem = X2SmemBytes(tileRows, static_cast<int32_t>(block.x * block.y), sizeof(TIn));
             cudaError_t attr = cudaSuccess;
             if (plan.schedule == BilinearPlan::kX2 && x2Smem > 48 * 1024 && x2Smem <= 100 * 1024) {
-                attr = cudaFuncSetAttribute(BilinearBwdX2Kernel<TIn, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(x2Smem));
+                attr = cudaFuncSetAttribute(plan.zeroTwins ? BilinearBwdX2Kernel<TIn, TOut, true>
+                                                           : BilinearBwdX2Kernel<TIn, TOut, false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(x2Smem));
             }
             if (plan.schedule == BilinearPlan::kX2 && x2Smem <= 100 * 1024 && attr == cudaSuccess) {
-                BilinearBwdX2Kernel<TIn, TOut><<<grid, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win, th, tw, rh,
-                                                                           tileRows);
+                if (plan.zeroTwins) {
+                    BilinearBwdX2Kernel<TIn, TOut, true><<<grid, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win, th,
+                                                                                     tw, rh, tileRows);
+                } else {
+                    BilinearBwdX2Kernel<TIn, TOut, false><<<grid, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win, th,
+                                                                                      tw, rh, tileRows);
+                }
             } else {
                 BilinearBwdW2Kernel<TIn, TOut><<<grid, block, 0, s>>>(pg, po, planes, sh.hin, sh.win, sh.hout, th, tw,
                                                                       rh, tileRows);
@@ -1224,6 +1233,16 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
     const host::Lerp tW = host::LerpTable(sh.win, sh.wout, gw.scale, halfPixel, 1);
     const host::Ranges rH = host::LerpBwdRanges(tH, sh.hin);
     const host::Ranges rW = host::LerpBwdRanges(tW, sh.win);
+    // clamped-border sources whose two taps share an index and one weight is exactly zero (align_corners)
+    auto hasTwins = [](const host::Lerp& t) {
+        for (size_t j = 0; j < t.lo.size(); ++j) {
+            if (t.lo[j] == t.hi[j] && (t.delta[j] == 0.0f || t.delta[j] == 1.0f)) {
+                return true;
+            }
+        }
+        return false;
+    };
+    plan.zeroTwins = hasTwins(tH) || hasTwins(tW);
     if (sh.win % 4 == 0 && IsW2BackwardPattern(rW, sh.win, sh.wout)) {
         plan.schedule = IsW2BackwardPattern(rH, sh.hin, sh.hout) ? BilinearPlan::kX2 : BilinearPlan::kW2;
         return plan;
