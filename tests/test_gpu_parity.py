@@ -578,3 +578,22 @@ def test_nonfinite_values_spread_as_in_the_reference(ops, oracle, dev, shape):
                     "bicubic-AA fwd")
     _same_nonfinite(ops.upsample_bicubic2d_aa_grad(god, (ho, wo), (n, c, hi, wi), False),
                     oracle.bicubic_aa_bwd(go.numpy(), (hi, wi), False), "bicubic-AA bwd")
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 8, 8, 16, 16), (1, 5, 9, 7, 5, 11)])
+def test_nonfinite_values_nhwc(ops, oracle, dev, shape):
+    """The same check for the channels-last kernels (nearest and bilinear, both directions)."""
+    n, c, hi, wi, ho, wo = shape
+    rng = np.random.default_rng(hi * 10 + wo)
+    x = _poison(torch.randn((n, hi, wi, c), generator=gen(82)), rng, 3)
+    go = _poison(torch.randn((n, ho, wo, c), generator=gen(83)), rng, 3)
+    xd, god = x.to(dev), go.to(dev)
+    _same_nonfinite(ops.upsample_nearest2d(xd, (ho, wo), "NHWC"),
+                    oracle.nearest2d_fwd(x.numpy(), (ho, wo), fmt=oracle.NHWC), "nearest fwd")
+    _same_nonfinite(ops.upsample_nearest2d_backward(god, (ho, wo), (n, hi, wi, c), "NHWC"),
+                    oracle.nearest2d_bwd(go.numpy(), (hi, wi), fmt=oracle.NHWC), "nearest bwd")
+    for align in (False, True):
+        _same_nonfinite(ops.upsample_bilinear2d(xd, (ho, wo), align, "NHWC"),
+                        oracle.bilinear2d_fwd(x.numpy(), (ho, wo), align, fmt=oracle.NHWC), f"bilinear fwd {align}")
+        _same_nonfinite(ops.upsample_bilinear2d_backward(god, (ho, wo), (n, hi, wi, c), align, "NHWC"),
+                        oracle.bilinear2d_bwd(go.numpy(), (hi, wi), align, fmt=oracle.NHWC), f"bilinear bwd {align}")
