@@ -226,17 +226,52 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// ---- per-thread asynchronous row queues ------------------------------------------------------------------------
+// The row walks below are serial chains per thread, so what bounds them is the number of bytes a thread has in
+// flight. cp.async copies a thread's own piece of the next rows into a private shared-memory queue (one commit
+// group per row, cp.async.wait_group to consume in order), which holds several times what registers could.
+__device__ __forceinline__ void CpAsync16(void* smem, const void* gmem)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+                 "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void CpAsync4(void* smem, const void* gmem)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+                 "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void CpAsyncWait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ---- forward, NCHW, output width = 2 x input width, input-major ---------------------------------------------------
 // The host has verified the column pattern lo[w] = max((w-1)>>1, 0), hi[w] = w ? min((w+1)>>1, win-1) : 0, so the
 // 2*VI outputs of input columns c0..c0+VI-1 read columns c0-1..c0+VI (clamped). Weights still come from the table.
 // grid = (plane groups, tiles per plane), block = (column threads, planes); rows are table-driven (any vertical
 // scale).
-template <typename T, int VI>
+constexpr int kFwdQueueDepth = 4;
+
+// QUEUE (needs VI * sizeof(T) == 16): the input rows stream through a per-thread cp.async queue.
+template <typename T, int VI, bool QUEUE>
 __global__ void __launch_bounds__(kThreads)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores)
 {
     constexpr int VO = 2 * VI;
+    constexpr int HE = 4 / sizeof(T); // elements in a 4-byte neighbour word
+    extern __shared__ __align__(16) unsigned char fwdQueue[];
+    const int32_t tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
+    // [depth][nthreads] 16-byte vectors, then the left and right neighbour words
+    uint4* qMid = reinterpret_cast<uint4*>(fwdQueue);
+    uint32_t* qLeft = reinterpret_cast<uint32_t*>(qMid + static_cast<size_t>(kFwdQueueDepth) * nthreads);
+    uint32_t* qRight = qLeft + static_cast<size_t>(kFwdQueueDepth) * nthreads;
     const int32_t wout = 2 * win;
     // block = (column threads, planes): every thread of a block walks the same rows, so the row logic is uniform
     const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.y + threadIdx.y;
@@ -257,17 +292,70 @@ __global__ void __launch_bounds__(kThreads)
             dx[k] = __ldg(tw.delta + c0 * 2 + k);
             dx1[k] = Sub(1.0f, dx[k]);
         }
+        // QUEUE: the input rows this walk needs are lo[ha] .. hi[hb-1], in increasing order; they stream through
+        // the thread's queue kFwdQueueDepth rows ahead (one commit group per row, empty past the end).
+        const int32_t lastRow = QUEUE ? __ldg(th.hi + hb - 1) : 0;
+        int32_t nextRow = QUEUE ? __ldg(th.lo + ha) : 0; // next row the queue delivers
+        int32_t issued = nextRow;                        // next row to start copying
+        auto issue = [&]() {
+            if (issued <= lastRow) {
+                const int32_t slot = (issued & (kFwdQueueDepth - 1)) * nthreads + tid;
+                const T* xr = xp + static_cast<int64_t>(issued) * win + c0;
+                CpAsync16(qMid + slot, xr);
+                if (c0 > 0) { // the word holding column c0-1 (4-byte aligned: c0 is a multiple of VI)
+                    CpAsync4(qLeft + slot, xr - HE);
+                }
+                if (c0 + VI < win) {
+                    CpAsync4(qRight + slot, xr + VI);
+                }
+            }
+            ++issued;
+            CpAsyncCommit();
+        };
+        if (QUEUE) {
+#pragma unroll
+            for (int d = 0; d < kFwdQueueDepth; ++d) {
+                issue();
+            }
+        }
         auto loadRow = [&](int32_t r, float (&h)[VO]) {
             const T* xr = xp + static_cast<int64_t>(r) * win;
-            float v[VI + 2]; // columns c0-1 .. c0+4
-            v[0] = DType<T>::Load(xr + cl);
-            float mid[VI];
-            LoadPackLdg<T, VI>(xr + c0, mid);
+            float v[VI + 2]; // columns c0-1 .. c0+VI
+            if (QUEUE) {
+                while (nextRow < r) { // rows the walk skips (down-scaling) are dropped
+                    ++nextRow;
+                    issue();
+                }
+                CpAsyncWait<kFwdQueueDepth - 1>();
+                const int32_t slot = (r & (kFwdQueueDepth - 1)) * nthreads + tid;
+                const uint4 raw = qMid[slot];
+                const T* me = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-            for (int k = 0; k < VI; ++k) {
-                v[k + 1] = mid[k];
+                for (int k = 0; k < VI; ++k) {
+                    v[k + 1] = DType<T>::ToF(me[k]);
+                }
+                v[0] = v[1];
+                v[VI + 1] = v[VI];
+                if (c0 > 0) {
+                    const uint32_t wl = qLeft[slot];
+                    v[0] = DType<T>::ToF(reinterpret_cast<const T*>(&wl)[HE - 1]);
+                }
+                if (c0 + VI < win) {
+                    const uint32_t wr = qRight[slot];
+                    v[VI + 1] = DType<T>::ToF(reinterpret_cast<const T*>(&wr)[0]);
+                }
+                ++nextRow;
+                issue();
+            } else {
+                v[0] = DType<T>::Load(xr + cl);
+                float mid[VI];
+                LoadPackLdg<T, VI>(xr + c0, mid);
+#pragma unroll
+                for (int k = 0; k < VI; ++k) {
+                    v[k + 1] = mid[k];
+                }
+                v[VI + 1] = DType<T>::Load(xr + cr);
             }
-            v[VI + 1] = DType<T>::Load(xr + cr);
 #pragma unroll
             for (int j = 0; j < VI; ++j) {
                 // outputs 2(c0+j) (taps c0+j-1, c0+j) and 2(c0+j)+1 (taps c0+j, c0+j+1)
@@ -304,6 +392,9 @@ __global__ void __launch_bounds__(kThreads)
             }
             BlendStore<T, VO>(dst, top, bot, __ldg(th.delta + h), wideStores != 0);
             dst += wout;
+        }
+        if (QUEUE) {
+            CpAsyncWait<0>(); // nothing of this thread's queue is in flight when the next column group reuses it
         }
     }
 }
@@ -585,27 +676,6 @@ __global__ void __launch_bounds__(kThreads)
 // reference still adds that zero-weight product to row 1; keeping it preserves NaN / Inf propagation.
 constexpr int kX2Depth = 8; // a power of two: the slot of a stream element is a mask away
 
-__device__ __forceinline__ void CpAsync16(void* smem, const void* gmem)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
-                 "l"(gmem)
-                 : "memory");
-}
-__device__ __forceinline__ void CpAsync4(void* smem, const void* gmem)
-{
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
-                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
-                 "l"(gmem)
-                 : "memory");
-}
-__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void CpAsyncWait()
-{
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 inline size_t X2SmemBytes(int32_t tileRows, int32_t threads, int elemSize)
 {
     const size_t taps = (static_cast<size_t>(tileRows) * 6 * sizeof(float) + 15) & ~static_cast<size_t>(15);
@@ -819,12 +889,17 @@ __global__ void __launch_bounds__(kThreads, 3)
 // element is the reference's, (1-dy) * ((1-dx) * TL + dx * TR) + dy * ((1-dx) * BL + dx * BR), unchanged.
 // Consecutive threads hold consecutive channel vectors, then consecutive columns: every load and store of a warp
 // is one contiguous run, and neighbouring columns find their shared input pixels in L1.
-template <typename T, int V>
+// QUEUE (16-byte channel vectors): the two pixels a thread needs of every input row stream through a per-thread
+// cp.async queue kFwdQueueDepth rows ahead; without it the walk exposes one memory latency per new input row.
+template <typename T, int V, bool QUEUE>
 __global__ void __launch_bounds__(kThreads)
     BilinearFwdNHWCKernel(const T* __restrict__ x, T* __restrict__ y, int32_t c, int32_t hin, int32_t win,
                           int32_t hout, int32_t wout, LerpAxis th, LerpAxis tw, int32_t rows, int32_t rowChunks,
                           int64_t walkers)
 {
+    extern __shared__ __align__(16) unsigned char nhwcQueue[];
+    uint4* qL = reinterpret_cast<uint4*>(nhwcQueue);                 // [depth][blockDim.x] left pixel
+    uint4* qR = qL + static_cast<size_t>(kFwdQueueDepth) * blockDim.x; // [depth][blockDim.x] right pixel
     const int32_t groups = c / V;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     const int64_t total = walkers * rowChunks;
@@ -845,10 +920,47 @@ __global__ void __launch_bounds__(kThreads)
         const int64_t outStride = static_cast<int64_t>(wout) * c;
         float a[V], b[V];
         int32_t ia = -1, ib = -1;
+        // QUEUE: rows lo[h0] .. hi[h1-1] are needed in increasing order
+        const int32_t lastRow = QUEUE ? __ldg(th.hi + h1 - 1) : 0;
+        int32_t nextRow = QUEUE ? __ldg(th.lo + h0) : 0, issued = nextRow;
+        auto issue = [&]() {
+            if (issued <= lastRow) {
+                const int32_t slot = (issued & (kFwdQueueDepth - 1)) * blockDim.x + threadIdx.x;
+                CpAsync16(qL + slot, xl + issued * rowStride);
+                CpAsync16(qR + slot, xr + issued * rowStride);
+            }
+            ++issued;
+            CpAsyncCommit();
+        };
+        if (QUEUE) {
+#pragma unroll
+            for (int d = 0; d < kFwdQueueDepth; ++d) {
+                issue();
+            }
+        }
         auto hrow = [&](int32_t r, float (&dst)[V]) {
             float l[V], rr[V];
-            LoadPackLdg<T, V>(xl + r * rowStride, l);
-            LoadPackLdg<T, V>(xr + r * rowStride, rr);
+            if (QUEUE) {
+                while (nextRow < r) { // rows the walk skips (down-scaling) are dropped
+                    ++nextRow;
+                    issue();
+                }
+                CpAsyncWait<kFwdQueueDepth - 1>();
+                const int32_t slot = (r & (kFwdQueueDepth - 1)) * blockDim.x + threadIdx.x;
+                const uint4 rawL = qL[slot], rawR = qR[slot];
+                const T* pl = reinterpret_cast<const T*>(&rawL);
+                const T* pr = reinterpret_cast<const T*>(&rawR);
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    l[k] = DType<T>::ToF(pl[k]);
+                    rr[k] = DType<T>::ToF(pr[k]);
+                }
+                ++nextRow;
+                issue();
+            } else {
+                LoadPackLdg<T, V>(xl + r * rowStride, l);
+                LoadPackLdg<T, V>(xr + r * rowStride, rr);
+            }
 #pragma unroll
             for (int k = 0; k < V; ++k) {
                 dst[k] = Add(Mul(dx1, l[k]), Mul(dx, rr[k]));
@@ -886,6 +998,9 @@ __global__ void __launch_bounds__(kThreads)
             }
             StorePack<T, V>(yp, out);
             yp += outStride;
+        }
+        if (QUEUE) {
+            CpAsyncWait<0>(); // the queue is empty before the thread takes another walker
         }
     }
 }
@@ -1286,19 +1401,28 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
             if (w2Ok) {
                 // 16-bit tensors: eight input columns (one 16-byte load) per thread when the rows allow it
                 const int vi = (sizeof(T) == 2 && sh.win % 8 == 0 && Aligned(x, 16)) ? 8 : 4;
-                const int32_t tileRows = RowsForOccupancy(planes * (sh.win / vi), sh.hout);
+                // every tile interpolates one extra input row and sets up its column weights again: taller tiles
+                // measured faster (28 rows: 64 us, 11 rows: 68 us on fp16 32x256x56x56 -> 112x112)
+                const int32_t tileRows =
+                    std::max(RowsForOccupancy(planes * (sh.win / vi), sh.hout), std::min(sh.hout, 28));
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
                 const dim3 block = PlaneBlock(sh.win / vi, planes);
                 const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
                 // a thread writes 2 * vi elements per row; when that is 32 bytes and the rows are 32-byte aligned
                 // they go out as one 32-byte store
                 const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0) ? 1 : 0;
+                // 16-byte pieces (fp32 x 4, 16-bit x 8) stream through the per-thread queue
+                const size_t qBytes = static_cast<size_t>(kFwdQueueDepth) * block.x * block.y * 24;
                 if (vi == 8) {
                     if constexpr (sizeof(T) == 2) {
-                        BilinearFwdW2Kernel<T, 8><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
+                        BilinearFwdW2Kernel<T, 8, true><<<grid, block, qBytes, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
+                    }
+                } else if (sizeof(T) == 4) {
+                    if constexpr (sizeof(T) == 4) {
+                        BilinearFwdW2Kernel<T, 4, true><<<grid, block, qBytes, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
                     }
                 } else {
-                    BilinearFwdW2Kernel<T, 4><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
+                    BilinearFwdW2Kernel<T, 4, false><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
                 }
             } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
@@ -1344,9 +1468,22 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                     const int32_t rowChunks = static_cast<int32_t>(CeilDiv(sh.hout, rows));
                     const unsigned blocks = static_cast<unsigned>(
                         std::min<int64_t>(CeilDiv(walkers * rowChunks, kThreads), 0x7fffffff));
-                    BilinearFwdNHWCKernel<T, V><<<blocks, kThreads, 0, s>>>(
+                    bool queued = false;
+                    if constexpr (V * sizeof(T) == 16) {
+                        if (Aligned(x, 16)) {
+                            BilinearFwdNHWCKernel<T, V, true>
+                                <<<blocks, kThreads, static_cast<size_t>(kFwdQueueDepth) * kThreads * 32, s>>>(
                         static_cast<const T*>(x), static_cast<T*>(y), static_cast<int32_t>(sh.c), sh.hin, sh.win,
                         sh.hout, sh.wout, th, tw, rows, rowChunks, walkers);
+                            queued = true;
+                        }
+                    }
+                    if (!queued) {
+    BilinearFwdNHWCKernel<T, V, false><<<blocks, kThreads, 0, s>>>(
+                        static_cast<const T*>(x), static_cast<T*>(y), static_cast<int32_t>(sh.c), sh.hin, sh.win,
+                        sh.hout, sh.wout, th, tw, rows, rowChunks, walkers);
+                    }
+
                 }
             });
         }
