@@ -162,8 +162,8 @@ __global__ void __launch_bounds__(MAXT, (VC == 4 && !BULK) ? 4 : (BULK ? 1 : 2))
                       int32_t wout, AAAxis th, AAAxis tw, const float* __restrict__ wrow, int32_t bandRows,
                       int32_t metaRows, int32_t wTaps, int32_t ringGroups)
 {
-    // input rows in flight per thread / rows per ring group (three keep the 4-column variant within 64 registers)
-    constexpr int PF = (VC == 4 && !BULK) ? 3 : 4;
+    // input rows in flight per thread / rows per ring group (two keep the 4-column variant within 64 registers without spills)
+    constexpr int PF = (VC == 4 && !BULK) ? 2 : 4;
     constexpr int LV = 16 / sizeof(T);     // elements per 16-byte load
     constexpr int NL = VC / LV;            // 16-byte loads per row
     extern __shared__ __align__(16) float smemAll[];
