@@ -260,7 +260,7 @@ constexpr int kFwdQueueDepth = 4;
 
 // QUEUE (needs VI * sizeof(T) == 16): the input rows stream through a per-thread cp.async queue.
 template <typename T, int VI, bool QUEUE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores)
 {
