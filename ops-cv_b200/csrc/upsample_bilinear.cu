@@ -297,10 +297,11 @@ __global__ void __launch_bounds__(kThreads, 3)
         const int32_t lastRow = QUEUE ? __ldg(th.hi + hb - 1) : 0;
         int32_t nextRow = QUEUE ? __ldg(th.lo + ha) : 0; // next row the queue delivers
         int32_t issued = nextRow;                        // next row to start copying
+        const T* issuePtr = xp + static_cast<int64_t>(nextRow) * win + c0;
         auto issue = [&]() {
             if (issued <= lastRow) {
                 const int32_t slot = (issued & (kFwdQueueDepth - 1)) * nthreads + tid;
-                const T* xr = xp + static_cast<int64_t>(issued) * win + c0;
+                const T* xr = issuePtr;
                 CpAsync16(qMid + slot, xr);
                 if (c0 > 0) { // the word holding column c0-1 (4-byte aligned: c0 is a multiple of VI)
                     CpAsync4(qLeft + slot, xr - HE);
@@ -310,6 +311,7 @@ __global__ void __launch_bounds__(kThreads, 3)
                 }
             }
             ++issued;
+            issuePtr += win;
             CpAsyncCommit();
         };
         if (QUEUE) {
@@ -923,13 +925,17 @@ __global__ void __launch_bounds__(kThreads)
         // QUEUE: rows lo[h0] .. hi[h1-1] are needed in increasing order
         const int32_t lastRow = QUEUE ? __ldg(th.hi + h1 - 1) : 0;
         int32_t nextRow = QUEUE ? __ldg(th.lo + h0) : 0, issued = nextRow;
+        const T* issueL = xl + nextRow * rowStride; // row `issued` of the left / right pixel
+        const T* issueR = xr + nextRow * rowStride;
         auto issue = [&]() {
             if (issued <= lastRow) {
                 const int32_t slot = (issued & (kFwdQueueDepth - 1)) * blockDim.x + threadIdx.x;
-                CpAsync16(qL + slot, xl + issued * rowStride);
-                CpAsync16(qR + slot, xr + issued * rowStride);
+                CpAsync16(qL + slot, issueL);
+                CpAsync16(qR + slot, issueR);
             }
             ++issued;
+            issueL += rowStride;
+            issueR += rowStride;
             CpAsyncCommit();
         };
         if (QUEUE) {
