@@ -365,35 +365,53 @@ __global__ void __launch_bounds__(kThreads, 3)
                 h[2 * j + 1] = Add(Mul(dx1[2 * j + 1], v[j + 1]), Mul(dx[2 * j + 1], v[j + 2]));
             }
         };
-        float top[VO], bot[VO];
+        // Two row buffers; which of them holds the upper row alternates, so a row that moves from "lower" to "upper"
+        // (every other output row when up-scaling) stays where it is. step() is the walk for one output row with
+        // `up` as the upper and `dn` as the lower buffer and returns true when the two have traded places.
+        float bufA[VO], bufB[VO];
         int32_t curTop = -1, curBot = -1;
         T* dst = yp + static_cast<int64_t>(ha) * wout + c0 * 2;
-        for (int32_t h = ha; h < hb; ++h) {
+        auto step = [&](int32_t h, float (&up)[VO], float (&dn)[VO]) -> bool {
             const int32_t lo = __ldg(th.lo + h), hi = __ldg(th.hi + h);
-            if (lo != curTop) {
-                if (lo == curBot) {
+            const float dy = __ldg(th.delta + h);
+            if (lo == curBot && lo != curTop) { // the lower row becomes the upper one: trade places
+                curTop = lo;
+                if (hi == lo) {
 #pragma unroll
                     for (int k = 0; k < VO; ++k) {
-                        top[k] = bot[k];
+                        up[k] = dn[k];
                     }
                 } else {
-                    loadRow(lo, top);
+                    loadRow(hi, up);
                 }
+                curBot = hi;
+                BlendStore<T, VO>(dst, dn, up, dy, wideStores != 0);
+                dst += wout;
+                return true;
+            }
+            if (lo != curTop) {
+                loadRow(lo, up);
                 curTop = lo;
             }
             if (hi != curBot) {
                 if (hi == curTop) {
 #pragma unroll
                     for (int k = 0; k < VO; ++k) {
-                        bot[k] = top[k];
+                        dn[k] = up[k];
                     }
                 } else {
-                    loadRow(hi, bot);
+                    loadRow(hi, dn);
                 }
                 curBot = hi;
             }
-            BlendStore<T, VO>(dst, top, bot, __ldg(th.delta + h), wideStores != 0);
+            BlendStore<T, VO>(dst, up, dn, dy, wideStores != 0);
             dst += wout;
+            return false;
+        };
+        bool traded = false; // false: bufA is the upper row
+        for (int32_t h = ha; h < hb; ++h) {
+            const bool t = traded ? step(h, bufB, bufA) : step(h, bufA, bufB);
+            traded ^= t;
         }
         if (QUEUE) {
             CpAsyncWait<0>(); // nothing of this thread's queue is in flight when the next column group reuses it
@@ -664,29 +682,29 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 // ---- backward, NCHW, grads = 2 x grad_input on both axes, input-major ---------------------------------------------
-// The host has verified the pattern on both axes: grad_input row y is fed by grads rows 2y-1 .. 2y+2 (clipped to the
-// plane; row 1 also by row 0, see below), and the same for columns. A thread owns four grad_input columns and walks
-// down the grad_input rows of its tile. It keeps the horizontally reduced grads rows of the current window in
-// registers, so every grads row is reduced once per tile.
-// The grads rows a thread consumes form a plain stream (rows 2*ya-2, 2*ya-1, ...). The thread copies its own piece of
-// each row (its eight columns plus one neighbour on each side) with cp.async into a private shared-memory queue
-// kX2Depth rows ahead: the walk is a serial chain per thread, so what bounds it is the number of bytes in flight,
-// and a queue in shared memory holds several times what the registers could.
-// The vertical weights of a tile's rows (five taps: grads rows 2y-2 .. 2y+2, with a mask of the taps that lie in the
-// row's range) are evaluated once per block into shared memory.
-// Tap 2y-2 exists because grads row 0 is clamped to input row 0 with weight 0 for its upper neighbour, and the
-// reference still adds that zero-weight product to row 1; keeping it preserves NaN / Inf propagation.
+// The host has verified the pattern on both axes: grads row i feeds grad_input rows lo[i] = max((i-1)>>1, 0) and
+// hi[i] (lo[i] + 1 clipped to the plane; row 0 feeds rows 0 and 1), and the same for columns. A thread owns four
+// grad_input columns and walks down the grads rows that feed its tile of grad_input rows. Every grads row is reduced
+// horizontally once and added into the (at most two) open grad_input rows, in increasing grads-row order and lower
+// tap first, which is the order of the reference's scatter loop; zero-weight taps at clamped borders are real
+// products here, so NaN / Inf propagate as they do there.
+// The grads rows a thread consumes form a plain stream. The thread copies its own piece of each row (its eight
+// columns plus one neighbour on each side) with cp.async into a private shared-memory queue kX2Depth rows ahead: the
+// walk is a serial chain per thread, so what bounds it is the number of bytes in flight, and a queue in shared
+// memory holds several times what the registers could.
+// What a grads row does to the open rows (its two weights, which of the open rows they go to, how many finished rows
+// to store first) is the same for every thread: it is evaluated once per block into shared memory.
 constexpr int kX2Depth = 8; // a power of two: the slot of a stream element is a mask away
 
 inline size_t X2SmemBytes(int32_t tileRows, int32_t threads, int elemSize)
 {
-    const size_t taps = (static_cast<size_t>(tileRows) * 6 * sizeof(float) + 15) & ~static_cast<size_t>(15);
-    return taps + static_cast<size_t>(kX2Depth) * threads * (8 * elemSize + 8);
+    const size_t recs = static_cast<size_t>(2 * tileRows + 4) * 16; // one 16-byte record per grads row of the tile
+    return recs + static_cast<size_t>(kX2Depth) * threads * (8 * elemSize + 8);
 }
 
-// TWINS: the tables hold clamped-border sources whose two taps fall on one index with a weight of exactly zero
-// (align_corners); the host knows from its copy of the tables, and only then the extra zero-weight products are
-// compiled in.
+// TWINS: the column table holds clamped-border sources whose two taps fall on one index with a weight of exactly
+// zero (align_corners); the host knows from its copy of the tables, and only then the extra zero-weight products of
+// the horizontal reduction are compiled in.
 template <typename TIn, typename TOut, bool TWINS>
 __global__ void __launch_bounds__(kThreads, 3)
     BilinearBwdX2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
@@ -695,39 +713,54 @@ __global__ void __launch_bounds__(kThreads, 3)
     constexpr int V = 4, VG = 8;
     constexpr int NM = VG * sizeof(TIn) / 16; // 16-byte vectors holding grads columns j0 .. j0+7
     constexpr int HE = 4 / sizeof(TIn);       // elements in a 4-byte neighbour word
+    // bits of a row record
+    constexpr int kLoA = 1, kHiA = 4, kHiB = 8, kFlushShift = 4;
     extern __shared__ __align__(16) unsigned char x2Smem[];
-    float* rowTaps = reinterpret_cast<float*>(x2Smem); // [tileRows][6]: five weights and the tap mask
-    const int32_t wout = 2 * win, hout = 2 * hin;
-    const int32_t ya = blockIdx.y * tileRows, yb = min(hin, ya + tileRows);
+    float4* rowRec = reinterpret_cast<float4*>(x2Smem); // per grads row of the tile: {1-d, d, bits, -}
+    const int32_t wout = 2 * win;
     const int32_t tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
-    // queue: [kX2Depth][nthreads] 16-byte vectors (NM per entry), then the left and right neighbour words
-    uint4* qMid = reinterpret_cast<uint4*>(x2Smem + ((static_cast<size_t>(tileRows) * 6 * sizeof(float) + 15) & ~size_t(15)));
-    uint32_t* qLeft = reinterpret_cast<uint32_t*>(qMid + static_cast<size_t>(kX2Depth) * nthreads * NM);
-    uint32_t* qRight = qLeft + static_cast<size_t>(kX2Depth) * nthreads;
-    for (int32_t e = tid; e < (yb - ya) * 5; e += nthreads) {
-        const int32_t r = e / 5, t = e - r * 5, y = ya + r;
-        const int32_t i = 2 * y - 2 + t;
-        const bool in = i >= __ldg(rh.start + y) && i < __ldg(rh.end + y);
-        rowTaps[r * 6 + t] = in ? CombinedWeight(th, i, y) : 0.0f;
-    }
-    for (int32_t r = tid; r < yb - ya; r += nthreads) {
-        const int32_t y = ya + r;
-        int32_t mask = 0;
-        for (int t = 0; t < 5; ++t) {
-            const int32_t i = 2 * y - 2 + t;
-            const bool in = i >= __ldg(rh.start + y) && i < __ldg(rh.end + y);
-            mask |= in ? (1 << t) : 0;
-            mask |= (TWINS && in && HasZeroTwin(th, i, y)) ? (256 << t) : 0; // one more zero-weight product
-        }
-        rowTaps[r * 6 + 5] = __int_as_float(mask);
+    // queue: [kX2Depth][nthreads] entries of NM 16-byte vectors, then [kX2Depth][nthreads] {left, right} word pairs
+    unsigned char* qBase = x2Smem + static_cast<size_t>(2 * tileRows + 4) * 16;
+    const uint32_t strideMid = static_cast<uint32_t>(nthreads) * 16 * NM; // bytes between slots
+    unsigned char* midP = qBase + static_cast<size_t>(tid) * 16 * NM;
+    unsigned char* lrP = qBase + static_cast<size_t>(kX2Depth) * strideMid + static_cast<size_t>(tid) * 8;
+    // The grad_input rows of all plane groups form one sequence (group-major); the blocks cut it into gridDim.x equal
+    // runs, so that one wave of resident blocks finishes together whatever the number of planes. A run is walked as
+    // tiles: its pieces of consecutive plane groups, none taller than tileRows.
+    const int64_t planeGroups = (planes + blockDim.y - 1) / blockDim.y;
+    const int64_t totalRows = planeGroups * hin;
+    const int64_t share = totalRows / gridDim.x, rest = totalRows - share * gridDim.x; // the first `rest` runs get one more
+    int64_t pos = share * blockIdx.x + min(static_cast<int64_t>(blockIdx.x), rest);
+    const int64_t end = pos + share + (blockIdx.x < rest ? 1 : 0);
+    while (pos < end) {
+    const int64_t pg = pos / hin;
+    const int32_t ya = static_cast<int32_t>(pos - pg * hin);
+    const int32_t yb = static_cast<int32_t>(min(static_cast<int64_t>(min(hin, ya + tileRows)), ya + (end - pos)));
+    pos += yb - ya;
+    // grads rows [first, first + count) feed grad_input rows [ya, yb)
+    const int32_t first = __ldg(rh.start + ya);
+    const int32_t count = min(max(first, __ldg(rh.end + yb - 1)) - first, 2 * tileRows + 4);
+    __syncthreads(); // the previous tile's records are no longer read
+    for (int32_t n = tid; n < count; n += nthreads) {
+        const int32_t i = first + n;
+        const int32_t lo = __ldg(th.lo + i), hi = __ldg(th.hi + i);
+        const float d = __ldg(th.delta + i);
+        // the older open row when row i is added: rows below lo[i] are complete
+        const int32_t cur = max(ya, lo);
+        const int32_t prev = n > 0 ? max(ya, __ldg(th.lo + i - 1)) : ya;
+        int32_t bits = (cur - prev) << kFlushShift;
+        bits |= (lo == cur) ? kLoA : 0;
+        bits |= (hi == cur) ? kHiA : 0;
+        bits |= (hi == cur + 1 && hi < yb) ? kHiB : 0;
+        rowRec[n] = make_float4(Sub(1.0f, d), d, __int_as_float(bits), 0.0f);
     }
     __syncthreads();
-    const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.y + threadIdx.y;
+    const int64_t p = pg * blockDim.y + threadIdx.y;
     if (p >= planes) {
-        return;
+        continue; // the barriers above are reached by every thread of the block in every tile
     }
     const int32_t groups = win / V;
-    const TIn* gp = go + p * hout * static_cast<int64_t>(wout);
+    const TIn* gp = go + p * (2 * static_cast<int64_t>(hin)) * wout;
     TOut* op = gi + p * hin * static_cast<int64_t>(win);
     for (int32_t g = threadIdx.x; g < groups; g += blockDim.x) {
         const int32_t x0 = g * V, j0 = 2 * x0;
@@ -748,64 +781,50 @@ __global__ void __launch_bounds__(kThreads, 3)
         }
         const bool extra = x0 == 0 && win > 1; // column 1 also takes grads column 0 (zero weight), as for rows
         const float wExtra = extra ? CombinedWeight(tw, 0, 1) : 0.0f;
-        // stream of grads rows: element n of the stream is row first + n, for n < count
-        const int32_t first = 2 * ya - 2, count = 2 * (yb - ya) + 3;
-        // one commit group per stream element, empty for rows outside the plane; elements are issued in order, so
-        // the source row advances by one row per call
+        // one commit group per stream element (empty past the end); elements are issued in order, so the source
+        // advances by one row per call
         const TIn* issueRow = gp + static_cast<int64_t>(first) * wout + j0;
-        int32_t issueIdx = first; // grads row of the next element to issue
         int32_t issueLeft = count;
-        auto issue = [&]() {
-            if (issueLeft > 0 && issueIdx >= 0 && issueIdx < hout) {
-                const int32_t slot = ((issueIdx - first) & (kX2Depth - 1)) * nthreads + tid;
+        auto issue = [&](unsigned char* pm, unsigned char* plr) {
+            if (issueLeft > 0) {
 #pragma unroll
                 for (int m = 0; m < NM; ++m) {
-                    CpAsync16(qMid + static_cast<size_t>(slot) * NM + m, reinterpret_cast<const uint4*>(issueRow) + m);
+                    CpAsync16(pm + 16 * m, reinterpret_cast<const uint4*>(issueRow) + m);
                 }
                 if (hasLeft) { // the word holding column j0-1 (4-byte aligned: j0 is a multiple of 8)
-                    CpAsync4(qLeft + slot, issueRow - HE);
+                    CpAsync4(plr, issueRow - HE);
                 }
                 if (hasRight) {
-                    CpAsync4(qRight + slot, issueRow + VG);
+                    CpAsync4(plr + 4, issueRow + VG);
                 }
             }
             issueRow += wout;
-            ++issueIdx;
             --issueLeft;
             CpAsyncCommit();
         };
-        // Reduced row n of the stream (zeros outside the plane). Waits until all but the newest kX2Depth-1 groups
-        // have landed, i.e. until element n has, then refills the slot with element n + kX2Depth.
+        // Reduced row n of the stream. Waits until all but the newest kX2Depth-1 groups have landed, i.e. until
+        // element n has, then refills its slot with element n + kX2Depth.
         auto take = [&](int32_t n, float (&hp)[V]) {
             CpAsyncWait<kX2Depth - 1>();
-            const int32_t i = first + n;
+            const uint32_t off = static_cast<uint32_t>(n & (kX2Depth - 1)) * strideMid;
+            unsigned char* pm = midP + off;
+            unsigned char* plr = lrP + off / (2 * NM);
+            uint4 mid[NM];
+#pragma unroll
+            for (int m = 0; m < NM; ++m) {
+                mid[m] = reinterpret_cast<const uint4*>(pm)[m];
+            }
+            const uint2 lr = *reinterpret_cast<const uint2*>(plr);
+            issue(pm, plr);
             float v[VG + 2]; // grads columns j0-1 .. j0+8
+            const TIn* me = reinterpret_cast<const TIn*>(mid);
 #pragma unroll
-            for (int k = 0; k < VG + 2; ++k) {
-                v[k] = 0.0f;
+            for (int k = 0; k < VG; ++k) {
+                v[k + 1] = DType<TIn>::ToF(me[k]);
             }
-            if (i >= 0 && i < hout) {
-                const int32_t slot = (n & (kX2Depth - 1)) * nthreads + tid;
-                uint4 mid[NM];
-#pragma unroll
-                for (int m = 0; m < NM; ++m) {
-                    mid[m] = qMid[static_cast<size_t>(slot) * NM + m];
-                }
-                const TIn* me = reinterpret_cast<const TIn*>(mid);
-#pragma unroll
-                for (int k = 0; k < VG; ++k) {
-                    v[k + 1] = DType<TIn>::ToF(me[k]);
-                }
-                if (hasLeft) {
-                    const uint32_t wl = qLeft[slot];
-                    v[0] = DType<TIn>::ToF(reinterpret_cast<const TIn*>(&wl)[HE - 1]);
-                }
-                if (hasRight) {
-                    const uint32_t wr = qRight[slot];
-                    v[VG + 1] = DType<TIn>::ToF(reinterpret_cast<const TIn*>(&wr)[0]);
-                }
-            }
-            issue();
+            // the neighbour words are not written (and not read as numbers) where the row ends
+            v[0] = hasLeft ? DType<TIn>::ToF(reinterpret_cast<const TIn*>(&lr.x)[HE - 1]) : 0.0f;
+            v[VG + 1] = hasRight ? DType<TIn>::ToF(reinterpret_cast<const TIn*>(&lr.y)[0]) : 0.0f;
 #pragma unroll
             for (int k = 0; k < V; ++k) {
                 float a = 0.0f;
@@ -832,54 +851,62 @@ __global__ void __launch_bounds__(kThreads, 3)
         };
 #pragma unroll
         for (int n = 0; n < kX2Depth; ++n) {
-            issue();
+            issue(midP + n * strideMid, lrP + n * (strideMid / (2 * NM)));
         }
-        // window of reduced rows: P = 2y-2, A = 2y-1, B = 2y, C = 2y+1, D = 2y+2 (rows outside the plane are 0
-        // and their taps are masked off)
-        float hpP[V], hpA[V], hpB[V], hpC[V], hpD[V];
-        take(0, hpP);
-        take(1, hpA);
-        take(2, hpB);
-        int32_t n = 3;
+        float accA[V] = {0.0f, 0.0f, 0.0f, 0.0f}, accB[V] = {0.0f, 0.0f, 0.0f, 0.0f}; // rows cur and cur + 1
+        int32_t cur = ya;
         TOut* dst = op + static_cast<int64_t>(ya) * win + x0;
-        for (int32_t y = ya; y < yb; ++y) {
-            take(n, hpC);
-            take(n + 1, hpD);
-            n += 2;
-            const float* tp = rowTaps + (y - ya) * 6;
-            const int32_t mask = __float_as_int(tp[5]);
-            float out[V] = {0.0f, 0.0f, 0.0f, 0.0f};
-            auto tap = [&](int t, const float (&hp)[V]) {
-                if (mask & (1 << t)) { // uniform over the block; taps outside the row's range are not touched
-                    const float w = tp[t];
-#pragma unroll
-                    for (int k = 0; k < V; ++k) {
-                        out[k] = fmaf(w, hp[k], out[k]);
-                    }
-                    if (TWINS && (mask & (256 << t))) {
-#pragma unroll
-                        for (int k = 0; k < V; ++k) {
-                            out[k] = fmaf(0.0f, hp[k], out[k]);
-                        }
-                    }
-                }
-            };
-            tap(0, hpP);
-            tap(1, hpA);
-            tap(2, hpB);
-            tap(3, hpC);
-            tap(4, hpD);
-            StorePack<TOut, V>(dst, out);
+        auto flush = [&]() {
+            StorePack<TOut, V>(dst, accA);
             dst += win;
+            ++cur;
 #pragma unroll
             for (int k = 0; k < V; ++k) {
-                hpP[k] = hpB[k];
-                hpA[k] = hpC[k];
-                hpB[k] = hpD[k];
+                accA[k] = accB[k];
+                accB[k] = 0.0f;
             }
+        };
+        for (int32_t n = 0; n < count; ++n) {
+            float hp[V];
+            take(n, hp);
+            const float4 rec = rowRec[n];
+            const int32_t bits = __float_as_int(rec.z);
+            for (int32_t f = bits >> kFlushShift; f > 0; --f) { // uniform over the block
+                flush();
+            }
+            if ((bits & 15) == (kLoA | kHiB)) { // the interior case
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    accA[k] = fmaf(rec.x, hp[k], accA[k]);
+                    accB[k] = fmaf(rec.y, hp[k], accB[k]);
+                }
+            } else {
+                if (bits & kLoA) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        accA[k] = fmaf(rec.x, hp[k], accA[k]);
+                    }
+                }
+                if (bits & kHiA) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        accA[k] = fmaf(rec.y, hp[k], accA[k]);
+                    }
+                }
+                if (bits & kHiB) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        accB[k] = fmaf(rec.y, hp[k], accB[k]);
+                    }
+                }
+            }
+        }
+        while (cur < yb) {
+            flush();
         }
         CpAsyncWait<0>(); // nothing of this thread's queue is in flight when the next column group reuses it
     }
+    } // tiles of this block's run
 }
 
 // ---- forward, NHWC ----------------------------------------------------------------------------------------
@@ -1242,20 +1269,47 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, tileRows));
             const dim3 block = PlaneBlock(sh.win / 4, planes);
             const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
-            const size_t x2Smem = X2SmemBytes(tileRows, static_cast<int32_t>(block.x * block.y), sizeof(TIn));
+            // kX2: one wave of resident blocks shares the rows of all plane groups equally
+            const int32_t x2Threads = static_cast<int32_t>(block.x * block.y);
+            const int64_t x2Total = CeilDiv(planes, block.y) * sh.hin;
+            int x2PerSm = 0;
+            int32_t x2Rows = 0;
+            unsigned x2Blocks = 0;
             cudaError_t attr = cudaSuccess;
-            if (plan.schedule == BilinearPlan::kX2 && x2Smem > 48 * 1024 && x2Smem <= 100 * 1024) {
-                attr = cudaFuncSetAttribute(plan.zeroTwins ? BilinearBwdX2Kernel<TIn, TOut, true>
-                                                           : BilinearBwdX2Kernel<TIn, TOut, false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(x2Smem));
+            if (plan.schedule == BilinearPlan::kX2) {
+                auto kernel = plan.zeroTwins ? BilinearBwdX2Kernel<TIn, TOut, true> : BilinearBwdX2Kernel<TIn, TOut, false>;
+                // tile height first for a full machine at three blocks per SM, then for what really fits
+                for (int pass = 0; pass < 2 && attr == cudaSuccess; ++pass) {
+                    const int64_t slots = static_cast<int64_t>(NumSMs()) * (pass == 0 ? 3 : std::max(x2PerSm, 1));
+                    const int64_t blocks = std::max<int64_t>(1, std::min(slots, x2Total / 8));
+                    x2Blocks = static_cast<unsigned>(blocks);
+                    x2Rows = static_cast<int32_t>(std::min<int64_t>(sh.hin, CeilDiv(x2Total, blocks)));
+                    const size_t bytes = X2SmemBytes(x2Rows, x2Threads, sizeof(TIn));
+                    if (bytes > 100 * 1024) {
+                        attr = cudaErrorInvalidValue;
+                        break;
+                    }
+                    if (bytes > 48 * 1024) {
+                        attr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    static_cast<int>(bytes));
+                    }
+                    if (attr == cudaSuccess) {
+                        attr = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&x2PerSm, kernel, x2Threads, bytes);
+                    }
+                    if (attr == cudaSuccess && x2PerSm < 1) {
+                        attr = cudaErrorInvalidValue;
+                    }
+                }
+                (void)cudaGetLastError();
             }
-            if (plan.schedule == BilinearPlan::kX2 && x2Smem <= 100 * 1024 && attr == cudaSuccess) {
+            if (plan.schedule == BilinearPlan::kX2 && attr == cudaSuccess) {
+                const size_t x2Smem = X2SmemBytes(x2Rows, x2Threads, sizeof(TIn));
                 if (plan.zeroTwins) {
-                    BilinearBwdX2Kernel<TIn, TOut, true><<<grid, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win, th,
-                                                                                     tw, rh, tileRows);
+                    BilinearBwdX2Kernel<TIn, TOut, true><<<x2Blocks, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win,
+                                                                                         th, tw, rh, x2Rows);
                 } else {
-                    BilinearBwdX2Kernel<TIn, TOut, false><<<grid, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win, th,
-                                                                                      tw, rh, tileRows);
+                    BilinearBwdX2Kernel<TIn, TOut, false><<<x2Blocks, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win,
+                                                                                          th, tw, rh, x2Rows);
                 }
             } else {
                 BilinearBwdW2Kernel<TIn, TOut><<<grid, block, 0, s>>>(pg, po, planes, sh.hin, sh.win, sh.hout, th, tw,
