@@ -273,12 +273,24 @@ __global__ void __launch_bounds__(kThreads, 3)
     uint32_t* qLeft = reinterpret_cast<uint32_t*>(qMid + static_cast<size_t>(kFwdQueueDepth) * nthreads);
     uint32_t* qRight = qLeft + static_cast<size_t>(kFwdQueueDepth) * nthreads;
     const int32_t wout = 2 * win;
-    // block = (column threads, planes): every thread of a block walks the same rows, so the row logic is uniform
-    const int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.y + threadIdx.y;
+    // block = (column threads, planes): every thread of a block walks the same rows, so the row logic is uniform.
+    // The output rows of all plane groups form one sequence (group-major); the blocks cut it into gridDim.x equal
+    // runs, so that one wave of resident blocks finishes together whatever the number of planes. A run is walked as
+    // tiles: its pieces of consecutive plane groups, none taller than tileRows.
+    const int64_t planeGroups = (planes + blockDim.y - 1) / blockDim.y;
+    const int64_t totalRows = planeGroups * hout;
+    const int64_t share = totalRows / gridDim.x, rest = totalRows - share * gridDim.x; // the first `rest` runs get one more
+    int64_t pos = share * blockIdx.x + min(static_cast<int64_t>(blockIdx.x), rest);
+    const int64_t end = pos + share + (blockIdx.x < rest ? 1 : 0);
+    while (pos < end) {
+    const int64_t pg = pos / hout;
+    const int32_t ha = static_cast<int32_t>(pos - pg * hout);
+    const int32_t hb = static_cast<int32_t>(min(static_cast<int64_t>(min(hout, ha + tileRows)), ha + (end - pos)));
+    pos += hb - ha;
+    const int64_t p = pg * blockDim.y + threadIdx.y;
     if (p >= planes) {
-        return;
+        continue;
     }
-    const int32_t ha = blockIdx.y * tileRows, hb = min(hout, ha + tileRows);
     const int32_t groups = win / VI;
     const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
     const T* xp = x + p * hin * static_cast<int64_t>(win);
@@ -417,6 +429,7 @@ __global__ void __launch_bounds__(kThreads, 3)
             CpAsyncWait<0>(); // nothing of this thread's queue is in flight when the next column group reuses it
         }
     }
+    } // tiles of this block's run
 }
 
 // ---- backward row walk ---------------------------------------------------------------------------------------
@@ -1461,13 +1474,13 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
             if (w2Ok) {
                 // 16-bit tensors: eight input columns (one 16-byte load) per thread when the rows allow it
                 const int vi = (sizeof(T) == 2 && sh.win % 8 == 0 && Aligned(x, 16)) ? 8 : 4;
-                // every tile interpolates one extra input row and sets up its column weights again: taller tiles
-                // measured faster (28 rows: 64 us, 11 rows: 68 us on fp16 32x256x56x56 -> 112x112)
-                const int32_t tileRows =
-                    std::max(RowsForOccupancy(planes * (sh.win / vi), sh.hout), std::min(sh.hout, 28));
-                const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, tileRows));
+                // one wave of resident blocks shares the output rows of all plane groups equally (three blocks per
+                // SM: the kernels' launch bound); runs of at least 8 rows
+                const int32_t tileRows = sh.hout;
                 const dim3 block = PlaneBlock(sh.win / vi, planes);
-                const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
+                const int64_t totalRows = CeilDiv(planes, block.y) * sh.hout;
+                const dim3 grid(static_cast<unsigned>(
+                    std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(NumSMs()) * 3, totalRows / 8))));
                 // a thread writes 2 * vi elements per row; when that is 32 bytes and the rows are 32-byte aligned
                 // they go out as one 32-byte store
                 const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0) ? 1 : 0;
