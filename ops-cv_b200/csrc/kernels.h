@@ -90,6 +90,10 @@ struct BilinearPlan {
     int32_t tapsW;    // kTiled backward: most grads columns feeding one grad_input column
     int32_t planesPerBlock; // kTiled: planes whose bands share one block's shared memory
     bool zeroTwins;         // backward: the tables hold clamped-border sources with a zero-weight twin tap
+    // kW2 forward: the column weights repeat with period two from column 1 on (delta[w] == delta[w-2] for w >= 3),
+    // so the kernel takes them as three scalars (column 0, even columns, odd columns) instead of table reads
+    bool periodicW;
+    float dxFirst, dxEven, dxOdd;
 };
 BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
 BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);

@@ -26,6 +26,7 @@
 // Reference arithmetic: image/resize_bilinear_v2/op_kernel/arch35/resize_bilinear_v2_simt_nchw.h:84-146,
 // _simt_nhwc.h:88-151; image/resize_bilinear_v2_grad/op_kernel/arch35/resize_bilinear_v2_grad_simt.h:107-152.
 #include <algorithm>
+#include <cstring>
 
 #include "host_tables.h"
 #include "launch_util.cuh"
@@ -259,10 +260,16 @@ __device__ __forceinline__ void CpAsyncWait()
 constexpr int kFwdQueueDepth = 4;
 
 // QUEUE (needs VI * sizeof(T) == 16): the input rows stream through a per-thread cp.async queue.
-template <typename T, int VI, bool QUEUE>
-__global__ void __launch_bounds__(kThreads, 3)
+// PERIODIC: the column weights are the three scalars (dxFirst for output column 0, dxEven, dxOdd) instead of tw.delta.
+// Seven warps per block: three resident blocks then leave 96 registers per thread, which the two row buffers of the
+// 16-column variant need (at 256 threads and 80 registers the walk spilled and recomputed its weights).
+constexpr int kW2Threads = 128;
+
+template <typename T, int VI, bool QUEUE, bool PERIODIC>
+__global__ void __launch_bounds__(kW2Threads, 5)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
-                        int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores)
+                        int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores, float dxFirst,
+                        float dxEven, float dxOdd)
 {
     constexpr int VO = 2 * VI;
     constexpr int HE = 4 / sizeof(T); // elements in a 4-byte neighbour word
@@ -298,12 +305,19 @@ __global__ void __launch_bounds__(kThreads, 3)
     for (int32_t g = cg0; g < groups; g += colThreads) {
         const int32_t c0 = g * VI;
         const int32_t cl = max(c0 - 1, 0), cr = min(c0 + VI, win - 1);
-        float dx[VO], dx1[VO];
+        float dx[PERIODIC ? 1 : VO], dx1[PERIODIC ? 1 : VO];
+        if constexpr (!PERIODIC) {
 #pragma unroll
-        for (int k = 0; k < VO; ++k) {
-            dx[k] = __ldg(tw.delta + c0 * 2 + k);
-            dx1[k] = Sub(1.0f, dx[k]);
+            for (int k = 0; k < VO; ++k) {
+                dx[k] = __ldg(tw.delta + c0 * 2 + k);
+                dx1[k] = Sub(1.0f, dx[k]);
+            }
         }
+        // PERIODIC: only this thread's first output column can differ from the two repeating weights
+        const float dxHead = c0 == 0 ? dxFirst : dxEven;
+        const float dxHead1 = Sub(1.0f, dxHead), dxEven1 = Sub(1.0f, dxEven), dxOdd1 = Sub(1.0f, dxOdd);
+        auto wR = [&](int k) { return PERIODIC ? (k == 0 ? dxHead : ((k & 1) ? dxOdd : dxEven)) : dx[PERIODIC ? 0 : k]; };
+        auto wL = [&](int k) { return PERIODIC ? (k == 0 ? dxHead1 : ((k & 1) ? dxOdd1 : dxEven1)) : dx1[PERIODIC ? 0 : k]; };
         // QUEUE: the input rows this walk needs are lo[ha] .. hi[hb-1], in increasing order; they stream through
         // the thread's queue kFwdQueueDepth rows ahead (one commit group per row, empty past the end).
         const int32_t lastRow = QUEUE ? __ldg(th.hi + hb - 1) : 0;
@@ -373,8 +387,8 @@ __global__ void __launch_bounds__(kThreads, 3)
 #pragma unroll
             for (int j = 0; j < VI; ++j) {
                 // outputs 2(c0+j) (taps c0+j-1, c0+j) and 2(c0+j)+1 (taps c0+j, c0+j+1)
-                h[2 * j] = Add(Mul(dx1[2 * j], v[j]), Mul(dx[2 * j], v[j + 1]));
-                h[2 * j + 1] = Add(Mul(dx1[2 * j + 1], v[j + 1]), Mul(dx[2 * j + 1], v[j + 2]));
+                h[2 * j] = Add(Mul(wL(2 * j), v[j]), Mul(wR(2 * j), v[j + 1]));
+                h[2 * j + 1] = Add(Mul(wL(2 * j + 1), v[j + 1]), Mul(wR(2 * j + 1), v[j + 2]));
             }
         };
         // Two row buffers; which of them holds the upper row alternates, so a row that moves from "lower" to "upper"
@@ -1242,10 +1256,10 @@ bool IsW2BackwardPattern(const host::Ranges& r, int32_t in, int32_t out)
 }
 
 // Block shape (column threads, planes per block).
-dim3 PlaneBlock(int32_t groups, int64_t planes, int32_t maxPlanes = 256)
+dim3 PlaneBlock(int32_t groups, int64_t planes, int32_t maxPlanes = 256, int32_t maxThreads = kThreads)
 {
-    const int32_t ct = std::max(1, std::min(groups, kThreads));
-    int64_t pb = std::max(1, kThreads / ct);
+    const int32_t ct = std::max(1, std::min(groups, maxThreads));
+    int64_t pb = std::max(1, maxThreads / ct);
     pb = std::min<int64_t>({pb, planes, static_cast<int64_t>(maxPlanes)});
     return dim3(static_cast<unsigned>(ct), static_cast<unsigned>(std::max<int64_t>(pb, 1)), 1);
 }
@@ -1386,6 +1400,13 @@ BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, Axis
     const host::Lerp tW = host::LerpTable(sh.win, sh.wout, gw.scale, halfPixel, 0);
     if (sh.win % 4 == 0 && IsW2ForwardPattern(tW, sh.win)) {
         plan.schedule = BilinearPlan::kW2;
+        plan.periodicW = true;
+        for (int32_t w = 3; w < sh.wout; ++w) {
+            plan.periodicW = plan.periodicW && std::memcmp(&tW.delta[w], &tW.delta[w - 2], sizeof(float)) == 0;
+        }
+        plan.dxFirst = tW.delta[0];
+        plan.dxEven = tW.delta[2];
+        plan.dxOdd = tW.delta[1];
         return plan;
     }
     // Several planes share a block (uniform row walks, full warps even for narrow images); their bands share the
@@ -1474,28 +1495,46 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
             if (w2Ok) {
                 // 16-bit tensors: eight input columns (one 16-byte load) per thread when the rows allow it
                 const int vi = (sizeof(T) == 2 && sh.win % 8 == 0 && Aligned(x, 16)) ? 8 : 4;
-                // one wave of resident blocks shares the output rows of all plane groups equally (three blocks per
-                // SM: the kernels' launch bound); runs of at least 8 rows
+                // one wave of resident blocks shares the output rows of all plane groups equally; runs of at
+                // least 8 rows
                 const int32_t tileRows = sh.hout;
-                const dim3 block = PlaneBlock(sh.win / vi, planes);
+                const dim3 block = PlaneBlock(sh.win / vi, planes, 256, kW2Threads);
                 const int64_t totalRows = CeilDiv(planes, block.y) * sh.hout;
-                const dim3 grid(static_cast<unsigned>(
-                    std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(NumSMs()) * 3, totalRows / 8))));
                 // a thread writes 2 * vi elements per row; when that is 32 bytes and the rows are 32-byte aligned
                 // they go out as one 32-byte store
                 const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0) ? 1 : 0;
                 // 16-byte pieces (fp32 x 4, 16-bit x 8) stream through the per-thread queue
                 const size_t qBytes = static_cast<size_t>(kFwdQueueDepth) * block.x * block.y * 24;
+                auto launch = [&](auto kernel, size_t smem) {
+                    int perSm = 0;
+                    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, static_cast<int>(block.x * block.y),
+                                                                      smem) != cudaSuccess || perSm < 1) {
+                        (void)cudaGetLastError();
+                        perSm = 1;
+                    }
+                    const dim3 grid(static_cast<unsigned>(std::max<int64_t>(
+                        1, std::min<int64_t>(static_cast<int64_t>(NumSMs()) * perSm, totalRows / 8))));
+                    kernel<<<grid, block, smem, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide,
+                                                     plan.dxFirst, plan.dxEven, plan.dxOdd);
+                };
                 if (vi == 8) {
                     if constexpr (sizeof(T) == 2) {
-                        BilinearFwdW2Kernel<T, 8, true><<<grid, block, qBytes, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
+                        if (plan.periodicW) {
+                            launch(BilinearFwdW2Kernel<T, 8, true, true>, qBytes);
+                        } else {
+                            launch(BilinearFwdW2Kernel<T, 8, true, false>, qBytes);
+                        }
                     }
                 } else if (sizeof(T) == 4) {
                     if constexpr (sizeof(T) == 4) {
-                        BilinearFwdW2Kernel<T, 4, true><<<grid, block, qBytes, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
+                        if (plan.periodicW) {
+                            launch(BilinearFwdW2Kernel<T, 4, true, true>, qBytes);
+                        } else {
+                            launch(BilinearFwdW2Kernel<T, 4, true, false>, qBytes);
+                        }
                     }
                 } else {
-                    BilinearFwdW2Kernel<T, 4, false><<<grid, block, 0, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide);
+                    launch(BilinearFwdW2Kernel<T, 4, false, false>, 0);
                 }
             } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
