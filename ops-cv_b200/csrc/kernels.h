@@ -94,6 +94,8 @@ struct BilinearPlan {
     // so the kernel takes them as three scalars (column 0, even columns, odd columns) instead of table reads
     bool periodicW;
     float dxFirst, dxEven, dxOdd;
+    // kX2 backward with periodicW: the four column weights shared by every grad_input column but the first and last
+    float bw[4];
 };
 BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
 BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);

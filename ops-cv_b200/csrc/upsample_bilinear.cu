@@ -721,24 +721,31 @@ __global__ void __launch_bounds__(kThreads)
 // memory holds several times what the registers could.
 // What a grads row does to the open rows (its two weights, which of the open rows they go to, how many finished rows
 // to store first) is the same for every thread: it is evaluated once per block into shared memory.
-constexpr int kX2Depth = 8; // a power of two: the slot of a stream element is a mask away
+// rows in flight per thread (a power of two: the slot of a stream element is a mask away); the same bytes for both widths
+constexpr int X2Depth(int cols) { return cols == 8 ? 4 : 8; }
 
-inline size_t X2SmemBytes(int32_t tileRows, int32_t threads, int elemSize)
+inline size_t X2SmemBytes(int32_t tileRows, int32_t threads, int elemSize, int cols)
 {
     const size_t recs = static_cast<size_t>(2 * tileRows + 4) * 16; // one 16-byte record per grads row of the tile
-    return recs + static_cast<size_t>(kX2Depth) * threads * (8 * elemSize + 8);
+    return recs + static_cast<size_t>(X2Depth(cols)) * threads * (2 * cols * elemSize + 8);
 }
 
 // TWINS: the column table holds clamped-border sources whose two taps fall on one index with a weight of exactly
 // zero (align_corners); the host knows from its copy of the tables, and only then the extra zero-weight products of
 // the horizontal reduction are compiled in.
-template <typename TIn, typename TOut, bool TWINS>
-__global__ void __launch_bounds__(kThreads, 3)
+// V: grad_input columns per thread (4, or 8 with PERIODIC and 16-bit tensors).
+// PERIODIC: the host has checked that the four column weights of a grad_input column are the same for every column
+// but the first and the last of a row; they arrive as scalars (pw0..pw3) and only the two border weights are read
+// from the table, which frees the registers a second group of four columns needs.
+template <typename TIn, typename TOut, bool TWINS, int V, bool PERIODIC>
+__global__ void __launch_bounds__(kW2Threads, 5)
     BilinearBwdX2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
-                        LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows)
+                        LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows, float pw0, float pw1, float pw2,
+                        float pw3)
 {
-    constexpr int V = 4, VG = 8;
-    constexpr int NM = VG * sizeof(TIn) / 16; // 16-byte vectors holding grads columns j0 .. j0+7
+    constexpr int VG = 2 * V;
+    constexpr int kX2Depth = X2Depth(V);
+    constexpr int NM = VG * sizeof(TIn) / 16; // 16-byte vectors holding grads columns j0 .. j0+VG-1
     constexpr int HE = 4 / sizeof(TIn);       // elements in a 4-byte neighbour word
     // bits of a row record
     constexpr int kLoA = 1, kHiA = 4, kHiB = 8, kFlushShift = 4;
@@ -746,7 +753,9 @@ __global__ void __launch_bounds__(kThreads, 3)
     float4* rowRec = reinterpret_cast<float4*>(x2Smem); // per grads row of the tile: {1-d, d, bits, -}
     const int32_t wout = 2 * win;
     const int32_t tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
-    // queue: [kX2Depth][nthreads] entries of NM 16-byte vectors, then [kX2Depth][nthreads] {left, right} word pairs
+    // queue: [kX2Depth][nthreads] entries of NM 16-byte vectors, then [kX2Depth][nthreads] {left, right} word pairs.
+    // A thread's vectors stay next to each other: spreading them over separate planes (no bank conflicts) doubled
+    // the L2 requests of the copies and was slower (85 us against 67 us on fp16 32x256x112x112 -> 56x56).
     unsigned char* qBase = x2Smem + static_cast<size_t>(2 * tileRows + 4) * 16;
     const uint32_t strideMid = static_cast<uint32_t>(nthreads) * 16 * NM; // bytes between slots
     unsigned char* midP = qBase + static_cast<size_t>(tid) * 16 * NM;
@@ -793,19 +802,34 @@ __global__ void __launch_bounds__(kThreads, 3)
         const int32_t x0 = g * V, j0 = 2 * x0;
         const bool hasLeft = j0 > 0, hasRight = j0 + VG < wout;
         // wx[k][t]: weight of grads column 2*(x0+k) - 1 + t for grad_input column x0+k (0 outside the row)
-        float wx[V][4];
+        float wx[PERIODIC ? 1 : V][4];
         uint32_t zeroTwins = 0; // bit k * 4 + t: that source adds one more zero-weight product (clamped border)
+        if constexpr (!PERIODIC) {
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
+            for (int k = 0; k < V; ++k) {
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const int32_t j = j0 + 2 * k - 1 + t;
-                wx[k][t] = (j >= 0 && j < wout) ? CombinedWeight(tw, j, x0 + k) : 0.0f;
-                if (TWINS && j >= 0 && j < wout && HasZeroTwin(tw, j, x0 + k)) {
-                    zeroTwins |= 1u << (k * 4 + t);
+                for (int t = 0; t < 4; ++t) {
+                    const int32_t j = j0 + 2 * k - 1 + t;
+                    wx[k][t] = (j >= 0 && j < wout) ? CombinedWeight(tw, j, x0 + k) : 0.0f;
+                    if (TWINS && j >= 0 && j < wout && HasZeroTwin(tw, j, x0 + k)) {
+                        zeroTwins |= 1u << (k * 4 + t);
+                    }
                 }
             }
         }
+        // PERIODIC: grads column 0 feeds column 0 and grads column wout-1 feeds column win-1 with their own weights;
+        // the taps that fall outside the row multiply a zero
+        const float wHead = (PERIODIC && x0 == 0) ? CombinedWeight(tw, 0, 0) : pw1;
+        const float wTail = (PERIODIC && x0 + V == win) ? CombinedWeight(tw, wout - 1, win - 1) : pw2;
+        auto weight = [&](int k, int t) {
+            if constexpr (PERIODIC) {
+                return (k == 0 && t == 1)
+                           ? wHead
+                           : ((k == V - 1 && t == 2) ? wTail : (t == 0 ? pw0 : (t == 1 ? pw1 : (t == 2 ? pw2 : pw3))));
+            } else {
+                return wx[k][t];
+            }
+        };
         const bool extra = x0 == 0 && win > 1; // column 1 also takes grads column 0 (zero weight), as for rows
         const float wExtra = extra ? CombinedWeight(tw, 0, 1) : 0.0f;
         // one commit group per stream element (empty past the end); elements are issued in order, so the source
@@ -857,7 +881,7 @@ __global__ void __launch_bounds__(kThreads, 3)
                 float a = 0.0f;
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                    a = fmaf(wx[k][t], v[2 * k + t], a);
+                    a = fmaf(weight(k, t), v[2 * k + t], a);
                 }
                 hp[k] = a;
             }
@@ -880,7 +904,12 @@ __global__ void __launch_bounds__(kThreads, 3)
         for (int n = 0; n < kX2Depth; ++n) {
             issue(midP + n * strideMid, lrP + n * (strideMid / (2 * NM)));
         }
-        float accA[V] = {0.0f, 0.0f, 0.0f, 0.0f}, accB[V] = {0.0f, 0.0f, 0.0f, 0.0f}; // rows cur and cur + 1
+        float accA[V], accB[V]; // rows cur and cur + 1
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            accA[k] = 0.0f;
+            accB[k] = 0.0f;
+        }
         int32_t cur = ya;
         TOut* dst = op + static_cast<int64_t>(ya) * win + x0;
         auto flush = [&]() {
@@ -1294,24 +1323,29 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
                 tileRows = std::max(tileRows, std::min(sh.hin, 28));
             }
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, tileRows));
-            const dim3 block = PlaneBlock(sh.win / 4, planes);
+            const bool x2 = plan.schedule == BilinearPlan::kX2;
+            // kX2 with periodic weights and 16-bit tensors: eight grad_input columns per thread
+            const bool x2Wide = x2 && plan.periodicW && sizeof(TIn) == 2 && sizeof(TOut) == 2 && sh.win % 8 == 0 &&
+                                Aligned(gi, 16);
+            const int32_t x2Cols = x2Wide ? 8 : 4;
+            const dim3 block = PlaneBlock(sh.win / x2Cols, planes, 256, x2 ? kW2Threads : kThreads);
             const dim3 grid(static_cast<unsigned>(CeilDiv(planes, block.y)), static_cast<unsigned>(tiles));
             // kX2: one wave of resident blocks shares the rows of all plane groups equally
             const int32_t x2Threads = static_cast<int32_t>(block.x * block.y);
             const int64_t x2Total = CeilDiv(planes, block.y) * sh.hin;
-            int x2PerSm = 0;
-            int32_t x2Rows = 0;
-            unsigned x2Blocks = 0;
             cudaError_t attr = cudaSuccess;
-            if (plan.schedule == BilinearPlan::kX2) {
-                auto kernel = plan.zeroTwins ? BilinearBwdX2Kernel<TIn, TOut, true> : BilinearBwdX2Kernel<TIn, TOut, false>;
-                // tile height first for a full machine at three blocks per SM, then for what really fits
+            auto launchX2 = [&](auto kernel) {
+                int perSm = 0;
+                int32_t rows = 0;
+                unsigned blocks = 0;
+                size_t bytes = 0;
+                // tile height first for a full machine at five blocks per SM, then for what really fits
                 for (int pass = 0; pass < 2 && attr == cudaSuccess; ++pass) {
-                    const int64_t slots = static_cast<int64_t>(NumSMs()) * (pass == 0 ? 3 : std::max(x2PerSm, 1));
-                    const int64_t blocks = std::max<int64_t>(1, std::min(slots, x2Total / 8));
-                    x2Blocks = static_cast<unsigned>(blocks);
-                    x2Rows = static_cast<int32_t>(std::min<int64_t>(sh.hin, CeilDiv(x2Total, blocks)));
-                    const size_t bytes = X2SmemBytes(x2Rows, x2Threads, sizeof(TIn));
+                    const int64_t slots = static_cast<int64_t>(NumSMs()) * (pass == 0 ? 5 : std::max(perSm, 1));
+                    const int64_t nb = std::max<int64_t>(1, std::min(slots, x2Total / 8));
+                    blocks = static_cast<unsigned>(nb);
+                    rows = static_cast<int32_t>(std::min<int64_t>(sh.hin, CeilDiv(x2Total, nb)));
+                    bytes = X2SmemBytes(rows, x2Threads, sizeof(TIn), x2Cols);
                     if (bytes > 100 * 1024) {
                         attr = cudaErrorInvalidValue;
                         break;
@@ -1321,23 +1355,33 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
                                                     static_cast<int>(bytes));
                     }
                     if (attr == cudaSuccess) {
-                        attr = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&x2PerSm, kernel, x2Threads, bytes);
+                        attr = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, x2Threads, bytes);
                     }
-                    if (attr == cudaSuccess && x2PerSm < 1) {
+                    if (attr == cudaSuccess && perSm < 1) {
                         attr = cudaErrorInvalidValue;
                     }
                 }
                 (void)cudaGetLastError();
-            }
-            if (plan.schedule == BilinearPlan::kX2 && attr == cudaSuccess) {
-                const size_t x2Smem = X2SmemBytes(x2Rows, x2Threads, sizeof(TIn));
-                if (plan.zeroTwins) {
-                    BilinearBwdX2Kernel<TIn, TOut, true><<<x2Blocks, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win,
-                                                                                         th, tw, rh, x2Rows);
-                } else {
-                    BilinearBwdX2Kernel<TIn, TOut, false><<<x2Blocks, block, x2Smem, s>>>(pg, po, planes, sh.hin, sh.win,
-                                                                                          th, tw, rh, x2Rows);
+                if (attr == cudaSuccess) {
+                    kernel<<<blocks, block, bytes, s>>>(pg, po, planes, sh.hin, sh.win, th, tw, rh, rows, plan.bw[0],
+                                                        plan.bw[1], plan.bw[2], plan.bw[3]);
                 }
+            };
+            if (x2) {
+                if (x2Wide) {
+                    if constexpr (sizeof(TIn) == 2 && sizeof(TOut) == 2) {
+                        launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 8, true>);
+                    }
+                } else if (plan.periodicW) {
+                    launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, true>);
+                } else if (plan.zeroTwins) {
+                    launchX2(BilinearBwdX2Kernel<TIn, TOut, true, 4, false>);
+                } else {
+                    launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, false>);
+                }
+            }
+            if (x2 && attr == cudaSuccess) {
+                // launched above
             } else {
                 BilinearBwdW2Kernel<TIn, TOut><<<grid, block, 0, s>>>(pg, po, planes, sh.hin, sh.win, sh.hout, th, tw,
                                                                       rh, tileRows);
@@ -1454,6 +1498,29 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
     plan.zeroTwins = hasTwins(tH) || hasTwins(tW);
     if (sh.win % 4 == 0 && IsW2BackwardPattern(rW, sh.win, sh.wout)) {
         plan.schedule = IsW2BackwardPattern(rH, sh.hin, sh.hout) ? BilinearPlan::kX2 : BilinearPlan::kW2;
+        // weight of grads column j for grad_input column x, as the kernels combine it
+        auto combined = [&](int32_t j, int32_t x) {
+            float w = 0.0f;
+            if (tW.lo[j] == x) {
+                w = 1.0f - tW.delta[j];
+            }
+            if (tW.hi[j] == x) {
+                w = w + tW.delta[j];
+            }
+            return w;
+        };
+        plan.periodicW = plan.schedule == BilinearPlan::kX2 && !plan.zeroTwins && sh.win >= 3;
+        if (plan.periodicW) {
+            for (int t = 0; t < 4; ++t) {
+                plan.bw[t] = combined(1 + t, 1);
+            }
+            for (int32_t x = 1; x + 1 < sh.win && plan.periodicW; ++x) {
+                for (int t = 0; t < 4; ++t) {
+                    const float w = combined(2 * x - 1 + t, x);
+                    plan.periodicW = plan.periodicW && std::memcmp(&w, &plan.bw[t], sizeof(float)) == 0;
+                }
+            }
+        }
         return plan;
     }
     int32_t taps = 0;
