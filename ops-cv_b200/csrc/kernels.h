@@ -94,6 +94,9 @@ struct BilinearPlan {
     // so the kernel takes them as three scalars (column 0, even columns, odd columns) instead of table reads
     bool periodicW;
     float dxFirst, dxEven, dxOdd;
+    // forward, 16-bit tensors: 24 minus the most significant bits any column weight or its complement has; a value
+    // of T with at most this many significand bits times a weight is exact in fp32 (0: unknown, never assume it)
+    int32_t weightSlack;
     // kX2 backward with periodicW: the four column weights shared by every grad_input column but the first and last
     float bw[4];
 };

@@ -27,6 +27,7 @@
 // _simt_nhwc.h:88-151; image/resize_bilinear_v2_grad/op_kernel/arch35/resize_bilinear_v2_grad_simt.h:107-152.
 #include <algorithm>
 #include <cstring>
+#include <type_traits>
 
 #include "host_tables.h"
 #include "launch_util.cuh"
@@ -265,7 +266,9 @@ constexpr int kFwdQueueDepth = 4;
 // 16-column variant need (at 256 threads and 80 registers the walk spilled and recomputed its weights).
 constexpr int kW2Threads = 128;
 
-template <typename T, int VI, bool QUEUE, bool PERIODIC>
+// FUSE (with PERIODIC, 16-bit T): the host has checked that every column weight times any value of T is exact in
+// fp32, so the horizontal interpolation may use one fused multiply-add: same bits, one instruction fewer.
+template <typename T, int VI, bool QUEUE, bool PERIODIC, bool FUSE = false>
 __global__ void __launch_bounds__(kW2Threads, 5)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores, float dxFirst,
@@ -387,8 +390,13 @@ __global__ void __launch_bounds__(kW2Threads, 5)
 #pragma unroll
             for (int j = 0; j < VI; ++j) {
                 // outputs 2(c0+j) (taps c0+j-1, c0+j) and 2(c0+j)+1 (taps c0+j, c0+j+1)
-                h[2 * j] = Add(Mul(wL(2 * j), v[j]), Mul(wR(2 * j), v[j + 1]));
-                h[2 * j + 1] = Add(Mul(wL(2 * j + 1), v[j + 1]), Mul(wR(2 * j + 1), v[j + 2]));
+                if constexpr (FUSE) {
+                    h[2 * j] = fmaf(wR(2 * j), v[j + 1], Mul(wL(2 * j), v[j]));
+                    h[2 * j + 1] = fmaf(wR(2 * j + 1), v[j + 2], Mul(wL(2 * j + 1), v[j + 1]));
+                } else {
+                    h[2 * j] = Add(Mul(wL(2 * j), v[j]), Mul(wR(2 * j), v[j + 1]));
+                    h[2 * j + 1] = Add(Mul(wL(2 * j + 1), v[j + 1]), Mul(wR(2 * j + 1), v[j + 2]));
+                }
             }
         };
         // Two row buffers; which of them holds the upper row alternates, so a row that moves from "lower" to "upper"
@@ -976,7 +984,9 @@ __global__ void __launch_bounds__(kW2Threads, 5)
 // is one contiguous run, and neighbouring columns find their shared input pixels in L1.
 // QUEUE (16-byte channel vectors): the two pixels a thread needs of every input row stream through a per-thread
 // cp.async queue kFwdQueueDepth rows ahead; without it the walk exposes one memory latency per new input row.
-template <typename T, int V, bool QUEUE>
+// FUSE (16-bit T): the host has checked that every column weight times any value of T is exact in fp32, so the
+// horizontal interpolation uses one fused multiply-add: same bits, one instruction fewer.
+template <typename T, int V, bool QUEUE, bool FUSE = false>
 __global__ void __launch_bounds__(kThreads)
     BilinearFwdNHWCKernel(const T* __restrict__ x, T* __restrict__ y, int32_t c, int32_t hin, int32_t win,
                           int32_t hout, int32_t wout, LerpAxis th, LerpAxis tw, int32_t rows, int32_t rowChunks,
@@ -1052,7 +1062,7 @@ __global__ void __launch_bounds__(kThreads)
             }
 #pragma unroll
             for (int k = 0; k < V; ++k) {
-                dst[k] = Add(Mul(dx1, l[k]), Mul(dx, rr[k]));
+                dst[k] = FUSE ? fmaf(dx, rr[k], Mul(dx1, l[k])) : Add(Mul(dx1, l[k]), Mul(dx, rr[k]));
             }
         };
         for (int32_t h = h0; h < h1; ++h) {
@@ -1254,6 +1264,27 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 
+// Significant bits of a weight (0 for zero). A weight of b bits times a 16-bit value of m significand bits is exact in
+// fp32 when b + m <= 24; a fused multiply-add then gives the same bits as the reference's multiply, multiply, add.
+int SignificantBits(float w)
+{
+    uint32_t u;
+    std::memcpy(&u, &w, sizeof(u));
+    if ((u & 0x7fffffffu) == 0) {
+        return 0;
+    }
+    if (((u >> 23) & 0xffu) == 0) {
+        return 24; // subnormal: not worth reasoning about
+    }
+    uint32_t m = (u & 0x7fffffu) | 0x800000u;
+    int bits = 24;
+    while ((m & 1u) == 0) {
+        m >>= 1;
+        --bits;
+    }
+    return bits;
+}
+
 bool IsW2ForwardPattern(const host::Lerp& t, int32_t in)
 {
     const int32_t out = static_cast<int32_t>(t.lo.size());
@@ -1437,6 +1468,14 @@ BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, Axis
     BilinearPlan plan{};
     plan.schedule = BilinearPlan::kDirect;
     if (lay != kNCHW) {
+        if (DtSize(dt) == 2) { // can the 16-bit walker fuse its horizontal interpolation?
+            const host::Lerp tW = host::LerpTable(sh.win, sh.wout, gw.scale, halfPixel, 0);
+            int bits = 0;
+            for (float d : tW.delta) {
+                bits = std::max({bits, SignificantBits(d), SignificantBits(1.0f - d)});
+            }
+            plan.weightSlack = 24 - bits;
+        }
         return plan;
     }
     const int es = DtSize(dt);
@@ -1451,6 +1490,11 @@ BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, Axis
         plan.dxFirst = tW.delta[0];
         plan.dxEven = tW.delta[2];
         plan.dxOdd = tW.delta[1];
+        int bits = 0;
+        for (float w : {plan.dxFirst, plan.dxEven, plan.dxOdd}) {
+            bits = std::max({bits, SignificantBits(w), SignificantBits(1.0f - w)});
+        }
+        plan.weightSlack = 24 - bits;
         return plan;
     }
     // Several planes share a block (uniform row walks, full warps even for narrow images); their bands share the
@@ -1586,7 +1630,11 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                 };
                 if (vi == 8) {
                     if constexpr (sizeof(T) == 2) {
-                        if (plan.periodicW) {
+                        // significand bits of T: 11 (fp16), 8 (bf16)
+                        const int mant = std::is_same<T, __half>::value ? 11 : 8;
+                        if (plan.periodicW && mant <= plan.weightSlack) {
+                            launch(BilinearFwdW2Kernel<T, 8, true, true, true>, qBytes);
+                        } else if (plan.periodicW) {
                             launch(BilinearFwdW2Kernel<T, 8, true, true>, qBytes);
                         } else {
                             launch(BilinearFwdW2Kernel<T, 8, true, false>, qBytes);
@@ -1650,10 +1698,20 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                     bool queued = false;
                     if constexpr (V * sizeof(T) == 16) {
                         if (Aligned(x, 16)) {
-                            BilinearFwdNHWCKernel<T, V, true>
-                                <<<blocks, kThreads, static_cast<size_t>(kFwdQueueDepth) * kThreads * 32, s>>>(
-                        static_cast<const T*>(x), static_cast<T*>(y), static_cast<int32_t>(sh.c), sh.hin, sh.win,
-                        sh.hout, sh.wout, th, tw, rows, rowChunks, walkers);
+                            const size_t qBytes = static_cast<size_t>(kFwdQueueDepth) * kThreads * 32;
+                            const int mant = std::is_same<T, __half>::value ? 11 : 8; // significand bits of T
+                            auto launch = [&](auto kernel) {
+                                kernel<<<blocks, kThreads, qBytes, s>>>(
+                                    static_cast<const T*>(x), static_cast<T*>(y), static_cast<int32_t>(sh.c), sh.hin,
+                                    sh.win, sh.hout, sh.wout, th, tw, rows, rowChunks, walkers);
+                            };
+                            if (sizeof(T) == 2 && mant <= plan.weightSlack) {
+                                if constexpr (sizeof(T) == 2) {
+                                    launch(BilinearFwdNHWCKernel<T, V, true, true>);
+                                }
+                            } else {
+                                launch(BilinearFwdNHWCKernel<T, V, true>);
+                            }
                             queued = true;
                         }
                     }
