@@ -549,11 +549,13 @@ __global__ void __launch_bounds__(1024)
                     const int32_t s = __float_as_int(m1.z), cnt = __float_as_int(m1.w);
                     const float w[kSlots] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y};
                     const float* gcol = gos + (s - i0) * wout + j;
+                    const int32_t run = min(cnt, i1 - s); // slots past the run (or past the staged rows) are not read
 #pragma unroll
                     for (int a = 0; a < kSlots; ++a) {
-                        if (a < cnt && s + a < i1) { // slots past the run (or past the staged rows) are not read
-                            v = fmaf(w[a], gcol[a * wout], v);
+                        if (a >= run) { // the same for every thread of the block
+                            break;
                         }
+                        v = fmaf(w[a], gcol[a * wout], v);
                     }
                 }
                 tbuf[ry * wout + j] = v;
