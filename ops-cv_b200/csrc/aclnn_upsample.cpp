@@ -359,11 +359,7 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
-            cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 1, th, tw, s);
-            if (e != cudaSuccess) {
-                return e;
-            }
-            e = BuildLerpBwdRanges(ah, aw, th, tw, qh, qw, s);
+            const cudaError_t e = BuildLerpBwdTablesAndRanges(ah, aw, halfPixel, th, tw, qh, qw, s);
             if (e != cudaSuccess) {
                 return e;
             }

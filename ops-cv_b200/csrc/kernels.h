@@ -50,6 +50,9 @@ cudaError_t BuildNearestBwdTables(AxisGeom h, AxisGeom w, RangeAxis th, RangeAxi
 cudaError_t BuildLerpTables(AxisGeom h, AxisGeom w, bool halfPixel, int variant, LerpAxis th, LerpAxis tw,
                             cudaStream_t s);
 // For every grad_input index y: [first, first+count) = the grad_output indices i with lo[i] == y or hi[i] == y.
+// Backward tables (variant 1) and their ranges in one launch.
+cudaError_t BuildLerpBwdTablesAndRanges(AxisGeom h, AxisGeom w, bool halfPixel, LerpAxis th, LerpAxis tw, RangeAxis rh,
+                                        RangeAxis rw, cudaStream_t s);
 cudaError_t BuildLerpBwdRanges(AxisGeom h, AxisGeom w, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw,
                                cudaStream_t s);
 // backward = true: centre rule of the reference's backward kernel (0.5 when the scale is 0).

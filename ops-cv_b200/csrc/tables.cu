@@ -5,6 +5,7 @@
 // Every expression keeps the operation order of the reference's arch35 SIMT kernels and uses the non-fusing
 // intrinsics from common.cuh, so the integer tables (source indices, window bounds) and the fp32 weights can be
 // checked bit for bit against a CPU statement of the same formulas.
+#include <algorithm>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -68,14 +69,10 @@ __global__ void NearestBwdTableKernel(AxisGeom gh, AxisGeom gw, RangeAxis th, Ra
 // ---- bilinear --------------------------------------------------------------------------------------------
 // variant 0: image/resize_bilinear_v2/op_kernel/arch35/resize_bilinear_v2_simt_nchw.h:110-133
 // variant 1: image/resize_bilinear_v2_grad/op_kernel/arch35/resize_bilinear_v2_grad_simt.h:121-135
-__global__ void LerpTableKernel(AxisGeom gh, AxisGeom gw, int halfPixel, int variant, LerpAxis th, LerpAxis tw)
+// One table entry: source index pair and weight of destination index d.
+__device__ __forceinline__ void LerpEntry(const AxisGeom& g, int halfPixel, int variant, int32_t d, int32_t& loOut,
+                                          int32_t& hiOut, float& deltaOut)
 {
-    const AxisGeom g = blockIdx.y == 0 ? gh : gw;
-    const LerpAxis t = blockIdx.y == 0 ? th : tw;
-    const int32_t d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d >= g.out) {
-        return;
-    }
     const long long last = g.in - 1;
     if (variant == 0) {
         float src;
@@ -91,9 +88,9 @@ __global__ void LerpTableKernel(AxisGeom gh, AxisGeom gw, int halfPixel, int var
         lo = lo < last ? lo : last;
         long long hi = (src > 0.0f) ? static_cast<long long>(ceilf(src)) : 0;
         hi = hi < last ? hi : last;
-        t.lo[d] = static_cast<int32_t>(lo);
-        t.hi[d] = static_cast<int32_t>(hi);
-        t.delta[d] = Sub(src, floorf(src));
+        loOut = static_cast<int32_t>(lo);
+        hiOut = static_cast<int32_t>(hi);
+        deltaOut = Sub(src, floorf(src));
     } else {
         const float offset = halfPixel ? 0.5f : 0.0f;
         float src = Sub(Mul(Add(static_cast<float>(d), offset), g.scale), offset);
@@ -102,10 +99,82 @@ __global__ void LerpTableKernel(AxisGeom gh, AxisGeom gw, int halfPixel, int var
         lo = lo < last ? lo : last;
         const float delta = fminf(fmaxf(Sub(src, static_cast<float>(lo)), 0.0f), 1.0f);
         const long long hi = (lo < last) ? lo + 1 : lo;
-        t.lo[d] = static_cast<int32_t>(lo);
-        t.hi[d] = static_cast<int32_t>(hi);
-        t.delta[d] = delta;
+        loOut = static_cast<int32_t>(lo);
+        hiOut = static_cast<int32_t>(hi);
+        deltaOut = delta;
     }
+}
+
+__global__ void LerpTableKernel(AxisGeom gh, AxisGeom gw, int halfPixel, int variant, LerpAxis th, LerpAxis tw)
+{
+    const AxisGeom g = blockIdx.y == 0 ? gh : gw;
+    const LerpAxis t = blockIdx.y == 0 ? th : tw;
+    const int32_t d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= g.out) {
+        return;
+    }
+    int32_t lo, hi;
+    float delta;
+    LerpEntry(g, halfPixel, variant, d, lo, hi, delta);
+    t.lo[d] = lo;
+    t.hi[d] = hi;
+    t.delta[d] = delta;
+}
+
+// The backward tables (variant 1) and their transposed ranges in one launch: blockIdx.y = 0, 1 write the tables of
+// the two axes, 2, 3 the ranges. The range search evaluates table entries from the formula instead of reading
+// them, so it does not have to wait for the table blocks; the entries are the same bits either way.
+__global__ void LerpBwdTablesAndRangesKernel(AxisGeom gh, AxisGeom gw, int halfPixel, LerpAxis th, LerpAxis tw,
+                                             RangeAxis rh, RangeAxis rw)
+{
+    const bool axisW = (blockIdx.y & 1) != 0;
+    const AxisGeom g = axisW ? gw : gh;
+    const int32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (blockIdx.y < 2) {
+        const LerpAxis t = axisW ? tw : th;
+        if (idx < g.out) {
+            int32_t lo, hi;
+            float delta;
+            LerpEntry(g, halfPixel, 1, idx, lo, hi, delta);
+            t.lo[idx] = lo;
+            t.hi[idx] = hi;
+            t.delta[idx] = delta;
+        }
+        return;
+    }
+    const RangeAxis r = axisW ? rw : rh;
+    const int32_t y = idx;
+    if (y >= g.in) {
+        return;
+    }
+    int32_t lo, hi;
+    float delta;
+    // first i with hi[i] >= y
+    int32_t a = 0, b = g.out;
+    while (a < b) {
+        const int32_t m = a + ((b - a) >> 1);
+        LerpEntry(g, halfPixel, 1, m, lo, hi, delta);
+        if (hi >= y) {
+            b = m;
+        } else {
+            a = m + 1;
+        }
+    }
+    const int32_t first = a;
+    // first i with lo[i] > y
+    a = first;
+    b = g.out;
+    while (a < b) {
+        const int32_t m = a + ((b - a) >> 1);
+        LerpEntry(g, halfPixel, 1, m, lo, hi, delta);
+        if (lo > y) {
+            b = m;
+        } else {
+            a = m + 1;
+        }
+    }
+    r.start[y] = first;
+    r.end[y] = a > first ? a : first;
 }
 
 // Transposed ranges for the gather backward. lo and hi are non-decreasing in the grads index, and hi <= lo + 1,
@@ -271,6 +340,16 @@ cudaError_t BuildLerpBwdRanges(AxisGeom h, AxisGeom w, LerpAxis th, LerpAxis tw,
                                cudaStream_t s)
 {
     LerpBwdRangeKernel<<<TableGrid(h.in, w.in), kTableThreads, 0, s>>>(h, w, th, tw, rh, rw);
+    CountLaunch();
+    return cudaGetLastError();
+}
+
+cudaError_t BuildLerpBwdTablesAndRanges(AxisGeom h, AxisGeom w, bool halfPixel, LerpAxis th, LerpAxis tw, RangeAxis rh,
+                                        RangeAxis rw, cudaStream_t s)
+{
+    dim3 grid = TableGrid(std::max(h.out, h.in), std::max(w.out, w.in));
+    grid.y = 4;
+    LerpBwdTablesAndRangesKernel<<<grid, kTableThreads, 0, s>>>(h, w, halfPixel ? 1 : 0, th, tw, rh, rw);
     CountLaunch();
     return cudaGetLastError();
 }

@@ -258,7 +258,8 @@ __device__ __forceinline__ void CpAsyncWait()
 // 2*VI outputs of input columns c0..c0+VI-1 read columns c0-1..c0+VI (clamped). Weights still come from the table.
 // grid = (plane groups, tiles per plane), block = (column threads, planes); rows are table-driven (any vertical
 // scale).
-constexpr int kFwdQueueDepth = 4;
+constexpr int kFwdQueueDepth = 4; // NHWC column walker
+constexpr int kW2QueueDepth = 4;  // 2x-width row walker (8 measured the same)
 
 // QUEUE (needs VI * sizeof(T) == 16): the input rows stream through a per-thread cp.async queue.
 // PERIODIC: the column weights are the three scalars (dxFirst for output column 0, dxEven, dxOdd) instead of tw.delta.
@@ -280,8 +281,8 @@ __global__ void __launch_bounds__(kW2Threads, 5)
     const int32_t tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
     // [depth][nthreads] 16-byte vectors, then the left and right neighbour words
     uint4* qMid = reinterpret_cast<uint4*>(fwdQueue);
-    uint32_t* qLeft = reinterpret_cast<uint32_t*>(qMid + static_cast<size_t>(kFwdQueueDepth) * nthreads);
-    uint32_t* qRight = qLeft + static_cast<size_t>(kFwdQueueDepth) * nthreads;
+    uint32_t* qLeft = reinterpret_cast<uint32_t*>(qMid + static_cast<size_t>(kW2QueueDepth) * nthreads);
+    uint32_t* qRight = qLeft + static_cast<size_t>(kW2QueueDepth) * nthreads;
     const int32_t wout = 2 * win;
     // block = (column threads, planes): every thread of a block walks the same rows, so the row logic is uniform.
     // The output rows of all plane groups form one sequence (group-major); the blocks cut it into gridDim.x equal
@@ -322,14 +323,14 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         auto wR = [&](int k) { return PERIODIC ? (k == 0 ? dxHead : ((k & 1) ? dxOdd : dxEven)) : dx[PERIODIC ? 0 : k]; };
         auto wL = [&](int k) { return PERIODIC ? (k == 0 ? dxHead1 : ((k & 1) ? dxOdd1 : dxEven1)) : dx1[PERIODIC ? 0 : k]; };
         // QUEUE: the input rows this walk needs are lo[ha] .. hi[hb-1], in increasing order; they stream through
-        // the thread's queue kFwdQueueDepth rows ahead (one commit group per row, empty past the end).
+        // the thread's queue kW2QueueDepth rows ahead (one commit group per row, empty past the end).
         const int32_t lastRow = QUEUE ? __ldg(th.hi + hb - 1) : 0;
         int32_t nextRow = QUEUE ? __ldg(th.lo + ha) : 0; // next row the queue delivers
         int32_t issued = nextRow;                        // next row to start copying
         const T* issuePtr = xp + static_cast<int64_t>(nextRow) * win + c0;
         auto issue = [&]() {
             if (issued <= lastRow) {
-                const int32_t slot = (issued & (kFwdQueueDepth - 1)) * nthreads + tid;
+                const int32_t slot = (issued & (kW2QueueDepth - 1)) * nthreads + tid;
                 const T* xr = issuePtr;
                 CpAsync16(qMid + slot, xr);
                 if (c0 > 0) { // the word holding column c0-1 (4-byte aligned: c0 is a multiple of VI)
@@ -345,7 +346,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         };
         if (QUEUE) {
 #pragma unroll
-            for (int d = 0; d < kFwdQueueDepth; ++d) {
+            for (int d = 0; d < kW2QueueDepth; ++d) {
                 issue();
             }
         }
@@ -357,8 +358,8 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                     ++nextRow;
                     issue();
                 }
-                CpAsyncWait<kFwdQueueDepth - 1>();
-                const int32_t slot = (r & (kFwdQueueDepth - 1)) * nthreads + tid;
+                CpAsyncWait<kW2QueueDepth - 1>();
+                const int32_t slot = (r & (kW2QueueDepth - 1)) * nthreads + tid;
                 const uint4 raw = qMid[slot];
                 const T* me = reinterpret_cast<const T*>(&raw);
 #pragma unroll
@@ -1615,7 +1616,7 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                 // they go out as one 32-byte store
                 const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0) ? 1 : 0;
                 // 16-byte pieces (fp32 x 4, 16-bit x 8) stream through the per-thread queue
-                const size_t qBytes = static_cast<size_t>(kFwdQueueDepth) * block.x * block.y * 24;
+                const size_t qBytes = static_cast<size_t>(kW2QueueDepth) * block.x * block.y * 24;
                 auto launch = [&](auto kernel, size_t smem) {
                     int perSm = 0;
                     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, static_cast<int>(block.x * block.y),
