@@ -635,11 +635,7 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     const BilinearPlan plan = MakeBilinearFwdPlan(dt, lay, sh, ah, aw, halfPixel);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
-        cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 0, th, tw, s);
-        if (e != cudaSuccess) {
-            return e;
-        }
-        return BilinearFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, plan, s);
+        return BilinearFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, plan, s, true); // builds the tables if it reads them
     });
     FinishOutput(out, y, ex);
     ex->workspaceSize = ws.Size();

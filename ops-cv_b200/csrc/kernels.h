@@ -102,11 +102,17 @@ struct BilinearPlan {
     int32_t weightSlack;
     // kX2 backward with periodicW: the four column weights shared by every grad_input column but the first and last
     float bw[4];
+    // what the tables are built from (filled by the plan makers): kernels that evaluate their own entries, and the
+    // entry points that build the tables on demand, take it from here
+    AxisGeom geomH, geomW;
+    bool halfPixel;
 };
 BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
 BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
+// buildTables: th / tw are workspace that has not been filled; BilinearFwd fills it (plan.geomH / geomW, forward
+// formula) unless the kernel it picks evaluates its own entries. false: the caller has built the tables.
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
-                        const BilinearPlan& plan, cudaStream_t s);
+                        const BilinearPlan& plan, cudaStream_t s, bool buildTables = false);
 // Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
                               LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s);

@@ -31,6 +31,7 @@
 
 #include "host_tables.h"
 #include "launch_util.cuh"
+#include "lerp_entry.cuh"
 #include "tile_stage.cuh"
 
 namespace opscv {
@@ -273,14 +274,17 @@ template <typename T, int VI, bool QUEUE, bool PERIODIC, bool FUSE = false>
 __global__ void __launch_bounds__(kW2Threads, 5)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores, float dxFirst,
-                        float dxEven, float dxOdd)
+                        float dxEven, float dxOdd, AxisGeom geomH, int32_t halfPixel)
 {
     constexpr int VO = 2 * VI;
     constexpr int HE = 4 / sizeof(T); // elements in a 4-byte neighbour word
     extern __shared__ __align__(16) unsigned char fwdQueue[];
     const int32_t tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
+    // PERIODIC: [tileRows] row entries {lo, hi, delta} of the tile, evaluated by the block itself (this variant reads
+    // no table, so none has to be built before it); then
     // [depth][nthreads] 16-byte vectors, then the left and right neighbour words
-    uint4* qMid = reinterpret_cast<uint4*>(fwdQueue);
+    float4* rowT = reinterpret_cast<float4*>(fwdQueue);
+    uint4* qMid = reinterpret_cast<uint4*>(fwdQueue) + (PERIODIC ? tileRows : 0);
     uint32_t* qLeft = reinterpret_cast<uint32_t*>(qMid + static_cast<size_t>(kW2QueueDepth) * nthreads);
     uint32_t* qRight = qLeft + static_cast<size_t>(kW2QueueDepth) * nthreads;
     const int32_t wout = 2 * win;
@@ -298,9 +302,32 @@ __global__ void __launch_bounds__(kW2Threads, 5)
     const int32_t ha = static_cast<int32_t>(pos - pg * hout);
     const int32_t hb = static_cast<int32_t>(min(static_cast<int64_t>(min(hout, ha + tileRows)), ha + (end - pos)));
     pos += hb - ha;
+    if constexpr (PERIODIC) {
+        __syncthreads(); // the previous tile's entries are no longer read
+        for (int32_t i = tid; i < hb - ha; i += nthreads) {
+            int32_t lo, hi;
+            float delta;
+            LerpEntry(geomH, halfPixel, 0, ha + i, lo, hi, delta);
+            rowT[i] = make_float4(__int_as_float(lo), __int_as_float(hi), delta, 0.0f);
+        }
+        __syncthreads();
+    }
+    // row entry of output row h of this tile
+    auto rowEntry = [&](int32_t h, int32_t& lo, int32_t& hi, float& delta) {
+        if constexpr (PERIODIC) {
+            const float4 e = rowT[h - ha];
+            lo = __float_as_int(e.x);
+            hi = __float_as_int(e.y);
+            delta = e.z;
+        } else {
+            lo = __ldg(th.lo + h);
+            hi = __ldg(th.hi + h);
+            delta = __ldg(th.delta + h);
+        }
+    };
     const int64_t p = pg * blockDim.y + threadIdx.y;
     if (p >= planes) {
-        continue;
+        continue; // the barriers above are reached by every thread of the block in every tile
     }
     const int32_t groups = win / VI;
     const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
@@ -324,8 +351,14 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         auto wL = [&](int k) { return PERIODIC ? (k == 0 ? dxHead1 : ((k & 1) ? dxOdd1 : dxEven1)) : dx1[PERIODIC ? 0 : k]; };
         // QUEUE: the input rows this walk needs are lo[ha] .. hi[hb-1], in increasing order; they stream through
         // the thread's queue kW2QueueDepth rows ahead (one commit group per row, empty past the end).
-        const int32_t lastRow = QUEUE ? __ldg(th.hi + hb - 1) : 0;
-        int32_t nextRow = QUEUE ? __ldg(th.lo + ha) : 0; // next row the queue delivers
+        int32_t firstLo = 0, firstHi = 0, lastLo = 0, lastHi = 0;
+        float unusedDelta = 0.0f;
+        if (QUEUE) {
+            rowEntry(ha, firstLo, firstHi, unusedDelta);
+            rowEntry(hb - 1, lastLo, lastHi, unusedDelta);
+        }
+        const int32_t lastRow = lastHi;
+        int32_t nextRow = firstLo; // next row the queue delivers
         int32_t issued = nextRow;                        // next row to start copying
         const T* issuePtr = xp + static_cast<int64_t>(nextRow) * win + c0;
         auto issue = [&]() {
@@ -407,8 +440,9 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         int32_t curTop = -1, curBot = -1;
         T* dst = yp + static_cast<int64_t>(ha) * wout + c0 * 2;
         auto step = [&](int32_t h, float (&up)[VO], float (&dn)[VO]) -> bool {
-            const int32_t lo = __ldg(th.lo + h), hi = __ldg(th.hi + h);
-            const float dy = __ldg(th.delta + h);
+            int32_t lo, hi;
+            float dy;
+            rowEntry(h, lo, hi, dy);
             if (lo == curBot && lo != curTop) { // the lower row becomes the upper one: trade places
                 curTop = lo;
                 if (hi == lo) {
@@ -1468,6 +1502,9 @@ BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, Axis
 {
     BilinearPlan plan{};
     plan.schedule = BilinearPlan::kDirect;
+    plan.geomH = gh;
+    plan.geomW = gw;
+    plan.halfPixel = halfPixel;
     if (lay != kNCHW) {
         if (DtSize(dt) == 2) { // can the 16-bit walker fuse its horizontal interpolation?
             const host::Lerp tW = host::LerpTable(sh.win, sh.wout, gw.scale, halfPixel, 0);
@@ -1523,6 +1560,9 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
 {
     BilinearPlan plan{};
     plan.schedule = BilinearPlan::kDirect;
+    plan.geomH = gh;
+    plan.geomW = gw;
+    plan.halfPixel = halfPixel;
     if (lay != kNCHW) {
         return plan;
     }
@@ -1593,9 +1633,19 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
 }
 
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
-                        const BilinearPlan& plan, cudaStream_t s)
+                        const BilinearPlan& plan, cudaStream_t s, bool buildTables)
 {
     const int64_t planes = sh.n * sh.c;
+    // buildTables: th / tw are still empty; they are filled here (from the geometry in the plan) unless the kernel
+    // chosen below evaluates the entries it needs itself
+    bool tablesBuilt = !buildTables;
+    cudaError_t tableError = cudaSuccess;
+    auto needTables = [&]() {
+        if (!tablesBuilt) {
+            tableError = BuildLerpTables(plan.geomH, plan.geomW, plan.halfPixel, 0, th, tw, s);
+            tablesBuilt = true;
+        }
+    };
     OPSCV_DISPATCH_DT(dt, T, {
         if (lay == kNCHW) {
             const int v = PickVec(sizeof(T), sh.wout, {y});
@@ -1604,12 +1654,15 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
             // the 2x kernel loads 4 input columns and stores 8 output columns per thread as vectors
             const bool w2Ok = plan.schedule == BilinearPlan::kW2 && Aligned(x, 4 * sizeof(T)) &&
                               Aligned(y, sizeof(T) == 2 ? 16 : 16) && (sh.wout * sizeof(T)) % 16 == 0;
+            if (!w2Ok) {
+                needTables();
+            }
             if (w2Ok) {
                 // 16-bit tensors: eight input columns (one 16-byte load) per thread when the rows allow it
                 const int vi = (sizeof(T) == 2 && sh.win % 8 == 0 && Aligned(x, 16)) ? 8 : 4;
                 // one wave of resident blocks shares the output rows of all plane groups equally; runs of at
                 // least 8 rows
-                const int32_t tileRows = sh.hout;
+                const int32_t tileRows = std::min(sh.hout, 512);
                 const dim3 block = PlaneBlock(sh.win / vi, planes, 256, kW2Threads);
                 const int64_t totalRows = CeilDiv(planes, block.y) * sh.hout;
                 // a thread writes 2 * vi elements per row; when that is 32 bytes and the rows are 32-byte aligned
@@ -1617,7 +1670,12 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                 const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0) ? 1 : 0;
                 // 16-byte pieces (fp32 x 4, 16-bit x 8) stream through the per-thread queue
                 const size_t qBytes = static_cast<size_t>(kW2QueueDepth) * block.x * block.y * 24;
-                auto launch = [&](auto kernel, size_t smem) {
+                auto launch = [&](auto kernel, size_t smem, bool periodic) {
+                    if (periodic) {
+                        smem += static_cast<size_t>(tileRows) * 16; // the tile's row entries
+                    } else {
+                        needTables();
+                    }
                     int perSm = 0;
                     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, static_cast<int>(block.x * block.y),
                                                                       smem) != cudaSuccess || perSm < 1) {
@@ -1627,30 +1685,31 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                     const dim3 grid(static_cast<unsigned>(std::max<int64_t>(
                         1, std::min<int64_t>(static_cast<int64_t>(NumSMs()) * perSm, totalRows / 8))));
                     kernel<<<grid, block, smem, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide,
-                                                     plan.dxFirst, plan.dxEven, plan.dxOdd);
+                                                     plan.dxFirst, plan.dxEven, plan.dxOdd, plan.geomH,
+                                                     plan.halfPixel ? 1 : 0);
                 };
                 if (vi == 8) {
                     if constexpr (sizeof(T) == 2) {
                         // significand bits of T: 11 (fp16), 8 (bf16)
                         const int mant = std::is_same<T, __half>::value ? 11 : 8;
                         if (plan.periodicW && mant <= plan.weightSlack) {
-                            launch(BilinearFwdW2Kernel<T, 8, true, true, true>, qBytes);
+                            launch(BilinearFwdW2Kernel<T, 8, true, true, true>, qBytes, true);
                         } else if (plan.periodicW) {
-                            launch(BilinearFwdW2Kernel<T, 8, true, true>, qBytes);
+                            launch(BilinearFwdW2Kernel<T, 8, true, true>, qBytes, true);
                         } else {
-                            launch(BilinearFwdW2Kernel<T, 8, true, false>, qBytes);
+                            launch(BilinearFwdW2Kernel<T, 8, true, false>, qBytes, false);
                         }
                     }
                 } else if (sizeof(T) == 4) {
                     if constexpr (sizeof(T) == 4) {
                         if (plan.periodicW) {
-                            launch(BilinearFwdW2Kernel<T, 4, true, true>, qBytes);
+                            launch(BilinearFwdW2Kernel<T, 4, true, true>, qBytes, true);
                         } else {
-                            launch(BilinearFwdW2Kernel<T, 4, true, false>, qBytes);
+                            launch(BilinearFwdW2Kernel<T, 4, true, false>, qBytes, false);
                         }
                     }
                 } else {
-                    launch(BilinearFwdW2Kernel<T, 4, false, false>, 0);
+                    launch(BilinearFwdW2Kernel<T, 4, false, false>, 0, false);
                 }
             } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
@@ -1683,6 +1742,7 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                 });
             }
         } else {
+            needTables();
             const int v = PickVec(sizeof(T), sh.c, {x, y});
             OPSCV_DISPATCH_VEC(v, V, {
                 if constexpr (V * sizeof(T) <= 16) {
@@ -1727,6 +1787,9 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
         }
     });
     CountLaunch();
+    if (tableError != cudaSuccess) {
+        return tableError;
+    }
     return cudaGetLastError();
 }
 
