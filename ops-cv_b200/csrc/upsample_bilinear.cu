@@ -31,6 +31,7 @@
 
 #include "host_tables.h"
 #include "launch_util.cuh"
+#include "cp_async.cuh"
 #include "lerp_entry.cuh"
 #include "tile_stage.cuh"
 
@@ -233,27 +234,6 @@ __global__ void __launch_bounds__(kThreads)
 // The row walks below are serial chains per thread, so what bounds them is the number of bytes a thread has in
 // flight. cp.async copies a thread's own piece of the next rows into a private shared-memory queue (one commit
 // group per row, cp.async.wait_group to consume in order), which holds several times what registers could.
-__device__ __forceinline__ void CpAsync16(void* smem, const void* gmem)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
-                 "l"(gmem)
-                 : "memory");
-}
-__device__ __forceinline__ void CpAsync4(void* smem, const void* gmem)
-{
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
-                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
-                 "l"(gmem)
-                 : "memory");
-}
-__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void CpAsyncWait()
-{
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 // ---- forward, NCHW, output width = 2 x input width, input-major ---------------------------------------------------
 // The host has verified the column pattern lo[w] = max((w-1)>>1, 0), hi[w] = w ? min((w+1)>>1, win-1) : 0, so the
 // 2*VI outputs of input columns c0..c0+VI-1 read columns c0-1..c0+VI (clamped). Weights still come from the table.
