@@ -134,3 +134,34 @@ def test_grid_sampler_random(ops, oracle, dev, seed):
             ops.set_deterministic(False)
         check_sum(gi, ri, dtype)
         check_sum(gg, rg, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("fmt", ["NCHW", "NHWC"])
+def test_bilinear_2x_16bit_forward_is_bit_exact(ops, oracle, dev, dtype, fmt):
+    """Exact 2x: the weights are 0, 0.25, 0.75 and 1, so every weight * value product is exact in fp32 and the kernels
+    use a fused multiply-add in the horizontal pass. That must give the oracle's bits, not only its value to 1 ulp.
+    Values span many binades so that sums do round."""
+    n, c, hi, wi = 3, 16, 21, 40
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn((n, c, hi, wi), generator=g) * torch.exp2(torch.randint(-12, 12, (n, c, hi, wi), generator=g).float())
+    if fmt == "NHWC":
+        x = x.permute(0, 2, 3, 1).contiguous()
+    xs, x32 = quant(x, dtype)
+    ofmt = oracle.NHWC if fmt == "NHWC" else oracle.NCHW
+    y = ops.upsample_bilinear2d(xs.to(dev), (2 * hi, 2 * wi), False, fmt)
+    check(y, oracle.bilinear2d_fwd(x32, (2 * hi, 2 * wi), False, fmt=ofmt), dtype, exact=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_bilinear_2x_tall_planes(ops, oracle, dev, dtype):
+    """Planes taller than one tile of the 2x kernels (forward: 512 output rows per tile; backward: as many rows as fit
+    the shared-memory budget), few planes, so every block's run crosses tile and plane-group borders."""
+    n, c, hi, wi = 1, 3, 700, 16
+    g = torch.Generator().manual_seed(78)
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=g), dtype)
+    go, go32 = quant(torch.randn((n, c, 2 * hi, 2 * wi), generator=g), dtype)
+    y = ops.upsample_bilinear2d(x.to(dev), (2 * hi, 2 * wi), False)
+    check(y, oracle.bilinear2d_fwd(x32, (2 * hi, 2 * wi), False), dtype, exact=(dtype == torch.float32))
+    gi = ops.upsample_bilinear2d_backward(go.to(dev), (2 * hi, 2 * wi), (n, c, hi, wi), False)
+    check_sum(gi, oracle.bilinear2d_bwd(go32, (hi, wi), False), dtype)
