@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 // Backward: gi[y][x] = sum over the RH x RW block of grads, rows outer, columns inner (the reference's order).
-template <typename T, int RW>
+// RH > 0: the row factor is known at compile time; the rows of a block are then loaded together before they are added.
+template <typename T, int RW, int RH = 0>
 __global__ void __launch_bounds__(kThreads)
     NearestBwdPoolKernel(const T* __restrict__ go, T* __restrict__ gi, int32_t hin, int32_t win, int32_t rh,
                          int64_t planes)
@@ -208,17 +209,35 @@ __global__ void __launch_bounds__(kThreads)
             for (int k = 0; k < VO; ++k) {
                 acc[k] = 0.0f;
             }
-            for (int32_t i = 0; i < rh; ++i) {
-                float g[VI];
-                LoadPackLdg<T, VI>(src, g);
+            if constexpr (RH > 0) {
+                float g[RH][VI];
 #pragma unroll
-                for (int k = 0; k < VO; ++k) {
+                for (int i = 0; i < RH; ++i) {
+                    LoadPackLdg<T, VI>(src + static_cast<int64_t>(i) * wout, g[i]);
+                }
 #pragma unroll
-                    for (int j = 0; j < RW; ++j) {
-                        acc[k] = Add(acc[k], g[k * RW + j]);
+                for (int i = 0; i < RH; ++i) {
+#pragma unroll
+                    for (int k = 0; k < VO; ++k) {
+#pragma unroll
+                        for (int j = 0; j < RW; ++j) {
+                            acc[k] = Add(acc[k], g[i][k * RW + j]);
+                        }
                     }
                 }
-                src += wout;
+            } else {
+                for (int32_t i = 0; i < rh; ++i) {
+                    float g[VI];
+                    LoadPackLdg<T, VI>(src, g);
+#pragma unroll
+                    for (int k = 0; k < VO; ++k) {
+#pragma unroll
+                        for (int j = 0; j < RW; ++j) {
+                            acc[k] = Add(acc[k], g[k * RW + j]);
+                        }
+                    }
+                    src += wout;
+                }
             }
             StorePack<T, VO>(op + static_cast<int64_t>(r) * win + cv * VO, acc);
         }
@@ -485,7 +504,9 @@ cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, R
                 const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(planes, 1 << 30));
                 const T* pg = static_cast<const T*>(go);
                 T* po = static_cast<T*>(gi);
-                if (plan.rw == 2) {
+                if (plan.rw == 2 && plan.rh == 2) {
+                    NearestBwdPoolKernel<T, 2, 2><<<blocks, kThreads, 0, s>>>(pg, po, sh.hin, sh.win, plan.rh, planes);
+                } else if (plan.rw == 2) {
                     NearestBwdPoolKernel<T, 2><<<blocks, kThreads, 0, s>>>(pg, po, sh.hin, sh.win, plan.rh, planes);
                 } else {
                     NearestBwdPoolKernel<T, 4><<<blocks, kThreads, 0, s>>>(pg, po, sh.hin, sh.win, plan.rh, planes);
