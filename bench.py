@@ -76,6 +76,9 @@ def nbytes(t):
 def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
     """Returns (description, make_buffers(gen) -> dict of CPU tensors, [Op], config dict)."""
     ws = ops.Workspace(dev) if ops is not None else None  # None: only the description is wanted
+    # one workspace per operator for workloads whose operators are independent of each other: they may then run on
+    # parallel branches of the step graph
+    wss = [ws] + [ops.Workspace(dev) for _ in range(3)] if ops is not None else [None] * 4
 
     if name == "cfg2":
         n, c, hi, wi, ho, wo = 32 // batch_div, 256, 56, 56, 112, 112
@@ -90,16 +93,16 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
             }
         small, big = n * c * hi * wi * 2, n * c * ho * wo * 2
         oplist = [
-            Op("UpsampleNearest2d", lambda b: ops.upsample_nearest2d(b["x"], (ho, wo), out=b["y_nearest"], workspace=ws),
+            Op("UpsampleNearest2d", lambda b: ops.upsample_nearest2d(b["x"], (ho, wo), out=b["y_nearest"], workspace=wss[0]),
                small + big, n * ho * wo, ["x"], ["y_nearest"]),
             Op("UpsampleBilinear2d", lambda b: ops.upsample_bilinear2d(b["x"], (ho, wo), False, scales=(2.0, 2.0),
-                                                                       out=b["y_bilinear"], workspace=ws),
+                                                                       out=b["y_bilinear"], workspace=wss[1]),
                small + big, n * ho * wo, ["x"], ["y_bilinear"]),
             Op("UpsampleNearest2dBackward", lambda b: ops.upsample_nearest2d_backward(
-                b["go"], (ho, wo), (n, c, hi, wi), scales=(2.0, 2.0), out=b["gi_nearest"], workspace=ws),
+                b["go"], (ho, wo), (n, c, hi, wi), scales=(2.0, 2.0), out=b["gi_nearest"], workspace=wss[2]),
                small + big, n * ho * wo, ["go"], ["gi_nearest"]),
             Op("UpsampleBilinear2dBackward", lambda b: ops.upsample_bilinear2d_backward(
-                b["go"], (ho, wo), (n, c, hi, wi), False, scales=(2.0, 2.0), out=b["gi_bilinear"], workspace=ws),
+                b["go"], (ho, wo), (n, c, hi, wi), False, scales=(2.0, 2.0), out=b["gi_bilinear"], workspace=wss[3]),
                small + big, n * ho * wo, ["go"], ["gi_bilinear"]),
         ]
         cfg = {"workload": "FPN-style upsampling: UpsampleNearest2d + UpsampleBilinear2d forward and backward, fp16 "
@@ -119,10 +122,10 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
             }
         big, small = n * c * hi * wi * 4, n * c * ho * wo * 4
         oplist = [
-            Op("UpsampleBicubic2dAA", lambda b: ops.upsample_bicubic2d_aa(b["x"], (ho, wo), False, out=b["y"], workspace=ws),
+            Op("UpsampleBicubic2dAA", lambda b: ops.upsample_bicubic2d_aa(b["x"], (ho, wo), False, out=b["y"], workspace=wss[0]),
                small + big, n * ho * wo, ["x"], ["y"]),
             Op("UpsampleBicubic2dAAGrad", lambda b: ops.upsample_bicubic2d_aa_grad(
-                b["go"], (ho, wo), (n, c, hi, wi), False, out=b["gi"], workspace=ws),
+                b["go"], (ho, wo), (n, c, hi, wi), False, out=b["gi"], workspace=wss[1]),
                small + big, n * ho * wo, ["go"], ["gi"]),
         ]
         cfg = {"workload": f"UpsampleBicubic2dAA forward and backward, fp32 NCHW N={n} C=3 1024x1024 -> 224x224 "
@@ -201,10 +204,10 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
             }
         oplist = [
             Op("UpsampleBilinear2d[NHWC bf16]", lambda b: ops.upsample_bilinear2d(b["x"], (ho, wo), False, "NHWC",
-                                                                                  out=b["y"], workspace=ws),
+                                                                                  out=b["y"], workspace=wss[0]),
                n * c * (hi * wi + ho * wo) * 2, n * ho * wo, ["x"], ["y"]),
             Op("GridSampler2D[affine fp32]", lambda b: ops.grid_sampler2d(b["gx"], b["grid"], 0, 0, False, out=b["gy"],
-                                                                         workspace=ws),
+                                                                         workspace=wss[1]),
                n2 * c2 * h2 * h2 * 4 * 2 + n2 * h2 * h2 * 2 * 4, n2 * h2 * h2, ["gx", "grid"], ["gy"]),
         ]
         cfg = {"workload": f"box sweep shard: UpsampleBilinear2d bf16 NHWC N={n} C=256 64x64 -> 128x128 + GridSampler2D "
@@ -387,6 +390,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls instead of CUDA-graph replays")
+    ap.add_argument("--serial-step", action="store_true",
+                    help="step graph with the operators one after the other instead of on parallel branches")
     ap.add_argument("--sets", type=int, default=0, help="buffer sets to rotate (0 = enough to exceed L2 four times)")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -449,7 +454,7 @@ def main():
         "dtype": head["config"]["dtype"], "data": "synthetic (seeded torch.Generator)",
         "config": {"workload": head["config"]["workload"], "l2": head["l2_note"], "per_gpu_batch": "fixed (weak scaling)",
                    "launch": "eager aclnn calls" if args.no_graph else
-                   "CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding all operators of the step; the per-operator times come from a separate pass: per-operator graphs launched back to back over all buffer sets between one pair of events"},
+                   "CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding all operators of the step (cfg2, cfg3, cfg5: the independent operators of a step on parallel branches, each with its own workspace; cfg4: one after the other, the two backward modes write the same tensors); the per-operator times come from a separate pass: per-operator graphs launched back to back over all buffer sets between one pair of events"},
         "mpix_per_s": head["mpix_per_s"], "pct_of_hbm_peak": head["value"] / (peak * world),
         "roofline": head["roofline"], "ops": head["ops"], "e2e": head["e2e"], "gpu_launches": head["gpu_launches"],
         "clocks": head["clocks"], "peak_source": peak_src,
@@ -507,7 +512,32 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
             graphs.append(row)
         # one graph per buffer set holding the whole step (all operators back to back): the timed region replays
         # these, so the GPU is not idle between operators while the host launches the next graph
-        step_graphs = [RawGraph(torch, side, lambda: [op.run(dsets[s_i]) for op in oplist]) for s_i in range(nsets)]
+        # Operators that share no output buffer (and no workspace) go on parallel branches of the graph: the tail of
+        # one kernel then overlaps the head of the next instead of waiting for it.
+        outs = [set(op.outputs) for op in oplist]
+        parallel = (wname in ("cfg2", "cfg3", "cfg5") and not args.serial_step and
+                    all(outs[a].isdisjoint(outs[b]) for a in range(len(outs)) for b in range(a)))
+        branches = [torch.cuda.Stream(dev) for _ in oplist] if parallel else []
+
+        def step_fn(s_i):
+            if not parallel:
+                for op in oplist:
+                    op.run(dsets[s_i])
+                return
+            keep = []  # events stay alive until the capture ends
+            fork = torch.cuda.Event()
+            fork.record(side)
+            keep.append(fork)
+            for op, st in zip(oplist, branches):
+                st.wait_event(fork)
+                with torch.cuda.stream(st):
+                    op.run(dsets[s_i])
+                join = torch.cuda.Event()
+                join.record(st)
+                side.wait_event(join)
+                keep.append(join)
+            return keep
+        step_graphs = [RawGraph(torch, side, lambda: step_fn(s_i)) for s_i in range(nsets)]
         torch.cuda.synchronize(dev)
         run_op = lambda j, s_i: graphs[j][s_i].replay(stream)  # noqa: E731
     else:
