@@ -359,11 +359,8 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
-            const cudaError_t e = BuildLerpBwdTablesAndRanges(ah, aw, halfPixel, th, tw, qh, qw, s);
-            if (e != cudaSuccess) {
-                return e;
-            }
-            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, plan, s);
+            // builds the tables and ranges if the kernel it picks reads them
+            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, plan, s, true);
         });
     }
     FinishOutput(out, y, ex);

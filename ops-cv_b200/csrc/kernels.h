@@ -102,6 +102,7 @@ struct BilinearPlan {
     int32_t weightSlack;
     // kX2 backward with periodicW: the four column weights shared by every grad_input column but the first and last
     float bw[4];
+    int32_t rowStart1; // kX2 backward: first grads row feeding grad_input row 1 (0 or 1; every other row follows 2y-1)
     // what the tables are built from (filled by the plan makers): kernels that evaluate their own entries, and the
     // entry points that build the tables on demand, take it from here
     AxisGeom geomH, geomW;
@@ -114,8 +115,10 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
                         const BilinearPlan& plan, cudaStream_t s, bool buildTables = false);
 // Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
+// buildTables: as for BilinearFwd, with the backward formula and the ranges.
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
-                              LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s);
+                              LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s,
+                              bool buildTables = false);
 // Scatter backward with fp32 atomics into `acc` (fp32, N*C*hin*win, zeroed by this call). If dtOut is fp32 the
 // caller passes acc == gi; otherwise a cast pass writes gi.
 cudaError_t BilinearBwdAtomic(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, float* acc, Shape4 sh,

@@ -764,8 +764,36 @@ template <typename TIn, typename TOut, bool TWINS, int V, bool PERIODIC>
 __global__ void __launch_bounds__(kW2Threads, 5)
     BilinearBwdX2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
                         LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows, float pw0, float pw1, float pw2,
-                        float pw3)
+                        float pw3, AxisGeom geomH, AxisGeom geomW, int32_t halfPixel, int32_t start1)
 {
+    // PERIODIC reads no table: row entries and the three border weights are evaluated from the geometry (LerpEntry is
+    // what the table kernel runs, so the bits are the same), and the first / last grads row of a tile follow from
+    // the 2x pattern the host has verified (start1: where the range of grad_input row 1 starts, 0 or 1).
+    // table entry of grads index i on the row (axis 0) or column axis
+    auto entry = [&](int axis, int32_t i, int32_t& lo, int32_t& hi, float& d) {
+        if constexpr (PERIODIC) {
+            LerpEntry(axis == 0 ? geomH : geomW, halfPixel, 1, i, lo, hi, d);
+        } else {
+            const LerpAxis& t = axis == 0 ? th : tw;
+            lo = __ldg(t.lo + i);
+            hi = __ldg(t.hi + i);
+            d = __ldg(t.delta + i);
+        }
+    };
+    // weight with which grads column j feeds grad_input column xcol (as CombinedWeight does from the table)
+    auto colWeight = [&](int32_t j, int32_t xcol) {
+        int32_t lo, hi;
+        float d;
+        entry(1, j, lo, hi, d);
+        float w = 0.0f;
+        if (lo == xcol) {
+            w = Sub(1.0f, d);
+        }
+        if (hi == xcol) {
+            w = Add(w, d);
+        }
+        return w;
+    };
     constexpr int VG = 2 * V;
     constexpr int kX2Depth = X2Depth(V);
     constexpr int NM = VG * sizeof(TIn) / 16; // 16-byte vectors holding grads columns j0 .. j0+VG-1
@@ -797,16 +825,21 @@ __global__ void __launch_bounds__(kW2Threads, 5)
     const int32_t yb = static_cast<int32_t>(min(static_cast<int64_t>(min(hin, ya + tileRows)), ya + (end - pos)));
     pos += yb - ya;
     // grads rows [first, first + count) feed grad_input rows [ya, yb)
-    const int32_t first = __ldg(rh.start + ya);
-    const int32_t count = min(max(first, __ldg(rh.end + yb - 1)) - first, 2 * tileRows + 4);
+    const int32_t first = PERIODIC ? (ya == 1 ? start1 : max(2 * ya - 1, 0)) : __ldg(rh.start + ya);
+    const int32_t last = PERIODIC ? min(2 * (yb - 1) + 3, 2 * hin) : __ldg(rh.end + yb - 1);
+    const int32_t count = min(max(first, last) - first, 2 * tileRows + 4);
     __syncthreads(); // the previous tile's records are no longer read
     for (int32_t n = tid; n < count; n += nthreads) {
         const int32_t i = first + n;
-        const int32_t lo = __ldg(th.lo + i), hi = __ldg(th.hi + i);
-        const float d = __ldg(th.delta + i);
+        int32_t lo, hi, loPrev = 0, hiPrev;
+        float d, dPrev;
+        entry(0, i, lo, hi, d);
+        if (n > 0) {
+            entry(0, i - 1, loPrev, hiPrev, dPrev);
+        }
         // the older open row when row i is added: rows below lo[i] are complete
         const int32_t cur = max(ya, lo);
-        const int32_t prev = n > 0 ? max(ya, __ldg(th.lo + i - 1)) : ya;
+        const int32_t prev = n > 0 ? max(ya, loPrev) : ya;
         int32_t bits = (cur - prev) << kFlushShift;
         bits |= (lo == cur) ? kLoA : 0;
         bits |= (hi == cur) ? kHiA : 0;
@@ -842,8 +875,8 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         }
         // PERIODIC: grads column 0 feeds column 0 and grads column wout-1 feeds column win-1 with their own weights;
         // the taps that fall outside the row multiply a zero
-        const float wHead = (PERIODIC && x0 == 0) ? CombinedWeight(tw, 0, 0) : pw1;
-        const float wTail = (PERIODIC && x0 + V == win) ? CombinedWeight(tw, wout - 1, win - 1) : pw2;
+        const float wHead = (PERIODIC && x0 == 0) ? colWeight(0, 0) : pw1;
+        const float wTail = (PERIODIC && x0 + V == win) ? colWeight(wout - 1, win - 1) : pw2;
         auto weight = [&](int k, int t) {
             if constexpr (PERIODIC) {
                 return (k == 0 && t == 1)
@@ -854,7 +887,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
             }
         };
         const bool extra = x0 == 0 && win > 1; // column 1 also takes grads column 0 (zero weight), as for rows
-        const float wExtra = extra ? CombinedWeight(tw, 0, 1) : 0.0f;
+        const float wExtra = extra ? colWeight(0, 1) : 0.0f;
         // one commit group per stream element (empty past the end); elements are issued in order, so the source
         // advances by one row per call
         const TIn* issueRow = gp + static_cast<int64_t>(first) * wout + j0;
@@ -1353,9 +1386,19 @@ int32_t RowsForOccupancy(int64_t threadsPerTileRowSet, int32_t rows)
 
 template <typename TIn, typename TOut>
 cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th, LerpAxis tw, RangeAxis rh,
-                         RangeAxis rw, const BilinearPlan& plan, cudaStream_t s)
+                         RangeAxis rw, const BilinearPlan& plan, cudaStream_t s, bool buildTables)
 {
     const int64_t planes = sh.n * sh.c;
+    // buildTables: the tables and ranges are workspace that has not been filled; they are built here (from the
+    // geometry in the plan) unless the kernel chosen below evaluates the entries it needs itself
+    bool tablesBuilt = !buildTables;
+    cudaError_t tableError = cudaSuccess;
+    auto needTables = [&]() {
+        if (!tablesBuilt) {
+            tableError = BuildLerpBwdTablesAndRanges(plan.geomH, plan.geomW, plan.halfPixel, th, tw, rh, rw, s);
+            tablesBuilt = true;
+        }
+    };
     if (lay == kNCHW) {
         const int v = PickVec(sizeof(TOut), sh.win, {gi});
         const TIn* pg = static_cast<const TIn*>(go);
@@ -1410,9 +1453,13 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
                 (void)cudaGetLastError();
                 if (attr == cudaSuccess) {
                     kernel<<<blocks, block, bytes, s>>>(pg, po, planes, sh.hin, sh.win, th, tw, rh, rows, plan.bw[0],
-                                                        plan.bw[1], plan.bw[2], plan.bw[3]);
+                                                        plan.bw[1], plan.bw[2], plan.bw[3], plan.geomH, plan.geomW,
+                                                        plan.halfPixel ? 1 : 0, plan.rowStart1);
                 }
             };
+            if (!(x2 && plan.periodicW)) {
+                needTables(); // the periodic variants evaluate their own entries
+            }
             if (x2) {
                 if (x2Wide) {
                     if constexpr (sizeof(TIn) == 2 && sizeof(TOut) == 2) {
@@ -1429,10 +1476,12 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
             if (x2 && attr == cudaSuccess) {
                 // launched above
             } else {
+                needTables(); // also after a periodic variant that could not be launched
                 BilinearBwdW2Kernel<TIn, TOut><<<grid, block, 0, s>>>(pg, po, planes, sh.hin, sh.win, sh.hout, th, tw,
                                                                       rh, tileRows);
             }
         } else if (plan.schedule != BilinearPlan::kDirect && plan.tileRows > 0) {
+            needTables();
             const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hin, plan.tileRows));
             const int32_t stride = static_cast<int32_t>(
                 (StageBytes(static_cast<int64_t>(plan.bandRows) * sh.wout, sizeof(TIn)) + 15) & ~size_t(15));
@@ -1452,6 +1501,7 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
                 }
             });
         } else {
+            needTables();
             OPSCV_DISPATCH_VEC(v, V, {
                 if constexpr (V * sizeof(TOut) <= 16) {
                     const int64_t total = planes * sh.hin * (sh.win / V);
@@ -1461,6 +1511,7 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
             });
         }
     } else {
+        needTables();
         const int elem = sizeof(TIn) > sizeof(TOut) ? sizeof(TIn) : sizeof(TOut);
         const int v = PickVec(elem, sh.c, {go, gi});
         OPSCV_DISPATCH_VEC(v, V, {
@@ -1473,6 +1524,9 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
         });
     }
     CountLaunch();
+    if (tableError != cudaSuccess) {
+        return tableError;
+    }
     return cudaGetLastError();
 }
 
@@ -1574,6 +1628,7 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
             }
             return w;
         };
+        plan.rowStart1 = sh.hin > 1 ? rH.start[1] : 0;
         plan.periodicW = plan.schedule == BilinearPlan::kX2 && !plan.zeroTwins && sh.win >= 3;
         if (plan.periodicW) {
             for (int t = 0; t < 4; ++t) {
@@ -1774,16 +1829,18 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
 }
 
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
-                              LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s)
+                              LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s,
+                              bool buildTables)
 {
     if (dtIn == dtOut) {
-        OPSCV_DISPATCH_DT(dtIn, T, { return (LaunchGather<T, T>(lay, go, gi, sh, th, tw, rh, rw, plan, s)); });
+        OPSCV_DISPATCH_DT(dtIn, T,
+                          { return (LaunchGather<T, T>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables)); });
     }
     if (dtIn == Dt::F32 && dtOut == Dt::F16) {
-        return LaunchGather<float, __half>(lay, go, gi, sh, th, tw, rh, rw, plan, s);
+        return LaunchGather<float, __half>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables);
     }
     if (dtIn == Dt::F32 && dtOut == Dt::BF16) {
-        return LaunchGather<float, __nv_bfloat16>(lay, go, gi, sh, th, tw, rh, rw, plan, s);
+        return LaunchGather<float, __nv_bfloat16>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables);
     }
     return cudaErrorInvalidValue;
 }
