@@ -47,8 +47,8 @@ def measured_peak():
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the main kernel of each operator, from the
 # captures summarised under profiles/ (None = not captured).
 NCU_TRAFFIC = {
-    ("cfg2", "UpsampleNearest2d"): 200.9e6, ("cfg2", "UpsampleBilinear2d"): 206.0e6,
-    ("cfg2", "UpsampleNearest2dBackward"): 241.4e6, ("cfg2", "UpsampleBilinear2dBackward"): 246.9e6,
+    ("cfg2", "UpsampleNearest2d"): 201.0e6, ("cfg2", "UpsampleBilinear2d"): 206.1e6,
+    ("cfg2", "UpsampleNearest2dBackward"): 242.2e6, ("cfg2", "UpsampleBilinear2dBackward"): 245.9e6,
     ("cfg3", "UpsampleBicubic2dAA"): 864.1e6, ("cfg3", "UpsampleBicubic2dAAGrad"): 785.0e6,
     ("cfg4", "GridSampler2D"): 278.9e6, ("cfg4", "GridSampler2DBackward[atomic]"): 394.8e6,
     ("cfg4", "GridSampler2DBackward[deterministic]"): 326.8e6 + 447.9e6,  # gather + grad_grid kernels
