@@ -241,17 +241,7 @@ aclnnStatus CheckBackwardShape(const char* api, const aclTensor* gradOut, const 
 
 // ---- UpsampleBilinear2d ---------------------------------------------------------------------------------------
 // image/resize_bilinear_v2/op_host/arch35/resize_bilinear_v2_tiling_arch35.cpp:175-243
-float BilinearScale(int64_t in, int64_t out, bool align, float userScale)
-{
-    if (!align) {
-        return userScale > 0.0f ? 1.0f / userScale : static_cast<float>(in) / static_cast<float>(out);
-    }
-    float s = static_cast<float>(in) / static_cast<float>(out);
-    if (out > 1) {
-        s = static_cast<float>(in - 1) / static_cast<float>(out - 1);
-    }
-    return s;
-}
+// BilinearScale: host_common.h (shared with the allocation-free entry point)
 
 // image/resize_bilinear_v2_grad/op_host/arch35/resize_bilinear_v2_grad_tiling_arch35.cpp:352-384 (scatter form)
 float BilinearGradScale(int64_t in, int64_t out, bool align, float userScale)

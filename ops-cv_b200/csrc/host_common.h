@@ -83,6 +83,20 @@ const char* FormatName(aclFormat f);
 int64_t GetDeterministic(); // thread-local ACL_OPT_DETERMINISTIC
 int32_t GetBackwardAlgo();
 
+// Forward source-coordinate scale of UpsampleBilinear2d
+// (image/resize_bilinear_v2/op_host/arch35/resize_bilinear_v2_tiling_arch35.cpp:175-243).
+inline float BilinearScale(int64_t in, int64_t out, bool align, float userScale)
+{
+    if (!align) {
+        return userScale > 0.0f ? 1.0f / userScale : static_cast<float>(in) / static_cast<float>(out);
+    }
+    float s = static_cast<float>(in) / static_cast<float>(out);
+    if (out > 1) {
+        s = static_cast<float>(in - 1) / static_cast<float>(out - 1);
+    }
+    return s;
+}
+
 // ---- workspace planning ----------------------------------------------------------------------------------------
 class WsPlan {
 public:

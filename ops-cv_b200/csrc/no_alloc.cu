@@ -12,7 +12,9 @@
 // (int32) and delta[kMaxExtent] (fp32): 2 * 3 * kMaxExtent * 4 bytes = 192 KiB per device. Output extents beyond
 // kMaxExtent are rejected with ACLNN_ERR_PARAM_INVALID. The device address of the array is looked up once per
 // device, on the first call made with that device current, and cached; that first call should therefore come
-// before any stream capture on that device. Nothing in the array has to start at zero: every call rewrites the
+// before any stream capture on that device. (If the application destroys the device's context with
+// cudaDeviceReset, the next call notices that the cached address is no longer device memory and looks it up
+// again; that call, too, should come before any capture.) Nothing in the array has to start at zero: every call rewrites the
 // entries it reads, on the caller's stream, before the sampling kernel runs.
 //
 // Sharing. Every call on a device uses the same array. Calls on one stream are ordered and safe. Calls that may
@@ -34,8 +36,9 @@ static __device__ __align__(256) uint32_t g_tapScratch[kScratchWords];
 std::mutex g_setupMutex;
 uint32_t* g_scratchAddr[kMaxDevices] = {};
 
-// Device address of g_tapScratch on the current device (looked up once per device).
-cudaError_t ScratchForCurrentDevice(uint32_t** out)
+// Device address of g_tapScratch on the current device (looked up once per device; `refresh` drops the cached
+// address first, for a device whose context was destroyed and re-created since the look-up).
+cudaError_t ScratchForCurrentDevice(uint32_t** out, bool refresh)
 {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -46,6 +49,9 @@ cudaError_t ScratchForCurrentDevice(uint32_t** out)
         return cudaErrorInvalidDevice;
     }
     std::lock_guard<std::mutex> lock(g_setupMutex);
+    if (refresh) {
+        g_scratchAddr[dev] = nullptr;
+    }
     if (g_scratchAddr[dev] == nullptr) {
         uint32_t* ptr = nullptr;
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_tapScratch);
@@ -56,17 +62,6 @@ cudaError_t ScratchForCurrentDevice(uint32_t** out)
     }
     *out = g_scratchAddr[dev];
     return cudaSuccess;
-}
-
-// Forward source-coordinate scale, as image/resize_bilinear_v2/op_host/arch35/resize_bilinear_v2_tiling_arch35.cpp
-// computes it (same rule as the two-phase entry point).
-float ForwardScale(int64_t in, int64_t out, bool align, float userScale)
-{
-    if (!align) {
-        return userScale > 0.0f ? 1.0f / userScale : static_cast<float>(in) / static_cast<float>(out);
-    }
-    return out > 1 ? static_cast<float>(in - 1) / static_cast<float>(out - 1)
-                   : static_cast<float>(in) / static_cast<float>(out);
 }
 
 } // namespace
@@ -106,8 +101,28 @@ extern "C" ACLNN_API aclnnStatus opscvUpsampleBilinear2dNoAlloc(const void* self
     if (n == 0 || c == 0 || outH == 0 || outW == 0) {
         return ACLNN_SUCCESS;
     }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (inH == outH && inW == outW) {
+        // Same extents: a plain copy whatever the scales say, as in the two-phase entry point and the reference
+        // (all-copy schedule, resize_bilinear_v2_tiling_arch35.cpp:245-252). No tables, so no shared state.
+        const size_t bytes = static_cast<size_t>(n) * c * inH * inW * ElemSize(dtype);
+        const cudaError_t ce = cudaMemcpyAsync(out, self, bytes, cudaMemcpyDeviceToDevice, s);
+        if (ce != cudaSuccess) {
+            return Fail(ACLNN_ERR_RUNTIME_ERROR, "%s: %s", api, cudaGetErrorString(ce));
+        }
+        return ACLNN_SUCCESS;
+    }
     uint32_t* scratch = nullptr;
-    cudaError_t e = ScratchForCurrentDevice(&scratch);
+    cudaError_t e = ScratchForCurrentDevice(&scratch, false);
+    if (e == cudaSuccess) {
+        // A cached address outlives its context if the application called cudaDeviceReset: ask the runtime
+        // whether the pointer is still device memory of the current context, and look it up again if not.
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, scratch) != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+            (void)cudaGetLastError();
+            e = ScratchForCurrentDevice(&scratch, true);
+        }
+    }
     if (e != cudaSuccess) {
         return Fail(ACLNN_ERR_RUNTIME_ERROR, "%s: cannot locate the table array: %s", api, cudaGetErrorString(e));
     }
@@ -123,10 +138,9 @@ extern "C" ACLNN_API aclnnStatus opscvUpsampleBilinear2dNoAlloc(const void* self
     sh.win = static_cast<int32_t>(inW);
     sh.hout = static_cast<int32_t>(outH);
     sh.wout = static_cast<int32_t>(outW);
-    const AxisGeom ah{sh.hin, sh.hout, ForwardScale(inH, outH, alignCorners, static_cast<float>(scalesH))};
-    const AxisGeom aw{sh.win, sh.wout, ForwardScale(inW, outW, alignCorners, static_cast<float>(scalesW))};
+    const AxisGeom ah{sh.hin, sh.hout, BilinearScale(inH, outH, alignCorners, static_cast<float>(scalesH))};
+    const AxisGeom aw{sh.win, sh.wout, BilinearScale(inW, outW, alignCorners, static_cast<float>(scalesW))};
     const bool halfPixel = !alignCorners;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     e = BuildLerpTables(ah, aw, halfPixel, 0, th, tw, s);
     if (e == cudaSuccess) {
         BilinearPlan plan{};

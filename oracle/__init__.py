@@ -148,10 +148,32 @@ def bilinear2d_fwd(x, out_hw, align=False, scales=(0.0, 0.0), fmt=NCHW):
     return y
 
 
-def bilinear2d_bwd(go, in_hw, align=False, scales=(0.0, 0.0), fmt=NCHW, definition="scatter"):
+def bilinear2d_bwd_kernel_choice(in_hw, out_hw, align=False, scales=(0.0, 0.0), deterministic=False, mixed_dtype=False):
+    """Which kernel the reference's tiling runs for an NCHW call: "scatter" (atomic), "gather" (determine) or
+    "gather_scales" (determine_scales)."""
+    fn = lib().orc_bilinear2d_bwd_kernel_choice
+    fn.restype = ctypes.c_int
+    k = fn(I64(in_hw[0]), I64(in_hw[1]), I64(out_hw[0]), I64(out_hw[1]), I32(int(align)), F32(scales[0]),
+           F32(scales[1]), I32(int(deterministic)), I32(int(mixed_dtype)))
+    return ("scatter", "gather", "gather_scales")[k]
+
+
+def bilinear2d_bwd(go, in_hw, align=False, scales=(0.0, 0.0), fmt=NCHW, definition="scatter", deterministic=False,
+                   mixed_dtype=False):
+    """definition: "scatter" (the atomic kernel run serially), "gather" (determine), "gather_scales"
+    (determine_scales, align_corners = false only) or "dispatch" (whichever of the three the reference's tiling
+    selects for these arguments)."""
     go, pg = _f(go)
     n, c, ho, wo = _dims(go.shape, fmt)
     gi = np.empty(_shape(n, c, in_hw[0], in_hw[1], fmt), dtype=np.float32)
+    if definition == "dispatch":
+        definition = bilinear2d_bwd_kernel_choice(in_hw, (ho, wo), align, scales, deterministic, mixed_dtype)
+    if definition == "gather_scales":
+        assert not align
+        lib().orc_bilinear2d_bwd_gather_scales(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_hw[0]),
+                                               I64(in_hw[1]), I64(ho), I64(wo), F32(scales[0]), F32(scales[1]),
+                                               I32(fmt))
+        return gi
     fn = lib().orc_bilinear2d_bwd_scatter if definition == "scatter" else lib().orc_bilinear2d_bwd_gather
     fn(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_hw[0]), I64(in_hw[1]), I64(ho), I64(wo),
        I32(int(align)), F32(scales[0]), F32(scales[1]), I32(fmt))

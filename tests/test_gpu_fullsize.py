@@ -33,7 +33,8 @@ def test_cfg2_fpn_upsample_fp16(ops, oracle, dev):
     back = ops.upsample_nearest2d_backward(yn, (ho, wo), (n, c, hi, wi), scales=(2.0, 2.0))
     assert torch.equal(back.cpu(), (x.float() * 4).to(torch.float16))
     gn = ops.upsample_nearest2d_backward(god, (ho, wo), (n, c, hi, wi), scales=(2.0, 2.0))
-    check(ends(gn), oracle.nearest2d_bwd(ends(go).float().numpy(), (hi, wi), (2.0, 2.0)), torch.float16)
+    # the kernel adds the four fp32 values in the reference's row-major order: same bits
+    check(ends(gn), oracle.nearest2d_bwd(ends(go).float().numpy(), (hi, wi), (2.0, 2.0)), torch.float16, exact=True)
     # bilinear
     yb = ops.upsample_bilinear2d(xd, (ho, wo), False, scales=(2.0, 2.0))
     check(ends(yb), oracle.bilinear2d_fwd(ends(x).float().numpy(), (ho, wo), False, (2.0, 2.0)), torch.float16)
@@ -43,7 +44,12 @@ def test_cfg2_fpn_upsample_fp16(ops, oracle, dev):
     gb = ops.upsample_bilinear2d_backward(god, (ho, wo), (n, c, hi, wi), False, scales=(2.0, 2.0))
     gb2 = ops.upsample_bilinear2d_backward(god, (ho, wo), (n, c, hi, wi), False, scales=(2.0, 2.0))
     assert torch.equal(gb.view(torch.int16), gb2.view(torch.int16))
-    check_sum(ends(gb), oracle.bilinear2d_bwd(ends(go).float().numpy(), (hi, wi), False, (2.0, 2.0)), torch.float16)
+    # the reference runs its gather ("determine") kernel for this call (up-scale, user scale equal to the size
+    # ratio): at most 1 ulp of fp16 from it, and from the atomic kernel's serial order as well
+    go_ends = ends(go).float().numpy()
+    assert oracle.bilinear2d_bwd_kernel_choice((hi, wi), (ho, wo), False, (2.0, 2.0)) == "gather"
+    check(ends(gb), oracle.bilinear2d_bwd(go_ends, (hi, wi), False, (2.0, 2.0), definition="gather"), torch.float16)
+    check(ends(gb), oracle.bilinear2d_bwd(go_ends, (hi, wi), False, (2.0, 2.0), definition="scatter"), torch.float16)
     # per-plane sums are preserved (fp32 sums of the fp16 tensors; the fp16 rounding of gi bounds the difference)
     s_in, s_out = god.float().sum((2, 3)), gb.float().sum((2, 3))
     assert (s_in - s_out).abs().max().item() <= 2.0 ** -10 * gb.float().abs().sum((2, 3)).max().item()
@@ -55,11 +61,11 @@ def test_cfg3_bicubic_aa_fp32(ops, oracle, dev):
     go = torch.randn((n, c, ho, wo), generator=gen(1239))
     xd, god = x.to(dev), go.to(dev)
     y = ops.upsample_bicubic2d_aa(xd, (ho, wo), False)
-    check(ends(y), oracle.bicubic_aa_fwd(ends(x).numpy(), (ho, wo), False), torch.float32, atol=2e-6)
+    check(ends(y), oracle.bicubic_aa_fwd(ends(x).numpy(), (ho, wo), False), torch.float32)
     const = ops.upsample_bicubic2d_aa(torch.full((2, 1, hi, wi), 0.625, device=dev), (ho, wo), False)
     assert (const - 0.625).abs().max().item() <= 1e-6
     gi = ops.upsample_bicubic2d_aa_grad(god, (ho, wo), (n, c, hi, wi), False)
-    check(ends(gi), oracle.bicubic_aa_bwd(ends(go).numpy(), (hi, wi), False), torch.float32, atol=2e-6)
+    check(ends(gi), oracle.bicubic_aa_bwd(ends(go).numpy(), (hi, wi), False), torch.float32)
     s_in, s_out = god.double().sum((2, 3)), gi.double().sum((2, 3))
     assert (s_in - s_out).abs().max().item() <= 1e-4 * god.double().abs().sum((2, 3)).max().item()
     assert ops.async_copy_timeouts() == 0
@@ -115,3 +121,48 @@ def test_cfg5_box_sweep_shard(ops, oracle, dev):
     gy = ops.grid_sampler2d(gx.to(dev), grid.to(dev), 0, 0, False)
     check(ends(gy), oracle.grid_sampler2d_fwd(ends(gx).numpy(), ends(grid).numpy(), 0, 0, False), torch.float32,
           exact=True)
+
+
+def _affine_grids(n, size, g):
+    phi = (torch.rand(n, generator=g) * 60 - 30) * np.pi / 180
+    s = torch.rand(n, generator=g) * 0.4 + 0.8
+    t = torch.rand((n, 2), generator=g) * 0.2 - 0.1
+    theta = torch.stack([torch.stack([s * torch.cos(phi), -s * torch.sin(phi), t[:, 0]], 1),
+                         torch.stack([s * torch.sin(phi), s * torch.cos(phi), t[:, 1]], 1)], 1)
+    return torch.nn.functional.affine_grid(theta, (n, 1, size, size), align_corners=False).contiguous()
+
+
+def test_cfg5_box_sweep_whole_batch_on_one_gpu(ops, oracle, dev):
+    """The one-GPU point of the box sweep: the whole batch in one call. The bilinear output has 512 * 128 * 128 * 256 =
+    2^31 elements, so every element offset of the last image is at or beyond 2^31 - 2^22 and the last one is 2^31 - 1:
+    in-kernel offsets must be 64-bit. The first and the last image are seeded on the CPU and checked against the
+    oracle; the images between them are filled on the device (the oracle, a scalar CPU program, could not check them
+    in reasonable time, and every image is computed independently)."""
+    n, c, hi, wi, ho, wo = 512, 256, 64, 64, 128, 128
+    x = torch.empty((n, hi, wi, c), dtype=torch.bfloat16, device=dev)
+    x.normal_(generator=torch.Generator(device=dev).manual_seed(1245))
+    first_last = torch.randn((2, hi, wi, c), generator=gen(1246)).to(torch.bfloat16)
+    x[0].copy_(first_last[0])
+    x[-1].copy_(first_last[1])
+    y = ops.upsample_bilinear2d(x, (ho, wo), False, "NHWC")
+    assert y.numel() == 2 ** 31
+    ref = oracle.bilinear2d_fwd(first_last.float().numpy(), (ho, wo), False, fmt=oracle.NHWC)
+    check(ends(y), ref, torch.bfloat16)
+    # an image in the middle against a separate single-image call (same kernel, small offsets)
+    mid = n // 2 + 1
+    assert torch.equal(y[mid].view(torch.int16),
+                       ops.upsample_bilinear2d(x[mid:mid + 1].contiguous(), (ho, wo), False, "NHWC")[0].view(torch.int16))
+    del y, x
+    # grid sampler fp32, N = 256, affine grids
+    n2, c2, h2 = 256, 128, 96
+    g = gen(1247)
+    grid = _affine_grids(n2, h2, g)
+    gx = torch.empty((n2, c2, h2, h2), device=dev)
+    gx.normal_(generator=torch.Generator(device=dev).manual_seed(1248))
+    fl = torch.randn((2, c2, h2, h2), generator=g)
+    gx[0].copy_(fl[0])
+    gx[-1].copy_(fl[1])
+    gy = ops.grid_sampler2d(gx, grid.to(dev), 0, 0, False)
+    check(ends(gy), oracle.grid_sampler2d_fwd(fl.numpy(), ends(grid).numpy(), 0, 0, False), torch.float32, exact=True)
+    mid = n2 // 2 + 1
+    assert torch.equal(gy[mid], ops.grid_sampler2d(gx[mid:mid + 1].contiguous(), grid[mid:mid + 1].to(dev), 0, 0, False)[0])
