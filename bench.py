@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the resampling hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5|all] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload default|cfg2|cfg3|cfg4|cfg4bf16|cfg5|all]
+                    [--batch-div D] [--impl reference]
 
 One "step" is one pass of every operator of the workload over one batch of seeded synthetic input, called
 through the library's C ABI (two-phase aclnn calls). The default workload is the FPN-style up-sampling case
@@ -15,7 +16,12 @@ Printed JSON (one line, rank 0):
   roofline   the operator with the largest share of the step: algorithmic bytes per launch / average launch
              duration (CUDA events on the launching stream) against the measured HBM copy peak;
   ops        the same figures for every operator of the workload;
-  cpu_baseline  the CPU oracle (the reference's kernel arithmetic restated in C++/OpenMP) on a bounded sample.
+  cpu_baseline  the CPU oracle (the reference's kernel arithmetic restated in C++/OpenMP) on a bounded sample, and
+             beside it the torch CPU operators the reference's own test scripts use as their golden, same sample;
+  other_workloads  (default run, one GPU) the same per-operator figures for the other benchmark configurations,
+             fewer steps each, every one with its own clock record;
+  box_sweep  BASELINE configuration 5 split evenly along N over the ranks (strong scaling): box time = slowest rank,
+             efficiency = T(1) / (G * T(G)) with T(1) measured in the same run on the whole batch.
 
 Timing: CUDA events on the launching stream, max over ranks; every step works on a different one of several
 buffer sets whose total exceeds the L2 capacity, so no operator finds its input in L2.
@@ -33,7 +39,27 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-L2_BYTES = 126 * 1024 * 1024
+L2_FALLBACK_BYTES = 126 * 1024 * 1024
+
+
+def l2_bytes(torch=None, dev=None):
+    """L2 capacity of the device (cudaDeviceProp::l2CacheSize); the B200 figure when no device is visible."""
+    try:
+        if torch is not None and torch.cuda.is_available():
+            return int(torch.cuda.get_device_properties(dev if dev is not None else 0).L2_cache_size)
+    except Exception:  # noqa: BLE001 - any failure means "no device to ask"
+        pass
+    return L2_FALLBACK_BYTES
+
+
+def buffer_sets(set_bytes, l2, wanted=0):
+    """How many buffer sets a workload rotates: enough to exceed L2 four times, at least 3, at most 16."""
+    return min(wanted or max(3, -(-4 * l2 // set_bytes)), 16)
+
+
+def l2_note(nsets, set_bytes, l2):
+    return (f"rotating {nsets} buffer sets of {set_bytes / 1e6:.0f} MB ({nsets * set_bytes / 1e6:.0f} MB > "
+            f"{l2 / 1e6:.0f} MB L2): each step's inputs come from HBM")
 
 
 def measured_peak():
@@ -41,11 +67,14 @@ def measured_peak():
     if os.path.exists(path):
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, STREAM-style copy)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s: no MEASURED_PEAKS.json beside this file)"
 
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the main kernel of each operator, from the
-# captures summarised under profiles/ (None = not captured).
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the main kernel of each operator, copied from the
+# captures summarised under profiles/ (None = not captured). These are constants from earlier profiler runs, not
+# measurements of this run: every row that carries one also names the summary it comes from (TRAFFIC_SOURCE).
+TRAFFIC_SOURCE = {"cfg2": "profiles/cfg2_fpn_upsample_kernels_ncu.md", "cfg3": "profiles/cfg3_bicubic_aa_kernels_ncu.md",
+                  "cfg4": "profiles/cfg4_grid_sampler_kernels_ncu.md", "cfg5": "profiles/cfg5_box_sweep_kernels_ncu.md"}
 NCU_TRAFFIC = {
     ("cfg2", "UpsampleNearest2d"): 201.0e6, ("cfg2", "UpsampleBilinear2d"): 206.1e6,
     ("cfg2", "UpsampleNearest2dBackward"): 242.2e6, ("cfg2", "UpsampleBilinear2dBackward"): 245.9e6,
@@ -73,8 +102,10 @@ def nbytes(t):
     return t.numel() * t.element_size()
 
 
-def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
-    """Returns (description, make_buffers(gen) -> dict of CPU tensors, [Op], config dict)."""
+def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
+    """Returns (make_buffers(gen) -> dict of tensors on the generator's device, [Op], config dict).
+    batch_div: the batch divided by this (small cases for profiler captures). shard = (world, rank): cfg5 only, the
+    rank's share of the box-level batch (contiguous split along N)."""
     ws = ops.Workspace(dev) if ops is not None else None  # None: only the description is wanted
     # one workspace per operator for workloads whose operators are independent of each other: they may then run on
     # parallel branches of the step graph
@@ -86,10 +117,12 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
 
         def buffers(gen):
             return {
-                "x": torch.randn((n, c, hi, wi), generator=gen).to(dt),
-                "go": torch.randn((n, c, ho, wo), generator=gen).to(dt),
-                "y_nearest": torch.empty((n, c, ho, wo), dtype=dt), "y_bilinear": torch.empty((n, c, ho, wo), dtype=dt),
-                "gi_nearest": torch.empty((n, c, hi, wi), dtype=dt), "gi_bilinear": torch.empty((n, c, hi, wi), dtype=dt),
+                "x": torch.randn((n, c, hi, wi), generator=gen, device=gen.device).to(dt),
+                "go": torch.randn((n, c, ho, wo), generator=gen, device=gen.device).to(dt),
+                "y_nearest": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "y_bilinear": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "gi_nearest": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
+                "gi_bilinear": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
             }
         small, big = n * c * hi * wi * 2, n * c * ho * wo * 2
         oplist = [
@@ -116,9 +149,10 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
 
         def buffers(gen):
             return {
-                "x": (torch.randint(0, 256, (n, c, hi, wi), generator=gen).to(dt) / 255.0),
-                "go": torch.randn((n, c, ho, wo), generator=gen),
-                "y": torch.empty((n, c, ho, wo), dtype=dt), "gi": torch.empty((n, c, hi, wi), dtype=dt),
+                "x": (torch.randint(0, 256, (n, c, hi, wi), generator=gen, device=gen.device).to(dt) / 255.0),
+                "go": torch.randn((n, c, ho, wo), generator=gen, device=gen.device),
+                "y": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "gi": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
             }
         big, small = n * c * hi * wi * 4, n * c * ho * wo * 4
         oplist = [
@@ -142,22 +176,23 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
 
         def make_grid(gen):
             if name != "cfg4affine":
-                return torch.rand((n, ho, wo, 2), generator=gen) * 2.2 - 1.1
+                return torch.rand((n, ho, wo, 2), generator=gen, device=gen.device) * 2.2 - 1.1
             import math
-            phi = (torch.rand(n, generator=gen) * 60 - 30) * math.pi / 180
-            sc = torch.rand(n, generator=gen) * 0.4 + 0.8
-            t = torch.rand((n, 2), generator=gen) * 0.2 - 0.1
+            phi = (torch.rand(n, generator=gen, device=gen.device) * 60 - 30) * math.pi / 180
+            sc = torch.rand(n, generator=gen, device=gen.device) * 0.4 + 0.8
+            t = torch.rand((n, 2), generator=gen, device=gen.device) * 0.2 - 0.1
             theta = torch.stack([torch.stack([sc * torch.cos(phi), -sc * torch.sin(phi), t[:, 0]], 1),
                                  torch.stack([sc * torch.sin(phi), sc * torch.cos(phi), t[:, 1]], 1)], 1)
             return torch.nn.functional.affine_grid(theta, (n, c, ho, wo), align_corners=False).contiguous()
 
         def buffers(gen):
             return {
-                "x": torch.randn((n, c, hi, wi), generator=gen).to(dt),
+                "x": torch.randn((n, c, hi, wi), generator=gen, device=gen.device).to(dt),
                 "grid": make_grid(gen).to(dt),
-                "go": torch.randn((n, c, ho, wo), generator=gen).to(dt),
-                "y": torch.empty((n, c, ho, wo), dtype=dt), "gi": torch.empty((n, c, hi, wi), dtype=dt),
-                "ggrid": torch.empty((n, ho, wo, 2), dtype=dt),
+                "go": torch.randn((n, c, ho, wo), generator=gen, device=gen.device).to(dt),
+                "y": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "gi": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
+                "ggrid": torch.empty((n, ho, wo, 2), dtype=dt, device=gen.device),
             }
         xin, gr, out = n * c * hi * wi * es, n * ho * wo * 2 * es, n * c * ho * wo * es
 
@@ -188,19 +223,26 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
         import math
         n, c, hi, wi, ho, wo = 512 // batch_div, 256, 64, 64, 128, 128
         n2, c2, h2 = 256 // batch_div, 128, 96
+        total = (n, n2)
+        if shard is not None:
+            from opscv_b200 import sharding
+            b, e = sharding.shard_range(n, *shard)
+            b2, e2 = sharding.shard_range(n2, *shard)
+            n, n2 = e - b, e2 - b2
 
         def buffers(gen):
-            phi = (torch.rand(n2, generator=gen) * 60 - 30) * math.pi / 180
-            s = torch.rand(n2, generator=gen) * 0.4 + 0.8
-            t = torch.rand((n2, 2), generator=gen) * 0.2 - 0.1
+            dv = gen.device
+            phi = (torch.rand(n2, generator=gen, device=dv) * 60 - 30) * math.pi / 180
+            s = torch.rand(n2, generator=gen, device=dv) * 0.4 + 0.8
+            t = torch.rand((n2, 2), generator=gen, device=dv) * 0.2 - 0.1
             theta = torch.stack([torch.stack([s * torch.cos(phi), -s * torch.sin(phi), t[:, 0]], 1),
                                  torch.stack([s * torch.sin(phi), s * torch.cos(phi), t[:, 1]], 1)], 1)
             grid = torch.nn.functional.affine_grid(theta, (n2, c2, h2, h2), align_corners=False)
             return {
-                "x": torch.randn((n, hi, wi, c), generator=gen).to(torch.bfloat16),
-                "y": torch.empty((n, ho, wo, c), dtype=torch.bfloat16),
-                "gx": torch.randn((n2, c2, h2, h2), generator=gen), "grid": grid.contiguous(),
-                "gy": torch.empty((n2, c2, h2, h2)),
+                "x": torch.randn((n, hi, wi, c), generator=gen, device=dv).to(torch.bfloat16),
+                "y": torch.empty((n, ho, wo, c), dtype=torch.bfloat16, device=dv),
+                "gx": torch.randn((n2, c2, h2, h2), generator=gen, device=dv), "grid": grid.contiguous(),
+                "gy": torch.empty((n2, c2, h2, h2), device=dv),
             }
         oplist = [
             Op("UpsampleBilinear2d[NHWC bf16]", lambda b: ops.upsample_bilinear2d(b["x"], (ho, wo), False, "NHWC",
@@ -210,8 +252,10 @@ def make_workload(name, ops, torch, dev, batch_div=1, seed=1234):
                                                                          workspace=wss[1]),
                n2 * c2 * h2 * h2 * 4 * 2 + n2 * h2 * h2 * 2 * 4, n2 * h2 * h2, ["gx", "grid"], ["gy"]),
         ]
-        cfg = {"workload": f"box sweep shard: UpsampleBilinear2d bf16 NHWC N={n} C=256 64x64 -> 128x128 + GridSampler2D "
-                           f"fp32 N={n2} C=128 96x96 affine grids", "dtype": "bf16/f32"}
+        cfg = {"workload": f"box sweep: UpsampleBilinear2d bf16 NHWC N={n} C=256 64x64 -> 128x128 + GridSampler2D "
+                           f"fp32 N={n2} C=128 96x96 affine grids" +
+                           (f" (this rank's share of N={total[0]} / N={total[1]})" if shard is not None else ""),
+               "dtype": "bf16/f32", "images": [n, n2]}
         return buffers, oplist, cfg
     raise ValueError(name)
 
@@ -313,17 +357,22 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------------------------
 # CPU baseline (the oracle, timed; never part of the GPU path)
 # ---------------------------------------------------------------------------------------------------------------
-def cpu_baseline(workload, budget_s=12.0):
-    """Times the CPU oracle on a bounded sample of `workload` on the host cores. Returns the JSON object."""
+def cpu_baseline(workload, budget_s=12.0, torch_budget_s=6.0):
+    """Times two CPU arms on a bounded sample of `workload` on the host cores: the oracle (the reference's kernel
+    arithmetic restated in C++/OpenMP) and, beside it, the torch CPU operators that the reference's own test scripts
+    compute their goldens with. Returns the JSON object (value = the oracle's figure)."""
     import numpy as np
     import torch
+    import torch.nn.functional as F
     import oracle
     oracle.build()
     # all host cores this process may use, whatever OMP_NUM_THREADS a launcher (torchrun sets 1) exported
-    oracle.set_num_threads(len(os.sched_getaffinity(0)))
+    threads = len(os.sched_getaffinity(0))
+    oracle.set_num_threads(threads)
     cores = oracle.num_threads()
+    torch.set_num_threads(threads)
     rng = np.random.default_rng(1234)
-    if workload in ("cfg2", "all"):
+    if workload in ("cfg2", "all", "default"):
         n, c = 4, 256  # 1/8 of the batch of the GPU workload; planes are independent
         x = rng.standard_normal((n, c, 56, 56)).astype(np.float32)
         go = rng.standard_normal((n, c, 112, 112)).astype(np.float32)
@@ -333,7 +382,15 @@ def cpu_baseline(workload, budget_s=12.0):
             oracle.nearest2d_fwd(x, (112, 112))
             oracle.bilinear2d_fwd(x, (112, 112), False, (2.0, 2.0))
             oracle.nearest2d_bwd(go, (56, 56), (2.0, 2.0))
-            oracle.bilinear2d_bwd(go, (56, 56), False, (2.0, 2.0), definition="gather")
+            # the kernel the reference dispatches for this call, the same definition the parity tests hold the GPU to
+            oracle.bilinear2d_bwd(go, (56, 56), False, (2.0, 2.0), definition="dispatch")
+        xt, got = torch.from_numpy(x), torch.from_numpy(go)
+
+        def run_torch():
+            F.interpolate(xt, size=(112, 112), mode="nearest")
+            F.interpolate(xt, size=(112, 112), mode="bilinear", align_corners=False)
+            torch.ops.aten.upsample_nearest2d_backward(got, [112, 112], [n, c, 56, 56], 2.0, 2.0)
+            torch.ops.aten.upsample_bilinear2d_backward(got, [112, 112], [n, c, 56, 56], False, 2.0, 2.0)
         algo = 4 * (small + big)
         sample = f"N={n} of 32 images (C={c}), all four operators, fp32 arithmetic"
     elif workload == "cfg3":
@@ -343,6 +400,11 @@ def cpu_baseline(workload, budget_s=12.0):
         def run():
             oracle.bicubic_aa_fwd(x, (224, 224))
             oracle.bicubic_aa_bwd(go, (1024, 1024), definition="scatter")
+        xt, got = torch.from_numpy(x), torch.from_numpy(go)
+
+        def run_torch():
+            F.interpolate(xt, size=(224, 224), mode="bicubic", align_corners=False, antialias=True)
+            torch.ops.aten._upsample_bicubic2d_aa_backward(got, [224, 224], [1, 3, 1024, 1024], False, None, None)
         algo = 2 * (x.size + go.size) * 4
         sample = "N=1 of 64 images, forward + backward (scatter definition)"
     elif workload in ("cfg4", "cfg4bf16", "cfg4affine"):
@@ -354,6 +416,11 @@ def cpu_baseline(workload, budget_s=12.0):
         def run():
             oracle.grid_sampler2d_fwd(x, grid)
             oracle.grid_sampler2d_bwd(go, x, grid)
+        xt, gt, got = torch.from_numpy(x), torch.from_numpy(grid), torch.from_numpy(go)
+
+        def run_torch():
+            F.grid_sample(xt, gt, mode="bilinear", padding_mode="zeros", align_corners=False)
+            torch.ops.aten.grid_sampler_2d_backward(got, xt, gt, 0, 0, False, [True, True])
         algo = ((x.size + grid.size + go.size) + (go.size + 2 * x.size + 2 * grid.size)) * es
         sample = "N=1 of 16 images, forward + backward"
     else:
@@ -364,60 +431,103 @@ def cpu_baseline(workload, budget_s=12.0):
         def run():
             oracle.bilinear2d_fwd(x, (128, 128), False, fmt=oracle.NHWC)
             oracle.grid_sampler2d_fwd(gx, grid)
+        xt = torch.from_numpy(x).permute(0, 3, 1, 2)  # channels-last storage seen as NCHW
+        gxt, gt = torch.from_numpy(gx), torch.from_numpy(grid)
+
+        def run_torch():
+            F.interpolate(xt, size=(128, 128), mode="bilinear", align_corners=False)
+            F.grid_sample(gxt, gt, mode="bilinear", padding_mode="zeros", align_corners=False)
         algo = x.size * 5 * 2 + (gx.size * 2 + grid.size) * 4
         sample = "N=4 of 512 (bilinear NHWC) and N=2 of 256 (grid sampler)"
-    run()  # warm-up (page faults, OpenMP pool)
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
-        run()
-        reps += 1
-        if (time.perf_counter() - t0 > budget_s and reps >= 3) or reps >= 5000:
-            break
-    dt = (time.perf_counter() - t0) / reps
-    return {"value": algo / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": sample + f"; {reps} repetitions, {dt * 1e3:.1f} ms each", "ms_per_sample": dt * 1e3}
+
+    def clock(fn, budget):
+        fn()  # warm-up (page faults, thread pools)
+        t0 = time.perf_counter()
+        reps = 0
+        while True:
+            fn()
+            reps += 1
+            if (time.perf_counter() - t0 > budget and reps >= 3) or reps >= 5000:
+                break
+        return (time.perf_counter() - t0) / reps, reps
+    dt, reps = clock(run, budget_s)
+    out = {"value": algo / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+           "sample": sample + f"; {reps} repetitions, {dt * 1e3:.1f} ms each", "ms_per_sample": dt * 1e3}
+    try:
+        with torch.no_grad():
+            tdt, treps = clock(run_torch, torch_budget_s)
+        out["torch_cpu"] = {"value": algo / tdt / 1e9, "unit": "GB/s", "threads": torch.get_num_threads(),
+                            "sample": f"same sample, torch {torch.__version__} CPU operators (interpolate / grid_sample "
+                                      f"and their aten backward functions); {treps} repetitions, {tdt * 1e3:.1f} ms each"}
+    except Exception as exc:  # noqa: BLE001 - the torch arm is a second opinion; the port's figure stands without it
+        out["torch_cpu"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+    return out
 
 
 # ---------------------------------------------------------------------------------------------------------------
+L2_RULE = ("no L2 flush: consecutive steps rotate over several buffer sets whose total is at least four times the L2 "
+           "capacity (cudaDeviceProp::l2CacheSize), so every step reads its inputs from HBM; sizes in l2_detail")
+
+
+def arm_config(cfg):
+    """The `config` object of a workload: the same keys and values in this library's arm and in the CPU reference
+    arm, which runs a bounded sample of the same workload (the sample is described in a key of its own)."""
+    return {"workload": cfg["workload"], "per_gpu_batch": "fixed (weak scaling)", "l2": L2_RULE}
+
+
+METRIC = "effective HBM GB/s (algorithmic bytes / device time), all operators of the step"
+OTHER_WORKLOADS = ["cfg3", "cfg4", "cfg4bf16", "cfg5"]
+LAUNCH_NOTE = ("CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding "
+               "all operators of the step (cfg2, cfg3, cfg5: the independent operators of a step on parallel branches, "
+               "each with its own workspace; cfg4: one after the other, the two backward modes write the same tensors); "
+               "the per-operator times come from a separate pass: per-operator graphs launched back to back over all "
+               "buffer sets between one pair of events")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--workload", default="default",
+                    help="default = cfg2 as the head line plus the other configurations with fewer steps")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="default workload: skip the other configurations")
+    ap.add_argument("--no-box-sweep", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls instead of CUDA-graph replays")
     ap.add_argument("--serial-step", action="store_true",
                     help="step graph with the operators one after the other instead of on parallel branches")
     ap.add_argument("--sets", type=int, default=0, help="buffer sets to rotate (0 = enough to exceed L2 four times)")
+    ap.add_argument("--batch-div", type=int, default=1,
+                    help="divide every batch by this: small cases for profiler captures (not a benchmark number)")
+    ap.add_argument("--other-steps", type=int, default=60, help="timed steps of each of the other configurations")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    head_name = "cfg2" if args.workload in ("default", "all") else args.workload
 
     if args.impl == "reference":
         # The reference's own implementation of this path needs the CANN toolkit (Ascend C kernels) and cannot be
-        # built here; its arithmetic restated on the CPU (the oracle) stands in, on all host threads.
+        # built here; its arithmetic restated on the CPU (the oracle) stands in, on all host threads, and the torch
+        # CPU operators its test scripts take their goldens from are timed beside it.
         if rank != 0:
             return
-        wl = "cfg2" if args.workload == "all" else args.workload
-        base = cpu_baseline(wl, budget_s=max(5.0, min(60.0, 2.0 * args.steps)))
+        base = cpu_baseline(head_name, budget_s=max(5.0, min(60.0, 2.0 * args.steps)))
         import torch
-        cfg = make_workload(wl, None, torch, None)[2]
+        cfg = make_workload(head_name, None, torch, None)[2]
         line = {
-            "impl": "reference",
-            "metric": "effective HBM GB/s (algorithmic bytes / device time), all operators of the step",
+            "impl": "reference", "metric": METRIC,
             "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": base["ms_per_sample"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": cfg["dtype"], "data": "synthetic",
-            "config": {"workload": cfg["workload"],
-                       "sample": "each step is a bounded sample on the host CPU: " + base["sample"]},
-            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "dtype": cfg["dtype"], "data": "synthetic (seeded)",
+            "config": arm_config(cfg),
+            "sample": "each step is a bounded sample of the workload on the host CPU: " + base["sample"],
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "torch_cpu")},
             "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
         print(json.dumps(line))
@@ -435,51 +545,102 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    names = ["cfg2", "cfg3", "cfg4", "cfg4bf16", "cfg5"] if args.workload == "all" else [args.workload]
     peak, peak_src = measured_peak()
-    results = {}
-    for wname in names:
-        results[wname] = run_workload(wname, args, ops, torch, dev, dist, world, rank, peak)
-        torch.cuda.empty_cache()
+    ctx = dict(args=args, ops=ops, torch=torch, dev=dev, dist=dist, world=world, rank=rank, peak=peak)
+    head = run_workload(head_name, steps=args.steps, do_e2e=not args.no_e2e, host_data=True, **ctx)
+    torch.cuda.empty_cache()
+    others = {}
+    if args.workload == "all" or (args.workload == "default" and world == 1 and not args.no_others):
+        for wname in OTHER_WORKLOADS:
+            others[wname] = run_workload(wname, steps=min(args.steps, args.other_steps), do_e2e=False, host_data=False,
+                                         **ctx)
+            torch.cuda.empty_cache()
+    sweep = None
+    if args.workload in ("default", "all") and not args.no_box_sweep and args.batch_div == 1:
+        sweep = box_sweep(others.get("cfg5"), **ctx)
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
-    head = results[names[0]]
     line = {
-        "metric": "effective HBM GB/s (algorithmic bytes / device time), all operators of the step",
+        "metric": METRIC,
         "value": head["value"], "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": head["config"]["dtype"], "data": "synthetic (seeded torch.Generator)",
-        "config": {"workload": head["config"]["workload"], "l2": head["l2_note"], "per_gpu_batch": "fixed (weak scaling)",
-                   "launch": "eager aclnn calls" if args.no_graph else
-                   "CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding all operators of the step (cfg2, cfg3, cfg5: the independent operators of a step on parallel branches, each with its own workspace; cfg4: one after the other, the two backward modes write the same tensors); the per-operator times come from a separate pass: per-operator graphs launched back to back over all buffer sets between one pair of events"},
+        "config": arm_config(head["config"]), "l2_detail": head["l2_note"],
+        "launch": "eager aclnn calls" if args.no_graph else LAUNCH_NOTE,
         "mpix_per_s": head["mpix_per_s"], "pct_of_hbm_peak": head["value"] / (peak * world),
         "roofline": head["roofline"], "ops": head["ops"], "e2e": head["e2e"], "gpu_launches": head["gpu_launches"],
         "clocks": head["clocks"], "peak_source": peak_src,
     }
+    if args.batch_div != 1:
+        line["batch_div"] = args.batch_div
     if not args.no_cpu_baseline and world == 1:  # reported at N=1 only
-        base = cpu_baseline(names[0])
-        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    if len(names) > 1:
-        line["other_workloads"] = {k: {kk: v[kk] for kk in ("value", "ms_per_step", "mpix_per_s", "ops", "config")}
-                                   for k, v in results.items() if k != names[0]}
+        base = cpu_baseline(head_name)
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "torch_cpu")}
+    if others:
+        line["other_workloads"] = {k: {kk: v[kk] for kk in ("value", "ms_per_step", "steps", "mpix_per_s", "ops", "clocks",
+                                                            "gpu_launches", "l2_note", "config")}
+                                   for k, v in others.items()}
+    if sweep is not None:
+        line["box_sweep"] = sweep
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
 
-def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
-    make_buffers, oplist, cfg = make_workload(wname, ops, torch, dev)
-    gen = torch.Generator().manual_seed(1234 + rank)
-    host = make_buffers(gen)
-    set_bytes = sum(nbytes(t) for t in host.values())
-    nsets = args.sets or max(3, -(-4 * L2_BYTES // set_bytes))
-    nsets = min(nsets, 16)
-    dsets = [{k: v.to(dev) for k, v in host.items()} for _ in range(nsets)]
-    l2_note = (f"rotating {nsets} buffer sets of {set_bytes / 1e6:.0f} MB ({nsets * set_bytes / 1e6:.0f} MB > "
-               f"{L2_BYTES / 1e6:.0f} MB L2): each step's inputs come from HBM")
+def box_sweep(cfg5_result, args, ops, torch, dev, dist, world, rank, peak):
+    """BASELINE configuration 5 split evenly along N over the ranks (strong scaling, no collective): rank r owns the
+    images sharding.shard_range(N, world, r) of both operators. T(1) is the same workload with the whole batch on one
+    GPU, measured in this run (every rank times it on its own GPU; the slowest counts); efficiency = T(1) / (G * T(G)).
+    With one rank the object just restates the cfg5 figures as the sweep's G = 1 point."""
+    steps = min(args.steps, args.other_steps)
+    ctx = dict(args=args, ops=ops, torch=torch, dev=dev, dist=dist, world=world, rank=rank, peak=peak)
+    whole = cfg5_result or run_workload("cfg5", steps=steps, do_e2e=False, host_data=False, **ctx)
+    torch.cuda.empty_cache()
+    part = whole if world == 1 else run_workload("cfg5", steps=steps, do_e2e=False, host_data=False,
+                                                 shard=(world, rank), **ctx)
+    torch.cuda.empty_cache()
+    n_b, n_g = 512, 256
+    pixels = n_b * 128 * 128 + n_g * 96 * 96
+    algo = sum(r["algorithmic_bytes"] for r in whole["ops"].values())
+    t1, tg = whole["ms_per_step"], part["ms_per_step"]
+    op_rows = {}
+    for name, row in whole["ops"].items():
+        g = part["ops"][name]
+        op_rows[name] = {"ms_1gpu": row["ms"], "ms": g["ms"], "efficiency": row["ms"] / (world * g["ms"]),
+                         "box_gb_per_s": row["algorithmic_bytes"] / (g["ms"] * 1e-3) / 1e9,
+                         "frac_of_peak_per_gpu": row["algorithmic_bytes"] / world / (g["ms"] * 1e-3) / 1e9 / peak}
+    return {"workload": f"UpsampleBilinear2d bf16 NHWC N={n_b} C=256 64x64 -> 128x128 + GridSampler2D fp32 N={n_g} C=128 "
+                        "96x96 random affine grids, split evenly along N over the ranks (contiguous, rank-local "
+                        "tensors, no collective)",
+            "scaling": "strong", "n_gpus": world,
+            "images_per_rank": [-(-n_b // world), -(-n_g // world)],
+            "ms_per_step_1gpu": t1, "ms_per_step": tg, "efficiency": t1 / (world * tg),
+            "box_gb_per_s": algo / (tg * 1e-3) / 1e9, "box_mpix_per_s": pixels / tg / 1e3,
+            "pct_of_hbm_peak_per_gpu": algo / world / (tg * 1e-3) / 1e9 / peak,
+            "steps": steps, "ops": op_rows, "clocks": part["clocks"]}
+
+
+def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak, steps, do_e2e, host_data, shard=None):
+    """One workload on this rank's GPU. host_data: the seeded inputs are drawn on the CPU and copied in (needed by the
+    end-to-end arm); otherwise they are drawn on the device from a seeded device generator (large configurations)."""
+    make_buffers, oplist, cfg = make_workload(wname, ops, torch, dev, args.batch_div, shard)
+    if host_data:
+        host = make_buffers(torch.Generator().manual_seed(1234 + rank))
+        set_bytes = sum(nbytes(t) for t in host.values())
+    else:
+        host = None
+        first = make_buffers(torch.Generator(device=dev).manual_seed(1234 + rank))
+        set_bytes = sum(nbytes(t) for t in first.values())
+    l2 = l2_bytes(torch, dev)
+    nsets = buffer_sets(set_bytes, l2, args.sets)
+    if host_data:
+        dsets = [{k: v.to(dev) for k, v in host.items()} for _ in range(nsets)]
+    else:
+        dsets = [first] + [{k: v.clone() for k, v in first.items()} for _ in range(nsets - 1)]
+    note = l2_note(nsets, set_bytes, l2)
     stream = torch.cuda.current_stream(dev)
 
     def barrier():
@@ -550,7 +711,7 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
     # An operator's time is the average over back-to-back launches on all buffer sets between one pair of events
     # (the sets rotate, so every launch still reads its inputs from HBM); bracketing single ~50 us launches would
     # add the few microseconds it takes the host to get the next graph launch to an idle GPU.
-    bsteps = max(1, min(args.steps, 50) // nsets)
+    bsteps = max(1, min(steps, 50) // nsets)
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in oplist]
           for _ in range(bsteps)]
     for i in range(bsteps):
@@ -572,7 +733,7 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
     ops.reset_launch_count()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record(stream)
-    for i in range(args.steps):
+    for i in range(steps):
         s_i = (args.warmup + i) % nsets
         if step_graphs is not None:
             step_graphs[s_i].replay(stream)
@@ -581,37 +742,42 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
                 run_op(j, s_i)
     t_end.record(stream)
     barrier()
-    launches = launches_per_step * args.steps if use_graph else ops.launch_count()
+    launches = launches_per_step * steps if use_graph else ops.launch_count()
     clocks = sampler.stop()
     total_ms = t_start.elapsed_time(t_end)
     from opscv_b200 import sharding  # the box time of a step is that of its slowest rank
     reduced = sharding.max_over_ranks([total_ms] + per_op_ms, dist, dev)
     total_ms, per_op_ms = reduced[0], reduced[1:]
-    step_ms = total_ms / args.steps
+    step_ms = total_ms / steps
     step_bytes = sum(op.algo_bytes for op in oplist)
     step_pix = sum(op.pixels for op in oplist)
     op_rows = {}
     for op, ms in zip(oplist, per_op_ms):
         gbs = op.algo_bytes / (ms * 1e-3) / 1e9
         op_rows[op.name] = {"ms": ms, "gb_per_s": gbs, "frac_of_peak": gbs / peak, "mpix_per_s": op.pixels / ms / 1e3,
-                            "algorithmic_bytes": op.algo_bytes, "traffic": NCU_TRAFFIC.get((wname, op.name))}
+                            "algorithmic_bytes": op.algo_bytes}
+        if shard is None and args.batch_div == 1 and NCU_TRAFFIC.get((wname, op.name)) is not None:
+            op_rows[op.name]["traffic_from_profile"] = NCU_TRAFFIC[(wname, op.name)]
+            op_rows[op.name]["traffic_source"] = TRAFFIC_SOURCE.get(wname[:4])
     dom = max(zip(oplist, per_op_ms), key=lambda p: p[1])
     dom_row = op_rows[dom[0].name]
     roofline = {"kernel": dom[0].name, "bound": "hbm", "achieved": dom_row["gb_per_s"], "peak": peak, "unit": "GB/s",
-                "frac": dom_row["frac_of_peak"], "traffic": dom_row["traffic"],
+                "frac": dom_row["frac_of_peak"], "traffic": dom_row.get("traffic_from_profile"),
+                "traffic_source": (dom_row.get("traffic_source", "") + " (ncu capture of this kernel; a constant from "
+                                   "that capture, not measured in this run)") if "traffic_source" in dom_row else None,
                 "share_of_step": dom[1] / sum(per_op_ms)}
     if use_graph:
         del graphs, step_graphs
 
     # ---- end-to-end arm: host buffers, copies inside the timed region ----------------------------------------
     e2e = None
-    if not args.no_e2e:
+    if do_e2e:
         pinned = {k: v.pin_memory() for k, v in host.items()}
         in_names = sorted({n for op in oplist for n in op.inputs})
         out_names = sorted({n for op in oplist for n in op.outputs})
         h2d = sum(nbytes(host[n]) for n in in_names)
         d2h = sum(nbytes(host[n]) for n in out_names)
-        e2e_steps = max(3, min(args.steps, 10))
+        e2e_steps = max(3, min(steps, 10))
 
         # Copies and kernels are pipelined the way a caller of an asynchronous API would: host->device copies on one
         # stream, the operators on the compute stream, device->host copies on a third, chained by events, so that
@@ -672,7 +838,7 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak):
     del dsets
     return {"value": world * step_bytes / (step_ms * 1e-3) / 1e9, "ms_per_step": step_ms,
             "mpix_per_s": world * step_pix / step_ms / 1e3, "ops": op_rows, "roofline": roofline, "e2e": e2e,
-            "gpu_launches": int(launches), "clocks": clocks, "config": cfg, "l2_note": l2_note}
+            "gpu_launches": int(launches), "clocks": clocks, "config": cfg, "l2_note": note, "steps": steps}
 
 
 if __name__ == "__main__":
