@@ -140,6 +140,41 @@ __device__ __forceinline__ float Add(float a, float b) { return __fadd_rn(a, b);
 __device__ __forceinline__ float Sub(float a, float b) { return __fsub_rn(a, b); }
 __device__ __forceinline__ float Div(float a, float b) { return __fdiv_rn(a, b); }
 
+// Packed fp32 arithmetic (sm_100: two independent IEEE round-to-nearest operations per instruction, one issue
+// slot). Each half has exactly the rounding of the scalar Mul / Add / fma above, so results stay bit-identical;
+// kernels whose limit is instruction issue use them on pairs of values that share an operation.
+struct F2 {
+    unsigned long long r; // two fp32 values in one 64-bit register: .x in the low half
+};
+__device__ __forceinline__ F2 MakeF2(float lo, float hi)
+{
+    F2 v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v.r) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void SplitF2(F2 v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v.r));
+}
+__device__ __forceinline__ F2 Mul2(F2 a, F2 b)
+{
+    F2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.r) : "l"(a.r), "l"(b.r));
+    return d;
+}
+__device__ __forceinline__ F2 Add2(F2 a, F2 b)
+{
+    F2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d.r) : "l"(a.r), "l"(b.r));
+    return d;
+}
+__device__ __forceinline__ F2 Fma2(F2 a, F2 b, F2 c)
+{
+    F2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.r) : "l"(a.r), "l"(b.r), "l"(c.r));
+    return d;
+}
+
 // Launch helper: ceil-div.
 __host__ __device__ __forceinline__ int64_t CeilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

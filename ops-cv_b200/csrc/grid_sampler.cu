@@ -11,6 +11,7 @@
 //     global memory; coordinates are computed once per pixel and reused for the thread's channels.
 //
 // Arithmetic: image/grid_sampler2_d/op_kernel/arch35/grid_sampler2_d_simt.h:303-514 (see grid_coords.cuh).
+#include "cp_async.cuh"
 #include "grid_coords.cuh"
 #include "launch_util.cuh"
 
@@ -269,6 +270,248 @@ __global__ void __launch_bounds__(kStageThreads)
     }
 }
 
+// ---- windowed kernel (bilinear, fp32, planes too large for the plane-major staged kernel) -----------------------
+// A block owns a 32 x 32 tile of output pixels of one image and walks all channels, four at a time. The source
+// coordinates and tap weights of a pixel do not depend on the channel: a thread evaluates them once for its two
+// pixels and keeps them in registers. The block then takes the bounding box of the tile's taps (smooth grids such as
+// affine warps keep it small: a rotated, scaled square a little larger than the tile). For every group of four
+// channels the box is copied from the four input planes into four small planes in shared memory, with 16-byte
+// cp.async into one of two buffers while the previous group is sampled from the other, so the taps are shared-memory
+// reads (neighbouring pixels of a smooth grid read neighbouring words: hardly any bank conflicts) and the copy of
+// the next group overlaps the arithmetic of this one. 16-byte pieces of the box that lie outside the image are
+// zero-filled (a tap there adds 0 * weight: the same fp32 sum as skipping it); rows are multiples of four pixels,
+// which is why the kernel wants win % 4 == 0 and a 16-byte aligned input.
+// A tile whose box does not fit a buffer (a grid that is not smooth) samples from global memory instead, like the
+// direct kernel; the choice is made per tile from the data.
+constexpr int kWinThreads = 512;
+constexpr int kWinTile = 32;
+constexpr int kWinChans = 4;
+constexpr int32_t kWinCapFloats = 3400; // floats per staged plane: 2 buffers * 4 planes * 3400 * 4 B = 106 KiB
+constexpr int kWinPieces = (kWinCapFloats / 4 + kWinThreads - 1) / kWinThreads; // 16-byte pieces a thread may own
+
+__device__ __forceinline__ void CpAsync16Zfill(void* smem, const void* gmem, bool valid)
+{
+    const int srcBytes = valid ? 16 : 0; // 0 source bytes: the sixteen destination bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                     static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+                 "l"(gmem), "r"(srcBytes)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kWinThreads, 2)
+    GridSamplerWindowKernel(const float* __restrict__ x, const float* __restrict__ grid, float* __restrict__ y,
+                            GridShape g, int32_t tilesX, int32_t tilesY, int32_t capFloats, float one)
+{
+    extern __shared__ __align__(16) unsigned char stagedSmem[];
+    __shared__ int32_t box[4]; // min x, max x, min y, max y of the clamped tap origins
+    float* const bufBase = reinterpret_cast<float*>(stagedSmem); // two buffers of kWinChans * capFloats floats
+    const int32_t inPlane = g.hin * g.win;
+    const int64_t outPlane = static_cast<int64_t>(g.hout) * g.wout;
+    const int32_t tx = blockIdx.x % tilesX;
+    const int32_t ty = (blockIdx.x / tilesX) % tilesY;
+    const int64_t n = blockIdx.x / (tilesX * tilesY);
+    const int32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        box[0] = INT32_MAX;
+        box[1] = INT32_MIN;
+        box[2] = INT32_MAX;
+        box[3] = INT32_MIN;
+    }
+    __syncthreads();
+    // The tile is 4 x 8 patches of 8 x 4 pixels; a warp takes the patches warp and warp + 16, a lane one pixel of
+    // each (column lane % 8, row lane / 8 of the patch). The taps of a compact patch conflict on fewer shared-memory
+    // banks than those of a 32 x 1 row (1.6 against 2.4 wavefronts per load for rotated grids, with the row pitch
+    // chosen below), and a warp's stores are four full 32-byte sectors.
+    float wt[2][4];
+    int32_t cx[2], cy[2];
+    int64_t outOff[2];
+    bool live[2], bad[2];
+    int32_t mnx = INT32_MAX, mxx = INT32_MIN, mny = INT32_MAX, mxy = INT32_MIN;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int32_t patch = warp + 16 * j;
+        const int32_t ox = tx * kWinTile + (patch & 3) * 8 + (lane & 7);
+        const int32_t oy = ty * kWinTile + (patch >> 2) * 4 + (lane >> 3);
+        live[j] = ox < g.wout && oy < g.hout;
+        bad[j] = false;
+        cx[j] = cy[j] = 0;
+        outOff[j] = static_cast<int64_t>(oy) * g.wout + ox;
+        if (live[j]) {
+            const int64_t s = n * outPlane + outOff[j];
+            float ix = gs::ComputeSourceIndex(__ldg(grid + 2 * s), g.win, g.pad, g.align);
+            float iy = gs::ComputeSourceIndex(__ldg(grid + 2 * s + 1), g.hin, g.pad, g.align);
+            bad[j] = gs::IsNanOrInf(ix) || gs::IsNanOrInf(iy);
+            ix = gs::SafeDowngradeToIntRange(ix);
+            iy = gs::SafeDowngradeToIntRange(iy);
+            const float ixF = floorf(ix), iyF = floorf(iy);
+            const float xe = Sub(Add(ixF, 1.0f), ix), ye = Sub(Add(iyF, 1.0f), iy);
+            const float xw = Sub(ix, ixF), yw = Sub(iy, iyF);
+            wt[j][0] = Mul(xe, ye);
+            wt[j][1] = Mul(xw, ye);
+            wt[j][2] = Mul(xe, yw);
+            wt[j][3] = Mul(xw, yw);
+            // tap origins far outside the image are pulled to the two zero columns / rows beside it
+            cx[j] = min(max(static_cast<int32_t>(ixF), -kBorder), g.win);
+            cy[j] = min(max(static_cast<int32_t>(iyF), -kBorder), g.hin);
+            if (!bad[j]) {
+                mnx = min(mnx, cx[j]);
+                mxx = max(mxx, cx[j]);
+                mny = min(mny, cy[j]);
+                mxy = max(mxy, cy[j]);
+            }
+        }
+    }
+    mnx = __reduce_min_sync(0xffffffffu, mnx);
+    mxx = __reduce_max_sync(0xffffffffu, mxx);
+    mny = __reduce_min_sync(0xffffffffu, mny);
+    mxy = __reduce_max_sync(0xffffffffu, mxy);
+    if (lane == 0) {
+        atomicMin(&box[0], mnx);
+        atomicMax(&box[1], mxx);
+        atomicMin(&box[2], mny);
+        atomicMax(&box[3], mxy);
+    }
+    __syncthreads();
+    const bool any = box[1] >= box[0];
+    // columns [wx0, wx0 + pitch) in whole 16-byte pieces (floor to a multiple of four: -4 holds the zero columns
+    // -2, -1), rows [wy0, wy0 + wh)
+    const int32_t wx0 = any ? (box[0] + 4) / 4 * 4 - 4 : 0, wy0 = any ? box[2] : 0;
+    const int32_t needW = any ? (box[1] + 2 - wx0 + 3) / 4 * 4 : 4; // floats per row that are copied
+    const int32_t pitch = needW + ((8 - needW % 16) + 16) % 16;       // row pitch: 8 or 24 modulo 32
+    const int32_t wh = any ? box[3] - box[2] + 2 : 1;
+    const int32_t wsize = pitch * wh;
+    const float* xn = x + n * g.c * inPlane;
+    float* yn = y + n * g.c * outPlane;
+    const float nanv = __int_as_float(0x7fc00000);
+
+    if (wsize > capFloats) {
+        // not a smooth tile: taps from global memory, channel by channel
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (!live[j]) {
+                continue;
+            }
+            const int32_t x0 = cx[j], y0 = cy[j];
+            const bool bnw = gs::Within(y0, x0, g.hin, g.win), bne = gs::Within(y0, x0 + 1, g.hin, g.win);
+            const bool bsw = gs::Within(y0 + 1, x0, g.hin, g.win), bse = gs::Within(y0 + 1, x0 + 1, g.hin, g.win);
+            const int64_t o = static_cast<int64_t>(y0) * g.win + x0;
+            for (int64_t c = 0; c < g.c; ++c) {
+                const float* xc = xn + c * inPlane + o;
+                float out = 0.0f;
+                if (bnw) {
+                    out = Add(out, Mul(__ldg(xc), wt[j][0]));
+                }
+                if (bne) {
+                    out = Add(out, Mul(__ldg(xc + 1), wt[j][1]));
+                }
+                if (bsw) {
+                    out = Add(out, Mul(__ldg(xc + g.win), wt[j][2]));
+                }
+                if (bse) {
+                    out = Add(out, Mul(__ldg(xc + g.win + 1), wt[j][3]));
+                }
+                yn[c * outPlane + outOff[j]] = bad[j] ? nanv : out;
+            }
+        }
+        return;
+    }
+
+    // byte offset of the thread's NW taps inside a staged plane
+    uint32_t rec[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        rec[j] = (live[j] && !bad[j]) ? static_cast<uint32_t>((cy[j] - wy0) * pitch + (cx[j] - wx0)) * 4u : 0u;
+    }
+    // the two pixels' weights side by side: one packed multiply and one packed add per tap and channel
+    F2 w2[4];
+#pragma unroll
+    for (int tap = 0; tap < 4; ++tap) {
+        w2[tap] = MakeF2(live[0] ? wt[0][tap] : 0.0f, live[1] ? wt[1][tap] : 0.0f);
+    }
+    const F2 one2 = MakeF2(one, one);
+    const int32_t groups = static_cast<int32_t>((g.c + kWinChans - 1) / kWinChans);
+    // Copies. The box is the same for every channel, so a thread owns the same 16-byte pieces (row r, piece q) of the
+    // box in every group: at most kWinPieces of them, whose source offset inside a plane, destination offset inside
+    // a staged plane and in-image flag are evaluated once.
+    const int32_t pieces = needW / 4;
+    const int32_t total = wh * pieces;
+    int32_t srcOff[kWinPieces];
+    uint32_t dstOff[kWinPieces];
+    int srcBytes[kWinPieces];
+#pragma unroll
+    for (int i = 0; i < kWinPieces; ++i) {
+        const int32_t id = threadIdx.x + i * kWinThreads;
+        const int32_t r = id / pieces, q = id - r * pieces;
+        const int32_t sy = wy0 + r, sx = wx0 + 4 * q;
+        const bool in = id < total && sy >= 0 && sy < g.hin && sx >= 0 && sx < g.win;
+        srcBytes[i] = id < total ? (in ? 16 : 0) : -1; // -1: the thread has no such piece
+        srcOff[i] = min(max(sy, 0), g.hin - 1) * g.win + min(max(sx, 0), g.win - 4);
+        dstOff[i] = static_cast<uint32_t>(r * pitch + 4 * q) * 4u;
+    }
+    const uint32_t smemBase = static_cast<uint32_t>(__cvta_generic_to_shared(bufBase));
+    const uint32_t planeBytes = static_cast<uint32_t>(pitch * wh) * 4u, pitchBytes = static_cast<uint32_t>(pitch) * 4u;
+    auto stage = [&](int32_t grp, uint32_t dstBase) {
+        const int32_t c0 = grp * kWinChans;
+#pragma unroll
+        for (int k = 0; k < kWinChans; ++k) {
+            const bool chIn = c0 + k < g.c;
+            const float* plane = xn + static_cast<int64_t>(chIn ? c0 + k : 0) * inPlane;
+#pragma unroll
+            for (int i = 0; i < kWinPieces; ++i) {
+                if (srcBytes[i] >= 0) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dstBase + k * planeBytes + dstOff[i]),
+                                 "l"(plane + srcOff[i]), "r"(chIn ? srcBytes[i] : 0)
+                                 : "memory");
+                }
+            }
+        }
+        CpAsyncCommit();
+    };
+    const uint32_t bufBytes = static_cast<uint32_t>(kWinChans) * capFloats * 4u;
+    float* yp0 = yn + outOff[0];
+    float* yp1 = yn + outOff[1];
+    stage(0, smemBase);
+    for (int32_t grp = 0; grp < groups; ++grp) {
+        if (grp + 1 < groups) {
+            stage(grp + 1, smemBase + ((grp + 1) & 1) * bufBytes);
+            CpAsyncWait<1>();
+        } else {
+            CpAsyncWait<0>();
+        }
+        __syncthreads();
+        const unsigned char* ta = stagedSmem + (grp & 1) * bufBytes + rec[0];
+        const unsigned char* tb = stagedSmem + (grp & 1) * bufBytes + rec[1];
+        const int32_t c0 = grp * kWinChans;
+#pragma unroll
+        for (int k = 0; k < kWinChans; ++k) {
+            auto tapv = [&](const unsigned char* t, uint32_t off) { return *reinterpret_cast<const float*>(t + off); };
+            // acc = acc + v * w with two roundings, as the reference: a packed multiply, then a packed fma by 1.0. (A
+            // packed multiply followed by a packed add gets contracted into one fused multiply-add by the assembler,
+            // even with explicit rounding modifiers; a multiplier it cannot see through, the kernel argument `one`,
+            // keeps the two roundings.)
+            F2 o = Fma2(Mul2(MakeF2(tapv(ta, 0), tapv(tb, 0)), w2[0]), one2, MakeF2(0.0f, 0.0f)); // 0 + (-0) is +0
+            o = Fma2(Mul2(MakeF2(tapv(ta, 4), tapv(tb, 4)), w2[1]), one2, o);
+            o = Fma2(Mul2(MakeF2(tapv(ta, pitchBytes), tapv(tb, pitchBytes)), w2[2]), one2, o);
+            o = Fma2(Mul2(MakeF2(tapv(ta, pitchBytes + 4), tapv(tb, pitchBytes + 4)), w2[3]), one2, o);
+            float o0, o1;
+            SplitF2(o, o0, o1);
+            if (c0 + k < g.c) {
+                if (live[0]) {
+                    *yp0 = bad[0] ? nanv : o0;
+                }
+                if (live[1]) {
+                    *yp1 = bad[1] ? nanv : o1;
+                }
+            }
+            ta += planeBytes;
+            tb += planeBytes;
+            yp0 += outPlane;
+            yp1 += outPlane;
+        }
+        __syncthreads(); // the buffer is free for the copies of group grp + 2
+    }
+}
+
 inline size_t StagedFwdSmem(int64_t hin, int64_t win, int nv)
 {
     return static_cast<size_t>((hin + 2 * kBorder) * (win + 2 * kBorder)) * nv * 16;
@@ -322,6 +565,9 @@ GridFwdPlan PlanGridSampler2DFwd(Dt dt, GridShape g)
     // shared-memory wavefronts, not by the per-pixel coordinate work.)
     if (StagedFwdSmem(g.hin, g.win, 1) + 1024 <= 110 * 1024) {
         plan.vectors = 1;
+    } else if (dt == Dt::F32 && g.c >= 4 && g.win % 4 == 0 && g.win >= 4 &&
+               g.n * CeilDiv(g.hout, kWinTile) * CeilDiv(g.wout, kWinTile) < (1LL << 31)) {
+        plan.windowed = 1; // larger planes: per-tile windows of the planes (no workspace)
     }
     if (plan.vectors > 0) {
         plan.recBytes = static_cast<uint64_t>(g.n) * outPlane * sizeof(float2);
@@ -347,6 +593,21 @@ cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, Gr
             }
         });
         return e;
+    }
+    if (plan.windowed != 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) { // 16-byte copies need an aligned input
+        const int32_t tilesX = static_cast<int32_t>(CeilDiv(g.wout, kWinTile));
+        const int32_t tilesY = static_cast<int32_t>(CeilDiv(g.hout, kWinTile));
+        const size_t smem = static_cast<size_t>(kWinCapFloats) * 2 * kWinChans * sizeof(float);
+        cudaError_t e = cudaFuncSetAttribute(GridSamplerWindowKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) {
+            return e;
+        }
+        GridSamplerWindowKernel<<<static_cast<unsigned>(g.n * tilesX * tilesY), kWinThreads, smem, s>>>(
+            static_cast<const float*>(x), static_cast<const float*>(grid), static_cast<float*>(y), g, tilesX, tilesY,
+            kWinCapFloats, 1.0f);
+        CountLaunch();
+        return cudaGetLastError();
     }
     // Split channels across threads only as far as needed to fill the machine.
     const int64_t wanted = static_cast<int64_t>(NumSMs()) * 2048 * 2;

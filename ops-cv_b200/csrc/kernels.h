@@ -159,11 +159,13 @@ struct GridShape {
     int32_t hin, win, hout, wout;
     int32_t interp, pad, align;
 };
-// Forward plan: vectors > 0 selects the shared-memory staged kernel with that many 16-byte channel vectors per
+// Forward plan: windowed != 0 selects the tile-major kernel that stages, per output tile, the window of the input
+// planes the tile's taps fall into. vectors > 0 selects the shared-memory staged kernel with that many 16-byte channel vectors per
 // pixel; it needs recBytes of workspace for the per-sample source coordinates.
 struct GridFwdPlan {
     int32_t vectors;
     uint64_t recBytes;
+    int32_t windowed; // 1: the per-tile windowed kernel (fp32 planes too large for the staged kernel)
 };
 GridFwdPlan PlanGridSampler2DFwd(Dt dt, GridShape g);
 cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, GridShape g, const GridFwdPlan& plan,

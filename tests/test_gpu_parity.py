@@ -336,6 +336,47 @@ def test_grid_sampler_forward_special_values(ops, oracle, dev):
             assert np.array_equal(np.nan_to_num(y), np.nan_to_num(ref)), (interp, pad)
 
 
+def affine_grid(n, ho, wo, seed, max_deg=30.0, scale=(0.8, 1.2), shift=0.1):
+    g = gen(seed)
+    phi = (torch.rand(n, generator=g) * 2 - 1) * max_deg * np.pi / 180
+    s = torch.rand(n, generator=g) * (scale[1] - scale[0]) + scale[0]
+    t = (torch.rand((n, 2), generator=g) * 2 - 1) * shift
+    theta = torch.stack([torch.stack([s * torch.cos(phi), -s * torch.sin(phi), t[:, 0]], 1),
+                         torch.stack([s * torch.sin(phi), s * torch.cos(phi), t[:, 1]], 1)], 1)
+    return torch.nn.functional.affine_grid(theta, (n, 1, ho, wo), align_corners=False).contiguous()
+
+
+@pytest.mark.parametrize("pad", [0, 1, 2])
+@pytest.mark.parametrize("align", [False, True])
+@pytest.mark.parametrize("case", ["affine", "random", "mixed", "far"])
+def test_grid_sampler_forward_large_planes(ops, oracle, dev, pad, align, case):
+    """fp32 planes too large for the plane-major staged kernel take the tile-major kernel that stages, per 32 x 32
+    output tile, the window of the input its taps fall into. Smooth grids (affine) stay in shared memory; a random
+    grid makes every tile fall back to global-memory taps; "mixed" has both kinds of tile plus NaN / Inf samples; "far"
+    puts a whole tile outside the image. C = 6 leaves a partial last channel group; the output is not a multiple of
+    the tile. Same operation order as the oracle: identical bits."""
+    n, c, hi, wi, ho, wo = 2, 6, 100, 92, 110, 85
+    x = torch.randn((n, c, hi, wi), generator=gen(50))
+    if case == "affine":
+        grid = affine_grid(n, ho, wo, 51)
+    elif case == "random":
+        grid = make_grid(n, ho, wo, 52, 1.2)
+    elif case == "mixed":
+        grid = affine_grid(n, ho, wo, 53, 45.0, (0.5, 1.5), 0.3)
+        grid[1, 40:70, :20] = make_grid(1, 30, 20, 54, 1.3)[0]
+        grid[0, 3, 4, 0] = float("nan")
+        grid[0, 50, 40, 1] = float("inf")
+        grid[1, 109, 84] = torch.tensor([-float("inf"), 0.2])
+    else:
+        grid = affine_grid(n, ho, wo, 55, 10.0, (0.9, 1.1), 0.05)
+        grid[0, :32, :32] += 5.0   # a tile whose taps all miss the image
+        grid[1, 32:64, :32, 0] = 1e30
+    y = ops.grid_sampler2d(x.to(dev), grid.to(dev), 0, pad, align).cpu().numpy()
+    ref = oracle.grid_sampler2d_fwd(x.numpy(), grid.numpy(), 0, pad, align)
+    assert np.array_equal(np.isnan(y), np.isnan(ref))
+    assert np.array_equal(np.nan_to_num(y).view(np.int32), np.nan_to_num(ref).view(np.int32))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("interp", [0, 1])
 @pytest.mark.parametrize("pad", [0, 1, 2])
