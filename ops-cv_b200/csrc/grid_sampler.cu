@@ -300,7 +300,7 @@ __device__ __forceinline__ void CpAsync16Zfill(void* smem, const void* gmem, boo
 
 __global__ void __launch_bounds__(kWinThreads, 2)
     GridSamplerWindowKernel(const float* __restrict__ x, const float* __restrict__ grid, float* __restrict__ y,
-                            GridShape g, int32_t tilesX, int32_t tilesY, int32_t capFloats, float one)
+                            GridShape g, int32_t tilesX, int32_t tilesY, int32_t capFloats)
 {
     extern __shared__ __align__(16) unsigned char stagedSmem[];
     __shared__ int32_t box[4]; // min x, max x, min y, max y of the clamped tap origins
@@ -428,7 +428,6 @@ __global__ void __launch_bounds__(kWinThreads, 2)
     for (int tap = 0; tap < 4; ++tap) {
         w2[tap] = MakeF2(live[0] ? wt[0][tap] : 0.0f, live[1] ? wt[1][tap] : 0.0f);
     }
-    const F2 one2 = MakeF2(one, one);
     const int32_t groups = static_cast<int32_t>((g.c + kWinChans - 1) / kWinChans);
     // Copies. The box is the same for every channel, so a thread owns the same 16-byte pieces (row r, piece q) of the
     // box in every group: at most kWinPieces of them, whose source offset inside a plane, destination offset inside
@@ -485,14 +484,11 @@ __global__ void __launch_bounds__(kWinThreads, 2)
 #pragma unroll
         for (int k = 0; k < kWinChans; ++k) {
             auto tapv = [&](const unsigned char* t, uint32_t off) { return *reinterpret_cast<const float*>(t + off); };
-            // acc = acc + v * w with two roundings, as the reference: a packed multiply, then a packed fma by 1.0. (A
-            // packed multiply followed by a packed add gets contracted into one fused multiply-add by the assembler,
-            // even with explicit rounding modifiers; a multiplier it cannot see through, the kernel argument `one`,
-            // keeps the two roundings.)
-            F2 o = Fma2(Mul2(MakeF2(tapv(ta, 0), tapv(tb, 0)), w2[0]), one2, MakeF2(0.0f, 0.0f)); // 0 + (-0) is +0
-            o = Fma2(Mul2(MakeF2(tapv(ta, 4), tapv(tb, 4)), w2[1]), one2, o);
-            o = Fma2(Mul2(MakeF2(tapv(ta, pitchBytes), tapv(tb, pitchBytes)), w2[2]), one2, o);
-            o = Fma2(Mul2(MakeF2(tapv(ta, pitchBytes + 4), tapv(tb, pitchBytes + 4)), w2[3]), one2, o);
+            // acc = acc + v * w with two roundings, as the reference (see AddProduct2)
+            F2 o = AddProduct2(Mul2(MakeF2(tapv(ta, 0), tapv(tb, 0)), w2[0]), MakeF2(0.0f, 0.0f)); // 0 + (-0) is +0
+            o = AddProduct2(Mul2(MakeF2(tapv(ta, 4), tapv(tb, 4)), w2[1]), o);
+            o = AddProduct2(Mul2(MakeF2(tapv(ta, pitchBytes), tapv(tb, pitchBytes)), w2[2]), o);
+            o = AddProduct2(Mul2(MakeF2(tapv(ta, pitchBytes + 4), tapv(tb, pitchBytes + 4)), w2[3]), o);
             float o0, o1;
             SplitF2(o, o0, o1);
             if (c0 + k < g.c) {
@@ -605,7 +601,7 @@ cudaError_t GridSampler2DFwd(Dt dt, const void* x, const void* grid, void* y, Gr
         }
         GridSamplerWindowKernel<<<static_cast<unsigned>(g.n * tilesX * tilesY), kWinThreads, smem, s>>>(
             static_cast<const float*>(x), static_cast<const float*>(grid), static_cast<float*>(y), g, tilesX, tilesY,
-            kWinCapFloats, 1.0f);
+            kWinCapFloats);
         CountLaunch();
         return cudaGetLastError();
     }

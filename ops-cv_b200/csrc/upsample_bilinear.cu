@@ -120,6 +120,13 @@ __device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const 
                                            bool wide = false)
 {
     const float dy1 = Sub(1.0f, dy);
+    // out = dy1 * top + dy * bot with the reference's three roundings, two values per instruction: packed multiplies
+    // and an exact packed add of the products (AddProduct2), which halves the issue slots of the blend.
+    const F2 wTop = MakeF2(dy1, dy1), wBot = MakeF2(dy, dy);
+    auto blend = [&](int k, float& a, float& b) { // outputs k and k + 1
+        const F2 r = AddProduct2(Mul2(wBot, MakeF2(bot[k], bot[k + 1])), Mul2(wTop, MakeF2(top[k], top[k + 1])));
+        SplitF2(r, a, b);
+    };
     if constexpr (V * sizeof(T) == 32) {
         if (wide) { // dst is 32-byte aligned: one full-sector store per lane
             Pack<T, V / 2> half[2];
@@ -127,8 +134,8 @@ __device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const 
             for (int q = 0; q < 2; ++q) {
                 float out[V / 2];
 #pragma unroll
-                for (int k = 0; k < V / 2; ++k) {
-                    out[k] = Add(Mul(dy1, top[q * (V / 2) + k]), Mul(dy, bot[q * (V / 2) + k]));
+                for (int k = 0; k < V / 2; k += 2) {
+                    blend(q * (V / 2) + k, out[k], out[k + 1]);
                 }
                 StorePack<T, V / 2>(half[q].v, out);
             }
@@ -140,9 +147,16 @@ __device__ __forceinline__ void BlendStore(T* dst, const float (&top)[V], const 
 #pragma unroll
     for (int q = 0; q < V / kPer; ++q) {
         float out[kPer];
+        if constexpr (kPer % 2 == 0) {
 #pragma unroll
-        for (int k = 0; k < kPer; ++k) {
-            out[k] = Add(Mul(dy1, top[q * kPer + k]), Mul(dy, bot[q * kPer + k]));
+            for (int k = 0; k < kPer; k += 2) {
+                blend(q * kPer + k, out[k], out[k + 1]);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) {
+                out[k] = Add(Mul(dy1, top[q * kPer + k]), Mul(dy, bot[q * kPer + k]));
+            }
         }
         StorePack<T, kPer>(dst + q * kPer, out);
     }
