@@ -200,4 +200,82 @@ __device__ __forceinline__ float SourceIndexSetGrad(float coord, int32_t size, i
 }
 
 } // namespace gs
+
+// ---- staging of channel-interleaved pixel records ------------------------------------------------------------------
+// The plane-major grid-sampler kernels keep, per pixel, one 16-byte record holding LV = 16 / sizeof(T) channels.
+// This copies LV planes of `rows` x `cols` elements (plane k at src + k * planeStride, rows `rowStride` elements
+// apart) into records dst[(r * dstPitch + c)] (r, c relative to the caller's origin), channels past nch zero.
+// Fast path (cols a multiple of LV, 16-byte aligned rows): a work item is LV consecutive pixels of one row; the
+// thread reads them with one 16-byte load per channel, transposes the LV x LV block in registers and writes LV
+// 16-byte records, instead of one scalar load per pixel and channel (for 16-bit types that was eight 2-byte loads
+// per record and more instructions than the sampling itself when a plane is staged by several blocks).
+template <typename T>
+__device__ __forceinline__ void StageRecords(Pack<T, 16 / sizeof(T)>* dst, int32_t dstPitch, const T* __restrict__ src,
+                                             int64_t planeStride, int32_t rowStride, int32_t nch, int32_t rows,
+                                             int32_t cols, int32_t tid, int32_t nthreads)
+{
+    constexpr int LV = 16 / sizeof(T);
+    using Vec = Pack<T, LV>;
+    const bool fast = cols % LV == 0 && rowStride % LV == 0 && planeStride % LV == 0 &&
+                      (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+    if (fast) {
+        const int32_t perRow = cols / LV;
+        for (int32_t i = tid; i < rows * perRow; i += nthreads) {
+            const int32_t r = i / perRow, q = i - r * perRow;
+            const T* p = src + static_cast<int64_t>(r) * rowStride + q * LV;
+            uint4* out = reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * dstPitch + q * LV);
+            if constexpr (LV == 4) { // 4 x 4 words: pixel j takes word j of every channel
+                uint4 in[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    in[k] = k < nch ? __ldg(reinterpret_cast<const uint4*>(p + k * planeStride)) : make_uint4(0, 0, 0, 0);
+                }
+                const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&in[0]);
+                const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&in[1]);
+                const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&in[2]);
+                const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&in[3]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    out[j] = make_uint4(w0[j], w1[j], w2[j], w3[j]);
+                }
+            } else {
+                // 8 x 8 halves in two passes of four channels (sixteen registers of input at a time): pixel j takes
+                // half j of every channel, two channels per output word, so a pass writes half a record per pixel
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint4 in[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        in[k] = 4 * h + k < nch ? __ldg(reinterpret_cast<const uint4*>(p + (4 * h + k) * planeStride))
+                                                : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t o[2];
+#pragma unroll
+                        for (int c2 = 0; c2 < 2; ++c2) {
+                            const uint32_t a = reinterpret_cast<const uint32_t*>(&in[2 * c2])[j >> 1];
+                            const uint32_t b = reinterpret_cast<const uint32_t*>(&in[2 * c2 + 1])[j >> 1];
+                            // low half of the word from channel 2*c2, high half from channel 2*c2 + 1 (of this pass)
+                            o[c2] = (j & 1) ? __byte_perm(a, b, 0x7632) : __byte_perm(a, b, 0x5410);
+                        }
+                        reinterpret_cast<uint2*>(out + j)[h] = make_uint2(o[0], o[1]);
+                    }
+                }
+            }
+        }
+        return;
+    }
+    for (int32_t i = tid; i < rows * cols; i += nthreads) {
+        const int32_t r = i / cols, c = i - r * cols;
+        const T* p = src + static_cast<int64_t>(r) * rowStride + c;
+        Vec v;
+#pragma unroll
+        for (int k = 0; k < LV; ++k) {
+            v.v[k] = k < nch ? __ldg(p + k * planeStride) : DType<T>::FromF(0.0f);
+        }
+        dst[static_cast<int64_t>(r) * dstPitch + c] = v;
+    }
+}
+
 } // namespace opscv

@@ -187,7 +187,7 @@ constexpr int kStageThreads = 512;
 constexpr int kBorder = 2;
 
 template <typename T, int NV>
-__global__ void __launch_bounds__(kStageThreads)
+__global__ void __launch_bounds__(kStageThreads, NV == 1 ? 3 : 1)
     GridSamplerStagedKernel(const T* __restrict__ x, const float2* __restrict__ rec, T* __restrict__ y, GridShape g,
                             int32_t groups, int32_t split, int32_t per)
 {
@@ -204,6 +204,19 @@ __global__ void __launch_bounds__(kStageThreads)
     const int32_t c0 = static_cast<int32_t>(ng - n * groups) * CG;
     const int32_t nch = min(CG, static_cast<int32_t>(g.c) - c0);
     const T* xb = x + (n * g.c + c0) * inPlane;
+    if constexpr (NV == 1) {
+        // the zero border (two rows above and below, two columns left and right), then the planes as pixel records
+        const Vec zero{};
+        for (int32_t i = threadIdx.x; i < 2 * kBorder * tw; i += blockDim.x) {
+            const int32_t r = i / tw;
+            tile[(r < kBorder ? r : g.hin + r) * tw + (i - r * tw)] = zero;
+        }
+        for (int32_t i = threadIdx.x; i < g.hin * 2 * kBorder; i += blockDim.x) {
+            const int32_t r = i / (2 * kBorder), c = i - r * (2 * kBorder);
+            tile[(r + kBorder) * tw + (c < kBorder ? c : g.win + c)] = zero;
+        }
+        StageRecords<T>(tile + kBorder * tw + kBorder, tw, xb, inPlane, g.win, nch, g.hin, g.win, threadIdx.x, blockDim.x);
+    } else {
     const int32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     for (int32_t ty = warp; ty < th; ty += warps) {
         const int32_t sy = ty - kBorder;
@@ -223,6 +236,7 @@ __global__ void __launch_bounds__(kStageThreads)
                 tile[(ty * tw + tx) * NV + v] = q;
             }
         }
+    }
     }
     __syncthreads();
     const int32_t p1 = min(outPlane, (part + 1) * per);
