@@ -135,9 +135,11 @@ ACLNN_API aclnnStatus aclnnGridSampler2D(void* workspace, uint64_t workspaceSize
 /* Replaces image/grid_sampler2_d_grad/op_host/op_api/aclnn_grid_sampler2d_backward.h:58-91 (implementation
  * aclnn_grid_sampler2d_backward.cpp:214-357; arithmetic image/grid_sampler3_d_grad/op_kernel/arch35/
  * grid_sampler3_d_grad_simt_base.h:51-184 and image/grid_sampler2_d_grad/op_kernel/arch35/
- * grid_sampler2_d_grad_simt.h:64-144,235-290). outputMask = {want inputGrad, want gridGrad}; a NULL mask or
- * {false,false} is a successful no-op. Atomic accumulation by default; bit-reproducible when
- * ACL_OPT_DETERMINISTIC is set. Bilinear and nearest interpolation; bicubic returns ACLNN_ERR_PARAM_INVALID. */
+ * grid_sampler2_d_grad_simt.h:64-230,235-290). outputMask = {want inputGrad, want gridGrad}; a NULL mask or
+ * {false,false} is a successful no-op. Atomic accumulation by default; bit-reproducible, in the summation order of
+ * the reference's deterministic kernel (grid_sampler2_d_grad_simt_det.h), when ACL_OPT_DETERMINISTIC is set.
+ * interpolationMode 0 bilinear, 1 nearest, 2 bicubic (A = -0.75, every neighbour of the 4 x 4 window through the
+ * padding mode). */
 ACLNN_API aclnnStatus aclnnGridSampler2DBackwardGetWorkspaceSize(const aclTensor* gradOutput, const aclTensor* input,
                                                                  const aclTensor* grid, int64_t interpolationMode,
                                                                  int64_t paddingMode, bool alignCorners,

@@ -192,11 +192,8 @@ aclnnStatus aclnnGridSampler2DBackwardGetWorkspaceSize(const aclTensor* gradOutp
     if (!wantInput && !wantGrid) { // :242-248
         return EmptySuccess(api, workspaceSize, executor);
     }
-    if (interpolationMode == 2) {
-        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: bicubic interpolation is not implemented for the backward", api);
-    }
     if (!FitsInt32Dims(input) || !FitsInt32Dims(grid) || input->dims[2] * input->dims[3] >= INT32_MAX ||
-        grid->dims[1] * grid->dims[2] >= INT32_MAX / 4) {
+        grid->dims[1] * grid->dims[2] >= INT32_MAX / 16) {
         return Fail(ACLNN_ERR_PARAM_INVALID, "%s: extents exceed the supported range", api);
     }
     aclOpExecutor* ex = NewExecutor(api);

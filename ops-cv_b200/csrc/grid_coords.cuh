@@ -199,6 +199,59 @@ __device__ __forceinline__ float SourceIndexSetGrad(float coord, int32_t size, i
     return coord;
 }
 
+// ---- bicubic backward: image/grid_sampler3_d_grad/op_kernel/arch35/grid_sampler3_d_grad_simt_base.h:186-311 -------
+// Derivatives of the four cubic coefficients with respect to t (A = -0.75), separate roundings.
+__device__ __forceinline__ float Cubic2Slope(float x) // (3A x - 10A) x + 8A
+{
+    return Add(Mul(Sub(Mul(-2.25f, x), -7.5f), x), -6.0f);
+}
+__device__ __forceinline__ float Cubic1Slope(float x) // (3(A+2) x - 2(A+3)) x
+{
+    return Mul(Sub(Mul(3.75f, x), 4.5f), x);
+}
+__device__ __forceinline__ void CubicCoefficients(float (&c)[4], float t)
+{
+    c[0] = Cubic2(Add(t, 1.0f));
+    c[1] = Cubic1(t);
+    c[2] = Cubic1(Sub(1.0f, t));
+    c[3] = Cubic2(Sub(2.0f, t));
+}
+__device__ __forceinline__ void CubicCoefficientsGrad(float (&c)[4], float t)
+{
+    c[0] = Cubic2Slope(Add(t, 1.0f));
+    c[1] = Cubic1Slope(t);
+    c[2] = -Cubic1Slope(Sub(1.0f, t));
+    c[3] = -Cubic2Slope(Sub(2.0f, t));
+}
+// Pixel index that a neighbour coordinate maps to under the padding mode, or -1 (GetValueBounded / AddValueBounded:
+// zeros tests the float coordinate, border clamps it, reflection reflects and clips; a coordinate that is not finite
+// ends as -100 and is out of range).
+__device__ __forceinline__ int32_t BoundedIndex(float x, float y, int32_t w, int32_t h, int32_t pad, int32_t align)
+{
+    if (pad == 0) {
+        if (x < 0.0f || x >= static_cast<float>(w) || y < 0.0f || y >= static_cast<float>(h)) {
+            return -1;
+        }
+    } else if (pad == 1) {
+        x = x < 0.0f ? 0.0f : (x >= static_cast<float>(w) ? static_cast<float>(w) - 1.0f : x);
+        y = y < 0.0f ? 0.0f : (y >= static_cast<float>(h) ? static_cast<float>(h) - 1.0f : y);
+    } else {
+        float gr, gc;
+        if (align != 0) {
+            x = ReflectSetGrad(x, 0, 2 * (w - 1), &gr);
+            y = ReflectSetGrad(y, 0, 2 * (h - 1), &gr);
+        } else {
+            x = ReflectSetGrad(x, -1, 2 * w - 1, &gr);
+            y = ReflectSetGrad(y, -1, 2 * h - 1, &gr);
+        }
+        x = ClipSetGrad(x, w, &gc);
+        y = ClipSetGrad(y, h, &gc);
+    }
+    const int32_t ix = static_cast<int32_t>(isfinite(x) ? x : -100.0f);
+    const int32_t iy = static_cast<int32_t>(isfinite(y) ? y : -100.0f);
+    return (ix >= 0 && ix < w && iy >= 0 && iy < h) ? iy * w + ix : -1;
+}
+
 } // namespace gs
 
 // ---- staging of channel-interleaved pixel records ------------------------------------------------------------------

@@ -68,6 +68,38 @@ __device__ __forceinline__ GradTaps MakeGradTaps(float gx, float gy, const GridS
     return t;
 }
 
+// Bicubic (interp == 2): only un-normalised coordinates (the 4 x 4 neighbourhood keeps negative positions and every
+// neighbour goes through the padding mode on its own), taps visited x-outer, y-inner: tap = 4 * i + j is the
+// neighbour (floor(ix) - 1 + i, floor(iy) - 1 + j) with weight cx[i] * cy[j]
+// (image/grid_sampler2_d_grad/op_kernel/arch35/grid_sampler2_d_grad_simt.h:171-230).
+struct CubicTaps {
+    float ixF, iyF, mx, my;
+    float cx[4], cy[4];
+};
+__device__ __forceinline__ CubicTaps MakeCubicTaps(float gx, float gy, const GridShape& g)
+{
+    CubicTaps t;
+    const float ix = gs::UnnormalizeSetGrad(gx, g.win, g.align, &t.mx);
+    const float iy = gs::UnnormalizeSetGrad(gy, g.hin, g.align, &t.my);
+    t.ixF = floorf(ix);
+    t.iyF = floorf(iy);
+    gs::CubicCoefficients(t.cx, Sub(ix, t.ixF));
+    gs::CubicCoefficients(t.cy, Sub(iy, t.iyF));
+    return t;
+}
+__device__ __forceinline__ int32_t CubicDest(const CubicTaps& t, int tap, const GridShape& g)
+{
+    return gs::BoundedIndex(Add(Sub(t.ixF, 1.0f), static_cast<float>(tap >> 2)),
+                            Add(Sub(t.iyF, 1.0f), static_cast<float>(tap & 3)), g.win, g.hin, g.pad, g.align);
+}
+__device__ __forceinline__ float CubicWeight(const CubicTaps& t, int tap)
+{
+    const int i = tap >> 2, j = tap & 3; // selected without dynamic indexing of the register arrays
+    const float x = i == 0 ? t.cx[0] : (i == 1 ? t.cx[1] : (i == 2 ? t.cx[2] : t.cx[3]));
+    const float y = j == 0 ? t.cy[0] : (j == 1 ? t.cy[1] : (j == 2 ? t.cy[2] : t.cy[3]));
+    return Mul(x, y);
+}
+
 // Source coordinates of every sample, evaluated once instead of once per channel group (staged kernel).
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -154,6 +186,37 @@ __global__ void __launch_bounds__(kThreads)
                 ggrid[2 * s] = DType<T>::FromF(Mul(t.mx, gix));
                 ggrid[2 * s + 1] = DType<T>::FromF(Mul(t.my, giy));
             }
+        } else if (g.interp == 2) {
+            const float gxv = DType<T>::Load(grid + 2 * s), gyv = DType<T>::Load(grid + 2 * s + 1);
+            const CubicTaps ct = MakeCubicTaps(gxv, gyv, g);
+            float mxu, myu, gcx[4], gcy[4];
+            const float ixu = gs::UnnormalizeSetGrad(gxv, g.win, g.align, &mxu);
+            const float iyu = gs::UnnormalizeSetGrad(gyv, g.hin, g.align, &myu);
+            gs::CubicCoefficientsGrad(gcx, Sub(ixu, ct.ixF));
+            gs::CubicCoefficientsGrad(gcy, Sub(iyu, ct.iyF));
+            float gix = 0.0f, giy = 0.0f;
+            for (int64_t c = 0; c < g.c; ++c) {
+                const float gv = DType<T>::Load(gob + c * outPlane);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int32_t o = CubicDest(ct, 4 * i + j, g);
+                        if (ATOMIC_GI && o >= 0) { // grad_output * cx * cy, in this order (:216-217)
+                            atomicAdd(ab + c * inPlane + o, Mul(Mul(gv, ct.cx[i]), ct.cy[j]));
+                        }
+                        if (WANT_GRID) {
+                            const float v = o >= 0 ? DType<T>::Load(xb + c * inPlane + o) : 0.0f;
+                            gix = Add(gix, Mul(Mul(Mul(v, gcx[i]), ct.cy[j]), gv));
+                            giy = Add(giy, Mul(Mul(Mul(v, gcy[j]), ct.cx[i]), gv));
+                        }
+                    }
+                }
+            }
+            if (WANT_GRID) {
+                ggrid[2 * s] = DType<T>::FromF(Mul(ct.mx, gix));
+                ggrid[2 * s + 1] = DType<T>::FromF(Mul(ct.my, giy));
+            }
         } else {
             if (ATOMIC_GI && gs::Within(t.y0, t.x0, g.hin, g.win)) {
                 const int64_t o = static_cast<int64_t>(t.y0) * g.win + t.x0;
@@ -232,8 +295,19 @@ __global__ void __launch_bounds__(kThreads)
     for (int64_t s = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; s < total; s += stride) {
         const int64_t n = s / outPlane;
         const int64_t c = (s - n * outPlane) / chunkSamples;
-        const GradTaps t = MakeGradTaps(DType<T>::Load(grid + 2 * s), DType<T>::Load(grid + 2 * s + 1), g);
         int32_t* cnt = counts + (n * chunks + c) * inPlane;
+        if (g.interp == 2) {
+            const CubicTaps ct = MakeCubicTaps(DType<T>::Load(grid + 2 * s), DType<T>::Load(grid + 2 * s + 1), g);
+#pragma unroll
+            for (int tap = 0; tap < 16; ++tap) {
+                const int32_t d = CubicDest(ct, tap, g);
+                if (d >= 0) {
+                    atomicAdd(cnt + d, 1);
+                }
+            }
+            continue;
+        }
+        const GradTaps t = MakeGradTaps(DType<T>::Load(grid + 2 * s), DType<T>::Load(grid + 2 * s + 1), g);
 #pragma unroll
         for (int tap = 0; tap < 4; ++tap) {
             const int32_t d = TapDest(t, tap, g);
@@ -363,18 +437,30 @@ __global__ void __launch_bounds__(kDetStep)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const unsigned lower = (1u << lane) - 1u;
     const int64_t p0 = static_cast<int64_t>(c) * chunkSamples, p1 = min(outPlane, p0 + chunkSamples);
-    const int numTaps = g.interp == 0 ? 4 : 1;
+    const int numTaps = g.interp == 0 ? 4 : (g.interp == 2 ? 16 : 1);
     for (int64_t base = p0; base < p1; base += kDetStep) {
         const int64_t p = base + threadIdx.x;
         GradTaps t{};
+        CubicTaps ct{};
         t.x0 = INT32_MIN / 2; // far out of bounds: a thread past the end has no tap in range
         t.y0 = INT32_MIN / 2;
         if (p < p1) {
-            t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
+            if (g.interp == 2) {
+                ct = MakeCubicTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
+            } else {
+                t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
+            }
         }
         for (int tap = 0; tap < numTaps; ++tap) {
-            const int32_t d = TapDest(t, tap, g);
-            const float wgt = tap == 0 ? t.tnw : (tap == 1 ? t.tne : (tap == 2 ? t.tsw : t.tse));
+            int32_t d;
+            float wgt;
+            if (g.interp == 2) {
+                d = p < p1 ? CubicDest(ct, tap, g) : -1;
+                wgt = CubicWeight(ct, tap); // the deterministic kernel multiplies grad_output by cx * cy (:312-314)
+            } else {
+                d = TapDest(t, tap, g);
+                wgt = tap == 0 ? t.tnw : (tap == 1 ? t.tne : (tap == 2 ? t.tsw : t.tse));
+            }
             for (int turn = 0; turn < kDetStep / 32; ++turn) {
                 if (warp == turn) {
                     // lanes without a tap get a key no other lane has: they match only themselves
@@ -761,7 +847,7 @@ GridGradPlan PlanGridSampler2DBwd(Dt dt, GridShape g, bool deterministic, bool w
             // positions [N][chunks][inPlane] and segment starts [N][inPlane+1], then entries [N][4*outPlane]
             p.countBytes = Align256(static_cast<uint64_t>(g.n) * chunks * inPlane * 4) +
                            Align256(static_cast<uint64_t>(g.n) * (inPlane + 1) * 4);
-            p.entryBytes = Align256(static_cast<uint64_t>(g.n) * 4 * outPlane * sizeof(Entry));
+            p.entryBytes = Align256(static_cast<uint64_t>(g.n) * (g.interp == 2 ? 16 : 4) * outPlane * sizeof(Entry));
         } else if (dt != Dt::F32) {
             p.accBytes = Align256(static_cast<uint64_t>(g.n) * g.c * inPlane * 4);
         }
@@ -872,7 +958,7 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
     int32_t* positions = reinterpret_cast<int32_t*>(ws);
     int32_t* segStart = reinterpret_cast<int32_t*>(ws + posBytes);
     Entry* entries = reinterpret_cast<Entry*>(ws + plan.countBytes);
-    const int64_t entriesPerImage = 4 * outPlane;
+    const int64_t entriesPerImage = (g.interp == 2 ? 16 : 4) * outPlane;
     e = cudaMemsetAsync(positions, 0, static_cast<size_t>(g.n) * plan.detChunks * inPlane * 4, s);
     if (e != cudaSuccess) {
         return e;

@@ -209,6 +209,9 @@ def test_grid_sampler_backward_status(ops):
     assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, mask_=BA(ops, [False, False]).ptr) == (OK, 0)
     assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, mask_=BA(ops, [True]).ptr)[0] == INVALID
     assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, interp=3)[0] == INVALID
+    # all three interpolation modes are accepted, bicubic included (aclnn_grid_sampler2d_backward.cpp:40-41,92-99)
+    for mode in (0, 1, 2):
+        assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, interp=mode)[0] == OK
     assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, gg.ptr, pad=-1)[0] == INVALID
     assert call(go.ptr, x.ptr, grid.ptr, T(ops, (1, 1, 5, 7)).ptr, gg.ptr)[0] == INVALID
     assert call(go.ptr, x.ptr, grid.ptr, gi.ptr, T(ops, (1, 3, 4, 2), fmt="ND").ptr)[0] == INVALID

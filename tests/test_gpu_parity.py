@@ -378,7 +378,7 @@ def test_grid_sampler_forward_large_planes(ops, oracle, dev, pad, align, case):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("interp", [0, 1])
+@pytest.mark.parametrize("interp", [0, 1, 2])
 @pytest.mark.parametrize("pad", [0, 1, 2])
 @pytest.mark.parametrize("align", [False, True])
 @pytest.mark.parametrize("det", [False, True])
@@ -400,6 +400,8 @@ def test_grid_sampler_backward(ops, oracle, dev, dtype, interp, pad, align, det)
     ri, rg = oracle.grid_sampler2d_bwd(g32, x32, grid32, interp, pad, align)
     check(gi, ri, dtype)
     check(gg, rg, dtype, exact=True)  # per-sample channel sum in channel order, as the oracle
+    if det:  # the reproducible mode replays the reference's deterministic order: the same bits as a serial replay
+        check(gi, oracle.grid_sampler2d_bwd_det_order(g32, x32.shape, grid32, interp, pad, align), dtype, exact=True)
 
 
 
@@ -460,7 +462,7 @@ def test_grid_sampler_staged_kernels(ops, oracle, dev, dtype, pad, align, c):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("interp", [0, 1])
+@pytest.mark.parametrize("interp", [0, 1, 2])
 @pytest.mark.parametrize("shape", [(2, 5, 9, 11, 12, 23), (3, 4, 16, 16, 40, 37), (8, 80, 9, 11, 30, 29)])
 def test_grid_sampler_backward_deterministic_order(ops, oracle, dev, dtype, interp, shape):
     """The reproducible mode adds the contributions of a destination in the order of the reference's deterministic
