@@ -15,6 +15,15 @@ Sources of the golden outputs (the reference stores no golden vectors; its tests
     {0..39} (1,1,5,8) with a 3x3 grid on {-1,0,1}, image/grid_sampler2_d_grad/examples/
     test_aclnn_grid_sampler2_d_backward.cpp:107-109), with outputs computed by the same torch calls.
 Inputs are seeded (the reference's generators are not).
+
+A second file, tests/golden/atk_replay.npz, replays the reference's own test inputs:
+  * a seeded slice of every ST case matrix of the hot-path APIs (image/*/tests/st/aclnn*/atk_aclnn*.json: ~200
+    cases per API with shapes, dtypes, attributes and value distributions), with the torch CPU call of the matching
+    executor_aclnn*.py (16-bit inputs up-cast to fp32, computed in fp32; backward cases with grad_output = ones as
+    the executors do, and with a seeded random grad_output beside it). N and C are cut to at most 2 and 3 (they do
+    not enter the arithmetic) and cases whose planes are too large for a small fixture are skipped;
+  * the reference's kernel-UT generator for UpsampleBilinear2d, imported and run
+    (image/upsample_bilinear2d/tests/ut/op_kernel/upsample_bilinear2d_data/gen_data.py, numpy seeded from outside).
 """
 import importlib.util
 import os
@@ -137,5 +146,179 @@ def main():
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(data), "arrays")
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# replay of the reference's ST case matrices and kernel-UT generators
+# ---------------------------------------------------------------------------------------------------------------
+ATK = {
+    # api: (json path, kind)
+    "UpsampleNearest2d": ("image/resize_nearest_neighbor_v2/tests/st/aclnnUpsampleNearest2d/atk_aclnnUpsampleNearest2d.json", "interp_fwd"),
+    "UpsampleNearest2dBackward": ("image/upsample_nearest2d_grad/tests/st/aclnnUpsampleNearest2dBackward/atk_aclnnUpsampleNearest2dBackward.json", "interp_bwd"),
+    "UpsampleBilinear2d": ("image/upsample_bilinear2d/tests/st/aclnnUpsampleBilinear2d/atk_aclnnUpsampleBilinear2d.json", "interp_fwd"),
+    "UpsampleBilinear2dBackward": ("image/resize_bilinear_v2_grad/tests/st/aclnnUpsampleBilinear2dBackward/atk_aclnnUpsampleBilinear2dBackward.json", "interp_bwd"),
+    "UpsampleBilinear2dBackwardV2": ("image/upsample_bilinear2d_grad/tests/st/aclnnUpsampleBilinear2dBackwardV2/atk_aclnnUpsampleBilinear2dBackwardV2.json", "interp_bwd"),
+    "UpsampleBicubic2dAA": ("image/upsample_bicubic2d_aa/tests/st/aclnnUpsampleBicubic2dAA/atk_aclnnUpsampleBicubic2dAA.json", "interp_fwd"),
+    "UpsampleBicubic2dAAGrad": ("image/upsample_bicubic2d_aa_grad/tests/st/aclnnUpsampleBicubic2dAAGrad/atk_aclnnUpsampleBicubic2dAAGrad.json", "interp_bwd"),
+    "GridSampler2D": ("image/grid_sample/tests/st/aclnnGridSampler2D/atk_aclnnGridSampler2D.json", "grid_fwd"),
+    "GridSampler2DBackward": ("image/grid_sampler2_d_grad/tests/st/aclnnGridSampler2DBackward/atk_aclnnGridSampler2DBackward.json", "grid_bwd"),
+}
+TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+CASES_PER_API = 20
+MAX_PLANE = 1000   # H * W of any tensor of a kept case
+
+
+def case_fields(case):
+    """Flattens the `inputs` list of an ATK case into {name: value}: tensors -> (dtype, shape, range), int arrays ->
+    list, scalar attributes -> value."""
+    out = {}
+    for inp in case["inputs"]:
+        if isinstance(inp, list):
+            if inp:
+                out[inp[0]["name"]] = [i.get("range_values") for i in inp]
+        elif inp.get("type") == "tensor":
+            out[inp["name"]] = ("tensor", inp["dtype"], inp["shape"], inp["range_values"])
+        else:
+            out[inp["name"]] = inp.get("range_values")
+    return out
+
+
+def draw(rng, shape, spec, dtype):
+    """A seeded tensor with the case's value distribution, rounded to the case's dtype and returned as fp32."""
+    if isinstance(spec, dict):  # {"name": "nd", "mean": [lo, hi], "std": [lo, hi]}
+        mean, std = rng.uniform(*spec["mean"]), rng.uniform(*spec["std"])
+        a = rng.normal(mean, std, size=shape)
+    elif isinstance(spec, list) and len(spec) == 2 and all(isinstance(v, (int, float)) for v in spec):
+        a = rng.uniform(spec[0], spec[1], size=shape)
+    else:
+        return None  # special-value cases (inf / nan fills) are covered by the parity tests' own cases
+    return torch.from_numpy(a.astype(np.float32)).to(dtype).float()
+
+
+def as_bool(v):
+    return v if isinstance(v, bool) else str(v).lower() == "true"
+
+
+def replay_atk(data, index):
+    import json
+    for api, (rel, kind) in ATK.items():
+        cases = json.load(open(os.path.join(REF, rel)))
+        kept = 0
+        for case in cases:
+            if kept >= CASES_PER_API:
+                break
+            f = case_fields(case)
+            rng = np.random.default_rng(7000 + 1000 * list(ATK).index(api) + int(case["id"]))
+            name = f"atk.{api}.{case['id']}"
+            if kind in ("interp_fwd", "interp_bwd"):
+                _, dt, shape, spec = f["input"]
+                if dt not in TORCH_DT or len(shape) != 4 or "size" not in f:
+                    continue
+                n, c, h, w = min(shape[0], 2), min(shape[1], 3), shape[2], shape[3]
+                oh, ow = f["size"]
+                if min(n, c, h, w, oh, ow) < 1 or h * w > MAX_PLANE or oh * ow > MAX_PLANE:
+                    continue
+                x = draw(rng, (n, c, h, w), spec, TORCH_DT[dt])
+                if x is None:
+                    continue
+                mode = f.get("mode", "nearest")
+                kw = {"size": (oh, ow), "mode": mode}
+                if mode != "nearest":
+                    kw["align_corners"] = as_bool(f.get("align_corners", False))
+                if as_bool(f.get("antialias", False)):
+                    kw["antialias"] = True
+                xg = x.clone().requires_grad_(kind == "interp_bwd")
+                y = F.interpolate(xg, **kw)
+                data[name + ".x"] = x.numpy() if dt == "fp32" else x.to(torch.float16 if dt == "fp16" else torch.float32).numpy()
+                meta = {"api": api, "dtype": dt, "shape": [n, c, h, w], "size": [oh, ow], "mode": mode,
+                        "align": kw.get("align_corners", False), "aa": kw.get("antialias", False)}
+                if kind == "interp_fwd":
+                    data[name + ".y"] = y.detach().numpy()
+                else:
+                    # grad_output = ones, as executor_aclnnUpsampleBilinear2dBackwardV2.py:82-83, and a seeded random one
+                    (gx_ones,) = torch.autograd.grad(y, xg, torch.ones_like(y), retain_graph=True)
+                    g = torch.from_numpy(rng.standard_normal(tuple(y.shape)).astype(np.float32)).to(TORCH_DT[dt]).float()
+                    (gx_rand,) = torch.autograd.grad(y, xg, g)
+                    data[name + ".g"] = g.numpy()
+                    data[name + ".gx_ones"] = gx_ones.numpy()
+                    data[name + ".gx"] = gx_rand.numpy()
+                index.append(meta | {"name": name})
+                kept += 1
+            else:
+                _, dt, ishape, ispec = f["input"]
+                _, _, gshape, gspec = f["grid"]
+                if dt not in TORCH_DT or len(ishape) != 4:
+                    continue
+                n, c, h, w = min(ishape[0], 2), min(ishape[1], 3), ishape[2], ishape[3]
+                # samples are independent of each other: a large grid is cut to its first 24 x 24 samples
+                ho, wo = min(gshape[1], 24), min(gshape[2], 24)
+                if min(n, c, h, w, ho, wo) < 1 or h * w > MAX_PLANE + 100:
+                    continue
+                x = draw(rng, (n, c, h, w), ispec, TORCH_DT[dt])
+                grid = draw(rng, (n, ho, wo, 2), gspec, TORCH_DT[dt])
+                if x is None or grid is None:
+                    continue
+                mode = int(f.get("mode", f.get("interpolationMode", 0)))
+                pad = int(f.get("padding_mode", f.get("paddingMode", 0)))
+                align = as_bool(f.get("align_corners", f.get("alignCorners", False)))
+                data[name + ".x"] = x.numpy()
+                data[name + ".grid"] = grid.numpy()
+                meta = {"api": api, "dtype": dt, "mode": mode, "pad": pad, "align": align, "name": name}
+                if kind == "grid_fwd":
+                    data[name + ".y"] = F.grid_sample(x, grid, mode=["bilinear", "nearest", "bicubic"][mode],
+                                                      padding_mode=["zeros", "border", "reflection"][pad],
+                                                      align_corners=align).numpy()
+                else:
+                    _, _, _, gospec = f["gradOutput"]
+                    go = draw(rng, (n, c, ho, wo), gospec, TORCH_DT[dt])
+                    gi, gg = torch.ops.aten.grid_sampler_2d_backward(go, x, grid, mode, pad, align, [True, True])
+                    data[name + ".g"] = go.numpy()
+                    data[name + ".gx"] = gi.numpy()
+                    data[name + ".ggrid"] = gg.numpy()
+                index.append(meta)
+                kept += 1
+        print(f"{api}: {kept} cases of {len(cases)}")
+
+
+def replay_gen_data(data, index):
+    """Runs the reference's kernel-UT generator of UpsampleBilinear2d in a scratch directory (it writes the input and
+    the torch golden as .bin files) and stores what it wrote."""
+    import runpy
+    import tempfile
+    gen = os.path.join(REF, "image/upsample_bilinear2d/tests/ut/op_kernel/upsample_bilinear2d_data/gen_data.py")
+    mod = runpy.run_path(gen)
+    cwd = os.getcwd()
+    for i, (shape, size) in enumerate([("(1,1,4,4)", "(16,16)"), ("(2,3,9,7)", "(5,20)"), ("(1,2,16,16)", "(32,32)")]):
+        with tempfile.TemporaryDirectory() as tmp:
+            os.chdir(tmp)
+            try:
+                np.random.seed(4242 + i)
+                mod["gen_data_and_golden"](shape, size, f"case{i}", "float32")
+                x = np.fromfile(f"case{i}_float32_input_upsample_bilinear2d.bin", dtype=np.float32)
+                y = np.fromfile(f"case{i}_float32_golden_upsample_bilinear2d.bin", dtype=np.float32)
+            finally:
+                os.chdir(cwd)
+        ishape, osize = eval(shape), eval(size)
+        name = f"gen_data.UpsampleBilinear2d.{i}"
+        data[name + ".x"] = x.reshape(ishape)
+        data[name + ".y"] = y.reshape(ishape[:2] + osize)
+        index.append({"api": "UpsampleBilinear2d", "dtype": "fp32", "shape": list(ishape), "size": list(osize),
+                      "mode": "bilinear", "align": False, "aa": False, "name": name})
+
+
+def main_replay():
+    import json
+    torch.set_num_threads(1)
+    data, index = {}, []
+    replay_atk(data, index)
+    replay_gen_data(data, index)
+    data["index"] = np.array(json.dumps(index))
+    data["meta.torch_version"] = np.array(torch.__version__)
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "atk_replay.npz")
+    np.savez_compressed(out, **data)
+    print("wrote", out, os.path.getsize(out), "bytes,", len(index), "cases")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 2 and sys.argv[2] == "replay":
+        main_replay()
+    else:
+        main()
