@@ -1,4 +1,5 @@
 // The acl object model (tensors, arrays, executors), error reporting and per-thread options.
+#include <nvtx3/nvToolsExt.h>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -61,8 +62,37 @@ void LogInfo(const char* fmt, ...)
     fprintf(stderr, "[opscv][I] %s\n", buf);
 }
 
+// NVTX ranges around the two phases of every call (the tracing hook of this library, as the reference's
+// entry points log through its dfx macros): off unless OPSCV_NVTX is set to a non-zero value or OPSCV_LOG_LEVEL >= 2.
+// nvtx3 is header-only and finds the profiler's injection library at run time; without a profiler a range is a
+// few nanoseconds of no-op.
+bool NvtxEnabled()
+{
+    static const bool on = [] {
+        const char* e = std::getenv("OPSCV_NVTX");
+        return (e != nullptr && std::atoi(e) != 0) || LogLevel() >= 2;
+    }();
+    return on;
+}
+struct NvtxRange {
+    explicit NvtxRange(const char* name) : on(NvtxEnabled())
+    {
+        if (on) {
+            nvtxRangePushA(name);
+        }
+    }
+    ~NvtxRange()
+    {
+        if (on) {
+            nvtxRangePop();
+        }
+    }
+    bool on;
+};
+
 aclOpExecutor* NewExecutor(const char* api)
 {
+    const NvtxRange range(api); // phase 1: the executor is created at the end of validation and planning
     aclOpExecutor* e = new (std::nothrow) aclOpExecutor();
     if (e == nullptr) {
         return nullptr;
@@ -121,6 +151,7 @@ aclnnStatus RunExecutor(const char* api, void* workspace, uint64_t workspaceSize
     }
     aclnnStatus status = ACLNN_SUCCESS;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const NvtxRange range(api); // phase 2: the launches of this call
     for (auto& step : executor->steps) {
         const cudaError_t e = step(static_cast<char*>(workspace), s);
         if (e != cudaSuccess) {

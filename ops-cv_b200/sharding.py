@@ -6,6 +6,8 @@ rank-local tensors and no data-path collective. What ranks exchange is only book
 timed region, the maximum of the device times and the sum of the units processed. These helpers are that
 bookkeeping; they work on any torch.distributed backend (nccl on the GPUs, gloo in the CPU tests).
 """
+import datetime
+
 import torch
 
 
@@ -49,3 +51,33 @@ def box_throughput(units_per_rank, ms_per_rank, dist=None, device=None):
     total = sum_over_ranks([units_per_rank], dist, device)[0]
     worst = max_over_ranks([ms_per_rank], dist, device)[0]
     return total / (worst * 1e-3)
+
+
+class RankLost(RuntimeError):
+    """A rank did not check in for a step within the time limit (it exited, hung or never joined)."""
+
+
+class StepGuard:
+    """Host-side liveness check between steps of a batch-sharded job. There is no data-path collective whose failure
+    would reveal a lost rank, so every rank checks in on the process group's store before a step
+    (`guard.check_in(step)`) and waits, with a time limit, for the check-ins of all others; a rank that exited or
+    hung between steps makes the others raise RankLost instead of entering the step (and instead of waiting in the
+    next barrier for ever). Ranks must leave only between steps, with none of their kernels in flight; this class is
+    pure host logic and touches no GPU."""
+
+    def __init__(self, store, world, rank, timeout_s=5.0, tag="opscv"):
+        self.store, self.world, self.rank = store, world, rank
+        self.timeout = datetime.timedelta(seconds=timeout_s)
+        self.tag = tag
+
+    def check_in(self, step):
+        self.store.set(f"{self.tag}/step{step}/rank{self.rank}", "1")
+        keys = [f"{self.tag}/step{step}/rank{r}" for r in range(self.world) if r != self.rank]
+        missing = []
+        for key in keys:  # one key at a time, so that the message can name the rank
+            try:
+                self.store.wait([key], self.timeout)
+            except Exception:  # noqa: BLE001 - the store raises a backend-specific timeout error
+                missing.append(int(key.rsplit("rank", 1)[1]))
+        if missing:
+            raise RankLost(f"step {step}: no check-in from rank(s) {missing} within {self.timeout.total_seconds():.1f} s")

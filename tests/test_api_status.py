@@ -15,6 +15,8 @@ import re
 import pytest
 import torch
 
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
 OK, NULLPTR, INVALID, INNER_NULL = 0, 161001, 161002, 561103
 
 
@@ -260,3 +262,35 @@ def test_options_and_executor_lifecycle(ops):
     assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(256), ws.value, ex, None) == INVALID
     assert L.aclnnUpsampleNearest2d(ctypes.c_void_p(256), ws.value, None, None) == NULLPTR
     assert L.aclCreateTensor(None, 4, 0, None, 0, 0, None, 0, None) is None
+
+
+def test_second_phase_without_a_device_reports_a_runtime_error():
+    """Phase 2 with no CUDA device visible: the first launch fails, the call returns ACLNN_ERR_RUNTIME_ERROR (361001)
+    with the CUDA error in the message, and the executor is consumed. Run in a child process with
+    CUDA_VISIBLE_DEVICES empty, so that it means the same on a machine that has GPUs (nothing can be launched there
+    either, whatever the pointers are)."""
+    import subprocess
+    import sys
+    code = (
+        "import ctypes, os, sys\n"
+        f"sys.path.insert(0, {ROOT!r})\n"
+        "import __graft_entry__ as entry\n"
+        "ops = entry.load_package(); L = ops.lib()\n"
+        "dims = (ctypes.c_int64 * 4)(1, 1, 4, 4); odims = (ctypes.c_int64 * 4)(1, 1, 8, 8)\n"
+        "st = (ctypes.c_int64 * 4)(16, 16, 4, 1); ost = (ctypes.c_int64 * 4)(64, 64, 8, 1)\n"
+        "x = L.aclCreateTensor(dims, 4, 0, st, 0, 0, dims, 4, ctypes.c_void_p(4096))\n"
+        "y = L.aclCreateTensor(odims, 4, 0, ost, 0, 0, odims, 4, ctypes.c_void_p(8192))\n"
+        "size = (ctypes.c_int64 * 2)(8, 8); sz = L.aclCreateIntArray(size, 2)\n"
+        "ws, ex = ctypes.c_uint64(0), ctypes.c_void_p(None)\n"
+        "assert L.aclnnUpsampleBilinear2dGetWorkspaceSize(x, sz, False, 0.0, 0.0, y, ctypes.byref(ws), ctypes.byref(ex)) == 0\n"
+        "status = L.aclnnUpsampleBilinear2d(ctypes.c_void_p(1 << 20), ws.value, ex, None)\n"
+        "msg = L.aclGetRecentErrMsg().decode()\n"
+        "again = L.aclnnUpsampleBilinear2d(ctypes.c_void_p(1 << 20), ws.value, ex, None)\n"
+        "print(status, again, msg)\n"
+    )
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
+    assert out.returncode == 0, out.stderr[-2000:]
+    status, again, msg = out.stdout.strip().split(" ", 2)
+    assert int(status) == 361001 and "CUDA error" in msg
+    assert int(again) == INVALID  # the executor was consumed by the failed call

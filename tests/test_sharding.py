@@ -108,3 +108,46 @@ def test_shard_range_covers_batch():
         sharding.shard_range(8, 2, 2)
     t = torch.arange(10).reshape(5, 2)
     assert torch.equal(torch.cat([sharding.shard_batch(t, 2, r) for r in range(2)]), t)
+
+
+def _liveness_worker(rank, world, port, q):
+    """Rank 1 leaves after step 1 (between steps, nothing in flight); rank 0 must notice at step 2."""
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from opscv_b200 import sharding
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=20))
+    guard = sharding.StepGuard(store, world, rank, timeout_s=1.5)
+    done = []
+    try:
+        for step in range(4):
+            if rank == 1 and step == 2:
+                q.put((rank, "left", done))
+                return
+            guard.check_in(step)
+            done.append(step)
+        q.put((rank, "finished", done))
+    except sharding.RankLost as exc:
+        q.put((rank, "lost: " + str(exc), done))
+        if rank == 0:
+            import time
+            time.sleep(0.5)  # keep the store alive until the message is out
+
+
+def test_a_rank_that_leaves_between_steps_is_reported():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_liveness_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(world):
+        rank, what, done = q.get(timeout=60)
+        results[rank] = (what, done)
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert results[1] == ("left", [0, 1])
+    what, done = results[0]
+    assert done == [0, 1] and what.startswith("lost: step 2") and "[1]" in what  # reported, not waited for
