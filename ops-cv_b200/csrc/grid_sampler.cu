@@ -437,10 +437,12 @@ __global__ void __launch_bounds__(kWinThreads, 2)
         rec[j] = (live[j] && !bad[j]) ? static_cast<uint32_t>((cy[j] - wy0) * pitch + (cx[j] - wx0)) * 4u : 0u;
     }
     // the two pixels' weights side by side: one packed multiply and one packed add per tap and channel
+    // (a sample whose coordinates were NaN or infinite gets NaN weights: every one of its outputs is then NaN, which
+    // is what the reference writes for it)
     F2 w2[4];
 #pragma unroll
     for (int tap = 0; tap < 4; ++tap) {
-        w2[tap] = MakeF2(live[0] ? wt[0][tap] : 0.0f, live[1] ? wt[1][tap] : 0.0f);
+        w2[tap] = MakeF2(bad[0] ? nanv : (live[0] ? wt[0][tap] : 0.0f), bad[1] ? nanv : (live[1] ? wt[1][tap] : 0.0f));
     }
     const int32_t groups = static_cast<int32_t>((g.c + kWinChans - 1) / kWinChans);
     // Copies. The box is the same for every channel, so a thread owns the same 16-byte pieces (row r, piece q) of the
@@ -505,12 +507,12 @@ __global__ void __launch_bounds__(kWinThreads, 2)
             o = AddProduct2(Mul2(MakeF2(tapv(ta, pitchBytes + 4), tapv(tb, pitchBytes + 4)), w2[3]), o);
             float o0, o1;
             SplitF2(o, o0, o1);
-            if (c0 + k < g.c) {
+            if (c0 + k < g.c) { // written once and not read again by this kernel: streaming stores
                 if (live[0]) {
-                    *yp0 = bad[0] ? nanv : o0;
+                    __stcs(yp0, o0);
                 }
                 if (live[1]) {
-                    *yp1 = bad[1] ? nanv : o1;
+                    __stcs(yp1, o1);
                 }
             }
             ta += planeBytes;
