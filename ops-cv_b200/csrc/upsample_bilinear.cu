@@ -906,16 +906,25 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         // advances by one row per call
         const TIn* issueRow = gp + static_cast<int64_t>(first) * wout + j0;
         int32_t issueLeft = count;
+        // The neighbour columns j0-1 and j0+VG are the last / first column of the threads to the left and right, whose
+        // queue slots lie next to this thread's. When that thread is a lane of the same warp (same plane row, same
+        // stream element at the same time) its copy is read instead of copying the word again: the separate 4-byte
+        // copies made every 32-byte sector of grads travel from L2 three times (ncu: 3.4 x the tensor on the L2-to-SM
+        // path, which is what bounded the kernel). Only lanes at a warp edge still copy their own neighbour word.
+        const unsigned warpMask = __activemask();
+        const int32_t laneId = tid & 31;
+        const bool leftShared = hasLeft && threadIdx.x > 0 && laneId > 0;
+        const bool rightShared = hasRight && threadIdx.x + 1 < blockDim.x && laneId < 31 && g + 1 < groups;
         auto issue = [&](unsigned char* pm, unsigned char* plr) {
             if (issueLeft > 0) {
 #pragma unroll
                 for (int m = 0; m < NM; ++m) {
                     CpAsync16(pm + 16 * m, reinterpret_cast<const uint4*>(issueRow) + m);
                 }
-                if (hasLeft) { // the word holding column j0-1 (4-byte aligned: j0 is a multiple of 8)
+                if (hasLeft && !leftShared) { // the word holding column j0-1 (4-byte aligned: j0 is a multiple of 8)
                     CpAsync4(plr, issueRow - HE);
                 }
-                if (hasRight) {
+                if (hasRight && !rightShared) {
                     CpAsync4(plr + 4, issueRow + VG);
                 }
             }
@@ -927,6 +936,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         // element n has, then refills its slot with element n + kX2Depth.
         auto take = [&](int32_t n, float (&hp)[V]) {
             CpAsyncWait<kX2Depth - 1>();
+            __syncwarp(warpMask); // every lane's copy of element n has landed: the neighbours' slots may be read
             const uint32_t off = static_cast<uint32_t>(n & (kX2Depth - 1)) * strideMid;
             unsigned char* pm = midP + off;
             unsigned char* plr = lrP + off / (2 * NM);
@@ -935,7 +945,14 @@ __global__ void __launch_bounds__(kW2Threads, 5)
             for (int m = 0; m < NM; ++m) {
                 mid[m] = reinterpret_cast<const uint4*>(pm)[m];
             }
-            const uint2 lr = *reinterpret_cast<const uint2*>(plr);
+            uint2 lr = *reinterpret_cast<const uint2*>(plr);
+            if (leftShared) {
+                lr.x = *reinterpret_cast<const uint32_t*>(pm - 4);        // last word of the left neighbour's slot
+            }
+            if (rightShared) {
+                lr.y = *reinterpret_cast<const uint32_t*>(pm + 16 * NM);  // first word of the right neighbour's slot
+            }
+            __syncwarp(warpMask); // all lanes have read before any slot is refilled
             issue(pm, plr);
             float v[VG + 2]; // grads columns j0-1 .. j0+8
             const TIn* me = reinterpret_cast<const TIn*>(mid);
