@@ -284,7 +284,9 @@ constexpr int kDetStep = 256;
 
 // counts[(n * chunks + c) * inPlane + d] = taps of the samples of chunk c of image n that land on destination d.
 // A chunk is `chunkSamples` consecutive samples (a multiple of kDetStep).
-template <typename T>
+// CUBIC: the bicubic variant (16 taps per sample); a template flag so that the bilinear / nearest kernels carry none
+// of its registers.
+template <typename T, bool CUBIC>
 __global__ void __launch_bounds__(kThreads)
     DetCountKernel(const T* __restrict__ grid, int32_t* __restrict__ counts, GridShape g, int32_t chunks,
                    int32_t chunkSamples, int64_t total)
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(kThreads)
         const int64_t n = s / outPlane;
         const int64_t c = (s - n * outPlane) / chunkSamples;
         int32_t* cnt = counts + (n * chunks + c) * inPlane;
-        if (g.interp == 2) {
+        if constexpr (CUBIC) {
             const CubicTaps ct = MakeCubicTaps(DType<T>::Load(grid + 2 * s), DType<T>::Load(grid + 2 * s + 1), g);
 #pragma unroll
             for (int tap = 0; tap < 16; ++tap) {
@@ -409,7 +411,7 @@ __global__ void __launch_bounds__(1024) DetScanKernel(int32_t* __restrict__ segS
 // (a barrier between turns), and inside a warp the rank among lanes with the same destination comes from
 // __match_any_sync, so the position of every entry is a function of the data alone. The running positions live in
 // shared memory when the plane fits (cursorInSmem), else in the chunk's own slice of the offsets array.
-template <typename T>
+template <typename T, bool CUBIC>
 __global__ void __launch_bounds__(kDetStep)
     DetFillKernel(const T* __restrict__ grid, int32_t* offsets, const int32_t* __restrict__ segStart,
                   Entry* __restrict__ entries, GridShape g, int32_t chunks, int32_t chunkSamples,
@@ -437,7 +439,7 @@ __global__ void __launch_bounds__(kDetStep)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const unsigned lower = (1u << lane) - 1u;
     const int64_t p0 = static_cast<int64_t>(c) * chunkSamples, p1 = min(outPlane, p0 + chunkSamples);
-    const int numTaps = g.interp == 0 ? 4 : (g.interp == 2 ? 16 : 1);
+    const int numTaps = CUBIC ? 16 : (g.interp == 0 ? 4 : 1);
     for (int64_t base = p0; base < p1; base += kDetStep) {
         const int64_t p = base + threadIdx.x;
         GradTaps t{};
@@ -445,7 +447,7 @@ __global__ void __launch_bounds__(kDetStep)
         t.x0 = INT32_MIN / 2; // far out of bounds: a thread past the end has no tap in range
         t.y0 = INT32_MIN / 2;
         if (p < p1) {
-            if (g.interp == 2) {
+            if constexpr (CUBIC) {
                 ct = MakeCubicTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
             } else {
                 t = MakeGradTaps(DType<T>::Load(gb + 2 * p), DType<T>::Load(gb + 2 * p + 1), g);
@@ -454,7 +456,7 @@ __global__ void __launch_bounds__(kDetStep)
         for (int tap = 0; tap < numTaps; ++tap) {
             int32_t d;
             float wgt;
-            if (g.interp == 2) {
+            if constexpr (CUBIC) {
                 d = p < p1 ? CubicDest(ct, tap, g) : -1;
                 wgt = CubicWeight(ct, tap); // the deterministic kernel multiplies grad_output by cx * cy (:312-314)
             } else {
@@ -969,20 +971,32 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
         const T* px = static_cast<const T*>(x);
         const T* pg = static_cast<const T*>(grid);
         T* pgi = static_cast<T*>(gi);
-        DetCountKernel<T><<<GridFor(samples, kThreads), kThreads, 0, s>>>(pg, positions, g, plan.detChunks,
-                                                                          plan.detChunkSamples, samples);
+        if (g.interp == 2) {
+            DetCountKernel<T, true><<<GridFor(samples, kThreads), kThreads, 0, s>>>(pg, positions, g, plan.detChunks,
+                                                                                    plan.detChunkSamples, samples);
+        } else {
+            DetCountKernel<T, false><<<GridFor(samples, kThreads), kThreads, 0, s>>>(pg, positions, g, plan.detChunks,
+                                                                                     plan.detChunkSamples, samples);
+        }
         DetColumnKernel<<<GridFor(g.n * inPlane, kThreads), kThreads, 0, s>>>(positions, segStart, inPlane,
                                                                               plan.detChunks, g.n * inPlane);
         DetScanKernel<<<static_cast<unsigned>(g.n), 1024, 0, s>>>(segStart, inPlane);
         const size_t cursorBytes = plan.detCursorSmem ? static_cast<size_t>(inPlane) * 4 : 0;
-        if (cursorBytes > 48 * 1024) {
-            e = cudaFuncSetAttribute(DetFillKernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(cursorBytes));
-        }
-        if (e == cudaSuccess) {
-            DetFillKernel<T><<<static_cast<unsigned>(g.n * plan.detChunks), kDetStep, cursorBytes, s>>>(
-                pg, positions, segStart, entries, g, plan.detChunks, plan.detChunkSamples, entriesPerImage,
-                plan.detCursorSmem ? 1 : 0);
+        auto fill = [&](auto kernel) {
+            if (cursorBytes > 48 * 1024) {
+                e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(cursorBytes));
+            }
+            if (e == cudaSuccess) {
+                kernel<<<static_cast<unsigned>(g.n * plan.detChunks), kDetStep, cursorBytes, s>>>(
+                    pg, positions, segStart, entries, g, plan.detChunks, plan.detChunkSamples, entriesPerImage,
+                    plan.detCursorSmem ? 1 : 0);
+            }
+        };
+        if (g.interp == 2) {
+            fill(DetFillKernel<T, true>);
+        } else {
+            fill(DetFillKernel<T, false>);
         }
         CountLaunch(4);
         if (e == cudaSuccess && plan.detGatherGroup > 0) {
