@@ -77,12 +77,15 @@ TRAFFIC_SOURCE = {"cfg2": "profiles/cfg2_fpn_upsample_kernels_ncu.md", "cfg3": "
                   "cfg4": "profiles/cfg4_grid_sampler_kernels_ncu.md", "cfg5": "profiles/cfg5_box_sweep_kernels_ncu.md"}
 NCU_TRAFFIC = {
     ("cfg2", "UpsampleNearest2d"): 201.0e6, ("cfg2", "UpsampleBilinear2d"): 206.1e6,
-    ("cfg2", "UpsampleNearest2dBackward"): 242.2e6, ("cfg2", "UpsampleBilinear2dBackward"): 245.9e6,
+    ("cfg2", "UpsampleNearest2dBackward"): 242.2e6, ("cfg2", "UpsampleBilinear2dBackward"): 208.0e6,
     ("cfg3", "UpsampleBicubic2dAA"): 864.1e6, ("cfg3", "UpsampleBicubic2dAAGrad"): 785.0e6,
     ("cfg4", "GridSampler2D"): 278.9e6, ("cfg4", "GridSampler2DBackward[atomic]"): 394.8e6,
     ("cfg4", "GridSampler2DBackward[deterministic]"): 326.8e6 + 447.9e6,  # gather + grad_grid kernels
-    ("cfg5", "UpsampleBilinear2d[NHWC bf16]"): 5311.5e6, ("cfg5", "GridSampler2D[affine fp32]"): 2593.2e6,
+    ("cfg5", "UpsampleBilinear2d[NHWC bf16]"): 5311.5e6, ("cfg5", "GridSampler2D[affine fp32]"): 2252.0e6,
 }
+# rows whose figure comes from a single-kernel capture of a reduced batch, scaled by the batch divisor
+TRAFFIC_SOURCE_OP = {("cfg2", "UpsampleBilinear2dBackward"): "profiles/cfg2_bilinear_backward_kernel_ncu.md",
+                     ("cfg5", "GridSampler2D[affine fp32]"): "profiles/cfg5_grid_sampler_window_kernel_ncu.md"}
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -758,7 +761,7 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak, steps, d
                             "algorithmic_bytes": op.algo_bytes}
         if shard is None and args.batch_div == 1 and NCU_TRAFFIC.get((wname, op.name)) is not None:
             op_rows[op.name]["traffic_from_profile"] = NCU_TRAFFIC[(wname, op.name)]
-            op_rows[op.name]["traffic_source"] = TRAFFIC_SOURCE.get(wname[:4])
+            op_rows[op.name]["traffic_source"] = TRAFFIC_SOURCE_OP.get((wname, op.name), TRAFFIC_SOURCE.get(wname[:4]))
     dom = max(zip(oplist, per_op_ms), key=lambda p: p[1])
     dom_row = op_rows[dom[0].name]
     roofline = {"kernel": dom[0].name, "bound": "hbm", "achieved": dom_row["gb_per_s"], "peak": peak, "unit": "GB/s",
