@@ -120,6 +120,34 @@ ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTens
 ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGrad(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                                    aclrtStream stream);
 
+/* ---- UpsampleBicubic2d (no antialiasing) ------------------------------------------------------------------
+ * Replaces image/upsample_bicubic2d/op_host/op_api/aclnn_upsample_bicubic_2d.h:25-34 (implementation
+ * aclnn_upsample_bicubic_2d.cpp:233-330, regbase branch; kernel
+ * image/resize_bicubic_v2/op_kernel/arch35/resize_bicubic_v2_simt_base.h:23-171; schedules and scales
+ * image/resize_bicubic_v2/op_host/arch35/resize_bicubic_v2_tiling_arch35.cpp:484-588). NCHW, NHWC or ND; cubic
+ * convolution with A = -0.75 over four clamped taps per axis. */
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                             const bool alignCorners, const double scalesH,
+                                                             const double scalesW, aclTensor* out,
+                                                             uint64_t* workspaceSize, aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                             aclrtStream stream);
+
+/* Replaces image/upsample_bicubic2d_grad/op_host/op_api/aclnn_upsample_bicubic_2d_backward.h:24-33 (implementation
+ * aclnn_upsample_bicubic_2d_backward.cpp:308-366, regbase branch; gather kernel
+ * image/resize_bicubic_v2_grad/op_kernel/arch35/resize_bicubic_v2_grad_simt_determine.h:95-350, which the reference
+ * runs when the deterministic option is set or an extent grows; its atomic kernel resize_bicubic_v2_grad_simt.h:108-146
+ * adds the same terms in no fixed order). Always the gather here, so results do not change from run to run. */
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2dBackwardGetWorkspaceSize(const aclTensor* gradOut,
+                                                                     const aclIntArray* outputSize,
+                                                                     const aclIntArray* inputSize,
+                                                                     const bool alignCorners, double scalesH,
+                                                                     double scalesW, aclTensor* gradInput,
+                                                                     uint64_t* workspaceSize,
+                                                                     aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBicubic2dBackward(void* workspace, uint64_t workspaceSize,
+                                                     aclOpExecutor* executor, aclrtStream stream);
+
 /* ---- GridSampler2D -------------------------------------------------------------------------------------
  * Replaces image/grid_sample/op_api/aclnn_grid_sampler2d.h:53-82 (implementation aclnn_grid_sampler2d.cpp:266-340;
  * arithmetic image/grid_sampler2_d/op_kernel/arch35/grid_sampler2_d_simt.h:106-215,303-514).

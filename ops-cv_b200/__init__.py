@@ -69,6 +69,10 @@ SYMBOLS = {
     "aclnnUpsampleBicubic2dAA": _PHASE2,
     "aclnnUpsampleBicubic2dAAGradGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleBicubic2dAAGrad": _PHASE2,
+    "aclnnUpsampleBicubic2dGetWorkspaceSize": (_I32, [_P, _P, _B, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleBicubic2d": _PHASE2,
+    "aclnnUpsampleBicubic2dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleBicubic2dBackward": _PHASE2,
     "aclnnGridSampler2DGetWorkspaceSize": (_I32, [_P, _P, _I64, _I64, _B, _P, _PU64, _PP]),
     "aclnnGridSampler2D": _PHASE2,
     "aclnnGridSampler2DBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _I64, _I64, _B, _P, _P, _P, _PU64, _PP]),

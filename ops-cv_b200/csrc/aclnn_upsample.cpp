@@ -3,6 +3,7 @@
 // each function) and then freezes a launch plan into the executor: table builders, the resampling kernel, and
 // the staging copies for strided views. Scales are computed here, on the host, with the expressions of the
 // reference's arch35 tiling code.
+#include <cfloat>
 #include <cmath>
 
 #include "host_common.h"
@@ -410,6 +411,55 @@ bool AAIsCopy(const Geom& in, const Geom& out, const AAGeom& h, const AAGeom& w)
 {
     // upsample_bicubic2d_aa_tiling_arch35.cpp:115-125
     return out.h == in.h && out.w == in.w && std::fabs(h.scale - 1.0f) < 1e-6f && std::fabs(w.scale - 1.0f) < 1e-6f;
+}
+
+// ---- UpsampleBicubic2d (no antialiasing) ----------------------------------------------------------------------
+// Schedule of the forward (image/resize_bicubic_v2/op_host/arch35/resize_bicubic_v2_tiling_arch35.cpp:484-522):
+// 1 equal extents (copy), 3 a single output pixel of an align_corners call, 2 a single input pixel, 4 integer
+// source positions (integer scales with align_corners, odd integer scales without), 0 the general kernel. The
+// NHWC copy schedules of :391-420 give the results of 1 and 4.
+bool IsIntegerScale(float s)
+{
+    const float back = static_cast<float>(static_cast<int32_t>(s));
+    return std::fabs(s - back) < FLT_EPSILON;
+}
+int32_t BicubicFwdSchedule(const Geom& in, const Geom& out, bool align, float scaleH, float scaleW)
+{
+    const bool intH = IsIntegerScale(scaleH), intW = IsIntegerScale(scaleW);
+    const bool odd = !align && intH && intW && static_cast<int32_t>(scaleH) % 2 == 1 &&
+                     static_cast<int32_t>(scaleW) % 2 == 1;
+    if (out.h == in.h && out.w == in.w) {
+        return 1;
+    }
+    if (out.h == 1 && out.w == 1 && align) {
+        return 3;
+    }
+    if (in.h == 1 && in.w == 1) {
+        return 2;
+    }
+    return ((align && intH && intW) || odd) ? 4 : 0;
+}
+
+// Scale and inverse scale of the backward gather kernel
+// (image/resize_bicubic_v2_grad/op_host/arch35/resize_bicubic_v2_grad_base_tiling_arch35.cpp:316-364, the
+// isMatchDetermine branch). `in` = grad_input extent, `out` = grads extent.
+struct BicubicGradScale {
+    float scale, inverse;
+};
+BicubicGradScale MakeBicubicGradScale(int64_t in, int64_t out, bool align, float userScale)
+{
+    BicubicGradScale g;
+    if (align && in > 1 && out > 1) {
+        g.scale = static_cast<float>(in - 1) / static_cast<float>(out - 1);
+        g.inverse = static_cast<float>(out - 1) / static_cast<float>(in - 1);
+    } else if (!align && userScale > 0.0f) {
+        g.scale = 1.0f / userScale;
+        g.inverse = userScale;
+    } else {
+        g.scale = static_cast<float>(in) / static_cast<float>(out);
+        g.inverse = static_cast<float>(out) / static_cast<float>(in);
+    }
+    return g;
 }
 
 } // namespace
@@ -959,6 +1009,208 @@ aclnnStatus aclnnUpsampleBicubic2dAAGrad(void* workspace, uint64_t workspaceSize
                                          aclrtStream stream)
 {
     return RunExecutor("aclnnUpsampleBicubic2dAAGrad", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/upsample_bicubic2d/op_host/op_api/aclnn_upsample_bicubic_2d.cpp:70-172 (CheckParams: null, dtype, format,
+// shape), :233-276 (the first phase: checks, empty tensors succeed, ResizeBicubicV2 with float(scales))
+aclnnStatus aclnnUpsampleBicubic2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                   const bool alignCorners, const double scalesH, const double scalesW,
+                                                   aclTensor* out, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleBicubic2d";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (outputSize == nullptr || self == nullptr || out == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (!DtypeSupported(self->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(self->dtype));
+    }
+    if (self->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from self dtype %s", api, DtypeName(out->dtype),
+                    DtypeName(self->dtype));
+    }
+    if (self->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self (%s) and out (%s) must have the same format", api,
+                    FormatName(self->format), FormatName(out->format));
+    }
+    if (out->format != ACL_FORMAT_NCHW && out->format != ACL_FORMAT_NHWC && out->format != ACL_FORMAT_ND) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: the format must be NCHW, NHWC or ND, got %s", api,
+                    FormatName(out->format));
+    }
+    if (self->dims.size() != 4 || out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self and out must be 4-D, got %zu-D and %zu-D", api,
+                    self->dims.size(), out->dims.size());
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: outputSize must have 2 values, got %zu", api, outputSize->v.size());
+    }
+    const Geom gi = GeomOf(self);
+    Geom go = gi;
+    go.h = outputSize->v[0];
+    go.w = outputSize->v[1];
+    if (!(gi.c > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: non-empty 4-D data tensor expected", api);
+    }
+    if (!(gi.h > 0 && gi.w > 0 && go.h > 0 && go.w > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID,
+                    "%s: size of H and W must be greater than 0, got input (H: %ld, W: %ld), output (H: %ld, W: %ld)",
+                    api, (long)gi.h, (long)gi.w, (long)go.h, (long)go.w);
+    }
+    const Geom gOut = GeomOf(out);
+    if (gOut.n != go.n || gOut.c != go.c || gOut.h != go.h || gOut.w != go.w) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out shape differs from (N, C, outputSize) of self", api);
+    }
+    if (!FitsInt32(gi) || !FitsInt32(go) || gi.w * gi.c > INT32_MAX || go.w * go.c > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H, W and W*C must not exceed INT32_MAX", api);
+    }
+    if (IsEmpty(self)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    const float sH = BilinearScale(gi.h, go.h, alignCorners, static_cast<float>(scalesH));
+    const float sW = BilinearScale(gi.w, go.w, alignCorners, static_cast<float>(scalesW));
+    const int32_t schedule = BicubicFwdSchedule(gi, go, alignCorners, sH, sW);
+    if (schedule == 1) {
+        return PlanCopy(api, self, out, workspaceSize, executor);
+    }
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef xin = StageInput(self, ws, ex);
+    const BufRef y = StageOutput(out, ws);
+    const Shape4 sh = MakeShape(gi, go);
+    const Dt dt = ToDt(self->dtype);
+    const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
+    const bool halfPixel = !alignCorners;
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        return Bicubic2dFwd(dt, lay, xin.At(w), y.At(w), sh, sH, sW, halfPixel, schedule, s);
+    });
+    FinishOutput(out, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnUpsampleBicubic2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                   aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBicubic2d", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/upsample_bicubic2d_grad/op_host/op_api/aclnn_upsample_bicubic_2d_backward.cpp:229-247 (CheckParams: null,
+// elements, format, dtype), :317-366 (empty gradOut succeeds; ResizeBicubicV2Grad with float(scales))
+aclnnStatus aclnnUpsampleBicubic2dBackwardGetWorkspaceSize(const aclTensor* gradOut, const aclIntArray* outputSize,
+                                                           const aclIntArray* inputSize, const bool alignCorners,
+                                                           double scalesH, double scalesW, aclTensor* gradInput,
+                                                           uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleBicubic2dBackward";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (inputSize == nullptr || gradInput == nullptr || gradOut == nullptr || outputSize == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (gradOut->dims.size() != 4 || gradInput->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut and gradInput must be 4-D, got %zu-D and %zu-D", api,
+                    gradOut->dims.size(), gradInput->dims.size());
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: outputSize must have two elements, got %zu", api,
+                    outputSize->v.size());
+    }
+    if (inputSize->v.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: inputSize must have four elements, got %zu", api,
+                    inputSize->v.size());
+    }
+    const bool nhwc = gradInput->format == ACL_FORMAT_NHWC;
+    if (!nhwc && gradInput->format != ACL_FORMAT_NCHW && gradInput->format != ACL_FORMAT_ND) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format only supports NCHW, NHWC or ND, got %s", api,
+                    FormatName(gradInput->format));
+    }
+    Geom gi, gg;
+    gi.n = inputSize->v[0];
+    gi.c = nhwc ? inputSize->v[3] : inputSize->v[1];
+    gi.h = nhwc ? inputSize->v[1] : inputSize->v[2];
+    gi.w = nhwc ? inputSize->v[2] : inputSize->v[3];
+    gg = gi;
+    gg.h = outputSize->v[0];
+    gg.w = outputSize->v[1];
+    if (!(gi.h > 0 && gi.w > 0 && gg.h > 0 && gg.w > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID,
+                    "%s: size of H and W must be greater than 0, got input (H: %ld, W: %ld), output (H: %ld, W: %ld)",
+                    api, (long)gi.h, (long)gi.w, (long)gg.h, (long)gg.w);
+    }
+    for (int i = 0; i < 4; ++i) {
+        const int64_t wantOut = nhwc ? (i == 0 ? gi.n : i == 1 ? gg.h : i == 2 ? gg.w : gi.c)
+                                     : (i == 0 ? gi.n : i == 1 ? gi.c : i == 2 ? gg.h : gg.w);
+        if (gradOut->dims[i] != wantOut) {
+            return Fail(ACLNN_ERR_PARAM_INVALID, "%s: dim %d of gradOut should be %ld, got %ld", api, i, (long)wantOut,
+                        (long)gradOut->dims[i]);
+        }
+        if (gradInput->dims[i] != inputSize->v[i]) {
+            return Fail(ACLNN_ERR_PARAM_INVALID, "%s: dim %d of gradInput should be %ld, got %ld", api, i,
+                        (long)inputSize->v[i], (long)gradInput->dims[i]);
+        }
+    }
+    if (gradOut->format != ACL_FORMAT_ND && gradOut->format != ACL_FORMAT_NCHW && gradOut->format != ACL_FORMAT_NHWC) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format only supports NCHW, NHWC or ND, got %s", api,
+                    FormatName(gradOut->format));
+    }
+    if (gradOut->format != gradInput->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut (%s) and gradInput (%s) must have the same format", api,
+                    FormatName(gradOut->format), FormatName(gradInput->format));
+    }
+    if (!DtypeSupported(gradOut->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOut dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(gradOut->dtype));
+    }
+    if (gradOut->dtype != gradInput->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradInput dtype %s differs from gradOut dtype %s", api,
+                    DtypeName(gradInput->dtype), DtypeName(gradOut->dtype));
+    }
+    if (!FitsInt32(gi) || !FitsInt32(gg) || gi.w * gi.c > INT32_MAX || gg.w * gg.c > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H, W and W*C must not exceed INT32_MAX", api);
+    }
+    if (IsEmpty(gradOut)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    if (gi.h == gg.h && gi.w == gg.w) { // resize_bicubic_v2_grad_all_copy_tiling_arch35.cpp:23-30
+        return PlanCopy(api, gradOut, gradInput, workspaceSize, executor);
+    }
+    aclOpExecutor* ex = NewExecutor(api);
+    if (ex == nullptr) {
+        return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
+    }
+    WsPlan ws;
+    const BufRef g = StageInput(gradOut, ws, ex);
+    const BufRef y = StageOutput(gradInput, ws);
+    const Shape4 sh = MakeShape(gi, gg);
+    const Dt dt = ToDt(gradOut->dtype);
+    const Layout lay = nhwc ? kNHWC : kNCHW;
+    const BicubicGradScale bh = MakeBicubicGradScale(gi.h, gg.h, alignCorners, static_cast<float>(scalesH));
+    const BicubicGradScale bw = MakeBicubicGradScale(gi.w, gg.w, alignCorners, static_cast<float>(scalesW));
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        return Bicubic2dBwd(dt, lay, g.At(w), y.At(w), sh, bh.scale, bw.scale, bh.inverse, bw.inverse, alignCorners, s);
+    });
+    FinishOutput(gradInput, y, ex);
+    ex->workspaceSize = ws.Size();
+    *workspaceSize = ws.Size();
+    *executor = ex;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnUpsampleBicubic2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                           aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBicubic2dBackward", workspace, workspaceSize, executor, stream);
 }
 
 // ===============================================================================================================

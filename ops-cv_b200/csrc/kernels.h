@@ -154,6 +154,13 @@ cudaError_t BicubicAABwdGather(Dt dt, const void* go, void* gi, Shape4 sh, AAAxi
 cudaError_t BicubicAABwdAtomic(Dt dt, const void* go, void* gi, float* acc, Shape4 sh, AAAxis th, AAAxis tw,
                                cudaStream_t s);
 
+// UpsampleBicubic2d without antialiasing. schedule: 0 general, 2 / 3 one input / one output pixel, 4 integer
+// source positions (equal extents are a copy made by the host layer). The backward is a gather in a fixed order.
+cudaError_t Bicubic2dFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, float scaleH, float scaleW,
+                         bool halfPixel, int32_t schedule, cudaStream_t s);
+cudaError_t Bicubic2dBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, float scaleH, float scaleW,
+                         float invH, float invW, bool align, cudaStream_t s);
+
 struct GridShape {
     int64_t n, c;
     int32_t hin, win, hout, wout;

@@ -199,6 +199,50 @@ def bicubic_aa_bwd(go, in_hw, align=False, scales=(0.0, 0.0), definition="scatte
     return gi
 
 
+def bicubic2d_fwd_schedule(in_hw, out_hw, align=False, scales=(0.0, 0.0)):
+    """The schedule the reference's tiling picks for UpsampleBicubic2d: "general", "copy", "one_input_pixel",
+    "one_output_pixel" or "integer_positions"."""
+    fn = lib().orc_bicubic2d_fwd_schedule
+    fn.restype = ctypes.c_int
+    k = fn(I64(in_hw[0]), I64(in_hw[1]), I64(out_hw[0]), I64(out_hw[1]), I32(int(align)), F32(scales[0]),
+           F32(scales[1]))
+    return ("general", "copy", "one_input_pixel", "one_output_pixel", "integer_positions")[k]
+
+
+def bicubic2d_fwd(x, out_hw, align=False, scales=(0.0, 0.0), fmt=NCHW):
+    x, px = _f(x)
+    n, c, h, w = _dims(x.shape, fmt)
+    y = np.empty(_shape(n, c, out_hw[0], out_hw[1], fmt), dtype=np.float32)
+    lib().orc_bicubic2d_fwd(px, y.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(h), I64(w), I64(out_hw[0]),
+                            I64(out_hw[1]), I32(int(align)), F32(scales[0]), F32(scales[1]), I32(fmt))
+    return y
+
+
+def bicubic2d_bwd_kernel_choice(in_hw, out_hw, align=False, scales=(0.0, 0.0), deterministic=False):
+    """Which kernel the reference's tiling runs for UpsampleBicubic2dBackward: "copy", "scatter" (atomic) or
+    "gather" (determine)."""
+    fn = lib().orc_bicubic2d_bwd_kernel_choice
+    fn.restype = ctypes.c_int
+    k = fn(I64(in_hw[0]), I64(in_hw[1]), I64(out_hw[0]), I64(out_hw[1]), I32(int(align)), F32(scales[0]),
+           F32(scales[1]), I32(int(deterministic)))
+    return ("copy", "scatter", "gather")[k]
+
+
+def bicubic2d_bwd(go, in_hw, align=False, scales=(0.0, 0.0), fmt=NCHW, definition="scatter", deterministic=False):
+    """definition: "scatter" (the atomic kernel run serially), "gather" (the determine kernel) or "dispatch"
+    (whichever the reference's tiling selects; equal extents copy under every definition)."""
+    go, pg = _f(go)
+    n, c, ho, wo = _dims(go.shape, fmt)
+    gi = np.empty(_shape(n, c, in_hw[0], in_hw[1], fmt), dtype=np.float32)
+    if definition == "dispatch":
+        definition = bicubic2d_bwd_kernel_choice(in_hw, (ho, wo), align, scales, deterministic)
+        definition = "scatter" if definition == "copy" else definition
+    fn = lib().orc_bicubic2d_bwd_scatter if definition == "scatter" else lib().orc_bicubic2d_bwd_gather
+    fn(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_hw[0]), I64(in_hw[1]), I64(ho), I64(wo),
+       I32(int(align)), F32(scales[0]), F32(scales[1]), I32(fmt))
+    return gi
+
+
 def grid_sampler2d_coords(grid, in_hw, pad=ZEROS, align=False):
     grid, pg = _f(grid)
     ns = grid.size // 2

@@ -160,6 +160,8 @@ ATK = {
     "UpsampleBicubic2dAAGrad": ("image/upsample_bicubic2d_aa_grad/tests/st/aclnnUpsampleBicubic2dAAGrad/atk_aclnnUpsampleBicubic2dAAGrad.json", "interp_bwd"),
     "GridSampler2D": ("image/grid_sample/tests/st/aclnnGridSampler2D/atk_aclnnGridSampler2D.json", "grid_fwd"),
     "GridSampler2DBackward": ("image/grid_sampler2_d_grad/tests/st/aclnnGridSampler2DBackward/atk_aclnnGridSampler2DBackward.json", "grid_bwd"),
+    "UpsampleBicubic2d": ("image/upsample_bicubic2d/tests/st/aclnnUpsampleBicubic2d/atk_aclnnUpsampleBicubic2d.json", "interp_fwd"),
+    "UpsampleBicubic2dBackward": ("image/upsample_bicubic2d_grad/tests/st/aclnnUpsampleBicubic2dBackward/atk_aclnnUpsampleBicubic2dBackward.json", "interp_bwd"),
 }
 TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
 CASES_PER_API = 20

@@ -171,6 +171,68 @@ def test_bicubic_aa_forward_status(ops):
                   T(ops, (2, 3, 7, 9), fmt="ND").ptr)[0] == OK
 
 
+def test_bicubic_forward_status(ops):
+    """image/upsample_bicubic2d/tests/ut/op_host/op_api/test_aclnn_upsample_bicubic_2d.cpp:27-310: one null case per
+    pointer, float / float16 / bfloat16 succeed, int64 and mixed dtypes are invalid, N = 0 succeeds, C = 0, H = 0,
+    an output size of 0, three output sizes and 3-D tensors are invalid."""
+    api = "aclnnUpsampleBicubic2d"
+    x, y, sz = T(ops, (1, 1, 3, 3)), T(ops, (1, 1, 5, 5)), IA(ops, [5, 5])
+    st, ws = phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, y.ptr)
+    assert st == OK and ws == 0
+    assert phase1(ops, api, None, sz.ptr, False, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, None, False, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, None)[0] == NULLPTR
+    for dt in (torch.float16, torch.bfloat16):
+        assert phase1(ops, api, T(ops, (1, 1, 3, 3), dt).ptr, sz.ptr, False, 0.0, 0.0, T(ops, (1, 1, 5, 5), dt).ptr)[0] == OK
+    assert phase1(ops, api, T(ops, (1, 1, 3, 3), torch.int64).ptr, sz.ptr, False, 0.0, 0.0,
+                  T(ops, (1, 1, 5, 5), torch.int64).ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, T(ops, (1, 1, 5, 5), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (0, 1, 3, 3)).ptr, sz.ptr, False, 0.0, 0.0, T(ops, (0, 1, 5, 5)).ptr) == (OK, 0)
+    assert phase1(ops, api, T(ops, (1, 0, 3, 3)).ptr, sz.ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (1, 1, 0, 3)).ptr, sz.ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, IA(ops, [5, 0]).ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, IA(ops, [5, 5, 5]).ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (1, 3, 3)).ptr, sz.ptr, False, 0.0, 0.0, T(ops, (1, 5, 5)).ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, T(ops, (1, 1, 5, 6)).ptr)[0] == INVALID
+    # NHWC and ND are accepted, a format mismatch is not
+    assert phase1(ops, api, T(ops, (1, 3, 3, 2), fmt="NHWC").ptr, sz.ptr, True, 0.0, 0.0,
+                  T(ops, (1, 5, 5, 2), fmt="NHWC").ptr)[0] == OK
+    assert phase1(ops, api, T(ops, (1, 1, 3, 3), fmt="ND").ptr, sz.ptr, False, 0.0, 0.0,
+                  T(ops, (1, 1, 5, 5), fmt="ND").ptr)[0] == OK
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, T(ops, (1, 1, 5, 5), fmt="NHWC").ptr)[0] == INVALID
+
+
+def test_bicubic_backward_status(ops):
+    """image/upsample_bicubic2d_grad/tests/ut/op_host/op_api/test_aclnn_upsample_bicubic_2d_backward.cpp: float and
+    float16 succeed, every other dtype is invalid, N = 0 succeeds, 2-D / 5-D gradOut, a dtype mismatch and sizes that
+    disagree with the tensors are invalid."""
+    api = "aclnnUpsampleBicubic2dBackward"
+    g, out = T(ops, (1, 1, 2, 2)), T(ops, (1, 1, 3, 3))
+    osz, isz = IA(ops, [2, 2]), IA(ops, [1, 1, 3, 3])
+    st, ws = phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 2.0, 2.0, out.ptr)
+    assert st == OK and ws == 0
+    for args in ((None, osz.ptr, isz.ptr, out.ptr), (g.ptr, None, isz.ptr, out.ptr), (g.ptr, osz.ptr, None, out.ptr),
+                 (g.ptr, osz.ptr, isz.ptr, None)):
+        assert phase1(ops, api, args[0], args[1], args[2], False, 2.0, 2.0, args[3])[0] == NULLPTR
+    for dt, want in ((torch.float16, OK), (torch.bfloat16, OK), (torch.float64, INVALID), (torch.int32, INVALID),
+                     (torch.int64, INVALID), (torch.uint8, INVALID)):
+        assert phase1(ops, api, T(ops, (1, 1, 2, 2), dt).ptr, osz.ptr, isz.ptr, False, 2.0, 2.0,
+                      T(ops, (1, 1, 3, 3), dt).ptr)[0] == want
+    assert phase1(ops, api, T(ops, (0, 1, 2, 2)).ptr, osz.ptr, IA(ops, [0, 1, 3, 3]).ptr, False, 2.0, 2.0,
+                  T(ops, (0, 1, 3, 3)).ptr) == (OK, 0)
+    assert phase1(ops, api, T(ops, (2, 2)).ptr, osz.ptr, isz.ptr, False, 2.0, 2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (1, 1, 1, 2, 2)).ptr, osz.ptr, isz.ptr, False, 2.0, 2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 2.0, 2.0, T(ops, (1, 1, 3, 3), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, IA(ops, [2, 3]).ptr, isz.ptr, False, 2.0, 2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, IA(ops, [2]).ptr, isz.ptr, False, 2.0, 2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [1, 1, 3]).ptr, False, 2.0, 2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [1, 1, 3, 4]).ptr, False, 2.0, 2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [1, 1, 0, 3]).ptr, False, 2.0, 2.0, T(ops, (1, 1, 0, 3)).ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (1, 2, 2, 4), fmt="NHWC").ptr, osz.ptr, IA(ops, [1, 3, 3, 4]).ptr, True, 0.0, 0.0,
+                  T(ops, (1, 3, 3, 4), fmt="NHWC").ptr)[0] == OK
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 2.0, 2.0, T(ops, (1, 1, 3, 3), fmt="NHWC").ptr)[0] == INVALID
+
+
 def test_grid_sampler_status(ops):
     x, grid, out = T(ops, (2, 3, 6, 7)), T(ops, (2, 5, 4, 2), fmt="ND"), T(ops, (2, 3, 5, 4))
     call = lambda *a: phase1(ops, "aclnnGridSampler2D", *a)[0]  # noqa: E731

@@ -1,5 +1,5 @@
 """Replay of the reference's own test inputs (tests/golden/atk_replay.npz, made by tests/golden/make_golden.py
-<reference> replay): a seeded slice of the ST case matrices of the nine hot-path APIs plus the kernel-UT generator of
+<reference> replay): a seeded slice of the ST case matrices of the eleven APIs plus the kernel-UT generator of
 UpsampleBilinear2d, each with the torch CPU golden that the reference's executors compute.
 
 The CPU half holds the oracle to these goldens, the GPU half the library (through the C ABI). The bar is the one the
@@ -55,6 +55,9 @@ def run_case(m, backend, oracle):
         elif api == "UpsampleBilinear2d":
             got = back(backend.upsample_bilinear2d(t(x), size, align)) if gpu else rnd(oracle.bilinear2d_fwd(x, size, align))
             out["y"] = (got, GOLD[name + ".y"])
+        elif api == "UpsampleBicubic2d":
+            got = back(backend.upsample_bicubic2d(t(x), size, align)) if gpu else rnd(oracle.bicubic2d_fwd(x, size, align))
+            out["y"] = (got, GOLD[name + ".y"])
         elif api == "UpsampleBicubic2dAA":
             got = back(backend.upsample_bicubic2d_aa(t(x), size, align)) if gpu else rnd(oracle.bicubic_aa_fwd(x, size, align))
             out["y"] = (got, GOLD[name + ".y"])
@@ -68,6 +71,9 @@ def run_case(m, backend, oracle):
                     v2 = api.endswith("V2")
                     got = back(backend.upsample_bilinear2d_backward(t(g), size, shape, align, v2=v2)) if gpu else rnd(
                         oracle.bilinear2d_bwd(g, shape[2:], align, definition="dispatch"))
+                elif api == "UpsampleBicubic2dBackward":
+                    got = back(backend.upsample_bicubic2d_backward(t(g), size, shape, align)) if gpu else rnd(
+                        oracle.bicubic2d_bwd(g, shape[2:], align, definition="dispatch"))
                 else:
                     got = back(backend.upsample_bicubic2d_aa_grad(t(g), size, shape, align)) if gpu else rnd(
                         oracle.bicubic_aa_bwd(g, shape[2:], align))
