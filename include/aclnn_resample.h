@@ -120,6 +120,32 @@ ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTens
 ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGrad(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                                    aclrtStream stream);
 
+/* ---- UpsampleBilinear2dAA ----------------------------------------------------------------------------------
+ * Replaces image/upsample_bilinear2d_aa/op_host/op_api/aclnn_upsample_bilinear2d_aa.h:38-49 (implementation
+ * aclnn_upsample_bilinear2d_aa.cpp:184-252; kernel image/upsample_bilinear2d_aa/op_kernel/arch35/
+ * upsample_bilinear2d_aa_simt_base.h:30-91; scale / support upsample_bilinear2d_aa_tiling_arch35.cpp:104-154).
+ * NCHW (or ND) only; triangle filter, support `scale` when down-scaling. Same tables and kernels as
+ * UpsampleBicubic2dAA with the other filter. */
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dAAGetWorkspaceSize(const aclTensor* input, const aclIntArray* outputSize,
+                                                                bool alignCorners, double scalesH, double scalesW,
+                                                                aclTensor* out, uint64_t* workspaceSize,
+                                                                aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dAA(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                aclrtStream stream);
+
+/* Replaces image/upsample_bilinear2d_aa_backward/op_host/op_api/aclnn_upsample_bilinear2d_aa_backward.h:40-56
+ * (implementation aclnn_upsample_bilinear2d_aa_backward.cpp:179-250; kernels
+ * upsample_bilinear2d_aa_backward_simt_base.h:74-126 atomic, :128-171 deterministic). */
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dAABackwardGetWorkspaceSize(const aclTensor* gradOutput,
+                                                                        const aclIntArray* outputSize,
+                                                                        const aclIntArray* inputSize,
+                                                                        bool alignCorners, double scalesH,
+                                                                        double scalesW, aclTensor* out,
+                                                                        uint64_t* workspaceSize,
+                                                                        aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleBilinear2dAABackward(void* workspace, uint64_t workspaceSize,
+                                                        aclOpExecutor* executor, aclrtStream stream);
+
 /* ---- UpsampleBicubic2d (no antialiasing) ------------------------------------------------------------------
  * Replaces image/upsample_bicubic2d/op_host/op_api/aclnn_upsample_bicubic_2d.h:25-34 (implementation
  * aclnn_upsample_bicubic_2d.cpp:233-330, regbase branch; kernel
@@ -184,7 +210,8 @@ ACLNN_API aclnnStatus aclnnGridSampler2DBackward(void* workspace, uint64_t works
  * 1 nearest backward ranges (i0 = start[inSize], i1 = end[inSize]);
  * 2 bilinear forward (i0 = lo[outSize], i1 = hi[outSize], f0 = delta[outSize]);
  * 3 bicubic-AA forward (i0 = xmin[outSize], i1 = xsize[outSize], f0 = weights[outSize * taps], taps returned
- *   through *tapsOut; pass f0 == NULL to query taps only).
+ *   through *tapsOut; pass f0 == NULL to query taps only);
+ * 4 bilinear-AA forward, laid out as kind 3.
  * Synchronises the device. Returns 0 or an aclnn status. */
 ACLNN_API aclnnStatus opscvDebugAxisTable(int32_t kind, int64_t inSize, int64_t outSize, int32_t alignCorners,
                                           float userScale, int32_t* i0, int32_t* i1, float* f0, int32_t* tapsOut);

@@ -10,7 +10,8 @@ __all__ = [
     "AclnnError", "acl_tensor", "int_array", "bool_array", "two_phase", "set_deterministic", "set_backward_algo",
     "launch_count", "reset_launch_count", "async_copy_timeouts", "last_error", "debug_axis_table", "upsample_nearest2d",
     "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_no_alloc",
-    "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bicubic2d_aa",
+    "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bilinear2d_aa",
+    "upsample_bilinear2d_aa_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
 ]
 
@@ -129,7 +130,7 @@ def debug_axis_table(kind, in_size, out_size, align=False, user_scale=0.0):
     """Index / weight tables as the device builds them, copied to numpy arrays (see opscvDebugAxisTable)."""
     import numpy as np
     L = lib()
-    kinds = {"nearest_fwd": 0, "nearest_bwd": 1, "bilinear": 2, "bicubic_aa": 3}
+    kinds = {"nearest_fwd": 0, "nearest_bwd": 1, "bilinear": 2, "bicubic_aa": 3, "bilinear_aa": 4}
     k = kinds[kind]
     n = in_size if k == 1 else out_size
     i0 = np.zeros(n, dtype=np.int32)
@@ -138,7 +139,7 @@ def debug_axis_table(kind, in_size, out_size, align=False, user_scale=0.0):
     f0 = None
     if k == 2:
         f0 = np.zeros(n, dtype=np.float32)
-    if k == 3:
+    if k >= 3:
         status = L.opscvDebugAxisTable(k, in_size, out_size, int(align), user_scale, None, None, None,
                                        ctypes.byref(taps))
         if status != 0:
@@ -229,6 +230,24 @@ def upsample_bicubic2d_aa_grad(grad_out, out_hw, input_size, align_corners=False
     osz, isz = int_array(out_hw), int_array(input_size)
     two_phase("aclnnUpsampleBicubic2dAAGrad", [tg.ptr, osz.ptr, isz.ptr, bool(align_corners), float(scales[0]),
                                                float(scales[1]), ty.ptr], grad_out.device, workspace)
+    return out
+
+
+def upsample_bilinear2d_aa(x, out_hw, align_corners=False, scales=(0.0, 0.0), out=None, workspace=None):
+    out = torch.empty(_out_shape(x, out_hw, "NCHW"), dtype=x.dtype, device=x.device) if out is None else out
+    tx, ty, size = acl_tensor(x, "NCHW"), acl_tensor(out, "NCHW"), int_array(out_hw)
+    two_phase("aclnnUpsampleBilinear2dAA", [tx.ptr, size.ptr, bool(align_corners), float(scales[0]), float(scales[1]),
+                                            ty.ptr], x.device, workspace)
+    return out
+
+
+def upsample_bilinear2d_aa_backward(grad_out, out_hw, input_size, align_corners=False, scales=(0.0, 0.0), out=None,
+                                    workspace=None):
+    out = torch.empty(tuple(input_size), dtype=grad_out.dtype, device=grad_out.device) if out is None else out
+    tg, ty = acl_tensor(grad_out, "NCHW"), acl_tensor(out, "NCHW")
+    osz, isz = int_array(out_hw), int_array(input_size)
+    two_phase("aclnnUpsampleBilinear2dAABackward", [tg.ptr, osz.ptr, isz.ptr, bool(align_corners), float(scales[0]),
+                                                    float(scales[1]), ty.ptr], grad_out.device, workspace)
     return out
 
 

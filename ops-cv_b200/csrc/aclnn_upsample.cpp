@@ -366,23 +366,29 @@ struct AAGeom {
     float scale, inv, support;
     int32_t taps;
 };
-// image/upsample_bicubic2d_aa/op_host/upsample_bicubic2d_aa_tiling_arch35.cpp:139-168 (forward: originalScale is the
-// API's scales value) and image/upsample_bicubic2d_aa_grad/op_host/upsample_bicubic2d_aa_grad_tiling_arch35.cpp:158-183
-// (backward: the API passes float(1/scales), used as the scale itself). `in` = forward input extent.
-AAGeom MakeAAGeom(int64_t in, int64_t out, bool align, double userScale, bool backward)
+// Scale, inverse scale, support and widest window of one axis. `in` = forward input extent.
+// Cubic (filter 0): image/upsample_bicubic2d_aa/op_host/upsample_bicubic2d_aa_tiling_arch35.cpp:139-168 (forward:
+// originalScale is the API's scales value, used as 1.0f / float(scales)) and
+// image/upsample_bicubic2d_aa_grad/op_host/upsample_bicubic2d_aa_grad_tiling_arch35.cpp:158-183 (backward: the API
+// passes float(1.0 / scales), used as the scale itself); support 2 * scale when down-scaling, else 2.
+// Triangle (filter 1): image/upsample_bilinear2d_aa/op_host/upsample_bilinear2d_aa_tiling_arch35.cpp:125-154 and
+// image/upsample_bilinear2d_aa_backward/op_host/upsample_bilinear2d_aa_backward_tiling_arch35.cpp:143-171: both
+// directions receive float(1.0 / scales) and use it as the scale; support scale when down-scaling, else 1.
+AAGeom MakeAAGeom(int64_t in, int64_t out, bool align, double userScale, bool reciprocalInDouble, int filter = 0)
 {
     AAGeom g;
     if (align) {
         g.scale = out > 1 ? static_cast<float>(in - 1) / static_cast<float>(out - 1) : 0.0f;
-    } else if (!backward) {
+    } else if (!reciprocalInDouble) {
         const float original = userScale > 0 ? static_cast<float>(userScale) : 0.0f;
         g.scale = original > 0.0f ? 1.0f / original : static_cast<float>(in) / static_cast<float>(out);
     } else {
         const float original = userScale > 0 ? static_cast<float>(1.0 / userScale) : 0.0f;
         g.scale = original > 0.0f ? original : static_cast<float>(in) / static_cast<float>(out);
     }
+    const float unit = filter == 0 ? 2.0f : 1.0f;
     g.inv = g.scale >= 1.0f ? 1.0f / g.scale : 1.0f;
-    g.support = g.scale >= 1.0f ? 2.0f * g.scale : 2.0f;
+    g.support = g.scale >= 1.0f ? unit * g.scale : unit;
     // window = floor(c + s + 0.5) - floor(c - s + 0.5) <= 2s + 1
     int64_t taps = static_cast<int64_t>(std::floor(2.0 * static_cast<double>(g.support))) + 2;
     taps = taps > in ? in : taps;
@@ -771,13 +777,14 @@ aclnnStatus aclnnUpsampleBilinear2dBackwardV2(void* workspace, uint64_t workspac
 }
 
 // ===============================================================================================================
-// image/upsample_bicubic2d_aa/op_host/op_api/aclnn_upsample_bicubic2d_aa.cpp:145-162 (CheckParams), :59-124
-aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const aclIntArray* outputSize,
-                                                     const bool alignCorners, const double scalesH,
-                                                     const double scalesW, aclTensor* out, uint64_t* workspaceSize,
-                                                     aclOpExecutor** executor)
+// The two anti-aliased forwards share one planner. filter 0: aclnnUpsampleBicubic2dAA
+// (image/upsample_bicubic2d_aa/op_host/op_api/aclnn_upsample_bicubic2d_aa.cpp:145-162 CheckParams, :59-124);
+// filter 1: aclnnUpsampleBilinear2dAA (image/upsample_bilinear2d_aa/op_host/op_api/aclnn_upsample_bilinear2d_aa.cpp
+// :155-182 CheckParams: the same checks plus negative scales; :214-219 scale passing).
+static aclnnStatus PlanAAForward(const char* api, int filter, const aclTensor* x, const aclIntArray* outputSize,
+                                 const bool alignCorners, const double scalesH, const double scalesW, aclTensor* out,
+                                 uint64_t* workspaceSize, aclOpExecutor** executor)
 {
-    static const char* api = "aclnnUpsampleBicubic2dAA";
     if (workspaceSize == nullptr || executor == nullptr) { // OP_CHECK_COMM_INPUT (:168)
         return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
     }
@@ -800,6 +807,9 @@ aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const a
     }
     if (out->dims.size() != 4) {
         return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out must be 4-D, got %zu-D", api, out->dims.size());
+    }
+    if (filter == 1 && (scalesH < 0 || scalesW < 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales cannot be negative (w %f, h %f)", api, scalesW, scalesH);
     }
     const int64_t inH = x->dims[2], inW = x->dims[3], outH = outputSize->v[0], outW = outputSize->v[1];
     if (!(inH > 0 && inW > 0 && outH > 0 && outW > 0)) {
@@ -830,8 +840,8 @@ aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const a
         return EmptySuccess(api, workspaceSize, executor);
     }
     Geom gi{x->dims[0], x->dims[1], inH, inW}, go{x->dims[0], x->dims[1], outH, outW};
-    const AAGeom ah = MakeAAGeom(inH, outH, alignCorners, scalesH, false);
-    const AAGeom aw = MakeAAGeom(inW, outW, alignCorners, scalesW, false);
+    const AAGeom ah = MakeAAGeom(inH, outH, alignCorners, scalesH, filter == 1, filter);
+    const AAGeom aw = MakeAAGeom(inW, outW, alignCorners, scalesW, filter == 1, filter);
     if (AAIsCopy(gi, go, ah, aw)) {
         return PlanCopy(api, x, out, workspaceSize, executor);
     }
@@ -852,7 +862,7 @@ aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const a
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
         const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
-        cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, false, s);
+        cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, false, filter, s);
         if (e != cudaSuccess) {
             return e;
         }
@@ -871,6 +881,15 @@ aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const a
     return ACLNN_SUCCESS;
 }
 
+aclnnStatus aclnnUpsampleBicubic2dAAGetWorkspaceSize(const aclTensor* x, const aclIntArray* outputSize,
+                                                     const bool alignCorners, const double scalesH,
+                                                     const double scalesW, aclTensor* out, uint64_t* workspaceSize,
+                                                     aclOpExecutor** executor)
+{
+    return PlanAAForward("aclnnUpsampleBicubic2dAA", 0, x, outputSize, alignCorners, scalesH, scalesW, out,
+                         workspaceSize, executor);
+}
+
 aclnnStatus aclnnUpsampleBicubic2dAA(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                      aclrtStream stream)
 {
@@ -878,14 +897,16 @@ aclnnStatus aclnnUpsampleBicubic2dAA(void* workspace, uint64_t workspaceSize, ac
 }
 
 // ===============================================================================================================
-// image/upsample_bicubic2d_aa_grad/op_host/op_api/aclnn_upsample_bicubic2d_aa_grad.cpp:159-181 (CheckParams):
-// null, dtype, scales, shape, N/C, elements
-aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOutput, const aclIntArray* outputSize,
-                                                         const aclIntArray* inputSize, bool alignCorners,
-                                                         double scalesH, double scalesW, aclTensor* out,
-                                                         uint64_t* workspaceSize, aclOpExecutor** executor)
+// The two anti-aliased backwards share one planner. filter 0: aclnnUpsampleBicubic2dAAGrad
+// (image/upsample_bicubic2d_aa_grad/op_host/op_api/aclnn_upsample_bicubic2d_aa_grad.cpp:159-181 CheckParams: null,
+// dtype, scales, shape, N/C, elements); filter 1: aclnnUpsampleBilinear2dAABackward
+// (image/upsample_bilinear2d_aa_backward/op_host/op_api/aclnn_upsample_bilinear2d_aa_backward.cpp:153-177, the same
+// checks; :209-213 scale passing).
+static aclnnStatus PlanAABackward(const char* api, int filter, const aclTensor* gradOutput,
+                                  const aclIntArray* outputSize, const aclIntArray* inputSize, bool alignCorners,
+                                  double scalesH, double scalesW, aclTensor* out, uint64_t* workspaceSize,
+                                  aclOpExecutor** executor)
 {
-    static const char* api = "aclnnUpsampleBicubic2dAAGrad";
     if (workspaceSize == nullptr || executor == nullptr) {
         return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
     }
@@ -945,8 +966,8 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
         return EmptySuccess(api, workspaceSize, executor);
     }
     Geom gi{outN, outC, inH, inW}, gg{outN, outC, outH, outW};
-    const AAGeom ah = MakeAAGeom(inH, outH, alignCorners, scalesH, true);
-    const AAGeom aw = MakeAAGeom(inW, outW, alignCorners, scalesW, true);
+    const AAGeom ah = MakeAAGeom(inH, outH, alignCorners, scalesH, true, filter);
+    const AAGeom aw = MakeAAGeom(inW, outW, alignCorners, scalesW, true, filter);
     if (AAIsCopy(gi, gg, ah, aw)) {
         return PlanCopy(api, gradOutput, out, workspaceSize, executor);
     }
@@ -965,14 +986,15 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
     // With scale == 0 (align_corners and a single output pixel) the reference's two backward kernels disagree on
     // the filter centre: the default (atomic) kernel uses 0.5, the deterministic one keeps the forward's 0
     // (upsample_bicubic2d_aa_grad_simt_base.h:38 vs ..._simt_base_deter.h:96). Follow whichever the mode selects.
-    const bool bwdCentre = GetDeterministic() == 0;
+    // The triangle-filter kernels (upsample_bilinear2d_aa_backward_simt_base.h:88,146) keep scale * (i + 0.5) in both.
+    const bool bwdCentre = filter == 0 && GetDeterministic() == 0;
     if (atomic) {
         const int64_t elems = gi.n * gi.c * gi.h * gi.w;
         const bool needAcc = dt != Dt::F32;
         const uint64_t accOff = needAcc ? ws.Alloc(static_cast<uint64_t>(elems) * 4) : 0;
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
-            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, bwdCentre, s);
+            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, bwdCentre, filter, s);
             if (e != cudaSuccess) {
                 return e;
             }
@@ -986,7 +1008,7 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
         ex->steps.push_back([=](char* w, cudaStream_t s) {
             const AAAxis th = AAAt(w, oh, ah.taps), tw = AAAt(w, ow, aw.taps);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
-            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, bwdCentre, s);
+            cudaError_t e = BuildAATables(gh, gw, ah.inv, aw.inv, ah.support, aw.support, th, tw, bwdCentre, filter, s);
             if (e != cudaSuccess) {
                 return e;
             }
@@ -1005,10 +1027,51 @@ aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOu
     return ACLNN_SUCCESS;
 }
 
+aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTensor* gradOutput, const aclIntArray* outputSize,
+                                                         const aclIntArray* inputSize, bool alignCorners,
+                                                         double scalesH, double scalesW, aclTensor* out,
+                                                         uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    return PlanAABackward("aclnnUpsampleBicubic2dAAGrad", 0, gradOutput, outputSize, inputSize, alignCorners, scalesH,
+                          scalesW, out, workspaceSize, executor);
+}
+
 aclnnStatus aclnnUpsampleBicubic2dAAGrad(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                          aclrtStream stream)
 {
     return RunExecutor("aclnnUpsampleBicubic2dAAGrad", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+aclnnStatus aclnnUpsampleBilinear2dAAGetWorkspaceSize(const aclTensor* input, const aclIntArray* outputSize,
+                                                      bool alignCorners, double scalesH, double scalesW,
+                                                      aclTensor* out, uint64_t* workspaceSize,
+                                                      aclOpExecutor** executor)
+{
+    return PlanAAForward("aclnnUpsampleBilinear2dAA", 1, input, outputSize, alignCorners, scalesH, scalesW, out,
+                         workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleBilinear2dAA(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                      aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBilinear2dAA", workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus aclnnUpsampleBilinear2dAABackwardGetWorkspaceSize(const aclTensor* gradOutput,
+                                                              const aclIntArray* outputSize,
+                                                              const aclIntArray* inputSize, bool alignCorners,
+                                                              double scalesH, double scalesW, aclTensor* out,
+                                                              uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    return PlanAABackward("aclnnUpsampleBilinear2dAABackward", 1, gradOutput, outputSize, inputSize, alignCorners,
+                          scalesH, scalesW, out, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleBilinear2dAABackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                              aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleBilinear2dAABackward", workspace, workspaceSize, executor, stream);
 }
 
 // ===============================================================================================================
@@ -1223,13 +1286,16 @@ aclnnStatus opscvDebugAxisTable(int32_t kind, int64_t inSize, int64_t outSize, i
     }
     const int32_t in = static_cast<int32_t>(inSize), out = static_cast<int32_t>(outSize);
     AAGeom aa{};
+    int aaFilter = 0;
     int64_t nInt = 0, nFloat = 0;
     switch (kind) {
         case 0: nInt = out; break;
         case 1: nInt = in; break;
         case 2: nInt = out; nFloat = out; break;
         case 3:
-            aa = MakeAAGeom(in, out, alignCorners != 0, userScale, false);
+        case 4:
+            aaFilter = kind == 4 ? 1 : 0;
+            aa = MakeAAGeom(in, out, alignCorners != 0, userScale, aaFilter == 1, aaFilter);
             if (tapsOut != nullptr) {
                 *tapsOut = aa.taps;
             }
@@ -1306,7 +1372,7 @@ aclnnStatus opscvDebugAxisTable(int32_t kind, int64_t inSize, int64_t outSize, i
             }
             if (e == cudaSuccess) {
                 e = BuildAATables(g, g, aa.inv, aa.inv, aa.support, aa.support, AAAxis{d0, d1, df, aa.taps},
-                                  AAAxis{s0, s1, sf, aa.taps}, false, nullptr);
+                                  AAAxis{s0, s1, sf, aa.taps}, false, aaFilter, nullptr);
             }
             if (e == cudaSuccess) {
                 e = cudaDeviceSynchronize();

@@ -55,9 +55,10 @@ cudaError_t BuildLerpBwdTablesAndRanges(AxisGeom h, AxisGeom w, bool halfPixel, 
                                         RangeAxis rw, cudaStream_t s);
 cudaError_t BuildLerpBwdRanges(AxisGeom h, AxisGeom w, LerpAxis th, LerpAxis tw, RangeAxis rh, RangeAxis rw,
                                cudaStream_t s);
-// backward = true: centre rule of the reference's backward kernel (0.5 when the scale is 0).
+// backward = true: centre rule of the reference's cubic backward kernel (0.5 when the scale is 0).
+// filter: 0 Keys cubic (UpsampleBicubic2dAA), 1 triangle (UpsampleBilinear2dAA).
 cudaError_t BuildAATables(AxisGeom h, AxisGeom w, float invH, float invW, float supH, float supW, AAAxis th,
-                          AAAxis tw, bool backward, cudaStream_t s);
+                          AAAxis tw, bool backward, int filter, cudaStream_t s);
 // For every forward-input index y: [start, end) = output indices whose window covers y.
 cudaError_t BuildAABwdRanges(AxisGeom h, AxisGeom w, AAAxis th, AAAxis tw, RangeAxis rh, RangeAxis rw,
                              cudaStream_t s);

@@ -192,9 +192,21 @@ __device__ __forceinline__ float CubicFilterAA(float m)
     return 0.0f;
 }
 
-// upsample_bicubic2d_aa_simt_base.h:70-124: window [xmin, xmin+xsize), weights normalised by their sum.
+// image/upsample_bilinear2d_aa/op_kernel/arch35/upsample_bilinear2d_aa_simt_base.h:30-37 (triangle)
+__device__ __forceinline__ float TriangleFilterAA(float m)
+{
+    m = fabsf(m);
+    return m < 1.0f ? Sub(1.0f, m) : 0.0f;
+}
+__device__ __forceinline__ float FilterAA(int filter, float m)
+{
+    return filter == 0 ? CubicFilterAA(m) : TriangleFilterAA(m);
+}
+
+// upsample_bicubic2d_aa_simt_base.h:70-124 and upsample_bilinear2d_aa_simt_base.h:52-88: window
+// [xmin, xmin+xsize), weights normalised by their sum. filter: 0 Keys cubic, 1 triangle.
 __global__ void AATableKernel(AxisGeom gh, AxisGeom gw, float invH, float invW, float supH, float supW, AAAxis th,
-                              AAAxis tw, int backward)
+                              AAAxis tw, int backward, int filter)
 {
     const bool isH = blockIdx.y == 0;
     const AxisGeom g = isH ? gh : gw;
@@ -227,14 +239,14 @@ __global__ void AATableKernel(AxisGeom gh, AxisGeom gw, float invH, float invW, 
     float total = 0.0f;
     for (int32_t j = 0; j < size; ++j) {
         const float dist = Mul(Add(Sub(static_cast<float>(lo + j), center), 0.5f), inv);
-        total = Add(total, CubicFilterAA(dist));
+        total = Add(total, FilterAA(filter, dist));
     }
     float* w = t.w + static_cast<int64_t>(i) * t.taps;
     for (int32_t j = 0; j < t.taps; ++j) {
         float wj = 0.0f;
         if (j < size) {
             const float dist = Mul(Add(Sub(static_cast<float>(lo + j), center), 0.5f), inv);
-            wj = CubicFilterAA(dist);
+            wj = FilterAA(filter, dist);
             if (total != 0.0f) {
                 wj = Div(wj, total);
             }
@@ -320,10 +332,10 @@ cudaError_t BuildLerpBwdTablesAndRanges(AxisGeom h, AxisGeom w, bool halfPixel, 
 }
 
 cudaError_t BuildAATables(AxisGeom h, AxisGeom w, float invH, float invW, float supH, float supW, AAAxis th,
-                          AAAxis tw, bool backward, cudaStream_t s)
+                          AAAxis tw, bool backward, int filter, cudaStream_t s)
 {
     AATableKernel<<<TableGrid(h.out, w.out), kTableThreads, 0, s>>>(h, w, invH, invW, supH, supW, th, tw,
-                                                                    backward ? 1 : 0);
+                                                                    backward ? 1 : 0, filter);
     CountLaunch();
     return cudaGetLastError();
 }

@@ -199,6 +199,39 @@ def bicubic_aa_bwd(go, in_hw, align=False, scales=(0.0, 0.0), definition="scatte
     return gi
 
 
+def bilinear_aa_table(in_size, out_size, align, user_scale=0.0):
+    """(xmin, xsize, weights[out, taps]) of UpsampleBilinear2dAA for one axis."""
+    fn = lib().orc_bilinear_aa_table
+    fn.restype = ctypes.c_int32
+    taps = max(1, fn(I64(in_size), I64(out_size), I32(int(align)), F32(user_scale), None, None, None, I32(0)))
+    xmin, pm = _i32(out_size)
+    xsize, ps = _i32(out_size)
+    w = np.zeros((out_size, taps), dtype=np.float32)
+    fn(I64(in_size), I64(out_size), I32(int(align)), F32(user_scale), pm, ps, w.ctypes.data_as(ctypes.c_void_p),
+       I32(taps))
+    return xmin, xsize, w
+
+
+def bilinear_aa_fwd(x, out_hw, align=False, scales=(0.0, 0.0)):
+    x, px = _f(x)
+    n, c, h, w = x.shape
+    y = np.empty((n, c, out_hw[0], out_hw[1]), dtype=np.float32)
+    lib().orc_bilinear_aa_fwd(px, y.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(h), I64(w), I64(out_hw[0]),
+                              I64(out_hw[1]), I32(int(align)), F32(scales[0]), F32(scales[1]))
+    return y
+
+
+def bilinear_aa_bwd(go, in_hw, align=False, scales=(0.0, 0.0), definition="scatter"):
+    """definition: "scatter" (the atomic kernel run serially) or "gather" (the deterministic kernel)."""
+    go, pg = _f(go)
+    n, c, ho, wo = go.shape
+    gi = np.empty((n, c, in_hw[0], in_hw[1]), dtype=np.float32)
+    fn = lib().orc_bilinear_aa_bwd_scatter if definition == "scatter" else lib().orc_bilinear_aa_bwd_gather
+    fn(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_hw[0]), I64(in_hw[1]), I64(ho), I64(wo),
+       I32(int(align)), F32(scales[0]), F32(scales[1]))
+    return gi
+
+
 def bicubic2d_fwd_schedule(in_hw, out_hw, align=False, scales=(0.0, 0.0)):
     """The schedule the reference's tiling picks for UpsampleBicubic2d: "general", "copy", "one_input_pixel",
     "one_output_pixel" or "integer_positions"."""

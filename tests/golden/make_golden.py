@@ -162,7 +162,10 @@ ATK = {
     "GridSampler2DBackward": ("image/grid_sampler2_d_grad/tests/st/aclnnGridSampler2DBackward/atk_aclnnGridSampler2DBackward.json", "grid_bwd"),
     "UpsampleBicubic2d": ("image/upsample_bicubic2d/tests/st/aclnnUpsampleBicubic2d/atk_aclnnUpsampleBicubic2d.json", "interp_fwd"),
     "UpsampleBicubic2dBackward": ("image/upsample_bicubic2d_grad/tests/st/aclnnUpsampleBicubic2dBackward/atk_aclnnUpsampleBicubic2dBackward.json", "interp_bwd"),
+    "UpsampleBilinear2dAA": ("image/upsample_bilinear2d_aa/tests/st/aclnnUpsampleBilinear2dAA/atk_aclnnUpsampleBilinear2dAA.json", "interp_fwd"),
+    "UpsampleBilinear2dAABackward": ("image/upsample_bilinear2d_aa_backward/tests/st/aclnnUpsampleBilinear2dAABackward/atk_aclnnUpsampleBilinear2dAABackward.json", "interp_bwd"),
 }
+SCALE_FACTOR_APIS = ("UpsampleBilinear2dAA", "UpsampleBilinear2dAABackward")
 TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
 CASES_PER_API = 20
 MAX_PLANE = 1000   # H * W of any tensor of a kept case
@@ -212,26 +215,37 @@ def replay_atk(data, index):
             name = f"atk.{api}.{case['id']}"
             if kind in ("interp_fwd", "interp_bwd"):
                 _, dt, shape, spec = f["input"]
-                if dt not in TORCH_DT or len(shape) != 4 or "size" not in f:
+                # cases given by scale_factor are replayed for the APIs added after the first fixture was cut (a
+                # change for the others would reshuffle their kept cases)
+                by_factor = "size" not in f and "scale_factor" in f and api in SCALE_FACTOR_APIS
+                if dt not in TORCH_DT or len(shape) != 4 or ("size" not in f and not by_factor):
                     continue
                 n, c, h, w = min(shape[0], 2), min(shape[1], 3), shape[2], shape[3]
-                oh, ow = f["size"]
+                if by_factor:
+                    sf = [float(v) for v in f["scale_factor"]]
+                    oh, ow = int(np.floor(h * sf[0])), int(np.floor(w * sf[1]))
+                else:
+                    oh, ow = f["size"]
                 if min(n, c, h, w, oh, ow) < 1 or h * w > MAX_PLANE or oh * ow > MAX_PLANE:
                     continue
                 x = draw(rng, (n, c, h, w), spec, TORCH_DT[dt])
                 if x is None:
                     continue
                 mode = f.get("mode", "nearest")
-                kw = {"size": (oh, ow), "mode": mode}
+                kw = {"scale_factor": sf, "recompute_scale_factor": False, "mode": mode} if by_factor else {
+                    "size": (oh, ow), "mode": mode}
                 if mode != "nearest":
                     kw["align_corners"] = as_bool(f.get("align_corners", False))
                 if as_bool(f.get("antialias", False)):
                     kw["antialias"] = True
                 xg = x.clone().requires_grad_(kind == "interp_bwd")
                 y = F.interpolate(xg, **kw)
+                assert tuple(y.shape[2:]) == (oh, ow)
                 data[name + ".x"] = x.numpy() if dt == "fp32" else x.to(torch.float16 if dt == "fp16" else torch.float32).numpy()
                 meta = {"api": api, "dtype": dt, "shape": [n, c, h, w], "size": [oh, ow], "mode": mode,
                         "align": kw.get("align_corners", False), "aa": kw.get("antialias", False)}
+                if by_factor:
+                    meta["scales"] = sf
                 if kind == "interp_fwd":
                     data[name + ".y"] = y.detach().numpy()
                 else:

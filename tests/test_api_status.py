@@ -171,6 +171,39 @@ def test_bicubic_aa_forward_status(ops):
                   T(ops, (2, 3, 7, 9), fmt="ND").ptr)[0] == OK
 
 
+def test_bilinear_aa_status(ops):
+    """aclnnUpsampleBilinear2dAA / ...Backward: the checks of the bicubic-AA pair (NCHW or ND only, one dtype, 4-D,
+    sizes > 0) plus negative scales in the forward."""
+    api = "aclnnUpsampleBilinear2dAA"
+    x, y, sz = T(ops, (2, 3, 32, 32)), T(ops, (2, 3, 7, 9)), IA(ops, [7, 9])
+    st, ws = phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, y.ptr)
+    assert st == OK and ws > 0
+    assert phase1(ops, api, None, sz.ptr, False, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, None, False, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sz.ptr, False, -1.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, IA(ops, [7, 8]).ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, IA(ops, [0, 9]).ptr, False, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, T(ops, (2, 3, 7, 9), torch.bfloat16).ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 3, 32, 32), torch.int32).ptr, sz.ptr, False, 0.0, 0.0,
+                  T(ops, (2, 3, 7, 9), torch.int32).ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 32, 32, 3), fmt="NHWC").ptr, sz.ptr, False, 0.0, 0.0,
+                  T(ops, (2, 7, 9, 3), fmt="NHWC").ptr)[0] == INVALID
+    api = "aclnnUpsampleBilinear2dAABackward"
+    g, out = T(ops, (2, 3, 7, 9)), T(ops, (2, 3, 32, 32))
+    osz, isz = IA(ops, [7, 9]), IA(ops, [2, 3, 32, 32])
+    st, ws = phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, out.ptr)
+    assert st == OK and ws > 0
+    assert phase1(ops, api, None, osz.ptr, isz.ptr, False, 0.0, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, None, False, 0.0, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, -2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [2, 3, 32]).ptr, False, 0.0, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, IA(ops, [7, 8]).ptr, isz.ptr, False, 0.0, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, T(ops, (2, 3, 32, 32), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, T(ops, (2, 4, 32, 32)).ptr)[0] == INVALID
+
+
 def test_bicubic_forward_status(ops):
     """image/upsample_bicubic2d/tests/ut/op_host/op_api/test_aclnn_upsample_bicubic_2d.cpp:27-310: one null case per
     pointer, float / float16 / bfloat16 succeed, int64 and mixed dtypes are invalid, N = 0 succeeds, C = 0, H = 0,
