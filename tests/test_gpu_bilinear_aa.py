@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from test_gpu_parity import AA_SHAPES, DTYPES, check, gen, quant
+from test_gpu_parity import AA_SHAPES, DTYPES, check, check_dispatched, gen, quant
 
 pytestmark = pytest.mark.gpu
 
@@ -52,8 +52,13 @@ def test_bilinear_aa_backward(ops, oracle, dev, dtype, align, shape, algo):
         ops.set_backward_algo("gather")
     scatter = oracle.bilinear_aa_bwd(g32, (hi, wi), align, definition="scatter")
     gather = oracle.bilinear_aa_bwd(g32, (hi, wi), align, definition="gather")
-    check(gi, scatter, dtype)
-    check(gi, gather, dtype)   # the reference's two kernels add the same terms
+    # the reference's two kernels add the same terms; a 16-bit result that cancels to nearly zero is held to the
+    # absolute bar (its ulp is far below the rounding of the fp32 sum)
+    if dtype == torch.float32:
+        check(gi, scatter, dtype)
+        check(gi, gather, dtype)
+    else:
+        check_dispatched(gi, scatter, gather, dtype)
     ops.set_deterministic(True)
     try:
         gd = ops.upsample_bilinear2d_aa_backward(g.to(dev), (ho, wo), (n, c, hi, wi), align)
@@ -61,7 +66,10 @@ def test_bilinear_aa_backward(ops, oracle, dev, dtype, align, shape, algo):
     finally:
         ops.set_deterministic(False)
     assert torch.equal(gd, gd2)
-    check(gd, gather, dtype)
+    if dtype == torch.float32:
+        check(gd, gather, dtype)
+    else:
+        check_dispatched(gd, gather, scatter, dtype)
 
 
 def test_bilinear_aa_user_scales_and_copy(ops, oracle, dev):
