@@ -120,6 +120,31 @@ ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGradGetWorkspaceSize(const aclTens
 ACLNN_API aclnnStatus aclnnUpsampleBicubic2dAAGrad(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                                    aclrtStream stream);
 
+/* ---- UpsampleNearestExact2d -------------------------------------------------------------------------------
+ * Replaces image/upsample_nearest/op_host/op_api/aclnn_upsample_nearest_exact2d.h:42-60 (implementation
+ * aclnn_upsample_nearest_exact2d.cpp:284-340, regbase branch: ResizeNearestNeighborV2 with half_pixel_centers = true;
+ * index image/resize_nearest_neighbor_v2/op_kernel/arch35/resize_nearest_neighbor_v2_simt.h:115-123:
+ * src = min(floor((dst + 0.5) * scale), in - 1)). NCHW, NHWC or ND. Same kernels as UpsampleNearest2d with the
+ * other index table. */
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                                  double scalesH, double scalesW, aclTensor* out,
+                                                                  uint64_t* workspaceSize, aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                  aclrtStream stream);
+
+/* Replaces image/upsample_nearest_exact2d_grad/op_host/op_api/aclnn_upsample_nearest_exact2d_backward.h:39-56
+ * (implementation aclnn_upsample_nearest_exact2d_backward.cpp:178-240; kernel
+ * op_kernel/arch35/upsample_nearest_exact2d_grad_simt_base.h:33-139: grad_input[y] sums the grads window
+ * [ceil(y * s - 0.5), ceil((y + 1) * s - 0.5)) in fp32). NCHW or ND. */
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact2dBackwardGetWorkspaceSize(const aclTensor* gradOutput,
+                                                                          const aclIntArray* outputSize,
+                                                                          const aclIntArray* inputSize,
+                                                                          double scalesH, double scalesW,
+                                                                          aclTensor* out, uint64_t* workspaceSize,
+                                                                          aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact2dBackward(void* workspace, uint64_t workspaceSize,
+                                                          aclOpExecutor* executor, aclrtStream stream);
+
 /* ---- UpsampleBilinear2dAA ----------------------------------------------------------------------------------
  * Replaces image/upsample_bilinear2d_aa/op_host/op_api/aclnn_upsample_bilinear2d_aa.h:38-49 (implementation
  * aclnn_upsample_bilinear2d_aa.cpp:184-252; kernel image/upsample_bilinear2d_aa/op_kernel/arch35/

@@ -69,6 +69,10 @@ SYMBOLS = {
     "aclnnUpsampleBicubic2dAA": _PHASE2,
     "aclnnUpsampleBicubic2dAAGradGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleBicubic2dAAGrad": _PHASE2,
+    "aclnnUpsampleNearestExact2dGetWorkspaceSize": (_I32, [_P, _P, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearestExact2d": _PHASE2,
+    "aclnnUpsampleNearestExact2dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearestExact2dBackward": _PHASE2,
     "aclnnUpsampleBilinear2dAAGetWorkspaceSize": (_I32, [_P, _P, _B, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleBilinear2dAA": _PHASE2,
     "aclnnUpsampleBilinear2dAABackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _P, _PU64, _PP]),

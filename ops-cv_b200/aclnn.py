@@ -11,7 +11,7 @@ __all__ = [
     "launch_count", "reset_launch_count", "async_copy_timeouts", "last_error", "debug_axis_table", "upsample_nearest2d",
     "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_no_alloc",
     "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bilinear2d_aa",
-    "upsample_bilinear2d_aa_backward", "upsample_bicubic2d_aa",
+    "upsample_bilinear2d_aa_backward", "upsample_nearest_exact2d", "upsample_nearest_exact2d_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
 ]
 
@@ -230,6 +230,23 @@ def upsample_bicubic2d_aa_grad(grad_out, out_hw, input_size, align_corners=False
     osz, isz = int_array(out_hw), int_array(input_size)
     two_phase("aclnnUpsampleBicubic2dAAGrad", [tg.ptr, osz.ptr, isz.ptr, bool(align_corners), float(scales[0]),
                                                float(scales[1]), ty.ptr], grad_out.device, workspace)
+    return out
+
+
+def upsample_nearest_exact2d(x, out_hw, fmt="NCHW", scales=(0.0, 0.0), out=None, workspace=None):
+    out = torch.empty(_out_shape(x, out_hw, fmt), dtype=x.dtype, device=x.device) if out is None else out
+    tx, ty, size = acl_tensor(x, fmt), acl_tensor(out, fmt), int_array(out_hw)
+    two_phase("aclnnUpsampleNearestExact2d", [tx.ptr, size.ptr, float(scales[0]), float(scales[1]), ty.ptr], x.device,
+              workspace)
+    return out
+
+
+def upsample_nearest_exact2d_backward(grad_out, out_hw, input_size, scales=(0.0, 0.0), out=None, workspace=None):
+    out = torch.empty(tuple(input_size), dtype=grad_out.dtype, device=grad_out.device) if out is None else out
+    tg, ty = acl_tensor(grad_out, "NCHW"), acl_tensor(out, "NCHW")
+    osz, isz = int_array(out_hw), int_array(input_size)
+    two_phase("aclnnUpsampleNearestExact2dBackward", [tg.ptr, osz.ptr, isz.ptr, float(scales[0]), float(scales[1]),
+                                                      ty.ptr], grad_out.device, workspace)
     return out
 
 

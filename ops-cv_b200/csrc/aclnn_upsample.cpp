@@ -135,7 +135,7 @@ aclnnStatus CheckNearestFwd(const char* api, const aclTensor* self, const aclInt
 }
 
 aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTensor* out, float userScaleH,
-                           float userScaleW, uint64_t* workspaceSize, aclOpExecutor** executor)
+                           float userScaleW, uint64_t* workspaceSize, aclOpExecutor** executor, bool exact = false)
 {
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
@@ -148,8 +148,8 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
-    const AxisGeom ah{sh.hin, sh.hout, NearestScale(gi.h, go.h, userScaleH)};
-    const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, go.w, userScaleW)};
+    const AxisGeom ah{sh.hin, sh.hout, NearestScale(gi.h, go.h, userScaleH), exact ? 1 : 0};
+    const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, go.w, userScaleW), exact ? 1 : 0};
     const uint64_t offH = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.hout));
     const uint64_t offW = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.wout));
     const NearestPlan plan = MakeNearestFwdPlan(dt, lay, sh, ah, aw);
@@ -470,6 +470,9 @@ BicubicGradScale MakeBicubicGradScale(int64_t in, int64_t out, bool align, float
 
 } // namespace
 
+static aclnnStatus PlanNearestBwd(const char* api, const aclTensor* gradOut, aclTensor* gradInput, float scaleH,
+                                  float scaleW, bool exact, uint64_t* workspaceSize, aclOpExecutor** executor);
+
 extern "C" {
 
 // ===============================================================================================================
@@ -563,6 +566,24 @@ aclnnStatus aclnnUpsampleNearest2dBackwardGetWorkspaceSize(const aclTensor* grad
         // all-copy schedule (resize_nearest_neighbor_v2_grad_tiling_base.cpp:449-452)
         return PlanCopy(api, gradOut, gradInput, workspaceSize, executor);
     }
+    // scales reach the tiling as floats (aclnn_upsample_nearest_2d_backward.cpp:351-354)
+    return PlanNearestBwd(api, gradOut, gradInput, NearestScale(gi.h, gg.h, static_cast<float>(scalesH)),
+                          NearestScale(gi.w, gg.w, static_cast<float>(scalesW)), false, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleNearest2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                           aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearest2dBackward", workspace, workspaceSize, executor, stream);
+}
+
+} // extern "C"
+
+// Window tables and the gather kernel shared by UpsampleNearest2dBackward and UpsampleNearestExact2dBackward.
+static aclnnStatus PlanNearestBwd(const char* api, const aclTensor* gradOut, aclTensor* gradInput, float scaleH,
+                                  float scaleW, bool exact, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    const Geom gg = GeomOf(gradOut), gi = GeomOf(gradInput);
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
@@ -573,9 +594,8 @@ aclnnStatus aclnnUpsampleNearest2dBackwardGetWorkspaceSize(const aclTensor* grad
     const Shape4 sh = MakeShape(gi, gg);
     const Dt dt = ToDt(gradOut->dtype);
     const Layout lay = gradOut->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
-    // scales reach the tiling as floats (aclnn_upsample_nearest_2d_backward.cpp:351-354)
-    const AxisGeom ah{sh.hin, sh.hout, NearestScale(gi.h, gg.h, static_cast<float>(scalesH))};
-    const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, gg.w, static_cast<float>(scalesW))};
+    const AxisGeom ah{sh.hin, sh.hout, scaleH, exact ? 1 : 0};
+    const AxisGeom aw{sh.win, sh.wout, scaleW, exact ? 1 : 0};
     const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
     const NearestPlan plan = MakeNearestBwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
@@ -595,10 +615,161 @@ aclnnStatus aclnnUpsampleNearest2dBackwardGetWorkspaceSize(const aclTensor* grad
     return ACLNN_SUCCESS;
 }
 
-aclnnStatus aclnnUpsampleNearest2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
-                                           aclrtStream stream)
+extern "C" {
+
+// ===============================================================================================================
+// image/upsample_nearest/op_host/op_api/aclnn_upsample_nearest_exact2d.cpp:284-340: null check, empty tensors
+// succeed, then CheckParams (:185-196: dtype, shape, elements, format); the regbase branch runs
+// ResizeNearestNeighborV2 with half_pixel_centers = true and float(scales) (:249, :316-317).
+aclnnStatus aclnnUpsampleNearestExact2dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                        double scalesH, double scalesW, aclTensor* out,
+                                                        uint64_t* workspaceSize, aclOpExecutor** executor)
 {
-    return RunExecutor("aclnnUpsampleNearest2dBackward", workspace, workspaceSize, executor, stream);
+    static const char* api = "aclnnUpsampleNearestExact2d";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (self == nullptr || outputSize == nullptr || out == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (IsEmpty(self) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    if (!DtypeSupported(self->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(self->dtype));
+    }
+    if (self->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from self dtype %s", api, DtypeName(out->dtype),
+                    DtypeName(self->dtype));
+    }
+    if (self->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self must be 4-D, got %zu-D", api, self->dims.size());
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: output_size must have 2 values, got %zu", api, outputSize->v.size());
+    }
+    if (out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out must be 4-D, got %zu-D", api, out->dims.size());
+    }
+    if (self->format != ACL_FORMAT_NCHW && self->format != ACL_FORMAT_NHWC && self->format != ACL_FORMAT_ND) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format of self only supports NCHW, NHWC, ND, got %s", api,
+                    FormatName(self->format));
+    }
+    if (self->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format of self (%s) and out (%s) must be equal", api,
+                    FormatName(self->format), FormatName(out->format));
+    }
+    const Geom gi = GeomOf(self), go = GeomOf(out);
+    const int64_t outH = outputSize->v[0], outW = outputSize->v[1];
+    if (!(gi.h > 0 && gi.w > 0 && outH > 0 && outW > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input and output sizes should be greater than 0", api);
+    }
+    if (gi.n != go.n || gi.c != go.c) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: N %ld/%ld or C %ld/%ld of self and out differ", api, (long)gi.n,
+                    (long)go.n, (long)gi.c, (long)go.c);
+    }
+    if (go.h != outH || go.w != outW) { // the reference leaves this to the kernel's shape inference
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out H/W (%ld, %ld) differ from output_size (%ld, %ld)", api,
+                    (long)go.h, (long)go.w, (long)outH, (long)outW);
+    }
+    if (!FitsInt32(gi) || !FitsInt32(go)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
+    }
+    const float sH = scalesH > 0 ? static_cast<float>(scalesH) : 0.0f;
+    const float sW = scalesW > 0 ? static_cast<float>(scalesW) : 0.0f;
+    return PlanNearestFwd(api, self, out, sH, sW, workspaceSize, executor, true);
+}
+
+aclnnStatus aclnnUpsampleNearestExact2d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                        aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearestExact2d", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/upsample_nearest_exact2d_grad/op_host/op_api/aclnn_upsample_nearest_exact2d_backward.cpp:178-240: null
+// check, empty tensors succeed, CheckParams (:153-175: dtype, shape, N/C with NHWC rejected, negative scales,
+// elements with the up-scale limit of 50); UpsampleNearestExact2dGrad with float(scales) (:215-228).
+aclnnStatus aclnnUpsampleNearestExact2dBackwardGetWorkspaceSize(const aclTensor* gradOutput,
+                                                                const aclIntArray* outputSize,
+                                                                const aclIntArray* inputSize, double scalesH,
+                                                                double scalesW, aclTensor* out,
+                                                                uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleNearestExact2dBackward";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (gradOutput == nullptr || inputSize == nullptr || out == nullptr || outputSize == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (IsEmpty(gradOutput) || IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    if (!DtypeSupported(gradOutput->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOutput dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(gradOutput->dtype));
+    }
+    if (gradOutput->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from gradOutput dtype %s", api,
+                    DtypeName(out->dtype), DtypeName(gradOutput->dtype));
+    }
+    if (gradOutput->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format of gradOutput (%s) and out (%s) must be equal", api,
+                    FormatName(gradOutput->format), FormatName(out->format));
+    }
+    if (gradOutput->dims.size() != 4 || out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOutput and out must be 4-D", api);
+    }
+    if (inputSize->v.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input_size must have 4 values, got %zu", api, inputSize->v.size());
+    }
+    if (outputSize->v.size() != 2) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: output_size must have 2 values, got %zu", api, outputSize->v.size());
+    }
+    if (gradOutput->format == ACL_FORMAT_NHWC) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: only the NCHW and ND formats are supported", api);
+    }
+    if (gradOutput->dims[0] != out->dims[0] || gradOutput->dims[1] != out->dims[1]) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: N and C of gradOutput and out differ", api);
+    }
+    if (scalesH < 0 || scalesW < 0) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales cannot be negative (w %f, h %f)", api, scalesW, scalesH);
+    }
+    const int64_t inH = inputSize->v[2], inW = inputSize->v[3];
+    const Geom gg = GeomOf(gradOutput), gi = GeomOf(out);
+    const double realH = scalesH > 0 ? 1.0 / scalesH : static_cast<double>(inH) / static_cast<double>(gg.h);
+    const double realW = scalesW > 0 ? 1.0 / scalesW : static_cast<double>(inW) / static_cast<double>(gg.w);
+    if (!(realH >= 0.02 && realW >= 0.02)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales are too large (h %f, w %f)", api, realH, realW);
+    }
+    if (!(inH > 0 && inW > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input and output sizes should be greater than 0", api);
+    }
+    if (gi.h != inH || gi.w != inW || gi.n != inputSize->v[0] || gi.c != inputSize->v[1] ||
+        gg.h != outputSize->v[0] || gg.w != outputSize->v[1]) {
+        // the reference's tiling rejects this (upsample_nearest_exact2d_grad_tiling_arch35.cpp:244-246)
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: tensor shapes differ from input_size / output_size", api);
+    }
+    if (!FitsInt32(gi) || !FitsInt32(gg)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
+    }
+    // upsample_nearest_exact2d_grad_tiling_arch35.cpp:189-200: grads extent over grad_input extent, or the scale given
+    const float userH = scalesH > 0 ? static_cast<float>(scalesH) : 0.0f;
+    const float userW = scalesW > 0 ? static_cast<float>(scalesW) : 0.0f;
+    const float sH = userH > 0.0f ? userH : static_cast<float>(gg.h) / static_cast<float>(gi.h);
+    const float sW = userW > 0.0f ? userW : static_cast<float>(gg.w) / static_cast<float>(gi.w);
+    if (gg.h == gi.h && gg.w == gi.w && std::fabs(sH - 1.0f) <= 1e-8f && std::fabs(sW - 1.0f) <= 1e-8f) {
+        return PlanCopy(api, gradOutput, out, workspaceSize, executor); // :112-119
+    }
+    return PlanNearestBwd(api, gradOutput, out, sH, sW, true, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleNearestExact2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearestExact2dBackward", workspace, workspaceSize, executor, stream);
 }
 
 // ===============================================================================================================

@@ -14,12 +14,13 @@
 namespace opscv {
 namespace host {
 
-inline std::vector<int32_t> NearestSrc(int32_t in, int32_t out, float scale)
+inline std::vector<int32_t> NearestSrc(int32_t in, int32_t out, float scale, bool exact = false)
 {
     std::vector<int32_t> src(static_cast<size_t>(out));
     const long long last = in - 1;
     for (int32_t d = 0; d < out; ++d) {
-        const long long s = static_cast<long long>(std::floor(static_cast<float>(d) * scale));
+        const float pos = exact ? static_cast<float>(d) + 0.5f : static_cast<float>(d);
+        const long long s = static_cast<long long>(std::floor(pos * scale));
         src[d] = static_cast<int32_t>(s < last ? s : last);
     }
     return src;
@@ -29,7 +30,7 @@ struct Ranges {
     std::vector<int32_t> start, end;
 };
 
-inline Ranges NearestBwdRanges(int32_t in, int32_t out, float scale)
+inline Ranges NearestBwdRanges(int32_t in, int32_t out, float scale, bool exact = false)
 {
     Ranges r;
     r.start.resize(in);
@@ -37,8 +38,14 @@ inline Ranges NearestBwdRanges(int32_t in, int32_t out, float scale)
     const float inv = 1.0f / scale;
     const long long lim = out;
     for (int32_t y = 0; y < in; ++y) {
-        long long a = static_cast<long long>(std::ceil(static_cast<float>(y) * inv));
-        long long b = static_cast<long long>(std::ceil(static_cast<float>(y + 1) * inv));
+        long long a, b;
+        if (exact) {
+            a = static_cast<long long>(std::ceil(static_cast<float>(y) * scale - 0.5f));
+            b = static_cast<long long>(std::ceil(static_cast<float>(y + 1) * scale - 0.5f));
+        } else {
+            a = static_cast<long long>(std::ceil(static_cast<float>(y) * inv));
+            b = static_cast<long long>(std::ceil(static_cast<float>(y + 1) * inv));
+        }
         a = std::max<long long>(0, std::min(a, lim));
         b = std::max(a, std::min(b, lim));
         r.start[y] = static_cast<int32_t>(a);

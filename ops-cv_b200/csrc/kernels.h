@@ -41,6 +41,9 @@ struct AxisGeom {
     int32_t in;  // extent on the forward-input side (grad_input side for backward ops)
     int32_t out; // extent on the forward-output side
     float scale; // forward source-coordinate scale as the reference's tiling computes it
+    // Nearest tables only: 1 selects the UpsampleNearestExact2d index rules (forward: floor((d + 0.5) * scale);
+    // backward: `scale` is then the grads-per-grad_input ratio and the window starts at ceil(y * scale - 0.5)).
+    int32_t exact = 0;
 };
 
 // Table builders (tables.cu). Each fills the H and the W table in one launch.

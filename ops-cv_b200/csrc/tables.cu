@@ -36,7 +36,9 @@ __global__ void NearestFwdTableKernel(AxisGeom gh, AxisGeom gw, NearestAxis th, 
     if (d >= g.out) {
         return;
     }
-    long long s = static_cast<long long>(floorf(Mul(static_cast<float>(d), g.scale)));
+    // exact: half_pixel_centers = true, resize_nearest_neighbor_v2_simt.h:115-117
+    const float pos = g.exact ? Add(static_cast<float>(d), 0.5f) : static_cast<float>(d);
+    long long s = static_cast<long long>(floorf(Mul(pos, g.scale)));
     const long long last = g.in - 1;
     src[d] = static_cast<int32_t>(s < last ? s : last);
 }
@@ -51,9 +53,16 @@ __global__ void NearestBwdTableKernel(AxisGeom gh, AxisGeom gw, RangeAxis th, Ra
     if (y >= g.in) {
         return;
     }
-    const float inv = Div(1.0f, g.scale);
-    long long a = static_cast<long long>(ceilf(Mul(static_cast<float>(y), inv)));
-    long long b = static_cast<long long>(ceilf(Mul(static_cast<float>(y + 1), inv)));
+    long long a, b;
+    if (g.exact) {
+        // image/upsample_nearest_exact2d_grad/op_kernel/arch35/upsample_nearest_exact2d_grad_simt_base.h:33-43
+        a = static_cast<long long>(ceilf(Sub(Mul(static_cast<float>(y), g.scale), 0.5f)));
+        b = static_cast<long long>(ceilf(Sub(Mul(static_cast<float>(y + 1), g.scale), 0.5f)));
+    } else {
+        const float inv = Div(1.0f, g.scale);
+        a = static_cast<long long>(ceilf(Mul(static_cast<float>(y), inv)));
+        b = static_cast<long long>(ceilf(Mul(static_cast<float>(y + 1), inv)));
+    }
     const long long lim = g.out;
     a = a < lim ? a : lim;
     b = b < lim ? b : lim;

@@ -366,8 +366,8 @@ NearestPlan MakeNearestFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGe
         return plan;
     }
     const int es = DtSize(dt), vi = 16 / es;
-    const std::vector<int32_t> srcH = host::NearestSrc(sh.hin, sh.hout, gh.scale);
-    const std::vector<int32_t> srcW = host::NearestSrc(sh.win, sh.wout, gw.scale);
+    const std::vector<int32_t> srcH = host::NearestSrc(sh.hin, sh.hout, gh.scale, gh.exact != 0);
+    const std::vector<int32_t> srcW = host::NearestSrc(sh.win, sh.wout, gw.scale, gw.exact != 0);
     const int32_t rh = sh.hout / sh.hin, rw = sh.wout / sh.win;
     if (sh.hout == rh * sh.hin && sh.wout == rw * sh.win && (rw == 2 || rw == 3 || rw == 4) && sh.win % vi == 0 &&
         IsIntegerReplication(srcH, rh) && IsIntegerReplication(srcW, rw)) {
@@ -396,8 +396,8 @@ NearestPlan MakeNearestBwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, AxisGe
         return plan;
     }
     const int es = DtSize(dt), vi = 16 / es;
-    const host::Ranges rH = host::NearestBwdRanges(sh.hin, sh.hout, gh.scale);
-    const host::Ranges rW = host::NearestBwdRanges(sh.win, sh.wout, gw.scale);
+    const host::Ranges rH = host::NearestBwdRanges(sh.hin, sh.hout, gh.scale, gh.exact != 0);
+    const host::Ranges rW = host::NearestBwdRanges(sh.win, sh.wout, gw.scale, gw.exact != 0);
     const int32_t rh = sh.hout / sh.hin, rw = sh.wout / sh.win;
     if (sh.hout == rh * sh.hin && sh.wout == rw * sh.win && (rw == 2 || rw == 4) && sh.wout % vi == 0 &&
         IsIntegerPooling(rH, rh) && IsIntegerPooling(rW, rw)) {

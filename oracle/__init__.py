@@ -139,6 +139,37 @@ def nearest2d_bwd(go, in_hw, scales=(0.0, 0.0), fmt=NCHW):
     return gi
 
 
+def nearest_exact_src_index(in_size, out_size, user_scale=0.0):
+    idx, p = _i32(out_size)
+    lib().orc_nearest_exact_src_index(I64(in_size), I64(out_size), F32(user_scale), p)
+    return idx
+
+
+def nearest_exact_bwd_ranges(in_size, out_size, user_scale=0.0):
+    s, ps = _i32(in_size)
+    e, pe = _i32(in_size)
+    lib().orc_nearest_exact_bwd_ranges(I64(in_size), I64(out_size), F32(user_scale), ps, pe)
+    return s, e
+
+
+def nearest_exact2d_fwd(x, out_hw, scales=(0.0, 0.0), fmt=NCHW):
+    x, px = _f(x)
+    n, c, h, w = _dims(x.shape, fmt)
+    y = np.empty(_shape(n, c, out_hw[0], out_hw[1], fmt), dtype=np.float32)
+    lib().orc_nearest_exact2d_fwd(px, y.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(h), I64(w),
+                                  I64(out_hw[0]), I64(out_hw[1]), F32(scales[0]), F32(scales[1]), I32(fmt))
+    return y
+
+
+def nearest_exact2d_bwd(go, in_hw, scales=(0.0, 0.0)):
+    go, pg = _f(go)
+    n, c, ho, wo = go.shape
+    gi = np.empty((n, c, in_hw[0], in_hw[1]), dtype=np.float32)
+    lib().orc_nearest_exact2d_bwd(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_hw[0]),
+                                  I64(in_hw[1]), I64(ho), I64(wo), F32(scales[0]), F32(scales[1]))
+    return gi
+
+
 def bilinear2d_fwd(x, out_hw, align=False, scales=(0.0, 0.0), fmt=NCHW):
     x, px = _f(x)
     n, c, h, w = _dims(x.shape, fmt)

@@ -164,8 +164,11 @@ ATK = {
     "UpsampleBicubic2dBackward": ("image/upsample_bicubic2d_grad/tests/st/aclnnUpsampleBicubic2dBackward/atk_aclnnUpsampleBicubic2dBackward.json", "interp_bwd"),
     "UpsampleBilinear2dAA": ("image/upsample_bilinear2d_aa/tests/st/aclnnUpsampleBilinear2dAA/atk_aclnnUpsampleBilinear2dAA.json", "interp_fwd"),
     "UpsampleBilinear2dAABackward": ("image/upsample_bilinear2d_aa_backward/tests/st/aclnnUpsampleBilinear2dAABackward/atk_aclnnUpsampleBilinear2dAABackward.json", "interp_bwd"),
+    "UpsampleNearestExact2d": ("image/upsample_nearest/tests/st/aclnnUpsampleNearestExact2d/atk_aclnnUpsampleNearestExact2d.json", "interp_fwd"),
+    "UpsampleNearestExact2dBackward": ("image/upsample_nearest_exact2d_grad/tests/st/aclnnUpsampleNearestExact2dBackward/atk_aclnnUpsampleNearestExact2dBackward.json", "interp_bwd"),
 }
-SCALE_FACTOR_APIS = ("UpsampleBilinear2dAA", "UpsampleBilinear2dAABackward")
+SCALE_FACTOR_APIS = ("UpsampleBilinear2dAA", "UpsampleBilinear2dAABackward", "UpsampleNearestExact2d",
+                     "UpsampleNearestExact2dBackward")
 TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
 CASES_PER_API = 20
 MAX_PLANE = 1000   # H * W of any tensor of a kept case
@@ -234,7 +237,7 @@ def replay_atk(data, index):
                 mode = f.get("mode", "nearest")
                 kw = {"scale_factor": sf, "recompute_scale_factor": False, "mode": mode} if by_factor else {
                     "size": (oh, ow), "mode": mode}
-                if mode != "nearest":
+                if mode not in ("nearest", "nearest-exact"):
                     kw["align_corners"] = as_bool(f.get("align_corners", False))
                 if as_bool(f.get("antialias", False)):
                     kw["antialias"] = True

@@ -171,6 +171,42 @@ def test_bicubic_aa_forward_status(ops):
                   T(ops, (2, 3, 7, 9), fmt="ND").ptr)[0] == OK
 
 
+def test_nearest_exact_status(ops):
+    api = "aclnnUpsampleNearestExact2d"
+    x, y, sz = T(ops, (2, 3, 8, 8)), T(ops, (2, 3, 16, 12)), IA(ops, [16, 12])
+    st, ws = phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, y.ptr)
+    assert st == OK and ws > 0
+    assert phase1(ops, api, None, sz.ptr, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, None, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, None)[0] == NULLPTR
+    # empty tensors succeed before any other check
+    assert phase1(ops, api, T(ops, (0, 3, 8, 8)).ptr, IA(ops, [16]).ptr, 0.0, 0.0, T(ops, (0, 3, 16, 12)).ptr) == (OK, 0)
+    assert phase1(ops, api, T(ops, (2, 3, 8, 8), torch.int32).ptr, sz.ptr, 0.0, 0.0,
+                  T(ops, (2, 3, 16, 12), torch.int32).ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, T(ops, (2, 3, 16, 12), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (3, 8, 8)).ptr, sz.ptr, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, IA(ops, [16, 12, 1]).ptr, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, T(ops, (2, 4, 16, 12)).ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, T(ops, (2, 3, 16, 12), fmt="NHWC").ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 8, 8, 3), fmt="NHWC").ptr, sz.ptr, 0.0, 0.0,
+                  T(ops, (2, 16, 12, 3), fmt="NHWC").ptr)[0] == OK
+    api = "aclnnUpsampleNearestExact2dBackward"
+    g, out = T(ops, (2, 3, 16, 12)), T(ops, (2, 3, 8, 8))
+    osz, isz = IA(ops, [16, 12]), IA(ops, [2, 3, 8, 8])
+    st, ws = phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, 0.0, out.ptr)
+    assert st == OK and ws > 0
+    assert phase1(ops, api, None, osz.ptr, isz.ptr, 0.0, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, None, 0.0, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, -1.0, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 100.0, 0.0, out.ptr)[0] == INVALID   # up-scale limit of 50
+    assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [2, 3, 8]).ptr, 0.0, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, 0.0, T(ops, (2, 3, 8, 8), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, 0.0, T(ops, (2, 4, 8, 8)).ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 16, 12, 3), fmt="NHWC").ptr, osz.ptr, IA(ops, [2, 8, 8, 3]).ptr, 0.0, 0.0,
+                  T(ops, (2, 8, 8, 3), fmt="NHWC").ptr)[0] == INVALID
+
+
 def test_bilinear_aa_status(ops):
     """aclnnUpsampleBilinear2dAA / ...Backward: the checks of the bicubic-AA pair (NCHW or ND only, one dtype, 4-D,
     sizes > 0) plus negative scales in the forward."""

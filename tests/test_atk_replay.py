@@ -1,5 +1,5 @@
 """Replay of the reference's own test inputs (tests/golden/atk_replay.npz, made by tests/golden/make_golden.py
-<reference> replay): a seeded slice of the ST case matrices of the thirteen APIs plus the kernel-UT generator of
+<reference> replay): a seeded slice of the ST case matrices of the fifteen APIs plus the kernel-UT generator of
 UpsampleBilinear2d, each with the torch CPU golden that the reference's executors compute.
 
 The CPU half holds the oracle to these goldens, the GPU half the library (through the C ABI). The bar is the one the
@@ -59,6 +59,10 @@ def run_case(m, backend, oracle):
         elif api == "UpsampleBicubic2d":
             got = back(backend.upsample_bicubic2d(t(x), size, align)) if gpu else rnd(oracle.bicubic2d_fwd(x, size, align))
             out["y"] = (got, GOLD[name + ".y"])
+        elif api == "UpsampleNearestExact2d":
+            got = back(backend.upsample_nearest_exact2d(t(x), size, scales=scales)) if gpu else rnd(
+                oracle.nearest_exact2d_fwd(x, size, scales))
+            out["y"] = (got, GOLD[name + ".y"])
         elif api == "UpsampleBilinear2dAA":
             got = back(backend.upsample_bilinear2d_aa(t(x), size, align, scales)) if gpu else rnd(
                 oracle.bilinear_aa_fwd(x, size, align, scales))
@@ -76,6 +80,9 @@ def run_case(m, backend, oracle):
                     v2 = api.endswith("V2")
                     got = back(backend.upsample_bilinear2d_backward(t(g), size, shape, align, v2=v2)) if gpu else rnd(
                         oracle.bilinear2d_bwd(g, shape[2:], align, definition="dispatch"))
+                elif api == "UpsampleNearestExact2dBackward":
+                    got = back(backend.upsample_nearest_exact2d_backward(t(g), size, shape, scales)) if gpu else rnd(
+                        oracle.nearest_exact2d_bwd(g, shape[2:], scales))
                 elif api == "UpsampleBilinear2dAABackward":
                     got = back(backend.upsample_bilinear2d_aa_backward(t(g), size, shape, align, scales)) if gpu else rnd(
                         oracle.bilinear_aa_bwd(g, shape[2:], align, scales))
