@@ -145,6 +145,24 @@ ACLNN_API aclnnStatus aclnnUpsampleNearestExact2dBackwardGetWorkspaceSize(const 
 ACLNN_API aclnnStatus aclnnUpsampleNearestExact2dBackward(void* workspace, uint64_t workspaceSize,
                                                           aclOpExecutor* executor, aclrtStream stream);
 
+/* The 1-D pair: (N, C, L) tensors in NCL or ND format, computed as the 2-D operator on the (N, C, 1, L) view with
+ * scales {1, scales}. Replaces image/upsample_nearest/op_host/op_api/aclnn_upsample_nearest_exact1d.h
+ * (implementation aclnn_upsample_nearest_exact1d.cpp:166-226) and
+ * image/upsample_nearest_exact2d_grad/op_host/op_api/aclnn_upsample_nearest_exact1d_backward.h (implementation
+ * aclnn_upsample_nearest_exact1d_backward.cpp, first phase). */
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact1dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                                  double scales, aclTensor* out,
+                                                                  uint64_t* workspaceSize, aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact1d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                  aclrtStream stream);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact1dBackwardGetWorkspaceSize(const aclTensor* gradOutput,
+                                                                          const aclIntArray* outputSize,
+                                                                          const aclIntArray* inputSize, double scales,
+                                                                          aclTensor* out, uint64_t* workspaceSize,
+                                                                          aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact1dBackward(void* workspace, uint64_t workspaceSize,
+                                                          aclOpExecutor* executor, aclrtStream stream);
+
 /* ---- UpsampleBilinear2dAA ----------------------------------------------------------------------------------
  * Replaces image/upsample_bilinear2d_aa/op_host/op_api/aclnn_upsample_bilinear2d_aa.h:38-49 (implementation
  * aclnn_upsample_bilinear2d_aa.cpp:184-252; kernel image/upsample_bilinear2d_aa/op_kernel/arch35/

@@ -62,7 +62,8 @@ typedef enum {
     ACL_FORMAT_UNDEFINED = -1,
     ACL_FORMAT_NCHW = 0,
     ACL_FORMAT_NHWC = 1,
-    ACL_FORMAT_ND = 2
+    ACL_FORMAT_ND = 2,
+    ACL_FORMAT_NCL = 47
 } aclFormat;
 
 typedef enum { ACL_OPT_DETERMINISTIC = 0 } aclSysParamOpt;

@@ -18,7 +18,7 @@ CSRC_DIR = os.path.join(_HERE, "csrc")
 
 # aclDataType / aclFormat values (include/opscv_acl.h)
 ACL_FLOAT, ACL_FLOAT16, ACL_INT8, ACL_INT32, ACL_UINT8, ACL_INT64, ACL_DOUBLE, ACL_BOOL, ACL_BF16 = 0, 1, 2, 3, 4, 9, 11, 12, 27
-ACL_FORMAT_NCHW, ACL_FORMAT_NHWC, ACL_FORMAT_ND = 0, 1, 2
+ACL_FORMAT_NCHW, ACL_FORMAT_NHWC, ACL_FORMAT_ND, ACL_FORMAT_NCL = 0, 1, 2, 47
 ACL_OPT_DETERMINISTIC = 0
 
 ACLNN_SUCCESS = 0
@@ -73,6 +73,10 @@ SYMBOLS = {
     "aclnnUpsampleNearestExact2d": _PHASE2,
     "aclnnUpsampleNearestExact2dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleNearestExact2dBackward": _PHASE2,
+    "aclnnUpsampleNearestExact1dGetWorkspaceSize": (_I32, [_P, _P, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearestExact1d": _PHASE2,
+    "aclnnUpsampleNearestExact1dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearestExact1dBackward": _PHASE2,
     "aclnnUpsampleBilinear2dAAGetWorkspaceSize": (_I32, [_P, _P, _B, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleBilinear2dAA": _PHASE2,
     "aclnnUpsampleBilinear2dAABackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _P, _PU64, _PP]),

@@ -3,7 +3,7 @@ import ctypes
 
 import torch
 
-from . import (ACL_BF16, ACL_DOUBLE, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_NCHW, ACL_FORMAT_ND, ACL_FORMAT_NHWC,
+from . import (ACL_BF16, ACL_DOUBLE, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_NCHW, ACL_FORMAT_NCL, ACL_FORMAT_ND, ACL_FORMAT_NHWC,
                ACL_INT32, ACL_INT64, ACL_OPT_DETERMINISTIC, ACL_UINT8, lib)
 
 __all__ = [
@@ -11,13 +11,14 @@ __all__ = [
     "launch_count", "reset_launch_count", "async_copy_timeouts", "last_error", "debug_axis_table", "upsample_nearest2d",
     "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_no_alloc",
     "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bilinear2d_aa",
-    "upsample_bilinear2d_aa_backward", "upsample_nearest_exact2d", "upsample_nearest_exact2d_backward", "upsample_bicubic2d_aa",
+    "upsample_bilinear2d_aa_backward", "upsample_nearest_exact2d", "upsample_nearest_exact2d_backward",
+    "upsample_nearest_exact1d", "upsample_nearest_exact1d_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
 ]
 
 _DTYPES = {torch.float32: ACL_FLOAT, torch.float16: ACL_FLOAT16, torch.bfloat16: ACL_BF16, torch.float64: ACL_DOUBLE,
            torch.uint8: ACL_UINT8, torch.int32: ACL_INT32, torch.int64: ACL_INT64}
-_FORMATS = {"NCHW": ACL_FORMAT_NCHW, "NHWC": ACL_FORMAT_NHWC, "ND": ACL_FORMAT_ND}
+_FORMATS = {"NCHW": ACL_FORMAT_NCHW, "NHWC": ACL_FORMAT_NHWC, "ND": ACL_FORMAT_ND, "NCL": ACL_FORMAT_NCL}
 
 
 class AclnnError(RuntimeError):
@@ -247,6 +248,22 @@ def upsample_nearest_exact2d_backward(grad_out, out_hw, input_size, scales=(0.0,
     osz, isz = int_array(out_hw), int_array(input_size)
     two_phase("aclnnUpsampleNearestExact2dBackward", [tg.ptr, osz.ptr, isz.ptr, float(scales[0]), float(scales[1]),
                                                       ty.ptr], grad_out.device, workspace)
+    return out
+
+
+def upsample_nearest_exact1d(x, out_l, scale=0.0, fmt="NCL", out=None, workspace=None):
+    out = torch.empty((x.shape[0], x.shape[1], out_l), dtype=x.dtype, device=x.device) if out is None else out
+    tx, ty, size = acl_tensor(x, fmt), acl_tensor(out, fmt), int_array([out_l])
+    two_phase("aclnnUpsampleNearestExact1d", [tx.ptr, size.ptr, float(scale), ty.ptr], x.device, workspace)
+    return out
+
+
+def upsample_nearest_exact1d_backward(grad_out, out_l, input_size, scale=0.0, fmt="NCL", out=None, workspace=None):
+    out = torch.empty(tuple(input_size), dtype=grad_out.dtype, device=grad_out.device) if out is None else out
+    tg, ty = acl_tensor(grad_out, fmt), acl_tensor(out, fmt)
+    osz, isz = int_array([out_l]), int_array(input_size)
+    two_phase("aclnnUpsampleNearestExact1dBackward", [tg.ptr, osz.ptr, isz.ptr, float(scale), ty.ptr],
+              grad_out.device, workspace)
     return out
 
 

@@ -205,6 +205,7 @@ const char* FormatName(aclFormat f)
         case ACL_FORMAT_NCHW: return "NCHW";
         case ACL_FORMAT_NHWC: return "NHWC";
         case ACL_FORMAT_ND: return "ND";
+        case ACL_FORMAT_NCL: return "NCL";
         default: return "UNKNOWN";
     }
 }

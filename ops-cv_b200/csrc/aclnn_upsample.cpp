@@ -472,6 +472,8 @@ BicubicGradScale MakeBicubicGradScale(int64_t in, int64_t out, bool align, float
 
 static aclnnStatus PlanNearestBwd(const char* api, const aclTensor* gradOut, aclTensor* gradInput, float scaleH,
                                   float scaleW, bool exact, uint64_t* workspaceSize, aclOpExecutor** executor);
+static aclnnStatus PlanNearestExactBwd(const char* api, const aclTensor* gradOutput, aclTensor* out, double scalesH,
+                                       double scalesW, uint64_t* workspaceSize, aclOpExecutor** executor);
 
 extern "C" {
 
@@ -755,6 +757,22 @@ aclnnStatus aclnnUpsampleNearestExact2dBackwardGetWorkspaceSize(const aclTensor*
     if (!FitsInt32(gi) || !FitsInt32(gg)) {
         return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
     }
+    return PlanNearestExactBwd(api, gradOutput, out, scalesH, scalesW, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleNearestExact2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearestExact2dBackward", workspace, workspaceSize, executor, stream);
+}
+
+} // extern "C"
+
+// Checked 4-D tensors in, plan out; shared by the 2-D and the 1-D entry point.
+static aclnnStatus PlanNearestExactBwd(const char* api, const aclTensor* gradOutput, aclTensor* out, double scalesH,
+                                       double scalesW, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    const Geom gg = GeomOf(gradOutput), gi = GeomOf(out);
     // upsample_nearest_exact2d_grad_tiling_arch35.cpp:189-200: grads extent over grad_input extent, or the scale given
     const float userH = scalesH > 0 ? static_cast<float>(scalesH) : 0.0f;
     const float userW = scalesW > 0 ? static_cast<float>(scalesW) : 0.0f;
@@ -766,10 +784,144 @@ aclnnStatus aclnnUpsampleNearestExact2dBackwardGetWorkspaceSize(const aclTensor*
     return PlanNearestBwd(api, gradOutput, out, sH, sW, true, workspaceSize, executor);
 }
 
-aclnnStatus aclnnUpsampleNearestExact2dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+// (N, C, L) seen as (N, C, 1, L), as the reference's View3dAs4d does (aclnn_upsample_nearest_exact1d.cpp:45-62).
+static aclTensor View3dAs4d(const aclTensor* t)
+{
+    aclTensor v = *t;
+    v.dims = {t->dims[0], t->dims[1], 1, t->dims[2]};
+    v.strides = {t->strides[0], t->strides[1], t->strides[2] * t->dims[2], t->strides[2]};
+    v.format = ACL_FORMAT_NCHW;
+    return v;
+}
+
+extern "C" {
+
+// ===============================================================================================================
+// image/upsample_nearest/op_host/op_api/aclnn_upsample_nearest_exact1d.cpp:166-226: CheckParams (:110-121: null,
+// dtype, elements, shape), empty self succeeds, then the 2-D operator on the (N, C, 1, L) view with scales
+// {1, float(scales)}; formats other than NCL / ND end in ACLNN_ERR_INNER_NULLPTR (:139-141, :213).
+aclnnStatus aclnnUpsampleNearestExact1dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                        double scales, aclTensor* out, uint64_t* workspaceSize,
+                                                        aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleNearestExact1d";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (self == nullptr || out == nullptr || outputSize == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (!DtypeSupported(self->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(self->dtype));
+    }
+    if (self->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from self dtype %s", api, DtypeName(out->dtype),
+                    DtypeName(self->dtype));
+    }
+    if (self->dims.size() != 3 || out->dims.size() != 3) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self and out must be 3-D, got %zu-D and %zu-D", api,
+                    self->dims.size(), out->dims.size());
+    }
+    if (outputSize->v.size() != 1) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: output_size must have 1 value, got %zu", api, outputSize->v.size());
+    }
+    const int64_t outL = outputSize->v[0];
+    if (!(self->dims[0] > 0 && self->dims[1] > 0 && self->dims[2] > 0 && outL > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input and output sizes should be greater than 0", api);
+    }
+    if (out->dims[0] != self->dims[0] || out->dims[1] != self->dims[1] || out->dims[2] != outL) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out shape differs from (N, C, output_size)", api);
+    }
+    if ((self->format != ACL_FORMAT_NCL && self->format != ACL_FORMAT_ND) || out->format != self->format) {
+        return Fail(ACLNN_ERR_INNER_NULLPTR, "%s: only the NCL and ND formats are supported, got %s and %s", api,
+                    FormatName(self->format), FormatName(out->format));
+    }
+    if (self->dims[2] > INT32_MAX || outL > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: L must not exceed INT32_MAX", api);
+    }
+    const aclTensor self4 = View3dAs4d(self);
+    aclTensor out4 = View3dAs4d(out);
+    const float s = scales > 0 ? static_cast<float>(scales) : 0.0f;
+    return PlanNearestFwd(api, &self4, &out4, 1.0f, s, workspaceSize, executor, true);
+}
+
+aclnnStatus aclnnUpsampleNearestExact1d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                        aclrtStream stream)
+{
+    return RunExecutor("aclnnUpsampleNearestExact1d", workspace, workspaceSize, executor, stream);
+}
+
+// image/upsample_nearest_exact2d_grad/op_host/op_api/aclnn_upsample_nearest_exact1d_backward.cpp: CheckParams (null,
+// dtype, shape, N/C, negative scale, elements with the up-scale limit of 50), empty tensors succeed, then the 2-D
+// backward on the (N, C, 1, L) views with scales {1, float(scales)}.
+aclnnStatus aclnnUpsampleNearestExact1dBackwardGetWorkspaceSize(const aclTensor* gradOutput,
+                                                                const aclIntArray* outputSize,
+                                                                const aclIntArray* inputSize, double scales,
+                                                                aclTensor* out, uint64_t* workspaceSize,
+                                                                aclOpExecutor** executor)
+{
+    static const char* api = "aclnnUpsampleNearestExact1dBackward";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (gradOutput == nullptr || inputSize == nullptr || out == nullptr || outputSize == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    if (!DtypeSupported(gradOutput->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOutput dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(gradOutput->dtype));
+    }
+    if (gradOutput->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from gradOutput dtype %s", api,
+                    DtypeName(out->dtype), DtypeName(gradOutput->dtype));
+    }
+    if (gradOutput->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: format of gradOutput (%s) and out (%s) must be equal", api,
+                    FormatName(gradOutput->format), FormatName(out->format));
+    }
+    if (gradOutput->dims.size() != 3 || out->dims.size() != 3) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: gradOutput and out must be 3-D", api);
+    }
+    if (inputSize->v.size() != 3) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input_size must have 3 values, got %zu", api, inputSize->v.size());
+    }
+    if (outputSize->v.size() != 1) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: output_size must have 1 value, got %zu", api, outputSize->v.size());
+    }
+    if (gradOutput->dims[0] != out->dims[0] || gradOutput->dims[1] != out->dims[1]) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: N and C of gradOutput and out differ", api);
+    }
+    if (scales < 0) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales cannot be negative (%f)", api, scales);
+    }
+    const int64_t inL = inputSize->v[2], outL = gradOutput->dims[2];
+    const double real = scales > 0 ? 1.0 / scales : (outL != 0 ? static_cast<double>(inL) / static_cast<double>(outL) : 0.0);
+    if (!(real >= 0.02)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales is too large (%f)", api, real);
+    }
+    if (!(gradOutput->dims[0] > 0 && inL > 0 && gradOutput->dims[1] > 0 && outL > 0)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: input and output sizes should be greater than 0", api);
+    }
+    if (IsEmpty(out)) {
+        return EmptySuccess(api, workspaceSize, executor);
+    }
+    if (out->dims[2] != inL || out->dims[0] != inputSize->v[0] || out->dims[1] != inputSize->v[1] ||
+        outL != outputSize->v[0]) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: tensor shapes differ from input_size / output_size", api);
+    }
+    if (inL > INT32_MAX || outL > INT32_MAX) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: L must not exceed INT32_MAX", api);
+    }
+    const aclTensor g4 = View3dAs4d(gradOutput);
+    aclTensor out4 = View3dAs4d(out);
+    return PlanNearestExactBwd(api, &g4, &out4, 1.0, scales, workspaceSize, executor);
+}
+
+aclnnStatus aclnnUpsampleNearestExact1dBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                                 aclrtStream stream)
 {
-    return RunExecutor("aclnnUpsampleNearestExact2dBackward", workspace, workspaceSize, executor, stream);
+    return RunExecutor("aclnnUpsampleNearestExact1dBackward", workspace, workspaceSize, executor, stream);
 }
 
 // ===============================================================================================================

@@ -207,6 +207,33 @@ def test_nearest_exact_status(ops):
                   T(ops, (2, 8, 8, 3), fmt="NHWC").ptr)[0] == INVALID
 
 
+def test_nearest_exact_1d_status(ops):
+    api = "aclnnUpsampleNearestExact1d"
+    x, y, sz = T(ops, (2, 3, 8), fmt="NCL"), T(ops, (2, 3, 16), fmt="NCL"), IA(ops, [16])
+    assert phase1(ops, api, x.ptr, sz.ptr, 0.0, y.ptr)[0] == OK
+    assert phase1(ops, api, None, sz.ptr, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, None, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sz.ptr, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, IA(ops, [16, 1]).ptr, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 3, 1, 8)).ptr, sz.ptr, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (0, 3, 8), fmt="NCL").ptr, sz.ptr, 0.0, T(ops, (0, 3, 16), fmt="NCL").ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, 0.0, T(ops, (2, 3, 16), torch.float16, fmt="NCL").ptr)[0] == INVALID
+    # a format the reference has no branch for ends in its inner-null status
+    assert phase1(ops, api, T(ops, (2, 3, 8), fmt="NCHW").ptr, sz.ptr, 0.0, T(ops, (2, 3, 16), fmt="NCHW").ptr)[0] == INNER_NULL
+    api = "aclnnUpsampleNearestExact1dBackward"
+    g, out = T(ops, (2, 3, 16), fmt="NCL"), T(ops, (2, 3, 8), fmt="NCL")
+    osz, isz = IA(ops, [16]), IA(ops, [2, 3, 8])
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, out.ptr)[0] == OK
+    assert phase1(ops, api, None, osz.ptr, isz.ptr, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, None, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, -2.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 80.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [2, 3, 1, 8]).ptr, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, IA(ops, [16, 1]).ptr, isz.ptr, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, T(ops, (2, 4, 8), fmt="NCL").ptr)[0] == INVALID
+
+
 def test_bilinear_aa_status(ops):
     """aclnnUpsampleBilinear2dAA / ...Backward: the checks of the bicubic-AA pair (NCHW or ND only, one dtype, 4-D,
     sizes > 0) plus negative scales in the forward."""

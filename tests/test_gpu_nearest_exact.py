@@ -78,3 +78,28 @@ def test_nearest_exact_strided_and_empty(ops, oracle, dev):
     assert np.array_equal(y.cpu().numpy(), oracle.nearest_exact2d_fwd(x.contiguous().cpu().numpy(), (20, 13)))
     e = ops.upsample_nearest_exact2d(torch.zeros((0, 3, 4, 4), device=dev), (8, 8))
     assert e.shape == (0, 3, 8, 8)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("fmt", ["NCL", "ND"])
+@pytest.mark.parametrize("lens", [(9, 20), (33, 7), (1, 5), (6, 1), (16, 32), (12, 12)])
+def test_nearest_exact_1d(ops, oracle, dev, dtype, fmt, lens):
+    """The 1-D pair is the 2-D operator on the (N, C, 1, L) view."""
+    li, lo = lens
+    x, x32 = quant(torch.randn((3, 4, li), generator=gen(77)), dtype)
+    for scale in (0.0, 1.9):
+        y = ops.upsample_nearest_exact1d(x.to(dev), lo, scale, fmt)
+        ref = oracle.nearest_exact2d_fwd(x32.reshape(3, 4, 1, li), (1, lo), (1.0, scale)).reshape(3, 4, lo)
+        check(y, ref, dtype, exact=True)
+        g, g32 = quant(torch.randn((3, 4, lo), generator=gen(78)), dtype)
+        gi = ops.upsample_nearest_exact1d_backward(g.to(dev), lo, (3, 4, li), scale, fmt)
+        ref = oracle.nearest_exact2d_bwd(g32.reshape(3, 4, 1, lo), (1, li), (1.0, scale)).reshape(3, 4, li)
+        check(gi, ref, dtype, exact=True)
+
+
+def test_nearest_exact_1d_strided(ops, oracle, dev):
+    base = torch.randn((2, 3, 40), generator=gen(79)).to(dev)
+    x = base[:, :, 3:35:2]
+    y = ops.upsample_nearest_exact1d(x, 37)
+    ref = oracle.nearest_exact2d_fwd(x.contiguous().cpu().numpy().reshape(2, 3, 1, 16), (1, 37)).reshape(2, 3, 37)
+    assert np.array_equal(y.cpu().numpy(), ref)
