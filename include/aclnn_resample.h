@@ -217,6 +217,15 @@ ACLNN_API aclnnStatus aclnnUpsampleBicubic2dBackwardGetWorkspaceSize(const aclTe
 ACLNN_API aclnnStatus aclnnUpsampleBicubic2dBackward(void* workspace, uint64_t workspaceSize,
                                                      aclOpExecutor* executor, aclrtStream stream);
 
+/* ---- Resize ---------------------------------------------------------------------------------------------------
+ * Replaces image/resize_bilinear_v2/op_api/aclnn_resize.h:32-46 (implementation aclnn_resize.cpp:231-300, regbase
+ * branch). `scales` holds one factor per dimension of `self` (4 values); `mode` starts with "nearest" or "bilinear".
+ * nearest: UpsampleNearest2d; bilinear: UpsampleBilinear2d with align_corners = false. NCHW or NHWC. */
+ACLNN_API aclnnStatus aclnnResizeGetWorkspaceSize(const aclTensor* self, const aclFloatArray* scales, const char* mode,
+                                                  aclTensor* out, uint64_t* workspaceSize, aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnResize(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                  aclrtStream stream);
+
 /* ---- GridSampler2D -------------------------------------------------------------------------------------
  * Replaces image/grid_sample/op_api/aclnn_grid_sampler2d.h:53-82 (implementation aclnn_grid_sampler2d.cpp:266-340;
  * arithmetic image/grid_sampler2_d/op_kernel/arch35/grid_sampler2_d_simt.h:106-215,303-514).

@@ -71,6 +71,7 @@ typedef enum { ACL_OPT_DETERMINISTIC = 0 } aclSysParamOpt;
 typedef struct aclTensor aclTensor;
 typedef struct aclIntArray aclIntArray;
 typedef struct aclBoolArray aclBoolArray;
+typedef struct aclFloatArray aclFloatArray;
 typedef struct aclOpExecutor aclOpExecutor;
 typedef void* aclrtStream; /* a cudaStream_t */
 
@@ -88,6 +89,10 @@ ACLNN_API aclIntArray* aclCreateIntArray(const int64_t* value, uint64_t size);
 ACLNN_API aclnnStatus aclDestroyIntArray(const aclIntArray* array);
 ACLNN_API aclBoolArray* aclCreateBoolArray(const bool* value, uint64_t size);
 ACLNN_API aclnnStatus aclDestroyBoolArray(const aclBoolArray* array);
+ACLNN_API aclFloatArray* aclCreateFloatArray(const float* value, uint64_t size);
+ACLNN_API aclnnStatus aclDestroyFloatArray(const aclFloatArray* array);
+/* Number of values of `array` through *size; a non-zero status for a NULL argument. */
+ACLNN_API aclnnStatus aclGetFloatArraySize(const aclFloatArray* array, uint64_t* size);
 
 /* Frees an executor returned by a GetWorkspaceSize call that will not be passed to its second-phase call. */
 ACLNN_API aclnnStatus aclDestroyAclOpExecutor(aclOpExecutor* executor);

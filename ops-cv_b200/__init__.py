@@ -41,6 +41,9 @@ SYMBOLS = {
     "aclDestroyIntArray": (_I32, [_P]),
     "aclCreateBoolArray": (_P, [ctypes.POINTER(_B), _U64]),
     "aclDestroyBoolArray": (_I32, [_P]),
+    "aclCreateFloatArray": (_P, [ctypes.POINTER(_F), _U64]),
+    "aclDestroyFloatArray": (_I32, [_P]),
+    "aclGetFloatArraySize": (_I32, [_P, _PU64]),
     "aclDestroyAclOpExecutor": (_I32, [_P]),
     "aclGetRecentErrMsg": (ctypes.c_char_p, []),
     "aclrtCtxSetSysParamOpt": (ctypes.c_int, [_I32, _I64]),
@@ -85,6 +88,8 @@ SYMBOLS = {
     "aclnnUpsampleBicubic2d": _PHASE2,
     "aclnnUpsampleBicubic2dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleBicubic2dBackward": _PHASE2,
+    "aclnnResizeGetWorkspaceSize": (_I32, [_P, _P, ctypes.c_char_p, _P, _PU64, _PP]),
+    "aclnnResize": _PHASE2,
     "aclnnGridSampler2DGetWorkspaceSize": (_I32, [_P, _P, _I64, _I64, _B, _P, _PU64, _PP]),
     "aclnnGridSampler2D": _PHASE2,
     "aclnnGridSampler2DBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _I64, _I64, _B, _P, _P, _P, _PU64, _PP]),

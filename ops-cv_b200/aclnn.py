@@ -7,7 +7,7 @@ from . import (ACL_BF16, ACL_DOUBLE, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_NCHW, AC
                ACL_INT32, ACL_INT64, ACL_OPT_DETERMINISTIC, ACL_UINT8, lib)
 
 __all__ = [
-    "AclnnError", "acl_tensor", "int_array", "bool_array", "two_phase", "set_deterministic", "set_backward_algo",
+    "AclnnError", "acl_tensor", "int_array", "bool_array", "float_array", "resize", "two_phase", "set_deterministic", "set_backward_algo",
     "launch_count", "reset_launch_count", "async_copy_timeouts", "last_error", "debug_axis_table", "upsample_nearest2d",
     "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_no_alloc",
     "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bilinear2d_aa",
@@ -59,6 +59,11 @@ def acl_tensor(t, fmt="NCHW"):
 def int_array(values):
     arr = (ctypes.c_int64 * len(values))(*values)
     return _Handle(lib().aclCreateIntArray(arr, len(values)), lib().aclDestroyIntArray)
+
+
+def float_array(values):
+    arr = (ctypes.c_float * len(values))(*values)
+    return _Handle(lib().aclCreateFloatArray(arr, len(values)), lib().aclDestroyFloatArray)
 
 
 def bool_array(values):
@@ -300,6 +305,17 @@ def upsample_bicubic2d_backward(grad_out, out_hw, input_size, align_corners=Fals
     osz, isz = int_array(out_hw), int_array(input_size)
     two_phase("aclnnUpsampleBicubic2dBackward", [tg.ptr, osz.ptr, isz.ptr, bool(align_corners), float(scales[0]),
                                                  float(scales[1]), ty.ptr], grad_out.device, workspace)
+    return out
+
+
+def resize(x, scales, mode="bilinear", fmt="NCHW", out=None, workspace=None):
+    """aclnnResize: `scales` has one factor per dimension of x; the output extent is floor(extent * factor)."""
+    if out is None:
+        h_dim, w_dim = (1, 2) if fmt == "NHWC" else (2, 3)
+        out_hw = (int(x.shape[h_dim] * float(scales[h_dim])), int(x.shape[w_dim] * float(scales[w_dim])))
+        out = torch.empty(_out_shape(x, out_hw, fmt), dtype=x.dtype, device=x.device)
+    tx, ty, sc = acl_tensor(x, fmt), acl_tensor(out, fmt), float_array([float(v) for v in scales])
+    two_phase("aclnnResize", [tx.ptr, sc.ptr, mode.encode(), ty.ptr], x.device, workspace)
     return out
 
 

@@ -350,6 +350,33 @@ aclBoolArray* aclCreateBoolArray(const bool* value, uint64_t size)
     return a;
 }
 
+aclFloatArray* aclCreateFloatArray(const float* value, uint64_t size)
+{
+    if (size > 0 && value == nullptr) {
+        return nullptr;
+    }
+    aclFloatArray* a = new (std::nothrow) aclFloatArray();
+    if (a != nullptr) {
+        a->v.assign(value, value + size);
+    }
+    return a;
+}
+
+aclnnStatus aclDestroyFloatArray(const aclFloatArray* array)
+{
+    delete array;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclGetFloatArraySize(const aclFloatArray* array, uint64_t* size)
+{
+    if (array == nullptr || size == nullptr) {
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    *size = array->v.size();
+    return ACLNN_SUCCESS;
+}
+
 aclnnStatus aclDestroyBoolArray(const aclBoolArray* array)
 {
     delete array;

@@ -5,6 +5,7 @@
 // reference's arch35 tiling code.
 #include <cfloat>
 #include <cmath>
+#include <cstring>
 
 #include "host_common.h"
 
@@ -1597,6 +1598,82 @@ aclnnStatus aclnnUpsampleBicubic2dBackward(void* workspace, uint64_t workspaceSi
                                            aclrtStream stream)
 {
     return RunExecutor("aclnnUpsampleBicubic2dBackward", workspace, workspaceSize, executor, stream);
+}
+
+// ===============================================================================================================
+// image/resize_bilinear_v2/op_api/aclnn_resize.cpp:172-190 (CheckParams: null, mode, dtype, format, elements, shape),
+// :245-278 (regbase branch: "nearest" runs ResizeNearestNeighborV2 without scales, align_corners or half-pixel
+// centres, "bilinear" runs ResizeBilinearV2 with half-pixel centres). The output extent is the out tensor's, which the
+// element check ties to floor(extent * scale) within 1e-5 of the scale.
+aclnnStatus aclnnResizeGetWorkspaceSize(const aclTensor* self, const aclFloatArray* scales, const char* mode,
+                                        aclTensor* out, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    static const char* api = "aclnnResize";
+    if (workspaceSize == nullptr || executor == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: workspaceSize or executor is null", api);
+    }
+    if (self == nullptr || scales == nullptr || out == nullptr || mode == nullptr) {
+        return Fail(ACLNN_ERR_PARAM_NULLPTR, "%s: null argument", api);
+    }
+    const bool nearest = std::strncmp(mode, "nearest", 7) == 0;
+    if (!nearest && std::strncmp(mode, "bilinear", 8) != 0) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: mode %s is not nearest or bilinear", api, mode);
+    }
+    if (!DtypeSupported(self->dtype)) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self dtype %s not supported (FLOAT, FLOAT16, BF16)", api,
+                    DtypeName(self->dtype));
+    }
+    if (self->dtype != out->dtype) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: out dtype %s differs from self dtype %s", api, DtypeName(out->dtype),
+                    DtypeName(self->dtype));
+    }
+    if (self->format != out->format) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: the format of self and out must be the same", api);
+    }
+    if (self->format != ACL_FORMAT_NCHW && self->format != ACL_FORMAT_NHWC) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: the format of self must be NCHW or NHWC, got %s", api,
+                    FormatName(self->format));
+    }
+    if (self->dims.size() != 4 || out->dims.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: self and out must be 4-D", api);
+    }
+    if (scales->v.size() != 4) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: scales must have 4 values, got %zu", api, scales->v.size());
+    }
+    const Geom gi = GeomOf(self), go = GeomOf(out);
+    if (gi.n != go.n || gi.c != go.c) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: the batch or channel extent of self and out differ", api);
+    }
+    const bool nhwc = self->format == ACL_FORMAT_NHWC;
+    const double sh = static_cast<double>(scales->v[nhwc ? 1 : 2]), sw = static_cast<double>(scales->v[nhwc ? 2 : 3]);
+    const double eps = 1e-5;
+    const int64_t hMax = static_cast<int64_t>(static_cast<double>(gi.h) * (sh + eps));
+    const int64_t hMin = static_cast<int64_t>(static_cast<double>(gi.h) * (sh - eps));
+    const int64_t wMax = static_cast<int64_t>(static_cast<double>(gi.w) * (sw + eps));
+    const int64_t wMin = static_cast<int64_t>(static_cast<double>(gi.w) * (sw - eps));
+    if (go.h < hMin || go.h > hMax) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: the height of out (%ld) does not match %ld * %f", api, (long)go.h,
+                    (long)gi.h, sh);
+    }
+    if (go.w < wMin || go.w > wMax) {
+        return Fail(ACLNN_ERR_PARAM_INVALID, "%s: the width of out (%ld) does not match %ld * %f", api, (long)go.w,
+                    (long)gi.w, sw);
+    }
+    aclIntArray size;
+    size.v = {go.h, go.w};
+    const aclnnStatus st = nearest
+                               ? aclnnUpsampleNearest2dGetWorkspaceSize(self, &size, out, workspaceSize, executor)
+                               : aclnnUpsampleBilinear2dGetWorkspaceSize(self, &size, false, 0.0, 0.0, out,
+                                                                         workspaceSize, executor);
+    if (st == ACLNN_SUCCESS && *executor != nullptr) {
+        (*executor)->api = api;
+    }
+    return st;
+}
+
+aclnnStatus aclnnResize(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    return RunExecutor("aclnnResize", workspace, workspaceSize, executor, stream);
 }
 
 // ===============================================================================================================

@@ -28,6 +28,10 @@ struct aclBoolArray {
     std::vector<uint8_t> v;
 };
 
+struct aclFloatArray {
+    std::vector<float> v;
+};
+
 namespace opscv {
 
 using Step = std::function<cudaError_t(char* ws, cudaStream_t stream)>;

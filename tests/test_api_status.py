@@ -234,6 +234,34 @@ def test_nearest_exact_1d_status(ops):
     assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, T(ops, (2, 4, 8), fmt="NCL").ptr)[0] == INVALID
 
 
+def FA(ops, values):
+    h = ops.float_array(values)
+    _KEEP.append(h)
+    return h
+
+
+def test_resize_status(ops):
+    api = "aclnnResize"
+    x, y, sc = T(ops, (2, 3, 8, 8)), T(ops, (2, 3, 16, 12)), FA(ops, [1.0, 1.0, 2.0, 1.5])
+    for mode in (b"nearest", b"bilinear", b"nearest-anything"):
+        assert phase1(ops, api, x.ptr, sc.ptr, mode, y.ptr)[0] == OK
+    assert phase1(ops, api, None, sc.ptr, b"nearest", y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, None, b"nearest", y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sc.ptr, None, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sc.ptr, b"nearest", None)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sc.ptr, b"bicubic", y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, FA(ops, [2.0, 1.5]).ptr, b"nearest", y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, FA(ops, [1.0, 1.0, 2.0, 2.0]).ptr, b"nearest", y.ptr)[0] == INVALID   # width 16 != 12
+    assert phase1(ops, api, x.ptr, sc.ptr, b"nearest", T(ops, (2, 4, 16, 12)).ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sc.ptr, b"nearest", T(ops, (2, 3, 16, 12), torch.float16).ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 3, 8, 8), fmt="ND").ptr, sc.ptr, b"nearest", T(ops, (2, 3, 16, 12), fmt="ND").ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 8, 8, 3), fmt="NHWC").ptr, FA(ops, [1.0, 2.0, 1.5, 1.0]).ptr, b"bilinear",
+                  T(ops, (2, 16, 12, 3), fmt="NHWC").ptr)[0] == OK
+    n = ctypes.c_uint64(0)
+    assert ops.lib().aclGetFloatArraySize(sc.ptr, ctypes.byref(n)) == 0 and n.value == 4
+    assert ops.lib().aclGetFloatArraySize(None, ctypes.byref(n)) != 0
+
+
 def test_bilinear_aa_status(ops):
     """aclnnUpsampleBilinear2dAA / ...Backward: the checks of the bicubic-AA pair (NCHW or ND only, one dtype, 4-D,
     sizes > 0) plus negative scales in the forward."""
