@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the resampling hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload default|cfg2|cfg3|cfg4|cfg4bf16|cfg5|all]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload default|cfg2|cfg3|cfg4|cfg4bf16|cfg5|adj2|adj3|all]
                     [--batch-div D] [--impl reference]
 
 One "step" is one pass of every operator of the workload over one batch of seeded synthetic input, called
@@ -222,6 +222,65 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
                             else "uniform[-1.1,1.1]"), "dtype": "f32" if es == 4 else "bf16"}
         return buffers, oplist, cfg
 
+    if name == "adj2":
+        # the operators next to the path at the cfg2 shapes: UpsampleNearestExact2d and UpsampleBicubic2d
+        n, c, hi, wi, ho, wo = 32 // batch_div, 256, 56, 56, 112, 112
+        dt = torch.float16
+
+        def buffers(gen):
+            return {
+                "x": torch.randn((n, c, hi, wi), generator=gen, device=gen.device).to(dt),
+                "go": torch.randn((n, c, ho, wo), generator=gen, device=gen.device).to(dt),
+                "y_exact": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "y_bicubic": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "gi_exact": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
+                "gi_bicubic": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
+            }
+        small, big = n * c * hi * wi * 2, n * c * ho * wo * 2
+        oplist = [
+            Op("UpsampleNearestExact2d", lambda b: ops.upsample_nearest_exact2d(b["x"], (ho, wo), out=b["y_exact"],
+                                                                                workspace=wss[0]),
+               small + big, n * ho * wo, ["x"], ["y_exact"]),
+            Op("UpsampleBicubic2d", lambda b: ops.upsample_bicubic2d(b["x"], (ho, wo), False, out=b["y_bicubic"],
+                                                                     workspace=wss[1]),
+               small + big, n * ho * wo, ["x"], ["y_bicubic"]),
+            Op("UpsampleNearestExact2dBackward", lambda b: ops.upsample_nearest_exact2d_backward(
+                b["go"], (ho, wo), (n, c, hi, wi), out=b["gi_exact"], workspace=wss[2]),
+               small + big, n * ho * wo, ["go"], ["gi_exact"]),
+            Op("UpsampleBicubic2dBackward", lambda b: ops.upsample_bicubic2d_backward(
+                b["go"], (ho, wo), (n, c, hi, wi), False, out=b["gi_bicubic"], workspace=wss[3]),
+               small + big, n * ho * wo, ["go"], ["gi_bicubic"]),
+        ]
+        cfg = {"workload": "operators next to the path at the FPN shapes: UpsampleNearestExact2d + UpsampleBicubic2d "
+                           f"forward and backward, fp16 NCHW N={n} C=256 56x56 -> 112x112, align_corners=false",
+               "dtype": "f16"}
+        return buffers, oplist, cfg
+
+    if name == "adj3":
+        # UpsampleBilinear2dAA at the cfg3 shapes
+        n, c, hi, wi, ho, wo = 64 // batch_div, 3, 1024, 1024, 224, 224
+        dt = torch.float32
+
+        def buffers(gen):
+            return {
+                "x": (torch.randint(0, 256, (n, c, hi, wi), generator=gen, device=gen.device).to(dt) / 255.0),
+                "go": torch.randn((n, c, ho, wo), generator=gen, device=gen.device),
+                "y": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "gi": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
+            }
+        big, small = n * c * hi * wi * 4, n * c * ho * wo * 4
+        oplist = [
+            Op("UpsampleBilinear2dAA", lambda b: ops.upsample_bilinear2d_aa(b["x"], (ho, wo), False, out=b["y"],
+                                                                            workspace=wss[0]),
+               small + big, n * ho * wo, ["x"], ["y"]),
+            Op("UpsampleBilinear2dAABackward", lambda b: ops.upsample_bilinear2d_aa_backward(
+                b["go"], (ho, wo), (n, c, hi, wi), False, out=b["gi"], workspace=wss[1]),
+               small + big, n * ho * wo, ["go"], ["gi"]),
+        ]
+        cfg = {"workload": f"UpsampleBilinear2dAA forward and backward, fp32 NCHW N={n} C=3 1024x1024 -> 224x224 "
+                           "(triangle filter, support = scale), align_corners=false", "dtype": "f32"}
+        return buffers, oplist, cfg
+
     if name == "cfg5":
         import math
         n, c, hi, wi, ho, wo = 512 // batch_div, 256, 64, 64, 128, 128
@@ -410,6 +469,39 @@ def cpu_baseline(workload, budget_s=12.0, torch_budget_s=6.0):
             torch.ops.aten._upsample_bicubic2d_aa_backward(got, [224, 224], [1, 3, 1024, 1024], False, None, None)
         algo = 2 * (x.size + go.size) * 4
         sample = "N=1 of 64 images, forward + backward (scatter definition)"
+    elif workload == "adj2":
+        n, c = 4, 256
+        x = rng.standard_normal((n, c, 56, 56)).astype(np.float32)
+        go = rng.standard_normal((n, c, 112, 112)).astype(np.float32)
+
+        def run():
+            oracle.nearest_exact2d_fwd(x, (112, 112))
+            oracle.bicubic2d_fwd(x, (112, 112), False)
+            oracle.nearest_exact2d_bwd(go, (56, 56))
+            oracle.bicubic2d_bwd(go, (56, 56), False, definition="dispatch")
+        xt, got = torch.from_numpy(x), torch.from_numpy(go)
+
+        def run_torch():
+            F.interpolate(xt, size=(112, 112), mode="nearest-exact")
+            F.interpolate(xt, size=(112, 112), mode="bicubic", align_corners=False)
+            torch.ops.aten._upsample_nearest_exact2d_backward(got, [112, 112], [n, c, 56, 56], None, None)
+            torch.ops.aten.upsample_bicubic2d_backward(got, [112, 112], [n, c, 56, 56], False, None, None)
+        algo = 4 * (x.size + go.size) * 2
+        sample = f"N={n} of 32 images (C={c}), all four operators, fp32 arithmetic"
+    elif workload == "adj3":
+        x = rng.random((1, 3, 1024, 1024), dtype=np.float32)
+        go = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
+
+        def run():
+            oracle.bilinear_aa_fwd(x, (224, 224))
+            oracle.bilinear_aa_bwd(go, (1024, 1024), definition="scatter")
+        xt, got = torch.from_numpy(x), torch.from_numpy(go)
+
+        def run_torch():
+            F.interpolate(xt, size=(224, 224), mode="bilinear", align_corners=False, antialias=True)
+            torch.ops.aten._upsample_bilinear2d_aa_backward(got, [224, 224], [1, 3, 1024, 1024], False, None, None)
+        algo = 2 * (x.size + go.size) * 4
+        sample = "N=1 of 64 images, forward + backward (scatter definition)"
     elif workload in ("cfg4", "cfg4bf16", "cfg4affine"):
         es = 4 if workload == "cfg4" else 2
         x = rng.standard_normal((1, 256, 64, 64)).astype(np.float32)
@@ -479,9 +571,9 @@ def arm_config(cfg):
 
 
 METRIC = "effective HBM GB/s (algorithmic bytes / device time), all operators of the step"
-OTHER_WORKLOADS = ["cfg3", "cfg4", "cfg4bf16", "cfg5"]
+OTHER_WORKLOADS = ["cfg3", "cfg4", "cfg4bf16", "cfg5", "adj2", "adj3"]
 LAUNCH_NOTE = ("CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding "
-               "all operators of the step (cfg2, cfg3, cfg5: the independent operators of a step on parallel branches, "
+               "all operators of the step (cfg2, cfg3, cfg5, adj2, adj3: the independent operators of a step on parallel branches, "
                "each with its own workspace; cfg4: one after the other, the two backward modes write the same tensors); "
                "the per-operator times come from a separate pass: per-operator graphs launched back to back over all "
                "buffer sets between one pair of events")
@@ -679,7 +771,7 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak, steps, d
         # Operators that share no output buffer (and no workspace) go on parallel branches of the graph: the tail of
         # one kernel then overlaps the head of the next instead of waiting for it.
         outs = [set(op.outputs) for op in oplist]
-        parallel = (wname in ("cfg2", "cfg3", "cfg5") and not args.serial_step and
+        parallel = (wname in ("cfg2", "cfg3", "cfg5", "adj2", "adj3") and not args.serial_step and
                     all(outs[a].isdisjoint(outs[b]) for a in range(len(outs)) for b in range(a)))
         branches = [torch.cuda.Stream(dev) for _ in oplist] if parallel else []
 

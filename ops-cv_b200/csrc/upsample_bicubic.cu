@@ -1,8 +1,9 @@
 // UpsampleBicubic2d forward and backward (cubic convolution with A = -0.75, no antialiasing), NCHW and NHWC.
 //
-// Forward: one thread per output element; the sixteen clamped taps are read through the read-only path and
-// combined in the reference's order (four row sums left to right, then the column sum), every operation rounded
-// on its own, so fp32 results carry the bits of a serial CPU statement of
+// Forward: a thread owns one or two adjacent elements of an output row and walks down a band of rows, keeping the
+// four horizontal sums of the current source rows in registers; the sixteen clamped taps are combined in the
+// reference's order (four row sums left to right, then the column sum), every operation rounded on its own, so
+// fp32 results carry the bits of a serial CPU statement of
 // image/resize_bicubic_v2/op_kernel/arch35/resize_bicubic_v2_simt_base.h:23-120. The four special schedules of
 // resize_bicubic_v2_simt_nchw.h:50-90 (copy, one input pixel, one output pixel, integer positions) are selected on
 // the host with the reference's rule and are plain copies here too.
@@ -12,7 +13,8 @@
 // gather kernel (image/resize_bicubic_v2_grad/op_kernel/arch35/resize_bicubic_v2_grad_simt_determine.h:95-350):
 // an axis on which the element is interior is walked by distance to the source position, a first or last index
 // tap by tap with clamped destinations. The sum has a fixed order, so results are reproducible from run to run
-// and fp32 results carry the bits of that kernel run serially.
+// and fp32 results carry the bits of that kernel run serially. The column side of the walk is the same for every
+// row, so each thread evaluates it once into a shared-memory list.
 #include <algorithm>
 
 #include "launch_util.cuh"
@@ -64,6 +66,7 @@ __device__ __forceinline__ int32_t ClampIdx(long long v, int32_t last)
 {
     return static_cast<int32_t>(v < 0 ? 0 : (v > last ? last : v));
 }
+__device__ __forceinline__ int32_t ClampIdx32(int32_t v, int32_t last) { return min(max(v, 0), last); }
 
 struct BicubicGeom {
     int64_t rows;  // forward: planes * hout; backward: planes * hin
@@ -74,8 +77,9 @@ struct BicubicGeom {
     int32_t schedule;
 };
 
+// Copy schedules (one input pixel, one output pixel, integer source positions): no arithmetic.
 template <typename T, bool NHWC>
-__global__ void __launch_bounds__(kThreads) Bicubic2dFwdKernel(const T* __restrict__ x, T* __restrict__ y, BicubicGeom g)
+__global__ void __launch_bounds__(kThreads) Bicubic2dFwdCopyKernel(const T* __restrict__ x, T* __restrict__ y, BicubicGeom g)
 {
     const int32_t inner = g.wout * g.chan;
     const int64_t planeIn = static_cast<int64_t>(g.hin) * g.win * g.chan;
@@ -85,15 +89,8 @@ __global__ void __launch_bounds__(kThreads) Bicubic2dFwdKernel(const T* __restri
         const int32_t H = static_cast<int32_t>(row - plane * g.hout);
         const float oh = g.align ? Mul(static_cast<float>(H), g.scaleH)
                                  : Sub(Mul(Add(static_cast<float>(H), 0.5f), g.scaleH), 0.5f);
-        const float fh = floorf(oh);
-        const long long top = static_cast<long long>(fh);
-        float ch[4];
-        FwdCoeff(Sub(oh, fh), ch);
         const T* px = x + plane * planeIn;
-        const T* r0 = px + ClampIdx(top - 1, g.hin - 1) * rowIn;
-        const T* r1 = px + ClampIdx(top, g.hin - 1) * rowIn;
-        const T* r2 = px + ClampIdx(top + 1, g.hin - 1) * rowIn;
-        const T* r3 = px + ClampIdx(top + 2, g.hin - 1) * rowIn;
+        const T* r1 = px + ClampIdx(static_cast<long long>(floorf(oh)), g.hin - 1) * rowIn;
         T* py = y + row * inner;
         for (int32_t t = blockIdx.x * kThreads + threadIdx.x; t < inner; t += gridDim.x * kThreads) {
             const int32_t W = NHWC ? t / g.chan : t;
@@ -104,26 +101,120 @@ __global__ void __launch_bounds__(kThreads) Bicubic2dFwdKernel(const T* __restri
             }
             const float ow = g.align ? Mul(static_cast<float>(W), g.scaleW)
                                      : Sub(Mul(Add(static_cast<float>(W), 0.5f), g.scaleW), 0.5f);
-            const float fw = floorf(ow);
-            const long long left = static_cast<long long>(fw);
-            if (g.schedule == 4) { // integer source positions: the pixel itself
-                py[t] = r1[static_cast<int64_t>(ClampIdx(left, g.win - 1)) * g.chan + c];
-                continue;
+            const long long left = static_cast<long long>(floorf(ow));
+            py[t] = r1[static_cast<int64_t>(ClampIdx(left, g.win - 1)) * g.chan + c]; // integer positions
+        }
+    }
+}
+
+// General schedule. A thread owns V adjacent elements of an output row (one column for NHWC: its channel of one
+// pixel) and walks down a band of output rows. The four horizontal sums that an output row needs are kept in
+// registers and shifted as the source row advances: an input row's horizontal sum is computed once per band and
+// column instead of once per output row that uses it, and the vertical combination stays the reference's
+// left-to-right sum of four products, so the bits do not change.
+template <typename T, bool NHWC, int V>
+__global__ void __launch_bounds__(kThreads) Bicubic2dFwdKernel(const T* __restrict__ x, T* __restrict__ y, BicubicGeom g,
+                                                                int32_t bandRows, int32_t bands)
+{
+    // per output row of the band: the source row above the four taps and the four vertical coefficients, evaluated
+    // once per band by the block instead of once per row by every thread
+    extern __shared__ float sRow[];
+    float* sCh = sRow;                                                   // [bandRows][4]
+    int32_t* sTop = reinterpret_cast<int32_t*>(sRow + 4 * bandRows);     // [bandRows]
+    const int32_t inner = g.wout * g.chan;
+    const int32_t t0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    const bool active = t0 < inner;
+    const int64_t planeIn = static_cast<int64_t>(g.hin) * g.win * g.chan;
+    const int64_t rowIn = static_cast<int64_t>(g.win) * g.chan;
+    // per-column taps and weights (V columns)
+    int32_t off[V][4];
+    float cw[V][4];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        const int32_t t = active ? t0 + v : 0;
+        const int32_t W = NHWC ? t / g.chan : t;
+        const int32_t c = NHWC ? t - W * g.chan : 0;
+        const float ow = g.align ? Mul(static_cast<float>(W), g.scaleW)
+                                 : Sub(Mul(Add(static_cast<float>(W), 0.5f), g.scaleW), 0.5f);
+        const float fw = floorf(ow);
+        const long long left = static_cast<long long>(fw);
+        FwdCoeff(Sub(ow, fw), cw[v]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            off[v][j] = ClampIdx(left - 1 + j, g.win - 1) * g.chan + c;
+        }
+    }
+    int32_t tableBand = -1;
+    for (int64_t item = blockIdx.y; item < g.rows; item += gridDim.y) { // g.rows = planes * bands here
+        const int64_t plane = item / bands;
+        const int32_t band = static_cast<int32_t>(item - plane * bands);
+        const int32_t h0 = band * bandRows;
+        const int32_t h1 = min(h0 + bandRows, g.hout);
+        if (band != tableBand) { // uniform over the block
+            __syncthreads();
+            for (int32_t r = threadIdx.x; r < h1 - h0; r += blockDim.x) {
+                const int32_t H = h0 + r;
+                const float oh = g.align ? Mul(static_cast<float>(H), g.scaleH)
+                                         : Sub(Mul(Add(static_cast<float>(H), 0.5f), g.scaleH), 0.5f);
+                const float fh = floorf(oh);
+                float ch[4];
+                FwdCoeff(Sub(oh, fh), ch);
+                // tops outside [-2, hin + 1] clamp every tap to the same row as the bound does
+                const float lim = fminf(fmaxf(fh, -2.0f), static_cast<float>(g.hin) + 1.0f);
+                sTop[r] = static_cast<int32_t>(lim);
+                sCh[4 * r + 0] = ch[0];
+                sCh[4 * r + 1] = ch[1];
+                sCh[4 * r + 2] = ch[2];
+                sCh[4 * r + 3] = ch[3];
             }
-            float cw[4];
-            FwdCoeff(Sub(ow, fw), cw);
-            const int64_t w0 = static_cast<int64_t>(ClampIdx(left - 1, g.win - 1)) * g.chan + c;
-            const int64_t w1 = static_cast<int64_t>(ClampIdx(left, g.win - 1)) * g.chan + c;
-            const int64_t w2 = static_cast<int64_t>(ClampIdx(left + 1, g.win - 1)) * g.chan + c;
-            const int64_t w3 = static_cast<int64_t>(ClampIdx(left + 2, g.win - 1)) * g.chan + c;
-            auto rowSum = [&](const T* r) {
-                const float v0 = DType<T>::Load(r + w0), v1 = DType<T>::Load(r + w1), v2 = DType<T>::Load(r + w2),
-                            v3 = DType<T>::Load(r + w3);
-                return Add(Add(Add(Mul(v0, cw[0]), Mul(v1, cw[1])), Mul(v2, cw[2])), Mul(v3, cw[3]));
-            };
-            const float s0 = rowSum(r0), s1 = rowSum(r1), s2 = rowSum(r2), s3 = rowSum(r3);
-            const float out = Add(Add(Add(Mul(s0, ch[0]), Mul(s1, ch[1])), Mul(s2, ch[2])), Mul(s3, ch[3]));
-            py[t] = DType<T>::FromF(out);
+            __syncthreads();
+            tableBand = band;
+        }
+        if (!active) {
+            continue;
+        }
+        const T* px = x + plane * planeIn;
+        T* py = y + (plane * g.hout + h0) * static_cast<int64_t>(inner) + t0;
+        float rs[V][4];
+        int32_t curTop = 0;
+        bool have = false;
+        auto rowSums = [&](int32_t srcRow, int slot) {
+            const T* r = px + ClampIdx32(srcRow, g.hin - 1) * rowIn;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const float v0 = DType<T>::Load(r + off[v][0]), v1 = DType<T>::Load(r + off[v][1]),
+                            v2 = DType<T>::Load(r + off[v][2]), v3 = DType<T>::Load(r + off[v][3]);
+                rs[v][slot] = Add(Add(Add(Mul(v0, cw[v][0]), Mul(v1, cw[v][1])), Mul(v2, cw[v][2])), Mul(v3, cw[v][3]));
+            }
+        };
+        for (int32_t r = 0; r < h1 - h0; ++r, py += inner) {
+            const int32_t top = sTop[r];
+            const float4 ch = *reinterpret_cast<const float4*>(sCh + 4 * r);
+            const int32_t shift = top - curTop;
+            if (!have || shift < 0 || shift >= 4) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    rowSums(top - 1 + k, k);
+                }
+                have = true;
+            } else {
+                for (int32_t sft = 0; sft < shift; ++sft) {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        rs[v][0] = rs[v][1];
+                        rs[v][1] = rs[v][2];
+                        rs[v][2] = rs[v][3];
+                    }
+                    rowSums(curTop + sft + 3, 3);
+                }
+            }
+            curTop = top;
+            float out[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                out[v] = Add(Add(Add(Mul(rs[v][0], ch.x), Mul(rs[v][1], ch.y)), Mul(rs[v][2], ch.z)), Mul(rs[v][3], ch.w));
+            }
+            StorePack<T, V>(py, out);
         }
     }
 }
@@ -141,96 +232,350 @@ __device__ __forceinline__ int32_t WalkStart(int32_t yIdx, float inverse, float 
     return static_cast<int32_t>(s < 0 ? 0 : (s > INT32_MAX ? INT32_MAX : s));
 }
 
-template <typename T, bool NHWC>
-__global__ void __launch_bounds__(kThreads) Bicubic2dBwdKernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g)
+// One grad_input element by the reference's walk, with nothing cached: the coefficients of a column are evaluated
+// again for every row. Used for elements whose column list does not fit the shared-memory lists of the kernel
+// below (an extent of 1 makes every grads index a tap of the single element).
+template <typename T>
+__device__ float BwdElementDirect(const T* __restrict__ pg, const BicubicGeom& g, int32_t yh, int32_t yw, int32_t c,
+                                  int64_t rowGo, float offset)
 {
+    const int32_t hStart = WalkStart(yh, g.invH, offset);
+    const float rhStart = Sub(Mul(Add(static_cast<float>(hStart), offset), g.scaleH), offset);
+    const bool borderH = yh == 0 || yh == g.hin - 1;
+    const int32_t wStart = WalkStart(yw, g.invW, offset);
+    const float rwStart = Sub(Mul(Add(static_cast<float>(wStart), offset), g.scaleW), offset);
+    const bool borderW = yw == 0 || yw == g.win - 1;
+    float add = 0.0f;
+    float rh = rhStart;
+    for (int32_t h = hStart; h < g.hout; ++h, rh = BwdSrc(g.scaleH, h, g.align)) {
+        float chTap[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float chPoint = 0.0f;
+        long long fh = 0;
+        if (borderH) {
+            fh = static_cast<long long>(floorf(rh));
+            if (yh == 0 && fh > 1 && g.hin > 1) {
+                break;
+            }
+            TapCoeff(Sub(rh, static_cast<float>(fh)), chTap);
+        } else {
+            if (!(rh < Add(static_cast<float>(yh), 2.0f))) {
+                break;
+            }
+            chPoint = PointCoeff(fabsf(Sub(rh, static_cast<float>(yh))));
+        }
+        const T* prow = pg + h * rowGo + c;
+        float rw = rwStart;
+        for (int32_t w = wStart; w < g.wout; ++w, rw = BwdSrc(g.scaleW, w, g.align)) {
+            float cwTap[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float cwPoint = 0.0f;
+            long long fw = 0;
+            if (borderW) {
+                fw = static_cast<long long>(floorf(rw));
+                if (yw == 0 && fw > 1 && g.win > 1) {
+                    break;
+                }
+                TapCoeff(Sub(rw, static_cast<float>(fw)), cwTap);
+            } else {
+                if (!(rw < Add(static_cast<float>(yw), 2.0f))) {
+                    break;
+                }
+                cwPoint = PointCoeff(fabsf(Sub(rw, static_cast<float>(yw))));
+            }
+            const float gv = DType<T>::Load(prow + static_cast<int64_t>(w) * g.chan);
+            if (!borderH && !borderW) {
+                add = Add(add, Mul(Mul(gv, chPoint), cwPoint));
+            } else if (!borderH) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (ClampIdx(fw - 1 + j, g.win - 1) == yw) {
+                        add = Add(add, Mul(Mul(gv, chPoint), cwTap[j]));
+                    }
+                }
+            } else if (!borderW) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (ClampIdx(fh - 1 + i, g.hin - 1) == yh) {
+                        add = Add(add, Mul(Mul(gv, chTap[i]), cwPoint));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (ClampIdx(fh - 1 + i, g.hin - 1) == yh && ClampIdx(fw - 1 + j, g.win - 1) == yw) {
+                            add = Add(add, Mul(Mul(gv, chTap[i]), cwTap[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    return add;
+}
+
+// The gather with the column side of the walk cached. A thread owns one element position of a grad_input row
+// (column yw; for NHWC also its channel) and keeps it while the block moves over rows and planes. It first walks
+// the grads columns once, exactly as the reference does, and stores every term it would add for one grads row as
+// an entry (grads column, coefficient) in its own column of a shared-memory table: one entry per grads column for
+// an interior yw, one per matching tap for a first or last yw. For each grads row h of the row walk it then has
+// one coefficient (interior yh) or the matching tap coefficients in tap order (first or last yh), and adds
+// (g * cH) * cW over the entries, grouped by grads column with the row taps outside the column taps. That is the
+// order and the rounding of the reference's four walks, so the sum has the same bits.
+// colsPB: element positions of a row that a block covers (its threads beyond that take further rows);
+// borderOnly: the block's positions are those of the first and the last column only.
+template <typename T, bool NHWC>
+__global__ void __launch_bounds__(kThreads) Bicubic2dBwdListKernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g,
+                                                                    int32_t maxW, int32_t colsPB, int32_t borderOnly)
+{
+    extern __shared__ float sList[];
+    const int32_t nt = blockDim.x, tid = threadIdx.x;
+    float* sCoef = sList;
+    int32_t* sCol = reinterpret_cast<int32_t*>(sList + static_cast<size_t>(maxW) * nt);
     const int32_t inner = g.win * g.chan;
+    const int32_t rowsPB = nt / colsPB;
+    const int32_t rowLane = tid / colsPB;
+    const int32_t pos = blockIdx.x * colsPB + (tid - rowLane * colsPB);
+    if (rowLane >= rowsPB || pos >= (borderOnly ? 2 * g.chan : inner)) {
+        return;
+    }
+    int32_t t = pos;
+    if (borderOnly) {
+        const int32_t side = NHWC ? pos / g.chan : pos;
+        t = side == 0 ? pos : inner - 2 * g.chan + pos; // column 0 or column win - 1, same channel
+    }
+    const int32_t yw = NHWC ? t / g.chan : t;
+    const int32_t c = NHWC ? t - yw * g.chan : 0;
     const int64_t planeGo = static_cast<int64_t>(g.hout) * g.wout * g.chan;
     const int64_t rowGo = static_cast<int64_t>(g.wout) * g.chan;
     const float offset = g.align ? 0.0f : 0.5f;
+    const bool borderW = yw == 0 || yw == g.win - 1;
+
+    // the column walk, once
+    int32_t cnt = 0;
+    bool overflow = false;
+    const int32_t wStart = WalkStart(yw, g.invW, offset);
+    {
+        float rw = Sub(Mul(Add(static_cast<float>(wStart), offset), g.scaleW), offset);
+        for (int32_t w = wStart; w < g.wout && !overflow; ++w, rw = BwdSrc(g.scaleW, w, g.align)) {
+            if (borderW) {
+                const long long fw = static_cast<long long>(floorf(rw));
+                if (yw == 0 && fw > 1 && g.win > 1) {
+                    break;
+                }
+                float cwTap[4];
+                TapCoeff(Sub(rw, static_cast<float>(fw)), cwTap);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (ClampIdx(fw - 1 + j, g.win - 1) == yw) {
+                        if (cnt < maxW) {
+                            sCoef[cnt * nt + tid] = cwTap[j];
+                            sCol[cnt * nt + tid] = w;
+                            ++cnt;
+                        } else {
+                            overflow = true;
+                        }
+                    }
+                }
+            } else {
+                if (!(rw < Add(static_cast<float>(yw), 2.0f))) {
+                    break;
+                }
+                if (cnt < maxW) {
+                    sCoef[cnt * nt + tid] = PointCoeff(fabsf(Sub(rw, static_cast<float>(yw))));
+                    sCol[cnt * nt + tid] = w;
+                    ++cnt;
+                } else {
+                    overflow = true;
+                }
+            }
+        }
+    }
+
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * rowsPB + rowLane; row < g.rows;
+         row += static_cast<int64_t>(gridDim.y) * rowsPB) {
+        const int64_t plane = row / g.hin;
+        const int32_t yh = static_cast<int32_t>(row - plane * g.hin);
+        const T* pg = go + plane * planeGo;
+        T* po = gi + row * inner;
+        if (overflow) {
+            po[t] = DType<T>::FromF(BwdElementDirect<T>(pg, g, yh, yw, c, rowGo, offset));
+            continue;
+        }
+        const bool borderH = yh == 0 || yh == g.hin - 1;
+        const int32_t hStart = WalkStart(yh, g.invH, offset);
+        float rh = Sub(Mul(Add(static_cast<float>(hStart), offset), g.scaleH), offset);
+        float add = 0.0f;
+        for (int32_t h = hStart; h < g.hout; ++h, rh = BwdSrc(g.scaleH, h, g.align)) {
+            const T* prow = pg + h * rowGo + c;
+            if (!borderH) {
+                if (!(rh < Add(static_cast<float>(yh), 2.0f))) {
+                    break;
+                }
+                const float ch = PointCoeff(fabsf(Sub(rh, static_cast<float>(yh))));
+                // one row coefficient: the entries in list order are already the reference's order
+                for (int32_t k = 0; k < cnt; ++k) {
+                    const float gv = DType<T>::Load(prow + static_cast<int64_t>(sCol[k * nt + tid]) * g.chan);
+                    add = Add(add, Mul(Mul(gv, ch), sCoef[k * nt + tid]));
+                }
+                continue;
+            }
+            const long long fh = static_cast<long long>(floorf(rh));
+            if (yh == 0 && fh > 1 && g.hin > 1) {
+                break;
+            }
+            float chTap[4];
+            TapCoeff(Sub(rh, static_cast<float>(fh)), chTap);
+            float chv[4];
+            int nH = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (ClampIdx(fh - 1 + i, g.hin - 1) == yh) {
+                    // compacted in tap order without dynamic register indexing
+                    chv[3] = chTap[i];
+                    if (nH == 0) chv[0] = chTap[i];
+                    if (nH == 1) chv[1] = chTap[i];
+                    if (nH == 2) chv[2] = chTap[i];
+                    ++nH;
+                }
+            }
+            int32_t k = 0;
+            while (k < cnt) {
+                const int32_t w = sCol[k * nt + tid];
+                int32_t k1 = k + 1;
+                while (k1 < cnt && sCol[k1 * nt + tid] == w) {
+                    ++k1;
+                }
+                const float gv = DType<T>::Load(prow + static_cast<int64_t>(w) * g.chan);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (i < nH) {
+                        const float gc = Mul(gv, i == 3 ? chv[3] : (i == 2 ? chv[2] : (i == 1 ? chv[1] : chv[0])));
+                        for (int32_t kk = k; kk < k1; ++kk) {
+                            add = Add(add, Mul(gc, sCoef[kk * nt + tid]));
+                        }
+                    }
+                }
+                k = k1;
+            }
+        }
+        po[t] = DType<T>::FromF(add);
+    }
+}
+
+// The same gather for the interior columns (1 .. win - 2), whose walk has one coefficient per grads column and at
+// most K columns (every up-scale factor up to (K - 1) / 4, and every down-scale): the list lives in registers and
+// the loop over it is unrolled. The first and the last column go through the list kernel in a launch of their own.
+// Terms, their order and their rounding are those of the list kernel.
+template <typename T, bool NHWC, int K>
+__global__ void __launch_bounds__(kThreads) Bicubic2dBwdRegKernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g)
+{
+    const int32_t inner = g.win * g.chan;
+    const int32_t pos = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pos >= inner - 2 * g.chan) {
+        return;
+    }
+    const int32_t t = pos + g.chan; // skip column 0
+    const int32_t yw = NHWC ? t / g.chan : t;
+    const int32_t c = NHWC ? t - yw * g.chan : 0;
+    const int64_t planeGo = static_cast<int64_t>(g.hout) * g.wout * g.chan;
+    const int64_t rowGo = static_cast<int64_t>(g.wout) * g.chan;
+    const float offset = g.align ? 0.0f : 0.5f;
+
+    float cw[K];
+    int32_t cnt = 0;
+    bool overflow = false;
+    const int32_t wStart = WalkStart(yw, g.invW, offset);
+    {
+        bool done = false;
+#pragma unroll
+        for (int k = 0; k < K + 1; ++k) {
+            const int32_t w = wStart + k;
+            if (k < K) {
+                cw[k] = 0.0f;
+            }
+            if (!done && w < g.wout) {
+                const float rw = k == 0 ? Sub(Mul(Add(static_cast<float>(wStart), offset), g.scaleW), offset)
+                                        : BwdSrc(g.scaleW, w, g.align);
+                if (!(rw < Add(static_cast<float>(yw), 2.0f))) {
+                    done = true;
+                } else if (k == K) {
+                    overflow = true;
+                } else {
+                    cw[k < K ? k : 0] = PointCoeff(fabsf(Sub(rw, static_cast<float>(yw))));
+                    cnt = k + 1;
+                }
+            }
+        }
+    }
+    const int32_t colStep = NHWC ? g.chan : 1; // a compile-time 1 for NCHW: the taps of a row are pw[0 .. K)
+
     for (int64_t row = blockIdx.y; row < g.rows; row += gridDim.y) {
         const int64_t plane = row / g.hin;
         const int32_t yh = static_cast<int32_t>(row - plane * g.hin);
-        const int32_t hStart = WalkStart(yh, g.invH, offset);
-        const float rhStart = Sub(Mul(Add(static_cast<float>(hStart), offset), g.scaleH), offset);
-        const bool borderH = yh == 0 || yh == g.hin - 1;
         const T* pg = go + plane * planeGo;
         T* po = gi + row * inner;
-        for (int32_t t = blockIdx.x * kThreads + threadIdx.x; t < inner; t += gridDim.x * kThreads) {
-            const int32_t yw = NHWC ? t / g.chan : t;
-            const int32_t c = NHWC ? t - yw * g.chan : 0;
-            const int32_t wStart = WalkStart(yw, g.invW, offset);
-            const float rwStart = Sub(Mul(Add(static_cast<float>(wStart), offset), g.scaleW), offset);
-            const bool borderW = yw == 0 || yw == g.win - 1;
-            float add = 0.0f;
-            float rh = rhStart;
+        if (overflow) {
+            po[t] = DType<T>::FromF(BwdElementDirect<T>(pg, g, yh, yw, c, rowGo, offset));
+            continue;
+        }
+        const bool borderH = yh == 0 || yh == g.hin - 1; // uniform over the block
+        const int32_t hStart = WalkStart(yh, g.invH, offset);
+        float rh = Sub(Mul(Add(static_cast<float>(hStart), offset), g.scaleH), offset);
+        float add = 0.0f;
+        const T* pw0 = pg + c + static_cast<int64_t>(wStart) * colStep; // K * chan fits 32 bits (W * C does)
+        if (!borderH) {
             for (int32_t h = hStart; h < g.hout; ++h, rh = BwdSrc(g.scaleH, h, g.align)) {
-                float chTap[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                float chPoint = 0.0f;
-                long long fh = 0;
-                if (borderH) {
-                    const float fl = floorf(rh);
-                    fh = static_cast<long long>(fl);
-                    if (yh == 0 && fh > 1 && g.hin > 1) {
-                        break;
-                    }
-                    TapCoeff(Sub(rh, static_cast<float>(fh)), chTap);
-                } else {
-                    if (!(rh < Add(static_cast<float>(yh), 2.0f))) {
-                        break;
-                    }
-                    chPoint = PointCoeff(fabsf(Sub(rh, static_cast<float>(yh))));
+                if (!(rh < Add(static_cast<float>(yh), 2.0f))) {
+                    break;
                 }
-                const T* prow = pg + h * rowGo + c;
-                float rw = rwStart;
-                for (int32_t w = wStart; w < g.wout; ++w, rw = BwdSrc(g.scaleW, w, g.align)) {
-                    float cwTap[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    float cwPoint = 0.0f;
-                    long long fw = 0;
-                    if (borderW) {
-                        fw = static_cast<long long>(floorf(rw));
-                        if (yw == 0 && fw > 1 && g.win > 1) {
-                            break;
-                        }
-                        TapCoeff(Sub(rw, static_cast<float>(fw)), cwTap);
-                    } else {
-                        if (!(rw < Add(static_cast<float>(yw), 2.0f))) {
-                            break;
-                        }
-                        cwPoint = PointCoeff(fabsf(Sub(rw, static_cast<float>(yw))));
+                const float ch = PointCoeff(fabsf(Sub(rh, static_cast<float>(yh))));
+                const T* pw = pw0 + h * rowGo;
+                float gv[K];
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    gv[k] = k < cnt ? DType<T>::Load(pw + k * colStep) : 0.0f;
+                }
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    gv[k] = Mul(Mul(gv[k], ch), cw[k]); // independent of the running sum: issued ahead of it
+                }
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    if (k < cnt) {
+                        add = Add(add, gv[k]);
                     }
-                    const float gv = DType<T>::Load(prow + static_cast<int64_t>(w) * g.chan);
-                    if (!borderH && !borderW) {
-                        add = Add(add, Mul(Mul(gv, chPoint), cwPoint));
-                    } else if (!borderH) {
+                }
+            }
+        } else {
+            for (int32_t h = hStart; h < g.hout; ++h, rh = BwdSrc(g.scaleH, h, g.align)) {
+                const long long fh = static_cast<long long>(floorf(rh));
+                if (yh == 0 && fh > 1 && g.hin > 1) {
+                    break;
+                }
+                float chTap[4];
+                TapCoeff(Sub(rh, static_cast<float>(fh)), chTap);
+                bool hit[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (ClampIdx(fw - 1 + j, g.win - 1) == yw) {
-                                add = Add(add, Mul(Mul(gv, chPoint), cwTap[j]));
-                            }
-                        }
-                    } else if (!borderW) {
+                for (int i = 0; i < 4; ++i) {
+                    hit[i] = ClampIdx(fh - 1 + i, g.hin - 1) == yh;
+                }
+                const T* pw = pw0 + h * rowGo;
+#pragma unroll
+                for (int k = 0; k < K; ++k) {
+                    if (k < cnt) {
+                        const float gvk = DType<T>::Load(pw + k * colStep);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            if (ClampIdx(fh - 1 + i, g.hin - 1) == yh) {
-                                add = Add(add, Mul(Mul(gv, chTap[i]), cwPoint));
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                if (ClampIdx(fh - 1 + i, g.hin - 1) == yh && ClampIdx(fw - 1 + j, g.win - 1) == yw) {
-                                    add = Add(add, Mul(Mul(gv, chTap[i]), cwTap[j]));
-                                }
+                            if (hit[i]) {
+                                add = Add(add, Mul(Mul(gvk, chTap[i]), cw[k]));
                             }
                         }
                     }
                 }
             }
-            po[t] = DType<T>::FromF(add);
         }
+        po[t] = DType<T>::FromF(add);
     }
 }
 
@@ -248,8 +593,9 @@ cudaError_t Bicubic2dFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, f
                          bool halfPixel, int32_t schedule, cudaStream_t s)
 {
     const bool nhwc = lay == kNHWC;
+    const int64_t planes = nhwc ? sh.n : sh.n * sh.c;
     BicubicGeom g;
-    g.rows = (nhwc ? sh.n : sh.n * sh.c) * sh.hout;
+    g.rows = planes * sh.hout;
     g.hin = sh.hin;
     g.win = sh.win;
     g.hout = sh.hout;
@@ -260,12 +606,50 @@ cudaError_t Bicubic2dFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, f
     g.invH = g.invW = 0.0f;
     g.align = halfPixel ? 0 : 1;
     g.schedule = schedule;
-    const dim3 grid = RowGrid(g.rows, static_cast<int64_t>(g.wout) * g.chan);
+    const int64_t inner = static_cast<int64_t>(g.wout) * g.chan;
+    if (schedule != 0) {
+        const dim3 grid = RowGrid(g.rows, inner);
+        OPSCV_DISPATCH_DT(dt, T, {
+            if (nhwc) {
+                Bicubic2dFwdCopyKernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), g);
+            } else {
+                Bicubic2dFwdCopyKernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), g);
+            }
+        });
+        CountLaunch();
+        return cudaGetLastError();
+    }
+    // Two elements per thread for 16-bit tensors (4-byte stores) when rows allow it. Bands: enough (plane, band)
+    // items to fill the device a few times over, but at least 16 output rows each, since every band starts by
+    // computing four horizontal sums afresh.
+    const int v = (DtSize(dt) == 2 && inner % 2 == 0 && Aligned(y, 4)) ? 2 : 1;
+    // a block as wide as the row when the row is short, so that no warp of it is idle
+    const int threads = static_cast<int>(std::min<int64_t>(kThreads, (CeilDiv(inner, v) + 31) / 32 * 32));
+    const int64_t colBlocks = CeilDiv(CeilDiv(inner, v), threads);
+    const int64_t want = static_cast<int64_t>(NumSMs()) * 8 * 4;
+    int64_t bands = std::max<int64_t>(1, std::min<int64_t>(CeilDiv(want, std::max<int64_t>(planes * colBlocks, 1)),
+                                                           std::max<int32_t>(sh.hout / 16, 1)));
+    int32_t bandRows = static_cast<int32_t>(CeilDiv(sh.hout, bands));
+    bandRows = std::min<int32_t>(bandRows, 2048); // 40 KB of row coefficients at most
+    bands = CeilDiv(sh.hout, bandRows);
+    const size_t smem = static_cast<size_t>(bandRows) * 5 * sizeof(float);
+    g.rows = planes * bands;
+    const dim3 grid(static_cast<unsigned>(colBlocks), static_cast<unsigned>(std::min<int64_t>(g.rows, 65535)), 1);
     OPSCV_DISPATCH_DT(dt, T, {
+        const T* px = static_cast<const T*>(x);
+        T* py = static_cast<T*>(y);
         if (nhwc) {
-            Bicubic2dFwdKernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), g);
+            if (v == 2) {
+                Bicubic2dFwdKernel<T, true, 2><<<grid, threads, smem, s>>>(px, py, g, bandRows, static_cast<int32_t>(bands));
+            } else {
+                Bicubic2dFwdKernel<T, true, 1><<<grid, threads, smem, s>>>(px, py, g, bandRows, static_cast<int32_t>(bands));
+            }
         } else {
-            Bicubic2dFwdKernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), g);
+            if (v == 2) {
+                Bicubic2dFwdKernel<T, false, 2><<<grid, threads, smem, s>>>(px, py, g, bandRows, static_cast<int32_t>(bands));
+            } else {
+                Bicubic2dFwdKernel<T, false, 1><<<grid, threads, smem, s>>>(px, py, g, bandRows, static_cast<int32_t>(bands));
+            }
         }
     });
     CountLaunch();
@@ -289,16 +673,72 @@ cudaError_t Bicubic2dBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh,
     g.invW = invW;
     g.align = align ? 1 : 0;
     g.schedule = 0;
-    const dim3 grid = RowGrid(g.rows, static_cast<int64_t>(g.win) * g.chan);
-    OPSCV_DISPATCH_DT(dt, T, {
-        if (nhwc) {
-            Bicubic2dBwdKernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g);
-        } else {
-            Bicubic2dBwdKernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g);
-        }
-    });
-    CountLaunch();
-    return cudaGetLastError();
+    const int64_t inner = static_cast<int64_t>(g.win) * g.chan;
+    const double perScale = invW > 0.0f ? static_cast<double>(invW) : 1.0;
+    // columns of the longest interior walk: 4 / scale within two source pixels either side, one more for rounding
+    const int64_t walk = static_cast<int64_t>(std::ceil(4.0 * perScale)) + 1;
+    const bool split = walk <= 17 && sh.win > 2; // interior columns from registers, the two border columns apart
+    // Entries of one column list: an interior column takes the grads columns of its walk, a first or last column
+    // up to three taps of each column within two and a half source pixels (at most 6 / scale + a few). Lists that
+    // would not fit make their thread fall back to the uncached walk, so the bound only has to be good, not safe;
+    // a single-column image (every grads column is a tap) always falls back.
+    int64_t maxW = static_cast<int64_t>(std::ceil(6.0 * perScale)) + 8;
+    cudaError_t err = cudaSuccess;
+    auto launchList = [&](bool borderOnly) {
+        const int64_t positions = borderOnly ? 2LL * g.chan : inner;
+        const int colsPB = static_cast<int>(std::min<int64_t>(kThreads, positions));
+        const int threads = static_cast<int>(std::min<int64_t>(kThreads, (std::max<int64_t>(colsPB, 64) + 31) / 32 * 32));
+        const int rowsPB = threads / colsPB;
+        const int64_t cap = 96 * 1024 / (8 * threads);
+        const int64_t entries = std::max<int64_t>(4, std::min<int64_t>(maxW, cap));
+        const size_t smem = static_cast<size_t>(entries) * threads * 8;
+        const int64_t gx = CeilDiv(positions, colsPB);
+        const int64_t rowBlocks = CeilDiv(g.rows, rowsPB);
+        const int64_t gyCap = std::max<int64_t>(static_cast<int64_t>(NumSMs()) * 32 / gx, 1);
+        const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(std::min<int64_t>(std::min<int64_t>(rowBlocks, gyCap), 65535)), 1);
+        OPSCV_DISPATCH_DT(dt, T, {
+            auto kernel = nhwc ? Bicubic2dBwdListKernel<T, true> : Bicubic2dBwdListKernel<T, false>;
+            if (smem > 48 * 1024) {
+                err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            }
+            if (err == cudaSuccess) {
+                kernel<<<grid, threads, smem, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g,
+                                                   static_cast<int32_t>(entries), colsPB, borderOnly ? 1 : 0);
+            }
+        });
+        CountLaunch();
+    };
+    if (!split) {
+        launchList(false);
+        return err != cudaSuccess ? err : cudaGetLastError();
+    }
+    {
+        const int64_t positions = inner - 2LL * g.chan;
+        const int threads = static_cast<int>(std::min<int64_t>(kThreads, (positions + 31) / 32 * 32));
+        const int64_t gx = CeilDiv(positions, threads);
+        const int64_t gyCap = std::max<int64_t>(static_cast<int64_t>(NumSMs()) * 32 / gx, 1);
+        const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(std::min<int64_t>(std::min<int64_t>(g.rows, gyCap), 65535)), 1);
+        OPSCV_DISPATCH_DT(dt, T, {
+            const T* pgo = static_cast<const T*>(go);
+            T* pgi = static_cast<T*>(gi);
+            if (walk <= 9) {
+                if (nhwc) {
+                    Bicubic2dBwdRegKernel<T, true, 9><<<grid, threads, 0, s>>>(pgo, pgi, g);
+                } else {
+                    Bicubic2dBwdRegKernel<T, false, 9><<<grid, threads, 0, s>>>(pgo, pgi, g);
+                }
+            } else {
+                if (nhwc) {
+                    Bicubic2dBwdRegKernel<T, true, 17><<<grid, threads, 0, s>>>(pgo, pgi, g);
+                } else {
+                    Bicubic2dBwdRegKernel<T, false, 17><<<grid, threads, 0, s>>>(pgo, pgi, g);
+                }
+            }
+        });
+        CountLaunch();
+    }
+    launchList(true);
+    return err != cudaSuccess ? err : cudaGetLastError();
 }
 
 } // namespace opscv
