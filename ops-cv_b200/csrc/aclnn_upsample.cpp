@@ -80,6 +80,53 @@ struct TableAlloc {
     uint64_t off[4]; // workspace offsets, meaning depends on the table type
 };
 
+// A 4-D view that is not contiguous in its own format but is a dense tensor in the OTHER layout's memory order: an
+// NCHW-format view [N, C, H, W] with the strides of an NHWC-contiguous tensor (what a channels-last framework tensor
+// looks like through an NCHW handle), or an NHWC-format view [N, H, W, C] with NCHW-contiguous strides. `alt`
+// receives the same memory described in that other format, contiguous.
+bool PermutedDense(const aclTensor* t, aclTensor& alt)
+{
+    if (t->dims.size() != 4 || (t->format != ACL_FORMAT_NCHW && t->format != ACL_FORMAT_NHWC) || IsContiguous(t)) {
+        return false;
+    }
+    const bool nchw = t->format == ACL_FORMAT_NCHW;
+    const int64_t n = t->dims[0], c = t->dims[nchw ? 1 : 3], h = t->dims[nchw ? 2 : 1], w = t->dims[nchw ? 3 : 2];
+    const int64_t sn = t->strides[0], sc = t->strides[nchw ? 1 : 3], sh = t->strides[nchw ? 2 : 1],
+                  sw = t->strides[nchw ? 3 : 2];
+    auto is = [](int64_t dim, int64_t stride, int64_t want) { return dim == 1 || stride == want; };
+    alt = *t;
+    if (nchw) { // memory order N, H, W, C
+        if (!(is(c, sc, 1) && is(w, sw, c) && is(h, sh, w * c) && is(n, sn, h * w * c))) {
+            return false;
+        }
+        alt.dims = {n, h, w, c};
+        alt.strides = {h * w * c, w * c, c, 1};
+        alt.format = ACL_FORMAT_NHWC;
+    } else { // memory order N, C, H, W
+        if (!(is(w, sw, 1) && is(h, sh, w) && is(c, sc, h * w) && is(n, sn, c * h * w))) {
+            return false;
+        }
+        alt.dims = {n, c, h, w};
+        alt.strides = {c * h * w, h * w, w, 1};
+        alt.format = ACL_FORMAT_NCHW;
+    }
+    alt.storageDims = alt.dims;
+    return true;
+}
+
+// Both tensors of a call are dense in the other layout: run that layout's kernels on the memory as it is instead
+// of gathering the input into the workspace and scattering the output back (the reference's Contiguous / ViewCopy).
+// Operators whose kernels exist for both layouts call this after their checks.
+bool UseOtherLayout(const aclTensor*& a, const aclTensor*& b, aclTensor& altA, aclTensor& altB)
+{
+    if (a->format != b->format || !PermutedDense(a, altA) || !PermutedDense(b, altB)) {
+        return false;
+    }
+    a = &altA;
+    b = &altB;
+    return true;
+}
+
 // ---- UpsampleNearest2d ----------------------------------------------------------------------------------------
 // image/resize_nearest_neighbor_v2/op_host/arch35/resize_nearest_neighbor_v2_tiling_base.cpp:251-262
 float NearestScale(int64_t in, int64_t out, float userScale)
@@ -138,6 +185,8 @@ aclnnStatus CheckNearestFwd(const char* api, const aclTensor* self, const aclInt
 aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTensor* out, float userScaleH,
                            float userScaleW, uint64_t* workspaceSize, aclOpExecutor** executor, bool exact = false)
 {
+    aclTensor altSelf, altOut;
+    UseOtherLayout(self, out, altSelf, altOut);
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
@@ -288,6 +337,8 @@ RangeAxis RangeAt(char* w, const RangeOffsets& o)
 aclnnStatus PlanCopy(const char* api, const aclTensor* src, const aclTensor* dst, uint64_t* workspaceSize,
                      aclOpExecutor** executor)
 {
+    aclTensor altSrc, altDst;
+    UseOtherLayout(src, dst, altSrc, altDst); // the same dense permutation on both sides: a flat copy
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
@@ -306,9 +357,12 @@ aclnnStatus PlanCopy(const char* api, const aclTensor* src, const aclTensor* dst
 
 // Shared by aclnnUpsampleBilinear2dBackward and ...BackwardV2 (both reach ResizeBilinearV2Grad on arch35).
 aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const aclIntArray* inputSize, bool alignCorners,
-                            double scalesH, double scalesW, aclTensor* out, uint64_t* workspaceSize,
+                            double scalesH, double scalesW, aclTensor* outParam, uint64_t* workspaceSize,
                             aclOpExecutor** executor)
 {
+    const aclTensor* out = outParam;
+    aclTensor altGrad, altOut;
+    UseOtherLayout(gradOut, out, altGrad, altOut);
     const Geom gg = GeomOf(gradOut), gi = GeomOf(out);
     (void)inputSize;
     if (gg.h == gi.h && gg.w == gi.w && gradOut->dtype == out->dtype) {
@@ -583,9 +637,12 @@ aclnnStatus aclnnUpsampleNearest2dBackward(void* workspace, uint64_t workspaceSi
 } // extern "C"
 
 // Window tables and the gather kernel shared by UpsampleNearest2dBackward and UpsampleNearestExact2dBackward.
-static aclnnStatus PlanNearestBwd(const char* api, const aclTensor* gradOut, aclTensor* gradInput, float scaleH,
+static aclnnStatus PlanNearestBwd(const char* api, const aclTensor* gradOut, aclTensor* gradInputParam, float scaleH,
                                   float scaleW, bool exact, uint64_t* workspaceSize, aclOpExecutor** executor)
 {
+    const aclTensor* gradInput = gradInputParam;
+    aclTensor altGrad, altIn;
+    UseOtherLayout(gradOut, gradInput, altGrad, altIn);
     const Geom gg = GeomOf(gradOut), gi = GeomOf(gradInput);
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
@@ -980,9 +1037,12 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     if (!FitsInt32(gi) || !FitsInt32(go)) {
         return Fail(ACLNN_ERR_PARAM_INVALID, "%s: H and W must not exceed INT32_MAX", api);
     }
+    const aclTensor* outT = out;
+    aclTensor altSelf, altOut;
+    UseOtherLayout(self, outT, altSelf, altOut);
     if (gi.h == go.h && gi.w == go.w) {
         // all-copy schedule (resize_bilinear_v2_tiling_arch35.cpp:245-252)
-        return PlanCopy(api, self, out, workspaceSize, executor);
+        return PlanCopy(api, self, outT, workspaceSize, executor);
     }
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
@@ -990,7 +1050,7 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     }
     WsPlan ws;
     const BufRef x = StageInput(self, ws, ex);
-    const BufRef y = StageOutput(out, ws);
+    const BufRef y = StageOutput(outT, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
@@ -1004,7 +1064,7 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
         const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
         return BilinearFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, plan, s, true); // builds the tables if it reads them
     });
-    FinishOutput(out, y, ex);
+    FinishOutput(outT, y, ex);
     ex->workspaceSize = ws.Size();
     *workspaceSize = ws.Size();
     *executor = ex;
@@ -1463,13 +1523,16 @@ aclnnStatus aclnnUpsampleBicubic2dGetWorkspaceSize(const aclTensor* self, const 
     if (schedule == 1) {
         return PlanCopy(api, self, out, workspaceSize, executor);
     }
+    const aclTensor* outT = out;
+    aclTensor altSelf, altOut;
+    UseOtherLayout(self, outT, altSelf, altOut);
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
     const BufRef xin = StageInput(self, ws, ex);
-    const BufRef y = StageOutput(out, ws);
+    const BufRef y = StageOutput(outT, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
@@ -1477,7 +1540,7 @@ aclnnStatus aclnnUpsampleBicubic2dGetWorkspaceSize(const aclTensor* self, const 
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         return Bicubic2dFwd(dt, lay, xin.At(w), y.At(w), sh, sH, sW, halfPixel, schedule, s);
     });
-    FinishOutput(out, y, ex);
+    FinishOutput(outT, y, ex);
     ex->workspaceSize = ws.Size();
     *workspaceSize = ws.Size();
     *executor = ex;
@@ -1572,22 +1635,25 @@ aclnnStatus aclnnUpsampleBicubic2dBackwardGetWorkspaceSize(const aclTensor* grad
     if (gi.h == gg.h && gi.w == gg.w) { // resize_bicubic_v2_grad_all_copy_tiling_arch35.cpp:23-30
         return PlanCopy(api, gradOut, gradInput, workspaceSize, executor);
     }
+    const aclTensor* inT = gradInput;
+    aclTensor altGrad, altIn;
+    UseOtherLayout(gradOut, inT, altGrad, altIn);
     aclOpExecutor* ex = NewExecutor(api);
     if (ex == nullptr) {
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
     const BufRef g = StageInput(gradOut, ws, ex);
-    const BufRef y = StageOutput(gradInput, ws);
+    const BufRef y = StageOutput(inT, ws);
     const Shape4 sh = MakeShape(gi, gg);
     const Dt dt = ToDt(gradOut->dtype);
-    const Layout lay = nhwc ? kNHWC : kNCHW;
+    const Layout lay = gradOut->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW; // after the layout swap
     const BicubicGradScale bh = MakeBicubicGradScale(gi.h, gg.h, alignCorners, static_cast<float>(scalesH));
     const BicubicGradScale bw = MakeBicubicGradScale(gi.w, gg.w, alignCorners, static_cast<float>(scalesW));
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         return Bicubic2dBwd(dt, lay, g.At(w), y.At(w), sh, bh.scale, bw.scale, bh.inverse, bw.inverse, alignCorners, s);
     });
-    FinishOutput(gradInput, y, ex);
+    FinishOutput(inT, y, ex);
     ex->workspaceSize = ws.Size();
     *workspaceSize = ws.Size();
     *executor = ex;

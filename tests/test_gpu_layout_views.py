@@ -1,0 +1,81 @@
+"""Views that are dense in the other layout's memory order (a channels-last tensor behind an NCHW handle, an NCHW
+tensor behind an NHWC handle) run on that layout's kernels in place: the same bits as the contiguous call and no
+staging copies (the launch count of the call equals that of a contiguous call)."""
+import pytest
+import torch
+
+from test_gpu_parity import gen
+
+pytestmark = pytest.mark.gpu
+
+
+def _launches(ops, fn):
+    ops.reset_launch_count()
+    out = fn()
+    torch.cuda.synchronize()
+    return out, ops.launch_count()
+
+
+def _cases(ops):
+    return [
+        ("nearest", lambda x, o, f, out: ops.upsample_nearest2d(x, o, f, out=out),
+         lambda g, o, s, f, out: ops.upsample_nearest2d_backward(g, o, s, f, out=out)),
+        ("bilinear", lambda x, o, f, out: ops.upsample_bilinear2d(x, o, False, f, out=out),
+         lambda g, o, s, f, out: ops.upsample_bilinear2d_backward(g, o, s, False, f, out=out)),
+        ("bicubic", lambda x, o, f, out: ops.upsample_bicubic2d(x, o, False, f, out=out),
+         lambda g, o, s, f, out: ops.upsample_bicubic2d_backward(g, o, s, False, f, out=out)),
+        ("nearest_exact", lambda x, o, f, out: ops.upsample_nearest_exact2d(x, o, f, out=out), None),
+    ]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(2, 8, 9, 12, 20, 31), (1, 16, 14, 14, 28, 28), (2, 3, 16, 10, 5, 7)])
+def test_channels_last_behind_an_nchw_handle(ops, dev, dtype, shape):
+    n, c, hi, wi, ho, wo = shape
+    x = torch.randn((n, c, hi, wi), generator=gen(90)).to(dtype).to(dev)
+    g = torch.randn((n, c, ho, wo), generator=gen(91)).to(dtype).to(dev)
+    for name, fwd, bwd in _cases(ops):
+        want, base = _launches(ops, lambda: fwd(x, (ho, wo), "NCHW", None))
+        x_cl = x.contiguous(memory_format=torch.channels_last)
+        out_cl = torch.empty_like(want, memory_format=torch.channels_last)
+        assert not x_cl.is_contiguous() or c == 1
+        _, count = _launches(ops, lambda: fwd(x_cl, (ho, wo), "NCHW", out_cl))
+        assert torch.equal(out_cl, want), name
+        # the NHWC kernel on the same memory, no gather / scatter copies around it
+        _, nhwc_count = _launches(ops, lambda: fwd(x.permute(0, 2, 3, 1).contiguous(), (ho, wo), "NHWC", None))
+        assert count == nhwc_count, (name, count, nhwc_count, base)
+        if bwd is None:
+            continue
+        want = bwd(g, (ho, wo), (n, c, hi, wi), "NCHW", None)
+        g_cl = g.contiguous(memory_format=torch.channels_last)
+        gi_cl = torch.empty_like(want, memory_format=torch.channels_last)
+        _, count = _launches(ops, lambda: bwd(g_cl, (ho, wo), (n, c, hi, wi), "NCHW", gi_cl))
+        _, nhwc_count = _launches(ops, lambda: bwd(g.permute(0, 2, 3, 1).contiguous(), (ho, wo), (n, hi, wi, c), "NHWC", None))
+        assert count == nhwc_count, (name, count, nhwc_count)
+        if name == "bilinear":   # the NHWC backward sums in another order than the NCHW one
+            torch.testing.assert_close(gi_cl.float(), want.float(), rtol=1e-5 if dtype == torch.float32 else 1e-2,
+                                       atol=1e-6 if dtype == torch.float32 else 2e-2)
+        else:
+            assert torch.equal(gi_cl, want), name
+
+
+def test_nchw_memory_behind_an_nhwc_handle(ops, dev):
+    x = torch.randn((2, 6, 9, 12), generator=gen(92)).to(dev)         # NCHW memory
+    view = x.permute(0, 2, 3, 1)                                        # dims N, H, W, C with NCHW strides
+    want = ops.upsample_bilinear2d(x, (20, 31), False, "NCHW")
+    out = torch.empty((2, 6, 20, 31), device=dev).permute(0, 2, 3, 1)   # the same kind of view for the output
+    _, count = _launches(ops, lambda: ops.upsample_bilinear2d(view, (20, 31), False, "NHWC", out=out))
+    _, base = _launches(ops, lambda: ops.upsample_bilinear2d(x, (20, 31), False, "NCHW"))
+    assert torch.equal(out.permute(0, 3, 1, 2), want) and count == base
+    # same extents: a flat copy of the permuted memory
+    same = torch.empty((2, 6, 9, 12), device=dev).permute(0, 2, 3, 1)
+    _, count = _launches(ops, lambda: ops.upsample_bilinear2d(view, (9, 12), False, "NHWC", out=same))
+    assert torch.equal(same, view) and count == 1
+
+
+def test_mixed_layouts_still_go_through_staging(ops, dev):
+    x = torch.randn((2, 8, 9, 12), generator=gen(93)).to(dev)
+    want = ops.upsample_bilinear2d(x, (20, 31), False, "NCHW")
+    x_cl = x.contiguous(memory_format=torch.channels_last)
+    got = ops.upsample_bilinear2d(x_cl, (20, 31), False, "NCHW")          # contiguous NCHW output
+    assert torch.equal(got, want)
