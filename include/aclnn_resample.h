@@ -217,6 +217,44 @@ ACLNN_API aclnnStatus aclnnUpsampleBicubic2dBackwardGetWorkspaceSize(const aclTe
 ACLNN_API aclnnStatus aclnnUpsampleBicubic2dBackward(void* workspace, uint64_t workspaceSize,
                                                      aclOpExecutor* executor, aclrtStream stream);
 
+/* ---- UpsampleNearest3d / UpsampleNearestExact3d -------------------------------------------------------------
+ * 5-D tensors in ACL_FORMAT_NCDHW (or ND) or ACL_FORMAT_NDHWC; outputSize = {D, H, W}.
+ * Replace image/upsample_nearest3d/op_host/op_api/aclnn_upsample_nearest_3d.h (implementation
+ * aclnn_upsample_nearest_3d.cpp:156-204; kernel op_kernel/arch35/upsample_nearest3d_simt_base.h:31-88),
+ * image/upsample_nearest_exact3d/op_host/op_api/aclnn_upsample_nearest_exact3d.h:25-34 (the same kernel with the
+ * half-pixel source index), image/upsample_nearest3d_grad/op_host/op_api/aclnn_upsample_nearest_3d_backward.h:25-33
+ * (kernel op_kernel/arch35/upsample_nearest3d_grad_simt_base.h:33-58) and
+ * image/upsample_nearest_exact3d_grad/op_host/op_api/aclnn_upsample_nearest_exact3d_backward.h:25-33. */
+ACLNN_API aclnnStatus aclnnUpsampleNearest3dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                             double scalesD, double scalesH, double scalesW,
+                                                             aclTensor* out, uint64_t* workspaceSize,
+                                                             aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearest3d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                             aclrtStream stream);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact3dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                                  double scalesD, double scalesH, double scalesW,
+                                                                  aclTensor* out, uint64_t* workspaceSize,
+                                                                  aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact3d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                  aclrtStream stream);
+ACLNN_API aclnnStatus aclnnUpsampleNearest3dBackwardGetWorkspaceSize(const aclTensor* gradOut,
+                                                                     const aclIntArray* outputSize,
+                                                                     const aclIntArray* inputSize, double scalesD,
+                                                                     double scalesH, double scalesW,
+                                                                     aclTensor* gradInput, uint64_t* workspaceSize,
+                                                                     aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearest3dBackward(void* workspace, uint64_t workspaceSize,
+                                                     aclOpExecutor* executor, aclrtStream stream);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact3dBackwardGetWorkspaceSize(const aclTensor* gradOut,
+                                                                          const aclIntArray* outputSize,
+                                                                          const aclIntArray* inputSize,
+                                                                          double scalesD, double scalesH,
+                                                                          double scalesW, aclTensor* gradInput,
+                                                                          uint64_t* workspaceSize,
+                                                                          aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleNearestExact3dBackward(void* workspace, uint64_t workspaceSize,
+                                                          aclOpExecutor* executor, aclrtStream stream);
+
 /* ---- Resize ---------------------------------------------------------------------------------------------------
  * Replaces image/resize_bilinear_v2/op_api/aclnn_resize.h:32-46 (implementation aclnn_resize.cpp:231-300, regbase
  * branch). `scales` holds one factor per dimension of `self` (4 values); `mode` starts with "nearest" or "bilinear".

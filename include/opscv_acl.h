@@ -63,6 +63,8 @@ typedef enum {
     ACL_FORMAT_NCHW = 0,
     ACL_FORMAT_NHWC = 1,
     ACL_FORMAT_ND = 2,
+    ACL_FORMAT_NDHWC = 27,
+    ACL_FORMAT_NCDHW = 30,
     ACL_FORMAT_NCL = 47
 } aclFormat;
 

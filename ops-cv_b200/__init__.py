@@ -19,6 +19,7 @@ CSRC_DIR = os.path.join(_HERE, "csrc")
 # aclDataType / aclFormat values (include/opscv_acl.h)
 ACL_FLOAT, ACL_FLOAT16, ACL_INT8, ACL_INT32, ACL_UINT8, ACL_INT64, ACL_DOUBLE, ACL_BOOL, ACL_BF16 = 0, 1, 2, 3, 4, 9, 11, 12, 27
 ACL_FORMAT_NCHW, ACL_FORMAT_NHWC, ACL_FORMAT_ND, ACL_FORMAT_NCL = 0, 1, 2, 47
+ACL_FORMAT_NDHWC, ACL_FORMAT_NCDHW = 27, 30
 ACL_OPT_DETERMINISTIC = 0
 
 ACLNN_SUCCESS = 0
@@ -88,6 +89,14 @@ SYMBOLS = {
     "aclnnUpsampleBicubic2d": _PHASE2,
     "aclnnUpsampleBicubic2dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleBicubic2dBackward": _PHASE2,
+    "aclnnUpsampleNearest3dGetWorkspaceSize": (_I32, [_P, _P, _D, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearest3d": _PHASE2,
+    "aclnnUpsampleNearestExact3dGetWorkspaceSize": (_I32, [_P, _P, _D, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearestExact3d": _PHASE2,
+    "aclnnUpsampleNearest3dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _D, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearest3dBackward": _PHASE2,
+    "aclnnUpsampleNearestExact3dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _D, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleNearestExact3dBackward": _PHASE2,
     "aclnnResizeGetWorkspaceSize": (_I32, [_P, _P, ctypes.c_char_p, _P, _PU64, _PP]),
     "aclnnResize": _PHASE2,
     "aclnnGridSampler2DGetWorkspaceSize": (_I32, [_P, _P, _I64, _I64, _B, _P, _PU64, _PP]),

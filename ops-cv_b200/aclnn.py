@@ -3,7 +3,8 @@ import ctypes
 
 import torch
 
-from . import (ACL_BF16, ACL_DOUBLE, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_NCHW, ACL_FORMAT_NCL, ACL_FORMAT_ND, ACL_FORMAT_NHWC,
+from . import (ACL_BF16, ACL_DOUBLE, ACL_FLOAT, ACL_FLOAT16, ACL_FORMAT_NCDHW, ACL_FORMAT_NCHW, ACL_FORMAT_NCL, ACL_FORMAT_ND,
+               ACL_FORMAT_NDHWC, ACL_FORMAT_NHWC,
                ACL_INT32, ACL_INT64, ACL_OPT_DETERMINISTIC, ACL_UINT8, lib)
 
 __all__ = [
@@ -12,13 +13,15 @@ __all__ = [
     "upsample_nearest2d_backward", "upsample_bilinear2d", "upsample_bilinear2d_no_alloc",
     "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bilinear2d_aa",
     "upsample_bilinear2d_aa_backward", "upsample_nearest_exact2d", "upsample_nearest_exact2d_backward",
-    "upsample_nearest_exact1d", "upsample_nearest_exact1d_backward", "upsample_bicubic2d_aa",
+    "upsample_nearest_exact1d", "upsample_nearest_exact1d_backward", "upsample_nearest3d",
+    "upsample_nearest3d_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
 ]
 
 _DTYPES = {torch.float32: ACL_FLOAT, torch.float16: ACL_FLOAT16, torch.bfloat16: ACL_BF16, torch.float64: ACL_DOUBLE,
            torch.uint8: ACL_UINT8, torch.int32: ACL_INT32, torch.int64: ACL_INT64}
-_FORMATS = {"NCHW": ACL_FORMAT_NCHW, "NHWC": ACL_FORMAT_NHWC, "ND": ACL_FORMAT_ND, "NCL": ACL_FORMAT_NCL}
+_FORMATS = {"NCHW": ACL_FORMAT_NCHW, "NHWC": ACL_FORMAT_NHWC, "ND": ACL_FORMAT_ND, "NCL": ACL_FORMAT_NCL,
+            "NCDHW": ACL_FORMAT_NCDHW, "NDHWC": ACL_FORMAT_NDHWC}
 
 
 class AclnnError(RuntimeError):
@@ -268,6 +271,28 @@ def upsample_nearest_exact1d_backward(grad_out, out_l, input_size, scale=0.0, fm
     tg, ty = acl_tensor(grad_out, fmt), acl_tensor(out, fmt)
     osz, isz = int_array([out_l]), int_array(input_size)
     two_phase("aclnnUpsampleNearestExact1dBackward", [tg.ptr, osz.ptr, isz.ptr, float(scale), ty.ptr],
+              grad_out.device, workspace)
+    return out
+
+
+def upsample_nearest3d(x, out_dhw, fmt="NCDHW", scales=(0.0, 0.0, 0.0), exact=False, out=None, workspace=None):
+    if out is None:
+        shape = (x.shape[0], *out_dhw, x.shape[4]) if fmt == "NDHWC" else (x.shape[0], x.shape[1], *out_dhw)
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    tx, ty, size = acl_tensor(x, fmt), acl_tensor(out, fmt), int_array(list(out_dhw))
+    name = "aclnnUpsampleNearestExact3d" if exact else "aclnnUpsampleNearest3d"
+    two_phase(name, [tx.ptr, size.ptr, float(scales[0]), float(scales[1]), float(scales[2]), ty.ptr], x.device,
+              workspace)
+    return out
+
+
+def upsample_nearest3d_backward(grad_out, out_dhw, input_size, fmt="NCDHW", scales=(0.0, 0.0, 0.0), exact=False,
+                                out=None, workspace=None):
+    out = torch.empty(tuple(input_size), dtype=grad_out.dtype, device=grad_out.device) if out is None else out
+    tg, ty = acl_tensor(grad_out, fmt), acl_tensor(out, fmt)
+    osz, isz = int_array(list(out_dhw)), int_array(list(input_size))
+    name = "aclnnUpsampleNearestExact3dBackward" if exact else "aclnnUpsampleNearest3dBackward"
+    two_phase(name, [tg.ptr, osz.ptr, isz.ptr, float(scales[0]), float(scales[1]), float(scales[2]), ty.ptr],
               grad_out.device, workspace)
     return out
 

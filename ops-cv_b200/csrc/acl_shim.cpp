@@ -206,6 +206,8 @@ const char* FormatName(aclFormat f)
         case ACL_FORMAT_NHWC: return "NHWC";
         case ACL_FORMAT_ND: return "ND";
         case ACL_FORMAT_NCL: return "NCL";
+        case ACL_FORMAT_NCDHW: return "NCDHW";
+        case ACL_FORMAT_NDHWC: return "NDHWC";
         default: return "UNKNOWN";
     }
 }
@@ -213,16 +215,45 @@ const char* FormatName(aclFormat f)
 int64_t GetDeterministic() { return g_deterministic; }
 int32_t GetBackwardAlgo() { return g_backwardAlgo; }
 
-static View4 MakeView4(const aclTensor* t)
+// The view as at most four (extent, stride) pairs: extents of 1 are dropped and neighbours that are contiguous with
+// respect to each other are merged, which brings every 5-D view with at least one such pair down to four.
+static bool CollapseView(const aclTensor* t, View4& v)
+{
+    std::vector<int64_t> dims, strides;
+    for (size_t i = 0; i < t->dims.size(); ++i) {
+        if (t->dims[i] == 1) {
+            continue;
+        }
+        if (!dims.empty() && strides.back() == t->strides[i] * t->dims[i]) {
+            dims.back() *= t->dims[i];
+            strides.back() = t->strides[i];
+        } else {
+            dims.push_back(t->dims[i]);
+            strides.push_back(t->strides[i]);
+        }
+    }
+    if (dims.size() > 4) {
+        return false;
+    }
+    const size_t rank = dims.size();
+    for (size_t i = 0; i < 4; ++i) { // right-align
+        const int64_t src = static_cast<int64_t>(i) - (4 - static_cast<int64_t>(rank));
+        v.dim[i] = src >= 0 ? dims[src] : 1;
+        v.stride[i] = src >= 0 ? strides[src] : 0;
+    }
+    return true;
+}
+
+bool ViewStageable(const aclTensor* t)
 {
     View4 v;
-    const size_t rank = t->dims.size();
-    for (size_t i = 0; i < 4; ++i) {
-        // right-align lower-rank tensors
-        const int64_t src = static_cast<int64_t>(i) - (4 - static_cast<int64_t>(rank));
-        v.dim[i] = src >= 0 ? t->dims[src] : 1;
-        v.stride[i] = src >= 0 ? t->strides[src] : 0;
-    }
+    return IsContiguous(t) || CollapseView(t, v);
+}
+
+static View4 MakeView4(const aclTensor* t)
+{
+    View4 v{};
+    CollapseView(t, v); // callers with tensors of rank above four check ViewStageable in their first phase
     return v;
 }
 

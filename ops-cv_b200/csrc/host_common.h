@@ -126,6 +126,9 @@ struct BufRef {
 
 // Input staging: returns a reference to contiguous data of `t`; for a strided view a gather-copy step into the
 // workspace is appended to the executor first (the reference's l0op::Contiguous).
+// False for a view of rank five or more that no merging of neighbouring dimensions brings down to four strided
+// dimensions (the staging copies handle four).
+bool ViewStageable(const aclTensor* t);
 BufRef StageInput(const aclTensor* t, WsPlan& ws, aclOpExecutor* ex);
 // Output staging: returns where the kernels must write; for a strided view that is a workspace buffer, and
 // FinishOutput appends the scatter-copy back into the view (the reference's l0op::ViewCopy).

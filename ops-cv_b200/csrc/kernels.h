@@ -165,6 +165,18 @@ cudaError_t Bicubic2dFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, f
 cudaError_t Bicubic2dBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, float scaleH, float scaleW,
                          float invH, float invW, bool align, cudaStream_t s);
 
+// UpsampleNearest3d / UpsampleNearestExact3d. rows: forward planes * dout * ho, backward planes * di * hi, with
+// planes = N * C for NCDHW (chan = 1) and N for NDHWC (chan = C). Forward scales are source-coordinate scales; the
+// backward's are the window scales (grads extent per grad_input extent).
+struct Nearest3dGeom {
+    int64_t rows;
+    int32_t di, hi, wi, dout, ho, wo, chan;
+    float sd, sh, sw;
+    int32_t exact;
+};
+cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStream_t s);
+cudaError_t Nearest3dBwd(Dt dt, const void* go, void* gi, Nearest3dGeom g, cudaStream_t s);
+
 struct GridShape {
     int64_t n, c;
     int32_t hin, win, hout, wout;

@@ -1,0 +1,154 @@
+// UpsampleNearest3d / UpsampleNearestExact3d forward and backward on NCDHW and NDHWC tensors.
+//
+// Forward (image/upsample_nearest3d/op_kernel/arch35/upsample_nearest3d_simt_base.h:31-88): a pure copy,
+// y[n, c, d, h, w] = x[n, c, sd(d), sh(h), sw(w)] with s(i) = min(floor((i [+ 0.5]) * scale), in - 1). A block row is
+// one output row (plane, d, h): its source row is found once, and each thread gathers a 16-byte pack of the row
+// (NCDHW: adjacent columns with their own source columns; NDHWC: adjacent channels of one pixel, one vector load).
+// Backward (image/upsample_nearest3d_grad/op_kernel/arch35/upsample_nearest3d_grad_simt_base.h:33-58): every
+// grad_input element sums its window [ceil(y * s [- 0.5]), ceil((y + 1) * s [- 0.5])) per axis in fp32, in d, h, w
+// order, and is rounded once.
+#include <algorithm>
+
+#include "launch_util.cuh"
+
+namespace opscv {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ int32_t SrcIdx(int32_t i, float scale, int32_t exact, int32_t in)
+{
+    const float pos = exact ? Mul(Add(static_cast<float>(i), 0.5f), scale) : Mul(static_cast<float>(i), scale);
+    const long long s = static_cast<long long>(floorf(pos));
+    const long long last = in - 1;
+    return static_cast<int32_t>(s < last ? s : last);
+}
+
+__device__ __forceinline__ int32_t WindowEdge(int32_t y, float scale, int32_t exact, int32_t limit)
+{
+    const float v = exact ? Sub(Mul(static_cast<float>(y), scale), 0.5f) : Mul(static_cast<float>(y), scale);
+    long long e = static_cast<long long>(ceilf(v));
+    e = e < 0 ? 0 : e;
+    return static_cast<int32_t>(e < limit ? e : limit);
+}
+
+template <typename T, int V, bool CHANNELS_LAST>
+__global__ void __launch_bounds__(kThreads) Nearest3dFwdKernel(const T* __restrict__ x, T* __restrict__ y, Nearest3dGeom g)
+{
+    const int64_t inner = static_cast<int64_t>(g.wo) * g.chan; // elements of an output row
+    const int64_t rowIn = static_cast<int64_t>(g.wi) * g.chan;
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) * V;
+    if (t0 >= inner) {
+        return;
+    }
+    // source offsets of this thread's pack inside a source row (the same for every row)
+    int32_t off[CHANNELS_LAST ? 1 : V];
+    if (CHANNELS_LAST) {
+        const int32_t w = static_cast<int32_t>(t0 / g.chan);
+        off[0] = SrcIdx(w, g.sw, g.exact, g.wi) * g.chan + static_cast<int32_t>(t0 - static_cast<int64_t>(w) * g.chan);
+    } else {
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            off[CHANNELS_LAST ? 0 : v] = SrcIdx(static_cast<int32_t>(t0) + v, g.sw, g.exact, g.wi);
+        }
+    }
+    for (int64_t row = blockIdx.y; row < g.rows; row += gridDim.y) { // row = (plane, d, h)
+        const int64_t pd = row / g.ho;
+        const int32_t h = static_cast<int32_t>(row - pd * g.ho);
+        const int64_t plane = pd / g.dout;
+        const int32_t d = static_cast<int32_t>(pd - plane * g.dout);
+        const int64_t srcRow = (plane * g.di + SrcIdx(d, g.sd, g.exact, g.di)) * g.hi + SrcIdx(h, g.sh, g.exact, g.hi);
+        const T* px = x + srcRow * rowIn;
+        T* py = y + row * inner + t0;
+        if (CHANNELS_LAST) {
+            *reinterpret_cast<Pack<T, V>*>(py) = *reinterpret_cast<const Pack<T, V>*>(px + off[0]);
+        } else {
+            Pack<T, V> p;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                p.v[v] = __ldg(px + off[CHANNELS_LAST ? 0 : v]);
+            }
+            *reinterpret_cast<Pack<T, V>*>(py) = p;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) Nearest3dBwdKernel(const T* __restrict__ go, T* __restrict__ gi, Nearest3dGeom g)
+{
+    const int64_t inner = static_cast<int64_t>(g.wi) * g.chan; // elements of a grad_input row
+    const int64_t rowGo = static_cast<int64_t>(g.wo) * g.chan;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    if (t >= inner) {
+        return;
+    }
+    const int32_t w = static_cast<int32_t>(t / g.chan);
+    const int32_t c = static_cast<int32_t>(t - static_cast<int64_t>(w) * g.chan);
+    const int32_t w0 = WindowEdge(w, g.sw, g.exact, g.wo), w1 = WindowEdge(w + 1, g.sw, g.exact, g.wo);
+    for (int64_t row = blockIdx.y; row < g.rows; row += gridDim.y) { // row = (plane, d, h) of grad_input
+        const int64_t pd = row / g.hi;
+        const int32_t h = static_cast<int32_t>(row - pd * g.hi);
+        const int64_t plane = pd / g.di;
+        const int32_t d = static_cast<int32_t>(pd - plane * g.di);
+        const int32_t d0 = WindowEdge(d, g.sd, g.exact, g.dout), d1 = WindowEdge(d + 1, g.sd, g.exact, g.dout);
+        const int32_t h0 = WindowEdge(h, g.sh, g.exact, g.ho), h1 = WindowEdge(h + 1, g.sh, g.exact, g.ho);
+        float acc = 0.0f;
+        for (int32_t a = d0; a < d1; ++a) {
+            for (int32_t b = h0; b < h1; ++b) {
+                const T* pr = go + ((plane * g.dout + a) * g.ho + b) * rowGo + c;
+                for (int32_t e = w0; e < w1; ++e) {
+                    acc = Add(acc, DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan));
+                }
+            }
+        }
+        gi[row * inner + t] = DType<T>::FromF(acc);
+    }
+}
+
+dim3 RowGrid3(int64_t rows, int64_t colBlocks)
+{
+    const int64_t cap = std::max<int64_t>(static_cast<int64_t>(NumSMs()) * 16 / std::max<int64_t>(colBlocks, 1), 1);
+    return dim3(static_cast<unsigned>(colBlocks), static_cast<unsigned>(std::min<int64_t>(std::min<int64_t>(std::max<int64_t>(rows, 1), cap), 65535)), 1);
+}
+
+} // namespace
+
+cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStream_t s)
+{
+    const int64_t inner = static_cast<int64_t>(g.wo) * g.chan;
+    const int es = DtSize(dt);
+    const bool cl = g.chan > 1;
+    // pack width: 16 bytes when rows keep that alignment; channels-last packs must not straddle a pixel
+    int v = 16 / es;
+    while (v > 1 && (inner % v != 0 || (cl && g.chan % v != 0) || !Aligned(y, static_cast<size_t>(v) * es) ||
+                     (cl && (!Aligned(x, static_cast<size_t>(v) * es))))) {
+        v >>= 1;
+    }
+    const dim3 grid = RowGrid3(g.rows, CeilDiv(CeilDiv(inner, v), kThreads));
+    OPSCV_DISPATCH_DT(dt, T, {
+        const T* px = static_cast<const T*>(x);
+        T* py = static_cast<T*>(y);
+        OPSCV_DISPATCH_VEC(v, V, {
+            if constexpr (V * sizeof(T) <= 16) {
+                if (cl) {
+                    Nearest3dFwdKernel<T, V, true><<<grid, kThreads, 0, s>>>(px, py, g);
+                } else {
+                    Nearest3dFwdKernel<T, V, false><<<grid, kThreads, 0, s>>>(px, py, g);
+                }
+            }
+        });
+    });
+    CountLaunch();
+    return cudaGetLastError();
+}
+
+cudaError_t Nearest3dBwd(Dt dt, const void* go, void* gi, Nearest3dGeom g, cudaStream_t s)
+{
+    const int64_t inner = static_cast<int64_t>(g.wi) * g.chan;
+    const dim3 grid = RowGrid3(g.rows, CeilDiv(inner, kThreads));
+    OPSCV_DISPATCH_DT(dt, T, { Nearest3dBwdKernel<T><<<grid, kThreads, 0, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g); });
+    CountLaunch();
+    return cudaGetLastError();
+}
+
+} // namespace opscv

@@ -170,6 +170,39 @@ def nearest_exact2d_bwd(go, in_hw, scales=(0.0, 0.0)):
     return gi
 
 
+def _dims5(shape, fmt):
+    if fmt == NHWC:  # NDHWC
+        n, d, h, w, c = shape
+    else:
+        n, c, d, h, w = shape
+    return int(n), int(c), int(d), int(h), int(w)
+
+
+def _shape5(n, c, d, h, w, fmt):
+    return (n, d, h, w, c) if fmt == NHWC else (n, c, d, h, w)
+
+
+def nearest3d_fwd(x, out_dhw, scales=(0.0, 0.0, 0.0), exact=False, fmt=NCHW):
+    """UpsampleNearest3d / UpsampleNearestExact3d forward; fmt NCHW means NCDHW, NHWC means NDHWC."""
+    x, px = _f(x)
+    n, c, d, h, w = _dims5(x.shape, fmt)
+    y = np.empty(_shape5(n, c, *out_dhw, fmt), dtype=np.float32)
+    lib().orc_nearest3d_fwd(px, y.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(d), I64(h), I64(w),
+                            I64(out_dhw[0]), I64(out_dhw[1]), I64(out_dhw[2]), F32(scales[0]), F32(scales[1]),
+                            F32(scales[2]), I32(int(exact)), I32(fmt))
+    return y
+
+
+def nearest3d_bwd(go, in_dhw, scales=(0.0, 0.0, 0.0), exact=False, fmt=NCHW):
+    go, pg = _f(go)
+    n, c, do, ho, wo = _dims5(go.shape, fmt)
+    gi = np.empty(_shape5(n, c, *in_dhw, fmt), dtype=np.float32)
+    lib().orc_nearest3d_bwd(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_dhw[0]), I64(in_dhw[1]),
+                            I64(in_dhw[2]), I64(do), I64(ho), I64(wo), F32(scales[0]), F32(scales[1]), F32(scales[2]),
+                            I32(int(exact)), I32(fmt))
+    return gi
+
+
 def bilinear2d_fwd(x, out_hw, align=False, scales=(0.0, 0.0), fmt=NCHW):
     x, px = _f(x)
     n, c, h, w = _dims(x.shape, fmt)

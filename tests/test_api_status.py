@@ -262,6 +262,41 @@ def test_resize_status(ops):
     assert ops.lib().aclGetFloatArraySize(None, ctypes.byref(n)) != 0
 
 
+def test_nearest3d_status(ops):
+    for api in ("aclnnUpsampleNearest3d", "aclnnUpsampleNearestExact3d"):
+        x, y, sz = T(ops, (2, 3, 4, 8, 8), fmt="NCDHW"), T(ops, (2, 3, 8, 16, 12), fmt="NCDHW"), IA(ops, [8, 16, 12])
+        assert phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, 0.0, y.ptr)[0] == OK
+        assert phase1(ops, api, None, sz.ptr, 0.0, 0.0, 0.0, y.ptr)[0] == NULLPTR
+        assert phase1(ops, api, x.ptr, None, 0.0, 0.0, 0.0, y.ptr)[0] == NULLPTR
+        assert phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, 0.0, None)[0] == NULLPTR
+        assert phase1(ops, api, x.ptr, IA(ops, [8, 16]).ptr, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+        assert phase1(ops, api, x.ptr, IA(ops, [8, 16, 13]).ptr, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+        assert phase1(ops, api, T(ops, (2, 3, 8, 8)).ptr, sz.ptr, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+        assert phase1(ops, api, x.ptr, sz.ptr, 0.0, 0.0, 0.0, T(ops, (2, 3, 8, 16, 12), torch.float16, fmt="NCDHW").ptr)[0] == INVALID
+        assert phase1(ops, api, T(ops, (2, 0, 4, 8, 8), fmt="NCDHW").ptr, sz.ptr, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+        assert phase1(ops, api, T(ops, (0, 3, 4, 8, 8), fmt="NCDHW").ptr, sz.ptr, 0.0, 0.0, 0.0,
+                      T(ops, (0, 3, 8, 16, 12), fmt="NCDHW").ptr) == (OK, 0)
+        assert phase1(ops, api, T(ops, (2, 4, 8, 8, 3), fmt="NDHWC").ptr, sz.ptr, 0.0, 0.0, 0.0,
+                      T(ops, (2, 8, 16, 12, 3), fmt="NDHWC").ptr)[0] == OK
+    # the exact variant checks positive scales against the sizes
+    x, y, sz = T(ops, (2, 3, 4, 8, 8), fmt="NCDHW"), T(ops, (2, 3, 8, 16, 12), fmt="NCDHW"), IA(ops, [8, 16, 12])
+    assert phase1(ops, "aclnnUpsampleNearestExact3d", x.ptr, sz.ptr, 2.0, 2.0, 1.5, y.ptr)[0] == OK
+    assert phase1(ops, "aclnnUpsampleNearestExact3d", x.ptr, sz.ptr, 2.0, 2.0, 2.0, y.ptr)[0] == INVALID
+    for api in ("aclnnUpsampleNearest3dBackward", "aclnnUpsampleNearestExact3dBackward"):
+        g, out = T(ops, (2, 3, 8, 16, 12), fmt="NCDHW"), T(ops, (2, 3, 4, 8, 8), fmt="NCDHW")
+        osz, isz = IA(ops, [8, 16, 12]), IA(ops, [2, 3, 4, 8, 8])
+        assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, 0.0, 0.0, out.ptr)[0] == OK
+        assert phase1(ops, api, None, osz.ptr, isz.ptr, 0.0, 0.0, 0.0, out.ptr)[0] == NULLPTR
+        assert phase1(ops, api, g.ptr, None, isz.ptr, 0.0, 0.0, 0.0, out.ptr)[0] == NULLPTR
+        assert phase1(ops, api, g.ptr, osz.ptr, None, 0.0, 0.0, 0.0, out.ptr)[0] == NULLPTR
+        assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, 0.0, 0.0, None)[0] == NULLPTR
+        assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [2, 3, 4, 8]).ptr, 0.0, 0.0, 0.0, out.ptr)[0] == INVALID
+        assert phase1(ops, api, g.ptr, IA(ops, [8, 16, 13]).ptr, isz.ptr, 0.0, 0.0, 0.0, out.ptr)[0] == INVALID
+        assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, 0.0, 0.0, 0.0, T(ops, (2, 3, 4, 8, 9), fmt="NCDHW").ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearestExact3dBackward", g.ptr, osz.ptr, isz.ptr, -1.0, 0.0, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, "aclnnUpsampleNearestExact3dBackward", g.ptr, osz.ptr, isz.ptr, 90.0, 0.0, 0.0, out.ptr)[0] == INVALID
+
+
 def test_bilinear_aa_status(ops):
     """aclnnUpsampleBilinear2dAA / ...Backward: the checks of the bicubic-AA pair (NCHW or ND only, one dtype, 4-D,
     sizes > 0) plus negative scales in the forward."""
