@@ -255,6 +255,29 @@ ACLNN_API aclnnStatus aclnnUpsampleNearestExact3dBackwardGetWorkspaceSize(const 
 ACLNN_API aclnnStatus aclnnUpsampleNearestExact3dBackward(void* workspace, uint64_t workspaceSize,
                                                           aclOpExecutor* executor, aclrtStream stream);
 
+/* ---- GridSampler3D --------------------------------------------------------------------------------------------
+ * Replaces image/grid_sample/op_api/aclnn_grid_sampler3d.h (implementation aclnn_grid_sampler3d.cpp:194-380; kernel
+ * image/grid_sample/op_kernel/arch35/grid_sampler_3d_bilinear_smit.h:58-184) and
+ * image/grid_sampler3_d_grad/op_host/op_api/aclnn_grid_sampler3d_backward.h (implementation
+ * aclnn_grid_sampler3d_backward.cpp:183-310; kernel op_kernel/arch35/grid_sampler3_d_grad_simt.h:43-300).
+ * input (N, C, D, H, W) in NCDHW / ND (or NDHWC with permuted extents), grid (N, Do, Ho, Wo, 3) holding (x, y, z),
+ * out (N, C, Do, Ho, Wo). interpolationMode 0 bilinear, 1 nearest; paddingMode 0 zeros, 1 border, 2 reflection.
+ * outputMask = {grad_input wanted, grad_grid wanted}. */
+ACLNN_API aclnnStatus aclnnGridSampler3DGetWorkspaceSize(const aclTensor* input, const aclTensor* grid,
+                                                         int64_t interpolationMode, int64_t paddingMode,
+                                                         bool alignCorners, aclTensor* out, uint64_t* workspaceSize,
+                                                         aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnGridSampler3D(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                         aclrtStream stream);
+ACLNN_API aclnnStatus aclnnGridSampler3DBackwardGetWorkspaceSize(const aclTensor* gradOutput, const aclTensor* input,
+                                                                 const aclTensor* grid, int64_t interpolationMode,
+                                                                 int64_t paddingMode, bool alignCorners,
+                                                                 const aclBoolArray* outputMask, aclTensor* inputGrad,
+                                                                 aclTensor* gridGrad, uint64_t* workspaceSize,
+                                                                 aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnGridSampler3DBackward(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                                 aclrtStream stream);
+
 /* ---- Resize ---------------------------------------------------------------------------------------------------
  * Replaces image/resize_bilinear_v2/op_api/aclnn_resize.h:32-46 (implementation aclnn_resize.cpp:231-300, regbase
  * branch). `scales` holds one factor per dimension of `self` (4 values); `mode` starts with "nearest" or "bilinear".

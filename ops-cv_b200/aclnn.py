@@ -14,7 +14,7 @@ __all__ = [
     "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bilinear2d_aa",
     "upsample_bilinear2d_aa_backward", "upsample_nearest_exact2d", "upsample_nearest_exact2d_backward",
     "upsample_nearest_exact1d", "upsample_nearest_exact1d_backward", "upsample_nearest3d",
-    "upsample_nearest3d_backward", "upsample_bicubic2d_aa",
+    "upsample_nearest3d_backward", "grid_sampler3d", "grid_sampler3d_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
 ]
 
@@ -360,5 +360,27 @@ def grid_sampler2d_backward(grad_out, x, grid, interpolation=0, padding=0, align
     tgo, tx, tg = acl_tensor(grad_out, "NCHW"), acl_tensor(x, "NCHW"), acl_tensor(grid, "ND")
     tgi, tgg, m = acl_tensor(input_grad, "NCHW"), acl_tensor(grid_grad, "ND"), bool_array(list(mask))
     two_phase("aclnnGridSampler2DBackward", [tgo.ptr, tx.ptr, tg.ptr, int(interpolation), int(padding),
+                                             bool(align_corners), m.ptr, tgi.ptr, tgg.ptr], x.device, workspace)
+    return input_grad, grid_grad
+
+
+def grid_sampler3d(x, grid, interpolation=0, padding=0, align_corners=False, fmt="NCDHW", out=None, workspace=None):
+    if out is None:
+        n, do, ho, wo = grid.shape[0], grid.shape[1], grid.shape[2], grid.shape[3]
+        shape = (n, do, ho, wo, x.shape[4]) if fmt == "NDHWC" else (n, x.shape[1], do, ho, wo)
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    tx, tg, ty = acl_tensor(x, fmt), acl_tensor(grid, "ND"), acl_tensor(out, fmt)
+    two_phase("aclnnGridSampler3D", [tx.ptr, tg.ptr, int(interpolation), int(padding), bool(align_corners), ty.ptr],
+              x.device, workspace)
+    return out
+
+
+def grid_sampler3d_backward(grad_out, x, grid, interpolation=0, padding=0, align_corners=False, mask=(True, True),
+                            fmt="NCDHW", input_grad=None, grid_grad=None, workspace=None):
+    input_grad = torch.empty_like(x) if input_grad is None else input_grad
+    grid_grad = torch.empty_like(grid) if grid_grad is None else grid_grad
+    tgo, tx, tg = acl_tensor(grad_out, fmt), acl_tensor(x, fmt), acl_tensor(grid, "ND")
+    tgi, tgg, m = acl_tensor(input_grad, fmt), acl_tensor(grid_grad, "ND"), bool_array(list(mask))
+    two_phase("aclnnGridSampler3DBackward", [tgo.ptr, tx.ptr, tg.ptr, int(interpolation), int(padding),
                                              bool(align_corners), m.ptr, tgi.ptr, tgg.ptr], x.device, workspace)
     return input_grad, grid_grad

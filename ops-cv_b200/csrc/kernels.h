@@ -215,6 +215,16 @@ cudaError_t GridSampler2DBwd(Dt dt, const void* go, const void* x, const void* g
                              GridShape g, const GridGradPlan& plan, void* workspace, cudaStream_t s);
 
 // ---- strided views -----------------------------------------------------------------------------------------
+// GridSampler3D on NCDHW tensors; interp 0 bilinear, 1 nearest; pad 0 zeros, 1 border, 2 reflection.
+struct Grid3dShape {
+    int64_t n, c;
+    int32_t di, hi, wi, dout, ho, wo;
+    int32_t interp, pad, align;
+};
+cudaError_t GridSampler3dFwd(Dt dt, const void* x, const void* grid, void* y, Grid3dShape g, cudaStream_t s);
+cudaError_t GridSampler3dBwd(Dt dt, const void* go, const void* x, const void* grid, void* gi, void* ggrid, float* acc,
+                             Grid3dShape g, bool wantInput, bool wantGrid, cudaStream_t s);
+
 struct View4 {
     int64_t dim[4];
     int64_t stride[4]; // in elements

@@ -386,3 +386,30 @@ def grid_sampler2d_bwd_det_order(go, x_shape, grid, interp=BILINEAR, pad=ZEROS, 
     lib().orc_grid_sampler2d_bwd_det_order(pgo, pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I32(h), I32(w),
                                            I32(ho), I32(wo), I32(interp), I32(pad), I32(int(align)))
     return gi
+
+
+def grid_sampler3d_fwd(x, grid, pad=ZEROS, align=False):
+    """GridSampler3D, bilinear: x (N, C, D, H, W), grid (N, Do, Ho, Wo, 3) -> (N, C, Do, Ho, Wo)."""
+    x, px = _f(x)
+    grid, pg = _f(grid)
+    n, c, d, h, w = x.shape
+    _, do, ho, wo, _ = grid.shape
+    y = np.empty((n, c, do, ho, wo), dtype=np.float32)
+    lib().orc_grid_sampler3d_fwd(px, pg, y.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(d), I64(h), I64(w),
+                                 I64(do), I64(ho), I64(wo), I32(pad), I32(int(align)))
+    return y
+
+
+def grid_sampler3d_bwd(go, x, grid, interp=BILINEAR, pad=ZEROS, align=False):
+    """GridSampler3DGrad (bilinear or nearest): returns (grad_input, grad_grid); the scatter runs serially."""
+    go, pgo = _f(go)
+    x, px = _f(x)
+    grid, pg = _f(grid)
+    n, c, d, h, w = x.shape
+    _, do, ho, wo, _ = grid.shape
+    gi = np.empty_like(x)
+    gg = np.empty_like(grid)
+    lib().orc_grid_sampler3d_bwd(pgo, px, pg, gi.ctypes.data_as(ctypes.c_void_p), gg.ctypes.data_as(ctypes.c_void_p),
+                                 I64(n), I64(c), I64(d), I64(h), I64(w), I64(do), I64(ho), I64(wo), I32(interp),
+                                 I32(pad), I32(int(align)))
+    return gi, gg

@@ -297,6 +297,32 @@ def test_nearest3d_status(ops):
     assert phase1(ops, "aclnnUpsampleNearestExact3dBackward", g.ptr, osz.ptr, isz.ptr, 90.0, 0.0, 0.0, out.ptr)[0] == INVALID
 
 
+def test_grid_sampler3d_status(ops):
+    api = "aclnnGridSampler3D"
+    x, grid, out = T(ops, (2, 3, 4, 5, 6), fmt="NCDHW"), T(ops, (2, 3, 4, 5, 3), fmt="ND"), T(ops, (2, 3, 3, 4, 5), fmt="NCDHW")
+    assert phase1(ops, api, x.ptr, grid.ptr, 0, 0, False, out.ptr)[0] == OK
+    assert phase1(ops, api, x.ptr, grid.ptr, 1, 2, True, out.ptr)[0] == OK
+    assert phase1(ops, api, None, grid.ptr, 0, 0, False, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, None, 0, 0, False, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, grid.ptr, 0, 0, False, None)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, grid.ptr, 2, 0, False, out.ptr)[0] == INVALID     # no bicubic in 3-D
+    assert phase1(ops, api, x.ptr, grid.ptr, 0, 3, False, out.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, T(ops, (2, 3, 4, 5, 2), fmt="ND").ptr, 0, 0, False, out.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, T(ops, (2, 3, 4, 5, 3), torch.float16, fmt="ND").ptr, 0, 0, False, out.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, grid.ptr, 0, 0, False, T(ops, (2, 4, 3, 4, 5), fmt="NCDHW").ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 3, 5, 6), fmt="ND").ptr, grid.ptr, 0, 0, False, out.ptr)[0] == INVALID
+    api = "aclnnGridSampler3DBackward"
+    go, gi, gg, mask = T(ops, (2, 3, 3, 4, 5), fmt="NCDHW"), T(ops, (2, 3, 4, 5, 6), fmt="NCDHW"), T(ops, (2, 3, 4, 5, 3), fmt="ND"), BA(ops, [True, True])
+    assert phase1(ops, api, go.ptr, x.ptr, grid.ptr, 0, 0, False, mask.ptr, gi.ptr, gg.ptr)[0] == OK
+    assert phase1(ops, api, go.ptr, x.ptr, grid.ptr, 0, 0, False, None, gi.ptr, gg.ptr)[0] == NULLPTR
+    assert phase1(ops, api, None, x.ptr, grid.ptr, 0, 0, False, mask.ptr, gi.ptr, gg.ptr)[0] == NULLPTR
+    assert phase1(ops, api, go.ptr, x.ptr, grid.ptr, 0, 0, False, mask.ptr, None, gg.ptr)[0] == NULLPTR
+    assert phase1(ops, api, go.ptr, x.ptr, grid.ptr, 0, 0, False, BA(ops, [True]).ptr, gi.ptr, gg.ptr)[0] == INVALID
+    assert phase1(ops, api, go.ptr, x.ptr, grid.ptr, 2, 0, False, mask.ptr, gi.ptr, gg.ptr)[0] == INVALID
+    assert phase1(ops, api, go.ptr, x.ptr, grid.ptr, 0, 0, False, mask.ptr, T(ops, (2, 3, 4, 5, 7), fmt="NCDHW").ptr, gg.ptr)[0] == INVALID
+    assert phase1(ops, api, go.ptr, x.ptr, grid.ptr, 0, 0, False, BA(ops, [False, False]).ptr, gi.ptr, gg.ptr) == (OK, 0)
+
+
 def test_bilinear_aa_status(ops):
     """aclnnUpsampleBilinear2dAA / ...Backward: the checks of the bicubic-AA pair (NCHW or ND only, one dtype, 4-D,
     sizes > 0) plus negative scales in the forward."""
