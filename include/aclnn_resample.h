@@ -255,6 +255,30 @@ ACLNN_API aclnnStatus aclnnUpsampleNearestExact3dBackwardGetWorkspaceSize(const 
 ACLNN_API aclnnStatus aclnnUpsampleNearestExact3dBackward(void* workspace, uint64_t workspaceSize,
                                                           aclOpExecutor* executor, aclrtStream stream);
 
+/* ---- UpsampleTrilinear3d / UpsampleTrilinear3dBackward ------------------------------------------------------------
+ * Replace image/resize_upsample_trilinear/op_host/op_api/aclnn_upsample_trilinear_3d.h:25-34 (implementation
+ * aclnn_upsample_trilinear_3d.cpp:382-455; kernel arithmetic
+ * image/resize_upsample_trilinear/op_kernel/arch35/resize_upsample_trilinear_simt_base_common.h:47-188) and
+ * image/upsample_trilinear3d_backward/op_host/op_api/aclnn_upsample_trilinear_3d_backward.h:25-36 (implementation
+ * aclnn_upsample_trilinear_3d_backward.cpp:177-245; kernel
+ * image/upsample_trilinear3d_backward/op_kernel/upsample_trilinear3d_backward.h:141-263). The three scales are the
+ * output-per-input factors and are used only when all three are positive; inputSize is (N, C, D, H, W) in either
+ * format. */
+ACLNN_API aclnnStatus aclnnUpsampleTrilinear3dGetWorkspaceSize(const aclTensor* self, const aclIntArray* outputSize,
+                                                               bool alignCorners, double scalesD, double scalesH,
+                                                               double scalesW, aclTensor* out, uint64_t* workspaceSize,
+                                                               aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleTrilinear3d(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
+                                               aclrtStream stream);
+ACLNN_API aclnnStatus aclnnUpsampleTrilinear3dBackwardGetWorkspaceSize(const aclTensor* gradOut,
+                                                                       const aclIntArray* outputSize,
+                                                                       const aclIntArray* inputSize, bool alignCorners,
+                                                                       double scalesD, double scalesH, double scalesW,
+                                                                       aclTensor* gradInput, uint64_t* workspaceSize,
+                                                                       aclOpExecutor** executor);
+ACLNN_API aclnnStatus aclnnUpsampleTrilinear3dBackward(void* workspace, uint64_t workspaceSize,
+                                                       aclOpExecutor* executor, aclrtStream stream);
+
 /* ---- GridSampler3D --------------------------------------------------------------------------------------------
  * Replaces image/grid_sample/op_api/aclnn_grid_sampler3d.h (implementation aclnn_grid_sampler3d.cpp:194-380; kernel
  * image/grid_sample/op_kernel/arch35/grid_sampler_3d_bilinear_smit.h:58-184) and

@@ -97,6 +97,10 @@ SYMBOLS = {
     "aclnnUpsampleNearest3dBackward": _PHASE2,
     "aclnnUpsampleNearestExact3dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _D, _D, _D, _P, _PU64, _PP]),
     "aclnnUpsampleNearestExact3dBackward": _PHASE2,
+    "aclnnUpsampleTrilinear3dGetWorkspaceSize": (_I32, [_P, _P, _B, _D, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleTrilinear3d": _PHASE2,
+    "aclnnUpsampleTrilinear3dBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _B, _D, _D, _D, _P, _PU64, _PP]),
+    "aclnnUpsampleTrilinear3dBackward": _PHASE2,
     "aclnnGridSampler3DGetWorkspaceSize": (_I32, [_P, _P, _I64, _I64, _B, _P, _PU64, _PP]),
     "aclnnGridSampler3D": _PHASE2,
     "aclnnGridSampler3DBackwardGetWorkspaceSize": (_I32, [_P, _P, _P, _I64, _I64, _B, _P, _P, _P, _PU64, _PP]),

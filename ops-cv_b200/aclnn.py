@@ -14,7 +14,8 @@ __all__ = [
     "upsample_bilinear2d_backward", "upsample_bicubic2d", "upsample_bicubic2d_backward", "upsample_bilinear2d_aa",
     "upsample_bilinear2d_aa_backward", "upsample_nearest_exact2d", "upsample_nearest_exact2d_backward",
     "upsample_nearest_exact1d", "upsample_nearest_exact1d_backward", "upsample_nearest3d",
-    "upsample_nearest3d_backward", "grid_sampler3d", "grid_sampler3d_backward", "upsample_bicubic2d_aa",
+    "upsample_nearest3d_backward", "upsample_trilinear3d", "upsample_trilinear3d_backward", "grid_sampler3d",
+    "grid_sampler3d_backward", "upsample_bicubic2d_aa",
     "upsample_bicubic2d_aa_grad", "grid_sampler2d", "grid_sampler2d_backward", "Workspace",
 ]
 
@@ -294,6 +295,32 @@ def upsample_nearest3d_backward(grad_out, out_dhw, input_size, fmt="NCDHW", scal
     name = "aclnnUpsampleNearestExact3dBackward" if exact else "aclnnUpsampleNearest3dBackward"
     two_phase(name, [tg.ptr, osz.ptr, isz.ptr, float(scales[0]), float(scales[1]), float(scales[2]), ty.ptr],
               grad_out.device, workspace)
+    return out
+
+
+def upsample_trilinear3d(x, out_dhw, align_corners=False, fmt="NCDHW", scales=(0.0, 0.0, 0.0), out=None,
+                         workspace=None):
+    if out is None:
+        shape = (x.shape[0], *out_dhw, x.shape[4]) if fmt == "NDHWC" else (x.shape[0], x.shape[1], *out_dhw)
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    tx, ty, size = acl_tensor(x, fmt), acl_tensor(out, fmt), int_array(list(out_dhw))
+    two_phase("aclnnUpsampleTrilinear3d", [tx.ptr, size.ptr, bool(align_corners), float(scales[0]), float(scales[1]),
+                                           float(scales[2]), ty.ptr], x.device, workspace)
+    return out
+
+
+def upsample_trilinear3d_backward(grad_out, out_dhw, input_size, align_corners=False, fmt="NCDHW",
+                                  scales=(0.0, 0.0, 0.0), out=None, workspace=None):
+    """input_size is (N, C, D, H, W) in either format, as in the reference."""
+    if out is None:
+        n, c, d, h, w = input_size
+        shape = (n, d, h, w, c) if fmt == "NDHWC" else (n, c, d, h, w)
+        out = torch.empty(shape, dtype=grad_out.dtype, device=grad_out.device)
+    tg, ty = acl_tensor(grad_out, fmt), acl_tensor(out, fmt)
+    osz, isz = int_array(list(out_dhw)), int_array(list(input_size))
+    two_phase("aclnnUpsampleTrilinear3dBackward", [tg.ptr, osz.ptr, isz.ptr, bool(align_corners), float(scales[0]),
+                                                   float(scales[1]), float(scales[2]), ty.ptr], grad_out.device,
+              workspace)
     return out
 
 

@@ -112,6 +112,25 @@ inline Ranges LerpBwdRanges(const Lerp& t, int32_t in)
     return r;
 }
 
+// Longest weight list of one axis of the trilinear backward: the most grad_output indices whose lower tap is y - 1
+// or y, over all grad_input indices y (see TrilinearBwdTableKernel in upsample_trilinear3d.cu).
+inline int32_t TrilinearBwdTaps(int32_t in, int32_t out, float scale, bool align)
+{
+    std::vector<int32_t> perLower(static_cast<size_t>(in) + 1, 0); // perLower[i] = indices whose lower tap is i
+    const long long last = in - 1;
+    for (int32_t d = 0; d < out; ++d) {
+        const float real = align ? scale * static_cast<float>(d)
+                                 : std::fmax(scale * (static_cast<float>(d) + 0.5f) - 0.5f, 0.0f);
+        const long long i0 = std::min(static_cast<long long>(real), last);
+        ++perLower[static_cast<size_t>(i0)];
+    }
+    int32_t worst = 1;
+    for (int32_t y = 0; y < in; ++y) {
+        worst = std::max(worst, perLower[y] + (y > 0 ? perLower[y - 1] : 0));
+    }
+    return worst;
+}
+
 // Largest number of rows `need(h0, h1)` over all tiles of `tileRows` output rows.
 template <typename F>
 inline int32_t MaxBand(int32_t outRows, int32_t tileRows, F need)

@@ -177,6 +177,28 @@ struct Nearest3dGeom {
 cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStream_t s);
 cudaError_t Nearest3dBwd(Dt dt, const void* go, void* gi, Nearest3dGeom g, cudaStream_t s);
 
+// UpsampleTrilinear3d / UpsampleTrilinear3dBackward. rows and chan as for Nearest3dGeom; sd / sh / sw are the
+// source-coordinate scales of the reference's tiling. loop (forward only): 0 full, 1 / 2 / 3 only D / H / W is
+// resampled, 4 copy.
+struct Trilinear3dGeom {
+    int64_t rows;
+    int32_t di, hi, wi, dout, ho, wo, chan;
+    float sd, sh, sw;
+    int32_t align;
+    int32_t loop;
+};
+// Backward weight lists, one per grad_input index of each axis (0 D, 1 H, 2 W): the grad_output indices
+// [start, start + count) feed it with weights w[index * taps + k]; taps is the longest list of the axis.
+struct TrilinearBwdTables {
+    int32_t* start[3];
+    int32_t* count[3];
+    float* w[3];
+    int32_t taps[3];
+};
+cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, Trilinear3dGeom g, cudaStream_t s);
+cudaError_t BuildTrilinearBwdTables(TrilinearBwdTables t, Trilinear3dGeom g, cudaStream_t s);
+cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, Trilinear3dGeom g, TrilinearBwdTables t, cudaStream_t s);
+
 struct GridShape {
     int64_t n, c;
     int32_t hin, win, hout, wout;

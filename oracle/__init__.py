@@ -71,7 +71,7 @@ def _shape(n, c, h, w, fmt):
     return (n, c, h, w) if fmt == NCHW else (n, h, w, c)
 
 
-I64, F32, I32 = ctypes.c_int64, ctypes.c_float, ctypes.c_int
+I64, F32, I32, F64 = ctypes.c_int64, ctypes.c_float, ctypes.c_int, ctypes.c_double
 
 
 # ---- tables (index / weight computations, compared bit for bit) -----------------------------------------
@@ -200,6 +200,46 @@ def nearest3d_bwd(go, in_dhw, scales=(0.0, 0.0, 0.0), exact=False, fmt=NCHW):
     lib().orc_nearest3d_bwd(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_dhw[0]), I64(in_dhw[1]),
                             I64(in_dhw[2]), I64(do), I64(ho), I64(wo), F32(scales[0]), F32(scales[1]), F32(scales[2]),
                             I32(int(exact)), I32(fmt))
+    return gi
+
+
+def trilinear3d_scale(in_size, out_size, align=False, scales=(0.0, 0.0, 0.0), axis=0):
+    """Source-coordinate scale of one axis (0 D, 1 H, 2 W) as the reference's tiling computes it."""
+    fn = lib().orc_trilinear3d_scale
+    fn.restype = ctypes.c_float
+    return float(fn(I64(in_size), I64(out_size), I32(int(align)), F64(scales[0]), F64(scales[1]), F64(scales[2]),
+                    I32(axis)))
+
+
+def trilinear3d_fwd_loop(in_dhw, out_dhw, align=False, scales=(0.0, 0.0, 0.0)):
+    """Which loop of the reference's SIMT kernel the scales select."""
+    fn = lib().orc_trilinear3d_fwd_loop
+    fn.restype = ctypes.c_int
+    k = fn(I64(in_dhw[0]), I64(in_dhw[1]), I64(in_dhw[2]), I64(out_dhw[0]), I64(out_dhw[1]), I64(out_dhw[2]),
+           I32(int(align)), F64(scales[0]), F64(scales[1]), F64(scales[2]))
+    return ("full", "d_only", "h_only", "w_only", "copy")[k]
+
+
+def trilinear3d_fwd(x, out_dhw, align=False, scales=(0.0, 0.0, 0.0), fmt=NCHW):
+    """UpsampleTrilinear3d forward; fmt NCHW means NCDHW, NHWC means NDHWC. `scales` are the API's (output per
+    input) factors, used only when all three are positive."""
+    x, px = _f(x)
+    n, c, d, h, w = _dims5(x.shape, fmt)
+    y = np.empty(_shape5(n, c, *out_dhw, fmt), dtype=np.float32)
+    lib().orc_trilinear3d_fwd(px, y.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(d), I64(h), I64(w),
+                              I64(out_dhw[0]), I64(out_dhw[1]), I64(out_dhw[2]), I32(int(align)), F64(scales[0]),
+                              F64(scales[1]), F64(scales[2]), I32(fmt))
+    return y
+
+
+def trilinear3d_bwd(go, in_dhw, align=False, scales=(0.0, 0.0, 0.0), fmt=NCHW):
+    """UpsampleTrilinear3dBackward: three separable fp32 stages (W, H, D), ascending grad_output order in each."""
+    go, pg = _f(go)
+    n, c, do, ho, wo = _dims5(go.shape, fmt)
+    gi = np.empty(_shape5(n, c, *in_dhw, fmt), dtype=np.float32)
+    lib().orc_trilinear3d_bwd(pg, gi.ctypes.data_as(ctypes.c_void_p), I64(n), I64(c), I64(in_dhw[0]), I64(in_dhw[1]),
+                              I64(in_dhw[2]), I64(do), I64(ho), I64(wo), I32(int(align)), F64(scales[0]),
+                              F64(scales[1]), F64(scales[2]), I32(fmt))
     return gi
 
 

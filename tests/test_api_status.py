@@ -541,3 +541,47 @@ def test_second_phase_without_a_device_reports_a_runtime_error():
     status, again, msg = out.stdout.strip().split(" ", 2)
     assert int(status) == 361001 and "CUDA error" in msg
     assert int(again) == INVALID  # the executor was consumed by the failed call
+
+
+def test_trilinear3d_status(ops):
+    api = "aclnnUpsampleTrilinear3d"
+    x, y, sz = T(ops, (2, 3, 4, 8, 8), fmt="NCDHW"), T(ops, (2, 3, 8, 16, 12), fmt="NCDHW"), IA(ops, [8, 16, 12])
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == OK
+    assert phase1(ops, api, x.ptr, sz.ptr, True, 2.0, 2.0, 1.5, y.ptr)[0] == OK
+    assert phase1(ops, api, None, sz.ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, None, False, 0.0, 0.0, 0.0, y.ptr)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, api, x.ptr, IA(ops, [8, 16]).ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, IA(ops, [8, 16, 13]).ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, IA(ops, [8, 0, 12]).ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 3, 8, 8)).ptr, sz.ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, x.ptr, sz.ptr, False, 0.0, 0.0, 0.0,
+                  T(ops, (2, 3, 8, 16, 12), torch.float16, fmt="NCDHW").ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 3, 4, 8, 8), torch.int32, fmt="NCDHW").ptr, sz.ptr, False, 0.0, 0.0, 0.0,
+                  T(ops, (2, 3, 8, 16, 12), torch.int32, fmt="NCDHW").ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 3, 4, 8, 8), fmt="NCHW").ptr, sz.ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (2, 0, 4, 8, 8), fmt="NCDHW").ptr, sz.ptr, False, 0.0, 0.0, 0.0, y.ptr)[0] == INVALID
+    assert phase1(ops, api, T(ops, (0, 3, 4, 8, 8), fmt="NCDHW").ptr, sz.ptr, False, 0.0, 0.0, 0.0,
+                  T(ops, (0, 3, 8, 16, 12), fmt="NCDHW").ptr) == (OK, 0)
+    assert phase1(ops, api, T(ops, (2, 4, 8, 8, 3), fmt="NDHWC").ptr, sz.ptr, False, 0.0, 0.0, 0.0,
+                  T(ops, (2, 8, 16, 12, 3), fmt="NDHWC").ptr)[0] == OK
+    api = "aclnnUpsampleTrilinear3dBackward"
+    g, out = T(ops, (2, 3, 8, 16, 12), fmt="NCDHW"), T(ops, (2, 3, 4, 8, 8), fmt="NCDHW")
+    osz, isz = IA(ops, [8, 16, 12]), IA(ops, [2, 3, 4, 8, 8])
+    st, ws = phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, 0.0, out.ptr)
+    assert st == OK and ws > 0  # the per-axis weight lists live in the workspace
+    assert phase1(ops, api, None, osz.ptr, isz.ptr, False, 0.0, 0.0, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, None, isz.ptr, False, 0.0, 0.0, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, None, False, 0.0, 0.0, 0.0, out.ptr)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, 0.0, None)[0] == NULLPTR
+    assert phase1(ops, api, g.ptr, osz.ptr, IA(ops, [2, 3, 4, 8]).ptr, False, 0.0, 0.0, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, IA(ops, [8, 16, 13]).ptr, isz.ptr, False, 0.0, 0.0, 0.0, out.ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, 0.0,
+                  T(ops, (2, 3, 4, 8, 9), fmt="NCDHW").ptr)[0] == INVALID
+    assert phase1(ops, api, g.ptr, osz.ptr, isz.ptr, False, 0.0, 0.0, 0.0,
+                  T(ops, (2, 3, 4, 8, 8), torch.float16, fmt="NCDHW").ptr)[0] == INVALID
+    # input_size stays (N, C, D, H, W) for NDHWC tensors
+    assert phase1(ops, api, T(ops, (2, 8, 16, 12, 3), fmt="NDHWC").ptr, osz.ptr, isz.ptr, True, 0.0, 0.0, 0.0,
+                  T(ops, (2, 4, 8, 8, 3), fmt="NDHWC").ptr)[0] == OK
+    assert phase1(ops, api, T(ops, (0, 3, 8, 16, 12), fmt="NCDHW").ptr, osz.ptr, IA(ops, [0, 3, 4, 8, 8]).ptr, False,
+                  0.0, 0.0, 0.0, T(ops, (0, 3, 4, 8, 8), fmt="NCDHW").ptr) == (OK, 0)
