@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the resampling hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload default|cfg2|cfg3|cfg4|cfg4bf16|cfg5|adj2|adj3|all]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload default|cfg2|cfg3|cfg4|cfg4bf16|cfg5|adj2|adj3|adj4|adj5|all]
                     [--batch-div D] [--impl reference]
 
 One "step" is one pass of every operator of the workload over one batch of seeded synthetic input, called
@@ -281,6 +281,67 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
                            "(triangle filter, support = scale), align_corners=false", "dtype": "f32"}
         return buffers, oplist, cfg
 
+    if name == "adj4":
+        # the 3-D siblings of the up-samplers on a volumetric feature map: nearest and trilinear, both directions
+        n, c, di, hi, wi, do, ho, wo = max(2 // batch_div, 1), 32, 32, 56, 56, 64, 112, 112
+        dt = torch.float16
+
+        def buffers(gen):
+            return {
+                "x": torch.randn((n, c, di, hi, wi), generator=gen, device=gen.device).to(dt),
+                "go": torch.randn((n, c, do, ho, wo), generator=gen, device=gen.device).to(dt),
+                "y_nearest": torch.empty((n, c, do, ho, wo), dtype=dt, device=gen.device),
+                "y_trilinear": torch.empty((n, c, do, ho, wo), dtype=dt, device=gen.device),
+                "gi_nearest": torch.empty((n, c, di, hi, wi), dtype=dt, device=gen.device),
+                "gi_trilinear": torch.empty((n, c, di, hi, wi), dtype=dt, device=gen.device),
+            }
+        small, big = n * c * di * hi * wi * 2, n * c * do * ho * wo * 2
+        oplist = [
+            Op("UpsampleNearest3d", lambda b: ops.upsample_nearest3d(b["x"], (do, ho, wo), out=b["y_nearest"],
+                                                                      workspace=wss[0]),
+               small + big, n * do * ho * wo, ["x"], ["y_nearest"]),
+            Op("UpsampleTrilinear3d", lambda b: ops.upsample_trilinear3d(b["x"], (do, ho, wo), False,
+                                                                          out=b["y_trilinear"], workspace=wss[1]),
+               small + big, n * do * ho * wo, ["x"], ["y_trilinear"]),
+            Op("UpsampleNearest3dBackward", lambda b: ops.upsample_nearest3d_backward(
+                b["go"], (do, ho, wo), (n, c, di, hi, wi), out=b["gi_nearest"], workspace=wss[2]),
+               small + big, n * do * ho * wo, ["go"], ["gi_nearest"]),
+            Op("UpsampleTrilinear3dBackward", lambda b: ops.upsample_trilinear3d_backward(
+                b["go"], (do, ho, wo), (n, c, di, hi, wi), False, out=b["gi_trilinear"], workspace=wss[3]),
+               small + big, n * do * ho * wo, ["go"], ["gi_trilinear"]),
+        ]
+        cfg = {"workload": "3-D siblings on a volumetric feature map: UpsampleNearest3d + UpsampleTrilinear3d forward "
+                           f"and backward, fp16 NCDHW N={n} C=32 32x56x56 -> 64x112x112, align_corners=false",
+               "dtype": "f16"}
+        return buffers, oplist, cfg
+
+    if name == "adj5":
+        # GridSampler3D forward and backward, trilinear taps, uniform-random sample positions
+        n, c, di, hi, wi, do, ho, wo = max(2 // batch_div, 1), 32, 32, 64, 64, 32, 64, 64
+        dt = torch.float32
+
+        def buffers(gen):
+            return {
+                "x": torch.randn((n, c, di, hi, wi), generator=gen, device=gen.device),
+                "grid": torch.rand((n, do, ho, wo, 3), generator=gen, device=gen.device) * 2.2 - 1.1,
+                "go": torch.randn((n, c, do, ho, wo), generator=gen, device=gen.device),
+                "y": torch.empty((n, c, do, ho, wo), dtype=dt, device=gen.device),
+                "gi": torch.empty((n, c, di, hi, wi), dtype=dt, device=gen.device),
+                "ggrid": torch.empty((n, do, ho, wo, 3), dtype=dt, device=gen.device),
+            }
+        xin, gr, out = n * c * di * hi * wi * 4, n * do * ho * wo * 3 * 4, n * c * do * ho * wo * 4
+        oplist = [
+            Op("GridSampler3D", lambda b: ops.grid_sampler3d(b["x"], b["grid"], 0, 0, False, out=b["y"],
+                                                              workspace=wss[0]),
+               xin + gr + out, n * do * ho * wo, ["x", "grid"], ["y"]),
+            Op("GridSampler3DBackward", lambda b: ops.grid_sampler3d_backward(
+                b["go"], b["x"], b["grid"], 0, 0, False, input_grad=b["gi"], grid_grad=b["ggrid"], workspace=wss[1]),
+               out + xin + gr + xin + gr, n * do * ho * wo, ["go", "x", "grid"], ["gi", "ggrid"]),
+        ]
+        cfg = {"workload": f"GridSampler3D forward + backward, bilinear/zeros/align_corners=false, fp32 NCDHW N={n} "
+                           "C=32 32x64x64, grid 32x64x64 uniform[-1.1,1.1]", "dtype": "f32"}
+        return buffers, oplist, cfg
+
     if name == "cfg5":
         import math
         n, c, hi, wi, ho, wo = 512 // batch_div, 256, 64, 64, 128, 128
@@ -502,6 +563,40 @@ def cpu_baseline(workload, budget_s=12.0, torch_budget_s=6.0):
             torch.ops.aten._upsample_bilinear2d_aa_backward(got, [224, 224], [1, 3, 1024, 1024], False, None, None)
         algo = 2 * (x.size + go.size) * 4
         sample = "N=1 of 64 images, forward + backward (scatter definition)"
+    elif workload == "adj4":
+        x = rng.standard_normal((1, 4, 32, 56, 56)).astype(np.float32)
+        go = rng.standard_normal((1, 4, 64, 112, 112)).astype(np.float32)
+
+        def run():
+            oracle.nearest3d_fwd(x, (64, 112, 112))
+            oracle.trilinear3d_fwd(x, (64, 112, 112), False)
+            oracle.nearest3d_bwd(go, (32, 56, 56))
+            oracle.trilinear3d_bwd(go, (32, 56, 56), False)
+        xt, got = torch.from_numpy(x), torch.from_numpy(go)
+
+        def run_torch():
+            F.interpolate(xt, size=(64, 112, 112), mode="nearest")
+            F.interpolate(xt, size=(64, 112, 112), mode="trilinear", align_corners=False)
+            torch.ops.aten.upsample_nearest3d_backward(got, [64, 112, 112], [1, 4, 32, 56, 56], None, None, None)
+            torch.ops.aten.upsample_trilinear3d_backward(got, [64, 112, 112], [1, 4, 32, 56, 56], False, None, None,
+                                                         None)
+        algo = 4 * (x.size + go.size) * 2
+        sample = "N=1, C=4 of N=2, C=32, all four operators, fp32 arithmetic"
+    elif workload == "adj5":
+        x = rng.standard_normal((1, 8, 32, 64, 64)).astype(np.float32)
+        grid = (rng.random((1, 32, 64, 64, 3), dtype=np.float32) * 2.2 - 1.1)
+        go = rng.standard_normal((1, 8, 32, 64, 64)).astype(np.float32)
+
+        def run():
+            oracle.grid_sampler3d_fwd(x, grid)
+            oracle.grid_sampler3d_bwd(go, x, grid)
+        xt, gt, got = torch.from_numpy(x), torch.from_numpy(grid), torch.from_numpy(go)
+
+        def run_torch():
+            F.grid_sample(xt, gt, mode="bilinear", padding_mode="zeros", align_corners=False)
+            torch.ops.aten.grid_sampler_3d_backward(got, xt, gt, 0, 0, False, [True, True])
+        algo = ((x.size + grid.size + go.size) + (go.size + 2 * x.size + 2 * grid.size)) * 4
+        sample = "N=1, C=8 of N=2, C=32, forward + backward"
     elif workload in ("cfg4", "cfg4bf16", "cfg4affine"):
         es = 4 if workload == "cfg4" else 2
         x = rng.standard_normal((1, 256, 64, 64)).astype(np.float32)
@@ -571,9 +666,9 @@ def arm_config(cfg):
 
 
 METRIC = "effective HBM GB/s (algorithmic bytes / device time), all operators of the step"
-OTHER_WORKLOADS = ["cfg3", "cfg4", "cfg4bf16", "cfg5", "adj2", "adj3"]
+OTHER_WORKLOADS = ["cfg3", "cfg4", "cfg4bf16", "cfg5", "adj2", "adj3", "adj4", "adj5"]
 LAUNCH_NOTE = ("CUDA-graph replay of the aclnn second-phase calls: the timed steps replay one graph per buffer set holding "
-               "all operators of the step (cfg2, cfg3, cfg5, adj2, adj3: the independent operators of a step on parallel branches, "
+               "all operators of the step (cfg2, cfg3, cfg5, adj2 - adj5: the independent operators of a step on parallel branches, "
                "each with its own workspace; cfg4: one after the other, the two backward modes write the same tensors); "
                "the per-operator times come from a separate pass: per-operator graphs launched back to back over all "
                "buffer sets between one pair of events")
@@ -771,7 +866,7 @@ def run_workload(wname, args, ops, torch, dev, dist, world, rank, peak, steps, d
         # Operators that share no output buffer (and no workspace) go on parallel branches of the graph: the tail of
         # one kernel then overlaps the head of the next instead of waiting for it.
         outs = [set(op.outputs) for op in oplist]
-        parallel = (wname in ("cfg2", "cfg3", "cfg5", "adj2", "adj3") and not args.serial_step and
+        parallel = (wname in ("cfg2", "cfg3", "cfg5", "adj2", "adj3", "adj4", "adj5") and not args.serial_step and
                     all(outs[a].isdisjoint(outs[b]) for a in range(len(outs)) for b in range(a)))
         branches = [torch.cuda.Stream(dev) for _ in oplist] if parallel else []
 

@@ -166,12 +166,21 @@ ATK = {
     "UpsampleBilinear2dAABackward": ("image/upsample_bilinear2d_aa_backward/tests/st/aclnnUpsampleBilinear2dAABackward/atk_aclnnUpsampleBilinear2dAABackward.json", "interp_bwd"),
     "UpsampleNearestExact2d": ("image/upsample_nearest/tests/st/aclnnUpsampleNearestExact2d/atk_aclnnUpsampleNearestExact2d.json", "interp_fwd"),
     "UpsampleNearestExact2dBackward": ("image/upsample_nearest_exact2d_grad/tests/st/aclnnUpsampleNearestExact2dBackward/atk_aclnnUpsampleNearestExact2dBackward.json", "interp_bwd"),
+    "UpsampleNearest3d": ("image/upsample_nearest3d/tests/st/aclnnUpsampleNearest3d/atk_aclnnUpsampleNearest3d.json", "interp3_fwd"),
+    "UpsampleNearest3dBackward": ("image/upsample_nearest3d_grad/tests/st/aclnnUpsampleNearest3dBackward/atk_aclnnUpsampleNearest3dBackward.json", "interp3_bwd"),
+    "UpsampleNearestExact3d": ("image/upsample_nearest_exact3d/tests/st/aclnnUpsampleNearestExact3d/atk_aclnnUpsampleNearestExact3d.json", "interp3_fwd"),
+    "UpsampleNearestExact3dBackward": ("image/upsample_nearest_exact3d_grad/tests/st/aclnnUpsampleNearestExact3dBackward/atk_aclnnUpsampleNearestExact3dBackward.json", "interp3_bwd"),
+    "UpsampleTrilinear3d": ("image/resize_upsample_trilinear/tests/st/aclnnUpsampleTrilinear3d/atk_aclnnUpsampleTrilinear3d.json", "interp3_fwd"),
+    "UpsampleTrilinear3dBackward": ("image/upsample_trilinear3d_backward/tests/st/aclnnUpsampleTrilinear3dBackward/atk_aclnnUpsampleTrilinear3dBackward.json", "interp3_bwd"),
+    "GridSampler3D": ("image/grid_sample/tests/st/aclnnGridSampler3D/atk_aclnnGridSampler3D.json", "grid3_fwd"),
+    "GridSampler3DBackward": ("image/grid_sampler3_d_grad/tests/st/aclnnGridSampler3DBackward/atk_aclnnGridSampler3DBackward.json", "grid3_bwd"),
 }
 SCALE_FACTOR_APIS = ("UpsampleBilinear2dAA", "UpsampleBilinear2dAABackward", "UpsampleNearestExact2d",
                      "UpsampleNearestExact2dBackward")
 TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
 CASES_PER_API = 20
 MAX_PLANE = 1000   # H * W of any tensor of a kept case
+MAX_VOLUME = 9000  # D * H * W of any tensor of a kept 3-D case (those keep one batch entry and two channels)
 
 
 def case_fields(case):
@@ -211,12 +220,82 @@ def replay_atk(data, index):
         cases = json.load(open(os.path.join(REF, rel)))
         kept = 0
         for case in cases:
-            if kept >= CASES_PER_API:
+            if kept >= (12 if kind.startswith("interp3") else CASES_PER_API):
                 break
             f = case_fields(case)
             rng = np.random.default_rng(7000 + 1000 * list(ATK).index(api) + int(case["id"]))
             name = f"atk.{api}.{case['id']}"
-            if kind in ("interp_fwd", "interp_bwd"):
+            if kind in ("interp3_fwd", "interp3_bwd"):
+                # the executors call interpolate(input, size=size, mode=mode[, align_corners]); the scales are 0
+                _, dt, shape, spec = f["input"]
+                if dt not in TORCH_DT or len(shape) != 5 or "size" not in f:
+                    continue
+                n, c, d, h, w = min(shape[0], 1), min(shape[1], 2), shape[2], shape[3], shape[4]
+                od, oh, ow = f["size"]
+                if min(n, c, d, h, w, od, oh, ow) < 1 or d * h * w > MAX_VOLUME or od * oh * ow > MAX_VOLUME:
+                    continue
+                x = draw(rng, (n, c, d, h, w), spec, TORCH_DT[dt])
+                if x is None:
+                    continue
+                mode = f.get("mode", "nearest")
+                kw = {"size": (od, oh, ow), "mode": mode}
+                if mode == "trilinear":
+                    kw["align_corners"] = as_bool(f.get("align_corners", False))
+                xg = x.clone().requires_grad_(kind == "interp3_bwd")
+                y = F.interpolate(xg, **kw)
+                data[name + ".x"] = x.numpy()
+                meta = {"api": api, "dtype": dt, "shape": [n, c, d, h, w], "size": [od, oh, ow], "mode": mode,
+                        "align": kw.get("align_corners", False)}
+                if kind == "interp3_fwd":
+                    data[name + ".y"] = y.detach().numpy()
+                else:
+                    (gx_ones,) = torch.autograd.grad(y, xg, torch.ones_like(y), retain_graph=True)
+                    g = torch.from_numpy(rng.standard_normal(tuple(y.shape)).astype(np.float32)).to(TORCH_DT[dt]).float()
+                    (gx_rand,) = torch.autograd.grad(y, xg, g)
+                    data[name + ".g"] = g.numpy()
+                    data[name + ".gx_ones"] = gx_ones.numpy()
+                    data[name + ".gx"] = gx_rand.numpy()
+                index.append(meta | {"name": name})
+                kept += 1
+            elif kind in ("grid3_fwd", "grid3_bwd"):
+                _, dt, ishape, ispec = f["input"]
+                _, _, gshape, gspec = f["grid"]
+                if dt not in TORCH_DT or len(ishape) != 5:
+                    continue
+                n, c = min(ishape[0], 2), min(ishape[1], 3)
+                d, h, w = ishape[2], ishape[3], ishape[4]
+                # samples are independent of each other: a large grid is cut to its first 8 x 8 x 8 samples
+                do, ho, wo = min(gshape[1], 8), min(gshape[2], 8), min(gshape[3], 8)
+                if min(n, c, d, h, w, do, ho, wo) < 1 or d * h * w > MAX_VOLUME:
+                    continue
+                x = draw(rng, (n, c, d, h, w), ispec, TORCH_DT[dt])
+                grid = draw(rng, (n, do, ho, wo, 3), gspec, TORCH_DT[dt])
+                if x is None or grid is None:
+                    continue
+                mode = int(f.get("mode", 0))
+                pad = int(f.get("padding_mode", 0))
+                align = as_bool(f.get("align_corners", False))
+                if mode > 1:
+                    continue
+                data[name + ".x"] = x.numpy()
+                data[name + ".grid"] = grid.numpy()
+                meta = {"api": api, "dtype": dt, "mode": mode, "pad": pad, "align": align, "name": name}
+                if kind == "grid3_fwd":
+                    data[name + ".y"] = F.grid_sample(x, grid, mode=["bilinear", "nearest"][mode],
+                                                      padding_mode=["zeros", "border", "reflection"][pad],
+                                                      align_corners=align).numpy()
+                else:
+                    _, _, _, gospec = f["gradOutput"]
+                    go = draw(rng, (n, c, do, ho, wo), gospec, TORCH_DT[dt])
+                    if go is None:
+                        continue
+                    gi, gg = torch.ops.aten.grid_sampler_3d_backward(go, x, grid, mode, pad, align, [True, True])
+                    data[name + ".g"] = go.numpy()
+                    data[name + ".gx"] = gi.numpy()
+                    data[name + ".ggrid"] = gg.numpy()
+                index.append(meta)
+                kept += 1
+            elif kind in ("interp_fwd", "interp_bwd"):
                 _, dt, shape, spec = f["input"]
                 # cases given by scale_factor are replayed for the APIs added after the first fixture was cut (a
                 # change for the others would reshuffle their kept cases)

@@ -1,5 +1,5 @@
 """Replay of the reference's own test inputs (tests/golden/atk_replay.npz, made by tests/golden/make_golden.py
-<reference> replay): a seeded slice of the ST case matrices of the fifteen APIs plus the kernel-UT generator of
+<reference> replay): a seeded slice of the ST case matrices of twenty-three APIs plus the kernel-UT generator of
 UpsampleBilinear2d, each with the torch CPU golden that the reference's executors compute.
 
 The CPU half holds the oracle to these goldens, the GPU half the library (through the C ABI). The bar is the one the
@@ -47,7 +47,47 @@ def run_case(m, backend, oracle):
     t = (lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dt).to(dev)) if gpu else None
     back = lambda y: y.float().cpu().numpy()  # noqa: E731
     rnd = lambda a: torch.from_numpy(a).to(dt).float().numpy()  # noqa: E731  (the oracle's result in the case's dtype)
-    if api.startswith("Upsample"):
+    if api.endswith("3d") or api.endswith("3dBackward"):
+        size, align, shape = tuple(m["size"]), bool(m["align"]), tuple(m["shape"])
+        exact, tri = "Exact" in api, "Trilinear" in api
+        if not api.endswith("Backward"):
+            if tri:
+                got = back(backend.upsample_trilinear3d(t(x), size, align)) if gpu else rnd(
+                    oracle.trilinear3d_fwd(x, size, align))
+            else:
+                got = back(backend.upsample_nearest3d(t(x), size, exact=exact)) if gpu else rnd(
+                    oracle.nearest3d_fwd(x, size, exact=exact))
+            out["y"] = (got, GOLD[name + ".y"])
+        else:
+            for gname, gold in (("ones", "gx_ones"), ("rand", "gx")):
+                g = np.ones((shape[0], shape[1]) + size, np.float32) if gname == "ones" else GOLD[name + ".g"]
+                if tri:
+                    got = back(backend.upsample_trilinear3d_backward(t(g), size, shape, align)) if gpu else rnd(
+                        oracle.trilinear3d_bwd(g, shape[2:], align))
+                else:
+                    got = back(backend.upsample_nearest3d_backward(t(g), size, shape, exact=exact)) if gpu else rnd(
+                        oracle.nearest3d_bwd(g, shape[2:], exact=exact))
+                out[gold] = (got, GOLD[name + "." + gold])
+    elif api.startswith("GridSampler3D"):
+        grid = GOLD[name + ".grid"].astype(np.float32)
+        mode, pad, align = m["mode"], m["pad"], bool(m["align"])
+        if api == "GridSampler3D":
+            if not gpu and mode != 0:
+                return out  # the oracle states the reference's bilinear kernel only; nearest is held on the GPU half
+            got = back(backend.grid_sampler3d(t(x), t(grid), mode, pad, align)) if gpu else rnd(
+                oracle.grid_sampler3d_fwd(x, grid, pad, align))
+            out["y"] = (got, GOLD[name + ".y"])
+        else:
+            g = GOLD[name + ".g"]
+            if gpu:
+                gi, gg = backend.grid_sampler3d_backward(t(g), t(x), t(grid), mode, pad, align)
+                gi, gg = back(gi), back(gg)
+            else:
+                gi, gg = oracle.grid_sampler3d_bwd(g, x, grid, mode, pad, align)
+                gi, gg = rnd(gi), rnd(gg)
+            out["gx"] = (gi, GOLD[name + ".gx"])
+            out["ggrid"] = (gg, GOLD[name + ".ggrid"])
+    elif api.startswith("Upsample"):
         size, align, shape = tuple(m["size"]), bool(m["align"]), tuple(m["shape"])
         scales = tuple(m.get("scales", (0.0, 0.0)))
         if api == "UpsampleNearest2d":
