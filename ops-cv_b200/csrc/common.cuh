@@ -186,6 +186,25 @@ __device__ __forceinline__ F2 AddProduct2(F2 product, F2 b)
     return Fma2(product, MakeF2(one, one), b);
 }
 
+// row = (plane * mid + a) * inner + b. 32-bit divisions when the row count allows (`small`), which is the usual case.
+__device__ __forceinline__ void SplitRow(int64_t row, int32_t inner, int32_t mid, bool small, int64_t& plane, int32_t& a,
+                                         int32_t& b)
+{
+    if (small) {
+        const uint32_t r = static_cast<uint32_t>(row);
+        const uint32_t pa = r / static_cast<uint32_t>(inner);
+        b = static_cast<int32_t>(r - pa * static_cast<uint32_t>(inner));
+        const uint32_t p = pa / static_cast<uint32_t>(mid);
+        a = static_cast<int32_t>(pa - p * static_cast<uint32_t>(mid));
+        plane = p;
+    } else {
+        const int64_t pa = row / inner;
+        b = static_cast<int32_t>(row - pa * inner);
+        plane = pa / mid;
+        a = static_cast<int32_t>(pa - plane * mid);
+    }
+}
+
 // Launch helper: ceil-div.
 __host__ __device__ __forceinline__ int64_t CeilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

@@ -39,6 +39,31 @@ inline dim3 TileBlock(int32_t groups, int32_t rows, int32_t rowsPerThread = 16)
     return dim3(static_cast<unsigned>(ct), static_cast<unsigned>(rt), 1);
 }
 
+// Launch shape of the row kernels of the 3-D resamplers: a block is (column threads) x (row threads) with 256 threads
+// in all, the column side just wide enough for the `colItems` threads a row needs (a power of two), so that narrow
+// rows keep all lanes busy; grid.y walks the rows and is capped so that the grid stays near 16 blocks per SM.
+struct RowLaunch {
+    dim3 grid, block;
+};
+inline RowLaunch RowTiling(int64_t rows, int64_t colItems, int threads = 256)
+{
+    int ct = 1;
+    while (ct < colItems && ct < threads) {
+        ct <<= 1;
+    }
+    const int rt = threads / ct;
+    const int64_t colBlocks = CeilDiv(colItems, static_cast<int64_t>(ct));
+    const int64_t rowBlocks = CeilDiv(rows < 1 ? 1 : rows, static_cast<int64_t>(rt));
+    int64_t cap = static_cast<int64_t>(NumSMs()) * 16 / (colBlocks < 1 ? 1 : colBlocks);
+    cap = cap < 1 ? 1 : cap;
+    int64_t gy = rowBlocks < cap ? rowBlocks : cap;
+    gy = gy < 65535 ? gy : 65535;
+    RowLaunch r;
+    r.grid = dim3(static_cast<unsigned>(colBlocks), static_cast<unsigned>(gy), 1);
+    r.block = dim3(static_cast<unsigned>(ct), static_cast<unsigned>(rt), 1);
+    return r;
+}
+
 inline bool Aligned(const void* p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
 
 // Largest vector width (in elements, power of two, at most 16 bytes) such that `inner` is a multiple of it and

@@ -1,8 +1,8 @@
 // UpsampleNearest3d / UpsampleNearestExact3d forward and backward on NCDHW and NDHWC tensors.
 //
 // Forward (image/upsample_nearest3d/op_kernel/arch35/upsample_nearest3d_simt_base.h:31-88): a pure copy,
-// y[n, c, d, h, w] = x[n, c, sd(d), sh(h), sw(w)] with s(i) = min(floor((i [+ 0.5]) * scale), in - 1). A block row is
-// one output row (plane, d, h): its source row is found once, and each thread gathers a 16-byte pack of the row
+// y[n, c, d, h, w] = x[n, c, sd(d), sh(h), sw(w)] with s(i) = min(floor((i [+ 0.5]) * scale), in - 1). A thread row of a
+// block walks output rows (plane, d, h), finds the source row of each once, and each thread gathers a 16-byte pack of it
 // (NCDHW: adjacent columns with their own source columns; NDHWC: adjacent channels of one pixel, one vector load).
 // Backward (image/upsample_nearest3d_grad/op_kernel/arch35/upsample_nearest3d_grad_simt_base.h:33-58): every
 // grad_input element sums its window [ceil(y * s [- 0.5]), ceil((y + 1) * s [- 0.5])) per axis in fp32, in d, h, w
@@ -37,10 +37,11 @@ __global__ void __launch_bounds__(kThreads) Nearest3dFwdKernel(const T* __restri
 {
     const int64_t inner = static_cast<int64_t>(g.wo) * g.chan; // elements of an output row
     const int64_t rowIn = static_cast<int64_t>(g.wi) * g.chan;
-    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) * V;
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
     if (t0 >= inner) {
         return;
     }
+    const bool small = g.rows <= 0x7fffffffLL;
     // source offsets of this thread's pack inside a source row (the same for every row)
     int32_t off[CHANNELS_LAST ? 1 : V];
     if (CHANNELS_LAST) {
@@ -52,11 +53,11 @@ __global__ void __launch_bounds__(kThreads) Nearest3dFwdKernel(const T* __restri
             off[CHANNELS_LAST ? 0 : v] = SrcIdx(static_cast<int32_t>(t0) + v, g.sw, g.exact, g.wi);
         }
     }
-    for (int64_t row = blockIdx.y; row < g.rows; row += gridDim.y) { // row = (plane, d, h)
-        const int64_t pd = row / g.ho;
-        const int32_t h = static_cast<int32_t>(row - pd * g.ho);
-        const int64_t plane = pd / g.dout;
-        const int32_t d = static_cast<int32_t>(pd - plane * g.dout);
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
+        int64_t plane; // row = (plane, d, h)
+        int32_t d, h;
+        SplitRow(row, g.ho, g.dout, small, plane, d, h);
         const int64_t srcRow = (plane * g.di + SrcIdx(d, g.sd, g.exact, g.di)) * g.hi + SrcIdx(h, g.sh, g.exact, g.hi);
         const T* px = x + srcRow * rowIn;
         T* py = y + row * inner + t0;
@@ -78,18 +79,19 @@ __global__ void __launch_bounds__(kThreads) Nearest3dBwdKernel(const T* __restri
 {
     const int64_t inner = static_cast<int64_t>(g.wi) * g.chan; // elements of a grad_input row
     const int64_t rowGo = static_cast<int64_t>(g.wo) * g.chan;
-    const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (t >= inner) {
         return;
     }
+    const bool small = g.rows <= 0x7fffffffLL;
     const int32_t w = static_cast<int32_t>(t / g.chan);
     const int32_t c = static_cast<int32_t>(t - static_cast<int64_t>(w) * g.chan);
     const int32_t w0 = WindowEdge(w, g.sw, g.exact, g.wo), w1 = WindowEdge(w + 1, g.sw, g.exact, g.wo);
-    for (int64_t row = blockIdx.y; row < g.rows; row += gridDim.y) { // row = (plane, d, h) of grad_input
-        const int64_t pd = row / g.hi;
-        const int32_t h = static_cast<int32_t>(row - pd * g.hi);
-        const int64_t plane = pd / g.di;
-        const int32_t d = static_cast<int32_t>(pd - plane * g.di);
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
+        int64_t plane; // row = (plane, d, h) of grad_input
+        int32_t d, h;
+        SplitRow(row, g.hi, g.di, small, plane, d, h);
         const int32_t d0 = WindowEdge(d, g.sd, g.exact, g.dout), d1 = WindowEdge(d + 1, g.sd, g.exact, g.dout);
         const int32_t h0 = WindowEdge(h, g.sh, g.exact, g.ho), h1 = WindowEdge(h + 1, g.sh, g.exact, g.ho);
         float acc = 0.0f;
@@ -105,12 +107,6 @@ __global__ void __launch_bounds__(kThreads) Nearest3dBwdKernel(const T* __restri
     }
 }
 
-dim3 RowGrid3(int64_t rows, int64_t colBlocks)
-{
-    const int64_t cap = std::max<int64_t>(static_cast<int64_t>(NumSMs()) * 16 / std::max<int64_t>(colBlocks, 1), 1);
-    return dim3(static_cast<unsigned>(colBlocks), static_cast<unsigned>(std::min<int64_t>(std::min<int64_t>(std::max<int64_t>(rows, 1), cap), 65535)), 1);
-}
-
 } // namespace
 
 cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStream_t s)
@@ -124,16 +120,16 @@ cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStr
                      (cl && (!Aligned(x, static_cast<size_t>(v) * es))))) {
         v >>= 1;
     }
-    const dim3 grid = RowGrid3(g.rows, CeilDiv(CeilDiv(inner, v), kThreads));
+    const RowLaunch rl = RowTiling(g.rows, CeilDiv(inner, v), kThreads);
     OPSCV_DISPATCH_DT(dt, T, {
         const T* px = static_cast<const T*>(x);
         T* py = static_cast<T*>(y);
         OPSCV_DISPATCH_VEC(v, V, {
             if constexpr (V * sizeof(T) <= 16) {
                 if (cl) {
-                    Nearest3dFwdKernel<T, V, true><<<grid, kThreads, 0, s>>>(px, py, g);
+                    Nearest3dFwdKernel<T, V, true><<<rl.grid, rl.block, 0, s>>>(px, py, g);
                 } else {
-                    Nearest3dFwdKernel<T, V, false><<<grid, kThreads, 0, s>>>(px, py, g);
+                    Nearest3dFwdKernel<T, V, false><<<rl.grid, rl.block, 0, s>>>(px, py, g);
                 }
             }
         });
@@ -145,8 +141,8 @@ cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStr
 cudaError_t Nearest3dBwd(Dt dt, const void* go, void* gi, Nearest3dGeom g, cudaStream_t s)
 {
     const int64_t inner = static_cast<int64_t>(g.wi) * g.chan;
-    const dim3 grid = RowGrid3(g.rows, CeilDiv(inner, kThreads));
-    OPSCV_DISPATCH_DT(dt, T, { Nearest3dBwdKernel<T><<<grid, kThreads, 0, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g); });
+    const RowLaunch rl = RowTiling(g.rows, inner, kThreads);
+    OPSCV_DISPATCH_DT(dt, T, { Nearest3dBwdKernel<T><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g); });
     CountLaunch();
     return cudaGetLastError();
 }

@@ -8,8 +8,8 @@
 // multiplies and adds. A tap that holds Inf or NaN under a zero weight makes the output NaN. When only one axis is
 // resampled (the other two scales are exactly 1.0f) the reference runs a two-tap loop, fmaf(w0, v0, w1 * v1), in
 // which any Inf / NaN tap gives NaN (resize_upsample_trilinear_simt_base.h:30-60); equal extents are a copy.
-// A block row is one output row (plane, d, h): its D and H taps are found once per row, and each thread keeps the
-// W taps of its pack of adjacent outputs for all the rows it visits.
+// A thread row of a block walks output rows (plane, d, h) and finds the D and H taps of each once; each thread keeps
+// the W taps of its pack of adjacent outputs for all the rows it visits.
 //
 // Backward: the reference runs three separable fp32 stages, W then H then D, each a product with a matrix of the
 // per-axis weights (image/upsample_trilinear3d_backward/op_kernel/upsample_trilinear3d_backward.h:141-163,
@@ -70,10 +70,11 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
 {
     const int64_t inner = static_cast<int64_t>(g.wo) * g.chan; // elements of an output row
     const int64_t rowIn = static_cast<int64_t>(g.wi) * g.chan;
-    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) * V;
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
     if (t0 >= inner) {
         return;
     }
+    const bool small = g.rows <= 0x7fffffffLL;
     // W taps of this thread's pack (the same for every row). Channels-last packs are V channels of one pixel.
     constexpr int NW = CHANNELS_LAST ? 1 : V;
     int32_t o0[NW], o1[NW];
@@ -98,11 +99,11 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
         }
     }
     const float nan = __int_as_float(0x7fc00000);
-    for (int64_t row = blockIdx.y; row < g.rows; row += gridDim.y) { // row = (plane, d, h)
-        const int64_t pd = row / g.ho;
-        const int32_t h = static_cast<int32_t>(row - pd * g.ho);
-        const int64_t plane = pd / g.dout;
-        const int32_t d = static_cast<int32_t>(pd - plane * g.dout);
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
+        int64_t plane; // row = (plane, d, h)
+        int32_t d, h;
+        SplitRow(row, g.ho, g.dout, small, plane, d, h);
         Tap td, th;
         if (MODE == 0 || MODE == 1) {
             td = FwdTap(g.sd, d, g.align, g.di);
@@ -219,25 +220,34 @@ __global__ void TrilinearBwdTableKernel(TrilinearBwdTables t, Trilinear3dGeom g)
     }
 }
 
-template <typename T>
+// KW > 0: the W weight list of every grad_input column has at most KW entries and is kept in registers (zero padded,
+// so the padding adds nothing and is never read from grad_output); KW == 0: read through the table.
+template <typename T, int KW>
 __global__ void __launch_bounds__(kThreads) Trilinear3dBwdKernel(const T* __restrict__ go, T* __restrict__ gi,
                                                                  Trilinear3dGeom g, TrilinearBwdTables t)
 {
     const int64_t inner = static_cast<int64_t>(g.wi) * g.chan; // elements of a grad_input row
     const int64_t rowGo = static_cast<int64_t>(g.wo) * g.chan;
-    const int64_t e0 = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int64_t e0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (e0 >= inner) {
         return;
     }
+    const bool small = g.rows <= 0x7fffffffLL;
     const int32_t w = static_cast<int32_t>(e0 / g.chan);
     const int32_t c = static_cast<int32_t>(e0 - static_cast<int64_t>(w) * g.chan);
     const int32_t ws = __ldg(t.start[2] + w), wc = __ldg(t.count[2] + w);
     const float* __restrict__ ww = t.w[2] + static_cast<int64_t>(w) * t.taps[2];
-    for (int64_t row = blockIdx.y; row < g.rows; row += gridDim.y) { // row = (plane, d, h) of grad_input
-        const int64_t pd = row / g.hi;
-        const int32_t h = static_cast<int32_t>(row - pd * g.hi);
-        const int64_t plane = pd / g.di;
-        const int32_t d = static_cast<int32_t>(pd - plane * g.di);
+    float wr[KW > 0 ? KW : 1];
+#pragma unroll
+    for (int e = 0; e < KW; ++e) {
+        wr[e] = e < t.taps[2] ? __ldg(ww + e) : 0.0f;
+    }
+    const int64_t colOff = static_cast<int64_t>(ws) * g.chan + c;
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
+        int64_t plane; // row = (plane, d, h) of grad_input
+        int32_t d, h;
+        SplitRow(row, g.hi, g.di, small, plane, d, h);
         const int32_t ds = __ldg(t.start[0] + d), dc = __ldg(t.count[0] + d);
         const int32_t hs = __ldg(t.start[1] + h), hc = __ldg(t.count[1] + h);
         const float* __restrict__ wd = t.w[0] + static_cast<int64_t>(d) * t.taps[0];
@@ -245,11 +255,21 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dBwdKernel(const T* __rest
         float accD = 0.0f;
         for (int32_t a = 0; a < dc; ++a) {
             float accH = 0.0f;
+            const T* pa = go + ((plane * g.dout + ds + a) * g.ho + hs) * rowGo + colOff;
             for (int32_t b = 0; b < hc; ++b) {
-                const T* pr = go + ((plane * g.dout + ds + a) * g.ho + hs + b) * rowGo + static_cast<int64_t>(ws) * g.chan + c;
+                const T* pr = pa + b * rowGo;
                 float accW = 0.0f;
-                for (int32_t e = 0; e < wc; ++e) {
-                    accW = Add(accW, Mul(__ldg(ww + e), DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
+                if (KW > 0) {
+#pragma unroll
+                    for (int e = 0; e < KW; ++e) {
+                        if (e < wc) {
+                            accW = Add(accW, Mul(wr[e], DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
+                        }
+                    }
+                } else {
+                    for (int32_t e = 0; e < wc; ++e) {
+                        accW = Add(accW, Mul(__ldg(ww + e), DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
+                    }
                 }
                 accH = Add(accH, Mul(__ldg(wh + b), accW));
             }
@@ -259,22 +279,15 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dBwdKernel(const T* __rest
     }
 }
 
-dim3 RowGridT(int64_t rows, int64_t colBlocks)
-{
-    const int64_t cap = std::max<int64_t>(static_cast<int64_t>(NumSMs()) * 16 / std::max<int64_t>(colBlocks, 1), 1);
-    return dim3(static_cast<unsigned>(colBlocks),
-                static_cast<unsigned>(std::min<int64_t>(std::min<int64_t>(std::max<int64_t>(rows, 1), cap), 65535)), 1);
-}
-
 template <typename T, int V, bool CL>
-void LaunchFwd(const T* x, T* y, const Trilinear3dGeom& g, dim3 grid, cudaStream_t s)
+void LaunchFwd(const T* x, T* y, const Trilinear3dGeom& g, const RowLaunch& rl, cudaStream_t s)
 {
     switch (g.loop) {
-        case 1: Trilinear3dFwdKernel<T, V, CL, 1><<<grid, kThreads, 0, s>>>(x, y, g); break;
-        case 2: Trilinear3dFwdKernel<T, V, CL, 2><<<grid, kThreads, 0, s>>>(x, y, g); break;
-        case 3: Trilinear3dFwdKernel<T, V, CL, 3><<<grid, kThreads, 0, s>>>(x, y, g); break;
-        case 4: Trilinear3dFwdKernel<T, V, CL, 4><<<grid, kThreads, 0, s>>>(x, y, g); break;
-        default: Trilinear3dFwdKernel<T, V, CL, 0><<<grid, kThreads, 0, s>>>(x, y, g); break;
+        case 1: Trilinear3dFwdKernel<T, V, CL, 1><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        case 2: Trilinear3dFwdKernel<T, V, CL, 2><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        case 3: Trilinear3dFwdKernel<T, V, CL, 3><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        case 4: Trilinear3dFwdKernel<T, V, CL, 4><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        default: Trilinear3dFwdKernel<T, V, CL, 0><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
     }
 }
 
@@ -291,16 +304,16 @@ cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, Trilinear3dGeom g, cud
     while (v > 1 && (inner % v != 0 || (cl && g.chan % v != 0) || !Aligned(y, static_cast<size_t>(v) * es))) {
         v >>= 1;
     }
-    const dim3 grid = RowGridT(g.rows, CeilDiv(CeilDiv(inner, v), kThreads));
+    const RowLaunch rl = RowTiling(g.rows, CeilDiv(inner, v), kThreads);
     OPSCV_DISPATCH_DT(dt, T, {
         const T* px = static_cast<const T*>(x);
         T* py = static_cast<T*>(y);
         OPSCV_DISPATCH_VEC(v, V, {
             if constexpr (V * sizeof(T) <= 16) {
                 if (cl) {
-                    LaunchFwd<T, V, true>(px, py, g, grid, s);
+                    LaunchFwd<T, V, true>(px, py, g, rl, s);
                 } else {
-                    LaunchFwd<T, V, false>(px, py, g, grid, s);
+                    LaunchFwd<T, V, false>(px, py, g, rl, s);
                 }
             }
         });
@@ -321,9 +334,17 @@ cudaError_t BuildTrilinearBwdTables(TrilinearBwdTables t, Trilinear3dGeom g, cud
 cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, Trilinear3dGeom g, TrilinearBwdTables t, cudaStream_t s)
 {
     const int64_t inner = static_cast<int64_t>(g.wi) * g.chan;
-    const dim3 grid = RowGridT(g.rows, CeilDiv(inner, kThreads));
+    const RowLaunch rl = RowTiling(g.rows, inner, kThreads);
     OPSCV_DISPATCH_DT(dt, T, {
-        Trilinear3dBwdKernel<T><<<grid, kThreads, 0, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g, t);
+        const T* pg = static_cast<const T*>(go);
+        T* pi = static_cast<T*>(gi);
+        if (t.taps[2] <= 4) {
+            Trilinear3dBwdKernel<T, 4><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
+        } else if (t.taps[2] <= 8) {
+            Trilinear3dBwdKernel<T, 8><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
+        } else {
+            Trilinear3dBwdKernel<T, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
+        }
     });
     CountLaunch();
     return cudaGetLastError();
