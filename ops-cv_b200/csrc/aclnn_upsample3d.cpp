@@ -2,6 +2,7 @@
 // UpsampleTrilinear3d, forward and backward, on NCDHW (or ND) and NDHWC tensors. Same structure as the 2-D entry
 // points: the first phase repeats the reference's checks, computes the scales with the expressions of its arch35 tiling and freezes the
 // launches into the executor.
+#include <algorithm>
 #include <cmath>
 
 #include "host_common.h"
@@ -62,6 +63,41 @@ float FwdScale(int64_t in, int64_t out, float user)
 float BwdScale(int64_t gradsExtent, int64_t inputExtent, float user)
 {
     return user > 0.0f ? user : static_cast<float>(gradsExtent) / static_cast<float>(inputExtent);
+}
+
+// Whole-number up-scale factor of one axis, or 0: out = r * in and every source index (forward) / window edge
+// (backward) that the kernels' fp32 expressions give equals the integer rule d / r resp. r * y. Same operations in
+// the same order as SrcIdx / WindowEdge in upsample_nearest3d.cu (this file is compiled without contraction).
+int32_t WholeFactorFwd(int64_t in, int64_t out, float scale, bool exact)
+{
+    if (out % in != 0) {
+        return 0;
+    }
+    const int64_t r = out / in;
+    for (int64_t i = 0; i < out; ++i) {
+        const float pos = exact ? (static_cast<float>(i) + 0.5f) * scale : static_cast<float>(i) * scale;
+        const long long s = std::min<long long>(static_cast<long long>(std::floor(pos)), in - 1);
+        if (s != i / r) {
+            return 0;
+        }
+    }
+    return static_cast<int32_t>(r);
+}
+int32_t WholeFactorBwd(int64_t in, int64_t out, float scale, bool exact)
+{
+    if (out % in != 0) {
+        return 0;
+    }
+    const int64_t r = out / in;
+    for (int64_t y = 0; y <= in; ++y) {
+        const float v = exact ? static_cast<float>(y) * scale - 0.5f : static_cast<float>(y) * scale;
+        long long e = static_cast<long long>(std::ceil(v));
+        e = std::min<long long>(std::max<long long>(e, 0), out);
+        if (e != r * y) {
+            return 0;
+        }
+    }
+    return static_cast<int32_t>(r);
 }
 
 // image/upsample_nearest3d/op_host/op_api/aclnn_upsample_nearest_3d.cpp:117-128 (CheckParams), :156-204; the exact
@@ -149,6 +185,9 @@ aclnnStatus PlanForward(const char* api, bool exact, const aclTensor* self, cons
     g.sh = FwdScale(gi.h, oh, static_cast<float>(scalesH));
     g.sw = FwdScale(gi.w, ow, static_cast<float>(scalesW));
     g.exact = exact ? 1 : 0;
+    g.rd = WholeFactorFwd(gi.d, od, g.sd, exact);
+    g.rh = WholeFactorFwd(gi.h, oh, g.sh, exact);
+    g.rw = WholeFactorFwd(gi.w, ow, g.sw, exact);
     const Dt dt = ToDt(self->dtype);
     ex->steps.push_back([=](char* w, cudaStream_t s) { return Nearest3dFwd(dt, x.At(w), y.At(w), g, s); });
     FinishOutput(out, y, ex);
@@ -247,6 +286,9 @@ aclnnStatus PlanBackward(const char* api, bool exact, const aclTensor* gradOut, 
     g.sh = BwdScale(oh, gi.h, user ? static_cast<float>(scalesH) : 0.0f);
     g.sw = BwdScale(ow, gi.w, user ? static_cast<float>(scalesW) : 0.0f);
     g.exact = exact ? 1 : 0;
+    g.rd = WholeFactorBwd(gi.d, od, g.sd, exact);
+    g.rh = WholeFactorBwd(gi.h, oh, g.sh, exact);
+    g.rw = WholeFactorBwd(gi.w, ow, g.sw, exact);
     const Dt dt = ToDt(gradOut->dtype);
     ex->steps.push_back([=](char* w, cudaStream_t s) { return Nearest3dBwd(dt, g0.At(w), y.At(w), g, s); });
     FinishOutput(gradInput, y, ex);

@@ -173,6 +173,9 @@ struct Nearest3dGeom {
     int32_t di, hi, wi, dout, ho, wo, chan;
     float sd, sh, sw;
     int32_t exact;
+    // whole-number up-scale factors per axis when the host has checked that every index (forward) or window
+    // (backward) of the axis follows them, else 0; rw == 2 with rd, rh >= 1 selects the replicate / pool kernels
+    int32_t rd = 0, rh = 0, rw = 0;
 };
 cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStream_t s);
 cudaError_t Nearest3dBwd(Dt dt, const void* go, void* gi, Nearest3dGeom g, cudaStream_t s);

@@ -107,6 +107,73 @@ __global__ void __launch_bounds__(kThreads) Nearest3dBwdKernel(const T* __restri
     }
 }
 
+// ---- whole-number up-scales on NCDHW tensors (g.rd, g.rh >= 1 and g.rw == 2, checked on the host against the index
+// rules above): output (d, h, w) reads input (d / rd, h / rh, w / 2). A thread loads VI adjacent input elements of
+// an input row once and stores the 2 * VI outputs they become into each of the rd * rh output rows; the backward
+// loads 2 * VO adjacent grads of each of the rd * rh rows and adds them in (d, h, w) order, VO results per thread.
+template <typename T, int VI>
+__global__ void __launch_bounds__(kThreads) Nearest3dFwdX2Kernel(const T* __restrict__ x, T* __restrict__ y, Nearest3dGeom g)
+{
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VI;
+    if (t0 >= g.wi) {
+        return;
+    }
+    const int64_t rowsIn = g.rows / (static_cast<int64_t>(g.rd) * g.rh); // (plane, d, h) of the input
+    const bool small = rowsIn <= 0x7fffffffLL;
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rowsIn; row += rowStep) {
+        int64_t plane;
+        int32_t d, h;
+        SplitRow(row, g.hi, g.di, small, plane, d, h);
+        const Pack<T, VI> in = *reinterpret_cast<const Pack<T, VI>*>(x + row * g.wi + t0);
+        Pack<T, 2 * VI> out;
+#pragma unroll
+        for (int v = 0; v < VI; ++v) {
+            out.v[2 * v] = in.v[v];
+            out.v[2 * v + 1] = in.v[v];
+        }
+        for (int32_t a = 0; a < g.rd; ++a) {
+            for (int32_t b = 0; b < g.rh; ++b) {
+                const int64_t orow = (plane * g.dout + static_cast<int64_t>(d) * g.rd + a) * g.ho + static_cast<int64_t>(h) * g.rh + b;
+                *reinterpret_cast<Pack<T, 2 * VI>*>(y + orow * g.wo + 2 * t0) = out;
+            }
+        }
+    }
+}
+
+template <typename T, int VO>
+__global__ void __launch_bounds__(kThreads) Nearest3dBwdX2Kernel(const T* __restrict__ go, T* __restrict__ gi, Nearest3dGeom g)
+{
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VO;
+    if (t0 >= g.wi) {
+        return;
+    }
+    const bool small = g.rows <= 0x7fffffffLL;
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
+        int64_t plane; // row = (plane, d, h) of grad_input
+        int32_t d, h;
+        SplitRow(row, g.hi, g.di, small, plane, d, h);
+        float acc[VO];
+#pragma unroll
+        for (int v = 0; v < VO; ++v) {
+            acc[v] = 0.0f;
+        }
+        for (int32_t a = 0; a < g.rd; ++a) {
+            for (int32_t b = 0; b < g.rh; ++b) {
+                const int64_t orow = (plane * g.dout + static_cast<int64_t>(d) * g.rd + a) * g.ho + static_cast<int64_t>(h) * g.rh + b;
+                float gv[2 * VO];
+                LoadPackLdg<T, 2 * VO>(go + orow * g.wo + 2 * t0, gv);
+#pragma unroll
+                for (int v = 0; v < VO; ++v) {
+                    acc[v] = Add(Add(acc[v], gv[2 * v]), gv[2 * v + 1]);
+                }
+            }
+        }
+        StorePack<T, VO>(gi + row * g.wi + t0, acc);
+    }
+}
+
 } // namespace
 
 cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStream_t s)
@@ -114,6 +181,28 @@ cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStr
     const int64_t inner = static_cast<int64_t>(g.wo) * g.chan;
     const int es = DtSize(dt);
     const bool cl = g.chan > 1;
+    if (!cl && g.rw == 2 && g.rd >= 1 && g.rh >= 1) {
+        int vi = 8 / es; // 16 bytes of outputs per store
+        while (vi > 1 && (g.wi % vi != 0 || !Aligned(x, static_cast<size_t>(vi) * es) ||
+                          !Aligned(y, static_cast<size_t>(2 * vi) * es))) {
+            vi >>= 1;
+        }
+        if (Aligned(y, static_cast<size_t>(2 * vi) * es)) {
+            const int64_t rowsIn = g.rows / (static_cast<int64_t>(g.rd) * g.rh);
+            const RowLaunch rl = RowTiling(rowsIn, CeilDiv(static_cast<int64_t>(g.wi), vi), kThreads);
+            OPSCV_DISPATCH_DT(dt, T, {
+                const T* px = static_cast<const T*>(x);
+                T* py = static_cast<T*>(y);
+                OPSCV_DISPATCH_VEC(vi, VI, {
+                    if constexpr (2 * VI * sizeof(T) <= 16) {
+                        Nearest3dFwdX2Kernel<T, VI><<<rl.grid, rl.block, 0, s>>>(px, py, g);
+                    }
+                });
+            });
+            CountLaunch();
+            return cudaGetLastError();
+        }
+    }
     // pack width: 16 bytes when rows keep that alignment; channels-last packs must not straddle a pixel
     int v = 16 / es;
     while (v > 1 && (inner % v != 0 || (cl && g.chan % v != 0) || !Aligned(y, static_cast<size_t>(v) * es) ||
@@ -141,6 +230,28 @@ cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStr
 cudaError_t Nearest3dBwd(Dt dt, const void* go, void* gi, Nearest3dGeom g, cudaStream_t s)
 {
     const int64_t inner = static_cast<int64_t>(g.wi) * g.chan;
+    const int es = DtSize(dt);
+    if (g.chan == 1 && g.rw == 2 && g.rd >= 1 && g.rh >= 1) {
+        int vo = 8 / es; // 16 bytes of grads per load
+        while (vo > 1 && (g.wi % vo != 0 || !Aligned(gi, static_cast<size_t>(vo) * es) ||
+                          !Aligned(go, static_cast<size_t>(2 * vo) * es))) {
+            vo >>= 1;
+        }
+        if (Aligned(go, static_cast<size_t>(2 * vo) * es)) {
+            const RowLaunch rl = RowTiling(g.rows, CeilDiv(static_cast<int64_t>(g.wi), vo), kThreads);
+            OPSCV_DISPATCH_DT(dt, T, {
+                const T* pg = static_cast<const T*>(go);
+                T* pi = static_cast<T*>(gi);
+                OPSCV_DISPATCH_VEC(vo, VO, {
+                    if constexpr (2 * VO * sizeof(T) <= 16) {
+                        Nearest3dBwdX2Kernel<T, VO><<<rl.grid, rl.block, 0, s>>>(pg, pi, g);
+                    }
+                });
+            });
+            CountLaunch();
+            return cudaGetLastError();
+        }
+    }
     const RowLaunch rl = RowTiling(g.rows, inner, kThreads);
     OPSCV_DISPATCH_DT(dt, T, { Nearest3dBwdKernel<T><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(go), static_cast<T*>(gi), g); });
     CountLaunch();

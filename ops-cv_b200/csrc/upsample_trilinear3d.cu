@@ -50,7 +50,8 @@ __device__ __forceinline__ Tap FwdTap(float scale, int32_t dst, int32_t align, i
     return t;
 }
 
-__device__ __forceinline__ bool Special(float v) { return isinf(v) || isnan(v); }
+// Inf or NaN: all exponent bits set.
+__device__ __forceinline__ bool Special(float v) { return (__float_as_uint(v) & 0x7f800000u) == 0x7f800000u; }
 
 __device__ __forceinline__ bool ZeroSpecial(float v, float wd, float wh, float ww)
 {
@@ -79,6 +80,7 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
     constexpr int NW = CHANNELS_LAST ? 1 : V;
     int32_t o0[NW], o1[NW];
     float ww0[NW], ww1[NW];
+    bool colZero = false; // some W weight of the pack is zero: the zero-weight test below has to look at the taps
     {
         const int32_t wFirst = CHANNELS_LAST ? static_cast<int32_t>(t0 / g.chan) : static_cast<int32_t>(t0);
         const int32_t cOff = CHANNELS_LAST ? static_cast<int32_t>(t0 - static_cast<int64_t>(wFirst) * g.chan) : 0;
@@ -96,6 +98,7 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
             o1[v] = t.i1 * g.chan + cOff;
             ww0[v] = t.w0;
             ww1[v] = t.w1;
+            colZero = colZero || t.w0 == 0.0f || t.w1 == 0.0f;
         }
     }
     const float nan = __int_as_float(0x7fc00000);
@@ -119,6 +122,7 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
             th.w0 = 1.0f;
             th.w1 = 0.0f;
         }
+        const bool anyZero = colZero || td.w0 == 0.0f || td.w1 == 0.0f || th.w0 == 0.0f || th.w1 == 0.0f;
         const T* p00 = x + ((plane * g.di + td.i0) * g.hi + th.i0) * rowIn;
         const T* p01 = x + ((plane * g.di + td.i0) * g.hi + th.i1) * rowIn;
         const T* p10 = x + ((plane * g.di + td.i1) * g.hi + th.i0) * rowIn;
@@ -144,10 +148,13 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
                 const float v010 = DType<T>::Load(p01 + o0[k] + e), v011 = DType<T>::Load(p01 + o1[k] + e);
                 const float v100 = DType<T>::Load(p10 + o0[k] + e), v101 = DType<T>::Load(p10 + o1[k] + e);
                 const float v110 = DType<T>::Load(p11 + o0[k] + e), v111 = DType<T>::Load(p11 + o1[k] + e);
-                const bool bad = ZeroSpecial(v000, td.w0, th.w0, ww0[k]) || ZeroSpecial(v001, td.w0, th.w0, ww1[k]) ||
-                                 ZeroSpecial(v010, td.w0, th.w1, ww0[k]) || ZeroSpecial(v011, td.w0, th.w1, ww1[k]) ||
-                                 ZeroSpecial(v100, td.w1, th.w0, ww0[k]) || ZeroSpecial(v101, td.w1, th.w0, ww1[k]) ||
-                                 ZeroSpecial(v110, td.w1, th.w1, ww0[k]) || ZeroSpecial(v111, td.w1, th.w1, ww1[k]);
+                bool bad = false;
+                if (anyZero) { // no weight is zero for most rows and packs: nothing to test then
+                    bad = ZeroSpecial(v000, td.w0, th.w0, ww0[k]) || ZeroSpecial(v001, td.w0, th.w0, ww1[k]) ||
+                          ZeroSpecial(v010, td.w0, th.w1, ww0[k]) || ZeroSpecial(v011, td.w0, th.w1, ww1[k]) ||
+                          ZeroSpecial(v100, td.w1, th.w0, ww0[k]) || ZeroSpecial(v101, td.w1, th.w0, ww1[k]) ||
+                          ZeroSpecial(v110, td.w1, th.w1, ww0[k]) || ZeroSpecial(v111, td.w1, th.w1, ww1[k]);
+                }
                 const float lo = Plane(th.w0, th.w1, ww0[k], ww1[k], v000, v001, v010, v011);
                 const float hi = Plane(th.w0, th.w1, ww0[k], ww1[k], v100, v101, v110, v111);
                 out[v] = bad ? nan : Add(Mul(td.w0, lo), Mul(td.w1, hi));
@@ -221,8 +228,10 @@ __global__ void TrilinearBwdTableKernel(TrilinearBwdTables t, Trilinear3dGeom g)
 }
 
 // KW > 0: the W weight list of every grad_input column has at most KW entries and is kept in registers (zero padded,
-// so the padding adds nothing and is never read from grad_output); KW == 0: read through the table.
-template <typename T, int KW>
+// so the padding adds nothing and is never read from grad_output); KW == 0: read through the table. KH > 0: the H
+// list has at most KH entries and the loop over it is unrolled, so that the loads of a whole (depth) slab of taps
+// are in flight together.
+template <typename T, int KW, int KH>
 __global__ void __launch_bounds__(kThreads) Trilinear3dBwdKernel(const T* __restrict__ go, T* __restrict__ gi,
                                                                  Trilinear3dGeom g, TrilinearBwdTables t)
 {
@@ -256,22 +265,46 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dBwdKernel(const T* __rest
         for (int32_t a = 0; a < dc; ++a) {
             float accH = 0.0f;
             const T* pa = go + ((plane * g.dout + ds + a) * g.ho + hs) * rowGo + colOff;
-            for (int32_t b = 0; b < hc; ++b) {
-                const T* pr = pa + b * rowGo;
-                float accW = 0.0f;
-                if (KW > 0) {
+            if constexpr (KW > 0 && KH > 0) {
+                float gv[KH][KW];
+#pragma unroll
+                for (int b = 0; b < KH; ++b) {
 #pragma unroll
                     for (int e = 0; e < KW; ++e) {
-                        if (e < wc) {
-                            accW = Add(accW, Mul(wr[e], DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
-                        }
-                    }
-                } else {
-                    for (int32_t e = 0; e < wc; ++e) {
-                        accW = Add(accW, Mul(__ldg(ww + e), DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
+                        gv[b][e] = (b < hc && e < wc) ? DType<T>::Load(pa + b * rowGo + static_cast<int64_t>(e) * g.chan) : 0.0f;
                     }
                 }
-                accH = Add(accH, Mul(__ldg(wh + b), accW));
+#pragma unroll
+                for (int b = 0; b < KH; ++b) {
+                    if (b < hc) {
+                        float accW = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < KW; ++e) {
+                            if (e < wc) {
+                                accW = Add(accW, Mul(wr[e], gv[b][e]));
+                            }
+                        }
+                        accH = Add(accH, Mul(__ldg(wh + b), accW));
+                    }
+                }
+            } else {
+                for (int32_t b = 0; b < hc; ++b) {
+                    const T* pr = pa + b * rowGo;
+                    float accW = 0.0f;
+                    if (KW > 0) {
+#pragma unroll
+                        for (int e = 0; e < KW; ++e) {
+                            if (e < wc) {
+                                accW = Add(accW, Mul(wr[e], DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
+                            }
+                        }
+                    } else {
+                        for (int32_t e = 0; e < wc; ++e) {
+                            accW = Add(accW, Mul(__ldg(ww + e), DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
+                        }
+                    }
+                    accH = Add(accH, Mul(__ldg(wh + b), accW));
+                }
             }
             accD = Add(accD, Mul(__ldg(wd + a), accH));
         }
@@ -338,12 +371,14 @@ cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, Trilinear3dGeom g, T
     OPSCV_DISPATCH_DT(dt, T, {
         const T* pg = static_cast<const T*>(go);
         T* pi = static_cast<T*>(gi);
-        if (t.taps[2] <= 4) {
-            Trilinear3dBwdKernel<T, 4><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
+        if (t.taps[2] <= 4 && t.taps[1] <= 4) {
+            Trilinear3dBwdKernel<T, 4, 4><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
+        } else if (t.taps[2] <= 4) {
+            Trilinear3dBwdKernel<T, 4, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
         } else if (t.taps[2] <= 8) {
-            Trilinear3dBwdKernel<T, 8><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
+            Trilinear3dBwdKernel<T, 8, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
         } else {
-            Trilinear3dBwdKernel<T, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
+            Trilinear3dBwdKernel<T, 0, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
         }
     });
     CountLaunch();
