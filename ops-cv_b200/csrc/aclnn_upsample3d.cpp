@@ -406,7 +406,11 @@ aclnnStatus PlanTrilinearFwd(const char* api, const aclTensor* self, const aclIn
     const bool dEq = g.sd == 1.0f && gi.d == od, hEq = g.sh == 1.0f && gi.h == oh, wEq = g.sw == 1.0f && gi.w == ow;
     g.loop = (dEq && hEq && wEq) ? 4 : (hEq && wEq) ? 1 : (dEq && wEq) ? 2 : (dEq && hEq) ? 3 : 0;
     const Dt dt = ToDt(self->dtype);
-    ex->steps.push_back([=](char* w, cudaStream_t s) { return Trilinear3dFwd(dt, x.At(w), y.At(w), g, s); });
+    const uint64_t stageBytes = Trilinear3dFwdWorkspace(g, cl ? gi.n : gi.n * gi.c);
+    const uint64_t stageOff = stageBytes > 0 ? ws.Alloc(stageBytes) : 0;
+    ex->steps.push_back([=](char* w, cudaStream_t s) {
+        return Trilinear3dFwd(dt, x.At(w), y.At(w), stageBytes > 0 ? reinterpret_cast<float*>(w + stageOff) : nullptr, g, s);
+    });
     FinishOutput(out, y, ex);
     ex->workspaceSize = ws.Size();
     *workspaceSize = ws.Size();
@@ -500,6 +504,7 @@ aclnnStatus PlanTrilinearBwd(const char* api, const aclTensor* gradOut, const ac
         offW[a] = ws.Alloc(sizeof(float) * static_cast<uint64_t>(ins[a]) * static_cast<uint64_t>(taps[a]));
     }
     const Dt dt = ToDt(gradOut->dtype);
+    const uint64_t stageOff = ws.Alloc(Trilinear3dBwdWorkspace(g, cl ? gi.n : gi.n * gi.c));
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         TrilinearBwdTables t;
         for (int a = 0; a < 3; ++a) {
@@ -512,7 +517,7 @@ aclnnStatus PlanTrilinearBwd(const char* api, const aclTensor* gradOut, const ac
         if (e != cudaSuccess) {
             return e;
         }
-        return Trilinear3dBwd(dt, g0.At(w), y.At(w), g, t, s);
+        return Trilinear3dBwd(dt, g0.At(w), y.At(w), reinterpret_cast<float*>(w + stageOff), g, t, s);
     });
     FinishOutput(gradInput, y, ex);
     ex->workspaceSize = ws.Size();

@@ -198,9 +198,14 @@ struct TrilinearBwdTables {
     float* w[3];
     int32_t taps[3];
 };
-cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, Trilinear3dGeom g, cudaStream_t s);
+// stage: fp32 scratch of Trilinear3dFwdWorkspace / Trilinear3dBwdWorkspace bytes (planes = N * C for NCDHW, N for
+// NDHWC); the forward needs none for the one-axis loops and the copy.
+uint64_t Trilinear3dFwdWorkspace(const Trilinear3dGeom& g, int64_t planes);
+uint64_t Trilinear3dBwdWorkspace(const Trilinear3dGeom& g, int64_t planes);
+cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, float* stage, Trilinear3dGeom g, cudaStream_t s);
 cudaError_t BuildTrilinearBwdTables(TrilinearBwdTables t, Trilinear3dGeom g, cudaStream_t s);
-cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, Trilinear3dGeom g, TrilinearBwdTables t, cudaStream_t s);
+cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, float* stage, Trilinear3dGeom g, TrilinearBwdTables t,
+                           cudaStream_t s);
 
 struct GridShape {
     int64_t n, c;

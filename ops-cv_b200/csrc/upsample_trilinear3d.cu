@@ -8,14 +8,18 @@
 // multiplies and adds. A tap that holds Inf or NaN under a zero weight makes the output NaN. When only one axis is
 // resampled (the other two scales are exactly 1.0f) the reference runs a two-tap loop, fmaf(w0, v0, w1 * v1), in
 // which any Inf / NaN tap gives NaN (resize_upsample_trilinear_simt_base.h:30-60); equal extents are a copy.
-// A thread row of a block walks output rows (plane, d, h) and finds the D and H taps of each once; each thread keeps
-// the W taps of its pack of adjacent outputs for all the rows it visits.
+// The three axes are resampled one after the other, which is the nesting of the reference's expression: a W stage
+// writes a(plane, d_in, h_in, w_out) = wW0 * v0 + wW1 * v1 in fp32 to the workspace, and an H + D stage blends
+// four rows of it, wD0 * (wH0 * a00 + wH1 * a01) + wD1 * (wH0 * a10 + wH1 * a11), with 16-byte loads. The same
+// multiplies and adds in the same order as the reference's single expression, so the bits are the same; a zero
+// weight on an Inf or NaN tap gives NaN through the IEEE product itself, which is what the reference's explicit test
+// returns. The one-axis loops and the copy run in one kernel (two taps, explicit Inf / NaN test).
 //
 // Backward: the reference runs three separable fp32 stages, W then H then D, each a product with a matrix of the
 // per-axis weights (image/upsample_trilinear3d_backward/op_kernel/upsample_trilinear3d_backward.h:141-163,
-// :205-263; 16-bit tensors are cast to fp32 around it). Here one gather kernel evaluates the same nesting for
-// every grad_input element: sum over a of wD * (sum over b of wH * (sum over e of wW * g[a, b, e])), ascending
-// grad_output index in each sum, fp32 throughout, rounded once. The weights of each grad_input index (one list per
+// :205-263; 16-bit tensors are cast to fp32 around it). Here each stage is one launch of a gather kernel,
+// out(o, i, j) = sum over k of w[i][k] * in(o, start[i] + k, j), in ascending grad_output order, with fp32
+// intermediates in the workspace and one rounding at the end. The weights of each grad_input index (one list per
 // axis, zero padded to the longest) are built on the device by BuildTrilinearBwdTables.
 #include <algorithm>
 
@@ -53,20 +57,9 @@ __device__ __forceinline__ Tap FwdTap(float scale, int32_t dst, int32_t align, i
 // Inf or NaN: all exponent bits set.
 __device__ __forceinline__ bool Special(float v) { return (__float_as_uint(v) & 0x7f800000u) == 0x7f800000u; }
 
-__device__ __forceinline__ bool ZeroSpecial(float v, float wd, float wh, float ww)
-{
-    return (wd == 0.0f || wh == 0.0f || ww == 0.0f) && Special(v);
-}
-
-__device__ __forceinline__ float Plane(float wh0, float wh1, float ww0, float ww1, float v00, float v01, float v10,
-                                       float v11)
-{
-    return Add(Mul(wh0, Add(Mul(ww0, v00), Mul(ww1, v01))), Mul(wh1, Add(Mul(ww0, v10), Mul(ww1, v11))));
-}
-
-// MODE: 0 full, 1 D only, 2 H only, 3 W only, 4 copy.
+// One-axis loops and the copy. MODE: 1 D only, 2 H only, 3 W only, 4 copy.
 template <typename T, int V, bool CHANNELS_LAST, int MODE>
-__global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __restrict__ x, T* __restrict__ y,
+__global__ void __launch_bounds__(kThreads) Trilinear3dAxisKernel(const T* __restrict__ x, T* __restrict__ y,
                                                                  Trilinear3dGeom g)
 {
     const int64_t inner = static_cast<int64_t>(g.wo) * g.chan; // elements of an output row
@@ -80,14 +73,13 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
     constexpr int NW = CHANNELS_LAST ? 1 : V;
     int32_t o0[NW], o1[NW];
     float ww0[NW], ww1[NW];
-    bool colZero = false; // some W weight of the pack is zero: the zero-weight test below has to look at the taps
     {
         const int32_t wFirst = CHANNELS_LAST ? static_cast<int32_t>(t0 / g.chan) : static_cast<int32_t>(t0);
         const int32_t cOff = CHANNELS_LAST ? static_cast<int32_t>(t0 - static_cast<int64_t>(wFirst) * g.chan) : 0;
 #pragma unroll
         for (int v = 0; v < NW; ++v) {
             Tap t;
-            if (MODE == 0 || MODE == 3) {
+            if (MODE == 3) {
                 t = FwdTap(g.sw, wFirst + v, g.align, g.wi);
             } else {
                 t.i0 = t.i1 = wFirst + v;
@@ -98,7 +90,6 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
             o1[v] = t.i1 * g.chan + cOff;
             ww0[v] = t.w0;
             ww1[v] = t.w1;
-            colZero = colZero || t.w0 == 0.0f || t.w1 == 0.0f;
         }
     }
     const float nan = __int_as_float(0x7fc00000);
@@ -108,25 +99,23 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
         int32_t d, h;
         SplitRow(row, g.ho, g.dout, small, plane, d, h);
         Tap td, th;
-        if (MODE == 0 || MODE == 1) {
+        if (MODE == 1) {
             td = FwdTap(g.sd, d, g.align, g.di);
         } else {
             td.i0 = td.i1 = d;
             td.w0 = 1.0f;
             td.w1 = 0.0f;
         }
-        if (MODE == 0 || MODE == 2) {
+        if (MODE == 2) {
             th = FwdTap(g.sh, h, g.align, g.hi);
         } else {
             th.i0 = th.i1 = h;
             th.w0 = 1.0f;
             th.w1 = 0.0f;
         }
-        const bool anyZero = colZero || td.w0 == 0.0f || td.w1 == 0.0f || th.w0 == 0.0f || th.w1 == 0.0f;
         const T* p00 = x + ((plane * g.di + td.i0) * g.hi + th.i0) * rowIn;
         const T* p01 = x + ((plane * g.di + td.i0) * g.hi + th.i1) * rowIn;
         const T* p10 = x + ((plane * g.di + td.i1) * g.hi + th.i0) * rowIn;
-        const T* p11 = x + ((plane * g.di + td.i1) * g.hi + th.i1) * rowIn;
         float out[V];
 #pragma unroll
         for (int v = 0; v < V; ++v) {
@@ -143,22 +132,82 @@ __global__ void __launch_bounds__(kThreads) Trilinear3dFwdKernel(const T* __rest
             } else if (MODE == 3) {
                 const float v0 = DType<T>::Load(p00 + o0[k] + e), v1 = DType<T>::Load(p00 + o1[k] + e);
                 out[v] = (Special(v0) || Special(v1)) ? nan : __fmaf_rn(ww0[k], v0, Mul(ww1[k], v1));
-            } else {
-                const float v000 = DType<T>::Load(p00 + o0[k] + e), v001 = DType<T>::Load(p00 + o1[k] + e);
-                const float v010 = DType<T>::Load(p01 + o0[k] + e), v011 = DType<T>::Load(p01 + o1[k] + e);
-                const float v100 = DType<T>::Load(p10 + o0[k] + e), v101 = DType<T>::Load(p10 + o1[k] + e);
-                const float v110 = DType<T>::Load(p11 + o0[k] + e), v111 = DType<T>::Load(p11 + o1[k] + e);
-                bool bad = false;
-                if (anyZero) { // no weight is zero for most rows and packs: nothing to test then
-                    bad = ZeroSpecial(v000, td.w0, th.w0, ww0[k]) || ZeroSpecial(v001, td.w0, th.w0, ww1[k]) ||
-                          ZeroSpecial(v010, td.w0, th.w1, ww0[k]) || ZeroSpecial(v011, td.w0, th.w1, ww1[k]) ||
-                          ZeroSpecial(v100, td.w1, th.w0, ww0[k]) || ZeroSpecial(v101, td.w1, th.w0, ww1[k]) ||
-                          ZeroSpecial(v110, td.w1, th.w1, ww0[k]) || ZeroSpecial(v111, td.w1, th.w1, ww1[k]);
-                }
-                const float lo = Plane(th.w0, th.w1, ww0[k], ww1[k], v000, v001, v010, v011);
-                const float hi = Plane(th.w0, th.w1, ww0[k], ww1[k], v100, v101, v110, v111);
-                out[v] = bad ? nan : Add(Mul(td.w0, lo), Mul(td.w1, hi));
             }
+        }
+        StorePack<T, V>(y + row * inner + t0, out);
+    }
+}
+
+// ---- the full (three-axis) forward in two launches -----------------------------------------------------------
+// W stage: a[row][w_out] = wW0 * x[row][i0] + wW1 * x[row][i1] for every input row (plane, d_in, h_in), fp32.
+template <typename T, int V, bool CHANNELS_LAST>
+__global__ void __launch_bounds__(kThreads) TrilinearWStageKernel(const T* __restrict__ x, float* __restrict__ a,
+                                                                  Trilinear3dGeom g, int64_t rowsIn)
+{
+    const int64_t inner = static_cast<int64_t>(g.wo) * g.chan;
+    const int64_t rowIn = static_cast<int64_t>(g.wi) * g.chan;
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+    if (t0 >= inner) {
+        return;
+    }
+    constexpr int NW = CHANNELS_LAST ? 1 : V;
+    int32_t o0[NW], o1[NW];
+    float ww0[NW], ww1[NW];
+    {
+        const int32_t wFirst = CHANNELS_LAST ? static_cast<int32_t>(t0 / g.chan) : static_cast<int32_t>(t0);
+        const int32_t cOff = CHANNELS_LAST ? static_cast<int32_t>(t0 - static_cast<int64_t>(wFirst) * g.chan) : 0;
+#pragma unroll
+        for (int v = 0; v < NW; ++v) {
+            const Tap t = FwdTap(g.sw, wFirst + v, g.align, g.wi);
+            o0[v] = t.i0 * g.chan + cOff;
+            o1[v] = t.i1 * g.chan + cOff;
+            ww0[v] = t.w0;
+            ww1[v] = t.w1;
+        }
+    }
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rowsIn; row += rowStep) {
+        const T* px = x + row * rowIn;
+        float out[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const int k = CHANNELS_LAST ? 0 : v;
+            const int e = CHANNELS_LAST ? v : 0;
+            out[v] = Add(Mul(ww0[k], DType<T>::Load(px + o0[k] + e)), Mul(ww1[k], DType<T>::Load(px + o1[k] + e)));
+        }
+        StorePack<float, V>(a + row * inner + t0, out);
+    }
+}
+
+// H + D stage: y[plane, d, h, :] = wD0 * (wH0 * a[d0, h0, :] + wH1 * a[d0, h1, :]) + wD1 * (wH0 * a[d1, h0, :] + ...).
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads) TrilinearHDStageKernel(const float* __restrict__ a, T* __restrict__ y,
+                                                                   Trilinear3dGeom g)
+{
+    const int64_t inner = static_cast<int64_t>(g.wo) * g.chan;
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+    if (t0 >= inner) {
+        return;
+    }
+    const bool small = g.rows <= 0x7fffffffLL;
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
+        int64_t plane; // row = (plane, d, h)
+        int32_t d, h;
+        SplitRow(row, g.ho, g.dout, small, plane, d, h);
+        const Tap td = FwdTap(g.sd, d, g.align, g.di);
+        const Tap th = FwdTap(g.sh, h, g.align, g.hi);
+        float v00[V], v01[V], v10[V], v11[V];
+        LoadPack<float, V>(a + ((plane * g.di + td.i0) * g.hi + th.i0) * inner + t0, v00);
+        LoadPack<float, V>(a + ((plane * g.di + td.i0) * g.hi + th.i1) * inner + t0, v01);
+        LoadPack<float, V>(a + ((plane * g.di + td.i1) * g.hi + th.i0) * inner + t0, v10);
+        LoadPack<float, V>(a + ((plane * g.di + td.i1) * g.hi + th.i1) * inner + t0, v11);
+        float out[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const float lo = Add(Mul(th.w0, v00[v]), Mul(th.w1, v01[v]));
+            const float hi = Add(Mul(th.w0, v10[v]), Mul(th.w1, v11[v]));
+            out[v] = Add(Mul(td.w0, lo), Mul(td.w1, hi));
         }
         StorePack<T, V>(y + row * inner + t0, out);
     }
@@ -227,110 +276,126 @@ __global__ void TrilinearBwdTableKernel(TrilinearBwdTables t, Trilinear3dGeom g)
     }
 }
 
-// KW > 0: the W weight list of every grad_input column has at most KW entries and is kept in registers (zero padded,
-// so the padding adds nothing and is never read from grad_output); KW == 0: read through the table. KH > 0: the H
-// list has at most KH entries and the loop over it is unrolled, so that the loads of a whole (depth) slab of taps
-// are in flight together.
-template <typename T, int KW, int KH>
-__global__ void __launch_bounds__(kThreads) Trilinear3dBwdKernel(const T* __restrict__ go, T* __restrict__ gi,
-                                                                 Trilinear3dGeom g, TrilinearBwdTables t)
+// One separable stage of the backward: the axis of extent nIn shrinks to nOut,
+// out(o, i, j) = sum over k < count[i] of w[i * taps + k] * in(o, start[i] + k, j), j < inner, ascending k. A thread
+// owns V adjacent j of one (o, i).
+template <typename TI, typename TO, int V>
+__global__ void __launch_bounds__(kThreads) TrilinearBwdStageKernel(const TI* __restrict__ in, TO* __restrict__ out,
+                                                                    int64_t rows, int32_t nIn, int32_t nOut,
+                                                                    int64_t inner, const int32_t* __restrict__ start,
+                                                                    const int32_t* __restrict__ count,
+                                                                    const float* __restrict__ w, int32_t taps)
 {
-    const int64_t inner = static_cast<int64_t>(g.wi) * g.chan; // elements of a grad_input row
-    const int64_t rowGo = static_cast<int64_t>(g.wo) * g.chan;
-    const int64_t e0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (e0 >= inner) {
+    const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+    if (j0 >= inner) {
         return;
     }
-    const bool small = g.rows <= 0x7fffffffLL;
-    const int32_t w = static_cast<int32_t>(e0 / g.chan);
-    const int32_t c = static_cast<int32_t>(e0 - static_cast<int64_t>(w) * g.chan);
-    const int32_t ws = __ldg(t.start[2] + w), wc = __ldg(t.count[2] + w);
-    const float* __restrict__ ww = t.w[2] + static_cast<int64_t>(w) * t.taps[2];
-    float wr[KW > 0 ? KW : 1];
-#pragma unroll
-    for (int e = 0; e < KW; ++e) {
-        wr[e] = e < t.taps[2] ? __ldg(ww + e) : 0.0f;
-    }
-    const int64_t colOff = static_cast<int64_t>(ws) * g.chan + c;
+    const bool small = rows <= 0x7fffffffLL;
     const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
-    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
-        int64_t plane; // row = (plane, d, h) of grad_input
-        int32_t d, h;
-        SplitRow(row, g.hi, g.di, small, plane, d, h);
-        const int32_t ds = __ldg(t.start[0] + d), dc = __ldg(t.count[0] + d);
-        const int32_t hs = __ldg(t.start[1] + h), hc = __ldg(t.count[1] + h);
-        const float* __restrict__ wd = t.w[0] + static_cast<int64_t>(d) * t.taps[0];
-        const float* __restrict__ wh = t.w[1] + static_cast<int64_t>(h) * t.taps[1];
-        float accD = 0.0f;
-        for (int32_t a = 0; a < dc; ++a) {
-            float accH = 0.0f;
-            const T* pa = go + ((plane * g.dout + ds + a) * g.ho + hs) * rowGo + colOff;
-            if constexpr (KW > 0 && KH > 0) {
-                float gv[KH][KW];
-#pragma unroll
-                for (int b = 0; b < KH; ++b) {
-#pragma unroll
-                    for (int e = 0; e < KW; ++e) {
-                        gv[b][e] = (b < hc && e < wc) ? DType<T>::Load(pa + b * rowGo + static_cast<int64_t>(e) * g.chan) : 0.0f;
-                    }
-                }
-#pragma unroll
-                for (int b = 0; b < KH; ++b) {
-                    if (b < hc) {
-                        float accW = 0.0f;
-#pragma unroll
-                        for (int e = 0; e < KW; ++e) {
-                            if (e < wc) {
-                                accW = Add(accW, Mul(wr[e], gv[b][e]));
-                            }
-                        }
-                        accH = Add(accH, Mul(__ldg(wh + b), accW));
-                    }
-                }
-            } else {
-                for (int32_t b = 0; b < hc; ++b) {
-                    const T* pr = pa + b * rowGo;
-                    float accW = 0.0f;
-                    if (KW > 0) {
-#pragma unroll
-                        for (int e = 0; e < KW; ++e) {
-                            if (e < wc) {
-                                accW = Add(accW, Mul(wr[e], DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
-                            }
-                        }
-                    } else {
-                        for (int32_t e = 0; e < wc; ++e) {
-                            accW = Add(accW, Mul(__ldg(ww + e), DType<T>::Load(pr + static_cast<int64_t>(e) * g.chan)));
-                        }
-                    }
-                    accH = Add(accH, Mul(__ldg(wh + b), accW));
-                }
-            }
-            accD = Add(accD, Mul(__ldg(wd + a), accH));
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rows; row += rowStep) {
+        int64_t o; // row = (o, i)
+        int32_t i;
+        if (small) {
+            const uint32_t r = static_cast<uint32_t>(row), q = r / static_cast<uint32_t>(nOut);
+            o = q;
+            i = static_cast<int32_t>(r - q * static_cast<uint32_t>(nOut));
+        } else {
+            o = row / nOut;
+            i = static_cast<int32_t>(row - o * nOut);
         }
-        gi[row * inner + e0] = DType<T>::FromF(accD);
+        const int32_t first = __ldg(start + i), n = __ldg(count + i);
+        const float* __restrict__ wi = w + static_cast<int64_t>(i) * taps;
+        const TI* p = in + (o * nIn + first) * inner + j0;
+        float acc[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            acc[v] = 0.0f;
+        }
+        for (int32_t k = 0; k < n; ++k) {
+            float gv[V];
+            LoadPack<TI, V>(p + k * inner, gv);
+            const float wk = __ldg(wi + k);
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                acc[v] = Add(acc[v], Mul(wk, gv[v]));
+            }
+        }
+        StorePack<TO, V>(out + row * inner + j0, acc);
     }
 }
 
+template <typename TI, typename TO>
+void LaunchBwdStage(const TI* in, TO* out, int64_t outer, int32_t nIn, int32_t nOut, int64_t inner, const int32_t* start,
+                    const int32_t* count, const float* w, int32_t taps, cudaStream_t s)
+{
+    // 16 bytes of the wider type per thread where the rows keep that alignment
+    int v = 16 / static_cast<int>(sizeof(TI) > sizeof(TO) ? sizeof(TI) : sizeof(TO));
+    while (v > 1 && (inner % v != 0 || !Aligned(in, v * sizeof(TI)) || !Aligned(out, v * sizeof(TO)))) {
+        v >>= 1;
+    }
+    const int64_t rows = outer * nOut;
+    const RowLaunch rl = RowTiling(rows, CeilDiv(inner, v), kThreads);
+    OPSCV_DISPATCH_VEC(v, V, {
+        if constexpr (V <= 4) {
+            TrilinearBwdStageKernel<TI, TO, V><<<rl.grid, rl.block, 0, s>>>(in, out, rows, nIn, nOut, inner, start, count,
+                                                                          w, taps);
+        }
+    });
+    CountLaunch();
+}
+
 template <typename T, int V, bool CL>
-void LaunchFwd(const T* x, T* y, const Trilinear3dGeom& g, const RowLaunch& rl, cudaStream_t s)
+void LaunchAxis(const T* x, T* y, const Trilinear3dGeom& g, const RowLaunch& rl, cudaStream_t s)
 {
     switch (g.loop) {
-        case 1: Trilinear3dFwdKernel<T, V, CL, 1><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
-        case 2: Trilinear3dFwdKernel<T, V, CL, 2><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
-        case 3: Trilinear3dFwdKernel<T, V, CL, 3><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
-        case 4: Trilinear3dFwdKernel<T, V, CL, 4><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
-        default: Trilinear3dFwdKernel<T, V, CL, 0><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        case 1: Trilinear3dAxisKernel<T, V, CL, 1><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        case 2: Trilinear3dAxisKernel<T, V, CL, 2><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        case 3: Trilinear3dAxisKernel<T, V, CL, 3><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
+        default: Trilinear3dAxisKernel<T, V, CL, 4><<<rl.grid, rl.block, 0, s>>>(x, y, g); break;
     }
 }
 
 } // namespace
 
-cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, Trilinear3dGeom g, cudaStream_t s)
+uint64_t Trilinear3dFwdWorkspace(const Trilinear3dGeom& g, int64_t planes)
+{
+    if (g.loop != 0) {
+        return 0;
+    }
+    return static_cast<uint64_t>(planes) * g.di * g.hi * g.wo * g.chan * sizeof(float);
+}
+
+cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, float* stage, Trilinear3dGeom g, cudaStream_t s)
 {
     const int64_t inner = static_cast<int64_t>(g.wo) * g.chan;
     const int es = DtSize(dt);
     const bool cl = g.chan > 1;
+    if (g.loop == 0) {
+        const int64_t rowsIn = g.rows / (static_cast<int64_t>(g.dout) * g.ho) * g.di * g.hi; // planes * di * hi
+        int v = 4; // 16 bytes of the fp32 stage buffer per thread
+        while (v > 1 && (inner % v != 0 || (cl && g.chan % v != 0) || !Aligned(y, static_cast<size_t>(v) * es) ||
+                         !Aligned(stage, static_cast<size_t>(v) * sizeof(float)))) {
+            v >>= 1;
+        }
+        const RowLaunch rw = RowTiling(rowsIn, CeilDiv(inner, v), kThreads);
+        const RowLaunch rh = RowTiling(g.rows, CeilDiv(inner, v), kThreads);
+        OPSCV_DISPATCH_DT(dt, T, {
+            const T* px = static_cast<const T*>(x);
+            T* py = static_cast<T*>(y);
+            OPSCV_DISPATCH_VEC(v, V, {
+                if constexpr (V <= 4) {
+                    if (cl) {
+                        TrilinearWStageKernel<T, V, true><<<rw.grid, rw.block, 0, s>>>(px, stage, g, rowsIn);
+                    } else {
+                        TrilinearWStageKernel<T, V, false><<<rw.grid, rw.block, 0, s>>>(px, stage, g, rowsIn);
+                    }
+                    TrilinearHDStageKernel<T, V><<<rh.grid, rh.block, 0, s>>>(stage, py, g);
+                }
+            });
+        });
+        CountLaunch(2);
+        return cudaGetLastError();
+    }
     // pack width: at most 16 bytes of outputs; channels-last packs stay inside one pixel. The taps are read one
     // element at a time, so only the output needs the alignment.
     int v = 16 / es;
@@ -344,9 +409,9 @@ cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, Trilinear3dGeom g, cud
         OPSCV_DISPATCH_VEC(v, V, {
             if constexpr (V * sizeof(T) <= 16) {
                 if (cl) {
-                    LaunchFwd<T, V, true>(px, py, g, rl, s);
+                    LaunchAxis<T, V, true>(px, py, g, rl, s);
                 } else {
-                    LaunchFwd<T, V, false>(px, py, g, rl, s);
+                    LaunchAxis<T, V, false>(px, py, g, rl, s);
                 }
             }
         });
@@ -364,24 +429,31 @@ cudaError_t BuildTrilinearBwdTables(TrilinearBwdTables t, Trilinear3dGeom g, cud
     return cudaGetLastError();
 }
 
-cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, Trilinear3dGeom g, TrilinearBwdTables t, cudaStream_t s)
+uint64_t Trilinear3dBwdWorkspace(const Trilinear3dGeom& g, int64_t planes)
 {
-    const int64_t inner = static_cast<int64_t>(g.wi) * g.chan;
-    const RowLaunch rl = RowTiling(g.rows, inner, kThreads);
+    // after the W stage: planes * dout * ho * wi; after the H stage: planes * dout * hi * wi
+    const uint64_t t1 = static_cast<uint64_t>(planes) * g.dout * g.ho * g.wi * g.chan * sizeof(float);
+    const uint64_t t2 = static_cast<uint64_t>(planes) * g.dout * g.hi * g.wi * g.chan * sizeof(float);
+    return ((t1 + 255) & ~static_cast<uint64_t>(255)) + t2;
+}
+
+cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, float* stage, Trilinear3dGeom g, TrilinearBwdTables t,
+                           cudaStream_t s)
+{
+    const int64_t planes = g.rows / (static_cast<int64_t>(g.di) * g.hi);
+    const uint64_t t1Bytes = static_cast<uint64_t>(planes) * g.dout * g.ho * g.wi * g.chan * sizeof(float);
+    float* t1 = stage;
+    float* t2 = reinterpret_cast<float*>(reinterpret_cast<char*>(stage) + ((t1Bytes + 255) & ~static_cast<uint64_t>(255)));
     OPSCV_DISPATCH_DT(dt, T, {
-        const T* pg = static_cast<const T*>(go);
-        T* pi = static_cast<T*>(gi);
-        if (t.taps[2] <= 4 && t.taps[1] <= 4) {
-            Trilinear3dBwdKernel<T, 4, 4><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
-        } else if (t.taps[2] <= 4) {
-            Trilinear3dBwdKernel<T, 4, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
-        } else if (t.taps[2] <= 8) {
-            Trilinear3dBwdKernel<T, 8, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
-        } else {
-            Trilinear3dBwdKernel<T, 0, 0><<<rl.grid, rl.block, 0, s>>>(pg, pi, g, t);
-        }
+        // W: (planes * dout * ho) x wo x chan -> wi;  H: (planes * dout) x ho x (wi * chan) -> hi;  D: planes x dout x
+        // (hi * wi * chan) -> di
+        LaunchBwdStage<T, float>(static_cast<const T*>(go), t1, planes * g.dout * g.ho, g.wo, g.wi, g.chan, t.start[2],
+                                 t.count[2], t.w[2], t.taps[2], s);
+        LaunchBwdStage<float, float>(t1, t2, planes * g.dout, g.ho, g.hi, static_cast<int64_t>(g.wi) * g.chan,
+                                     t.start[1], t.count[1], t.w[1], t.taps[1], s);
+        LaunchBwdStage<float, T>(t2, static_cast<T*>(gi), planes, g.dout, g.di,
+                                 static_cast<int64_t>(g.hi) * g.wi * g.chan, t.start[0], t.count[0], t.w[0], t.taps[0], s);
     });
-    CountLaunch();
     return cudaGetLastError();
 }
 
