@@ -45,9 +45,8 @@ __device__ __forceinline__ Tap FwdTap(float scale, int32_t dst, int32_t align, i
         real = real < 0.0f ? 0.0f : real;
     }
     Tap t;
-    const long long i = static_cast<long long>(real);
-    const long long last = in - 1;
-    t.i0 = static_cast<int32_t>(i < last ? i : last);
+    const int32_t i = __float2int_rz(real); // real >= 0; saturates at INT32_MAX, above every valid index
+    t.i0 = i < in - 1 ? i : in - 1;
     t.i1 = t.i0 + 1 < in ? t.i0 + 1 : in - 1;
     t.w1 = fminf(fmaxf(Sub(real, static_cast<float>(t.i0)), 0.0f), 1.0f);
     t.w0 = Sub(1.0f, t.w1);
@@ -180,36 +179,44 @@ __global__ void __launch_bounds__(kThreads) TrilinearWStageKernel(const T* __res
 }
 
 // H + D stage: y[plane, d, h, :] = wD0 * (wH0 * a[d0, h0, :] + wH1 * a[d0, h1, :]) + wD1 * (wH0 * a[d1, h0, :] + ...).
+// grid.y walks the (plane, d) pairs, whose D taps are found once; the thread rows of a block walk h.
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads) TrilinearHDStageKernel(const float* __restrict__ a, T* __restrict__ y,
-                                                                   Trilinear3dGeom g)
+                                                                   Trilinear3dGeom g, int64_t planeDepths)
 {
     const int64_t inner = static_cast<int64_t>(g.wo) * g.chan;
     const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
     if (t0 >= inner) {
         return;
     }
-    const bool small = g.rows <= 0x7fffffffLL;
-    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
-    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < g.rows; row += rowStep) {
-        int64_t plane; // row = (plane, d, h)
-        int32_t d, h;
-        SplitRow(row, g.ho, g.dout, small, plane, d, h);
+    constexpr int C = V / 4 > 0 ? V / 4 : 1; // 16-byte chunks per row
+    constexpr int L = V < 4 ? V : 4;
+    for (int64_t pd = blockIdx.y; pd < planeDepths; pd += gridDim.y) {
+        const int64_t plane = pd / g.dout;
+        const int32_t d = static_cast<int32_t>(pd - plane * g.dout);
         const Tap td = FwdTap(g.sd, d, g.align, g.di);
-        const Tap th = FwdTap(g.sh, h, g.align, g.hi);
-        float v00[V], v01[V], v10[V], v11[V];
-        LoadPack<float, V>(a + ((plane * g.di + td.i0) * g.hi + th.i0) * inner + t0, v00);
-        LoadPack<float, V>(a + ((plane * g.di + td.i0) * g.hi + th.i1) * inner + t0, v01);
-        LoadPack<float, V>(a + ((plane * g.di + td.i1) * g.hi + th.i0) * inner + t0, v10);
-        LoadPack<float, V>(a + ((plane * g.di + td.i1) * g.hi + th.i1) * inner + t0, v11);
-        float out[V];
+        const float* a0 = a + (plane * g.di + td.i0) * g.hi * inner + t0;
+        const float* a1 = a + (plane * g.di + td.i1) * g.hi * inner + t0;
+        T* py = y + pd * g.ho * inner + t0;
+        for (int32_t h = threadIdx.y; h < g.ho; h += blockDim.y) {
+            const Tap th = FwdTap(g.sh, h, g.align, g.hi);
+            float out[V];
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            const float lo = Add(Mul(th.w0, v00[v]), Mul(th.w1, v01[v]));
-            const float hi = Add(Mul(th.w0, v10[v]), Mul(th.w1, v11[v]));
-            out[v] = Add(Mul(td.w0, lo), Mul(td.w1, hi));
+            for (int c = 0; c < C; ++c) {
+                float v00[L], v01[L], v10[L], v11[L];
+                LoadPack<float, L>(a0 + th.i0 * inner + c * L, v00);
+                LoadPack<float, L>(a0 + th.i1 * inner + c * L, v01);
+                LoadPack<float, L>(a1 + th.i0 * inner + c * L, v10);
+                LoadPack<float, L>(a1 + th.i1 * inner + c * L, v11);
+#pragma unroll
+                for (int v = 0; v < L; ++v) {
+                    const float lo = Add(Mul(th.w0, v00[v]), Mul(th.w1, v01[v]));
+                    const float hi = Add(Mul(th.w0, v10[v]), Mul(th.w1, v11[v]));
+                    out[c * L + v] = Add(Mul(td.w0, lo), Mul(td.w1, hi));
+                }
+            }
+            StorePack<T, V>(py + h * inner, out);
         }
-        StorePack<T, V>(y + row * inner + t0, out);
     }
 }
 
@@ -324,6 +331,52 @@ __global__ void __launch_bounds__(kThreads) TrilinearBwdStageKernel(const TI* __
     }
 }
 
+// The W stage of the backward for narrow inner extents (NCDHW: one element per column): a thread owns one
+// (column, channel) of the shrunken row for all the rows it visits and keeps that column's weights in registers
+// (KW > 0: at most KW of them, zero padded; KW == 0: read through the table).
+template <typename T, int KW>
+__global__ void __launch_bounds__(kThreads) TrilinearBwdWStageKernel(const T* __restrict__ go, float* __restrict__ out,
+                                                                     int64_t rows, int32_t wo, int32_t wi, int32_t chan,
+                                                                     const int32_t* __restrict__ start,
+                                                                     const int32_t* __restrict__ count,
+                                                                     const float* __restrict__ w, int32_t taps)
+{
+    const int64_t inner = static_cast<int64_t>(wi) * chan;
+    const int64_t rowGo = static_cast<int64_t>(wo) * chan;
+    const int64_t e0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e0 >= inner) {
+        return;
+    }
+    const int32_t col = static_cast<int32_t>(e0 / chan);
+    const int32_t c = static_cast<int32_t>(e0 - static_cast<int64_t>(col) * chan);
+    const int32_t first = __ldg(start + col), n = __ldg(count + col);
+    const float* __restrict__ wc = w + static_cast<int64_t>(col) * taps;
+    float wr[KW > 0 ? KW : 1];
+#pragma unroll
+    for (int e = 0; e < KW; ++e) {
+        wr[e] = e < taps ? __ldg(wc + e) : 0.0f;
+    }
+    const int64_t colOff = static_cast<int64_t>(first) * chan + c;
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rows; row += rowStep) {
+        const T* pr = go + row * rowGo + colOff;
+        float acc = 0.0f;
+        if (KW > 0) {
+#pragma unroll
+            for (int e = 0; e < KW; ++e) {
+                if (e < n) {
+                    acc = Add(acc, Mul(wr[e], DType<T>::Load(pr + static_cast<int64_t>(e) * chan)));
+                }
+            }
+        } else {
+            for (int32_t e = 0; e < n; ++e) {
+                acc = Add(acc, Mul(__ldg(wc + e), DType<T>::Load(pr + static_cast<int64_t>(e) * chan)));
+            }
+        }
+        out[row * inner + e0] = acc;
+    }
+}
+
 template <typename TI, typename TO>
 void LaunchBwdStage(const TI* in, TO* out, int64_t outer, int32_t nIn, int32_t nOut, int64_t inner, const int32_t* start,
                     const int32_t* count, const float* w, int32_t taps, cudaStream_t s)
@@ -372,13 +425,24 @@ cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, float* stage, Trilinea
     const bool cl = g.chan > 1;
     if (g.loop == 0) {
         const int64_t rowsIn = g.rows / (static_cast<int64_t>(g.dout) * g.ho) * g.di * g.hi; // planes * di * hi
-        int v = 4; // 16 bytes of the fp32 stage buffer per thread
-        while (v > 1 && (inner % v != 0 || (cl && g.chan % v != 0) || !Aligned(y, static_cast<size_t>(v) * es) ||
+        int v = 4; // W stage: 16 bytes of the fp32 stage buffer per thread
+        while (v > 1 && (inner % v != 0 || (cl && g.chan % v != 0) ||
                          !Aligned(stage, static_cast<size_t>(v) * sizeof(float)))) {
             v >>= 1;
         }
+        int vh = 16 / es; // H + D stage: 16 bytes of outputs per thread, read as 16-byte chunks of the stage buffer
+        while (vh > 1 && (inner % vh != 0 || !Aligned(y, static_cast<size_t>(vh) * es) ||
+                          !Aligned(stage, static_cast<size_t>(vh < 4 ? vh : 4) * sizeof(float)))) {
+            vh >>= 1;
+        }
         const RowLaunch rw = RowTiling(rowsIn, CeilDiv(inner, v), kThreads);
-        const RowLaunch rh = RowTiling(g.rows, CeilDiv(inner, v), kThreads);
+        const int64_t planeDepths = g.rows / g.ho;
+        RowLaunch rh = RowTiling(g.ho, CeilDiv(inner, vh), kThreads);
+        {
+            int64_t cap = static_cast<int64_t>(NumSMs()) * 16 / rh.grid.x;
+            cap = cap < 1 ? 1 : cap;
+            rh.grid.y = static_cast<unsigned>(std::min<int64_t>(std::min<int64_t>(planeDepths, cap), 65535));
+        }
         OPSCV_DISPATCH_DT(dt, T, {
             const T* px = static_cast<const T*>(x);
             T* py = static_cast<T*>(y);
@@ -389,7 +453,11 @@ cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, float* stage, Trilinea
                     } else {
                         TrilinearWStageKernel<T, V, false><<<rw.grid, rw.block, 0, s>>>(px, stage, g, rowsIn);
                     }
-                    TrilinearHDStageKernel<T, V><<<rh.grid, rh.block, 0, s>>>(stage, py, g);
+                }
+            });
+            OPSCV_DISPATCH_VEC(vh, V, {
+                if constexpr (V * sizeof(T) <= 16) {
+                    TrilinearHDStageKernel<T, V><<<rh.grid, rh.block, 0, s>>>(stage, py, g, planeDepths);
                 }
             });
         });
@@ -447,8 +515,28 @@ cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, float* stage, Trilin
     OPSCV_DISPATCH_DT(dt, T, {
         // W: (planes * dout * ho) x wo x chan -> wi;  H: (planes * dout) x ho x (wi * chan) -> hi;  D: planes x dout x
         // (hi * wi * chan) -> di
-        LaunchBwdStage<T, float>(static_cast<const T*>(go), t1, planes * g.dout * g.ho, g.wo, g.wi, g.chan, t.start[2],
-                                 t.count[2], t.w[2], t.taps[2], s);
+        if (g.chan <= 4) {
+            const int64_t rowsW = planes * g.dout * g.ho;
+            const RowLaunch rl = RowTiling(rowsW, static_cast<int64_t>(g.wi) * g.chan, kThreads);
+            const T* pg = static_cast<const T*>(go);
+            if (t.taps[2] <= 4) {
+                TrilinearBwdWStageKernel<T, 4><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
+                                                                           t.count[2], t.w[2], t.taps[2]);
+            } else if (t.taps[2] <= 6) {
+                TrilinearBwdWStageKernel<T, 6><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
+                                                                           t.count[2], t.w[2], t.taps[2]);
+            } else if (t.taps[2] <= 10) {
+                TrilinearBwdWStageKernel<T, 10><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
+                                                                            t.count[2], t.w[2], t.taps[2]);
+            } else {
+                TrilinearBwdWStageKernel<T, 0><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
+                                                                           t.count[2], t.w[2], t.taps[2]);
+            }
+            CountLaunch();
+        } else {
+            LaunchBwdStage<T, float>(static_cast<const T*>(go), t1, planes * g.dout * g.ho, g.wo, g.wi, g.chan,
+                                     t.start[2], t.count[2], t.w[2], t.taps[2], s);
+        }
         LaunchBwdStage<float, float>(t1, t2, planes * g.dout, g.ho, g.hi, static_cast<int64_t>(g.wi) * g.chan,
                                      t.start[1], t.count[1], t.w[1], t.taps[1], s);
         LaunchBwdStage<float, T>(t2, static_cast<T*>(gi), planes, g.dout, g.di,
