@@ -179,44 +179,80 @@ __global__ void __launch_bounds__(kThreads) TrilinearWStageKernel(const T* __res
 }
 
 // H + D stage: y[plane, d, h, :] = wD0 * (wH0 * a[d0, h0, :] + wH1 * a[d0, h1, :]) + wD1 * (wH0 * a[d1, h0, :] + ...).
-// grid.y walks the (plane, d) pairs, whose D taps are found once; the thread rows of a block walk h.
+// A thread owns V adjacent elements of one output row position (h, w) of one plane and walks down a range of output
+// depths. Its H taps never change, and the two H-blended rows (input depths d0 and d1) stay in registers: when the
+// next output depth keeps its input depths they are reused, when it moves on by one the second becomes the first
+// and one new row is blended. The sums are the same expressions as in the one-pass form, so the bits are the same.
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads) TrilinearHDStageKernel(const float* __restrict__ a, T* __restrict__ y,
-                                                                   Trilinear3dGeom g, int64_t planeDepths)
+                                                                   Trilinear3dGeom g, int32_t packs, int32_t depthChunks,
+                                                                   int64_t planeChunks)
 {
     const int64_t inner = static_cast<int64_t>(g.wo) * g.chan;
-    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
-    if (t0 >= inner) {
+    const int64_t item = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; // (h, pack)
+    if (item >= static_cast<int64_t>(g.ho) * packs) {
         return;
     }
+    const int32_t h = static_cast<int32_t>(item / packs);
+    const int64_t t0 = (item - static_cast<int64_t>(h) * packs) * V;
+    const Tap th = FwdTap(g.sh, h, g.align, g.hi);
+    const int32_t perChunk = (g.dout + depthChunks - 1) / depthChunks;
+    for (int64_t pc = blockIdx.y; pc < planeChunks; pc += gridDim.y) {
+    const int64_t plane = pc / depthChunks;
+    const int32_t chunk = static_cast<int32_t>(pc - plane * depthChunks);
+    const int32_t dBegin = chunk * perChunk;
+    const int32_t dEnd = dBegin + perChunk < g.dout ? dBegin + perChunk : g.dout;
     constexpr int C = V / 4 > 0 ? V / 4 : 1; // 16-byte chunks per row
     constexpr int L = V < 4 ? V : 4;
-    for (int64_t pd = blockIdx.y; pd < planeDepths; pd += gridDim.y) {
-        const int64_t plane = pd / g.dout;
-        const int32_t d = static_cast<int32_t>(pd - plane * g.dout);
-        const Tap td = FwdTap(g.sd, d, g.align, g.di);
-        const float* a0 = a + (plane * g.di + td.i0) * g.hi * inner + t0;
-        const float* a1 = a + (plane * g.di + td.i1) * g.hi * inner + t0;
-        T* py = y + pd * g.ho * inner + t0;
-        for (int32_t h = threadIdx.y; h < g.ho; h += blockDim.y) {
-            const Tap th = FwdTap(g.sh, h, g.align, g.hi);
-            float out[V];
+    const float* pa = a + plane * g.di * g.hi * inner + t0;
+    const int64_t off0 = th.i0 * inner, off1 = th.i1 * inner, depthStride = g.hi * inner;
+    auto blend = [&](int32_t j, float (&row)[V]) {
+        const float* p = pa + j * depthStride;
 #pragma unroll
-            for (int c = 0; c < C; ++c) {
-                float v00[L], v01[L], v10[L], v11[L];
-                LoadPack<float, L>(a0 + th.i0 * inner + c * L, v00);
-                LoadPack<float, L>(a0 + th.i1 * inner + c * L, v01);
-                LoadPack<float, L>(a1 + th.i0 * inner + c * L, v10);
-                LoadPack<float, L>(a1 + th.i1 * inner + c * L, v11);
+        for (int c = 0; c < C; ++c) {
+            float v0[L], v1[L];
+            LoadPack<float, L>(p + off0 + c * L, v0);
+            LoadPack<float, L>(p + off1 + c * L, v1);
 #pragma unroll
-                for (int v = 0; v < L; ++v) {
-                    const float lo = Add(Mul(th.w0, v00[v]), Mul(th.w1, v01[v]));
-                    const float hi = Add(Mul(th.w0, v10[v]), Mul(th.w1, v11[v]));
-                    out[c * L + v] = Add(Mul(td.w0, lo), Mul(td.w1, hi));
-                }
+            for (int v = 0; v < L; ++v) {
+                row[c * L + v] = Add(Mul(th.w0, v0[v]), Mul(th.w1, v1[v]));
             }
-            StorePack<T, V>(py + h * inner, out);
         }
+    };
+    float lo[V], hi[V];
+    int32_t cur0 = -1, cur1 = -1;
+    T* py = y + ((plane * g.dout + dBegin) * g.ho + h) * inner + t0;
+    for (int32_t d = dBegin; d < dEnd; ++d, py += g.ho * inner) {
+        const Tap td = FwdTap(g.sd, d, g.align, g.di);
+        if (td.i0 != cur0) {
+            if (td.i0 == cur1) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    lo[v] = hi[v];
+                }
+            } else {
+                blend(td.i0, lo);
+            }
+            cur0 = td.i0;
+        }
+        if (td.i1 != cur1) {
+            if (td.i1 == cur0) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    hi[v] = lo[v];
+                }
+            } else {
+                blend(td.i1, hi);
+            }
+            cur1 = td.i1;
+        }
+        float out[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            out[v] = Add(Mul(td.w0, lo[v]), Mul(td.w1, hi[v]));
+        }
+        StorePack<T, V>(py, out);
+    }
     }
 }
 
@@ -333,14 +369,16 @@ __global__ void __launch_bounds__(kThreads) TrilinearBwdStageKernel(const TI* __
 
 // The W stage of the backward for narrow inner extents (NCDHW: one element per column): a thread owns one
 // (column, channel) of the shrunken row for all the rows it visits and keeps that column's weights in registers
-// (KW > 0: at most KW of them, zero padded; KW == 0: read through the table).
-template <typename T, int KW>
+// (KW > 0: at most KW of them, zero padded; KW == 0: read through the table). UNIT: chan == 1, so the taps of a
+// column sit at constant offsets from its first one.
+template <typename T, int KW, bool UNIT>
 __global__ void __launch_bounds__(kThreads) TrilinearBwdWStageKernel(const T* __restrict__ go, float* __restrict__ out,
-                                                                     int64_t rows, int32_t wo, int32_t wi, int32_t chan,
+                                                                     int64_t rows, int32_t wo, int32_t wi, int32_t chanArg,
                                                                      const int32_t* __restrict__ start,
                                                                      const int32_t* __restrict__ count,
                                                                      const float* __restrict__ w, int32_t taps)
 {
+    const int32_t chan = UNIT ? 1 : chanArg;
     const int64_t inner = static_cast<int64_t>(wi) * chan;
     const int64_t rowGo = static_cast<int64_t>(wo) * chan;
     const int64_t e0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -356,16 +394,18 @@ __global__ void __launch_bounds__(kThreads) TrilinearBwdWStageKernel(const T* __
     for (int e = 0; e < KW; ++e) {
         wr[e] = e < taps ? __ldg(wc + e) : 0.0f;
     }
-    const int64_t colOff = static_cast<int64_t>(first) * chan + c;
     const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
-    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rows; row += rowStep) {
-        const T* pr = go + row * rowGo + colOff;
+    const int64_t row0 = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y;
+    const T* pr = go + row0 * rowGo + static_cast<int64_t>(first) * chan + c;
+    float* po = out + row0 * inner + e0;
+    const int64_t stepIn = rowStep * rowGo, stepOut = rowStep * inner;
+    for (int64_t row = row0; row < rows; row += rowStep, pr += stepIn, po += stepOut) {
         float acc = 0.0f;
         if (KW > 0) {
 #pragma unroll
             for (int e = 0; e < KW; ++e) {
                 if (e < n) {
-                    acc = Add(acc, Mul(wr[e], DType<T>::Load(pr + static_cast<int64_t>(e) * chan)));
+                    acc = Add(acc, Mul(wr[e], DType<T>::Load(pr + (UNIT ? e : e * chan))));
                 }
             }
         } else {
@@ -373,7 +413,20 @@ __global__ void __launch_bounds__(kThreads) TrilinearBwdWStageKernel(const T* __
                 acc = Add(acc, Mul(__ldg(wc + e), DType<T>::Load(pr + static_cast<int64_t>(e) * chan)));
             }
         }
-        out[row * inner + e0] = acc;
+        *po = acc;
+    }
+}
+
+template <typename T, int KW>
+void LaunchBwdWStage(const T* go, float* out, int64_t rows, const Trilinear3dGeom& g, const TrilinearBwdTables& t,
+                     const RowLaunch& rl, cudaStream_t s)
+{
+    if (g.chan == 1) {
+        TrilinearBwdWStageKernel<T, KW, true><<<rl.grid, rl.block, 0, s>>>(go, out, rows, g.wo, g.wi, 1, t.start[2],
+                                                                          t.count[2], t.w[2], t.taps[2]);
+    } else {
+        TrilinearBwdWStageKernel<T, KW, false><<<rl.grid, rl.block, 0, s>>>(go, out, rows, g.wo, g.wi, g.chan, t.start[2],
+                                                                           t.count[2], t.w[2], t.taps[2]);
     }
 }
 
@@ -436,13 +489,13 @@ cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, float* stage, Trilinea
             vh >>= 1;
         }
         const RowLaunch rw = RowTiling(rowsIn, CeilDiv(inner, v), kThreads);
-        const int64_t planeDepths = g.rows / g.ho;
-        RowLaunch rh = RowTiling(g.ho, CeilDiv(inner, vh), kThreads);
-        {
-            int64_t cap = static_cast<int64_t>(NumSMs()) * 16 / rh.grid.x;
-            cap = cap < 1 ? 1 : cap;
-            rh.grid.y = static_cast<unsigned>(std::min<int64_t>(std::min<int64_t>(planeDepths, cap), 65535));
-        }
+        const int64_t planes = g.rows / (static_cast<int64_t>(g.dout) * g.ho);
+        const int32_t packs = static_cast<int32_t>(inner / vh);
+        const int64_t items = static_cast<int64_t>(g.ho) * packs;
+        // enough depth chunks to fill the machine about twice over, each at least eight output depths long
+        int64_t chunks = CeilDiv(static_cast<int64_t>(NumSMs()) * 4096, std::max<int64_t>(planes * items, 1));
+        chunks = std::max<int64_t>(1, std::min<int64_t>(chunks, std::max<int32_t>(g.dout / 8, 1)));
+        const dim3 gridH(static_cast<unsigned>(CeilDiv(items, kThreads)), static_cast<unsigned>(std::min<int64_t>(planes * chunks, 65535)), 1);
         OPSCV_DISPATCH_DT(dt, T, {
             const T* px = static_cast<const T*>(x);
             T* py = static_cast<T*>(y);
@@ -457,7 +510,8 @@ cudaError_t Trilinear3dFwd(Dt dt, const void* x, void* y, float* stage, Trilinea
             });
             OPSCV_DISPATCH_VEC(vh, V, {
                 if constexpr (V * sizeof(T) <= 16) {
-                    TrilinearHDStageKernel<T, V><<<rh.grid, rh.block, 0, s>>>(stage, py, g, planeDepths);
+                    TrilinearHDStageKernel<T, V><<<gridH, kThreads, 0, s>>>(stage, py, g, packs, static_cast<int32_t>(chunks),
+                                                                             planes * chunks);
                 }
             });
         });
@@ -520,17 +574,13 @@ cudaError_t Trilinear3dBwd(Dt dt, const void* go, void* gi, float* stage, Trilin
             const RowLaunch rl = RowTiling(rowsW, static_cast<int64_t>(g.wi) * g.chan, kThreads);
             const T* pg = static_cast<const T*>(go);
             if (t.taps[2] <= 4) {
-                TrilinearBwdWStageKernel<T, 4><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
-                                                                           t.count[2], t.w[2], t.taps[2]);
+                LaunchBwdWStage<T, 4>(pg, t1, rowsW, g, t, rl, s);
             } else if (t.taps[2] <= 6) {
-                TrilinearBwdWStageKernel<T, 6><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
-                                                                           t.count[2], t.w[2], t.taps[2]);
+                LaunchBwdWStage<T, 6>(pg, t1, rowsW, g, t, rl, s);
             } else if (t.taps[2] <= 10) {
-                TrilinearBwdWStageKernel<T, 10><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
-                                                                            t.count[2], t.w[2], t.taps[2]);
+                LaunchBwdWStage<T, 10>(pg, t1, rowsW, g, t, rl, s);
             } else {
-                TrilinearBwdWStageKernel<T, 0><<<rl.grid, rl.block, 0, s>>>(pg, t1, rowsW, g.wo, g.wi, g.chan, t.start[2],
-                                                                           t.count[2], t.w[2], t.taps[2]);
+                LaunchBwdWStage<T, 0>(pg, t1, rowsW, g, t, rl, s);
             }
             CountLaunch();
         } else {
