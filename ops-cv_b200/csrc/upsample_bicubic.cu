@@ -16,6 +16,7 @@
 // and fp32 results carry the bits of that kernel run serially. The column side of the walk is the same for every
 // row, so each thread evaluates it once into a shared-memory list.
 #include <algorithm>
+#include <vector>
 
 #include "launch_util.cuh"
 
@@ -215,6 +216,124 @@ __global__ void __launch_bounds__(kThreads) Bicubic2dFwdKernel(const T* __restri
                 out[v] = Add(Add(Add(Mul(rs[v][0], ch.x), Mul(rs[v][1], ch.y)), Mul(rs[v][2], ch.z)), Mul(rs[v][3], ch.w));
             }
             StorePack<T, V>(py, out);
+        }
+    }
+}
+
+// General schedule, NCHW, tiled through shared memory. A block takes a (plane, band of output rows) item: it loads
+// the source rows the band touches once (converted to fp32), forms every horizontal sum of those rows once,
+// a[source row][output column], and then combines four rows of `a` per output row with 16-byte shared-memory loads.
+// The sums are the expressions of the kernel above in the same order, so the bits are the same; what changes is
+// that a tap is loaded and converted once per block instead of once per output column that uses it, and that the
+// column coefficients live in registers for all the rows of the tile.
+struct BicubicTile {
+    int32_t bandRows; // output rows per item
+    int32_t bands;
+    int32_t maxSrc;   // most source rows any band touches
+    int32_t tw;       // threads along a row in the horizontal pass (power of two)
+    int32_t pw;       // threads along a row in the vertical pass (power of two)
+};
+
+__host__ __device__ __forceinline__ int32_t FwdTop(int32_t H, float scaleH, int32_t align, int32_t hin, float (*ch)[4])
+{
+#ifdef __CUDA_ARCH__
+    const float oh = align ? Mul(static_cast<float>(H), scaleH) : Sub(Mul(Add(static_cast<float>(H), 0.5f), scaleH), 0.5f);
+    const float fh = floorf(oh);
+    if (ch != nullptr) {
+        FwdCoeff(Sub(oh, fh), *ch);
+    }
+#else
+    (void)ch;
+    float oh;
+    if (align) {
+        oh = static_cast<float>(H) * scaleH;
+    } else {
+        const float t = (static_cast<float>(H) + 0.5f) * scaleH;
+        oh = t - 0.5f;
+    }
+    const float fh = floorf(oh);
+#endif
+    // tops outside [-2, hin + 1] clamp every tap to the same row as the bound does
+    return static_cast<int32_t>(fminf(fmaxf(fh, -2.0f), static_cast<float>(hin) + 1.0f));
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads) Bicubic2dFwdTileKernel(const T* __restrict__ x, T* __restrict__ y, BicubicGeom g,
+                                                                   BicubicTile tile, int64_t items)
+{
+    extern __shared__ __align__(16) float sTile[];
+    float* sCh = sTile;                                           // [bandRows][4], read as float4
+    float* sA = sCh + 4 * tile.bandRows;                          // [maxSrc][wout], 16-byte aligned rows when V >= 4
+    float* sX = sA + static_cast<size_t>(tile.maxSrc) * g.wout;   // [maxSrc][win]
+    int32_t* sTop = reinterpret_cast<int32_t*>(sX + static_cast<size_t>(tile.maxSrc) * g.win); // [bandRows]
+    const int32_t tid = threadIdx.x;
+    const int32_t tx = tid & (tile.tw - 1), ty = tid / tile.tw, tyN = kThreads / tile.tw;
+    const int32_t px_ = tid & (tile.pw - 1), py_ = tid / tile.pw, pyN = kThreads / tile.pw;
+    const int32_t packs = g.wout / V;
+    const int64_t planeIn = static_cast<int64_t>(g.hin) * g.win;
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const int64_t plane = item / tile.bands;
+        const int32_t band = static_cast<int32_t>(item - plane * tile.bands);
+        const int32_t h0 = band * tile.bandRows;
+        const int32_t nOut = min(tile.bandRows, g.hout - h0);
+        __syncthreads(); // the previous item's tiles are no longer read
+        for (int32_t r = tid; r < nOut; r += kThreads) {
+            float ch[4];
+            sTop[r] = FwdTop(h0 + r, g.scaleH, g.align, g.hin, &ch);
+            *reinterpret_cast<float4*>(sCh + 4 * r) = make_float4(ch[0], ch[1], ch[2], ch[3]);
+        }
+        __syncthreads();
+        const int32_t srcLo = ClampIdx32(sTop[0] - 1, g.hin - 1);
+        const int32_t srcHi = ClampIdx32(sTop[nOut - 1] + 2, g.hin - 1);
+        const int32_t nSrc = min(srcHi - srcLo + 1, tile.maxSrc);
+        const T* px = x + plane * planeIn + static_cast<int64_t>(srcLo) * g.win;
+        for (int32_t i = tid; i < nSrc * g.win; i += kThreads) {
+            sX[i] = DType<T>::Load(px + i);
+        }
+        __syncthreads();
+        // horizontal sums: a thread keeps the taps and coefficients of its column for all the rows of the tile
+        for (int32_t w = tx; w < g.wout; w += tile.tw) {
+            const float ow = g.align ? Mul(static_cast<float>(w), g.scaleW)
+                                     : Sub(Mul(Add(static_cast<float>(w), 0.5f), g.scaleW), 0.5f);
+            const float fw = floorf(ow);
+            const long long left = static_cast<long long>(fw);
+            float cw[4];
+            FwdCoeff(Sub(ow, fw), cw);
+            const int32_t o0 = ClampIdx(left - 1, g.win - 1), o1 = ClampIdx(left, g.win - 1),
+                          o2 = ClampIdx(left + 1, g.win - 1), o3 = ClampIdx(left + 2, g.win - 1);
+            for (int32_t r = ty; r < nSrc; r += tyN) {
+                const float* row = sX + r * g.win;
+                sA[r * g.wout + w] = Add(Add(Add(Mul(row[o0], cw[0]), Mul(row[o1], cw[1])), Mul(row[o2], cw[2])), Mul(row[o3], cw[3]));
+            }
+        }
+        __syncthreads();
+        // vertical combination, V adjacent outputs per thread
+        T* py = y + (plane * g.hout + h0) * static_cast<int64_t>(g.wout);
+        constexpr int C = V / 4 > 0 ? V / 4 : 1;
+        constexpr int L = V < 4 ? V : 4;
+        for (int32_t p = px_; p < packs; p += tile.pw) {
+            for (int32_t r = py_; r < nOut; r += pyN) {
+                const int32_t top = sTop[r];
+                const float4 ch = *reinterpret_cast<const float4*>(sCh + 4 * r);
+                const float* a0 = sA + (ClampIdx32(top - 1, g.hin - 1) - srcLo) * g.wout + p * V;
+                const float* a1 = sA + (ClampIdx32(top, g.hin - 1) - srcLo) * g.wout + p * V;
+                const float* a2 = sA + (ClampIdx32(top + 1, g.hin - 1) - srcLo) * g.wout + p * V;
+                const float* a3 = sA + (ClampIdx32(top + 2, g.hin - 1) - srcLo) * g.wout + p * V;
+                float out[V];
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    float r0[L], r1[L], r2[L], r3[L];
+                    LoadPack<float, L>(a0 + c * L, r0);
+                    LoadPack<float, L>(a1 + c * L, r1);
+                    LoadPack<float, L>(a2 + c * L, r2);
+                    LoadPack<float, L>(a3 + c * L, r3);
+#pragma unroll
+                    for (int v = 0; v < L; ++v) {
+                        out[c * L + v] = Add(Add(Add(Mul(r0[v], ch.x), Mul(r1[v], ch.y)), Mul(r2[v], ch.z)), Mul(r3[v], ch.w));
+                    }
+                }
+                StorePack<T, V>(py + static_cast<int64_t>(r) * g.wout + p * V, out);
+            }
         }
     }
 }
@@ -618,6 +737,76 @@ cudaError_t Bicubic2dFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, f
         });
         CountLaunch();
         return cudaGetLastError();
+    }
+    if (!nhwc) {
+        // the shared-memory tile form: the largest band of output rows whose tiles fit 64 KB
+        const int es = DtSize(dt);
+        int v = 16 / es;
+        while (v > 1 && (g.wout % v != 0 || !Aligned(y, static_cast<size_t>(v) * es))) {
+            v >>= 1;
+        }
+        std::vector<int32_t> top(static_cast<size_t>(g.hout));
+        for (int32_t H = 0; H < g.hout; ++H) {
+            top[H] = FwdTop(H, g.scaleH, g.align, g.hin, nullptr);
+        }
+        auto clampRow = [&](int32_t r) { return std::min(std::max(r, 0), g.hin - 1); };
+        BicubicTile tile{};
+        size_t smem = 0;
+        for (int32_t band = g.hout; band >= 4; band = (band + 1) / 2) {
+            int32_t worst = 0;
+            for (int32_t h0 = 0; h0 < g.hout; h0 += band) {
+                const int32_t h1 = std::min(h0 + band, g.hout);
+                worst = std::max(worst, clampRow(top[h1 - 1] + 2) - clampRow(top[h0] - 1) + 1);
+            }
+            const size_t need = (static_cast<size_t>(worst) * (static_cast<size_t>(g.wout) + g.win) + 5u * band) * sizeof(float);
+            if (need <= 64u * 1024u) {
+                tile.bandRows = band;
+                tile.bands = static_cast<int32_t>(CeilDiv(g.hout, band));
+                tile.maxSrc = worst;
+                smem = need;
+                break;
+            }
+            if (band == 4) {
+                break;
+            }
+        }
+        // a band must still be long enough to amortise the three extra source rows it loads
+        if (smem != 0 && (tile.bandRows >= 16 || tile.bands == 1)) {
+            int tw = 1;
+            while (tw < g.wout && tw < kThreads) {
+                tw <<= 1;
+            }
+            int pw = 1;
+            while (pw < g.wout / v && pw < kThreads) {
+                pw <<= 1;
+            }
+            tile.tw = tw;
+            tile.pw = pw;
+            const int64_t items = planes * tile.bands;
+            const int64_t perSm = std::max<int64_t>(1, std::min<int64_t>(8, (200u * 1024u) / smem));
+            const unsigned grid = static_cast<unsigned>(std::min<int64_t>(items, static_cast<int64_t>(NumSMs()) * perSm * 4));
+            cudaError_t attr = cudaSuccess;
+            OPSCV_DISPATCH_DT(dt, T, {
+                const T* px = static_cast<const T*>(x);
+                T* py = static_cast<T*>(y);
+                OPSCV_DISPATCH_VEC(v, V, {
+                    if constexpr (V * sizeof(T) <= 16) {
+                        if (smem > 48u * 1024u) {
+                            attr = cudaFuncSetAttribute(Bicubic2dFwdTileKernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        static_cast<int>(smem));
+                        }
+                        if (attr == cudaSuccess) {
+                            Bicubic2dFwdTileKernel<T, V><<<grid, kThreads, smem, s>>>(px, py, g, tile, items);
+                        }
+                    }
+                });
+            });
+            if (attr != cudaSuccess) {
+                return attr;
+            }
+            CountLaunch();
+            return cudaGetLastError();
+        }
     }
     // Two elements per thread for 16-bit tensors (4-byte stores) when rows allow it. Bands: enough (plane, band)
     // items to fill the device a few times over, but at least 16 output rows each, since every band starts by
