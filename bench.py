@@ -328,6 +328,12 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
                 "y": torch.empty((n, c, do, ho, wo), dtype=dt, device=gen.device),
                 "gi": torch.empty((n, c, di, hi, wi), dtype=dt, device=gen.device),
                 "ggrid": torch.empty((n, do, ho, wo, 3), dtype=dt, device=gen.device),
+                # the same tensors channels-last (NDHWC)
+                "x_cl": torch.randn((n, di, hi, wi, c), generator=gen, device=gen.device),
+                "go_cl": torch.randn((n, do, ho, wo, c), generator=gen, device=gen.device),
+                "y_cl": torch.empty((n, do, ho, wo, c), dtype=dt, device=gen.device),
+                "gi_cl": torch.empty((n, di, hi, wi, c), dtype=dt, device=gen.device),
+                "ggrid_cl": torch.empty((n, do, ho, wo, 3), dtype=dt, device=gen.device),
             }
         xin, gr, out = n * c * di * hi * wi * 4, n * do * ho * wo * 3 * 4, n * c * do * ho * wo * 4
         oplist = [
@@ -337,8 +343,15 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
             Op("GridSampler3DBackward", lambda b: ops.grid_sampler3d_backward(
                 b["go"], b["x"], b["grid"], 0, 0, False, input_grad=b["gi"], grid_grad=b["ggrid"], workspace=wss[1]),
                out + xin + gr + xin + gr, n * do * ho * wo, ["go", "x", "grid"], ["gi", "ggrid"]),
+            Op("GridSampler3D[NDHWC]", lambda b: ops.grid_sampler3d(b["x_cl"], b["grid"], 0, 0, False, fmt="NDHWC",
+                                                                     out=b["y_cl"], workspace=wss[2]),
+               xin + gr + out, n * do * ho * wo, ["x_cl", "grid"], ["y_cl"]),
+            Op("GridSampler3DBackward[NDHWC]", lambda b: ops.grid_sampler3d_backward(
+                b["go_cl"], b["x_cl"], b["grid"], 0, 0, False, fmt="NDHWC", input_grad=b["gi_cl"],
+                grid_grad=b["ggrid_cl"], workspace=wss[3]),
+               out + xin + gr + xin + gr, n * do * ho * wo, ["go_cl", "x_cl", "grid"], ["gi_cl", "ggrid_cl"]),
         ]
-        cfg = {"workload": f"GridSampler3D forward + backward, bilinear/zeros/align_corners=false, fp32 NCDHW N={n} "
+        cfg = {"workload": f"GridSampler3D forward + backward, bilinear/zeros/align_corners=false, fp32 NCDHW and NDHWC N={n} "
                            "C=32 32x64x64, grid 32x64x64 uniform[-1.1,1.1]", "dtype": "f32"}
         return buffers, oplist, cfg
 

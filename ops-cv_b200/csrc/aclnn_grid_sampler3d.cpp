@@ -134,7 +134,8 @@ aclnnStatus aclnnGridSampler3DGetWorkspaceSize(const aclTensor* input, const acl
     if (IsEmpty(input) || IsEmpty(grid) || IsEmpty(out)) {
         return EmptyOk(api, workspaceSize, executor);
     }
-    if (!ViewStageable(&in5) || !ViewStageable(grid) || !ViewStageable(&out5)) {
+    if (!ViewStageable(&in5) || !ViewStageable(grid) || !ViewStageable(&out5) || !ViewStageable(input) ||
+        !ViewStageable(out)) {
         return Fail(ACLNN_ERR_PARAM_INVALID, "%s: view not supported (more than four strided dimensions)", api);
     }
     aclOpExecutor* ex = NewExecutor(api);
@@ -142,13 +143,19 @@ aclnnStatus aclnnGridSampler3DGetWorkspaceSize(const aclTensor* input, const acl
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    const BufRef x = StageInput(&in5, ws, ex);
+    // channels-last tensors on both sides keep their layout (the kernels read a tap as a contiguous run of channels);
+    // a mix of layouts goes through NCDHW views and the staging copies
+    const bool cl = input->format == ACL_FORMAT_NDHWC && out->format == ACL_FORMAT_NDHWC;
+    const aclTensor* xin = cl ? input : &in5;
+    const aclTensor* yout = cl ? out : &out5;
+    const BufRef x = StageInput(xin, ws, ex);
     const BufRef gr = StageInput(grid, ws, ex);
-    const BufRef y = StageOutput(&out5, ws);
-    const Grid3dShape g = MakeShape(in5, grid, interpolationMode, paddingMode, alignCorners);
+    const BufRef y = StageOutput(yout, ws);
+    Grid3dShape g = MakeShape(in5, grid, interpolationMode, paddingMode, alignCorners);
+    g.cl = cl ? 1 : 0;
     const Dt dt = ToDt(input->dtype);
     ex->steps.push_back([=](char* w, cudaStream_t s) { return GridSampler3dFwd(dt, x.At(w), gr.At(w), y.At(w), g, s); });
-    FinishOutput(&out5, y, ex);
+    FinishOutput(yout, y, ex);
     ex->workspaceSize = ws.Size();
     *workspaceSize = ws.Size();
     *executor = ex;
@@ -220,7 +227,7 @@ aclnnStatus aclnnGridSampler3DBackwardGetWorkspaceSize(const aclTensor* gradOutp
         return EmptyOk(api, workspaceSize, executor);
     }
     if (!ViewStageable(&in5) || !ViewStageable(grid) || !ViewStageable(&go5) || !ViewStageable(&gi5) ||
-        !ViewStageable(gridGrad)) {
+        !ViewStageable(gridGrad) || !ViewStageable(input) || !ViewStageable(gradOutput) || !ViewStageable(inputGrad)) {
         return Fail(ACLNN_ERR_PARAM_INVALID, "%s: view not supported (more than four strided dimensions)", api);
     }
     aclOpExecutor* ex = NewExecutor(api);
@@ -228,12 +235,18 @@ aclnnStatus aclnnGridSampler3DBackwardGetWorkspaceSize(const aclTensor* gradOutp
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    const BufRef go = StageInput(&go5, ws, ex);
-    const BufRef x = StageInput(&in5, ws, ex);
+    const bool cl = input->format == ACL_FORMAT_NDHWC && gradOutput->format == ACL_FORMAT_NDHWC &&
+                    inputGrad->format == ACL_FORMAT_NDHWC;
+    const aclTensor* goT = cl ? gradOutput : &go5;
+    const aclTensor* xT = cl ? input : &in5;
+    const aclTensor* giT = cl ? inputGrad : &gi5;
+    const BufRef go = StageInput(goT, ws, ex);
+    const BufRef x = StageInput(xT, ws, ex);
     const BufRef gr = StageInput(grid, ws, ex);
-    const BufRef gi = StageOutput(&gi5, ws);
+    const BufRef gi = StageOutput(giT, ws);
     const BufRef gg = StageOutput(gridGrad, ws);
-    const Grid3dShape g = MakeShape(in5, grid, interpolationMode, paddingMode, alignCorners);
+    Grid3dShape g = MakeShape(in5, grid, interpolationMode, paddingMode, alignCorners);
+    g.cl = cl ? 1 : 0;
     const Dt dt = ToDt(input->dtype);
     const bool needAcc = wantInput && dt != Dt::F32;
     const uint64_t accOff = needAcc ? ws.Alloc(static_cast<uint64_t>(Numel(input)) * 4) : 0;
@@ -242,7 +255,7 @@ aclnnStatus aclnnGridSampler3DBackwardGetWorkspaceSize(const aclTensor* gradOutp
         return GridSampler3dBwd(dt, go.At(w), x.At(w), gr.At(w), gi.At(w), gg.At(w), acc, g, wantInput, wantGrid, s);
     });
     if (wantInput) {
-        FinishOutput(&gi5, gi, ex);
+        FinishOutput(giT, gi, ex);
     }
     if (wantGrid) {
         FinishOutput(gridGrad, gg, ex);

@@ -1,5 +1,5 @@
-// GridSampler3D forward (bilinear, plus nearest) and GridSampler3DGrad (bilinear, nearest) on NCDHW tensors with a
-// (N, Do, Ho, Wo, 3) grid of (x, y, z) points.
+// GridSampler3D forward (bilinear, plus nearest) and GridSampler3DGrad (bilinear, nearest) on NCDHW and NDHWC tensors
+// with a (N, Do, Ho, Wo, 3) grid of (x, y, z) points.
 //
 // Forward: image/grid_sample/op_kernel/arch35/grid_sampler_3d_bilinear_smit.h:58-184 and
 // grid_sampler_bilinear_smit_common.h:37-91. A thread owns one output point of one image: it reads the grid point
@@ -58,12 +58,16 @@ __device__ __forceinline__ bool Inside3(float d, float h, float w, const Grid3dS
     return d >= 0 && h >= 0 && w >= 0 && d < g.di && h < g.hi && w < g.wi;
 }
 
-template <typename T>
+// CL: channels-last tensors (NDHWC): the channels of a voxel are contiguous, so a tap of a point is one contiguous run
+// of C elements and the channel loop reads and writes V of them at a time; NCDHW: V = 1 and channels are a plane apart.
+template <typename T, bool CL, int V>
 __global__ void __launch_bounds__(kThreads) GridSampler3dFwdKernel(const T* __restrict__ x, const T* __restrict__ grid,
                                                                     T* __restrict__ y, Grid3dShape g)
 {
     const int64_t outVol = static_cast<int64_t>(g.dout) * g.ho * g.wo, inVol = static_cast<int64_t>(g.di) * g.hi * g.wi;
     const int64_t total = g.n * outVol;
+    const int64_t cs = CL ? 1 : inVol, vs = CL ? g.c : 1;       // channel / voxel stride of the input
+    const int64_t ocs = CL ? 1 : outVol, ovs = CL ? g.c : 1;    // of the output
     for (int64_t idx = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; idx < total;
          idx += static_cast<int64_t>(gridDim.x) * kThreads) {
         const int64_t n = idx / outVol, p = idx - n * outVol;
@@ -72,13 +76,22 @@ __global__ void __launch_bounds__(kThreads) GridSampler3dFwdKernel(const T* __re
         const float ph = SourcePoint3(DType<T>::Load(gp + 1), g.hi, g.pad, g.align);
         const float pd = SourcePoint3(DType<T>::Load(gp + 2), g.di, g.pad, g.align);
         const T* xb = x + n * g.c * inVol;
-        T* yb = y + n * g.c * outVol + p;
+        T* yb = y + n * g.c * outVol + p * ovs;
         if (g.interp == 1) { // nearest: the rounding of the backward kernel (rint)
             const float dn = rintf(pd), hn = rintf(ph), wn = rintf(pw);
             const bool in = Inside3(dn, hn, wn, g);
-            const int64_t off = in ? (static_cast<int64_t>(dn) * g.hi + static_cast<int64_t>(hn)) * g.wi + static_cast<int64_t>(wn) : 0;
-            for (int64_t c = 0; c < g.c; ++c) {
-                yb[c * outVol] = in ? __ldg(xb + c * inVol + off) : DType<T>::FromF(0.0f);
+            const int64_t off = in ? ((static_cast<int64_t>(dn) * g.hi + static_cast<int64_t>(hn)) * g.wi + static_cast<int64_t>(wn)) * vs : 0;
+            for (int64_t c = 0; c < g.c; c += V) {
+                float v[V];
+                if (in) {
+                    LoadPack<T, V>(xb + c * cs + off, v);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        v[k] = 0.0f;
+                    }
+                }
+                StorePack<T, V>(yb + c * ocs, v);
             }
             continue;
         }
@@ -94,21 +107,42 @@ __global__ void __launch_bounds__(kThreads) GridSampler3dFwdKernel(const T* __re
             wt[k] = Mul(Mul(east ? wd : wd0, south ? hd : hd0), back ? dd : dd0);
             const float d = back ? Add(df, 1.0f) : df, h = south ? Add(hf, 1.0f) : hf, w = east ? Add(wf, 1.0f) : wf;
             in[k] = Inside3(d, h, w, g);
-            off[k] = in[k] ? (static_cast<int64_t>(d) * g.hi + static_cast<int64_t>(h)) * g.wi + static_cast<int64_t>(w) : 0;
+            off[k] = in[k] ? ((static_cast<int64_t>(d) * g.hi + static_cast<int64_t>(h)) * g.wi + static_cast<int64_t>(w)) * vs : 0;
         }
-        for (int64_t c = 0; c < g.c; ++c) {
-            const T* xc = xb + c * inVol;
-            float v = Mul(in[0] ? DType<T>::Load(xc + off[0]) : 0.0f, wt[0]);
+        for (int64_t c = 0; c < g.c; c += V) {
+            const T* xc = xb + c * cs;
+            float acc[V], t[V];
 #pragma unroll
-            for (int k = 1; k < 8; ++k) {
-                v = Add(v, Mul(in[k] ? DType<T>::Load(xc + off[k]) : 0.0f, wt[k]));
+            for (int k = 0; k < 8; ++k) {
+                if (in[k]) {
+                    LoadPack<T, V>(xc + off[k], t);
+                } else {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        t[v] = 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    acc[v] = k == 0 ? Mul(t[v], wt[0]) : Add(acc[v], Mul(t[v], wt[k]));
+                }
             }
-            yb[c * outVol] = DType<T>::FromF(v);
+            StorePack<T, V>(yb + c * ocs, acc);
         }
     }
 }
 
-template <typename T>
+__device__ __forceinline__ void AtomicAddPack(float* p, const float (&v)[1]) { atomicAdd(p, v[0]); }
+__device__ __forceinline__ void AtomicAddPack(float* p, const float (&v)[2])
+{
+    atomicAdd(reinterpret_cast<float2*>(p), make_float2(v[0], v[1])); // one 8-byte reduction (sm_90 and later)
+}
+__device__ __forceinline__ void AtomicAddPack(float* p, const float (&v)[4])
+{
+    atomicAdd(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3])); // one 16-byte reduction
+}
+
+template <typename T, bool CL, int V>
 __global__ void __launch_bounds__(kThreads)
     GridSampler3dBwdKernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ grid,
                            float* __restrict__ acc, T* __restrict__ ggrid, Grid3dShape g, int32_t wantInput,
@@ -116,6 +150,8 @@ __global__ void __launch_bounds__(kThreads)
 {
     const int64_t outVol = static_cast<int64_t>(g.dout) * g.ho * g.wo, inVol = static_cast<int64_t>(g.di) * g.hi * g.wi;
     const int64_t total = g.n * outVol;
+    const int64_t cs = CL ? 1 : inVol, vs = CL ? g.c : 1;
+    const int64_t ocs = CL ? 1 : outVol, ovs = CL ? g.c : 1;
     for (int64_t idx = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; idx < total;
          idx += static_cast<int64_t>(gridDim.x) * kThreads) {
         const int64_t n = idx / outVol, p = idx - n * outVol;
@@ -124,7 +160,7 @@ __global__ void __launch_bounds__(kThreads)
         const float ix = gs::SourceIndexSetGrad(DType<T>::Load(gp), g.wi, g.pad, g.align, &mx);
         const float iy = gs::SourceIndexSetGrad(DType<T>::Load(gp + 1), g.hi, g.pad, g.align, &my);
         const float iz = gs::SourceIndexSetGrad(DType<T>::Load(gp + 2), g.di, g.pad, g.align, &mz);
-        const T* gob = go + n * g.c * outVol + p;
+        const T* gob = go + n * g.c * outVol + p * ovs;
         const T* xb = x + n * g.c * inVol;
         float* ab = acc + n * g.c * inVol;
         auto inside = [&](int32_t d, int32_t h, int32_t w) {
@@ -134,9 +170,11 @@ __global__ void __launch_bounds__(kThreads)
             const int32_t xn = static_cast<int32_t>(rintf(ix)), yn = static_cast<int32_t>(rintf(iy)),
                           zn = static_cast<int32_t>(rintf(iz));
             if (wantInput && inside(zn, yn, xn)) {
-                const int64_t off = (static_cast<int64_t>(zn) * g.hi + yn) * g.wi + xn;
-                for (int64_t c = 0; c < g.c; ++c) {
-                    atomicAdd(ab + c * inVol + off, DType<T>::Load(gob + c * outVol));
+                const int64_t off = ((static_cast<int64_t>(zn) * g.hi + yn) * g.wi + xn) * vs;
+                for (int64_t c = 0; c < g.c; c += V) {
+                    float gv[V];
+                    LoadPack<T, V>(gob + c * ocs, gv);
+                    AtomicAddPack(ab + c * cs + off, gv);
                 }
             }
             if (wantGrid) {
@@ -158,28 +196,51 @@ __global__ void __launch_bounds__(kThreads)
             wt[k] = Mul(Mul(east ? xw : xe, south ? yw : ye), bottom ? zw : ze);
             const int32_t d = bottom ? z0 + 1 : z0, h = south ? y0 + 1 : y0, w = east ? x0 + 1 : x0;
             in[k] = inside(d, h, w);
-            off[k] = in[k] ? (static_cast<int64_t>(d) * g.hi + h) * g.wi + w : 0;
+            off[k] = in[k] ? ((static_cast<int64_t>(d) * g.hi + h) * g.wi + w) * vs : 0;
         }
         float gix = 0.0f, giy = 0.0f, giz = 0.0f;
-        for (int64_t c = 0; c < g.c; ++c) {
-            const float gv = DType<T>::Load(gob + c * outVol);
+        for (int64_t c = 0; c < g.c; c += V) {
+            float gv[V];
+            LoadPack<T, V>(gob + c * ocs, gv);
+            float xv[8][V];
+            if (wantGrid) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                if (!in[k]) {
-                    continue;
+                for (int k = 0; k < 8; ++k) {
+                    if (in[k]) {
+                        LoadPack<T, V>(xb + c * cs + off[k], xv[k]);
+                    }
                 }
-                const bool east = (k & 1) != 0, south = (k & 2) != 0, bottom = (k & 4) != 0;
-                if (wantInput) {
-                    atomicAdd(ab + c * inVol + off[k], Mul(wt[k], gv));
+            }
+            if (wantInput) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (in[k]) {
+                        float t[V];
+#pragma unroll
+                        for (int v = 0; v < V; ++v) {
+                            t[v] = Mul(wt[k], gv[v]);
+                        }
+                        AtomicAddPack(ab + c * cs + off[k], t);
+                    }
                 }
-                if (wantGrid) {
-                    const float v = DType<T>::Load(xb + c * inVol + off[k]);
-                    const float fx = east ? xw : xe, fy = south ? yw : ye, fz = bottom ? zw : ze;
-                    const float tx = Mul(Mul(Mul(v, fy), fz), gv), ty = Mul(Mul(Mul(v, fx), fz), gv),
-                                tz = Mul(Mul(Mul(v, fx), fy), gv);
-                    gix = east ? Add(gix, tx) : Sub(gix, tx);
-                    giy = south ? Add(giy, ty) : Sub(giy, ty);
-                    giz = bottom ? Add(giz, tz) : Sub(giz, tz);
+            }
+            if (wantGrid) { // channel by channel, corner by corner: the reference's order
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        if (!in[k]) {
+                            continue;
+                        }
+                        const bool east = (k & 1) != 0, south = (k & 2) != 0, bottom = (k & 4) != 0;
+                        const float val = xv[k][v];
+                        const float fx = east ? xw : xe, fy = south ? yw : ye, fz = bottom ? zw : ze;
+                        const float tx = Mul(Mul(Mul(val, fy), fz), gv[v]), ty = Mul(Mul(Mul(val, fx), fz), gv[v]),
+                                    tz = Mul(Mul(Mul(val, fx), fy), gv[v]);
+                        gix = east ? Add(gix, tx) : Sub(gix, tx);
+                        giy = south ? Add(giy, ty) : Sub(giy, ty);
+                        giz = bottom ? Add(giz, tz) : Sub(giz, tz);
+                    }
                 }
             }
         }
@@ -191,14 +252,46 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// Channel vector of the channels-last kernels: 16 bytes of fp32 accumulator at most, C a multiple of it, pointers aligned.
+int ChannelVec(const Grid3dShape& g, int es, std::initializer_list<const void*> ptrs, const float* acc)
+{
+    if (!g.cl) {
+        return 1;
+    }
+    int v = 4;
+    while (v > 1) {
+        bool ok = g.c % v == 0 && (acc == nullptr || Aligned(acc, static_cast<size_t>(v) * sizeof(float)));
+        for (const void* p : ptrs) {
+            ok = ok && Aligned(p, static_cast<size_t>(v) * es);
+        }
+        if (ok) {
+            break;
+        }
+        v >>= 1;
+    }
+    return v;
+}
+
 } // namespace
 
 cudaError_t GridSampler3dFwd(Dt dt, const void* x, const void* grid, void* y, Grid3dShape g, cudaStream_t s)
 {
     const int64_t total = g.n * g.dout * g.ho * g.wo;
+    const int v = ChannelVec(g, DtSize(dt), {x, y}, nullptr);
     OPSCV_DISPATCH_DT(dt, T, {
-        GridSampler3dFwdKernel<T><<<GridFor(total, kThreads), kThreads, 0, s>>>(
-            static_cast<const T*>(x), static_cast<const T*>(grid), static_cast<T*>(y), g);
+        const T* px = static_cast<const T*>(x);
+        const T* pg = static_cast<const T*>(grid);
+        T* py = static_cast<T*>(y);
+        const unsigned grid1 = GridFor(total, kThreads);
+        if (!g.cl) {
+            GridSampler3dFwdKernel<T, false, 1><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
+        } else if (v == 4) {
+            GridSampler3dFwdKernel<T, true, 4><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
+        } else if (v == 2) {
+            GridSampler3dFwdKernel<T, true, 2><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
+        } else {
+            GridSampler3dFwdKernel<T, true, 1><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
+        }
     });
     CountLaunch();
     return cudaGetLastError();
@@ -218,10 +311,23 @@ cudaError_t GridSampler3dBwd(Dt dt, const void* go, const void* x, const void* g
             return e;
         }
     }
+    const int v = ChannelVec(g, DtSize(dt), {go, x}, acc);
     OPSCV_DISPATCH_DT(dt, T, {
-        GridSampler3dBwdKernel<T><<<GridFor(total, kThreads), kThreads, 0, s>>>(
-            static_cast<const T*>(go), static_cast<const T*>(x), static_cast<const T*>(grid), acc,
-            static_cast<T*>(ggrid), g, wantInput ? 1 : 0, wantGrid ? 1 : 0);
+        const T* pgo = static_cast<const T*>(go);
+        const T* px = static_cast<const T*>(x);
+        const T* pg = static_cast<const T*>(grid);
+        T* pgg = static_cast<T*>(ggrid);
+        const unsigned grid1 = GridFor(total, kThreads);
+        const int32_t wi = wantInput ? 1 : 0, wg = wantGrid ? 1 : 0;
+        if (!g.cl) {
+            GridSampler3dBwdKernel<T, false, 1><<<grid1, kThreads, 0, s>>>(pgo, px, pg, acc, pgg, g, wi, wg);
+        } else if (v == 4) {
+            GridSampler3dBwdKernel<T, true, 4><<<grid1, kThreads, 0, s>>>(pgo, px, pg, acc, pgg, g, wi, wg);
+        } else if (v == 2) {
+            GridSampler3dBwdKernel<T, true, 2><<<grid1, kThreads, 0, s>>>(pgo, px, pg, acc, pgg, g, wi, wg);
+        } else {
+            GridSampler3dBwdKernel<T, true, 1><<<grid1, kThreads, 0, s>>>(pgo, px, pg, acc, pgg, g, wi, wg);
+        }
     });
     CountLaunch();
     e = cudaGetLastError();

@@ -250,6 +250,7 @@ struct Grid3dShape {
     int64_t n, c;
     int32_t di, hi, wi, dout, ho, wo;
     int32_t interp, pad, align;
+    int32_t cl = 0; // 1: input, output and gradients are channels-last (NDHWC), contiguous
 };
 cudaError_t GridSampler3dFwd(Dt dt, const void* x, const void* grid, void* y, Grid3dShape g, cudaStream_t s);
 cudaError_t GridSampler3dBwd(Dt dt, const void* go, const void* x, const void* grid, void* gi, void* ggrid, float* acc,

@@ -83,3 +83,36 @@ def test_grid_sampler3d_torch_nearest_layouts_and_special_values(ops, oracle, de
         assert np.array_equal(y.cpu().numpy(), oracle.grid_sampler3d_fwd(x.float().numpy(), bad.numpy(), pad, False))
     e = ops.grid_sampler3d(torch.zeros((0, 3, 4, 4, 4), device=dev), torch.zeros((0, 2, 2, 2, 3), device=dev))
     assert e.shape == (0, 3, 2, 2, 2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("channels", [8, 6, 5])   # channel vectors of 4, 2 and 1
+@pytest.mark.parametrize("interp", [0, 1])
+@pytest.mark.parametrize("pad", [0, 2])
+def test_grid_sampler3d_channels_last(ops, oracle, dev, dtype, channels, interp, pad):
+    """NDHWC tensors run on kernels that read a tap as one contiguous run of channels: the forward keeps the oracle's
+    bits, grad_grid too, grad_input is the same atomic sum as for NCDHW."""
+    x, x32 = quant(torch.randn((2, channels, 5, 6, 7), generator=gen(120)), dtype)
+    grid, g32 = quant(make_grid(2, 3, 4, 5, 121), dtype)
+    go, go32 = quant(torch.randn((2, channels, 3, 4, 5), generator=gen(122)), dtype)
+    cl = lambda t: t.permute(0, 2, 3, 4, 1).contiguous().to(dev)  # noqa: E731
+    y = ops.grid_sampler3d(cl(x), grid.to(dev), interp, pad, False, fmt="NDHWC").permute(0, 4, 1, 2, 3)
+    if interp == 0:
+        check(y, oracle.grid_sampler3d_fwd(x32, g32, pad, False), dtype, exact=(dtype == torch.float32))
+    else:
+        assert torch.equal(y, ops.grid_sampler3d(x.to(dev), grid.to(dev), interp, pad, False))
+    gi, gg = ops.grid_sampler3d_backward(cl(go), cl(x), grid.to(dev), interp, pad, False, fmt="NDHWC")
+    ri, rg = oracle.grid_sampler3d_bwd(go32, x32, g32, interp, pad, False)
+    gi = gi.permute(0, 4, 1, 2, 3)
+    if dtype == torch.float32:
+        np.testing.assert_allclose(gi.cpu().numpy(), ri, rtol=1e-5, atol=1e-6 * max(1.0, float(np.abs(ri).max())))
+        assert np.array_equal(gg.cpu().numpy(), rg)
+    else:
+        check(gg, rg, dtype)
+        step = np.maximum(np.abs(ri) * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10), 1e-6 * max(1.0, float(np.abs(ri).max())))
+        assert (np.abs(gi.float().cpu().numpy() - ri) <= step * 1.01 + 1e-6).all()
+    # a strided channels-last view (cropped W) goes through the staging copies and gives the same result
+    base = torch.zeros((2, 5, 6, 9, channels), dtype=dtype)
+    base[:, :, :, 1:8, :] = x.permute(0, 2, 3, 4, 1)
+    yv = ops.grid_sampler3d(base.to(dev)[:, :, :, 1:8, :], grid.to(dev), interp, pad, False, fmt="NDHWC")
+    assert torch.equal(yv.permute(0, 4, 1, 2, 3), y)
