@@ -198,61 +198,61 @@ __global__ void __launch_bounds__(kThreads) TrilinearHDStageKernel(const float* 
     const Tap th = FwdTap(g.sh, h, g.align, g.hi);
     const int32_t perChunk = (g.dout + depthChunks - 1) / depthChunks;
     for (int64_t pc = blockIdx.y; pc < planeChunks; pc += gridDim.y) {
-    const int64_t plane = pc / depthChunks;
-    const int32_t chunk = static_cast<int32_t>(pc - plane * depthChunks);
-    const int32_t dBegin = chunk * perChunk;
-    const int32_t dEnd = dBegin + perChunk < g.dout ? dBegin + perChunk : g.dout;
-    constexpr int C = V / 4 > 0 ? V / 4 : 1; // 16-byte chunks per row
-    constexpr int L = V < 4 ? V : 4;
-    const float* pa = a + plane * g.di * g.hi * inner + t0;
-    const int64_t off0 = th.i0 * inner, off1 = th.i1 * inner, depthStride = g.hi * inner;
-    auto blend = [&](int32_t j, float (&row)[V]) {
-        const float* p = pa + j * depthStride;
+        const int64_t plane = pc / depthChunks;
+        const int32_t chunk = static_cast<int32_t>(pc - plane * depthChunks);
+        const int32_t dBegin = chunk * perChunk;
+        const int32_t dEnd = dBegin + perChunk < g.dout ? dBegin + perChunk : g.dout;
+        constexpr int C = V / 4 > 0 ? V / 4 : 1; // 16-byte chunks per row
+        constexpr int L = V < 4 ? V : 4;
+        const float* pa = a + plane * g.di * g.hi * inner + t0;
+        const int64_t off0 = th.i0 * inner, off1 = th.i1 * inner, depthStride = g.hi * inner;
+        auto blend = [&](int32_t j, float (&row)[V]) {
+            const float* p = pa + j * depthStride;
 #pragma unroll
-        for (int c = 0; c < C; ++c) {
-            float v0[L], v1[L];
-            LoadPack<float, L>(p + off0 + c * L, v0);
-            LoadPack<float, L>(p + off1 + c * L, v1);
+            for (int c = 0; c < C; ++c) {
+                float v0[L], v1[L];
+                LoadPack<float, L>(p + off0 + c * L, v0);
+                LoadPack<float, L>(p + off1 + c * L, v1);
 #pragma unroll
-            for (int v = 0; v < L; ++v) {
-                row[c * L + v] = Add(Mul(th.w0, v0[v]), Mul(th.w1, v1[v]));
-            }
-        }
-    };
-    float lo[V], hi[V];
-    int32_t cur0 = -1, cur1 = -1;
-    T* py = y + ((plane * g.dout + dBegin) * g.ho + h) * inner + t0;
-    for (int32_t d = dBegin; d < dEnd; ++d, py += g.ho * inner) {
-        const Tap td = FwdTap(g.sd, d, g.align, g.di);
-        if (td.i0 != cur0) {
-            if (td.i0 == cur1) {
-#pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    lo[v] = hi[v];
+                for (int v = 0; v < L; ++v) {
+                    row[c * L + v] = Add(Mul(th.w0, v0[v]), Mul(th.w1, v1[v]));
                 }
-            } else {
-                blend(td.i0, lo);
             }
-            cur0 = td.i0;
-        }
-        if (td.i1 != cur1) {
-            if (td.i1 == cur0) {
+        };
+        float lo[V], hi[V];
+        int32_t cur0 = -1, cur1 = -1;
+        T* py = y + ((plane * g.dout + dBegin) * g.ho + h) * inner + t0;
+        for (int32_t d = dBegin; d < dEnd; ++d, py += g.ho * inner) {
+            const Tap td = FwdTap(g.sd, d, g.align, g.di);
+            if (td.i0 != cur0) {
+                if (td.i0 == cur1) {
 #pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    hi[v] = lo[v];
+                    for (int v = 0; v < V; ++v) {
+                        lo[v] = hi[v];
+                    }
+                } else {
+                    blend(td.i0, lo);
                 }
-            } else {
-                blend(td.i1, hi);
+                cur0 = td.i0;
             }
-            cur1 = td.i1;
-        }
-        float out[V];
+            if (td.i1 != cur1) {
+                if (td.i1 == cur0) {
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            out[v] = Add(Mul(td.w0, lo[v]), Mul(td.w1, hi[v]));
+                    for (int v = 0; v < V; ++v) {
+                        hi[v] = lo[v];
+                    }
+                } else {
+                    blend(td.i1, hi);
+                }
+                cur1 = td.i1;
+            }
+            float out[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                out[v] = Add(Mul(td.w0, lo[v]), Mul(td.w1, hi[v]));
+            }
+            StorePack<T, V>(py, out);
         }
-        StorePack<T, V>(py, out);
-    }
     }
 }
 
