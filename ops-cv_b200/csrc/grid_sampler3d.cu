@@ -132,6 +132,66 @@ __global__ void __launch_bounds__(kThreads) GridSampler3dFwdKernel(const T* __re
     }
 }
 
+// Channels-last forward with the channel vectors of a point on adjacent lanes: thread t owns channel vector t % G of
+// point t / G (G = C / V), so the G lanes of a point read each tap as one contiguous run of C elements and write the
+// point's C outputs as one run. Every lane of a point evaluates the point's coordinates itself (a hundred
+// instructions against eight 16-byte loads); the sums are those of the kernel above, in the same order.
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads) GridSampler3dFwdLanesKernel(const T* __restrict__ x, const T* __restrict__ grid,
+                                                                         T* __restrict__ y, Grid3dShape g, int32_t groups)
+{
+    const int64_t outVol = static_cast<int64_t>(g.dout) * g.ho * g.wo, inVol = static_cast<int64_t>(g.di) * g.hi * g.wi;
+    const int64_t total = g.n * outVol * groups;
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; t < total;
+         t += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int64_t idx = t / groups;
+        const int64_t c = (t - idx * groups) * V;
+        const int64_t n = idx / outVol;
+        const T* gp = grid + idx * 3;
+        const float pw = SourcePoint3(DType<T>::Load(gp), g.wi, g.pad, g.align);
+        const float ph = SourcePoint3(DType<T>::Load(gp + 1), g.hi, g.pad, g.align);
+        const float pd = SourcePoint3(DType<T>::Load(gp + 2), g.di, g.pad, g.align);
+        const T* xb = x + n * g.c * inVol + c;
+        T* yp = y + idx * g.c + c;
+        float acc[V], tv[V];
+        if (g.interp == 1) {
+            const float dn = rintf(pd), hn = rintf(ph), wn = rintf(pw);
+            if (Inside3(dn, hn, wn, g)) {
+                LoadPack<T, V>(xb + ((static_cast<int64_t>(dn) * g.hi + static_cast<int64_t>(hn)) * g.wi + static_cast<int64_t>(wn)) * g.c, acc);
+            } else {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    acc[v] = 0.0f;
+                }
+            }
+            StorePack<T, V>(yp, acc);
+            continue;
+        }
+        const float df = floorf(pd), hf = floorf(ph), wf = floorf(pw);
+        const float dd = Sub(pd, df), hd = Sub(ph, hf), wd = Sub(pw, wf);
+        const float wd0 = Sub(1.0f, wd), hd0 = Sub(1.0f, hd), dd0 = Sub(1.0f, dd);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const bool east = (k & 1) != 0, south = (k & 2) != 0, back = (k & 4) != 0;
+            const float wt = Mul(Mul(east ? wd : wd0, south ? hd : hd0), back ? dd : dd0);
+            const float d = back ? Add(df, 1.0f) : df, h = south ? Add(hf, 1.0f) : hf, w = east ? Add(wf, 1.0f) : wf;
+            if (Inside3(d, h, w, g)) {
+                LoadPack<T, V>(xb + ((static_cast<int64_t>(d) * g.hi + static_cast<int64_t>(h)) * g.wi + static_cast<int64_t>(w)) * g.c, tv);
+            } else {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    tv[v] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                acc[v] = k == 0 ? Mul(tv[v], wt) : Add(acc[v], Mul(tv[v], wt));
+            }
+        }
+        StorePack<T, V>(yp, acc);
+    }
+}
+
 __device__ __forceinline__ void AtomicAddPack(float* p, const float (&v)[1]) { atomicAdd(p, v[0]); }
 __device__ __forceinline__ void AtomicAddPack(float* p, const float (&v)[2])
 {
@@ -286,9 +346,11 @@ cudaError_t GridSampler3dFwd(Dt dt, const void* x, const void* grid, void* y, Gr
         if (!g.cl) {
             GridSampler3dFwdKernel<T, false, 1><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
         } else if (v == 4) {
-            GridSampler3dFwdKernel<T, true, 4><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
+            const int32_t groups = static_cast<int32_t>(g.c / 4);
+            GridSampler3dFwdLanesKernel<T, 4><<<GridFor(total * groups, kThreads), kThreads, 0, s>>>(px, pg, py, g, groups);
         } else if (v == 2) {
-            GridSampler3dFwdKernel<T, true, 2><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
+            const int32_t groups = static_cast<int32_t>(g.c / 2);
+            GridSampler3dFwdLanesKernel<T, 2><<<GridFor(total * groups, kThreads), kThreads, 0, s>>>(px, pg, py, g, groups);
         } else {
             GridSampler3dFwdKernel<T, true, 1><<<grid1, kThreads, 0, s>>>(px, pg, py, g);
         }
