@@ -126,16 +126,24 @@ __global__ void __launch_bounds__(kThreads) Nearest3dFwdX2Kernel(const T* __rest
         int32_t d, h;
         SplitRow(row, g.hi, g.di, small, plane, d, h);
         const Pack<T, VI> in = *reinterpret_cast<const Pack<T, VI>*>(x + row * g.wi + t0);
-        Pack<T, 2 * VI> out;
+        // the 2 * VI outputs as one or two 16-byte stores
+        constexpr int H = (2 * VI * sizeof(T) > 16) ? VI : 2 * VI;
+        Pack<T, H> out[2 * VI / H];
 #pragma unroll
         for (int v = 0; v < VI; ++v) {
-            out.v[2 * v] = in.v[v];
-            out.v[2 * v + 1] = in.v[v];
+            out[(2 * v) / H].v[(2 * v) % H] = in.v[v];
+            out[(2 * v + 1) / H].v[(2 * v + 1) % H] = in.v[v];
         }
         for (int32_t a = 0; a < g.rd; ++a) {
             for (int32_t b = 0; b < g.rh; ++b) {
                 const int64_t orow = (plane * g.dout + static_cast<int64_t>(d) * g.rd + a) * g.ho + static_cast<int64_t>(h) * g.rh + b;
-                *reinterpret_cast<Pack<T, 2 * VI>*>(y + orow * g.wo + 2 * t0) = out;
+                if constexpr (2 * VI * sizeof(T) == 32) {
+                    // one 32-byte store: two 16-byte stores would each touch half of every sector of the warp
+                    Store32Bytes(y + orow * g.wo + 2 * t0, reinterpret_cast<const uint4&>(out[0]),
+                                 reinterpret_cast<const uint4&>(out[1]));
+                } else {
+                    *reinterpret_cast<Pack<T, H>*>(y + orow * g.wo + 2 * t0) = out[0];
+                }
             }
         }
     }
@@ -162,11 +170,16 @@ __global__ void __launch_bounds__(kThreads) Nearest3dBwdX2Kernel(const T* __rest
         for (int32_t a = 0; a < g.rd; ++a) {
             for (int32_t b = 0; b < g.rh; ++b) {
                 const int64_t orow = (plane * g.dout + static_cast<int64_t>(d) * g.rd + a) * g.ho + static_cast<int64_t>(h) * g.rh + b;
-                float gv[2 * VO];
-                LoadPackLdg<T, 2 * VO>(go + orow * g.wo + 2 * t0, gv);
+                // 2 * VO grads as one or two 16-byte loads
+                constexpr int H = (2 * VO * sizeof(T) > 16) ? VO : 2 * VO; // elements per load
 #pragma unroll
-                for (int v = 0; v < VO; ++v) {
-                    acc[v] = Add(Add(acc[v], gv[2 * v]), gv[2 * v + 1]);
+                for (int part = 0; part < 2 * VO / H; ++part) {
+                    float gv[H];
+                    LoadPackLdg<T, H>(go + orow * g.wo + 2 * t0 + part * H, gv);
+#pragma unroll
+                    for (int v = 0; v < H / 2; ++v) {
+                        acc[part * (H / 2) + v] = Add(Add(acc[part * (H / 2) + v], gv[2 * v]), gv[2 * v + 1]);
+                    }
                 }
             }
         }
@@ -182,7 +195,7 @@ cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStr
     const int es = DtSize(dt);
     const bool cl = g.chan > 1;
     if (!cl && g.rw == 2 && g.rd >= 1 && g.rh >= 1) {
-        int vi = 8 / es; // 16 bytes of outputs per store
+        int vi = 16 / es; // a 16-byte load becomes 32 bytes of each output row, written as one 32-byte store
         while (vi > 1 && (g.wi % vi != 0 || !Aligned(x, static_cast<size_t>(vi) * es) ||
                           !Aligned(y, static_cast<size_t>(2 * vi) * es))) {
             vi >>= 1;
@@ -194,7 +207,7 @@ cudaError_t Nearest3dFwd(Dt dt, const void* x, void* y, Nearest3dGeom g, cudaStr
                 const T* px = static_cast<const T*>(x);
                 T* py = static_cast<T*>(y);
                 OPSCV_DISPATCH_VEC(vi, VI, {
-                    if constexpr (2 * VI * sizeof(T) <= 16) {
+                    if constexpr (VI * sizeof(T) <= 16) {
                         Nearest3dFwdX2Kernel<T, VI><<<rl.grid, rl.block, 0, s>>>(px, py, g);
                     }
                 });
@@ -232,18 +245,18 @@ cudaError_t Nearest3dBwd(Dt dt, const void* go, void* gi, Nearest3dGeom g, cudaS
     const int64_t inner = static_cast<int64_t>(g.wi) * g.chan;
     const int es = DtSize(dt);
     if (g.chan == 1 && g.rw == 2 && g.rd >= 1 && g.rh >= 1) {
-        int vo = 8 / es; // 16 bytes of grads per load
+        int vo = 16 / es; // 16 bytes of grad_input per store, read as 16-byte loads of grads
         while (vo > 1 && (g.wi % vo != 0 || !Aligned(gi, static_cast<size_t>(vo) * es) ||
-                          !Aligned(go, static_cast<size_t>(2 * vo) * es))) {
+                          !Aligned(go, std::min<size_t>(16, static_cast<size_t>(2 * vo) * es)))) {
             vo >>= 1;
         }
-        if (Aligned(go, static_cast<size_t>(2 * vo) * es)) {
+        if (Aligned(go, std::min<size_t>(16, static_cast<size_t>(2 * vo) * es))) {
             const RowLaunch rl = RowTiling(g.rows, CeilDiv(static_cast<int64_t>(g.wi), vo), kThreads);
             OPSCV_DISPATCH_DT(dt, T, {
                 const T* pg = static_cast<const T*>(go);
                 T* pi = static_cast<T*>(gi);
                 OPSCV_DISPATCH_VEC(vo, VO, {
-                    if constexpr (2 * VO * sizeof(T) <= 16) {
+                    if constexpr (VO * sizeof(T) <= 16) {
                         Nearest3dBwdX2Kernel<T, VO><<<rl.grid, rl.block, 0, s>>>(pg, pi, g);
                     }
                 });
