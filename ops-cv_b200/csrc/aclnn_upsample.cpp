@@ -182,6 +182,26 @@ aclnnStatus CheckNearestFwd(const char* api, const aclTensor* self, const aclInt
     return ACLNN_SUCCESS;
 }
 
+// An NCHW input view that the strided forward kernels can read in place: not contiguous (a contiguous one takes the
+// dense kernels), four dimensions in NCHW order, no negative stride.
+bool StridedNchwInput(const aclTensor* t, InStrides* st)
+{
+    if (t->format == ACL_FORMAT_NHWC || t->dims.size() != 4 || t->strides.size() != 4 || IsContiguous(t)) {
+        return false;
+    }
+    for (int64_t v : t->strides) {
+        if (v < 0) {
+            return false;
+        }
+    }
+    st->n = t->strides[0];
+    st->c = t->strides[1];
+    st->h = t->strides[2];
+    st->w = t->strides[3];
+    st->chan = static_cast<int32_t>(t->dims[1]);
+    return true;
+}
+
 aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTensor* out, float userScaleH,
                            float userScaleW, uint64_t* workspaceSize, aclOpExecutor** executor, bool exact = false)
 {
@@ -193,7 +213,14 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
     }
     WsPlan ws;
     const Geom gi = GeomOf(self), go = GeomOf(out);
-    const BufRef x = StageInput(self, ws, ex);
+    InStrides st{};
+    const bool strided = StridedNchwInput(self, &st);
+    BufRef x;
+    if (strided) { // read through the view's strides: no gather copy
+        x.base = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
+    } else {
+        x = StageInput(self, ws, ex);
+    }
     const BufRef y = StageOutput(out, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
@@ -202,6 +229,21 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
     const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, go.w, userScaleW), exact ? 1 : 0};
     const uint64_t offH = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.hout));
     const uint64_t offW = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.wout));
+    if (strided) {
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            const NearestAxis th{reinterpret_cast<int32_t*>(w + offH)}, tw{reinterpret_cast<int32_t*>(w + offW)};
+            const cudaError_t e = BuildNearestFwdTables(ah, aw, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            return NearestFwdStrided(dt, x.At(w), st, y.At(w), sh, th, tw, s);
+        });
+        FinishOutput(out, y, ex);
+        ex->workspaceSize = ws.Size();
+        *workspaceSize = ws.Size();
+        *executor = ex;
+        return ACLNN_SUCCESS;
+    }
     const NearestPlan plan = MakeNearestFwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const NearestAxis th{reinterpret_cast<int32_t*>(w + offH)}, tw{reinterpret_cast<int32_t*>(w + offW)};
@@ -1049,7 +1091,14 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    const BufRef x = StageInput(self, ws, ex);
+    InStrides st{};
+    const bool strided = StridedNchwInput(self, &st);
+    BufRef x;
+    if (strided) { // read through the view's strides: no gather copy
+        x.base = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
+    } else {
+        x = StageInput(self, ws, ex);
+    }
     const BufRef y = StageOutput(outT, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
@@ -1059,6 +1108,21 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     const AxisGeom aw{sh.win, sh.wout, BilinearScale(gi.w, go.w, alignCorners, static_cast<float>(scalesW))};
     const bool halfPixel = !alignCorners; // resize_bilinear_v2.cpp:99
     const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
+    if (strided) {
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
+            const cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 0, th, tw, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            return BilinearFwdStrided(dt, x.At(w), st, y.At(w), sh, th, tw, s);
+        });
+        FinishOutput(outT, y, ex);
+        ex->workspaceSize = ws.Size();
+        *workspaceSize = ws.Size();
+        *executor = ex;
+        return ACLNN_SUCCESS;
+    }
     const BilinearPlan plan = MakeBilinearFwdPlan(dt, lay, sh, ah, aw, halfPixel);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);

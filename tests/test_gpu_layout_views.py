@@ -79,3 +79,37 @@ def test_mixed_layouts_still_go_through_staging(ops, dev):
     x_cl = x.contiguous(memory_format=torch.channels_last)
     got = ops.upsample_bilinear2d(x_cl, (20, 31), False, "NCHW")          # contiguous NCHW output
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("align", [False, True])
+def test_strided_nchw_inputs_are_read_in_place(ops, dev, dtype, align):
+    """Crops, steps and broadcast batches of an NCHW tensor feed the nearest and bilinear forwards through their
+    strides: the bits of the call on a contiguous copy, and one launch less than the path through the gather copy
+    (two kernels: the table builder and the resampler)."""
+    base = torch.randn((3, 5, 20, 31), generator=gen(92)).to(dtype).to(dev)
+    views = {
+        "crop": base[:, 1:4, 2:17, 3:28],
+        "step": base[::2, :, ::2, 1::3],
+        "broadcast": base[:1, :, 4:12, 5:17].expand(4, 5, 8, 12),
+        "channel slice": base[:, ::2],
+    }
+    for name, v in views.items():
+        assert not v.is_contiguous()
+        ho, wo = v.shape[2] * 2 + 1, v.shape[3] * 2 - 1
+        dense = v.contiguous()
+        for op, call in (("nearest", lambda t: ops.upsample_nearest2d(t, (ho, wo))),
+                         ("nearest_exact", lambda t: ops.upsample_nearest_exact2d(t, (ho, wo))),
+                         ("bilinear", lambda t: ops.upsample_bilinear2d(t, (ho, wo), align)),
+                         ("resize", lambda t: ops.resize(t, (1.0, 1.0, 2.0, 2.0), "bilinear"))):
+            want, _ = _launches(ops, lambda: call(dense))
+            got, count = _launches(ops, lambda: call(v))
+            assert torch.equal(got, want), (name, op)
+            assert count == 2, (name, op, count)
+    # down-scaling, a strided output view at the same time (the output still goes through its scatter copy)
+    v = base[:, :, 1:19, 2:30]
+    out_base = torch.zeros((3, 5, 7, 22), dtype=dtype, device=dev)
+    out = out_base[:, :, :, ::2]
+    ops.upsample_bilinear2d(v, (7, 11), align, out=out)
+    assert torch.equal(out, ops.upsample_bilinear2d(v.contiguous(), (7, 11), align))
+    assert float(out_base[:, :, :, 1::2].abs().max()) == 0.0
