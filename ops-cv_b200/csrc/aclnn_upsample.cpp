@@ -182,15 +182,16 @@ aclnnStatus CheckNearestFwd(const char* api, const aclTensor* self, const aclInt
     return ACLNN_SUCCESS;
 }
 
-// An NCHW input view that the strided forward kernels can read in place: not contiguous (a contiguous one takes the
-// dense kernels), four dimensions in NCHW order, no negative stride.
-bool StridedNchwInput(const aclTensor* t, InStrides* st)
+// Strided NCHW views that the strided forward kernels address in place: four dimensions in NCHW order and no negative
+// stride (an output view must also not overlap itself: no zero stride on a dimension longer than 1). StridesOf fills
+// the strides of any such tensor, dense ones included.
+bool StridesOf(const aclTensor* t, bool output, InStrides* st)
 {
-    if (t->format == ACL_FORMAT_NHWC || t->dims.size() != 4 || t->strides.size() != 4 || IsContiguous(t)) {
+    if (t->format == ACL_FORMAT_NHWC || t->dims.size() != 4 || t->strides.size() != 4) {
         return false;
     }
-    for (int64_t v : t->strides) {
-        if (v < 0) {
+    for (size_t i = 0; i < 4; ++i) {
+        if (t->strides[i] < 0 || (output && t->strides[i] == 0 && t->dims[i] > 1)) {
             return false;
         }
     }
@@ -200,6 +201,16 @@ bool StridedNchwInput(const aclTensor* t, InStrides* st)
     st->w = t->strides[3];
     st->chan = static_cast<int32_t>(t->dims[1]);
     return true;
+}
+
+// True when the call should run on the strided kernels: at least one of the two tensors is a non-contiguous view and
+// both can be addressed through strides.
+bool UseStridedForward(const aclTensor* self, const aclTensor* out, InStrides* si, InStrides* so)
+{
+    if (IsContiguous(self) && IsContiguous(out)) {
+        return false;
+    }
+    return StridesOf(self, false, si) && StridesOf(out, true, so);
 }
 
 aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTensor* out, float userScaleH,
@@ -213,15 +224,16 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
     }
     WsPlan ws;
     const Geom gi = GeomOf(self), go = GeomOf(out);
-    InStrides st{};
-    const bool strided = StridedNchwInput(self, &st);
-    BufRef x;
-    if (strided) { // read through the view's strides: no gather copy
+    InStrides st{}, so{};
+    const bool strided = UseStridedForward(self, out, &st, &so);
+    BufRef x, y;
+    if (strided) { // read and written through the views' strides: no gather or scatter copy
         x.base = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
+        y.base = static_cast<char*>(out->data) + out->offset * ElemSize(out->dtype);
     } else {
         x = StageInput(self, ws, ex);
+        y = StageOutput(out, ws);
     }
-    const BufRef y = StageOutput(out, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
@@ -236,9 +248,8 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
             if (e != cudaSuccess) {
                 return e;
             }
-            return NearestFwdStrided(dt, x.At(w), st, y.At(w), sh, th, tw, s);
+            return NearestFwdStrided(dt, x.At(w), st, y.At(w), so, sh, th, tw, s);
         });
-        FinishOutput(out, y, ex);
         ex->workspaceSize = ws.Size();
         *workspaceSize = ws.Size();
         *executor = ex;
@@ -1091,15 +1102,16 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    InStrides st{};
-    const bool strided = StridedNchwInput(self, &st);
-    BufRef x;
-    if (strided) { // read through the view's strides: no gather copy
+    InStrides st{}, so{};
+    const bool strided = UseStridedForward(self, outT, &st, &so);
+    BufRef x, y;
+    if (strided) { // read and written through the views' strides: no gather or scatter copy
         x.base = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
+        y.base = static_cast<char*>(outT->data) + outT->offset * ElemSize(outT->dtype);
     } else {
         x = StageInput(self, ws, ex);
+        y = StageOutput(outT, ws);
     }
-    const BufRef y = StageOutput(outT, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
@@ -1115,9 +1127,8 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
             if (e != cudaSuccess) {
                 return e;
             }
-            return BilinearFwdStrided(dt, x.At(w), st, y.At(w), sh, th, tw, s);
+            return BilinearFwdStrided(dt, x.At(w), st, y.At(w), so, sh, th, tw, s);
         });
-        FinishOutput(outT, y, ex);
         ex->workspaceSize = ws.Size();
         *workspaceSize = ws.Size();
         *executor = ex;

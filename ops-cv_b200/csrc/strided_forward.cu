@@ -1,6 +1,9 @@
-// Nearest and bilinear forward on an NCHW input VIEW (any non-negative element strides: crops, steps, broadcast
-// batches) with a dense NCHW output: the kernels read the taps through the view's strides, so the gather copy that
-// would first make the input contiguous (a read and a write of the whole input, and a launch) is not needed. The
+// Nearest and bilinear forward on NCHW VIEWS (any non-negative element strides: crops, steps, channel slices of a
+// larger buffer, broadcast batches on the input side): the kernels read the taps and write the results through the
+// views' strides, so neither the gather copy that would first make the input contiguous nor the scatter copy that
+// would move a staged result into the output view (each a read and a write of a whole tensor, and a launch) is
+// needed. Packs of adjacent outputs are stored as one vector when the output's W stride is 1 and its other strides
+// and base keep the alignment; otherwise element by element. The
 // index tables and the arithmetic are those of the dense kernels: nearest is a copy; bilinear blends
 // (1 - dx) * v_lo + dx * v_hi per source row and then (1 - dy) * top + dy * bottom, every operation rounded on its
 // own (image/resize_bilinear_v2/op_kernel/arch35/resize_bilinear_v2_simt_nchw.h:84-146).
@@ -13,8 +16,8 @@ constexpr int kThreads = 256;
 
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
-    NearestFwdStridedKernel(const T* __restrict__ x, InStrides st, T* __restrict__ y, int32_t hout, int32_t wout,
-                            const int32_t* __restrict__ sh, const int32_t* __restrict__ sw, int64_t rows)
+    NearestFwdStridedKernel(const T* __restrict__ x, InStrides st, T* __restrict__ y, InStrides so, int32_t hout,
+                            int32_t wout, const int32_t* __restrict__ sh, const int32_t* __restrict__ sw, int64_t rows)
 {
     const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
     if (t0 >= wout) {
@@ -37,14 +40,19 @@ __global__ void __launch_bounds__(kThreads)
         for (int k = 0; k < V; ++k) {
             out.v[k] = __ldg(xr + off[k]);
         }
-        *reinterpret_cast<Pack<T, V>*>(y + row * wout + t0) = out;
+        T* yr = y + n * so.n + c * so.c + h * so.h + t0 * so.w;
+        if (V > 1) { // chosen only for a unit W stride
+            *reinterpret_cast<Pack<T, V>*>(yr) = out;
+        } else {
+            *yr = out.v[0];
+        }
     }
 }
 
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
-    BilinearFwdStridedKernel(const T* __restrict__ x, InStrides st, T* __restrict__ y, int32_t hout, int32_t wout,
-                             LerpAxis th, LerpAxis tw, int64_t rows)
+    BilinearFwdStridedKernel(const T* __restrict__ x, InStrides st, T* __restrict__ y, InStrides so, int32_t hout,
+                             int32_t wout, LerpAxis th, LerpAxis tw, int64_t rows)
 {
     const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
     if (t0 >= wout) {
@@ -77,23 +85,42 @@ __global__ void __launch_bounds__(kThreads)
             const float bot = Add(Mul(dx1[k], DType<T>::Load(r1 + ol[k])), Mul(dx[k], DType<T>::Load(r1 + oh[k])));
             out[k] = Add(Mul(dy1, top), Mul(dy, bot));
         }
-        StorePack<T, V>(y + row * wout + t0, out);
+        T* yr = y + n * so.n + c * so.c + h * so.h + t0 * so.w;
+        if (V > 1) {
+            StorePack<T, V>(yr, out);
+        } else {
+            *yr = DType<T>::FromF(out[0]);
+        }
     }
+}
+
+// Widest pack the output view allows: unit W stride, every other stride and the base aligned to the pack.
+int OutVec(int es, int32_t wout, const void* y, const InStrides& so)
+{
+    if (so.w != 1) {
+        return 1;
+    }
+    for (int v = 16 / es; v > 1; v >>= 1) {
+        if (wout % v == 0 && so.n % v == 0 && so.c % v == 0 && so.h % v == 0 && Aligned(y, static_cast<size_t>(v) * es)) {
+            return v;
+        }
+    }
+    return 1;
 }
 
 } // namespace
 
-cudaError_t NearestFwdStrided(Dt dt, const void* x, InStrides st, void* y, Shape4 sh, NearestAxis th, NearestAxis tw,
-                              cudaStream_t s)
+cudaError_t NearestFwdStrided(Dt dt, const void* x, InStrides st, void* y, InStrides so, Shape4 sh, NearestAxis th,
+                              NearestAxis tw, cudaStream_t s)
 {
     const int64_t rows = sh.n * sh.c * sh.hout;
-    const int v = PickVec(DtSize(dt), sh.wout, {y});
+    const int v = OutVec(DtSize(dt), sh.wout, y, so);
     const RowLaunch rl = RowTiling(rows, CeilDiv(static_cast<int64_t>(sh.wout), v), kThreads);
     OPSCV_DISPATCH_DT(dt, T, {
         OPSCV_DISPATCH_VEC(v, V, {
             if constexpr (V * sizeof(T) <= 16) {
                 NearestFwdStridedKernel<T, V><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(x), st, static_cast<T*>(y),
-                                                                           sh.hout, sh.wout, th.src, tw.src, rows);
+                                                                           so, sh.hout, sh.wout, th.src, tw.src, rows);
             }
         });
     });
@@ -101,17 +128,17 @@ cudaError_t NearestFwdStrided(Dt dt, const void* x, InStrides st, void* y, Shape
     return cudaGetLastError();
 }
 
-cudaError_t BilinearFwdStrided(Dt dt, const void* x, InStrides st, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
-                               cudaStream_t s)
+cudaError_t BilinearFwdStrided(Dt dt, const void* x, InStrides st, void* y, InStrides so, Shape4 sh, LerpAxis th,
+                               LerpAxis tw, cudaStream_t s)
 {
     const int64_t rows = sh.n * sh.c * sh.hout;
-    const int v = PickVec(DtSize(dt), sh.wout, {y});
+    const int v = OutVec(DtSize(dt), sh.wout, y, so);
     const RowLaunch rl = RowTiling(rows, CeilDiv(static_cast<int64_t>(sh.wout), v), kThreads);
     OPSCV_DISPATCH_DT(dt, T, {
         OPSCV_DISPATCH_VEC(v, V, {
             if constexpr (V * sizeof(T) <= 16) {
                 BilinearFwdStridedKernel<T, V><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(x), st, static_cast<T*>(y),
-                                                                            sh.hout, sh.wout, th, tw, rows);
+                                                                            so, sh.hout, sh.wout, th, tw, rows);
             }
         });
     });

@@ -106,10 +106,23 @@ def test_strided_nchw_inputs_are_read_in_place(ops, dev, dtype, align):
             got, count = _launches(ops, lambda: call(v))
             assert torch.equal(got, want), (name, op)
             assert count == 2, (name, op, count)
-    # down-scaling, a strided output view at the same time (the output still goes through its scatter copy)
+    # down-scaling with a strided output view at the same time (W stride 2: element stores)
     v = base[:, :, 1:19, 2:30]
     out_base = torch.zeros((3, 5, 7, 22), dtype=dtype, device=dev)
     out = out_base[:, :, :, ::2]
-    ops.upsample_bilinear2d(v, (7, 11), align, out=out)
+    _, count = _launches(ops, lambda: ops.upsample_bilinear2d(v, (7, 11), align, out=out))
+    assert count == 2
     assert torch.equal(out, ops.upsample_bilinear2d(v.contiguous(), (7, 11), align))
     assert float(out_base[:, :, :, 1::2].abs().max()) == 0.0
+    # a dense input written straight into a channel slice of a larger buffer (up-sample + concatenate): vector stores
+    x = base[:, :, :8, :16].contiguous()
+    cat = torch.full((3, 12, 16, 32), 7.0, dtype=dtype, device=dev)
+    for op, call in (("nearest", lambda o: ops.upsample_nearest2d(x, (16, 32), out=o)),
+                     ("bilinear", lambda o: ops.upsample_bilinear2d(x, (16, 32), align, out=o))):
+        cat.fill_(7.0)
+        _, count = _launches(ops, lambda: call(cat[:, 4:9]))
+        assert count == 2, (op, count)
+        assert torch.equal(cat[:, 4:9], call(None)), op
+        assert float((cat[:, :4] - 7.0).abs().max()) == 0.0 and float((cat[:, 9:] - 7.0).abs().max()) == 0.0
+    # an output view that overlaps itself is not written through strides (it takes the staged path, as before)
+    assert not torch.empty((1, 1, 1, 1), device=dev).expand(1, 1, 2, 2).is_contiguous()
