@@ -8,6 +8,7 @@
 #include <cstring>
 
 #include "host_common.h"
+#include "host_tables.h"
 
 using namespace opscv;
 
@@ -182,10 +183,9 @@ aclnnStatus CheckNearestFwd(const char* api, const aclTensor* self, const aclInt
     return ACLNN_SUCCESS;
 }
 
-// Strided NCHW views that the strided forward kernels address in place: four dimensions in NCHW order and no negative
-// stride (an output view must also not overlap itself: no zero stride on a dimension longer than 1). StridesOf fills
-// the strides of any such tensor, dense ones included.
-bool StridesOf(const aclTensor* t, bool output, InStrides* st)
+// Element strides of a four-dimensional NCHW view with no negative stride (an output view must also not overlap
+// itself: no zero stride on a dimension longer than 1).
+bool StridesOf(const aclTensor* t, bool output, ViewStrides* st)
 {
     if (t->format == ACL_FORMAT_NHWC || t->dims.size() != 4 || t->strides.size() != 4) {
         return false;
@@ -203,16 +203,6 @@ bool StridesOf(const aclTensor* t, bool output, InStrides* st)
     return true;
 }
 
-// True when the call should run on the strided kernels: at least one of the two tensors is a non-contiguous view and
-// both can be addressed through strides.
-bool UseStridedForward(const aclTensor* self, const aclTensor* out, InStrides* si, InStrides* so)
-{
-    if (IsContiguous(self) && IsContiguous(out)) {
-        return false;
-    }
-    return StridesOf(self, false, si) && StridesOf(out, true, so);
-}
-
 aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTensor* out, float userScaleH,
                            float userScaleW, uint64_t* workspaceSize, aclOpExecutor** executor, bool exact = false)
 {
@@ -224,37 +214,40 @@ aclnnStatus PlanNearestFwd(const char* api, const aclTensor* self, const aclTens
     }
     WsPlan ws;
     const Geom gi = GeomOf(self), go = GeomOf(out);
-    InStrides st{}, so{};
-    const bool strided = UseStridedForward(self, out, &st, &so);
-    BufRef x, y;
-    if (strided) { // read and written through the views' strides: no gather or scatter copy
-        x.base = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
-        y.base = static_cast<char*>(out->data) + out->offset * ElemSize(out->dtype);
-    } else {
-        x = StageInput(self, ws, ex);
-        y = StageOutput(out, ws);
-    }
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
     const AxisGeom ah{sh.hin, sh.hout, NearestScale(gi.h, go.h, userScaleH), exact ? 1 : 0};
     const AxisGeom aw{sh.win, sh.wout, NearestScale(gi.w, go.w, userScaleW), exact ? 1 : 0};
+    // A whole-number up-scale with a W factor of 2 between strided NCHW views (a crop or a channel slice on either
+    // side) runs on the replicate kernel with pitches: no gather copy, no scatter copy.
+    ViewStrides si{}, so{};
+    if ((!IsContiguous(self) || !IsContiguous(out)) && StridesOf(self, false, &si) && StridesOf(out, true, &so) &&
+        sh.wout == 2 * sh.win && sh.hout % sh.hin == 0) {
+        const int32_t rh = sh.hout / sh.hin;
+        const std::vector<int32_t> srcH = host::NearestSrc(sh.hin, sh.hout, ah.scale, exact);
+        const std::vector<int32_t> srcW = host::NearestSrc(sh.win, sh.wout, aw.scale, exact);
+        bool whole = true;
+        for (int32_t d = 0; d < sh.hout && whole; ++d) {
+            whole = srcH[d] == d / rh;
+        }
+        for (int32_t d = 0; d < sh.wout && whole; ++d) {
+            whole = srcW[d] == d / 2;
+        }
+        char* px = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
+        char* py = static_cast<char*>(out->data) + out->offset * ElemSize(out->dtype);
+        if (whole && NearestFwdX2PitchUsable(dt, px, si, py, so, sh)) {
+            ex->steps.push_back([=](char*, cudaStream_t s) { return NearestFwdX2Pitch(dt, px, si, py, so, sh, rh, s); });
+            ex->workspaceSize = 0;
+            *workspaceSize = 0;
+            *executor = ex;
+            return ACLNN_SUCCESS;
+        }
+    }
+    const BufRef x = StageInput(self, ws, ex);
+    const BufRef y = StageOutput(out, ws);
     const uint64_t offH = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.hout));
     const uint64_t offW = ws.Alloc(sizeof(int32_t) * static_cast<uint64_t>(sh.wout));
-    if (strided) {
-        ex->steps.push_back([=](char* w, cudaStream_t s) {
-            const NearestAxis th{reinterpret_cast<int32_t*>(w + offH)}, tw{reinterpret_cast<int32_t*>(w + offW)};
-            const cudaError_t e = BuildNearestFwdTables(ah, aw, th, tw, s);
-            if (e != cudaSuccess) {
-                return e;
-            }
-            return NearestFwdStrided(dt, x.At(w), st, y.At(w), so, sh, th, tw, s);
-        });
-        ex->workspaceSize = ws.Size();
-        *workspaceSize = ws.Size();
-        *executor = ex;
-        return ACLNN_SUCCESS;
-    }
     const NearestPlan plan = MakeNearestFwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const NearestAxis th{reinterpret_cast<int32_t*>(w + offH)}, tw{reinterpret_cast<int32_t*>(w + offW)};
@@ -1102,16 +1095,8 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    InStrides st{}, so{};
-    const bool strided = UseStridedForward(self, outT, &st, &so);
-    BufRef x, y;
-    if (strided) { // read and written through the views' strides: no gather or scatter copy
-        x.base = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
-        y.base = static_cast<char*>(outT->data) + outT->offset * ElemSize(outT->dtype);
-    } else {
-        x = StageInput(self, ws, ex);
-        y = StageOutput(outT, ws);
-    }
+    const BufRef x = StageInput(self, ws, ex);
+    const BufRef y = StageOutput(outT, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
@@ -1120,20 +1105,6 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     const AxisGeom aw{sh.win, sh.wout, BilinearScale(gi.w, go.w, alignCorners, static_cast<float>(scalesW))};
     const bool halfPixel = !alignCorners; // resize_bilinear_v2.cpp:99
     const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
-    if (strided) {
-        ex->steps.push_back([=](char* w, cudaStream_t s) {
-            const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
-            const cudaError_t e = BuildLerpTables(ah, aw, halfPixel, 0, th, tw, s);
-            if (e != cudaSuccess) {
-                return e;
-            }
-            return BilinearFwdStrided(dt, x.At(w), st, y.At(w), so, sh, th, tw, s);
-        });
-        ex->workspaceSize = ws.Size();
-        *workspaceSize = ws.Size();
-        *executor = ex;
-        return ACLNN_SUCCESS;
-    }
     const BilinearPlan plan = MakeBilinearFwdPlan(dt, lay, sh, ah, aw, halfPixel);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);

@@ -89,14 +89,16 @@ cudaError_t NearestFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Nea
                        const NearestPlan& plan, cudaStream_t s);
 cudaError_t NearestBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh, RangeAxis th, RangeAxis tw,
                        const NearestPlan& plan, cudaStream_t s);
-// Forward kernels that read an NCHW input view and write an NCHW output view through their element strides
-// (strided_forward.cu); st describes the input, so the output (a dense tensor has the strides of its extents).
-struct InStrides {
-    int64_t n, c, h, w; // element strides of the view's N, C, H, W dimensions (non-negative)
-    int32_t chan;       // C, to split a plane index into (n, c)
+// Element strides of an NCHW view (a dense tensor has the strides of its extents).
+struct ViewStrides {
+    int64_t n, c, h, w;
+    int32_t chan; // C, to split a plane index into (n, c)
 };
-cudaError_t NearestFwdStrided(Dt dt, const void* x, InStrides st, void* y, InStrides so, Shape4 sh, NearestAxis th,
-                              NearestAxis tw, cudaStream_t s);
+// Nearest forward for whole-number up-scales with a W factor of 2 on strided NCHW views with unit W strides
+// (strided_forward.cu): rh = the H factor. Usable() checks the strides and alignments the kernel needs.
+bool NearestFwdX2PitchUsable(Dt dt, const void* x, ViewStrides si, const void* y, ViewStrides so, Shape4 sh);
+cudaError_t NearestFwdX2Pitch(Dt dt, const void* x, ViewStrides si, void* y, ViewStrides so, Shape4 sh, int32_t rh,
+                              cudaStream_t s);
 struct BilinearPlan {
     enum Schedule : int32_t { kDirect = 0, kTiled = 1, kW2 = 2, kX2 = 3 }; // kX2: backward, 2x on both axes
     int32_t schedule;
@@ -126,8 +128,6 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
 // formula) unless the kernel it picks evaluates its own entries. false: the caller has built the tables.
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
                         const BilinearPlan& plan, cudaStream_t s, bool buildTables = false);
-cudaError_t BilinearFwdStrided(Dt dt, const void* x, InStrides st, void* y, InStrides so, Shape4 sh, LerpAxis th,
-                               LerpAxis tw, cudaStream_t s);
 // Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
 // buildTables: as for BilinearFwd, with the backward formula and the ranges.
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,

@@ -12,26 +12,63 @@ thread_local uint64_t g_launches = 0;
 
 constexpr int kThreads = 256;
 
-template <typename E>
+// One thread row of a block walks the rows (i0, i1, i2) of the view, whose offset is found once per row; a thread
+// moves V adjacent elements of the row (V > 1 only for a unit innermost stride with aligned rows).
+template <typename E, int V>
 __global__ void __launch_bounds__(kThreads)
-    StridedCopyKernel(E* __restrict__ contiguous, E* __restrict__ viewBase, View4 v, bool toView, int64_t total)
+    StridedCopyKernel(E* __restrict__ contiguous, E* __restrict__ viewBase, View4 v, bool toView, int64_t rows)
 {
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        int64_t r = idx;
-        const int64_t i3 = r % v.dim[3];
-        r /= v.dim[3];
-        const int64_t i2 = r % v.dim[2];
-        r /= v.dim[2];
-        const int64_t i1 = r % v.dim[1];
-        const int64_t i0 = r / v.dim[1];
-        const int64_t off = i0 * v.stride[0] + i1 * v.stride[1] + i2 * v.stride[2] + i3 * v.stride[3];
-        if (toView) {
-            viewBase[off] = contiguous[idx];
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+    if (t0 >= v.dim[3]) {
+        return;
+    }
+    const bool small = rows <= 0x7fffffffLL;
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rows; row += rowStep) {
+        int64_t i0, i1, i2;
+        if (small) { // 32-bit divisions (a row count below 2^31 bounds every extent)
+            const uint32_t r = static_cast<uint32_t>(row), d2 = static_cast<uint32_t>(v.dim[2]),
+                           d1 = static_cast<uint32_t>(v.dim[1]);
+            const uint32_t q = r / d2, p = q / d1;
+            i2 = r - q * d2;
+            i1 = q - p * d1;
+            i0 = p;
         } else {
-            contiguous[idx] = viewBase[off];
+            const int64_t q = row / v.dim[2];
+            i2 = row - q * v.dim[2];
+            i0 = q / v.dim[1];
+            i1 = q - i0 * v.dim[1];
+        }
+        E* pv = viewBase + i0 * v.stride[0] + i1 * v.stride[1] + i2 * v.stride[2] + t0 * v.stride[3];
+        E* pc = contiguous + row * v.dim[3] + t0;
+        if (toView) {
+            *reinterpret_cast<Pack<E, V>*>(pv) = *reinterpret_cast<const Pack<E, V>*>(pc);
+        } else {
+            *reinterpret_cast<Pack<E, V>*>(pc) = *reinterpret_cast<const Pack<E, V>*>(pv);
         }
     }
+}
+
+template <typename E>
+void LaunchStridedCopy(E* contiguous, E* viewBase, const View4& v, bool toView, cudaStream_t s)
+{
+    const int64_t rows = v.dim[0] * v.dim[1] * v.dim[2];
+    int vec = 1;
+    if (v.stride[3] == 1) {
+        for (int w = 16 / static_cast<int>(sizeof(E)); w > 1; w >>= 1) {
+            if (v.dim[3] % w == 0 && v.stride[0] % w == 0 && v.stride[1] % w == 0 && v.stride[2] % w == 0 &&
+                Aligned(contiguous, w * sizeof(E)) && Aligned(viewBase, w * sizeof(E))) {
+                vec = w;
+                break;
+            }
+        }
+    }
+    const RowLaunch rl = RowTiling(rows, CeilDiv(v.dim[3], static_cast<int64_t>(vec)), kThreads);
+    OPSCV_DISPATCH_VEC(vec, V, {
+        if constexpr (V * sizeof(E) <= 16) {
+            StridedCopyKernel<E, V><<<rl.grid, rl.block, 0, s>>>(contiguous, viewBase, v, toView, rows);
+        }
+    });
 }
 
 template <typename T>
@@ -83,11 +120,9 @@ cudaError_t StridedCopy(int elemSize, void* contiguous, void* viewBase, View4 v,
         return cudaSuccess;
     }
     if (elemSize == 4) {
-        StridedCopyKernel<uint32_t><<<GridFor(total, kThreads), kThreads, 0, s>>>(
-            static_cast<uint32_t*>(contiguous), static_cast<uint32_t*>(viewBase), v, toView, total);
+        LaunchStridedCopy<uint32_t>(static_cast<uint32_t*>(contiguous), static_cast<uint32_t*>(viewBase), v, toView, s);
     } else {
-        StridedCopyKernel<uint16_t><<<GridFor(total, kThreads), kThreads, 0, s>>>(
-            static_cast<uint16_t*>(contiguous), static_cast<uint16_t*>(viewBase), v, toView, total);
+        LaunchStridedCopy<uint16_t>(static_cast<uint16_t*>(contiguous), static_cast<uint16_t*>(viewBase), v, toView, s);
     }
     CountLaunch();
     return cudaGetLastError();

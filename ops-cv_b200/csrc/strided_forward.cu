@@ -1,12 +1,9 @@
-// Nearest and bilinear forward on NCHW VIEWS (any non-negative element strides: crops, steps, channel slices of a
-// larger buffer, broadcast batches on the input side): the kernels read the taps and write the results through the
-// views' strides, so neither the gather copy that would first make the input contiguous nor the scatter copy that
-// would move a staged result into the output view (each a read and a write of a whole tensor, and a launch) is
-// needed. Packs of adjacent outputs are stored as one vector when the output's W stride is 1 and its other strides
-// and base keep the alignment; otherwise element by element. The
-// index tables and the arithmetic are those of the dense kernels: nearest is a copy; bilinear blends
-// (1 - dx) * v_lo + dx * v_hi per source row and then (1 - dy) * top + dy * bottom, every operation rounded on its
-// own (image/resize_bilinear_v2/op_kernel/arch35/resize_bilinear_v2_simt_nchw.h:84-146).
+// UpsampleNearest2d / NearestExact2d forward on strided NCHW VIEWS for whole-number up-scales with a W factor of 2
+// (the common 2x up-sample): the input may be a crop or a channel slice of a larger tensor, the output a crop or a
+// channel slice of a larger buffer (an up-sample written straight into its place in a concatenation). Both views need
+// a unit W stride; the N, C and H strides are free. The kernel is the dense replicate kernel with pitches: a thread
+// loads VI adjacent input elements of a row once and stores the 2 * VI outputs they become into each of the rh output
+// rows, as one 32-byte store when the row pitch keeps that alignment. No gather copy, no scatter copy.
 #include "launch_util.cuh"
 
 namespace opscv {
@@ -14,131 +11,75 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <typename T, int V>
+template <typename T, int VI>
 __global__ void __launch_bounds__(kThreads)
-    NearestFwdStridedKernel(const T* __restrict__ x, InStrides st, T* __restrict__ y, InStrides so, int32_t hout,
-                            int32_t wout, const int32_t* __restrict__ sh, const int32_t* __restrict__ sw, int64_t rows)
+    NearestFwdX2PitchKernel(const T* __restrict__ x, ViewStrides si, T* __restrict__ y, ViewStrides so, int32_t hin,
+                            int32_t win, int32_t rh, int64_t rowsIn)
 {
-    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
-    if (t0 >= wout) {
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VI;
+    if (t0 >= win) {
         return;
     }
-    int64_t off[V];
-#pragma unroll
-    for (int k = 0; k < V; ++k) {
-        off[k] = __ldg(sw + t0 + k) * st.w;
-    }
-    const bool small = rows <= 0x7fffffffLL;
+    const bool small = rowsIn <= 0x7fffffffLL;
     const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
-    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rows; row += rowStep) {
-        int64_t n; // row = (n, c, h)
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rowsIn; row += rowStep) {
+        int64_t n; // row = (n, c, h) of the input
         int32_t c, h;
-        SplitRow(row, hout, st.chan, small, n, c, h);
-        const T* xr = x + n * st.n + c * st.c + __ldg(sh + h) * st.h;
-        Pack<T, V> out;
+        SplitRow(row, hin, si.chan, small, n, c, h);
+        const Pack<T, VI> in = *reinterpret_cast<const Pack<T, VI>*>(x + n * si.n + c * si.c + h * si.h + t0);
+        constexpr int H = (2 * VI * sizeof(T) > 16) ? VI : 2 * VI; // elements per 16-byte half of the outputs
+        Pack<T, H> out[2 * VI / H];
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-            out.v[k] = __ldg(xr + off[k]);
+        for (int v = 0; v < VI; ++v) {
+            out[(2 * v) / H].v[(2 * v) % H] = in.v[v];
+            out[(2 * v + 1) / H].v[(2 * v + 1) % H] = in.v[v];
         }
-        T* yr = y + n * so.n + c * so.c + h * so.h + t0 * so.w;
-        if (V > 1) { // chosen only for a unit W stride
-            *reinterpret_cast<Pack<T, V>*>(yr) = out;
-        } else {
-            *yr = out.v[0];
+        T* yr = y + n * so.n + c * so.c + static_cast<int64_t>(h) * rh * so.h + 2 * t0;
+        for (int32_t b = 0; b < rh; ++b, yr += so.h) {
+            if constexpr (2 * VI * sizeof(T) == 32) {
+                Store32Bytes(yr, reinterpret_cast<const uint4&>(out[0]), reinterpret_cast<const uint4&>(out[1]));
+            } else {
+                *reinterpret_cast<Pack<T, H>*>(yr) = out[0];
+            }
         }
     }
 }
 
-template <typename T, int V>
-__global__ void __launch_bounds__(kThreads)
-    BilinearFwdStridedKernel(const T* __restrict__ x, InStrides st, T* __restrict__ y, InStrides so, int32_t hout,
-                             int32_t wout, LerpAxis th, LerpAxis tw, int64_t rows)
+// Widest input pack: W extent, every pitch and both bases keep the alignment of the loads (VI elements) and of the
+// stores (2 * VI elements).
+int PitchVec(int es, int32_t win, const void* x, const ViewStrides& si, const void* y, const ViewStrides& so)
 {
-    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
-    if (t0 >= wout) {
-        return;
-    }
-    int64_t ol[V], oh[V];
-    float dx[V], dx1[V];
-#pragma unroll
-    for (int k = 0; k < V; ++k) {
-        ol[k] = __ldg(tw.lo + t0 + k) * st.w;
-        oh[k] = __ldg(tw.hi + t0 + k) * st.w;
-        dx[k] = __ldg(tw.delta + t0 + k);
-        dx1[k] = Sub(1.0f, dx[k]);
-    }
-    const bool small = rows <= 0x7fffffffLL;
-    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
-    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rows; row += rowStep) {
-        int64_t n;
-        int32_t c, h;
-        SplitRow(row, hout, st.chan, small, n, c, h);
-        const T* xp = x + n * st.n + c * st.c;
-        const T* r0 = xp + __ldg(th.lo + h) * st.h;
-        const T* r1 = xp + __ldg(th.hi + h) * st.h;
-        const float dy = __ldg(th.delta + h);
-        const float dy1 = Sub(1.0f, dy);
-        float out[V];
-#pragma unroll
-        for (int k = 0; k < V; ++k) {
-            const float top = Add(Mul(dx1[k], DType<T>::Load(r0 + ol[k])), Mul(dx[k], DType<T>::Load(r0 + oh[k])));
-            const float bot = Add(Mul(dx1[k], DType<T>::Load(r1 + ol[k])), Mul(dx[k], DType<T>::Load(r1 + oh[k])));
-            out[k] = Add(Mul(dy1, top), Mul(dy, bot));
-        }
-        T* yr = y + n * so.n + c * so.c + h * so.h + t0 * so.w;
-        if (V > 1) {
-            StorePack<T, V>(yr, out);
-        } else {
-            *yr = DType<T>::FromF(out[0]);
-        }
-    }
-}
-
-// Widest pack the output view allows: unit W stride, every other stride and the base aligned to the pack.
-int OutVec(int es, int32_t wout, const void* y, const InStrides& so)
-{
-    if (so.w != 1) {
-        return 1;
-    }
-    for (int v = 16 / es; v > 1; v >>= 1) {
-        if (wout % v == 0 && so.n % v == 0 && so.c % v == 0 && so.h % v == 0 && Aligned(y, static_cast<size_t>(v) * es)) {
+    for (int v = 16 / es; v >= 1; v >>= 1) {
+        const int64_t a = v, b = 2 * v;
+        if (win % a == 0 && si.n % a == 0 && si.c % a == 0 && si.h % a == 0 && Aligned(x, static_cast<size_t>(a) * es) &&
+            so.n % b == 0 && so.c % b == 0 && so.h % b == 0 && Aligned(y, static_cast<size_t>(b) * es)) {
             return v;
         }
     }
-    return 1;
+    return 0;
 }
 
 } // namespace
 
-cudaError_t NearestFwdStrided(Dt dt, const void* x, InStrides st, void* y, InStrides so, Shape4 sh, NearestAxis th,
-                              NearestAxis tw, cudaStream_t s)
+bool NearestFwdX2PitchUsable(Dt dt, const void* x, ViewStrides si, const void* y, ViewStrides so, Shape4 sh)
 {
-    const int64_t rows = sh.n * sh.c * sh.hout;
-    const int v = OutVec(DtSize(dt), sh.wout, y, so);
-    const RowLaunch rl = RowTiling(rows, CeilDiv(static_cast<int64_t>(sh.wout), v), kThreads);
-    OPSCV_DISPATCH_DT(dt, T, {
-        OPSCV_DISPATCH_VEC(v, V, {
-            if constexpr (V * sizeof(T) <= 16) {
-                NearestFwdStridedKernel<T, V><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(x), st, static_cast<T*>(y),
-                                                                           so, sh.hout, sh.wout, th.src, tw.src, rows);
-            }
-        });
-    });
-    CountLaunch();
-    return cudaGetLastError();
+    return si.w == 1 && so.w == 1 && PitchVec(DtSize(dt), sh.win, x, si, y, so) >= 1;
 }
 
-cudaError_t BilinearFwdStrided(Dt dt, const void* x, InStrides st, void* y, InStrides so, Shape4 sh, LerpAxis th,
-                               LerpAxis tw, cudaStream_t s)
+cudaError_t NearestFwdX2Pitch(Dt dt, const void* x, ViewStrides si, void* y, ViewStrides so, Shape4 sh, int32_t rh,
+                              cudaStream_t s)
 {
-    const int64_t rows = sh.n * sh.c * sh.hout;
-    const int v = OutVec(DtSize(dt), sh.wout, y, so);
-    const RowLaunch rl = RowTiling(rows, CeilDiv(static_cast<int64_t>(sh.wout), v), kThreads);
+    const int vi = PitchVec(DtSize(dt), sh.win, x, si, y, so);
+    if (vi < 1) {
+        return cudaErrorInvalidValue;
+    }
+    const int64_t rowsIn = sh.n * sh.c * sh.hin;
+    const RowLaunch rl = RowTiling(rowsIn, CeilDiv(static_cast<int64_t>(sh.win), vi), kThreads);
     OPSCV_DISPATCH_DT(dt, T, {
-        OPSCV_DISPATCH_VEC(v, V, {
-            if constexpr (V * sizeof(T) <= 16) {
-                BilinearFwdStridedKernel<T, V><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(x), st, static_cast<T*>(y),
-                                                                            so, sh.hout, sh.wout, th, tw, rows);
+        OPSCV_DISPATCH_VEC(vi, VI, {
+            if constexpr (VI * sizeof(T) <= 16) {
+                NearestFwdX2PitchKernel<T, VI><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(x), si, static_cast<T*>(y),
+                                                                            so, sh.hin, sh.win, rh, rowsIn);
             }
         });
     });

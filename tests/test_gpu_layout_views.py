@@ -83,46 +83,46 @@ def test_mixed_layouts_still_go_through_staging(ops, dev):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("align", [False, True])
-def test_strided_nchw_inputs_are_read_in_place(ops, dev, dtype, align):
-    """Crops, steps and broadcast batches of an NCHW tensor feed the nearest and bilinear forwards through their
-    strides: the bits of the call on a contiguous copy, and one launch less than the path through the gather copy
-    (two kernels: the table builder and the resampler)."""
-    base = torch.randn((3, 5, 20, 31), generator=gen(92)).to(dtype).to(dev)
+def test_strided_nchw_views(ops, dev, dtype, align):
+    """Crops, steps, channel slices and broadcast batches on either side of the forwards give the bits of the call on
+    contiguous copies. A 2x nearest up-sample between views with unit W strides runs on the replicate kernel with
+    pitches (one launch: no gather copy, no table builder, no scatter copy); everything else goes through the
+    staging copies."""
+    base = torch.randn((3, 6, 20, 32), generator=gen(92)).to(dtype).to(dev)
     views = {
-        "crop": base[:, 1:4, 2:17, 3:28],
+        "crop": base[:, 1:4, 2:17, 8:24],
         "step": base[::2, :, ::2, 1::3],
-        "broadcast": base[:1, :, 4:12, 5:17].expand(4, 5, 8, 12),
+        "broadcast": base[:1, :, 4:12, 8:24].expand(4, 6, 8, 16),
         "channel slice": base[:, ::2],
     }
     for name, v in views.items():
         assert not v.is_contiguous()
-        ho, wo = v.shape[2] * 2 + 1, v.shape[3] * 2 - 1
         dense = v.contiguous()
-        for op, call in (("nearest", lambda t: ops.upsample_nearest2d(t, (ho, wo))),
-                         ("nearest_exact", lambda t: ops.upsample_nearest_exact2d(t, (ho, wo))),
-                         ("bilinear", lambda t: ops.upsample_bilinear2d(t, (ho, wo), align)),
-                         ("resize", lambda t: ops.resize(t, (1.0, 1.0, 2.0, 2.0), "bilinear"))):
-            want, _ = _launches(ops, lambda: call(dense))
-            got, count = _launches(ops, lambda: call(v))
-            assert torch.equal(got, want), (name, op)
-            assert count == 2, (name, op, count)
-    # down-scaling with a strided output view at the same time (W stride 2: element stores)
+        for ho, wo in ((v.shape[2] * 2, v.shape[3] * 2), (v.shape[2] * 3, v.shape[3] * 2),
+                       (v.shape[2] * 2 + 1, v.shape[3] * 2 - 1)):
+            for op, call in (("nearest", lambda t: ops.upsample_nearest2d(t, (ho, wo))),
+                             ("nearest_exact", lambda t: ops.upsample_nearest_exact2d(t, (ho, wo))),
+                             ("bilinear", lambda t: ops.upsample_bilinear2d(t, (ho, wo), align))):
+                want = call(dense)
+                got, count = _launches(ops, lambda: call(v))
+                assert torch.equal(got, want), (name, op, ho, wo)
+                pitched = op != "bilinear" and wo == 2 * v.shape[3] and ho % v.shape[2] == 0 and v.stride(3) == 1
+                assert (count == 1) == pitched, (name, op, ho, wo, count)
+    # an up-sample written straight into a channel slice of a larger buffer (up-sample + concatenate)
+    x = base[:, :5, :8, :16].contiguous()
+    cat = torch.full((3, 12, 16, 32), 7.0, dtype=dtype, device=dev)
+    for op, call, one in (("nearest", lambda t, o: ops.upsample_nearest2d(t, (16, 32), out=o), True),
+                          ("bilinear", lambda t, o: ops.upsample_bilinear2d(t, (16, 32), align, out=o), False)):
+        for src in (x, base[:, :5, 3:11, 16:32]):   # dense input, cropped input
+            cat.fill_(7.0)
+            _, count = _launches(ops, lambda: call(src, cat[:, 4:9]))
+            assert (count == 1) == one, (op, count)
+            assert torch.equal(cat[:, 4:9], call(src.contiguous(), None)), op
+            assert float((cat[:, :4] - 7.0).abs().max()) == 0.0 and float((cat[:, 9:] - 7.0).abs().max()) == 0.0
+    # down-scaling into a view with a W stride of 2
     v = base[:, :, 1:19, 2:30]
-    out_base = torch.zeros((3, 5, 7, 22), dtype=dtype, device=dev)
+    out_base = torch.zeros((3, 6, 7, 22), dtype=dtype, device=dev)
     out = out_base[:, :, :, ::2]
-    _, count = _launches(ops, lambda: ops.upsample_bilinear2d(v, (7, 11), align, out=out))
-    assert count == 2
+    ops.upsample_bilinear2d(v, (7, 11), align, out=out)
     assert torch.equal(out, ops.upsample_bilinear2d(v.contiguous(), (7, 11), align))
     assert float(out_base[:, :, :, 1::2].abs().max()) == 0.0
-    # a dense input written straight into a channel slice of a larger buffer (up-sample + concatenate): vector stores
-    x = base[:, :, :8, :16].contiguous()
-    cat = torch.full((3, 12, 16, 32), 7.0, dtype=dtype, device=dev)
-    for op, call in (("nearest", lambda o: ops.upsample_nearest2d(x, (16, 32), out=o)),
-                     ("bilinear", lambda o: ops.upsample_bilinear2d(x, (16, 32), align, out=o))):
-        cat.fill_(7.0)
-        _, count = _launches(ops, lambda: call(cat[:, 4:9]))
-        assert count == 2, (op, count)
-        assert torch.equal(cat[:, 4:9], call(None)), op
-        assert float((cat[:, :4] - 7.0).abs().max()) == 0.0 and float((cat[:, 9:] - 7.0).abs().max()) == 0.0
-    # an output view that overlaps itself is not written through strides (it takes the staged path, as before)
-    assert not torch.empty((1, 1, 1, 1), device=dev).expand(1, 1, 2, 2).is_contiguous()
