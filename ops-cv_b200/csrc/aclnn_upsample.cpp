@@ -1096,7 +1096,6 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     }
     WsPlan ws;
     const BufRef x = StageInput(self, ws, ex);
-    const BufRef y = StageOutput(outT, ws);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
@@ -1106,6 +1105,24 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     const bool halfPixel = !alignCorners; // resize_bilinear_v2.cpp:99
     const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
     const BilinearPlan plan = MakeBilinearFwdPlan(dt, lay, sh, ah, aw, halfPixel);
+    // An output that is a pitched NCHW view (a crop or a channel slice of a larger buffer, unit W stride) is written in
+    // place by the 2x-width kernel: no staged result, no scatter copy. The input must already be in place too (the
+    // check needs its address).
+    ViewStrides so{};
+    if (!IsContiguous(outT) && !x.inWs && StridesOf(outT, true, &so)) {
+        char* py = static_cast<char*>(outT->data) + outT->offset * ElemSize(outT->dtype);
+        if (BilinearFwdTakesPitch(dt, lay, x.base, py, sh, plan, so)) {
+            ex->steps.push_back([=](char* w, cudaStream_t s) {
+                const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
+                return BilinearFwd(dt, lay, x.At(w), py, sh, th, tw, plan, s, true, &so);
+            });
+            ex->workspaceSize = ws.Size();
+            *workspaceSize = ws.Size();
+            *executor = ex;
+            return ACLNN_SUCCESS;
+        }
+    }
+    const BufRef y = StageOutput(outT, ws);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
         return BilinearFwd(dt, lay, x.At(w), y.At(w), sh, th, tw, plan, s, true); // builds the tables if it reads them

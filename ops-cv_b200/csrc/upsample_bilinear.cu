@@ -268,7 +268,7 @@ template <typename T, int VI, bool QUEUE, bool PERIODIC, bool FUSE = false>
 __global__ void __launch_bounds__(kW2Threads, 5)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores, float dxFirst,
-                        float dxEven, float dxOdd, AxisGeom geomH, int32_t halfPixel)
+                        float dxEven, float dxOdd, AxisGeom geomH, int32_t halfPixel, ViewStrides outPitch)
 {
     constexpr int VO = 2 * VI;
     constexpr int HE = 4 / sizeof(T); // elements in a 4-byte neighbour word
@@ -326,7 +326,9 @@ __global__ void __launch_bounds__(kW2Threads, 5)
     const int32_t groups = win / VI;
     const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
     const T* xp = x + p * hin * static_cast<int64_t>(win);
-    T* yp = y + p * hout * static_cast<int64_t>(wout);
+    // the output may be a view with N, C and H pitches (a dense tensor has those of its extents); its W stride is 1
+    const int64_t pn = p / outPitch.chan;
+    T* yp = y + pn * outPitch.n + (p - pn * outPitch.chan) * outPitch.c;
     for (int32_t g = cg0; g < groups; g += colThreads) {
         const int32_t c0 = g * VI;
         const int32_t cl = max(c0 - 1, 0), cr = min(c0 + VI, win - 1);
@@ -432,7 +434,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         // `up` as the upper and `dn` as the lower buffer and returns true when the two have traded places.
         float bufA[VO], bufB[VO];
         int32_t curTop = -1, curBot = -1;
-        T* dst = yp + static_cast<int64_t>(ha) * wout + c0 * 2;
+        T* dst = yp + static_cast<int64_t>(ha) * outPitch.h + c0 * 2;
         auto step = [&](int32_t h, float (&up)[VO], float (&dn)[VO]) -> bool {
             int32_t lo, hi;
             float dy;
@@ -449,7 +451,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                 }
                 curBot = hi;
                 BlendStore<T, VO>(dst, dn, up, dy, wideStores != 0);
-                dst += wout;
+                dst += outPitch.h;
                 return true;
             }
             if (lo != curTop) {
@@ -468,7 +470,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                 curBot = hi;
             }
             BlendStore<T, VO>(dst, up, dn, dy, wideStores != 0);
-            dst += wout;
+            dst += outPitch.h;
             return false;
         };
         bool traded = false; // false: bufA is the upper row
@@ -1698,10 +1700,28 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
     return plan;
 }
 
+bool BilinearFwdTakesPitch(Dt dt, Layout lay, const void* x, const void* y, Shape4 sh, const BilinearPlan& plan,
+                           const ViewStrides& out)
+{
+    const size_t es = static_cast<size_t>(DtSize(dt));
+    // the conditions of the 2x-width kernel below, with the view's pitches in place of the dense ones
+    return lay == kNCHW && plan.schedule == BilinearPlan::kW2 && out.w == 1 && Aligned(x, 4 * es) && Aligned(y, 16) &&
+           (sh.wout * es) % 16 == 0 && (out.n * es) % 16 == 0 && (out.c * es) % 16 == 0 && (out.h * es) % 16 == 0;
+}
+
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
-                        const BilinearPlan& plan, cudaStream_t s, bool buildTables)
+                        const BilinearPlan& plan, cudaStream_t s, bool buildTables, const ViewStrides* outPitch)
 {
     const int64_t planes = sh.n * sh.c;
+    ViewStrides op; // dense output unless the caller passes a view (only with BilinearFwdTakesPitch)
+    op.n = sh.c * static_cast<int64_t>(sh.hout) * sh.wout;
+    op.c = static_cast<int64_t>(sh.hout) * sh.wout;
+    op.h = sh.wout;
+    op.w = 1;
+    op.chan = static_cast<int32_t>(sh.c);
+    if (outPitch != nullptr) {
+        op = *outPitch;
+    }
     // buildTables: th / tw are still empty; they are filled here (from the geometry in the plan) unless the kernel
     // chosen below evaluates the entries it needs itself
     bool tablesBuilt = !buildTables;
@@ -1733,7 +1753,9 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                 const int64_t totalRows = CeilDiv(planes, block.y) * sh.hout;
                 // a thread writes 2 * vi elements per row; when that is 32 bytes and the rows are 32-byte aligned
                 // they go out as one 32-byte store
-                const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0) ? 1 : 0;
+                const int32_t wide = (2 * vi * sizeof(T) == 32 && Aligned(y, 32) && (sh.wout * sizeof(T)) % 32 == 0 &&
+                                      (op.n * sizeof(T)) % 32 == 0 && (op.c * sizeof(T)) % 32 == 0 &&
+                                      (op.h * sizeof(T)) % 32 == 0) ? 1 : 0;
                 // 16-byte pieces (fp32 x 4, 16-bit x 8) stream through the per-thread queue
                 const size_t qBytes = static_cast<size_t>(kW2QueueDepth) * block.x * block.y * 24;
                 auto launch = [&](auto kernel, size_t smem, bool periodic) {
@@ -1752,7 +1774,7 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                         1, std::min<int64_t>(static_cast<int64_t>(NumSMs()) * perSm, totalRows / 8))));
                     kernel<<<grid, block, smem, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide,
                                                      plan.dxFirst, plan.dxEven, plan.dxOdd, plan.geomH,
-                                                     plan.halfPixel ? 1 : 0);
+                                                     plan.halfPixel ? 1 : 0, op);
                 };
                 if (vi == 8) {
                     if constexpr (sizeof(T) == 2) {
