@@ -695,13 +695,39 @@ static aclnnStatus PlanNearestBwd(const char* api, const aclTensor* gradOut, acl
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    const BufRef g = StageInput(gradOut, ws, ex);
-    const BufRef y = StageOutput(gradInput, ws);
     const Shape4 sh = MakeShape(gi, gg);
     const Dt dt = ToDt(gradOut->dtype);
     const Layout lay = gradOut->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
     const AxisGeom ah{sh.hin, sh.hout, scaleH, exact ? 1 : 0};
     const AxisGeom aw{sh.win, sh.wout, scaleW, exact ? 1 : 0};
+    // Whole-number windows (rh x 2) between strided NCHW views with unit W strides: the pool kernel with pitches, no
+    // gather or scatter copy (grad_output as a channel slice of the gradient of a concatenation is the typical case).
+    ViewStrides big{}, small{};
+    if ((!IsContiguous(gradOut) || !IsContiguous(gradInput)) && gradOut->dtype == gradInput->dtype &&
+        StridesOf(gradOut, false, &big) && StridesOf(gradInput, true, &small) && sh.wout == 2 * sh.win &&
+        sh.hout % sh.hin == 0) {
+        const int32_t fh = sh.hout / sh.hin;
+        const host::Ranges wh = host::NearestBwdRanges(sh.hin, sh.hout, ah.scale, exact);
+        const host::Ranges ww = host::NearestBwdRanges(sh.win, sh.wout, aw.scale, exact);
+        bool whole = true;
+        for (int32_t i = 0; i < sh.hin && whole; ++i) {
+            whole = wh.start[i] == i * fh && wh.end[i] == (i + 1) * fh;
+        }
+        for (int32_t i = 0; i < sh.win && whole; ++i) {
+            whole = ww.start[i] == 2 * i && ww.end[i] == 2 * i + 2;
+        }
+        char* pg = static_cast<char*>(gradOut->data) + gradOut->offset * ElemSize(gradOut->dtype);
+        char* pi = static_cast<char*>(gradInput->data) + gradInput->offset * ElemSize(gradInput->dtype);
+        if (whole && NearestBwdX2PitchUsable(dt, pg, big, pi, small, sh)) {
+            ex->steps.push_back([=](char*, cudaStream_t s) { return NearestBwdX2Pitch(dt, pg, big, pi, small, sh, fh, s); });
+            ex->workspaceSize = 0;
+            *workspaceSize = 0;
+            *executor = ex;
+            return ACLNN_SUCCESS;
+        }
+    }
+    const BufRef g = StageInput(gradOut, ws, ex);
+    const BufRef y = StageOutput(gradInput, ws);
     const RangeOffsets rh = AllocRange(ws, sh.hin), rw = AllocRange(ws, sh.win);
     const NearestPlan plan = MakeNearestBwdPlan(dt, lay, sh, ah, aw);
     ex->steps.push_back([=](char* w, cudaStream_t s) {

@@ -99,6 +99,10 @@ struct ViewStrides {
 bool NearestFwdX2PitchUsable(Dt dt, const void* x, ViewStrides si, const void* y, ViewStrides so, Shape4 sh);
 cudaError_t NearestFwdX2Pitch(Dt dt, const void* x, ViewStrides si, void* y, ViewStrides so, Shape4 sh, int32_t rh,
                               cudaStream_t s);
+// The matching backward (rh x 2 window sums): `big` describes grad_output, `small_` grad_input.
+bool NearestBwdX2PitchUsable(Dt dt, const void* go, ViewStrides big, const void* gi, ViewStrides small_, Shape4 sh);
+cudaError_t NearestBwdX2Pitch(Dt dt, const void* go, ViewStrides big, void* gi, ViewStrides small_, Shape4 sh, int32_t rh,
+                              cudaStream_t s);
 struct BilinearPlan {
     enum Schedule : int32_t { kDirect = 0, kTiled = 1, kW2 = 2, kX2 = 3 }; // kX2: backward, 2x on both axes
     int32_t schedule;

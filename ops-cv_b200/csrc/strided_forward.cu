@@ -4,6 +4,8 @@
 // a unit W stride; the N, C and H strides are free. The kernel is the dense replicate kernel with pitches: a thread
 // loads VI adjacent input elements of a row once and stores the 2 * VI outputs they become into each of the rh output
 // rows, as one 32-byte store when the row pitch keeps that alignment. No gather copy, no scatter copy.
+#include <algorithm>
+
 #include "launch_util.cuh"
 
 namespace opscv {
@@ -45,6 +47,47 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// The matching backward: grad_input (n, c, h, w) = sum of the rh x 2 window of grad_output, rows outer, columns inner,
+// in fp32 (the order of the dense pool kernel and of the reference). grad_output may be a channel slice of the
+// gradient of a concatenation, grad_input a slice or crop of a larger gradient buffer. Sides swapped: `big` is
+// grad_output (2 * VO elements per thread and row), `small` is grad_input (VO elements).
+template <typename T, int VO>
+__global__ void __launch_bounds__(kThreads)
+    NearestBwdX2PitchKernel(const T* __restrict__ go, ViewStrides big, T* __restrict__ gi, ViewStrides small_, int32_t hin,
+                            int32_t win, int32_t rh, int64_t rowsIn)
+{
+    const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VO;
+    if (t0 >= win) {
+        return;
+    }
+    const bool small = rowsIn <= 0x7fffffffLL;
+    const int64_t rowStep = static_cast<int64_t>(gridDim.y) * blockDim.y;
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < rowsIn; row += rowStep) {
+        int64_t n; // row = (n, c, h) of grad_input
+        int32_t c, h;
+        SplitRow(row, hin, small_.chan, small, n, c, h);
+        float acc[VO];
+#pragma unroll
+        for (int v = 0; v < VO; ++v) {
+            acc[v] = 0.0f;
+        }
+        const T* gr = go + n * big.n + c * big.c + static_cast<int64_t>(h) * rh * big.h + 2 * t0;
+        for (int32_t b = 0; b < rh; ++b, gr += big.h) {
+            constexpr int H = (2 * VO * sizeof(T) > 16) ? VO : 2 * VO; // elements per 16-byte load
+#pragma unroll
+            for (int part = 0; part < 2 * VO / H; ++part) {
+                float gv[H];
+                LoadPackLdg<T, H>(gr + part * H, gv);
+#pragma unroll
+                for (int v = 0; v < H / 2; ++v) {
+                    acc[part * (H / 2) + v] = Add(Add(acc[part * (H / 2) + v], gv[2 * v]), gv[2 * v + 1]);
+                }
+            }
+        }
+        StorePack<T, VO>(gi + n * small_.n + c * small_.c + h * small_.h + t0, acc);
+    }
+}
+
 // Widest input pack: W extent, every pitch and both bases keep the alignment of the loads (VI elements) and of the
 // stores (2 * VI elements).
 int PitchVec(int es, int32_t win, const void* x, const ViewStrides& si, const void* y, const ViewStrides& so)
@@ -80,6 +123,47 @@ cudaError_t NearestFwdX2Pitch(Dt dt, const void* x, ViewStrides si, void* y, Vie
             if constexpr (VI * sizeof(T) <= 16) {
                 NearestFwdX2PitchKernel<T, VI><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(x), si, static_cast<T*>(y),
                                                                             so, sh.hin, sh.win, rh, rowsIn);
+            }
+        });
+    });
+    CountLaunch();
+    return cudaGetLastError();
+}
+
+} // namespace opscv
+
+namespace opscv {
+
+bool NearestBwdX2PitchUsable(Dt dt, const void* go, ViewStrides big, const void* gi, ViewStrides small_, Shape4 sh)
+{
+    // the same alignment rule with the sides swapped: grad_input takes the role of the forward's input
+    return big.w == 1 && small_.w == 1 && NearestFwdX2PitchUsable(dt, gi, small_, go, big, sh);
+}
+
+cudaError_t NearestBwdX2Pitch(Dt dt, const void* go, ViewStrides big, void* gi, ViewStrides small_, Shape4 sh, int32_t rh,
+                              cudaStream_t s)
+{
+    const int es = DtSize(dt);
+    int vo = 0;
+    for (int v = 16 / es; v >= 1; v >>= 1) {
+        const int64_t a = v, b = std::min<int64_t>(2 * v, 16 / es); // loads are at most 16 bytes each
+        if (sh.win % a == 0 && small_.n % a == 0 && small_.c % a == 0 && small_.h % a == 0 &&
+            Aligned(gi, static_cast<size_t>(a) * es) && big.n % b == 0 && big.c % b == 0 && big.h % b == 0 &&
+            Aligned(go, static_cast<size_t>(b) * es)) {
+            vo = v;
+            break;
+        }
+    }
+    if (vo < 1) {
+        return cudaErrorInvalidValue;
+    }
+    const int64_t rowsIn = sh.n * sh.c * sh.hin;
+    const RowLaunch rl = RowTiling(rowsIn, CeilDiv(static_cast<int64_t>(sh.win), vo), 256);
+    OPSCV_DISPATCH_DT(dt, T, {
+        OPSCV_DISPATCH_VEC(vo, VO, {
+            if constexpr (VO * sizeof(T) <= 16) {
+                NearestBwdX2PitchKernel<T, VO><<<rl.grid, rl.block, 0, s>>>(static_cast<const T*>(go), big, static_cast<T*>(gi),
+                                                                            small_, sh.hin, sh.win, rh, rowsIn);
             }
         });
     });

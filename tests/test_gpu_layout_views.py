@@ -130,3 +130,25 @@ def test_strided_nchw_views(ops, dev, dtype, align):
     ops.upsample_bilinear2d(v, (7, 11), align, out=out)
     assert torch.equal(out, ops.upsample_bilinear2d(v.contiguous(), (7, 11), align))
     assert float(out_base[:, :, :, 1::2].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_nearest_backward_between_pitched_views(ops, dev, dtype):
+    """grad_output as a channel slice of the gradient of a concatenation, grad_input as a crop of a larger buffer:
+    the 2x pool kernel with pitches gives the bits of the dense call in one launch."""
+    cat_grad = torch.randn((3, 12, 16, 32), generator=gen(93)).to(dtype).to(dev)
+    g = cat_grad[:, 4:9]
+    assert not g.is_contiguous()
+    for exact, call in ((False, ops.upsample_nearest2d_backward), (True, ops.upsample_nearest_exact2d_backward)):
+        for hin in (8, 4):   # H factors 2 and 4
+            want = call(g.contiguous(), (16, 32), (3, 5, hin, 16))
+            got, count = _launches(ops, lambda: call(g, (16, 32), (3, 5, hin, 16)))
+            assert torch.equal(got, want) and count == 1, (exact, hin, count)
+            buf = torch.full((3, 5, hin + 2, 24), 5.0, dtype=dtype, device=dev)
+            _, count = _launches(ops, lambda: call(g, (16, 32), (3, 5, hin, 16), out=buf[:, :, 1:1 + hin, 8:24]))
+            assert count == 1
+            assert torch.equal(buf[:, :, 1:1 + hin, 8:24], want)
+            assert float((buf[:, :, 0] - 5.0).abs().max()) == 0.0 and float((buf[:, :, :, :8] - 5.0).abs().max()) == 0.0
+    # a ragged size goes through the staging copies and still matches
+    want = ops.upsample_nearest2d_backward(g.contiguous(), (16, 32), (3, 5, 7, 13))
+    assert torch.equal(ops.upsample_nearest2d_backward(g, (16, 32), (3, 5, 7, 13)), want)
