@@ -420,18 +420,34 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    const BufRef g = StageInput(gradOut, ws, ex);
-    const BufRef y = StageOutput(out, ws);
     Shape4 sh = MakeShape(gi, gg); // hin/win = grad_input extent, hout/wout = grads extent
     const Dt dtIn = ToDt(gradOut->dtype), dtOut = ToDt(out->dtype);
     const Layout lay = gradOut->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
     const AxisGeom ah{sh.hin, sh.hout, BilinearGradScale(gi.h, gg.h, alignCorners, static_cast<float>(scalesH))};
     const AxisGeom aw{sh.win, sh.wout, BilinearGradScale(gi.w, gg.w, alignCorners, static_cast<float>(scalesW))};
     const bool halfPixel = !alignCorners;
-    const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
     // The atomic scatter is used only on request (opscvSetBackwardAlgo(1)) and never in deterministic mode or
     // when the output dtype differs (the reference's IsMatchSimtDetermine, ..._grad_tiling_arch35.cpp:296-299).
     const bool atomic = GetBackwardAlgo() == 1 && GetDeterministic() == 0 && dtIn == dtOut;
+    // A grad_output that is a pitched NCHW view (a channel slice of the gradient of a concatenation, unit W stride) is
+    // read in place by the 2x gather kernel when grad_input is written in place too: no gather copy.
+    ViewStrides gradsPitch{};
+    bool pitched = false;
+    if (!atomic && !IsContiguous(gradOut) && IsContiguous(out) && StridesOf(gradOut, false, &gradsPitch)) {
+        const BilinearPlan probe = MakeBilinearBwdPlan(dtIn, lay, sh, ah, aw, halfPixel);
+        pitched = BilinearBwdTakesPitch(dtIn, dtOut, lay,
+                                        static_cast<char*>(gradOut->data) + gradOut->offset * ElemSize(gradOut->dtype),
+                                        static_cast<char*>(out->data) + out->offset * ElemSize(out->dtype), sh, probe,
+                                        gradsPitch);
+    }
+    BufRef g;
+    if (pitched) {
+        g.base = static_cast<char*>(gradOut->data) + gradOut->offset * ElemSize(gradOut->dtype);
+    } else {
+        g = StageInput(gradOut, ws, ex);
+    }
+    const BufRef y = StageOutput(out, ws);
+    const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
     if (atomic) {
         const int64_t elems = gi.n * gi.c * gi.h * gi.w;
         const bool needAcc = dtOut != Dt::F32;
@@ -452,7 +468,8 @@ aclnnStatus PlanBilinearBwd(const char* api, const aclTensor* gradOut, const acl
             const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
             const RangeAxis qh = RangeAt(w, rh), qw = RangeAt(w, rw);
             // builds the tables and ranges if the kernel it picks reads them
-            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, plan, s, true);
+            return BilinearBwdGather(dtIn, dtOut, lay, g.At(w), y.At(w), sh, th, tw, qh, qw, plan, s, true,
+                                     pitched ? &gradsPitch : nullptr);
         });
     }
     FinishOutput(out, y, ex);

@@ -139,9 +139,13 @@ bool BilinearFwdTakesPitch(Dt dt, Layout lay, const void* x, const void* y, Shap
                            const ViewStrides& out);
 // Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
 // buildTables: as for BilinearFwd, with the backward formula and the ranges.
+// gradsPitch: grad_output is an NCHW view with these N, C and H pitches and a unit W stride; only where
+// BilinearBwdTakesPitch says the kernel the plan selects takes pitches (the 2x kernel does).
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
                               LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s,
-                              bool buildTables = false);
+                              bool buildTables = false, const ViewStrides* gradsPitch = nullptr);
+bool BilinearBwdTakesPitch(Dt dtIn, Dt dtOut, Layout lay, const void* go, const void* gi, Shape4 sh,
+                           const BilinearPlan& plan, const ViewStrides& grads);
 // Scatter backward with fp32 atomics into `acc` (fp32, N*C*hin*win, zeroed by this call). If dtOut is fp32 the
 // caller passes acc == gi; otherwise a cast pass writes gi.
 cudaError_t BilinearBwdAtomic(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, float* acc, Shape4 sh,

@@ -264,7 +264,9 @@ constexpr int kW2Threads = 128;
 
 // FUSE (with PERIODIC, 16-bit T): the host has checked that every column weight times any value of T is exact in
 // fp32, so the horizontal interpolation may use one fused multiply-add: same bits, one instruction fewer.
-template <typename T, int VI, bool QUEUE, bool PERIODIC, bool FUSE = false>
+// PITCH: the output is a view addressed through outPitch (N, C, H pitches); otherwise the dense expressions are kept
+// as they were, so that the dense kernel's code does not change.
+template <typename T, int VI, bool QUEUE, bool PERIODIC, bool FUSE = false, bool PITCH = false>
 __global__ void __launch_bounds__(kW2Threads, 5)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores, float dxFirst,
@@ -327,8 +329,9 @@ __global__ void __launch_bounds__(kW2Threads, 5)
     const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
     const T* xp = x + p * hin * static_cast<int64_t>(win);
     // the output may be a view with N, C and H pitches (a dense tensor has those of its extents); its W stride is 1
-    const int64_t pn = p / outPitch.chan;
-    T* yp = y + pn * outPitch.n + (p - pn * outPitch.chan) * outPitch.c;
+    const int64_t pn = PITCH ? p / outPitch.chan : 0;
+    T* yp = PITCH ? y + pn * outPitch.n + (p - pn * outPitch.chan) * outPitch.c : y + p * hout * static_cast<int64_t>(wout);
+    const int64_t outRow = PITCH ? outPitch.h : wout;
     for (int32_t g = cg0; g < groups; g += colThreads) {
         const int32_t c0 = g * VI;
         const int32_t cl = max(c0 - 1, 0), cr = min(c0 + VI, win - 1);
@@ -434,7 +437,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         // `up` as the upper and `dn` as the lower buffer and returns true when the two have traded places.
         float bufA[VO], bufB[VO];
         int32_t curTop = -1, curBot = -1;
-        T* dst = yp + static_cast<int64_t>(ha) * outPitch.h + c0 * 2;
+        T* dst = yp + static_cast<int64_t>(ha) * outRow + c0 * 2;
         auto step = [&](int32_t h, float (&up)[VO], float (&dn)[VO]) -> bool {
             int32_t lo, hi;
             float dy;
@@ -451,7 +454,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                 }
                 curBot = hi;
                 BlendStore<T, VO>(dst, dn, up, dy, wideStores != 0);
-                dst += outPitch.h;
+                dst += outRow;
                 return true;
             }
             if (lo != curTop) {
@@ -470,7 +473,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                 curBot = hi;
             }
             BlendStore<T, VO>(dst, up, dn, dy, wideStores != 0);
-            dst += outPitch.h;
+            dst += outRow;
             return false;
         };
         bool traded = false; // false: bufA is the upper row
@@ -776,11 +779,12 @@ inline size_t X2SmemBytes(int32_t tileRows, int32_t threads, int elemSize, int c
 // PERIODIC: the host has checked that the four column weights of a grad_input column are the same for every column
 // but the first and the last of a row; they arrive as scalars (pw0..pw3) and only the two border weights are read
 // from the table, which frees the registers a second group of four columns needs.
-template <typename TIn, typename TOut, bool TWINS, int V, bool PERIODIC>
+template <typename TIn, typename TOut, bool TWINS, int V, bool PERIODIC, bool PITCH = false>
 __global__ void __launch_bounds__(kW2Threads, 5)
     BilinearBwdX2Kernel(const TIn* __restrict__ go, TOut* __restrict__ gi, int64_t planes, int32_t hin, int32_t win,
                         LerpAxis th, LerpAxis tw, RangeAxis rh, int32_t tileRows, float pw0, float pw1, float pw2,
-                        float pw3, AxisGeom geomH, AxisGeom geomW, int32_t halfPixel, int32_t start1)
+                        float pw3, AxisGeom geomH, AxisGeom geomW, int32_t halfPixel, int32_t start1,
+                        ViewStrides gradsPitch)
 {
     // PERIODIC reads no table: row entries and the three border weights are evaluated from the geometry (LerpEntry is
     // what the table kernel runs, so the bits are the same), and the first / last grads row of a tile follow from
@@ -868,7 +872,11 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         continue; // the barriers above are reached by every thread of the block in every tile
     }
     const int32_t groups = win / V;
-    const TIn* gp = go + p * (2 * static_cast<int64_t>(hin)) * wout;
+    // grad_output may be a view with N, C and H pitches (a dense tensor has those of its extents); its W stride is 1
+    const int64_t pn = PITCH ? p / gradsPitch.chan : 0;
+    const TIn* gp = PITCH ? go + pn * gradsPitch.n + (p - pn * gradsPitch.chan) * gradsPitch.c
+                          : go + p * (2 * static_cast<int64_t>(hin)) * wout;
+    const int64_t gradsRow = PITCH ? gradsPitch.h : wout;
     TOut* op = gi + p * hin * static_cast<int64_t>(win);
     for (int32_t g = threadIdx.x; g < groups; g += blockDim.x) {
         const int32_t x0 = g * V, j0 = 2 * x0;
@@ -906,7 +914,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         const float wExtra = extra ? colWeight(0, 1) : 0.0f;
         // one commit group per stream element (empty past the end); elements are issued in order, so the source
         // advances by one row per call
-        const TIn* issueRow = gp + static_cast<int64_t>(first) * wout + j0;
+        const TIn* issueRow = gp + static_cast<int64_t>(first) * gradsRow + j0;
         int32_t issueLeft = count;
         // The neighbour columns j0-1 and j0+VG are the last / first column of the threads to the left and right, whose
         // queue slots lie next to this thread's. When that thread is a lane of the same warp (same plane row, same
@@ -930,7 +938,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                     CpAsync4(plr + 4, issueRow + VG);
                 }
             }
-            issueRow += wout;
+            issueRow += gradsRow;
             --issueLeft;
             CpAsyncCommit();
         };
@@ -1419,9 +1427,19 @@ int32_t RowsForOccupancy(int64_t threadsPerTileRowSet, int32_t rows)
 
 template <typename TIn, typename TOut>
 cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th, LerpAxis tw, RangeAxis rh,
-                         RangeAxis rw, const BilinearPlan& plan, cudaStream_t s, bool buildTables)
+                         RangeAxis rw, const BilinearPlan& plan, cudaStream_t s, bool buildTables,
+                         const ViewStrides* gradsPitch)
 {
     const int64_t planes = sh.n * sh.c;
+    ViewStrides gp; // grad_output dense unless the caller passes a view (only with BilinearBwdTakesPitch)
+    gp.n = sh.c * static_cast<int64_t>(sh.hout) * sh.wout;
+    gp.c = static_cast<int64_t>(sh.hout) * sh.wout;
+    gp.h = sh.wout;
+    gp.w = 1;
+    gp.chan = static_cast<int32_t>(sh.c);
+    if (gradsPitch != nullptr) {
+        gp = *gradsPitch;
+    }
     // buildTables: the tables and ranges are workspace that has not been filled; they are built here (from the
     // geometry in the plan) unless the kernel chosen below evaluates the entries it needs itself
     bool tablesBuilt = !buildTables;
@@ -1487,7 +1505,7 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
                 if (attr == cudaSuccess) {
                     kernel<<<blocks, block, bytes, s>>>(pg, po, planes, sh.hin, sh.win, th, tw, rh, rows, plan.bw[0],
                                                         plan.bw[1], plan.bw[2], plan.bw[3], plan.geomH, plan.geomW,
-                                                        plan.halfPixel ? 1 : 0, plan.rowStart1);
+                                                        plan.halfPixel ? 1 : 0, plan.rowStart1, gp);
                 }
             };
             if (!(x2 && plan.periodicW)) {
@@ -1496,14 +1514,30 @@ cudaError_t LaunchGather(Layout lay, const void* go, void* gi, Shape4 sh, LerpAx
             if (x2) {
                 if (x2Wide) {
                     if constexpr (sizeof(TIn) == 2 && sizeof(TOut) == 2) {
-                        launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 8, true>);
+                        if (gradsPitch != nullptr) {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 8, true, true>);
+                        } else {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 8, true, false>);
+                        }
                     }
                 } else if (plan.periodicW) {
-                    launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, true>);
+                    if (gradsPitch != nullptr) {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, true, true>);
+                        } else {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, true, false>);
+                        }
                 } else if (plan.zeroTwins) {
-                    launchX2(BilinearBwdX2Kernel<TIn, TOut, true, 4, false>);
+                    if (gradsPitch != nullptr) {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, true, 4, false, true>);
+                        } else {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, true, 4, false, false>);
+                        }
                 } else {
-                    launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, false>);
+                    if (gradsPitch != nullptr) {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, false, true>);
+                        } else {
+                            launchX2(BilinearBwdX2Kernel<TIn, TOut, false, 4, false, false>);
+                        }
                 }
             }
             if (x2 && attr == cudaSuccess) {
@@ -1781,23 +1815,47 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                         // significand bits of T: 11 (fp16), 8 (bf16)
                         const int mant = std::is_same<T, __half>::value ? 11 : 8;
                         if (plan.periodicW && mant <= plan.weightSlack) {
-                            launch(BilinearFwdW2Kernel<T, 8, true, true, true>, qBytes, true);
-                        } else if (plan.periodicW) {
-                            launch(BilinearFwdW2Kernel<T, 8, true, true>, qBytes, true);
+                            if (outPitch != nullptr) {
+                            launch(BilinearFwdW2Kernel<T, 8, true, true, true, true>, qBytes, true);
                         } else {
-                            launch(BilinearFwdW2Kernel<T, 8, true, false>, qBytes, false);
+                            launch(BilinearFwdW2Kernel<T, 8, true, true, true, false>, qBytes, true);
+                        }
+                        } else if (plan.periodicW) {
+                            if (outPitch != nullptr) {
+                            launch(BilinearFwdW2Kernel<T, 8, true, true, false, true>, qBytes, true);
+                        } else {
+                            launch(BilinearFwdW2Kernel<T, 8, true, true, false, false>, qBytes, true);
+                        }
+                        } else {
+                            if (outPitch != nullptr) {
+                            launch(BilinearFwdW2Kernel<T, 8, true, false, false, true>, qBytes, false);
+                        } else {
+                            launch(BilinearFwdW2Kernel<T, 8, true, false, false, false>, qBytes, false);
+                        }
                         }
                     }
                 } else if (sizeof(T) == 4) {
                     if constexpr (sizeof(T) == 4) {
                         if (plan.periodicW) {
-                            launch(BilinearFwdW2Kernel<T, 4, true, true>, qBytes, true);
+                            if (outPitch != nullptr) {
+                            launch(BilinearFwdW2Kernel<T, 4, true, true, false, true>, qBytes, true);
                         } else {
-                            launch(BilinearFwdW2Kernel<T, 4, true, false>, qBytes, false);
+                            launch(BilinearFwdW2Kernel<T, 4, true, true, false, false>, qBytes, true);
+                        }
+                        } else {
+                            if (outPitch != nullptr) {
+                            launch(BilinearFwdW2Kernel<T, 4, true, false, false, true>, qBytes, false);
+                        } else {
+                            launch(BilinearFwdW2Kernel<T, 4, true, false, false, false>, qBytes, false);
+                        }
                         }
                     }
                 } else {
-                    launch(BilinearFwdW2Kernel<T, 4, false, false>, 0, false);
+                    if (outPitch != nullptr) {
+                            launch(BilinearFwdW2Kernel<T, 4, false, false, false, true>, 0, false);
+                        } else {
+                            launch(BilinearFwdW2Kernel<T, 4, false, false, false, false>, 0, false);
+                        }
                 }
             } else if (plan.schedule == BilinearPlan::kTiled && plan.tileRows > 0) {
                 const int32_t tiles = static_cast<int32_t>(CeilDiv(sh.hout, plan.tileRows));
@@ -1881,19 +1939,30 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
     return cudaGetLastError();
 }
 
+bool BilinearBwdTakesPitch(Dt dtIn, Dt dtOut, Layout lay, const void* go, const void* gi, Shape4 sh,
+                           const BilinearPlan& plan, const ViewStrides& grads)
+{
+    const size_t es = static_cast<size_t>(DtSize(dtIn));
+    // the conditions under which LaunchGather runs the 2x kernel, with the view's pitches in place of the dense ones
+    return lay == kNCHW && plan.schedule == BilinearPlan::kX2 && grads.w == 1 &&
+           PickVec(DtSize(dtOut), sh.win, {gi}) >= 4 && Aligned(go, 16) && (grads.n * es) % 16 == 0 &&
+           (grads.c * es) % 16 == 0 && (grads.h * es) % 16 == 0;
+}
+
 cudaError_t BilinearBwdGather(Dt dtIn, Dt dtOut, Layout lay, const void* go, void* gi, Shape4 sh, LerpAxis th,
                               LerpAxis tw, RangeAxis rh, RangeAxis rw, const BilinearPlan& plan, cudaStream_t s,
-                              bool buildTables)
+                              bool buildTables, const ViewStrides* gradsPitch)
 {
     if (dtIn == dtOut) {
-        OPSCV_DISPATCH_DT(dtIn, T,
-                          { return (LaunchGather<T, T>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables)); });
+        OPSCV_DISPATCH_DT(dtIn, T, {
+            return (LaunchGather<T, T>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables, gradsPitch));
+        });
     }
     if (dtIn == Dt::F32 && dtOut == Dt::F16) {
-        return LaunchGather<float, __half>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables);
+        return LaunchGather<float, __half>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables, gradsPitch);
     }
     if (dtIn == Dt::F32 && dtOut == Dt::BF16) {
-        return LaunchGather<float, __nv_bfloat16>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables);
+        return LaunchGather<float, __nv_bfloat16>(lay, go, gi, sh, th, tw, rh, rw, plan, s, buildTables, gradsPitch);
     }
     return cudaErrorInvalidValue;
 }

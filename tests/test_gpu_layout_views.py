@@ -152,3 +152,19 @@ def test_nearest_backward_between_pitched_views(ops, dev, dtype):
     # a ragged size goes through the staging copies and still matches
     want = ops.upsample_nearest2d_backward(g.contiguous(), (16, 32), (3, 5, 7, 13))
     assert torch.equal(ops.upsample_nearest2d_backward(g, (16, 32), (3, 5, 7, 13)), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_bilinear_backward_reads_a_pitched_grad_output(ops, dev, dtype):
+    """grad_output as a channel slice of the gradient of a concatenation feeds the 2x gather kernel through its
+    pitches: the bits and the launch count of the dense call."""
+    cat_grad = torch.randn((2, 12, 32, 64), generator=gen(94)).to(dtype).to(dev)
+    g = cat_grad[:, 4:9]
+    assert not g.is_contiguous()
+    want, dense_count = _launches(ops, lambda: ops.upsample_bilinear2d_backward(g.contiguous(), (32, 64), (2, 5, 16, 32), False))
+    got, count = _launches(ops, lambda: ops.upsample_bilinear2d_backward(g, (32, 64), (2, 5, 16, 32), False))
+    assert torch.equal(got, want)
+    assert count == dense_count, (count, dense_count)
+    # other scales and a strided grad_input go through the staging copies and still match
+    want = ops.upsample_bilinear2d_backward(g.contiguous(), (32, 64), (2, 5, 13, 20), True)
+    assert torch.equal(ops.upsample_bilinear2d_backward(g, (32, 64), (2, 5, 13, 20), True), want)
