@@ -20,7 +20,7 @@ Printed JSON (one line, rank 0):
              beside it the torch CPU operators the reference's own test scripts use as their golden, same sample;
   other_workloads  (default run, one GPU) the same per-operator figures for the other benchmark configurations,
              fewer steps each, every one with its own clock record;
-  box_sweep  BASELINE configuration 5 split evenly along N over the ranks (strong scaling): box time = slowest rank,
+  box_sweep  the box-sweep configuration (bilinear bf16 NHWC N=512 plus grid sampler fp32 N=256) split evenly along N over the ranks (strong scaling): box time = slowest rank,
              efficiency = T(1) / (G * T(G)) with T(1) measured in the same run on the whole batch.
 
 Timing: CUDA events on the launching stream, max over ranks; every step works on a different one of several
@@ -171,7 +171,7 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
 
     if name in ("cfg4", "cfg4bf16", "cfg4affine"):
         # cfg4affine: the cfg4 shapes with smooth grids (random rotation / scale / shift, as in cfg5) instead of
-        # uniform-random sample positions; not a BASELINE configuration, it separates the cost of the random
+        # uniform-random sample positions; not one of the benchmark configurations, it separates the cost of the random
         # access pattern from the cost of the kernels
         n, c, hi, wi, ho, wo = 16 // batch_div, 256, 64, 64, 128, 128
         dt = torch.bfloat16 if name == "cfg4bf16" else torch.float32
@@ -794,7 +794,7 @@ def main():
 
 
 def box_sweep(cfg5_result, args, ops, torch, dev, dist, world, rank, peak):
-    """BASELINE configuration 5 split evenly along N over the ranks (strong scaling, no collective): rank r owns the
+    """the box-sweep configuration (bilinear bf16 NHWC N=512 plus grid sampler fp32 N=256) split evenly along N over the ranks (strong scaling, no collective): rank r owns the
     images sharding.shard_range(N, world, r) of both operators. T(1) is the same workload with the whole batch on one
     GPU, measured in this run (every rank times it on its own GPU; the slowest counts); efficiency = T(1) / (G * T(G)).
     With one rank the object just restates the cfg5 figures as the sweep's G = 1 point."""
