@@ -794,7 +794,7 @@ def main():
 
 
 def box_sweep(cfg5_result, args, ops, torch, dev, dist, world, rank, peak):
-    """the box-sweep configuration (bilinear bf16 NHWC N=512 plus grid sampler fp32 N=256) split evenly along N over the ranks (strong scaling, no collective): rank r owns the
+    """The box-sweep configuration (bilinear bf16 NHWC N=512 plus grid sampler fp32 N=256) split evenly along N over the ranks (strong scaling, no collective): rank r owns the
     images sharding.shard_range(N, world, r) of both operators. T(1) is the same workload with the whole batch on one
     GPU, measured in this run (every rank times it on its own GPU; the slowest counts); efficiency = T(1) / (G * T(G)).
     With one rank the object just restates the cfg5 figures as the sweep's G = 1 point."""
