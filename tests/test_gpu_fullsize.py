@@ -166,3 +166,34 @@ def test_cfg5_box_sweep_whole_batch_on_one_gpu(ops, oracle, dev):
     check(ends(gy), oracle.grid_sampler2d_fwd(fl.numpy(), ends(grid).numpy(), 0, 0, False), torch.float32, exact=True)
     mid = n2 // 2 + 1
     assert torch.equal(gy[mid], ops.grid_sampler2d(gx[mid:mid + 1].contiguous(), grid[mid:mid + 1].to(dev), 0, 0, False)[0])
+
+
+def test_volumes_past_two_to_the_31_elements(ops, oracle, dev):
+    """3-D resamplers on an output of 2^31 + 2^24 fp16 elements (4.3 GB): offsets of the last planes need 64 bits. The
+    oracle checks the first and the last plane; the rest of the tensor through size-independent properties: the 2x
+    nearest backward of the forward is exactly 8 x the input, and trilinear interpolation of a constant volume gives
+    the constant back."""
+    n, c, di, hi, wi = 1, 129, 64, 128, 256
+    do, ho, wo = 2 * di, 2 * hi, 2 * wi
+    assert n * c * do * ho * wo > 2 ** 31
+    x = (torch.randn((n, c, di, hi, wi), generator=gen(1250)) * 0.25).to(torch.float16)
+    xd = x.to(dev)
+    y = ops.upsample_nearest3d(xd, (do, ho, wo))
+    for ch in (0, c - 1):
+        ref = oracle.nearest3d_fwd(x[:, ch:ch + 1].float().numpy(), (do, ho, wo))
+        assert np.array_equal(y[:, ch:ch + 1].float().cpu().numpy(), ref)
+    back = ops.upsample_nearest3d_backward(y, (do, ho, wo), (n, c, di, hi, wi))
+    assert torch.equal(back.float(), xd.float() * 8.0)   # eight equal copies: exact in fp32, and x * 8 is a power-of-two scale
+    del back
+    t = ops.upsample_trilinear3d(xd, (do, ho, wo), False)
+    for ch in (0, c - 1):
+        ref = oracle.trilinear3d_fwd(x[:, ch:ch + 1].float().numpy(), (do, ho, wo), False)
+        check(t[:, ch:ch + 1], ref, torch.float16)
+    gi = ops.upsample_trilinear3d_backward(t, (do, ho, wo), (n, c, di, hi, wi), False)
+    for ch in (0, c - 1):
+        ref = oracle.trilinear3d_bwd(t[:, ch:ch + 1].float().cpu().numpy(), (di, hi, wi), False)
+        check(gi[:, ch:ch + 1], ref, torch.float16)
+    del t, gi, y
+    const = torch.full((n, c, di, hi, wi), 0.75, dtype=torch.float16, device=dev)
+    out = ops.upsample_trilinear3d(const, (do, ho, wo), True)
+    assert float(out.min()) == 0.75 and float(out.max()) == 0.75
