@@ -1138,7 +1138,6 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
         return Fail(ACLNN_ERR_INNER_CREATE_EXECUTOR, "%s: cannot create executor", api);
     }
     WsPlan ws;
-    const BufRef x = StageInput(self, ws, ex);
     const Shape4 sh = MakeShape(gi, go);
     const Dt dt = ToDt(self->dtype);
     const Layout lay = self->format == ACL_FORMAT_NHWC ? kNHWC : kNCHW;
@@ -1148,16 +1147,16 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
     const bool halfPixel = !alignCorners; // resize_bilinear_v2.cpp:99
     const LerpOffsets lh = AllocLerp(ws, sh.hout), lw = AllocLerp(ws, sh.wout);
     const BilinearPlan plan = MakeBilinearFwdPlan(dt, lay, sh, ah, aw, halfPixel);
-    // An output that is a pitched NCHW view (a crop or a channel slice of a larger buffer, unit W stride) is written in
-    // place by the 2x-width kernel: no staged result, no scatter copy. The input must already be in place too (the
-    // check needs its address).
-    ViewStrides so{};
-    if (!IsContiguous(outT) && !x.inWs && StridesOf(outT, true, &so)) {
+    // Pitched NCHW views (a crop or a channel slice of a larger tensor, unit W stride, 16-byte aligned pitches) on either
+    // side are read and written in place by the 2x-width kernel: no gather copy, no staged result, no scatter copy.
+    ViewStrides si{}, so{};
+    if ((!IsContiguous(self) || !IsContiguous(outT)) && StridesOf(self, false, &si) && StridesOf(outT, true, &so)) {
+        char* px = static_cast<char*>(self->data) + self->offset * ElemSize(self->dtype);
         char* py = static_cast<char*>(outT->data) + outT->offset * ElemSize(outT->dtype);
-        if (BilinearFwdTakesPitch(dt, lay, x.base, py, sh, plan, so)) {
+        if (BilinearFwdTakesPitch(dt, lay, px, py, sh, plan, si, so)) {
             ex->steps.push_back([=](char* w, cudaStream_t s) {
                 const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);
-                return BilinearFwd(dt, lay, x.At(w), py, sh, th, tw, plan, s, true, &so);
+                return BilinearFwd(dt, lay, px, py, sh, th, tw, plan, s, true, &so, &si);
             });
             ex->workspaceSize = ws.Size();
             *workspaceSize = ws.Size();
@@ -1165,6 +1164,7 @@ aclnnStatus aclnnUpsampleBilinear2dGetWorkspaceSize(const aclTensor* self, const
             return ACLNN_SUCCESS;
         }
     }
+    const BufRef x = StageInput(self, ws, ex);
     const BufRef y = StageOutput(outT, ws);
     ex->steps.push_back([=](char* w, cudaStream_t s) {
         const LerpAxis th = LerpAt(w, lh), tw = LerpAt(w, lw);

@@ -130,13 +130,13 @@ BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, Axis
 BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, AxisGeom gw, bool halfPixel);
 // buildTables: th / tw are workspace that has not been filled; BilinearFwd fills it (plan.geomH / geomW, forward
 // formula) unless the kernel it picks evaluates its own entries. false: the caller has built the tables.
-// outPitch: the output is an NCHW view with these N, C and H pitches and a unit W stride; only where
-// BilinearFwdTakesPitch says the kernel the plan selects takes pitches (the 2x-width kernel does).
+// outPitch / inPitch (both or neither): output and input are NCHW views with these N, C and H pitches and unit W
+// strides; only where BilinearFwdTakesPitch says the kernel the plan selects takes pitches (the 2x-width kernel does).
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
                         const BilinearPlan& plan, cudaStream_t s, bool buildTables = false,
-                        const ViewStrides* outPitch = nullptr);
+                        const ViewStrides* outPitch = nullptr, const ViewStrides* inPitch = nullptr);
 bool BilinearFwdTakesPitch(Dt dt, Layout lay, const void* x, const void* y, Shape4 sh, const BilinearPlan& plan,
-                           const ViewStrides& out);
+                           const ViewStrides& in, const ViewStrides& out);
 // Gather backward: dtIn = grad_output dtype, dtOut = grad_input dtype.
 // buildTables: as for BilinearFwd, with the backward formula and the ranges.
 // gradsPitch: grad_output is an NCHW view with these N, C and H pitches and a unit W stride; only where

@@ -270,7 +270,8 @@ template <typename T, int VI, bool QUEUE, bool PERIODIC, bool FUSE = false, bool
 __global__ void __launch_bounds__(kW2Threads, 5)
     BilinearFwdW2Kernel(const T* __restrict__ x, T* __restrict__ y, int64_t planes, int32_t hin, int32_t win,
                         int32_t hout, LerpAxis th, LerpAxis tw, int32_t tileRows, int32_t wideStores, float dxFirst,
-                        float dxEven, float dxOdd, AxisGeom geomH, int32_t halfPixel, ViewStrides outPitch)
+                        float dxEven, float dxOdd, AxisGeom geomH, int32_t halfPixel, ViewStrides outPitch,
+                        ViewStrides inPitch)
 {
     constexpr int VO = 2 * VI;
     constexpr int HE = 4 / sizeof(T); // elements in a 4-byte neighbour word
@@ -327,9 +328,10 @@ __global__ void __launch_bounds__(kW2Threads, 5)
     }
     const int32_t groups = win / VI;
     const int32_t colThreads = blockDim.x, cg0 = threadIdx.x;
-    const T* xp = x + p * hin * static_cast<int64_t>(win);
-    // the output may be a view with N, C and H pitches (a dense tensor has those of its extents); its W stride is 1
+    // input and output may be views with N, C and H pitches (a dense tensor has those of its extents); W strides are 1
     const int64_t pn = PITCH ? p / outPitch.chan : 0;
+    const T* xp = PITCH ? x + pn * inPitch.n + (p - pn * outPitch.chan) * inPitch.c : x + p * hin * static_cast<int64_t>(win);
+    const int64_t inRow = PITCH ? inPitch.h : win;
     T* yp = PITCH ? y + pn * outPitch.n + (p - pn * outPitch.chan) * outPitch.c : y + p * hout * static_cast<int64_t>(wout);
     const int64_t outRow = PITCH ? outPitch.h : wout;
     for (int32_t g = cg0; g < groups; g += colThreads) {
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
         const int32_t lastRow = lastHi;
         int32_t nextRow = firstLo; // next row the queue delivers
         int32_t issued = nextRow;                        // next row to start copying
-        const T* issuePtr = xp + static_cast<int64_t>(nextRow) * win + c0;
+        const T* issuePtr = xp + static_cast<int64_t>(nextRow) * inRow + c0;
         auto issue = [&]() {
             if (issued <= lastRow) {
                 const int32_t slot = (issued & (kW2QueueDepth - 1)) * nthreads + tid;
@@ -373,7 +375,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                 }
             }
             ++issued;
-            issuePtr += win;
+            issuePtr += inRow;
             CpAsyncCommit();
         };
         if (QUEUE) {
@@ -383,7 +385,7 @@ __global__ void __launch_bounds__(kW2Threads, 5)
             }
         }
         auto loadRow = [&](int32_t r, float (&h)[VO]) {
-            const T* xr = xp + static_cast<int64_t>(r) * win;
+            const T* xr = xp + static_cast<int64_t>(r) * inRow;
             float v[VI + 2]; // columns c0-1 .. c0+VI
             if (QUEUE) {
                 while (nextRow < r) { // rows the walk skips (down-scaling) are dropped
@@ -1735,18 +1737,30 @@ BilinearPlan MakeBilinearBwdPlan(Dt dtIn, Layout lay, Shape4 sh, AxisGeom gh, Ax
 }
 
 bool BilinearFwdTakesPitch(Dt dt, Layout lay, const void* x, const void* y, Shape4 sh, const BilinearPlan& plan,
-                           const ViewStrides& out)
+                           const ViewStrides& in, const ViewStrides& out)
 {
     const size_t es = static_cast<size_t>(DtSize(dt));
-    // the conditions of the 2x-width kernel below, with the view's pitches in place of the dense ones
-    return lay == kNCHW && plan.schedule == BilinearPlan::kW2 && out.w == 1 && Aligned(x, 4 * es) && Aligned(y, 16) &&
-           (sh.wout * es) % 16 == 0 && (out.n * es) % 16 == 0 && (out.c * es) % 16 == 0 && (out.h * es) % 16 == 0;
+    // the conditions of the 2x-width kernel below, with the views' pitches in place of the dense ones (the input
+    // queue copies 16 bytes at a time)
+    return lay == kNCHW && plan.schedule == BilinearPlan::kW2 && out.w == 1 && in.w == 1 && Aligned(x, 16) &&
+           Aligned(y, 16) && (sh.wout * es) % 16 == 0 && (out.n * es) % 16 == 0 && (out.c * es) % 16 == 0 &&
+           (out.h * es) % 16 == 0 && (in.n * es) % 16 == 0 && (in.c * es) % 16 == 0 && (in.h * es) % 16 == 0;
 }
 
 cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, LerpAxis th, LerpAxis tw,
-                        const BilinearPlan& plan, cudaStream_t s, bool buildTables, const ViewStrides* outPitch)
+                        const BilinearPlan& plan, cudaStream_t s, bool buildTables, const ViewStrides* outPitch,
+                        const ViewStrides* inPitch)
 {
     const int64_t planes = sh.n * sh.c;
+    ViewStrides ip; // dense input unless the caller passes a view
+    ip.n = sh.c * static_cast<int64_t>(sh.hin) * sh.win;
+    ip.c = static_cast<int64_t>(sh.hin) * sh.win;
+    ip.h = sh.win;
+    ip.w = 1;
+    ip.chan = static_cast<int32_t>(sh.c);
+    if (inPitch != nullptr) {
+        ip = *inPitch;
+    }
     ViewStrides op; // dense output unless the caller passes a view (only with BilinearFwdTakesPitch)
     op.n = sh.c * static_cast<int64_t>(sh.hout) * sh.wout;
     op.c = static_cast<int64_t>(sh.hout) * sh.wout;
@@ -1808,7 +1822,7 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                         1, std::min<int64_t>(static_cast<int64_t>(NumSMs()) * perSm, totalRows / 8))));
                     kernel<<<grid, block, smem, s>>>(px, py, planes, sh.hin, sh.win, sh.hout, th, tw, tileRows, wide,
                                                      plan.dxFirst, plan.dxEven, plan.dxOdd, plan.geomH,
-                                                     plan.halfPixel ? 1 : 0, op);
+                                                     plan.halfPixel ? 1 : 0, op, ip);
                 };
                 if (vi == 8) {
                     if constexpr (sizeof(T) == 2) {

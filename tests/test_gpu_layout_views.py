@@ -106,8 +106,13 @@ def test_strided_nchw_views(ops, dev, dtype, align):
                 want = call(dense)
                 got, count = _launches(ops, lambda: call(v))
                 assert torch.equal(got, want), (name, op, ho, wo)
-                pitched = op != "bilinear" and wo == 2 * v.shape[3] and ho % v.shape[2] == 0 and v.stride(3) == 1
-                assert (count == 1) == pitched, (name, op, ho, wo, count)
+                if op != "bilinear":
+                    pitched = wo == 2 * v.shape[3] and ho % v.shape[2] == 0 and v.stride(3) == 1
+                    assert (count == 1) == pitched, (name, op, ho, wo, count)
+                elif name == "channel slice" and wo == 2 * v.shape[3]:
+                    # 16-byte aligned pitches: the 2x-width kernel reads the view in place (the dense call's launches)
+                    _, dense_count = _launches(ops, lambda: call(dense))
+                    assert count == dense_count, (name, op, ho, wo, count, dense_count)
     # an up-sample written straight into a channel slice of a larger buffer (up-sample + concatenate)
     x = base[:, :5, :8, :16].contiguous()
     cat = torch.full((3, 12, 16, 32), 7.0, dtype=dtype, device=dev)
