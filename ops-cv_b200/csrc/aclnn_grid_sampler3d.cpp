@@ -154,7 +154,30 @@ aclnnStatus aclnnGridSampler3DGetWorkspaceSize(const aclTensor* input, const acl
     Grid3dShape g = MakeShape(in5, grid, interpolationMode, paddingMode, alignCorners);
     g.cl = cl ? 1 : 0;
     const Dt dt = ToDt(input->dtype);
-    ex->steps.push_back([=](char* w, cudaStream_t s) { return GridSampler3dFwd(dt, x.At(w), gr.At(w), y.At(w), g, s); });
+    // NCDHW tensors with enough channels: a tap of a point costs a 32-byte sector per channel in that layout, so the
+    // input is turned channels-last in the workspace (tiled transpose), sampled by the channels-last kernel, and the
+    // result turned back: two extra passes over tensors that the gather reads eight times over.
+    const int64_t inVol = static_cast<int64_t>(g.di) * g.hi * g.wi, outVol = static_cast<int64_t>(g.dout) * g.ho * g.wo;
+    if (!cl && g.c >= 16 && g.c % 4 == 0) {
+        const int es = ElemSize(input->dtype);
+        const uint64_t xtOff = ws.Alloc(static_cast<uint64_t>(g.n) * g.c * inVol * es);
+        const uint64_t ytOff = ws.Alloc(static_cast<uint64_t>(g.n) * g.c * outVol * es);
+        Grid3dShape gc = g;
+        gc.cl = 1;
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            cudaError_t e = TransposeBatched(es, x.At(w), w + xtOff, g.n, g.c, inVol, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            e = GridSampler3dFwd(dt, w + xtOff, gr.At(w), w + ytOff, gc, s);
+            if (e != cudaSuccess) {
+                return e;
+            }
+            return TransposeBatched(es, w + ytOff, y.At(w), g.n, outVol, g.c, s);
+        });
+    } else {
+        ex->steps.push_back([=](char* w, cudaStream_t s) { return GridSampler3dFwd(dt, x.At(w), gr.At(w), y.At(w), g, s); });
+    }
     FinishOutput(yout, y, ex);
     ex->workspaceSize = ws.Size();
     *workspaceSize = ws.Size();
@@ -249,11 +272,41 @@ aclnnStatus aclnnGridSampler3DBackwardGetWorkspaceSize(const aclTensor* gradOutp
     g.cl = cl ? 1 : 0;
     const Dt dt = ToDt(input->dtype);
     const bool needAcc = wantInput && dt != Dt::F32;
-    const uint64_t accOff = needAcc ? ws.Alloc(static_cast<uint64_t>(Numel(input)) * 4) : 0;
-    ex->steps.push_back([=](char* w, cudaStream_t s) {
-        float* acc = needAcc ? reinterpret_cast<float*>(w + accOff) : static_cast<float*>(gi.At(w));
-        return GridSampler3dBwd(dt, go.At(w), x.At(w), gr.At(w), gi.At(w), gg.At(w), acc, g, wantInput, wantGrid, s);
-    });
+    const int64_t inVol = static_cast<int64_t>(g.di) * g.hi * g.wi, outVol = static_cast<int64_t>(g.dout) * g.ho * g.wo;
+    if (!cl && g.c >= 16 && g.c % 4 == 0) {
+        // as in the forward: channels-last copies of grad_output and input, the channels-last kernel (16-byte vector
+        // reductions into an fp32 channels-last accumulator), and grad_input turned back to NCDHW
+        const int es = ElemSize(input->dtype);
+        const uint64_t gotOff = ws.Alloc(static_cast<uint64_t>(g.n) * g.c * outVol * es);
+        const uint64_t xtOff = ws.Alloc(static_cast<uint64_t>(g.n) * g.c * inVol * es);
+        const uint64_t accOff = wantInput ? ws.Alloc(static_cast<uint64_t>(g.n) * g.c * inVol * 4) : 0;
+        const uint64_t gitOff = needAcc ? ws.Alloc(static_cast<uint64_t>(g.n) * g.c * inVol * es) : 0;
+        Grid3dShape gc = g;
+        gc.cl = 1;
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            cudaError_t e = TransposeBatched(es, go.At(w), w + gotOff, g.n, g.c, outVol, s);
+            if (e == cudaSuccess) {
+                e = TransposeBatched(es, x.At(w), w + xtOff, g.n, g.c, inVol, s);
+            }
+            if (e != cudaSuccess) {
+                return e;
+            }
+            float* acc = reinterpret_cast<float*>(w + accOff);
+            // 16-bit tensors: the kernel's cast pass writes a channels-last grad_input of the storage type
+            void* giT = needAcc ? static_cast<void*>(w + gitOff) : static_cast<void*>(acc);
+            e = GridSampler3dBwd(dt, w + gotOff, w + xtOff, gr.At(w), giT, gg.At(w), acc, gc, wantInput, wantGrid, s);
+            if (e != cudaSuccess || !wantInput) {
+                return e;
+            }
+            return TransposeBatched(es, giT, gi.At(w), g.n, inVol, g.c, s);
+        });
+    } else {
+        const uint64_t accOff = needAcc ? ws.Alloc(static_cast<uint64_t>(Numel(input)) * 4) : 0;
+        ex->steps.push_back([=](char* w, cudaStream_t s) {
+            float* acc = needAcc ? reinterpret_cast<float*>(w + accOff) : static_cast<float*>(gi.At(w));
+            return GridSampler3dBwd(dt, go.At(w), x.At(w), gr.At(w), gi.At(w), gg.At(w), acc, g, wantInput, wantGrid, s);
+        });
+    }
     if (wantInput) {
         FinishOutput(giT, gi, ex);
     }

@@ -279,6 +279,10 @@ cudaError_t GridSampler3dFwd(Dt dt, const void* x, const void* grid, void* y, Gr
 cudaError_t GridSampler3dBwd(Dt dt, const void* go, const void* x, const void* grid, void* gi, void* ggrid, float* acc,
                              Grid3dShape g, bool wantInput, bool wantGrid, cudaStream_t s);
 
+// out[b][c][r] = in[b][r][c] (elements of 2 or 4 bytes): the NCDHW <-> NDHWC change of the 3-D grid sampler.
+cudaError_t TransposeBatched(int elemSize, const void* in, void* out, int64_t batch, int64_t rows, int64_t cols,
+                             cudaStream_t s);
+
 struct View4 {
     int64_t dim[4];
     int64_t stride[4]; // in elements

@@ -1,6 +1,8 @@
 // Data-movement helpers: strided view <-> contiguous staging (what the reference does with its Contiguous and
 // ViewCopy steps around every operator), device-to-device copies for the same-size shortcuts, and the final
 // fp32 -> storage-dtype cast of the atomic backward paths.
+#include <algorithm>
+
 #include "launch_util.cuh"
 
 namespace opscv {
@@ -71,6 +73,39 @@ void LaunchStridedCopy(E* contiguous, E* viewBase, const View4& v, bool toView, 
     });
 }
 
+// out[b][c][r] = in[b][r][c]: 32 x 32 tiles through shared memory (one padding column: no bank conflicts), so that
+// both the reads and the writes of a warp are contiguous. block = (32, 8).
+template <typename E>
+__global__ void __launch_bounds__(256)
+    TransposeKernel(const E* __restrict__ in, E* __restrict__ out, int64_t rows, int64_t cols, int64_t tilesR,
+                    int64_t tilesC, int64_t tiles)
+{
+    __shared__ E tile[32][33];
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t b = t / (tilesR * tilesC);
+        const int64_t rem = t - b * tilesR * tilesC;
+        const int64_t tr = rem / tilesC, tc = rem - tr * tilesC;
+        const E* pin = in + b * rows * cols;
+        E* pout = out + b * rows * cols;
+        __syncthreads(); // the previous tile has been written out
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const int64_t r = tr * 32 + threadIdx.y + j, c = tc * 32 + threadIdx.x;
+            if (r < rows && c < cols) {
+                tile[threadIdx.y + j][threadIdx.x] = pin[r * cols + c];
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const int64_t c = tc * 32 + threadIdx.y + j, r = tr * 32 + threadIdx.x;
+            if (r < rows && c < cols) {
+                pout[c * rows + r] = tile[threadIdx.x][threadIdx.y + j];
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) CastKernel(T* __restrict__ dst, const float* __restrict__ src, int64_t n)
 {
@@ -123,6 +158,26 @@ cudaError_t StridedCopy(int elemSize, void* contiguous, void* viewBase, View4 v,
         LaunchStridedCopy<uint32_t>(static_cast<uint32_t*>(contiguous), static_cast<uint32_t*>(viewBase), v, toView, s);
     } else {
         LaunchStridedCopy<uint16_t>(static_cast<uint16_t*>(contiguous), static_cast<uint16_t*>(viewBase), v, toView, s);
+    }
+    CountLaunch();
+    return cudaGetLastError();
+}
+
+cudaError_t TransposeBatched(int elemSize, const void* in, void* out, int64_t batch, int64_t rows, int64_t cols,
+                             cudaStream_t s)
+{
+    if (batch * rows * cols == 0) {
+        return cudaSuccess;
+    }
+    const int64_t tilesR = CeilDiv(rows, 32), tilesC = CeilDiv(cols, 32), tiles = batch * tilesR * tilesC;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, static_cast<int64_t>(NumSMs()) * 32));
+    const dim3 block(32, 8, 1);
+    if (elemSize == 4) {
+        TransposeKernel<uint32_t><<<grid, block, 0, s>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out),
+                                                         rows, cols, tilesR, tilesC, tiles);
+    } else {
+        TransposeKernel<uint16_t><<<grid, block, 0, s>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out),
+                                                         rows, cols, tilesR, tilesC, tiles);
     }
     CountLaunch();
     return cudaGetLastError();
