@@ -738,6 +738,299 @@ __global__ void __launch_bounds__(kThreads) Bicubic2dBwdRegKernel(const T* __res
     }
 }
 
+// ---- backward at exactly 2x (scales 0.5, align_corners = false), NCHW --------------------------------------------
+// At this scale every source coordinate w / 2 - 0.25 is exact, so the walk of an interior grad_input index y visits
+// the grads indices 2y - 3 .. 2y + 4 (those inside the image) and the coefficient of the k-th of them is the same
+// number PointCoeff(|k / 2 - 1.75|) for every y. A block stages the grads rows of a band of grad_input rows in shared
+// memory as fp32 (each grads value is loaded and converted once instead of sixteen times), with zero columns either
+// side: a term whose grads column lies outside the image then adds a zero, which leaves a round-to-nearest sum that
+// started from +0 unchanged, so the window of a column needs no bounds. A thread owns two adjacent grad_input
+// columns of one row and reads their ten grads columns of a grads row as three 16-byte shared-memory loads. The
+// first and last row and column, whose walk has up to three clamped taps per grads index, take their (index,
+// coefficient) entries from four lists that the block builds with the reference's walk; the border columns are items
+// of their own behind the pairs, so that their longer loop does not run in the warps of the interior. Terms, their
+// (row, column, row tap, column tap) order and their rounding are those of the other two backward kernels.
+constexpr int kX2Pad = 4;     // zero columns left of a staged grads row (the window of column 0 starts at -4)
+constexpr int kX2Groups = 5;  // grads indices in the walk of a first or last index at 2x
+constexpr int kX2Slots = 3;   // clamped taps of one grads index that fall on it (four only for an extent of 1)
+constexpr int kX2Threads = 256;
+
+// The walk of a first or last grad_input index in slot form: grads indices start .. start + 4, up to three tap
+// coefficients each in tap order; bit 3m + t of mask says that slot t of group m holds a term.
+struct X2BorderList {
+    int32_t start;
+    uint32_t mask;
+    float coef[kX2Groups * kX2Slots];
+};
+
+__device__ void X2BuildBorderList(int32_t yIdx, int32_t in, int32_t out, X2BorderList& list)
+{
+    const int32_t start = WalkStart(yIdx, 2.0f, 0.5f);
+    uint32_t mask = 0;
+    for (int k = 0; k < kX2Groups * kX2Slots; ++k) {
+        list.coef[k] = 0.0f;
+    }
+    float r = Sub(Mul(Add(static_cast<float>(start), 0.5f), 0.5f), 0.5f);
+    for (int32_t o = start; o < out && o - start < kX2Groups; ++o, r = BwdSrc(0.5f, o, 0)) {
+        const long long f = static_cast<long long>(floorf(r));
+        if (yIdx == 0 && f > 1 && in > 1) {
+            break;
+        }
+        float tap[4];
+        TapCoeff(Sub(r, static_cast<float>(f)), tap);
+        int t = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (ClampIdx(f - 1 + j, in - 1) == yIdx && t < kX2Slots) {
+                list.coef[(o - start) * kX2Slots + t] = tap[j];
+                mask |= 1u << ((o - start) * kX2Slots + t);
+                ++t;
+            }
+        }
+    }
+    list.start = start;
+    list.mask = mask;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g,
+                                                                   int32_t bandRows, int32_t bands, int32_t pitch,
+                                                                   int32_t vecLoad)
+{
+    extern __shared__ __align__(16) float sG[]; // (2 * bandRows + 6) grads rows of `pitch` floats
+    __shared__ X2BorderList sL[4];              // 0 first column, 1 last column, 2 first row, 3 last row
+    const int32_t tid = threadIdx.x, nt = blockDim.x;
+    const int64_t plane = blockIdx.x / bands;
+    const int32_t band = static_cast<int32_t>(blockIdx.x - plane * bands);
+    const int32_t yhA = band * bandRows, yhB = min(yhA + bandRows, g.hin);
+    const int32_t hBase = 2 * yhA - 3; // grads row of shared-memory row 0
+    const int32_t hLo = max(hBase, 0), hHi = min(2 * (yhB - 1) + 4, g.hout - 1);
+    const int32_t nRows = hHi - hLo + 1;
+
+    float c[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        c[k] = PointCoeff(fabsf(Sub(Mul(0.5f, static_cast<float>(k)), 1.75f)));
+    }
+    if (tid < 4) {
+        const bool col = tid < 2;
+        const int32_t in = col ? g.win : g.hin;
+        X2BuildBorderList((tid & 1) ? in - 1 : 0, in, col ? g.wout : g.hout, sL[tid]);
+    }
+    {
+        float* sRow0 = sG + (hLo - hBase) * pitch;
+        const int32_t padRight = pitch - kX2Pad - g.wout, padCols = kX2Pad + padRight;
+        for (int32_t i = tid; i < nRows * padCols; i += nt) {
+            const int32_t r = i / padCols, k = i - r * padCols;
+            sRow0[r * pitch + (k < kX2Pad ? k : g.wout + k)] = 0.0f;
+        }
+        const T* pg = go + plane * (static_cast<int64_t>(g.hout) * g.wout) + static_cast<int64_t>(hLo) * g.wout;
+        float* sBase = sRow0 + kX2Pad;
+        if (vecLoad) {
+            constexpr int VL = 16 / sizeof(T);
+            const int32_t packs = g.wout / VL;
+            for (int32_t i = tid; i < nRows * packs; i += nt) {
+                const int32_t r = i / packs, p = i - r * packs;
+                float v[VL];
+                LoadPackLdg<T, VL>(pg + r * g.wout + p * VL, v);
+                float4* dst = reinterpret_cast<float4*>(sBase + r * pitch + p * VL);
+#pragma unroll
+                for (int m = 0; m < VL / 4; ++m) {
+                    dst[m] = make_float4(v[4 * m], v[4 * m + 1], v[4 * m + 2], v[4 * m + 3]);
+                }
+            }
+        } else {
+            for (int32_t i = tid; i < nRows * g.wout; i += nt) {
+                const int32_t r = i / g.wout, w = i - r * g.wout;
+                sBase[r * pitch + w] = DType<T>::Load(pg + r * g.wout + w);
+            }
+        }
+    }
+    __syncthreads();
+
+    const int32_t pairs = (g.win + 1) / 2;
+    const int32_t bandN = yhB - yhA;
+    const int32_t nPair = bandN * pairs;
+    const int32_t borderBase = (nPair + 31) & ~31;
+    const int32_t total = borderBase + 2 * bandN;
+    T* pgi = gi + (plane * g.hin + yhA) * g.win;
+    for (int32_t item = tid; item < total; item += nt) {
+        if (item < nPair) {
+            const int32_t r = item / pairs, q = item - r * pairs;
+            const int32_t yh = yhA + r;
+            const float* sw = sG + 4 * q; // grads column 4q - 4
+            float a0 = 0.0f, a1 = 0.0f;
+            if (yh != 0 && yh != g.hin - 1) {
+                const int32_t h0 = 2 * yh - 3;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int32_t h = h0 + j;
+                    if (h >= 0 && h < g.hout) {
+                        const float4* row = reinterpret_cast<const float4*>(sw + (h - hBase) * pitch);
+                        const float4 A = row[0], B = row[1], C = row[2];
+                        const float v[12] = {A.x, A.y, A.z, A.w, B.x, B.y, B.z, B.w, C.x, C.y, C.z, C.w};
+                        float gc[10];
+#pragma unroll
+                        for (int k = 0; k < 10; ++k) {
+                            gc[k] = Mul(v[1 + k], c[j]);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            a0 = Add(a0, Mul(gc[k], c[k]));
+                            a1 = Add(a1, Mul(gc[2 + k], c[k]));
+                        }
+                    }
+                }
+            } else {
+                const X2BorderList& rows = sL[yh == 0 ? 2 : 3];
+                const uint32_t mask = rows.mask;
+#pragma unroll 1
+                for (int m = 0; m < kX2Groups; ++m) {
+                    const uint32_t bits = (mask >> (m * kX2Slots)) & 7u;
+                    if (bits == 0) {
+                        continue;
+                    }
+                    const float ch0 = rows.coef[m * kX2Slots], ch1 = rows.coef[m * kX2Slots + 1],
+                                ch2 = rows.coef[m * kX2Slots + 2];
+                    const float4* row = reinterpret_cast<const float4*>(sw + (rows.start + m - hBase) * pitch);
+                    const float4 A = row[0], B = row[1], C = row[2];
+                    const float v[12] = {A.x, A.y, A.z, A.w, B.x, B.y, B.z, B.w, C.x, C.y, C.z, C.w};
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { // slots fill in tap order, so bit 0 is set whenever the group is
+                        a0 = Add(a0, Mul(Mul(v[1 + k], ch0), c[k]));
+                        a1 = Add(a1, Mul(Mul(v[3 + k], ch0), c[k]));
+                        if (bits & 2u) {
+                            a0 = Add(a0, Mul(Mul(v[1 + k], ch1), c[k]));
+                            a1 = Add(a1, Mul(Mul(v[3 + k], ch1), c[k]));
+                        }
+                        if (bits & 4u) {
+                            a0 = Add(a0, Mul(Mul(v[1 + k], ch2), c[k]));
+                            a1 = Add(a1, Mul(Mul(v[3 + k], ch2), c[k]));
+                        }
+                    }
+                }
+            }
+            T* po = pgi + static_cast<int64_t>(r) * g.win;
+            const int32_t yw0 = 2 * q;
+            if (yw0 >= 1 && yw0 <= g.win - 2) {
+                po[yw0] = DType<T>::FromF(a0);
+            }
+            if (yw0 + 1 <= g.win - 2) {
+                po[yw0 + 1] = DType<T>::FromF(a1);
+            }
+        } else if (item >= borderBase) {
+            // a first or last column: its five grads columns and up to three coefficients each, in registers
+            const int32_t b = item - borderBase;
+            const int32_t r = b >> 1, side = b & 1;
+            const int32_t yh = yhA + r;
+            const X2BorderList& cols = sL[side];
+            const uint32_t cmask = cols.mask;
+            float cw[kX2Groups * kX2Slots];
+            int32_t wcol[kX2Groups];
+#pragma unroll
+            for (int k = 0; k < kX2Groups * kX2Slots; ++k) {
+                cw[k] = cols.coef[k];
+            }
+#pragma unroll
+            for (int m = 0; m < kX2Groups; ++m) { // a group without terms reads a zero column and adds nothing
+                wcol[m] = ((cmask >> (m * kX2Slots)) & 7u) ? cols.start + m : -1;
+            }
+            float add = 0.0f;
+            auto rowTerms = [&](const float* prow, float ch) {
+#pragma unroll
+                for (int m = 0; m < kX2Groups; ++m) {
+                    const float gch = Mul(prow[wcol[m]], ch);
+#pragma unroll
+                    for (int t = 0; t < kX2Slots; ++t) {
+                        if (cmask & (1u << (m * kX2Slots + t))) {
+                            add = Add(add, Mul(gch, cw[m * kX2Slots + t]));
+                        }
+                    }
+                }
+            };
+            if (yh != 0 && yh != g.hin - 1) {
+                const int32_t h0 = 2 * yh - 3;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int32_t h = h0 + j;
+                    if (h >= 0 && h < g.hout) {
+                        rowTerms(sG + (h - hBase) * pitch + kX2Pad, c[j]);
+                    }
+                }
+            } else {
+                // a corner: (row, column, row tap, column tap) order puts the row taps of a grads value outside its
+                // column taps
+                const X2BorderList& rows = sL[yh == 0 ? 2 : 3];
+                const uint32_t rmask = rows.mask;
+#pragma unroll 1
+                for (int mr = 0; mr < kX2Groups; ++mr) {
+                    const uint32_t bits = (rmask >> (mr * kX2Slots)) & 7u;
+                    if (bits == 0) {
+                        continue;
+                    }
+                    const float* prow = sG + (rows.start + mr - hBase) * pitch + kX2Pad;
+#pragma unroll
+                    for (int m = 0; m < kX2Groups; ++m) {
+                        const float gv = prow[wcol[m]];
+#pragma unroll 1
+                        for (int i = 0; i < kX2Slots; ++i) {
+                            if (bits & (1u << i)) {
+                                const float gch = Mul(gv, rows.coef[mr * kX2Slots + i]);
+#pragma unroll
+                                for (int t = 0; t < kX2Slots; ++t) {
+                                    if (cmask & (1u << (m * kX2Slots + t))) {
+                                        add = Add(add, Mul(gch, cw[m * kX2Slots + t]));
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            pgi[static_cast<int64_t>(r) * g.win + (side ? g.win - 1 : 0)] = DType<T>::FromF(add);
+        }
+    }
+}
+
+// Band height and block size of the 2x kernel: full lanes first, then little halo. false: the kernel does not apply.
+struct X2Launch {
+    int32_t bandRows, bands, threads, pitch;
+    size_t smem;
+};
+bool PlanBwdX2(const BicubicGeom& g, bool nhwc, X2Launch* out)
+{
+    if (nhwc || g.align || g.scaleH != 0.5f || g.scaleW != 0.5f || g.invH != 2.0f || g.invW != 2.0f ||
+        g.hin < 2 || g.win < 2 || g.hout != 2 * g.hin || g.wout != 2 * g.win || g.wout > (1 << 20)) {
+        return false;
+    }
+    const int32_t pitch = (g.wout + 12 + 3) & ~3;
+    const int32_t pairs = (g.win + 1) / 2;
+    double best = 0.0;
+    for (int32_t threads = 128; threads <= kX2Threads; threads += 32) {
+        for (int32_t passes = 1; passes <= 3; ++passes) {
+            int32_t bh = std::min(std::max(passes * threads / pairs, 1), g.hin);
+            const int32_t nb = (g.hin + bh - 1) / bh;
+            bh = (g.hin + nb - 1) / nb;
+            const size_t smem = static_cast<size_t>(2 * bh + 6) * pitch * sizeof(float);
+            if (smem > 48 * 1024) {
+                continue;
+            }
+            const int64_t items = ((static_cast<int64_t>(bh) * pairs + 31) & ~31LL) + 2 * bh;
+            const double slots = static_cast<double>(nb) * static_cast<double>(CeilDiv(items, threads)) * threads;
+            const double score = static_cast<double>(g.hin) * pairs / slots / (1.0 + 0.08 * (2.0 * bh + 6.0) / (2.0 * bh));
+            if (score > best) {
+                best = score;
+                *out = X2Launch{bh, nb, threads, pitch, smem};
+            }
+        }
+    }
+    if (best == 0.0) {
+        return false;
+    }
+    const int64_t planes = g.rows / g.hin;
+    return planes * out->bands <= INT32_MAX;
+}
+
 dim3 RowGrid(int64_t rows, int64_t inner)
 {
     const int64_t gx = std::min<int64_t>(std::max<int64_t>(CeilDiv(inner, kThreads), 1), 64);
@@ -937,6 +1230,17 @@ cudaError_t Bicubic2dBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh,
         });
         CountLaunch();
     };
+    X2Launch x2;
+    if (PlanBwdX2(g, nhwc, &x2)) {
+        const int64_t planes = g.rows / g.hin;
+        OPSCV_DISPATCH_DT(dt, T, {
+            const int vec = (g.wout % (16 / sizeof(T)) == 0 && Aligned(go, 16)) ? 1 : 0;
+            Bicubic2dBwdX2Kernel<T><<<static_cast<unsigned>(planes * x2.bands), x2.threads, x2.smem, s>>>(
+                static_cast<const T*>(go), static_cast<T*>(gi), g, x2.bandRows, x2.bands, x2.pitch, vec);
+        });
+        CountLaunch();
+        return cudaGetLastError();
+    }
     if (!split) {
         launchList(false);
         return err != cudaSuccess ? err : cudaGetLastError();

@@ -176,3 +176,53 @@ def test_bicubic_larger_case_is_bit_exact(ops, oracle, dev):
     g = torch.randn((40, 8, 48, 48), generator=gen(49))
     gi = ops.upsample_bicubic2d_backward(g.to(dev), (48, 48), (40, 8, 24, 24), False)
     assert np.array_equal(gi.cpu().numpy(), oracle.bicubic2d_bwd(g.numpy(), (24, 24), False, definition="gather"))
+
+
+X2_SHAPES = [
+    # (N, C, Hin, Win): grad_output is (N, C, 2 Hin, 2 Win)
+    (1, 2, 2, 2),      # corners only
+    (2, 1, 2, 5),      # two rows, both borders; odd width
+    (1, 3, 3, 3),      # one interior element
+    (1, 2, 5, 4),      # wout a multiple of 8: 16-byte staging loads for fp16
+    (2, 2, 7, 13),     # odd width: the last pair holds one column
+    (1, 1, 4, 300),    # a row longer than a block
+    (3, 2, 61, 20),    # several bands per plane, the last one short
+    (1, 1, 9, 1100),   # a wide row: one band row per block
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", X2_SHAPES)
+def test_bicubic_backward_at_2x(ops, oracle, dev, dtype, shape):
+    """The staged 2x kernel (NCHW, align_corners = false, scales 0.5): the oracle's bits in fp32, every border kind."""
+    n, c, hi, wi = shape
+    g, g32 = quant(torch.randn((n, c, 2 * hi, 2 * wi), generator=gen(140)), dtype)
+    gi = ops.upsample_bicubic2d_backward(g.to(dev), (2 * hi, 2 * wi), (n, c, hi, wi), False)
+    ref = oracle.bicubic2d_bwd(g32, (hi, wi), False, definition="gather")
+    check(gi, ref, dtype, exact=(dtype == torch.float32))
+    # a view with an offset base (the staging loads fall back to single elements when the base is not 16-byte aligned)
+    flat = torch.zeros(g.numel() + 1, dtype=dtype)
+    flat[1:] = g.flatten()
+    gv = flat.to(dev)[1:].view(n, c, 2 * hi, 2 * wi)
+    assert torch.equal(ops.upsample_bicubic2d_backward(gv, (2 * hi, 2 * wi), (n, c, hi, wi), False), gi)
+
+
+def test_bicubic_backward_at_2x_special_values(ops, oracle, dev):
+    """Inf / NaN grads reach exactly the grad_input elements whose walk includes them (the zero columns beside a
+    staged row never meet them), and sums of signed zeros keep the oracle's sign."""
+    g = torch.randn((1, 2, 12, 16), generator=gen(141))
+    g[0, 0, 0, 0] = float("inf")
+    g[0, 0, 11, 15] = float("-inf")
+    g[0, 1, 5, 7] = float("nan")
+    g[0, 1, 0, 15] = float("inf")
+    gi = ops.upsample_bicubic2d_backward(g.to(dev), (12, 16), (1, 2, 6, 8), False).cpu().numpy()
+    ref = oracle.bicubic2d_bwd(g.numpy(), (6, 8), False, definition="gather")
+    assert np.array_equal(np.isnan(gi), np.isnan(ref)) and np.array_equal(np.isinf(gi), np.isinf(ref))
+    fin = np.isfinite(ref)
+    assert np.array_equal(gi[fin], ref[fin])
+    z = torch.zeros((1, 1, 8, 8))
+    z[0, 0, :, ::2] = -0.0
+    z[0, 0, 3, 3] = -1e-45  # a denormal whose products underflow to -0
+    gz = ops.upsample_bicubic2d_backward(z.to(dev), (8, 8), (1, 1, 4, 4), False).cpu().numpy()
+    rz = oracle.bicubic2d_bwd(z.numpy(), (4, 4), False, definition="gather")
+    assert np.array_equal(gz.view(np.uint32), rz.view(np.uint32))
