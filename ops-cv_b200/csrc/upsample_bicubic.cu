@@ -757,48 +757,84 @@ constexpr int kX2Threads = 256;
 
 // The walk of a first or last grad_input index in slot form: grads indices start .. start + 4, up to three tap
 // coefficients each in tap order; bit 3m + t of mask says that slot t of group m holds a term.
+constexpr int kX2Flat = 9;    // terms of such a walk when the extent is at least 2
 struct X2BorderList {
     int32_t start;
     uint32_t mask;
     float coef[kX2Groups * kX2Slots];
+    // the same terms one after the other in walk order, filled up with (column -1, 0): a term of the zero column
+    // adds nothing, so a loop over all kX2Flat entries needs no test
+    int32_t flatIdx[kX2Flat];
+    float flatCoef[kX2Flat];
+    int32_t terms;
 };
 
-__device__ void X2BuildBorderList(int32_t yIdx, int32_t in, int32_t out, X2BorderList& list)
+struct X2BorderLists {
+    X2BorderList l[4]; // 0 first column, 1 last column, 2 first row, 3 last row
+    float interior[8]; // coefficient of the k-th grads index of an interior walk: PointCoeff(|k / 2 - 1.75|)
+};
+
+// The reference's walk for a first or last index at scale 0.5, on the host: this file's host code is compiled with
+// floating-point contraction off, so every operation below rounds as the device's non-fused multiply and add do
+// (and at this scale the coordinates and the fractions 0.25 / 0.75 are exact anyway).
+namespace x2host {
+inline float Conv1(float x) { return ((((kA + 2.0f) * x) - (kA + 3.0f)) * x) * x + 1.0f; }
+inline float Conv2(float x) { return ((((kA * x) - 5.0f * kA) * x) + 8.0f * kA) * x - 4.0f * kA; }
+inline float PointCoeff(float d) { return d <= 1.0f ? Conv1(d) : (d < 2.0f ? Conv2(d) : 0.0f); }
+inline X2BorderList BorderList(int32_t yIdx, int32_t in, int32_t out)
 {
-    const int32_t start = WalkStart(yIdx, 2.0f, 0.5f);
+    X2BorderList list;
+    const int32_t start = std::max(2 * yIdx - 3, 0); // ceil((y - 2 + 0.5) * 2 - 0.5), clamped at 0
     uint32_t mask = 0;
     for (int k = 0; k < kX2Groups * kX2Slots; ++k) {
         list.coef[k] = 0.0f;
     }
-    float r = Sub(Mul(Add(static_cast<float>(start), 0.5f), 0.5f), 0.5f);
-    for (int32_t o = start; o < out && o - start < kX2Groups; ++o, r = BwdSrc(0.5f, o, 0)) {
-        const long long f = static_cast<long long>(floorf(r));
+    for (int32_t o = start; o < out && o - start < kX2Groups; ++o) {
+        const float r = (static_cast<float>(o) + 0.5f) * 0.5f - 0.5f;
+        const long long f = static_cast<long long>(std::floor(r));
         if (yIdx == 0 && f > 1 && in > 1) {
             break;
         }
-        float tap[4];
-        TapCoeff(Sub(r, static_cast<float>(f)), tap);
-        int t = 0;
-#pragma unroll
+        const float t = r - static_cast<float>(f);
+        const float u = 1.0f - t;
+        const float tap[4] = {Conv2(t + 1.0f), Conv1(t), Conv1(u), Conv2(u + 1.0f)};
+        int slot = 0;
         for (int j = 0; j < 4; ++j) {
-            if (ClampIdx(f - 1 + j, in - 1) == yIdx && t < kX2Slots) {
-                list.coef[(o - start) * kX2Slots + t] = tap[j];
-                mask |= 1u << ((o - start) * kX2Slots + t);
-                ++t;
+            const long long idx = std::min<long long>(std::max<long long>(f - 1 + j, 0), in - 1);
+            if (idx == yIdx && slot < kX2Slots) {
+                list.coef[(o - start) * kX2Slots + slot] = tap[j];
+                mask |= 1u << ((o - start) * kX2Slots + slot);
+                ++slot;
             }
         }
     }
     list.start = start;
     list.mask = mask;
+    list.terms = 0;
+    for (int k = 0; k < kX2Flat; ++k) {
+        list.flatIdx[k] = -1;
+        list.flatCoef[k] = 0.0f;
+    }
+    for (int k = 0; k < kX2Groups * kX2Slots; ++k) {
+        if (mask & (1u << k)) {
+            if (list.terms < kX2Flat) {
+                list.flatIdx[list.terms] = start + k / kX2Slots;
+                list.flatCoef[list.terms] = list.coef[k];
+            }
+            ++list.terms;
+        }
+    }
+    return list;
 }
+} // namespace x2host
 
 template <typename T>
 __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g,
                                                                    int32_t bandRows, int32_t bands, int32_t pitch,
-                                                                   int32_t vecLoad)
+                                                                   int32_t vecLoad, const X2BorderLists lists)
 {
     extern __shared__ __align__(16) float sG[]; // (2 * bandRows + 6) grads rows of `pitch` floats
-    __shared__ X2BorderList sL[4];              // 0 first column, 1 last column, 2 first row, 3 last row
+    const X2BorderList* sL = lists.l;
     const int32_t tid = threadIdx.x, nt = blockDim.x;
     const int64_t plane = blockIdx.x / bands;
     const int32_t band = static_cast<int32_t>(blockIdx.x - plane * bands);
@@ -807,42 +843,52 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __re
     const int32_t hLo = max(hBase, 0), hHi = min(2 * (yhB - 1) + 4, g.hout - 1);
     const int32_t nRows = hHi - hLo + 1;
 
-    float c[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        c[k] = PointCoeff(fabsf(Sub(Mul(0.5f, static_cast<float>(k)), 1.75f)));
-    }
-    if (tid < 4) {
-        const bool col = tid < 2;
-        const int32_t in = col ? g.win : g.hin;
-        X2BuildBorderList((tid & 1) ? in - 1 : 0, in, col ? g.wout : g.hout, sL[tid]);
-    }
+    const float* c = lists.interior;
     {
+        // zero rows where the band's window leaves the image, zero columns either side of a row, as 8-byte stores (wout is even)
+        const int32_t rowsTop = hLo - hBase, rowsAll = 2 * (yhB - yhA) + 6;
+        const int32_t rowsZero = rowsAll - nRows; // above the first image row and below the last
+        for (int32_t i = tid; i < rowsZero * (pitch / 4); i += nt) {
+            const int32_t r = i / (pitch / 4), k = i - r * (pitch / 4);
+            const int32_t row = r < rowsTop ? r : nRows + r;
+            *reinterpret_cast<float4*>(sG + row * pitch + 4 * k) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
         float* sRow0 = sG + (hLo - hBase) * pitch;
-        const int32_t padRight = pitch - kX2Pad - g.wout, padCols = kX2Pad + padRight;
-        for (int32_t i = tid; i < nRows * padCols; i += nt) {
-            const int32_t r = i / padCols, k = i - r * padCols;
-            sRow0[r * pitch + (k < kX2Pad ? k : g.wout + k)] = 0.0f;
+        const int32_t padPairs = (pitch - g.wout) / 2;
+        for (int32_t i = tid; i < nRows * padPairs; i += nt) {
+            const int32_t r = i / padPairs, k = i - r * padPairs;
+            *reinterpret_cast<float2*>(sRow0 + r * pitch + (k < kX2Pad / 2 ? 2 * k : g.wout + 2 * k)) = make_float2(0.0f, 0.0f);
         }
         const T* pg = go + plane * (static_cast<int64_t>(g.hout) * g.wout) + static_cast<int64_t>(hLo) * g.wout;
         float* sBase = sRow0 + kX2Pad;
+        // a thread keeps its position in a row and steps over rows: one division per thread instead of one per load
         if (vecLoad) {
             constexpr int VL = 16 / sizeof(T);
             const int32_t packs = g.wout / VL;
-            for (int32_t i = tid; i < nRows * packs; i += nt) {
-                const int32_t r = i / packs, p = i - r * packs;
-                float v[VL];
-                LoadPackLdg<T, VL>(pg + r * g.wout + p * VL, v);
-                float4* dst = reinterpret_cast<float4*>(sBase + r * pitch + p * VL);
+            const int32_t lanesPerRow = min(packs, nt), rowsPerPass = nt / lanesPerRow;
+            const int32_t r0 = tid / lanesPerRow, p0 = tid - r0 * lanesPerRow;
+            if (r0 < rowsPerPass) {
+                for (int32_t r = r0; r < nRows; r += rowsPerPass) {
+                    for (int32_t p = p0; p < packs; p += lanesPerRow) {
+                        float v[VL];
+                        LoadPackLdg<T, VL>(pg + r * g.wout + p * VL, v);
+                        float4* dst = reinterpret_cast<float4*>(sBase + r * pitch + p * VL);
 #pragma unroll
-                for (int m = 0; m < VL / 4; ++m) {
-                    dst[m] = make_float4(v[4 * m], v[4 * m + 1], v[4 * m + 2], v[4 * m + 3]);
+                        for (int m = 0; m < VL / 4; ++m) {
+                            dst[m] = make_float4(v[4 * m], v[4 * m + 1], v[4 * m + 2], v[4 * m + 3]);
+                        }
+                    }
                 }
             }
         } else {
-            for (int32_t i = tid; i < nRows * g.wout; i += nt) {
-                const int32_t r = i / g.wout, w = i - r * g.wout;
-                sBase[r * pitch + w] = DType<T>::Load(pg + r * g.wout + w);
+            const int32_t lanesPerRow = min(g.wout, nt), rowsPerPass = nt / lanesPerRow;
+            const int32_t r0 = tid / lanesPerRow, w0 = tid - r0 * lanesPerRow;
+            if (r0 < rowsPerPass) {
+                for (int32_t r = r0; r < nRows; r += rowsPerPass) {
+                    for (int32_t w = w0; w < g.wout; w += lanesPerRow) {
+                        sBase[r * pitch + w] = DType<T>::Load(pg + r * g.wout + w);
+                    }
+                }
             }
         }
     }
@@ -851,8 +897,9 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __re
     const int32_t pairs = (g.win + 1) / 2;
     const int32_t bandN = yhB - yhA;
     const int32_t nPair = bandN * pairs;
-    const int32_t borderBase = (nPair + 31) & ~31;
-    const int32_t total = borderBase + 2 * bandN;
+    const int32_t borderBase = (nPair + 31) & ~31;      // first columns from here, one per row of the band
+    const int32_t borderBase1 = borderBase + ((bandN + 31) & ~31); // last columns: other warps, so that the slot
+    const int32_t total = borderBase1 + bandN;                 // tests below are uniform over a warp
     T* pgi = gi + (plane * g.hin + yhA) * g.win;
     for (int32_t item = tid; item < total; item += nt) {
         if (item < nPair) {
@@ -861,12 +908,10 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __re
             const float* sw = sG + 4 * q; // grads column 4q - 4
             float a0 = 0.0f, a1 = 0.0f;
             if (yh != 0 && yh != g.hin - 1) {
-                const int32_t h0 = 2 * yh - 3;
+                const float4* row = reinterpret_cast<const float4*>(sw + (2 * yh - 3 - hBase) * pitch);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int32_t h = h0 + j;
-                    if (h >= 0 && h < g.hout) {
-                        const float4* row = reinterpret_cast<const float4*>(sw + (h - hBase) * pitch);
+                for (int j = 0; j < 8; ++j, row += pitch / 4) {
+                    { // rows above or below the image are zero rows: their terms add nothing
                         const float4 A = row[0], B = row[1], C = row[2];
                         const float v[12] = {A.x, A.y, A.z, A.w, B.x, B.y, B.z, B.w, C.x, C.y, C.z, C.w};
                         float gc[10];
@@ -919,77 +964,85 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __re
                 po[yw0 + 1] = DType<T>::FromF(a1);
             }
         } else if (item >= borderBase) {
-            // a first or last column: its five grads columns and up to three coefficients each, in registers
-            const int32_t b = item - borderBase;
-            const int32_t r = b >> 1, side = b & 1;
+            // a first or last column of an interior row: the terms of its walk as one list
+            const int32_t side = item >= borderBase1 ? 1 : 0;
+            const int32_t r = item - (side ? borderBase1 : borderBase);
+            if (r >= bandN) {
+                continue;
+            }
             const int32_t yh = yhA + r;
+            if (yh == 0 || yh == g.hin - 1) {
+                continue; // the four corners of a plane: Bicubic2dBwdX2CornerKernel
+            }
             const X2BorderList& cols = sL[side];
-            const uint32_t cmask = cols.mask;
-            float cw[kX2Groups * kX2Slots];
-            int32_t wcol[kX2Groups];
-#pragma unroll
-            for (int k = 0; k < kX2Groups * kX2Slots; ++k) {
-                cw[k] = cols.coef[k];
-            }
-#pragma unroll
-            for (int m = 0; m < kX2Groups; ++m) { // a group without terms reads a zero column and adds nothing
-                wcol[m] = ((cmask >> (m * kX2Slots)) & 7u) ? cols.start + m : -1;
-            }
             float add = 0.0f;
-            auto rowTerms = [&](const float* prow, float ch) {
+            int32_t wI[kX2Flat];
+            float cw[kX2Flat];
 #pragma unroll
-                for (int m = 0; m < kX2Groups; ++m) {
-                    const float gch = Mul(prow[wcol[m]], ch);
+            for (int e = 0; e < kX2Flat; ++e) {
+                wI[e] = cols.flatIdx[e];
+                cw[e] = cols.flatCoef[e];
+            }
+            const float* prow = sG + (2 * yh - 3 - hBase) * pitch + kX2Pad;
 #pragma unroll
-                    for (int t = 0; t < kX2Slots; ++t) {
-                        if (cmask & (1u << (m * kX2Slots + t))) {
-                            add = Add(add, Mul(gch, cw[m * kX2Slots + t]));
-                        }
-                    }
-                }
-            };
-            if (yh != 0 && yh != g.hin - 1) {
-                const int32_t h0 = 2 * yh - 3;
+            for (int j = 0; j < 8; ++j, prow += pitch) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int32_t h = h0 + j;
-                    if (h >= 0 && h < g.hout) {
-                        rowTerms(sG + (h - hBase) * pitch + kX2Pad, c[j]);
-                    }
-                }
-            } else {
-                // a corner: (row, column, row tap, column tap) order puts the row taps of a grads value outside its
-                // column taps
-                const X2BorderList& rows = sL[yh == 0 ? 2 : 3];
-                const uint32_t rmask = rows.mask;
-#pragma unroll 1
-                for (int mr = 0; mr < kX2Groups; ++mr) {
-                    const uint32_t bits = (rmask >> (mr * kX2Slots)) & 7u;
-                    if (bits == 0) {
-                        continue;
-                    }
-                    const float* prow = sG + (rows.start + mr - hBase) * pitch + kX2Pad;
-#pragma unroll
-                    for (int m = 0; m < kX2Groups; ++m) {
-                        const float gv = prow[wcol[m]];
-#pragma unroll 1
-                        for (int i = 0; i < kX2Slots; ++i) {
-                            if (bits & (1u << i)) {
-                                const float gch = Mul(gv, rows.coef[mr * kX2Slots + i]);
-#pragma unroll
-                                for (int t = 0; t < kX2Slots; ++t) {
-                                    if (cmask & (1u << (m * kX2Slots + t))) {
-                                        add = Add(add, Mul(gch, cw[m * kX2Slots + t]));
-                                    }
-                                }
-                            }
-                        }
-                    }
+                for (int e = 0; e < kX2Flat; ++e) {
+                    add = Add(add, Mul(Mul(prow[wI[e]], c[j]), cw[e]));
                 }
             }
             pgi[static_cast<int64_t>(r) * g.win + (side ? g.win - 1 : 0)] = DType<T>::FromF(add);
         }
     }
+}
+
+// The four corners of every plane at 2x: both walks have clamped taps, so a grads value meets up to three row
+// coefficients times up to three column coefficients, row taps outside column taps. One thread per plane and corner,
+// the corner uniform over a block (blockIdx.y), so every slot test below is uniform; grads straight from global memory.
+template <typename T>
+__global__ void __launch_bounds__(128) Bicubic2dBwdX2CornerKernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g,
+                                                                  int64_t planes, const X2BorderLists lists)
+{
+    const int corner = blockIdx.y; // 0 (0, 0), 1 (0, win - 1), 2 (hin - 1, 0), 3 (hin - 1, win - 1)
+    const int64_t plane = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (plane >= planes) {
+        return;
+    }
+    const X2BorderList& rows = lists.l[2 + (corner >> 1)];
+    const X2BorderList& cols = lists.l[corner & 1];
+    const uint32_t rmask = rows.mask, cmask = cols.mask;
+    const T* pg = go + plane * (static_cast<int64_t>(g.hout) * g.wout);
+    float add = 0.0f;
+#pragma unroll
+    for (int mr = 0; mr < kX2Groups; ++mr) {
+        const uint32_t rbits = (rmask >> (mr * kX2Slots)) & 7u;
+        if (rbits == 0) {
+            continue;
+        }
+        const T* prow = pg + static_cast<int64_t>(rows.start + mr) * g.wout;
+#pragma unroll
+        for (int m = 0; m < kX2Groups; ++m) {
+            const uint32_t cbits = (cmask >> (m * kX2Slots)) & 7u;
+            if (cbits == 0) {
+                continue;
+            }
+            const float gv = DType<T>::Load(prow + cols.start + m);
+#pragma unroll
+            for (int i = 0; i < kX2Slots; ++i) {
+                if (rbits & (1u << i)) {
+                    const float gch = Mul(gv, rows.coef[mr * kX2Slots + i]);
+#pragma unroll
+                    for (int t = 0; t < kX2Slots; ++t) {
+                        if (cbits & (1u << t)) {
+                            add = Add(add, Mul(gch, cols.coef[m * kX2Slots + t]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    const int32_t yh = (corner >> 1) ? g.hin - 1 : 0, yw = (corner & 1) ? g.win - 1 : 0;
+    gi[(plane * g.hin + yh) * g.win + yw] = DType<T>::FromF(add);
 }
 
 // Band height and block size of the 2x kernel: full lanes first, then little halo. false: the kernel does not apply.
@@ -1015,7 +1068,7 @@ bool PlanBwdX2(const BicubicGeom& g, bool nhwc, X2Launch* out)
             if (smem > 48 * 1024) {
                 continue;
             }
-            const int64_t items = ((static_cast<int64_t>(bh) * pairs + 31) & ~31LL) + 2 * bh;
+            const int64_t items = ((static_cast<int64_t>(bh) * pairs + 31) & ~31LL) + ((bh + 31) & ~31) + bh;
             const double slots = static_cast<double>(nb) * static_cast<double>(CeilDiv(items, threads)) * threads;
             const double score = static_cast<double>(g.hin) * pairs / slots / (1.0 + 0.08 * (2.0 * bh + 6.0) / (2.0 * bh));
             if (score > best) {
@@ -1231,12 +1284,32 @@ cudaError_t Bicubic2dBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh,
         CountLaunch();
     };
     X2Launch x2;
-    if (PlanBwdX2(g, nhwc, &x2)) {
+    X2BorderLists lists;
+    bool useX2 = PlanBwdX2(g, nhwc, &x2);
+    if (useX2) {
+        lists.l[0] = x2host::BorderList(0, g.win, g.wout);
+        lists.l[1] = x2host::BorderList(g.win - 1, g.win, g.wout);
+        lists.l[2] = x2host::BorderList(0, g.hin, g.hout);
+        lists.l[3] = x2host::BorderList(g.hin - 1, g.hin, g.hout);
+        for (const X2BorderList& l : lists.l) {
+            useX2 = useX2 && l.terms <= kX2Flat;
+        }
+        for (int k = 0; k < 8; ++k) {
+            lists.interior[k] = x2host::PointCoeff(std::fabs(0.5f * static_cast<float>(k) - 1.75f));
+        }
+    }
+    if (useX2) {
         const int64_t planes = g.rows / g.hin;
         OPSCV_DISPATCH_DT(dt, T, {
             const int vec = (g.wout % (16 / sizeof(T)) == 0 && Aligned(go, 16)) ? 1 : 0;
-            Bicubic2dBwdX2Kernel<T><<<static_cast<unsigned>(planes * x2.bands), x2.threads, x2.smem, s>>>(
-                static_cast<const T*>(go), static_cast<T*>(gi), g, x2.bandRows, x2.bands, x2.pitch, vec);
+            auto k = Bicubic2dBwdX2Kernel<T>;
+            k<<<static_cast<unsigned>(planes * x2.bands), x2.threads, x2.smem, s>>>(
+                static_cast<const T*>(go), static_cast<T*>(gi), g, x2.bandRows, x2.bands, x2.pitch, vec, lists);
+        });
+        CountLaunch();
+        OPSCV_DISPATCH_DT(dt, T, {
+            Bicubic2dBwdX2CornerKernel<T><<<dim3(static_cast<unsigned>(CeilDiv(planes, 128)), 4, 1), 128, 0, s>>>(
+                static_cast<const T*>(go), static_cast<T*>(gi), g, planes, lists);
         });
         CountLaunch();
         return cudaGetLastError();
