@@ -1045,7 +1045,7 @@ __global__ void __launch_bounds__(128) Bicubic2dBwdX2CornerKernel(const T* __res
     gi[(plane * g.hin + yh) * g.win + yw] = DType<T>::FromF(add);
 }
 
-// Band height and block size of the 2x kernel: full lanes first, then little halo. false: the kernel does not apply.
+// Band height and block size of the 2x kernel. false: the kernel does not apply.
 struct X2Launch {
     int32_t bandRows, bands, threads, pitch;
     size_t smem;
@@ -1058,27 +1058,29 @@ bool PlanBwdX2(const BicubicGeom& g, bool nhwc, X2Launch* out)
     }
     const int32_t pitch = (g.wout + 12 + 3) & ~3;
     const int32_t pairs = (g.win + 1) / 2;
+    // Bands as tall as 32 KB of staged rows allow (measured at 56 x 56 planes: taller bands stage fewer halo rows and
+    // pay the per-block set-up less often, 301 us at 28 rows against 337 us at 14; a whole plane per block, 58 KB,
+    // leaves too few blocks per SM: 341 us), equal over the plane; then the block size that wastes the fewest warp
+    // slots over the passes of the item loop.
+    const size_t rowBytes = static_cast<size_t>(pitch) * sizeof(float);
+    int32_t bh = static_cast<int32_t>(std::min<int64_t>((32 * 1024 / rowBytes - 6) / 2, g.hin));
+    if (bh < 1) {
+        bh = 1;
+    }
+    if ((2 * bh + 6) * rowBytes > 48 * 1024) {
+        return false;
+    }
+    const int32_t nb = (g.hin + bh - 1) / bh;
+    bh = (g.hin + nb - 1) / nb;
+    const int64_t warpItems = CeilDiv(static_cast<int64_t>(bh) * pairs, 32) + 2 * CeilDiv(bh, 32);
     double best = 0.0;
     for (int32_t threads = 128; threads <= kX2Threads; threads += 32) {
-        for (int32_t passes = 1; passes <= 3; ++passes) {
-            int32_t bh = std::min(std::max(passes * threads / pairs, 1), g.hin);
-            const int32_t nb = (g.hin + bh - 1) / bh;
-            bh = (g.hin + nb - 1) / nb;
-            const size_t smem = static_cast<size_t>(2 * bh + 6) * pitch * sizeof(float);
-            if (smem > 48 * 1024) {
-                continue;
-            }
-            const int64_t items = ((static_cast<int64_t>(bh) * pairs + 31) & ~31LL) + ((bh + 31) & ~31) + bh;
-            const double slots = static_cast<double>(nb) * static_cast<double>(CeilDiv(items, threads)) * threads;
-            const double score = static_cast<double>(g.hin) * pairs / slots / (1.0 + 0.08 * (2.0 * bh + 6.0) / (2.0 * bh));
-            if (score > best) {
-                best = score;
-                *out = X2Launch{bh, nb, threads, pitch, smem};
-            }
+        const int64_t warps = threads / 32;
+        const double fill = static_cast<double>(warpItems) / static_cast<double>(CeilDiv(warpItems, warps) * warps);
+        if (fill > best) { // ties go to the smaller block: more blocks per SM to overlap staging with arithmetic
+            best = fill;
+            *out = X2Launch{bh, nb, threads, pitch, (2 * bh + 6) * rowBytes};
         }
-    }
-    if (best == 0.0) {
-        return false;
     }
     const int64_t planes = g.rows / g.hin;
     return planes * out->bands <= INT32_MAX;
