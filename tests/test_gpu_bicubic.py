@@ -226,3 +226,26 @@ def test_bicubic_backward_at_2x_special_values(ops, oracle, dev):
     gz = ops.upsample_bicubic2d_backward(z.to(dev), (8, 8), (1, 1, 4, 4), False).cpu().numpy()
     rz = oracle.bicubic2d_bwd(z.numpy(), (4, 4), False, definition="gather")
     assert np.array_equal(gz.view(np.uint32), rz.view(np.uint32))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", X2_SHAPES + [(1, 2, 1, 2), (2, 3, 1, 8), (1, 1, 70, 64), (2, 2, 33, 6)])
+def test_bicubic_forward_at_2x(ops, oracle, dev, dtype, shape):
+    """The staged 2x forward (NCHW, half-pixel, even input width; odd widths run the general kernel): the oracle's
+    bits in fp32, borders by replicated rows and columns."""
+    n, c, hi, wi = shape
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(142)), dtype)
+    y = ops.upsample_bicubic2d(x.to(dev), (2 * hi, 2 * wi), False)
+    check(y, oracle.bicubic2d_fwd(x32, (2 * hi, 2 * wi), False), dtype, exact=(dtype == torch.float32))
+    flat = torch.zeros(x.numel() + 1, dtype=dtype)
+    flat[1:] = x.flatten()
+    xv = flat.to(dev)[1:].view(n, c, hi, wi)  # a base that is not 16-byte aligned: single-element staging loads
+    assert torch.equal(ops.upsample_bicubic2d(xv, (2 * hi, 2 * wi), False), y)
+    xs = torch.randn((n, c, hi, wi), generator=gen(143))
+    xs[0, 0, 0, 0] = float("inf")
+    xs[-1, -1, -1, -1] = float("nan")
+    ys = ops.upsample_bicubic2d(xs.to(dev), (2 * hi, 2 * wi), False).cpu().numpy()
+    ref = oracle.bicubic2d_fwd(xs.numpy(), (2 * hi, 2 * wi), False)
+    assert np.array_equal(np.isnan(ys), np.isnan(ref)) and np.array_equal(np.isinf(ys), np.isinf(ref))
+    fin = np.isfinite(ref)
+    assert np.array_equal(ys[fin], ref[fin])
