@@ -844,16 +844,72 @@ inline X2BorderList BorderList(int32_t yIdx, int32_t in, int32_t out)
 }
 } // namespace x2host
 
+// The four corners of a plane at 2x: both walks have clamped taps, so a grads value meets up to three row
+// coefficients times up to three column coefficients, row taps outside column taps. One thread per plane and corner,
+// the corner uniform over a block, so every slot test is uniform; grads straight from global memory.
+template <typename T>
+__device__ __forceinline__ void X2Corner(const T* __restrict__ go, T* __restrict__ gi, const BicubicGeom& g, int64_t plane,
+                                         int corner, const X2BorderLists& lists)
+{
+    // corner: 0 (0, 0), 1 (0, win - 1), 2 (hin - 1, 0), 3 (hin - 1, win - 1)
+    const X2BorderList& rows = lists.l[2 + (corner >> 1)];
+    const X2BorderList& cols = lists.l[corner & 1];
+    const uint32_t rmask = rows.mask, cmask = cols.mask;
+    const T* pg = go + plane * (static_cast<int64_t>(g.hout) * g.wout);
+    float add = 0.0f;
+#pragma unroll
+    for (int mr = 0; mr < kX2Groups; ++mr) {
+        const uint32_t rbits = (rmask >> (mr * kX2Slots)) & 7u;
+        if (rbits == 0) {
+            continue;
+        }
+        const T* prow = pg + static_cast<int64_t>(rows.start + mr) * g.wout;
+#pragma unroll
+        for (int m = 0; m < kX2Groups; ++m) {
+            const uint32_t cbits = (cmask >> (m * kX2Slots)) & 7u;
+            if (cbits == 0) {
+                continue;
+            }
+            const float gv = DType<T>::Load(prow + cols.start + m);
+#pragma unroll
+            for (int i = 0; i < kX2Slots; ++i) {
+                if (rbits & (1u << i)) {
+                    const float gch = Mul(gv, rows.coef[mr * kX2Slots + i]);
+#pragma unroll
+                    for (int t = 0; t < kX2Slots; ++t) {
+                        if (cbits & (1u << t)) {
+                            add = Add(add, Mul(gch, cols.coef[m * kX2Slots + t]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    const int32_t yh = (corner >> 1) ? g.hin - 1 : 0, yw = (corner & 1) ? g.win - 1 : 0;
+    gi[(plane * g.hin + yh) * g.win + yw] = DType<T>::FromF(add);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g,
                                                                    int32_t bandRows, int32_t bands, int32_t pitch,
-                                                                   int32_t vecLoad, const X2BorderLists lists)
+                                                                   int32_t vecLoad, const X2BorderLists lists,
+                                                                   int64_t planes, int32_t cornerBlocks)
 {
     extern __shared__ __align__(16) float sG[]; // (2 * bandRows + 6) grads rows of `pitch` floats
     const X2BorderList* sL = lists.l;
     const int32_t tid = threadIdx.x, nt = blockDim.x;
-    const int64_t plane = blockIdx.x / bands;
-    const int32_t band = static_cast<int32_t>(blockIdx.x - plane * bands);
+    if (static_cast<int32_t>(blockIdx.x) < cornerBlocks) {
+        // the first blocks of the grid take the corners of all planes (four blocks per nt planes); they are resident
+        // next to band blocks from the start, so their chains of dependent additions cost no time of their own
+        const int64_t cp = static_cast<int64_t>(blockIdx.x >> 2) * nt + tid;
+        if (cp < planes) {
+            X2Corner<T>(go, gi, g, cp, static_cast<int>(blockIdx.x & 3), lists);
+        }
+        return;
+    }
+    const uint32_t bandBlock = blockIdx.x - cornerBlocks;
+    const int64_t plane = bandBlock / bands;
+    const int32_t band = static_cast<int32_t>(bandBlock - plane * bands);
     const int32_t yhA = band * bandRows, yhB = min(yhA + bandRows, g.hin);
     const int32_t hBase = 2 * yhA - 3; // grads row of shared-memory row 0
     const int32_t hLo = max(hBase, 0), hHi = min(2 * (yhB - 1) + 4, g.hout - 1);
@@ -988,7 +1044,7 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __re
             }
             const int32_t yh = yhA + r;
             if (yh == 0 || yh == g.hin - 1) {
-                continue; // the four corners of a plane: Bicubic2dBwdX2CornerKernel
+                continue; // the four corners of a plane: the corner blocks
             }
             const X2BorderList& cols = sL[side];
             float add = 0.0f;
@@ -1164,55 +1220,6 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __re
     }
 }
 
-// The four corners of every plane at 2x: both walks have clamped taps, so a grads value meets up to three row
-// coefficients times up to three column coefficients, row taps outside column taps. One thread per plane and corner,
-// the corner uniform over a block (blockIdx.y), so every slot test below is uniform; grads straight from global memory.
-template <typename T>
-__global__ void __launch_bounds__(128) Bicubic2dBwdX2CornerKernel(const T* __restrict__ go, T* __restrict__ gi, BicubicGeom g,
-                                                                  int64_t planes, const X2BorderLists lists)
-{
-    const int corner = blockIdx.y; // 0 (0, 0), 1 (0, win - 1), 2 (hin - 1, 0), 3 (hin - 1, win - 1)
-    const int64_t plane = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (plane >= planes) {
-        return;
-    }
-    const X2BorderList& rows = lists.l[2 + (corner >> 1)];
-    const X2BorderList& cols = lists.l[corner & 1];
-    const uint32_t rmask = rows.mask, cmask = cols.mask;
-    const T* pg = go + plane * (static_cast<int64_t>(g.hout) * g.wout);
-    float add = 0.0f;
-#pragma unroll
-    for (int mr = 0; mr < kX2Groups; ++mr) {
-        const uint32_t rbits = (rmask >> (mr * kX2Slots)) & 7u;
-        if (rbits == 0) {
-            continue;
-        }
-        const T* prow = pg + static_cast<int64_t>(rows.start + mr) * g.wout;
-#pragma unroll
-        for (int m = 0; m < kX2Groups; ++m) {
-            const uint32_t cbits = (cmask >> (m * kX2Slots)) & 7u;
-            if (cbits == 0) {
-                continue;
-            }
-            const float gv = DType<T>::Load(prow + cols.start + m);
-#pragma unroll
-            for (int i = 0; i < kX2Slots; ++i) {
-                if (rbits & (1u << i)) {
-                    const float gch = Mul(gv, rows.coef[mr * kX2Slots + i]);
-#pragma unroll
-                    for (int t = 0; t < kX2Slots; ++t) {
-                        if (cbits & (1u << t)) {
-                            add = Add(add, Mul(gch, cols.coef[m * kX2Slots + t]));
-                        }
-                    }
-                }
-            }
-        }
-    }
-    const int32_t yh = (corner >> 1) ? g.hin - 1 : 0, yw = (corner & 1) ? g.win - 1 : 0;
-    gi[(plane * g.hin + yh) * g.win + yw] = DType<T>::FromF(add);
-}
-
 // Band height and block size of the 2x kernel. false: the kernel does not apply.
 struct X2Launch {
     int32_t bandRows, bands, threads, pitch;
@@ -1251,7 +1258,7 @@ bool PlanBwdX2(const BicubicGeom& g, bool nhwc, X2Launch* out)
         }
     }
     const int64_t planes = g.rows / g.hin;
-    return planes * out->bands <= INT32_MAX;
+    return planes * out->bands + 4 * CeilDiv(planes, out->threads) <= INT32_MAX;
 }
 
 dim3 RowGrid(int64_t rows, int64_t inner)
@@ -1497,14 +1504,10 @@ cudaError_t Bicubic2dBwd(Dt dt, Layout lay, const void* go, void* gi, Shape4 sh,
         const int64_t planes = g.rows / g.hin;
         OPSCV_DISPATCH_DT(dt, T, {
             const int vec = (g.wout % (16 / sizeof(T)) == 0 && Aligned(go, 16)) ? 1 : 0;
-            auto k = Bicubic2dBwdX2Kernel<T>;
-            k<<<static_cast<unsigned>(planes * x2.bands), x2.threads, x2.smem, s>>>(
-                static_cast<const T*>(go), static_cast<T*>(gi), g, x2.bandRows, x2.bands, x2.pitch, vec, lists);
-        });
-        CountLaunch();
-        OPSCV_DISPATCH_DT(dt, T, {
-            Bicubic2dBwdX2CornerKernel<T><<<dim3(static_cast<unsigned>(CeilDiv(planes, 128)), 4, 1), 128, 0, s>>>(
-                static_cast<const T*>(go), static_cast<T*>(gi), g, planes, lists);
+            const int32_t cornerBlocks = 4 * static_cast<int32_t>(CeilDiv(planes, x2.threads));
+            Bicubic2dBwdX2Kernel<T><<<static_cast<unsigned>(planes * x2.bands + cornerBlocks), x2.threads, x2.smem, s>>>(
+                static_cast<const T*>(go), static_cast<T*>(gi), g, x2.bandRows, x2.bands, x2.pitch, vec, lists, planes,
+                cornerBlocks);
         });
         CountLaunch();
         return cudaGetLastError();
