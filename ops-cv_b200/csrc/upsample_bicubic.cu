@@ -15,6 +15,11 @@
 // tap by tap with clamped destinations. The sum has a fixed order, so results are reproducible from run to run
 // and fp32 results carry the bits of that kernel run serially. The column side of the walk is the same for every
 // row, so each thread evaluates it once into a shared-memory list.
+//
+// Calls at exactly 2x on NCHW tensors (scales 0.5 with half-pixel coordinates: every source coordinate is exact and
+// the coefficients are a handful of constants, evaluated on the host) have kernels of their own in both directions:
+// Bicubic2dFwdX2Kernel and Bicubic2dBwdX2Kernel stage a band of rows in shared memory as fp32 once and work from
+// register windows; their terms, order and rounding are those of the general kernels.
 #include <algorithm>
 #include <vector>
 
