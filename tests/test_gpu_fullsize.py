@@ -55,6 +55,26 @@ def test_cfg2_fpn_upsample_fp16(ops, oracle, dev):
     assert (s_in - s_out).abs().max().item() <= 2.0 ** -10 * gb.float().abs().sum((2, 3)).max().item()
 
 
+def test_adj2_bicubic_2x_fp16(ops, oracle, dev):
+    """The exactly-2x bicubic kernels at the benchmark shapes: first and last image against the oracle, a constant
+    image stays constant (the four coefficients of a set sum to one up to their rounding), the backward preserves
+    the sum of the gradient per plane, and a second call gives the same bits."""
+    n, c, hi, wi, ho, wo = 32, 256, 56, 56, 112, 112
+    x = torch.randn((n, c, hi, wi), generator=gen(1260)).to(torch.float16)
+    go = torch.randn((n, c, ho, wo), generator=gen(1261)).to(torch.float16)
+    xd, god = x.to(dev), go.to(dev)
+    y = ops.upsample_bicubic2d(xd, (ho, wo), False)
+    check(ends(y), oracle.bicubic2d_fwd(ends(x).float().numpy(), (ho, wo), False), torch.float16)
+    const = ops.upsample_bicubic2d(torch.full((n, c, hi, wi), 0.75, dtype=torch.float16, device=dev), (ho, wo), False)
+    assert (const.float() - 0.75).abs().max().item() <= 2.0 ** -11
+    gi = ops.upsample_bicubic2d_backward(god, (ho, wo), (n, c, hi, wi), False)
+    assert torch.equal(gi.view(torch.int16),
+                       ops.upsample_bicubic2d_backward(god, (ho, wo), (n, c, hi, wi), False).view(torch.int16))
+    check(ends(gi), oracle.bicubic2d_bwd(ends(go).float().numpy(), (hi, wi), False, definition="gather"), torch.float16)
+    s_in, s_out = god.float().sum((2, 3)), gi.float().sum((2, 3))
+    assert (s_in - s_out).abs().max().item() <= 2.0 ** -9 * gi.float().abs().sum((2, 3)).max().item()
+
+
 def test_cfg3_bicubic_aa_fp32(ops, oracle, dev):
     n, c, hi, wi, ho, wo = 64, 3, 1024, 1024, 224, 224
     x = torch.randint(0, 256, (n, c, hi, wi), generator=gen(1238)).float() / 255
