@@ -1073,11 +1073,11 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dBwdX2Kernel(const T* __re
     }
 }
 
-// ---- forward at exactly 2x (half-pixel coordinates, scales 0.5), NCHW, even input width --------------------------
+// ---- forward at exactly 2x (half-pixel coordinates, scales 0.5), NCHW ---------------------------------------------
 // Output index 2i has the source coordinate i - 0.25 (window i - 2 .. i + 1, fraction 0.75), output index 2i + 1 has
 // i + 0.25 (window i - 1 .. i + 2, fraction 0.25), all exact: two sets of four coefficients serve the whole image
 // and come from the host. A block stages the source rows of a band (with the two rows above and below it, clamped)
-// as fp32 with two replicated columns either side, so that neither pass clamps an index; pass A forms the
+// as fp32 with replicated columns either side, so that neither pass clamps an index; pass A forms the
 // horizontal sums of every staged row, eight adjacent output columns per thread from eight source values (four
 // 8-byte shared-memory loads, two 16-byte stores); pass B gives a thread four adjacent columns of the four output rows
 // of two source rows: six 16-byte loads of sums, four stores. Sums and products in the order of the general kernels.
@@ -1086,7 +1086,8 @@ struct X2FwdCoef {
     float odd[4];  // FwdCoeff(0.25): output indices 2i + 1
 };
 
-template <typename T>
+// FULL: every group of four output columns is whole and every row 8- or 16-byte aligned (one store per group).
+template <typename T, bool FULL>
 __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __restrict__ x, T* __restrict__ y, BicubicGeom g,
                                                                    int32_t bandRows, int32_t bands, int32_t vecIn,
                                                                    int32_t vecOut, const X2FwdCoef cf, const FastDiv halfPacks,
@@ -1094,7 +1095,8 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __re
 {
     extern __shared__ __align__(16) float sm[];
     const int32_t tid = threadIdx.x, nt = blockDim.x;
-    const int32_t pitchX = g.win + 4;
+    const int32_t pitchX = g.win + 4 + (g.win & 1); // two replicated columns left, two or three right (even pitch)
+    const int32_t packs = (g.wout + 3) / 4, pitchH = 4 * packs; // an odd input width leaves the last pack half used
     const int64_t plane = blockIdx.x / bands;
     const int32_t band = static_cast<int32_t>(blockIdx.x - plane * bands);
     const int32_t rA = band * bandRows, rB = min(rA + bandRows, g.hin);
@@ -1107,7 +1109,13 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __re
             const int32_t sl = i >> 1, right = i & 1;
             const int32_t row = ClampIdx32(rA - 2 + sl, g.hin - 1);
             const float v = DType<T>::Load(px + static_cast<int64_t>(row) * g.win + (right ? g.win - 1 : 0));
-            *reinterpret_cast<float2*>(sX + sl * pitchX + (right ? g.win + 2 : 0)) = make_float2(v, v);
+            if (right) {
+                for (int32_t k = g.win + 2; k < pitchX; ++k) {
+                    sX[sl * pitchX + k] = v;
+                }
+            } else {
+                *reinterpret_cast<float2*>(sX + sl * pitchX) = make_float2(v, v);
+            }
         }
         if (vecIn) {
             constexpr int VL = 16 / sizeof(T);
@@ -1142,7 +1150,6 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __re
         }
     }
     __syncthreads();
-    const int32_t packs = g.wout / 4;
     // Both passes use the packed fp32 operations: two sums that share their coefficients go through one instruction
     // per product and per addition (AddProduct2 keeps the product's own rounding), so the bits are the scalar ones.
     const F2 E0 = MakeF2(cf.even[0], cf.even[0]), E1 = MakeF2(cf.even[1], cf.even[1]), E2 = MakeF2(cf.even[2], cf.even[2]),
@@ -1168,7 +1175,7 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __re
         const float2 a = src[0], b = src[1], c = src[2];
         const F2 A = MakeF2(a.x, a.y), B = MakeF2(b.x, b.y), C = MakeF2(c.x, c.y);
         const F2 AB = MakeF2(a.y, b.x), BC = MakeF2(b.y, c.x);
-        F2* dst = reinterpret_cast<F2*>(sH + sl * g.wout + 4 * q);
+        F2* dst = reinterpret_cast<F2*>(sH + sl * pitchH + 4 * q);
         struct alignas(16) Quad {
             F2 lo, hi;
         };
@@ -1188,17 +1195,27 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __re
     // pass B: four adjacent columns of the four output rows of two source rows (two where the band ends)
     T* py = y + (plane * g.hout + 2 * rA) * static_cast<int64_t>(g.wout);
     const int32_t rows = rB - rA;
-    const int32_t step = g.wout / 4;
-    auto store = [&](T* dst, F2 lo, F2 hi) { // lo = columns (0, 2), hi = columns (1, 3) of the group
+    const int32_t step = packs;
+    // lo = columns (0, 2), hi = columns (1, 3) of the group; valid = columns of the group inside the row (4, or 2 in
+    // the last group of a row whose width is not a multiple of 4); vecOut = elements per store the rows allow
+    auto store = [&](T* dst, F2 lo, F2 hi, int32_t valid) {
         float vals[4];
         SplitF2(lo, vals[0], vals[2]);
         SplitF2(hi, vals[1], vals[3]);
-        if (vecOut) {
+        if (FULL) {
             StorePack<T, 4>(dst, vals);
+        } else if (vecOut == 2) {
+            const float a[2] = {vals[0], vals[1]}, b[2] = {vals[2], vals[3]};
+            StorePack<T, 2>(dst, a);
+            if (valid > 2) {
+                StorePack<T, 2>(dst + 2, b);
+            }
         } else {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-                dst[v] = DType<T>::FromF(vals[v]);
+                if (v < valid) {
+                    dst[v] = DType<T>::FromF(vals[v]);
+                }
             }
         }
     };
@@ -1208,19 +1225,20 @@ __global__ void __launch_bounds__(kX2Threads) Bicubic2dFwdX2Kernel(const T* __re
         if (r >= rows || q < 0 || q >= packs) {
             continue; // as in pass A
         }
-        const float4* col = reinterpret_cast<const float4*>(sH + r * g.wout + 4 * q); // slots r .. r + 5
+        const float4* col = reinterpret_cast<const float4*>(sH + r * pitchH + 4 * q); // slots r .. r + 5
         const float4 R0 = col[0], R1 = col[step], R2 = col[2 * step], R3 = col[3 * step], R4 = col[4 * step];
         const F2 l0 = MakeF2(R0.x, R0.y), h0 = MakeF2(R0.z, R0.w), l1 = MakeF2(R1.x, R1.y), h1 = MakeF2(R1.z, R1.w),
                  l2 = MakeF2(R2.x, R2.y), h2 = MakeF2(R2.z, R2.w), l3 = MakeF2(R3.x, R3.y), h3 = MakeF2(R3.z, R3.w),
                  l4 = MakeF2(R4.x, R4.y), h4 = MakeF2(R4.z, R4.w);
         T* dst = py + static_cast<int64_t>(2 * r) * g.wout + 4 * q;
-        store(dst, blend(l0, l1, l2, l3, E0, E1, E2, E3), blend(h0, h1, h2, h3, E0, E1, E2, E3));
-        store(dst + g.wout, blend(l1, l2, l3, l4, O0, O1, O2, O3), blend(h1, h2, h3, h4, O0, O1, O2, O3));
+        const int32_t valid = FULL ? 4 : min(4, g.wout - 4 * q);
+        store(dst, blend(l0, l1, l2, l3, E0, E1, E2, E3), blend(h0, h1, h2, h3, E0, E1, E2, E3), valid);
+        store(dst + g.wout, blend(l1, l2, l3, l4, O0, O1, O2, O3), blend(h1, h2, h3, h4, O0, O1, O2, O3), valid);
         if (r + 1 < rows) {
             const float4 R5 = col[5 * step];
             const F2 l5 = MakeF2(R5.x, R5.y), h5 = MakeF2(R5.z, R5.w);
-            store(dst + 2 * g.wout, blend(l1, l2, l3, l4, E0, E1, E2, E3), blend(h1, h2, h3, h4, E0, E1, E2, E3));
-            store(dst + 3 * g.wout, blend(l2, l3, l4, l5, O0, O1, O2, O3), blend(h2, h3, h4, h5, O0, O1, O2, O3));
+            store(dst + 2 * g.wout, blend(l1, l2, l3, l4, E0, E1, E2, E3), blend(h1, h2, h3, h4, E0, E1, E2, E3), valid);
+            store(dst + 3 * g.wout, blend(l2, l3, l4, l5, O0, O1, O2, O3), blend(h2, h3, h4, h5, O0, O1, O2, O3), valid);
         }
     }
 }
@@ -1307,14 +1325,15 @@ cudaError_t Bicubic2dFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, f
         return cudaGetLastError();
     }
     if (!nhwc && halfPixel && scaleH == 0.5f && scaleW == 0.5f && g.hout == 2 * g.hin && g.wout == 2 * g.win &&
-        g.win % 2 == 0 && g.win <= (1 << 20)) {
+        g.win <= (1 << 20)) {
         // exactly 2x: bands of source rows whose staged rows and horizontal sums take about 32 KB
-        const size_t slotBytes = (static_cast<size_t>(g.win) + 4 + g.wout) * sizeof(float);
+        const size_t pitchX = static_cast<size_t>(g.win) + 4 + (g.win & 1), pitchH = (static_cast<size_t>(g.wout) + 3) / 4 * 4;
+        const size_t slotBytes = (pitchX + pitchH) * sizeof(float);
         int32_t bh = static_cast<int32_t>(std::min<int64_t>(static_cast<int64_t>(32 * 1024 / slotBytes) - 4, g.hin));
         bh = std::max(bh, 1);
         const int32_t nb = (g.hin + bh - 1) / bh;
         bh = (g.hin + nb - 1) / nb;
-        const size_t smem = ((static_cast<size_t>(bh + 4) * (g.win + 4) + 3) / 4 * 4 + static_cast<size_t>(bh + 4) * g.wout) * sizeof(float);
+        const size_t smem = ((static_cast<size_t>(bh + 4) * pitchX + 3) / 4 * 4 + static_cast<size_t>(bh + 4) * pitchH) * sizeof(float);
         if (smem <= 48 * 1024 && planes * nb <= INT32_MAX) {
             X2FwdCoef cf;
             x2host::FwdCoeff(0.75f, cf.even);
@@ -1322,10 +1341,11 @@ cudaError_t Bicubic2dFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, f
             const int threads = 128; // measured at 56 x 56 planes: 101 us against 109 us with 256 (more blocks per SM overlap the three phases)
             OPSCV_DISPATCH_DT(dt, T, {
                 const int vecIn = (g.win % (16 / sizeof(T)) == 0 && Aligned(x, 16)) ? 1 : 0;
-                const int vecOut = Aligned(y, 4 * sizeof(T)) ? 1 : 0;
-                Bicubic2dFwdX2Kernel<T><<<static_cast<unsigned>(planes * nb), threads, smem, s>>>(
+                const int vecOut = (g.wout % 4 == 0 && Aligned(y, 4 * sizeof(T))) ? 4 : (Aligned(y, 2 * sizeof(T)) ? 2 : 1);
+                auto k = vecOut == 4 ? Bicubic2dFwdX2Kernel<T, true> : Bicubic2dFwdX2Kernel<T, false>;
+                k<<<static_cast<unsigned>(planes * nb), threads, smem, s>>>(
                     static_cast<const T*>(x), static_cast<T*>(y), g, bh, nb, vecIn, vecOut, cf,
-                    MakeFastDiv(static_cast<uint32_t>((g.wout / 4 + 1) / 2)), MakeFastDiv(static_cast<uint32_t>(g.wout / 4)));
+                    MakeFastDiv(static_cast<uint32_t>(((g.wout + 3) / 4 + 1) / 2)), MakeFastDiv(static_cast<uint32_t>((g.wout + 3) / 4)));
             });
             CountLaunch();
             return cudaGetLastError();

@@ -229,10 +229,10 @@ def test_bicubic_backward_at_2x_special_values(ops, oracle, dev):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", X2_SHAPES + [(1, 2, 1, 2), (2, 3, 1, 8), (1, 1, 70, 64), (2, 2, 33, 6)])
+@pytest.mark.parametrize("shape", X2_SHAPES + [(1, 2, 1, 2), (2, 3, 1, 8), (1, 1, 70, 64), (2, 2, 33, 6), (1, 2, 3, 1), (2, 1, 5, 21), (1, 3, 13, 25)])
 def test_bicubic_forward_at_2x(ops, oracle, dev, dtype, shape):
-    """The staged 2x forward (NCHW, half-pixel, even input width; odd widths run the general kernel): the oracle's
-    bits in fp32, borders by replicated rows and columns."""
+    """The staged 2x forward (NCHW, half-pixel; odd input widths leave the last group of four columns half used): the
+    oracle's bits in fp32, borders by replicated rows and columns."""
     n, c, hi, wi = shape
     x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(142)), dtype)
     y = ops.upsample_bicubic2d(x.to(dev), (2 * hi, 2 * wi), False)
