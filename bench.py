@@ -112,7 +112,7 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
     ws = ops.Workspace(dev) if ops is not None else None  # None: only the description is wanted
     # one workspace per operator for workloads whose operators are independent of each other: they may then run on
     # parallel branches of the step graph
-    wss = [ws] + [ops.Workspace(dev) for _ in range(3)] if ops is not None else [None] * 4
+    wss = [ws] + [ops.Workspace(dev) for _ in range(5)] if ops is not None else [None] * 6
 
     if name == "cfg2":
         n, c, hi, wi, ho, wo = 32 // batch_div, 256, 56, 56, 112, 112
@@ -235,6 +235,8 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
                 "y_bicubic": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
                 "gi_exact": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
                 "gi_bicubic": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
+                "y_bicubic_ac": torch.empty((n, c, ho, wo), dtype=dt, device=gen.device),
+                "gi_bicubic_ac": torch.empty((n, c, hi, wi), dtype=dt, device=gen.device),
             }
         small, big = n * c * hi * wi * 2, n * c * ho * wo * 2
         oplist = [
@@ -250,9 +252,18 @@ def make_workload(name, ops, torch, dev, batch_div=1, shard=None):
             Op("UpsampleBicubic2dBackward", lambda b: ops.upsample_bicubic2d_backward(
                 b["go"], (ho, wo), (n, c, hi, wi), False, out=b["gi_bicubic"], workspace=wss[3]),
                small + big, n * ho * wo, ["go"], ["gi_bicubic"]),
+            # the same tensors with align_corners=true: the scale is 55 / 111, so these two run the general kernels
+            # (the calls above are exactly 2x and run the kernels of that scale)
+            Op("UpsampleBicubic2d[align_corners]", lambda b: ops.upsample_bicubic2d(
+                b["x"], (ho, wo), True, out=b["y_bicubic_ac"], workspace=wss[4]),
+               small + big, n * ho * wo, ["x"], ["y_bicubic_ac"]),
+            Op("UpsampleBicubic2dBackward[align_corners]", lambda b: ops.upsample_bicubic2d_backward(
+                b["go"], (ho, wo), (n, c, hi, wi), True, out=b["gi_bicubic_ac"], workspace=wss[5]),
+               small + big, n * ho * wo, ["go"], ["gi_bicubic_ac"]),
         ]
         cfg = {"workload": "operators next to the path at the FPN shapes: UpsampleNearestExact2d + UpsampleBicubic2d "
-                           f"forward and backward, fp16 NCHW N={n} C=256 56x56 -> 112x112, align_corners=false",
+                           f"forward and backward, fp16 NCHW N={n} C=256 56x56 -> 112x112, align_corners=false; "
+                           "UpsampleBicubic2d again with align_corners=true",
                "dtype": "f16"}
         return buffers, oplist, cfg
 
@@ -553,6 +564,8 @@ def cpu_baseline(workload, budget_s=12.0, torch_budget_s=6.0):
             oracle.bicubic2d_fwd(x, (112, 112), False)
             oracle.nearest_exact2d_bwd(go, (56, 56))
             oracle.bicubic2d_bwd(go, (56, 56), False, definition="dispatch")
+            oracle.bicubic2d_fwd(x, (112, 112), True)
+            oracle.bicubic2d_bwd(go, (56, 56), True, definition="dispatch")
         xt, got = torch.from_numpy(x), torch.from_numpy(go)
 
         def run_torch():
@@ -560,8 +573,10 @@ def cpu_baseline(workload, budget_s=12.0, torch_budget_s=6.0):
             F.interpolate(xt, size=(112, 112), mode="bicubic", align_corners=False)
             torch.ops.aten._upsample_nearest_exact2d_backward(got, [112, 112], [n, c, 56, 56], None, None)
             torch.ops.aten.upsample_bicubic2d_backward(got, [112, 112], [n, c, 56, 56], False, None, None)
-        algo = 4 * (x.size + go.size) * 2
-        sample = f"N={n} of 32 images (C={c}), all four operators, fp32 arithmetic"
+            F.interpolate(xt, size=(112, 112), mode="bicubic", align_corners=True)
+            torch.ops.aten.upsample_bicubic2d_backward(got, [112, 112], [n, c, 56, 56], True, None, None)
+        algo = 6 * (x.size + go.size) * 2
+        sample = f"N={n} of 32 images (C={c}), all six operators, fp32 arithmetic"
     elif workload == "adj3":
         x = rng.random((1, 3, 1024, 1024), dtype=np.float32)
         go = rng.standard_normal((1, 3, 224, 224)).astype(np.float32)
