@@ -249,3 +249,19 @@ def test_bicubic_forward_at_2x(ops, oracle, dev, dtype, shape):
     assert np.array_equal(np.isnan(ys), np.isnan(ref)) and np.array_equal(np.isinf(ys), np.isinf(ref))
     fin = np.isfinite(ref)
     assert np.array_equal(ys[fin], ref[fin])
+
+
+def test_bicubic_2x_random_extents(ops, oracle, dev):
+    """Random extents at exactly 2x through both staged kernels (fp32: the oracle's bits): band counts, short last
+    bands, odd and even widths, widths past one block, the fall-back to the general kernels for very wide rows."""
+    rng = np.random.default_rng(20260)
+    shapes = [(int(rng.integers(1, 3)), int(rng.integers(1, 4)), int(rng.integers(1, 90)), int(rng.integers(1, 200)))
+              for _ in range(24)] + [(1, 1, 3, 800), (1, 1, 130, 7), (1, 2, 95, 96)]
+    for i, (n, c, hi, wi) in enumerate(shapes):
+        x = torch.randn((n, c, hi, wi), generator=gen(300 + i))
+        g = torch.randn((n, c, 2 * hi, 2 * wi), generator=gen(400 + i))
+        y = ops.upsample_bicubic2d(x.to(dev), (2 * hi, 2 * wi), False)
+        assert np.array_equal(y.cpu().numpy(), oracle.bicubic2d_fwd(x.numpy(), (2 * hi, 2 * wi), False)), (n, c, hi, wi)
+        gi = ops.upsample_bicubic2d_backward(g.to(dev), (2 * hi, 2 * wi), (n, c, hi, wi), False)
+        assert np.array_equal(gi.cpu().numpy(),
+                              oracle.bicubic2d_bwd(g.numpy(), (hi, wi), False, definition="gather")), (n, c, hi, wi)
