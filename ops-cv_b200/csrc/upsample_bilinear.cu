@@ -1151,9 +1151,19 @@ __global__ void __launch_bounds__(kThreads)
                 LoadPackLdg<T, V>(xl + r * rowStride, l);
                 LoadPackLdg<T, V>(xr + r * rowStride, rr);
             }
+            if constexpr (V % 2 == 0) {
+                // two channels per instruction; each half keeps the scalar form's products and its one rounded sum
+                const F2 DX = MakeF2(dx, dx), DX1 = MakeF2(dx1, dx1);
 #pragma unroll
-            for (int k = 0; k < V; ++k) {
-                dst[k] = FUSE ? fmaf(dx, rr[k], Mul(dx1, l[k])) : Add(Mul(dx1, l[k]), Mul(dx, rr[k]));
+                for (int k = 0; k < V; k += 2) {
+                    const F2 left = Mul2(DX1, MakeF2(l[k], l[k + 1])), right = MakeF2(rr[k], rr[k + 1]);
+                    SplitF2(FUSE ? Fma2(DX, right, left) : AddProduct2(Mul2(DX, right), left), dst[k], dst[k + 1]);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    dst[k] = FUSE ? fmaf(dx, rr[k], Mul(dx1, l[k])) : Add(Mul(dx1, l[k]), Mul(dx, rr[k]));
+                }
             }
         };
         for (int32_t h = h0; h < h1; ++h) {
@@ -1182,9 +1192,18 @@ __global__ void __launch_bounds__(kThreads)
                 ib = hh;
             }
             float out[V];
+            if constexpr (V % 2 == 0) {
+                const F2 DY = MakeF2(dy, dy), DY1 = MakeF2(dy1, dy1);
 #pragma unroll
-            for (int k = 0; k < V; ++k) {
-                out[k] = Add(Mul(dy1, a[k]), Mul(dy, b[k]));
+                for (int k = 0; k < V; k += 2) {
+                    SplitF2(AddProduct2(Mul2(DY, MakeF2(b[k], b[k + 1])), Mul2(DY1, MakeF2(a[k], a[k + 1]))), out[k],
+                            out[k + 1]);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    out[k] = Add(Mul(dy1, a[k]), Mul(dy, b[k]));
+                }
             }
             StorePack<T, V>(yp, out);
             yp += outStride;
