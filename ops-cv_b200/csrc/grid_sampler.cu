@@ -268,9 +268,11 @@ __global__ void __launch_bounds__(kStageThreads, NV == 1 ? 3 : 1)
 #pragma unroll
                 for (int v = 0; v < NV; ++v) {
                     const Vec q = tp[v];
+                    float qv[LV];
+                    UnpackToF<T, LV>(q, qv);
 #pragma unroll
                     for (int k = 0; k < LV; ++k) {
-                        out[v * LV + k] = Add(out[v * LV + k], Mul(DType<T>::ToF(q.v[k]), wt[tap]));
+                        out[v * LV + k] = Add(out[v * LV + k], Mul(qv[k], wt[tap]));
                     }
                 }
             }

@@ -516,9 +516,11 @@ __global__ void __launch_bounds__(1024)
         // halve their count. Four pairs per trip are loaded before the first use; additions stay in list order.
         auto add = [&](int32_t sample, float wgt) {
             const Vec v = tile[sample];
+            float vf[CG];
+            UnpackToF<T, CG>(v, vf);
 #pragma unroll
             for (int k = 0; k < CG; ++k) {
-                acc[k] = Add(acc[k], Mul(wgt, DType<T>::ToF(v.v[k])));
+                acc[k] = Add(acc[k], Mul(wgt, vf[k]));
             }
         };
         int32_t e = a;

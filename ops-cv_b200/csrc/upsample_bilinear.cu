@@ -395,10 +395,11 @@ __global__ void __launch_bounds__(kW2Threads, 5)
                 CpAsyncWait<kW2QueueDepth - 1>();
                 const int32_t slot = (r & (kW2QueueDepth - 1)) * nthreads + tid;
                 const uint4 raw = qMid[slot];
-                const T* me = reinterpret_cast<const T*>(&raw);
+                float mid[VI];
+                UnpackToF<T, VI>(reinterpret_cast<const Pack<T, VI>&>(raw), mid);
 #pragma unroll
                 for (int k = 0; k < VI; ++k) {
-                    v[k + 1] = DType<T>::ToF(me[k]);
+                    v[k + 1] = mid[k];
                 }
                 v[0] = v[1];
                 v[VI + 1] = v[VI];
@@ -1138,13 +1139,8 @@ __global__ void __launch_bounds__(kThreads)
                 CpAsyncWait<kFwdQueueDepth - 1>();
                 const int32_t slot = (r & (kFwdQueueDepth - 1)) * blockDim.x + threadIdx.x;
                 const uint4 rawL = qL[slot], rawR = qR[slot];
-                const T* pl = reinterpret_cast<const T*>(&rawL);
-                const T* pr = reinterpret_cast<const T*>(&rawR);
-#pragma unroll
-                for (int k = 0; k < V; ++k) {
-                    l[k] = DType<T>::ToF(pl[k]);
-                    rr[k] = DType<T>::ToF(pr[k]);
-                }
+                UnpackToF<T, V>(reinterpret_cast<const Pack<T, V>&>(rawL), l);
+                UnpackToF<T, V>(reinterpret_cast<const Pack<T, V>&>(rawR), rr);
                 ++nextRow;
                 issue();
             } else {
