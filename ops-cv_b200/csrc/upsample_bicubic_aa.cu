@@ -390,15 +390,22 @@ __global__ void __launch_bounds__(MAXT, (VC == 4 && !BULK) ? 4 : (BULK ? 1 : 2))
                         if (l * groupSpan + c < win) {
                             v = *reinterpret_cast<const Vec*>(srow + l * groupSpan + c);
                         }
+                        float part[LV];
+                        UnpackToF<T, LV>(v, part);
 #pragma unroll
                         for (int k = 0; k < LV; ++k) {
-                            xv[l * LV + k] = DType<T>::ToF(v.v[k]);
+                            xv[l * LV + k] = part[k];
                         }
                     }
                 } else {
 #pragma unroll
-                    for (int k = 0; k < VC; ++k) {
-                        xv[k] = DType<T>::ToF(q[f][k / LV].v[k % LV]);
+                    for (int l = 0; l < NL; ++l) {
+                        float part[LV];
+                        UnpackToF<T, LV>(q[f][l], part);
+#pragma unroll
+                        for (int k = 0; k < LV; ++k) {
+                            xv[l * LV + k] = part[k];
+                        }
                     }
                 }
 #pragma unroll
