@@ -118,6 +118,9 @@ struct BilinearPlan {
     // forward, 16-bit tensors: 24 minus the most significant bits any column weight or its complement has; a value
     // of T with at most this many significand bits times a weight is exact in fp32 (0: unknown, never assume it)
     int32_t weightSlack;
+    // forward NHWC: the row table is the 2x pattern (row 0 from input row 0 alone, rows 2i + 1 and 2i + 2 from input rows
+    // i and i + 1, the last row from the last input row alone), so the walk needs no row indices from the table
+    bool rowsX2;
     // kX2 backward with periodicW: the four column weights shared by every grad_input column but the first and last
     float bw[4];
     int32_t rowStart1; // kX2 backward: first grads row feeding grad_input row 1 (0 or 1; every other row follows 2y-1)

@@ -1078,7 +1078,10 @@ __global__ void __launch_bounds__(kW2Threads, 5)
 // cp.async queue kFwdQueueDepth rows ahead; without it the walk exposes one memory latency per new input row.
 // FUSE (16-bit T): the host has checked that every column weight times any value of T is exact in fp32, so the
 // horizontal interpolation uses one fused multiply-add: same bits, one instruction fewer.
-template <typename T, int V, bool QUEUE, bool FUSE = false>
+// X2ROWS (with QUEUE, one row chunk): the host has checked that the row table is the 2x pattern; the walk then takes
+// one new input row per two output rows in a straight line (no row indices, no comparisons, no copies between the
+// two row buffers: the loop body is written twice with the buffers trading places). Same expressions, same bits.
+template <typename T, int V, bool QUEUE, bool FUSE = false, bool X2ROWS = false>
 __global__ void __launch_bounds__(kThreads)
     BilinearFwdNHWCKernel(const T* __restrict__ x, T* __restrict__ y, int32_t c, int32_t hin, int32_t win,
                           int32_t hout, int32_t wout, LerpAxis th, LerpAxis tw, int32_t rows, int32_t rowChunks,
@@ -1097,7 +1100,14 @@ __global__ void __launch_bounds__(kThreads)
         const int32_t g = static_cast<int32_t>(wk - col * groups);
         const int64_t n = col / wout;
         const int32_t w = static_cast<int32_t>(col - n * wout);
-        const int32_t h0 = static_cast<int32_t>(chunk) * rows, h1 = min(hout, h0 + rows);
+        int32_t h0 = static_cast<int32_t>(chunk) * rows;
+        const int32_t h1 = min(hout, h0 + rows);
+        // X2ROWS: `rows` counts steps (a step = one new input row = two output rows); this walker takes the steps
+        // [sA, sB), with output row 0 if it starts at step 0 and the last output row if it ends at the last step
+        const int32_t sA = static_cast<int32_t>(chunk) * rows, sB = min(sA + rows, hin - 1);
+        if constexpr (X2ROWS) {
+            h0 = sA == 0 ? 0 : 2 * sA + 1;
+        }
         const int32_t wl = __ldg(tw.lo + w), wh = __ldg(tw.hi + w);
         const float dx = __ldg(tw.delta + w), dx1 = Sub(1.0f, dx);
         const int64_t rowStride = static_cast<int64_t>(win) * c;
@@ -1108,8 +1118,8 @@ __global__ void __launch_bounds__(kThreads)
         float a[V], b[V];
         int32_t ia = -1, ib = -1;
         // QUEUE: rows lo[h0] .. hi[h1-1] are needed in increasing order
-        const int32_t lastRow = QUEUE ? __ldg(th.hi + h1 - 1) : 0;
-        int32_t nextRow = QUEUE ? __ldg(th.lo + h0) : 0, issued = nextRow;
+        const int32_t lastRow = X2ROWS ? sB : (QUEUE ? __ldg(th.hi + h1 - 1) : 0);
+        int32_t nextRow = X2ROWS ? sA : (QUEUE ? __ldg(th.lo + h0) : 0), issued = nextRow;
         const T* issueL = xl + nextRow * rowStride; // row `issued` of the left / right pixel
         const T* issueR = xr + nextRow * rowStride;
         auto issue = [&]() {
@@ -1162,6 +1172,52 @@ __global__ void __launch_bounds__(kThreads)
                 }
             }
         };
+        if constexpr (X2ROWS && QUEUE) {
+            auto emit = [&](const float (&up)[V], const float (&dn)[V], int32_t h) {
+                const float dy = __ldg(th.delta + h), dy1 = Sub(1.0f, dy);
+                float out[V];
+                if constexpr (V % 2 == 0) {
+                    const F2 DY = MakeF2(dy, dy), DY1 = MakeF2(dy1, dy1);
+#pragma unroll
+                    for (int k = 0; k < V; k += 2) {
+                        SplitF2(AddProduct2(Mul2(DY, MakeF2(dn[k], dn[k + 1])), Mul2(DY1, MakeF2(up[k], up[k + 1]))),
+                                out[k], out[k + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        out[k] = Add(Mul(dy1, up[k]), Mul(dy, dn[k]));
+                    }
+                }
+                StorePack<T, V>(yp, out);
+                yp += outStride;
+            };
+            hrow(sA, a);
+            if (sA == 0) {
+                emit(a, a, 0);
+            }
+            int32_t i = sA;
+            for (; i + 2 <= sB; i += 2) {
+                hrow(i + 1, b);
+                emit(a, b, 2 * i + 1);
+                emit(a, b, 2 * i + 2);
+                hrow(i + 2, a);
+                emit(b, a, 2 * i + 3);
+                emit(b, a, 2 * i + 4);
+            }
+            if (i < sB) {
+                hrow(i + 1, b);
+                emit(a, b, 2 * i + 1);
+                emit(a, b, 2 * i + 2);
+                if (sB == hin - 1) {
+                    emit(b, b, hout - 1);
+                }
+            } else if (sB == hin - 1) {
+                emit(a, a, hout - 1);
+            }
+            CpAsyncWait<0>();
+            continue;
+        }
         for (int32_t h = h0; h < h1; ++h) {
             const int32_t hl = __ldg(th.lo + h), hh = __ldg(th.hi + h);
             const float dy = __ldg(th.delta + h), dy1 = Sub(1.0f, dy);
@@ -1632,6 +1688,14 @@ BilinearPlan MakeBilinearFwdPlan(Dt dt, Layout lay, Shape4 sh, AxisGeom gh, Axis
             }
             plan.weightSlack = 24 - bits;
         }
+        if (sh.hout == 2 * sh.hin) {
+            const host::Lerp tH = host::LerpTable(sh.hin, sh.hout, gh.scale, halfPixel, 0);
+            bool x2 = tH.lo[0] == 0 && tH.hi[0] == 0 && tH.lo[sh.hout - 1] == sh.hin - 1 && tH.hi[sh.hout - 1] == sh.hin - 1;
+            for (int32_t i = 0; i + 1 < sh.hin && x2; ++i) {
+                x2 = tH.lo[2 * i + 1] == i && tH.hi[2 * i + 1] == i + 1 && tH.lo[2 * i + 2] == i && tH.hi[2 * i + 2] == i + 1;
+            }
+            plan.rowsX2 = x2;
+        }
         return plan;
     }
     const int es = DtSize(dt);
@@ -1936,17 +2000,30 @@ cudaError_t BilinearFwd(Dt dt, Layout lay, const void* x, void* y, Shape4 sh, Le
                         if (Aligned(x, 16)) {
                             const size_t qBytes = static_cast<size_t>(kFwdQueueDepth) * kThreads * 32;
                             const int mant = std::is_same<T, __half>::value ? 11 : 8; // significand bits of T
-                            auto launch = [&](auto kernel) {
-                                kernel<<<blocks, kThreads, qBytes, s>>>(
+                            const bool x2Rows = plan.rowsX2 && sh.hout == 2 * sh.hin;
+                            // the 2x walk is cut into chunks of steps (one new input row each) instead of output rows
+                            const int32_t steps = std::max(sh.hin - 1, 1);
+                            const int32_t stepRows = static_cast<int32_t>(CeilDiv(steps, std::min<int64_t>(chunks, steps)));
+                            const int32_t stepChunks = static_cast<int32_t>(CeilDiv(steps, stepRows));
+                            auto launch = [&](auto kernel, bool stepped) {
+                                const int32_t r = stepped ? stepRows : rows, rc = stepped ? stepChunks : rowChunks;
+                                const unsigned nb = static_cast<unsigned>(std::min<int64_t>(CeilDiv(walkers * rc, kThreads), 0x7fffffff));
+                                kernel<<<nb, kThreads, qBytes, s>>>(
                                     static_cast<const T*>(x), static_cast<T*>(y), static_cast<int32_t>(sh.c), sh.hin,
-                                    sh.win, sh.hout, sh.wout, th, tw, rows, rowChunks, walkers);
+                                    sh.win, sh.hout, sh.wout, th, tw, r, rc, walkers);
                             };
                             if (sizeof(T) == 2 && mant <= plan.weightSlack) {
                                 if constexpr (sizeof(T) == 2) {
-                                    launch(BilinearFwdNHWCKernel<T, V, true, true>);
+                                    if (x2Rows) {
+                                        launch(BilinearFwdNHWCKernel<T, V, true, true, true>, true);
+                                    } else {
+                                        launch(BilinearFwdNHWCKernel<T, V, true, true>, false);
+                                    }
                                 }
+                            } else if (x2Rows) {
+                                launch(BilinearFwdNHWCKernel<T, V, true, false, true>, true);
                             } else {
-                                launch(BilinearFwdNHWCKernel<T, V, true>);
+                                launch(BilinearFwdNHWCKernel<T, V, true>, false);
                             }
                             queued = true;
                         }

@@ -173,6 +173,36 @@ def test_bilinear_forward(ops, oracle, dev, dtype, fmt, align, shape):
     check(y, oracle.bilinear2d_fwd(x32, (ho, wo), align, fmt=f), dtype, exact=True)  # same operation order
 
 
+NHWC_X2_SHAPES = [
+    # (N, C, Hin, Win): NHWC, output (2 Hin, 2 Win); C a multiple of 8 so that 16-bit tensors take 16-byte vectors
+    (1, 8, 1, 1),
+    (2, 8, 2, 3),
+    (1, 16, 3, 5),
+    (1, 8, 8, 8),
+    (2, 24, 33, 7),    # an odd number of steps, several row chunks
+    (1, 8, 130, 2),    # a long walk cut into chunks of steps
+    (64, 32, 6, 40),   # enough walkers for one chunk per column
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", NHWC_X2_SHAPES)
+def test_bilinear_forward_nhwc_2x_walk(ops, oracle, dev, dtype, shape):
+    """The straight-line 2x row walk of the NHWC kernel (with and without user scales): the oracle's bits."""
+    n, c, hi, wi = shape
+    x, x32 = quant(torch.randn((n, c, hi, wi), generator=gen(160)), dtype)
+    xl, x32l = x.permute(0, 2, 3, 1).contiguous(), nhwc(x32)
+    for scales in ((0.0, 0.0), (2.0, 2.0)):
+        y = ops.upsample_bilinear2d(xl.to(dev), (2 * hi, 2 * wi), False, "NHWC", scales=scales)
+        check(y, oracle.bilinear2d_fwd(x32l, (2 * hi, 2 * wi), False, scales, fmt=oracle.NHWC), dtype, exact=True)
+    xs = x32l.copy()
+    xs[0, 0, 0, 0] = np.inf
+    xs[-1, -1, -1, -1] = np.nan
+    ys = ops.upsample_bilinear2d(torch.from_numpy(xs).to(dtype).to(dev), (2 * hi, 2 * wi), False, "NHWC").float().cpu().numpy()
+    ref = oracle.bilinear2d_fwd(xs, (2 * hi, 2 * wi), False, fmt=oracle.NHWC)
+    assert np.array_equal(np.isnan(ys), np.isnan(ref)) and np.array_equal(np.isinf(ys), np.isinf(ref))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("fmt", ["NCHW", "NHWC"])
 @pytest.mark.parametrize("align", [False, True])
