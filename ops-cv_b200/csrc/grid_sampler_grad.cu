@@ -666,9 +666,10 @@ __global__ void __launch_bounds__(1024)
                 return;
             }
             const int32_t d = o + off;
-            Vec v{};
+            float xf[CG] = {};
             if (WANT_GRID) {
-                v = tile[d];
+                const Vec v = tile[d];
+                UnpackToF<T, CG>(v, xf);
             }
 #pragma unroll
             for (int k = 0; k < CG; ++k) {
@@ -677,7 +678,7 @@ __global__ void __launch_bounds__(1024)
                         atomicAdd(acc + k * inPlane + d, Mul(w, gv[k]));
                     }
                     if (WANT_GRID) {
-                        const float xv = DType<T>::ToF(v.v[k]);
+                        const float xv = xf[k];
                         const float tx = Mul(Mul(xv, fx), gv[k]), ty = Mul(Mul(xv, fy), gv[k]);
                         gix = negX ? Sub(gix, tx) : Add(gix, tx);
                         giy = negY ? Sub(giy, ty) : Add(giy, ty);
