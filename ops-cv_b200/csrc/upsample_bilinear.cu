@@ -1018,10 +1018,13 @@ __global__ void __launch_bounds__(kW2Threads, 5)
             __syncwarp(warpMask); // all lanes have read before any slot is refilled
             issue(pm, plr);
             float v[VG + 2]; // grads columns j0-1 .. j0+8
-            const TIn* me = reinterpret_cast<const TIn*>(mid);
+            {
+                float all[VG];
+                UnpackToF<TIn, VG>(*reinterpret_cast<const Pack<TIn, VG>*>(mid), all);
 #pragma unroll
-            for (int k = 0; k < VG; ++k) {
-                v[k + 1] = DType<TIn>::ToF(me[k]);
+                for (int k = 0; k < VG; ++k) {
+                    v[k + 1] = all[k];
+                }
             }
             // the neighbour words are not written (and not read as numbers) where the row ends
             v[0] = hasLeft ? DType<TIn>::ToF(reinterpret_cast<const TIn*>(&lr.x)[HE - 1]) : 0.0f;
